@@ -1,0 +1,204 @@
+"""Architecture description of the decoder families the framework trains and serves.
+
+One dataclass covers Llama / Mistral / Qwen2 / Qwen2.5 / Qwen3 dense models and Qwen3-MoE style sparse
+models; it converts from and to HF ``config.json`` dictionaries so checkpoints stay interchangeable.
+Reference: model families handled in ``verl/models/transformers/*`` and ``verl/utils/flops_counter.py``.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any, Optional
+
+__all__ = ["ModelConfig", "PRESETS", "get_preset"]
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen2"
+    vocab_size: int = 512
+    hidden_size: int = 128
+    intermediate_size: int = 256
+    num_hidden_layers: int = 2
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 2
+    head_dim: Optional[int] = None
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    qk_norm: bool = False
+    # mixture of experts (0 experts = dense MLP)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    # tokens
+    bos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None
+    pad_token_id: Optional[int] = None
+    initializer_range: float = 0.02
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.model_type in ("qwen2",) and "attention_bias" not in self.extra.get("_explicit", ()):
+            self.attention_bias = True
+        if self.model_type in ("qwen3", "qwen3_moe"):
+            self.qk_norm = True
+
+    # ------------------------------------------------------------------ derived sizes
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def qkv_size(self) -> int:
+        return self.q_size + 2 * self.kv_size
+
+    def num_parameters(self, value_head: bool = False) -> int:
+        h, v = self.hidden_size, self.vocab_size
+        per_layer = 2 * h + self.qkv_size * h + self.q_size * h
+        if self.attention_bias:
+            per_layer += self.qkv_size
+        if self.qk_norm:
+            per_layer += 2 * self.head_dim
+        if self.is_moe:
+            per_layer += self.num_experts * h + self.num_experts * 3 * h * self.moe_intermediate_size
+        else:
+            per_layer += 3 * h * self.intermediate_size
+        total = v * h + self.num_hidden_layers * per_layer + h
+        if value_head:
+            total += 8 * h
+        elif not self.tie_word_embeddings:
+            total += v * h
+        return total
+
+    # ------------------------------------------------------------------ HF interchange
+    @classmethod
+    def from_hf_dict(cls, d: dict[str, Any]) -> "ModelConfig":
+        mt = d.get("model_type", "llama")
+        kw = dict(
+            model_type=mt,
+            vocab_size=d["vocab_size"],
+            hidden_size=d["hidden_size"],
+            intermediate_size=d.get("intermediate_size", 0),
+            num_hidden_layers=d["num_hidden_layers"],
+            num_attention_heads=d["num_attention_heads"],
+            num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+            head_dim=d.get("head_dim"),
+            rms_norm_eps=d.get("rms_norm_eps", 1e-6),
+            rope_theta=float(d.get("rope_theta", 10000.0)),
+            max_position_embeddings=d.get("max_position_embeddings", 32768),
+            tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
+            attention_bias=bool(d.get("attention_bias", mt == "qwen2")),
+            num_experts=d.get("num_experts", d.get("num_local_experts", 0)) or 0,
+            num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            bos_token_id=d.get("bos_token_id"),
+            eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
+            pad_token_id=d.get("pad_token_id"),
+            initializer_range=d.get("initializer_range", 0.02),
+        )
+        cfg = cls(**kw, extra={"_explicit": ("attention_bias",)})
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_hf_dict(json.load(f))
+
+    def to_hf_dict(self) -> dict[str, Any]:
+        arch = {
+            "qwen2": "Qwen2ForCausalLM",
+            "qwen3": "Qwen3ForCausalLM",
+            "qwen3_moe": "Qwen3MoeForCausalLM",
+            "llama": "LlamaForCausalLM",
+            "mistral": "MistralForCausalLM",
+        }.get(self.model_type, "LlamaForCausalLM")
+        d = {
+            "architectures": [arch],
+            "model_type": self.model_type,
+            "vocab_size": self.vocab_size,
+            "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size,
+            "num_hidden_layers": self.num_hidden_layers,
+            "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_key_value_heads,
+            "head_dim": self.head_dim,
+            "rms_norm_eps": self.rms_norm_eps,
+            "rope_theta": self.rope_theta,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": self.attention_bias,
+            "hidden_act": "silu",
+            "torch_dtype": "bfloat16",
+            "bos_token_id": self.bos_token_id,
+            "eos_token_id": self.eos_token_id,
+            "pad_token_id": self.pad_token_id,
+            "initializer_range": self.initializer_range,
+        }
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+        return d
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.to_hf_dict(), f, indent=2)
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+
+PRESETS: dict[str, ModelConfig] = {
+    # BASELINE config 1 (CPU/gloo oracle)
+    "tiny-qwen2": ModelConfig(model_type="qwen2", vocab_size=512, hidden_size=128, intermediate_size=256,
+                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e4,
+                              eos_token_id=2, pad_token_id=0),
+    "qwen2.5-0.5b": ModelConfig(model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
+                                num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2,
+                                rope_theta=1e6, tie_word_embeddings=True, eos_token_id=151645, pad_token_id=151643),
+    "qwen2.5-7b": ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                              num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
+                              eos_token_id=151645, pad_token_id=151643),
+    "llama-3.1-8b": ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                                num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                                rope_theta=5e5, rms_norm_eps=1e-5, eos_token_id=128001, pad_token_id=128001),
+    "qwen3-30b-a3b": ModelConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                                 num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                                 rope_theta=1e6, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
+                                 eos_token_id=151645, pad_token_id=151643),
+    "tiny-moe": ModelConfig(model_type="qwen3_moe", vocab_size=512, hidden_size=128, intermediate_size=256,
+                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                            num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, eos_token_id=2,
+                            pad_token_id=0),
+    "tiny-llama": ModelConfig(model_type="llama", vocab_size=512, hidden_size=128, intermediate_size=256,
+                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, eos_token_id=2,
+                              pad_token_id=0),
+}
+
+
+def get_preset(name: str) -> ModelConfig:
+    import copy
+
+    key = name.lower().replace("_", "-")
+    for k, v in PRESETS.items():
+        if k == key or key.endswith(k) or k in key:
+            return copy.deepcopy(v)
+    raise KeyError(f"unknown model preset '{name}' (known: {sorted(PRESETS)})")

@@ -1,0 +1,405 @@
+"""Decoder-only transformer with hand-scheduled forward and backward passes.
+
+The model runs on packed ("remove-padding") token streams: ``input_ids`` / ``positions`` are 1-D over the
+concatenation of all sequences of a micro-batch and ``cu_seqlens`` marks the boundaries, so no FLOP is
+spent on padding.  The backward pass is written out explicitly instead of being traced by autograd:
+
+* the set of saved activations is chosen by hand (layer input, rotated QKV, attention output + LSE,
+  post-attention residual, gate/up pre-activation); norms and SwiGLU outputs are recomputed because
+  they are memory-bound and cheaper to redo than to keep in HBM;
+* ``recompute="full"`` keeps only each layer's input pair and replays the layer in backward;
+* weight gradients are accumulated by the wgrad GEMM straight into the fp32 ``main_grad`` buffer;
+* per-layer hooks let a sharded runtime gather parameters before a layer and reduce gradients after it.
+
+The same code runs in fp32 on CPU (through the functional fallbacks), which is what the CPU/gloo
+configuration and the numerics tests use.  Reference semantics: HF Llama/Qwen2/Qwen3(-MoE) modelling as
+used by ``verl/workers/engine/fsdp/transformer_impl.py:1122-1564`` (packed inputs, labels rolled by one,
+log-prob / entropy from the LM head).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+import torch
+
+from ..ops import functional as F
+from .config import ModelConfig
+from .weights import FlatParams
+
+__all__ = ["PackedBatch", "DecoderModel"]
+
+
+@dataclass
+class PackedBatch:
+    """A micro-batch of packed sequences."""
+
+    input_ids: torch.Tensor  # [T] int64
+    positions: torch.Tensor  # [T] int32/int64
+    cu_seqlens: torch.Tensor  # [B+1] int32 (device) ...
+    max_seqlen: int
+    cu_seqlens_cpu: Optional[torch.Tensor] = None  # host copy (avoids syncs in fallbacks)
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.input_ids.shape[0])
+
+    @classmethod
+    def from_lengths(cls, input_ids: torch.Tensor, lengths: list[int], device=None) -> "PackedBatch":
+        device = device if device is not None else input_ids.device
+        cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+        cu[1:] = torch.cumsum(torch.tensor(lengths, dtype=torch.int32), 0)
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.int32)
+        return cls(input_ids=input_ids.to(device), positions=pos.to(device), cu_seqlens=cu.to(device),
+                   max_seqlen=max(lengths) if lengths else 0, cu_seqlens_cpu=cu)
+
+
+class _Anchor(torch.autograd.Function):
+    """Autograd bridge: forward returns the model outputs, backward runs the hand-written backward."""
+
+    @staticmethod
+    def forward(ctx, anchor, model, state, *outs):
+        ctx.model = model
+        ctx.state = state
+        return tuple(o.detach() for o in outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.model._backward(ctx.state, grads)
+        ctx.state = None
+        dev = ctx.model.device
+        ctx.model = None
+        return (torch.zeros((), device=dev), None, None) + tuple(None for _ in grads)
+
+
+class DecoderModel:
+    def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
+                 pre_layer_hook: Optional[Callable[[int, str], None]] = None,
+                 post_layer_backward_hook: Optional[Callable[[int], None]] = None):
+        assert recompute in ("none", "full")
+        self.cfg = cfg
+        self.params = params
+        self.recompute = recompute
+        self.pre_layer_hook = pre_layer_hook
+        self.post_layer_backward_hook = post_layer_backward_hook
+        self.device = params.flat.device
+        self._rope_len = 0
+        self._cos = self._sin = None
+        self._ensure_rope(max_positions or min(cfg.max_position_embeddings, 8192))
+        self._anchor = torch.zeros((), device=self.device, requires_grad=True)
+
+    # ------------------------------------------------------------------------------------ helpers
+    def _ensure_rope(self, n: int) -> None:
+        if n > self._rope_len:
+            self._rope_len = int(2 ** math.ceil(math.log2(max(n, 16))))
+            self._cos, self._sin = F.rope_table(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, self.device)
+
+    def _wgrad(self, w: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> None:
+        mg = getattr(w, "main_grad", None)
+        if mg is None:
+            return
+        F.gemm(dy, x, out=mg, a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+
+    @staticmethod
+    def _cu_cpu(batch: PackedBatch) -> torch.Tensor:
+        if batch.cu_seqlens_cpu is None:
+            batch.cu_seqlens_cpu = batch.cu_seqlens.cpu()
+        return batch.cu_seqlens_cpu
+
+    # ------------------------------------------------------------------------------------ attention block
+    def _attn_fwd(self, W, h1, batch: PackedBatch, S: Optional[dict]):
+        cfg = self.cfg
+        T = h1.shape[0]
+        nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
+        qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+        q = qkv[:, :Q].view(T, nh, hd)
+        k = qkv[:, Q : Q + KV].view(T, nkv, hd)
+        v = qkv[:, Q + KV :].view(T, nkv, hd)
+        if cfg.qk_norm:
+            qp, kp = q.reshape(T * nh, hd).contiguous(), k.reshape(T * nkv, hd).contiguous()
+            qn, _, rq = F.rms_norm(qp, W["self_attn.q_norm.weight"], cfg.rms_norm_eps)
+            kn, _, rk = F.rms_norm(kp, W["self_attn.k_norm.weight"], cfg.rms_norm_eps)
+            q.copy_(qn.view(T, nh, hd))
+            k.copy_(kn.view(T, nkv, hd))
+            if S is not None:
+                S.update(q_pre=qp, k_pre=kp, rstd_q=rq, rstd_k=rk)
+        F.apply_rope_(q, batch.positions, self._cos, self._sin)
+        F.apply_rope_(k, batch.positions, self._cos, self._sin)
+        cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["fwd"] is not None else self._cu_cpu(batch)
+        attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
+        attn2 = attn.reshape(T, Q)
+        if S is not None:
+            S.update(qkv=qkv, attn=attn2, lse=lse)
+        return F.gemm(attn2, W["self_attn.o_proj.weight"])
+
+    def _attn_bwd(self, W, g_o, h1, batch: PackedBatch, S: dict):
+        cfg = self.cfg
+        T = g_o.shape[0]
+        nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
+        qkv, attn2, lse = S["qkv"], S["attn"], S["lse"]
+        g_attn = F.gemm(g_o, W["self_attn.o_proj.weight"], b_mn=True)
+        self._wgrad(W["self_attn.o_proj.weight"], g_o, attn2)
+        q = qkv[:, :Q].view(T, nh, hd)
+        k = qkv[:, Q : Q + KV].view(T, nkv, hd)
+        v = qkv[:, Q + KV :].view(T, nkv, hd)
+        cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["bwd"] is not None and lse is not None else self._cu_cpu(batch)
+        dq, dk, dv = F.attention_varlen_bwd(g_attn.view(T, nh, hd), q, k, v, attn2.view(T, nh, hd), lse, cu,
+                                            batch.max_seqlen)
+        g_qkv = torch.empty_like(qkv)
+        gq = g_qkv[:, :Q].view(T, nh, hd)
+        gk = g_qkv[:, Q : Q + KV].view(T, nkv, hd)
+        gq.copy_(dq)
+        gk.copy_(dk)
+        g_qkv[:, Q + KV :].view(T, nkv, hd).copy_(dv)
+        F.apply_rope_(gq, batch.positions, self._cos, self._sin, backward=True)
+        F.apply_rope_(gk, batch.positions, self._cos, self._sin, backward=True)
+        if cfg.qk_norm:
+            wq, wk = W["self_attn.q_norm.weight"], W["self_attn.k_norm.weight"]
+            dqp = F.rms_norm_bwd(gq.reshape(T * nh, hd).contiguous(), S["q_pre"], wq, S["rstd_q"], None,
+                                 self._grad_of(wq), True)
+            dkp = F.rms_norm_bwd(gk.reshape(T * nkv, hd).contiguous(), S["k_pre"], wk, S["rstd_k"], None,
+                                 self._grad_of(wk), True)
+            gq.copy_(dqp.view(T, nh, hd))
+            gk.copy_(dkp.view(T, nkv, hd))
+        g_h1 = F.gemm(g_qkv, W["self_attn.qkv_proj.weight"], b_mn=True)
+        self._wgrad(W["self_attn.qkv_proj.weight"], g_qkv, h1)
+        b = W.get("self_attn.qkv_proj.bias")
+        if b is not None and getattr(b, "main_grad", None) is not None:
+            b.main_grad.add_(g_qkv.float().sum(0))
+        return g_h1
+
+    def _grad_of(self, w: torch.Tensor) -> torch.Tensor:
+        mg = getattr(w, "main_grad", None)
+        return mg if mg is not None else torch.zeros_like(w, dtype=torch.float32)
+
+    # ------------------------------------------------------------------------------------ MLP blocks
+    def _mlp_fwd(self, W, h2, S: Optional[dict]):
+        if self.cfg.is_moe:
+            return self._moe_fwd(W, h2, S)
+        gu = F.gemm(h2, W["mlp.gate_up_proj.weight"])
+        if S is not None:
+            S["gu"] = gu
+        return F.gemm(F.swiglu(gu), W["mlp.down_proj.weight"])
+
+    def _mlp_bwd(self, W, g_d, h2, S: dict):
+        if self.cfg.is_moe:
+            return self._moe_bwd(W, g_d, h2, S)
+        gu = S["gu"]
+        act = F.swiglu(gu)
+        g_act = F.gemm(g_d, W["mlp.down_proj.weight"], b_mn=True)
+        self._wgrad(W["mlp.down_proj.weight"], g_d, act)
+        g_gu = F.swiglu_bwd(g_act, gu)
+        g_h2 = F.gemm(g_gu, W["mlp.gate_up_proj.weight"], b_mn=True)
+        self._wgrad(W["mlp.gate_up_proj.weight"], g_gu, h2)
+        return g_h2
+
+    # -- mixture of experts: softmax router, top-k, tokens grouped by expert ------------------------
+    def _route(self, logits: torch.Tensor):
+        cfg = self.cfg
+        probs = torch.softmax(logits.float(), dim=-1)
+        w, idx = torch.topk(probs, cfg.num_experts_per_tok, dim=-1)
+        if cfg.norm_topk_prob:
+            w = w / w.sum(-1, keepdim=True)
+        return w, idx
+
+    def _moe_fwd(self, W, h2, S: Optional[dict]):
+        cfg = self.cfg
+        T, H = h2.shape
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        logits = F.gemm(h2, W["mlp.gate.weight"])
+        w, idx = self._route(logits)
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        tok = torch.div(order, k, rounding_mode="floor")
+        counts = torch.bincount(flat_e, minlength=E).tolist()
+        xp = h2[tok]
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        gu = torch.empty(T * k, Wgu.shape[1], dtype=h2.dtype, device=h2.device)
+        y = torch.empty(T * k, H, dtype=h2.dtype, device=h2.device)
+        s0 = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            F.gemm(xp[s0 : s0 + n], Wgu[e], out=gu[s0 : s0 + n])
+            F.gemm(F.swiglu(gu[s0 : s0 + n]), Wd[e], out=y[s0 : s0 + n])
+            s0 += n
+        wp = w.reshape(-1)[order].to(h2.dtype)
+        out = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
+        out.index_add_(0, tok, (y * wp.unsqueeze(-1)).float())
+        if S is not None:
+            S.update(moe=dict(logits=logits, order=order, tok=tok, counts=counts, gu=gu, y=y, wp=wp))
+        return out.to(h2.dtype)
+
+    def _moe_bwd(self, W, g_d, h2, S: dict):
+        cfg = self.cfg
+        M = S["moe"]
+        order, tok, counts, gu, y, wp = M["order"], M["tok"], M["counts"], M["gu"], M["y"], M["wp"]
+        k = cfg.num_experts_per_tok
+        T, H = h2.shape
+        g_dp = g_d[tok]
+        g_wp = (g_dp.float() * y.float()).sum(-1)  # d loss / d routing weight, permuted order
+        g_y = (g_dp * wp.unsqueeze(-1)).contiguous()
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        xp = h2[tok]
+        g_xp = torch.empty_like(xp)
+        s0 = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            sl = slice(s0, s0 + n)
+            act = F.swiglu(gu[sl])
+            g_act = F.gemm(g_y[sl], Wd[e], b_mn=True)
+            mg = getattr(Wd, "main_grad", None)
+            if mg is not None:
+                F.gemm(g_y[sl], act, out=mg[e], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            g_gu = F.swiglu_bwd(g_act, gu[sl])
+            F.gemm(g_gu, Wgu[e], b_mn=True, out=g_xp[sl])
+            mg = getattr(Wgu, "main_grad", None)
+            if mg is not None:
+                F.gemm(g_gu, xp[sl], out=mg[e], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            s0 += n
+        g_h2 = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
+        g_h2.index_add_(0, tok, g_xp.float())
+        # router: differentiate softmax/top-k/normalise on the small [T, E] problem with autograd
+        g_w = torch.empty(T * k, dtype=torch.float32, device=h2.device)
+        g_w[order] = g_wp
+        with torch.enable_grad():
+            lg = M["logits"].detach().float().requires_grad_(True)
+            w, _ = self._route(lg)
+            (g_logits,) = torch.autograd.grad(w, lg, g_w.view(T, k))
+        g_logits = g_logits.to(h2.dtype)
+        g_h2 += F.gemm(g_logits, W["mlp.gate.weight"], b_mn=True).float()
+        self._wgrad(W["mlp.gate.weight"], g_logits, h2)
+        return g_h2.to(h2.dtype)
+
+    # ------------------------------------------------------------------------------------ layer
+    def _layer_fwd(self, i: int, a, r, batch: PackedBatch, S: Optional[dict]):
+        if self.pre_layer_hook is not None:
+            self.pre_layer_hook(i, "forward")
+        W = self.params.layer(i)
+        eps = self.cfg.rms_norm_eps
+        h1, x, rstd1 = F.rms_norm(a, W["input_layernorm.weight"], eps, residual=r)
+        o = self._attn_fwd(W, h1, batch, S)
+        h2, x2, rstd2 = F.rms_norm(o, W["post_attention_layernorm.weight"], eps, residual=x)
+        d = self._mlp_fwd(W, h2, S)
+        if S is not None:
+            S.update(x=x, rstd1=rstd1, x2=x2, rstd2=rstd2)
+        return d, x2
+
+    def _layer_bwd(self, i: int, g_d, g_x2, batch: PackedBatch, S: dict):
+        if self.pre_layer_hook is not None:
+            self.pre_layer_hook(i, "backward")
+        W = self.params.layer(i)
+        eps = self.cfg.rms_norm_eps
+        w1, w2 = W["input_layernorm.weight"], W["post_attention_layernorm.weight"]
+        h2 = F.rms_norm(S["x2"], w2, eps)[0]
+        g_h2 = self._mlp_bwd(W, g_d, h2, S)
+        g_x2t = F.rms_norm_bwd(g_h2, S["x2"], w2, S["rstd2"], g_x2, self._grad_of(w2), True)
+        h1 = F.rms_norm(S["x"], w1, eps)[0]
+        g_h1 = self._attn_bwd(W, g_x2t, h1, batch, S)
+        g_x = F.rms_norm_bwd(g_h1, S["x"], w1, S["rstd1"], g_x2t, self._grad_of(w1), True)
+        if self.post_layer_backward_hook is not None:
+            self.post_layer_backward_hook(i)
+        return g_x
+
+    # ------------------------------------------------------------------------------------ trunk
+    def _trunk_fwd(self, batch: PackedBatch, save: bool):
+        cfg = self.cfg
+        self._ensure_rope(batch.max_seqlen + 1)
+        if self.pre_layer_hook is not None:
+            self.pre_layer_hook(-1, "forward")
+        a = F.embedding(batch.input_ids, self.params["embed_tokens.weight"])
+        r = None
+        saved: list[Any] = []
+        for i in range(cfg.num_hidden_layers):
+            if save and self.recompute == "full":
+                saved.append((a, r))
+                a, r = self._layer_fwd(i, a, r, batch, None)
+            else:
+                S = {} if save else None
+                a, r = self._layer_fwd(i, a, r, batch, S)
+                if save:
+                    saved.append(S)
+        if self.pre_layer_hook is not None:
+            self.pre_layer_hook(cfg.num_hidden_layers, "forward")
+        hN, xN, rstdN = F.rms_norm(a, self.params["norm.weight"], cfg.rms_norm_eps, residual=r)
+        state = dict(batch=batch, layers=saved, xN=xN, rstdN=rstdN, hN=hN) if save else None
+        return hN, state
+
+    def _trunk_bwd(self, state: dict, g_hN: torch.Tensor) -> None:
+        cfg = self.cfg
+        batch = state["batch"]
+        wn = self.params["norm.weight"]
+        g = F.rms_norm_bwd(g_hN, state["xN"], wn, state["rstdN"], None, self._grad_of(wn), True)
+        if self.post_layer_backward_hook is not None:
+            self.post_layer_backward_hook(cfg.num_hidden_layers)
+        g_d = g_x2 = g
+        for i in reversed(range(cfg.num_hidden_layers)):
+            S = state["layers"][i]
+            if self.recompute == "full":
+                a, r = S
+                S = {}
+                self._layer_fwd(i, a, r, batch, S)
+            g = self._layer_bwd(i, g_d, g_x2, batch, S)
+            state["layers"][i] = None
+            g_d = g_x2 = g
+        emb = self.params["embed_tokens.weight"]
+        if getattr(emb, "main_grad", None) is not None:
+            if self.pre_layer_hook is not None:
+                self.pre_layer_hook(-1, "backward")
+            F.embedding_bwd_(batch.input_ids, g, emb.main_grad)
+        if self.post_layer_backward_hook is not None:
+            self.post_layer_backward_hook(-1)
+
+    # ------------------------------------------------------------------------------------ heads
+    def forward_logprobs(self, batch: PackedBatch, labels: torch.Tensor, temperature: float = 1.0,
+                         need_grad: Optional[bool] = None):
+        """(log_probs, entropy) per packed position of ``labels`` (fp32 [T]); differentiable when grads are on."""
+        need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
+        with torch.no_grad():
+            hN, state = self._trunk_fwd(batch, save=need_grad)
+            lp, ent, lse = F.lmhead_logprob_entropy(hN, self.params.lm_head_weight, labels, temperature)
+        if not need_grad:
+            return lp, ent
+        state.update(kind="lm", labels=labels, temperature=temperature, lse=lse, ent=ent)
+        return _Anchor.apply(self._anchor, self, state, lp, ent)
+
+    def forward_values(self, batch: PackedBatch, need_grad: Optional[bool] = None) -> torch.Tensor:
+        """Scalar value per packed position (fp32 [T]) from the value head."""
+        need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
+        with torch.no_grad():
+            hN, state = self._trunk_fwd(batch, save=need_grad)
+            vals = F.gemm(hN, self.params["v_head.weight"])[:, 0].float()
+        if not need_grad:
+            return vals
+        state.update(kind="value")
+        return _Anchor.apply(self._anchor, self, state, vals)[0]
+
+    def forward_hidden(self, batch: PackedBatch) -> torch.Tensor:
+        with torch.no_grad():
+            return self._trunk_fwd(batch, save=False)[0]
+
+    def forward_logits(self, batch: PackedBatch) -> torch.Tensor:
+        with torch.no_grad():
+            return F.gemm(self._trunk_fwd(batch, save=False)[0], self.params.lm_head_weight)
+
+    @torch.no_grad()
+    def _backward(self, state: dict, grads) -> None:
+        hN = state["hN"]
+        if state["kind"] == "lm":
+            g_lp, g_ent = grads
+            if g_lp is None:
+                g_lp = torch.zeros_like(state["lse"])
+            head = self.params.lm_head_weight
+            g_hN = F.lmhead_backward(hN, head, state["labels"], state["temperature"], state["lse"], state["ent"],
+                                     g_lp.float(), g_ent.float() if g_ent is not None else None, self._grad_of(head))
+        else:
+            (g_v,) = grads
+            wv = self.params["v_head.weight"]
+            dl = torch.zeros(hN.shape[0], wv.shape[0], dtype=hN.dtype, device=hN.device)
+            dl[:, 0] = g_v.to(hN.dtype)
+            g_hN = F.gemm(dl, wv, b_mn=True)
+            self._wgrad(wv, dl, hN)
+        self._trunk_bwd(state, g_hN)

@@ -8,17 +8,22 @@
 
 namespace {
 
+using at::Tensor;
+using OptTensor = c10::optional<at::Tensor>;
+
 inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline const void* optr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+inline const float* fptr(const OptTensor& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
 
-#define CHECK_CUDA_CONTIG(x) TORCH_CHECK((x).is_cuda() && (x).is_contiguous(), #x " must be a contiguous CUDA tensor")
+#define CHECK_BF16(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kBFloat16, #x " must be a CUDA bf16 tensor")
+#define CHECK_F32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kFloat, #x " must be a CUDA fp32 tensor")
+#define CHECK_RC(rc, what) TORCH_CHECK((rc) == 0, what " failed with code ", (rc))
 
-// D = A * B^T (+bias).  a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn). Rows may be strided views
-// (stride(1) == 1).
-at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& bias,
-                const c10::optional<at::Tensor>& out, bool a_mn, bool b_mn, bool out_f32, bool accumulate,
-                int64_t max_ctas) {
-  TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm: CUDA tensors required");
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 operands required");
+// D = A * B^T (+bias).  a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn); rows may be strided.
+Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTensor& out, bool a_mn, bool b_mn,
+            bool out_f32, bool accumulate, int64_t max_ctas) {
+  CHECK_BF16(a);
+  CHECK_BF16(b);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm: 2-D row-major operands");
   const c10::cuda::CUDAGuard guard(a.device());
   const int64_t M = a_mn ? a.size(1) : a.size(0);
@@ -26,7 +31,7 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   const int64_t Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "gemm: contraction mismatch ", K, " vs ", Kb);
-  at::Tensor d;
+  Tensor d;
   if (out.has_value()) {
     d = *out;
     TORCH_CHECK(d.dim() == 2 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm: bad out shape");
@@ -49,9 +54,280 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at
 
 int64_t gemm_status() { return vb_gemm_status(); }
 
+// (logprob, entropy, lse) of labels under softmax(hidden @ weight^T / temperature); [T,V] logits never exist.
+std::tuple<Tensor, Tensor, Tensor> lmhead_fwd(const Tensor& hidden, const Tensor& weight, const Tensor& labels,
+                                              double inv_temp) {
+  CHECK_BF16(hidden);
+  CHECK_BF16(weight);
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous(), "labels: int64");
+  TORCH_CHECK(hidden.dim() == 2 && weight.dim() == 2 && hidden.stride(1) == 1 && weight.stride(1) == 1);
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  const int64_t T = hidden.size(0), H = hidden.size(1), V = weight.size(0);
+  TORCH_CHECK(weight.size(1) == H && labels.numel() == T);
+  auto fo = hidden.options().dtype(at::kFloat);
+  Tensor lp = at::empty({T}, fo), ent = at::empty({T}, fo), lse = at::empty({T}, fo);
+  if (T == 0) return {lp, ent, lse};
+  Tensor partial = at::empty({3, (int64_t)vb_lmhead_num_tiles((int)V), T}, fo);
+  Tensor lab = at::zeros({T}, fo);
+  const int rc = vb_lmhead_fwd(hidden.data_ptr(), weight.data_ptr(), reinterpret_cast<long long*>(labels.data_ptr()), (float)inv_temp,
+                               partial.data_ptr<float>(), lab.data_ptr<float>(), lp.data_ptr<float>(),
+                               ent.data_ptr<float>(), lse.data_ptr<float>(), (int)T, (int)V, (int)H, hidden.stride(0),
+                               weight.stride(0), cur_stream());
+  CHECK_RC(rc, "vb_lmhead_fwd");
+  return {lp, ent, lse};
+}
+
+// d loss / d logits for vocabulary rows [v0, v0 + weight_chunk.size(0)) as bf16 [T, Vc].
+Tensor lmhead_dlogits(const Tensor& hidden, const Tensor& weight_chunk, const Tensor& labels, int64_t v0,
+                      double inv_temp, const Tensor& lse, const OptTensor& ex, const Tensor& g_lp,
+                      const OptTensor& g_ent, const OptTensor& out) {
+  CHECK_BF16(hidden);
+  CHECK_BF16(weight_chunk);
+  CHECK_F32(lse);
+  CHECK_F32(g_lp);
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  const int64_t T = hidden.size(0), H = hidden.size(1), Vc = weight_chunk.size(0);
+  Tensor d = out.has_value() ? *out : at::empty({T, Vc}, hidden.options());
+  TORCH_CHECK(d.size(0) == T && d.size(1) == Vc && d.stride(1) == 1);
+  const int rc = vb_lmhead_dlogits(hidden.data_ptr(), weight_chunk.data_ptr(), reinterpret_cast<long long*>(labels.data_ptr()), (int)v0,
+                                   (float)inv_temp, lse.data_ptr<float>(), fptr(ex), g_lp.data_ptr<float>(),
+                                   fptr(g_ent), d.data_ptr(), (int)T, (int)Vc, (int)H, hidden.stride(0),
+                                   weight_chunk.stride(0), d.stride(0), cur_stream());
+  CHECK_RC(rc, "vb_lmhead_dlogits");
+  return d;
+}
+
+// y = rmsnorm(x (+ residual)) * w. Returns (y, residual_out or x, rstd).
+std::tuple<Tensor, Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor& residual, const Tensor& w,
+                                               double eps) {
+  CHECK_BF16(x);
+  CHECK_BF16(w);
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t H = x.size(-1), T = x.numel() / H;
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
+  Tensor res_out = residual.has_value() ? at::empty_like(x) : x;
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->sizes() == x.sizes());
+  const int rc = vb_rmsnorm_fwd(x.data_ptr(), optr(residual), w.data_ptr(), y.data_ptr(),
+                                residual.has_value() ? res_out.data_ptr() : nullptr, rstd.data_ptr<float>(), (int)T,
+                                (int)H, (float)eps, cur_stream());
+  CHECK_RC(rc, "vb_rmsnorm_fwd");
+  return {y, res_out, rstd};
+}
+
+// dx = d/dx of rmsnorm (+ dres_in); dw accumulated into `dw` (fp32 [H]) when accumulate, else overwritten.
+Tensor rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, const OptTensor& dres_in,
+                   Tensor dw, bool accumulate) {
+  CHECK_BF16(dy);
+  CHECK_BF16(x);
+  CHECK_F32(dw);
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t H = x.size(-1), T = x.numel() / H;
+  Tensor dx = at::empty_like(x);
+  if (T == 0) return dx;
+  Tensor scratch = at::empty({(int64_t)vb_rmsnorm_bwd_blocks((int)T), H}, x.options().dtype(at::kFloat));
+  const int rc = vb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), optr(dres_in),
+                                dx.data_ptr(), dw.data_ptr<float>(), scratch.data_ptr<float>(), (int)T, (int)H,
+                                accumulate, cur_stream());
+  CHECK_RC(rc, "vb_rmsnorm_bwd");
+  return dx;
+}
+
+// In-place rotary embedding on x [T, nheads, hd] (a view with row stride x.stride(0)).
+void rope_(Tensor x, const Tensor& pos, const Tensor& cos_t, const Tensor& sin_t, bool backward) {
+  CHECK_BF16(x);
+  CHECK_F32(cos_t);
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: [T, nheads, hd] with packed heads");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && pos.is_contiguous(), "rope: int32 positions");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rc = vb_rope(x.data_ptr(), pos.data_ptr<int>(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                         (int)x.size(0), (int)x.size(1), (int)x.size(2), x.stride(0), backward, cur_stream());
+  CHECK_RC(rc, "vb_rope");
+}
+
+Tensor swiglu_fwd(const Tensor& gu) {
+  CHECK_BF16(gu);
+  TORCH_CHECK(gu.is_contiguous() && gu.dim() == 2);
+  const c10::cuda::CUDAGuard guard(gu.device());
+  const int64_t T = gu.size(0), I = gu.size(1) / 2;
+  Tensor out = at::empty({T, I}, gu.options());
+  CHECK_RC(vb_swiglu_fwd(gu.data_ptr(), out.data_ptr(), T, (int)I, cur_stream()), "vb_swiglu_fwd");
+  return out;
+}
+Tensor swiglu_bwd(const Tensor& dout, const Tensor& gu) {
+  CHECK_BF16(gu);
+  CHECK_BF16(dout);
+  TORCH_CHECK(gu.is_contiguous() && dout.is_contiguous());
+  const c10::cuda::CUDAGuard guard(gu.device());
+  Tensor dgu = at::empty_like(gu);
+  CHECK_RC(vb_swiglu_bwd(dout.data_ptr(), gu.data_ptr(), dgu.data_ptr(), gu.size(0), (int)(gu.size(1) / 2), cur_stream()),
+           "vb_swiglu_bwd");
+  return dgu;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& w) {
+  CHECK_BF16(w);
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && w.is_contiguous());
+  const c10::cuda::CUDAGuard guard(w.device());
+  Tensor out = at::empty({ids.numel(), w.size(1)}, w.options());
+  CHECK_RC(vb_embedding_fwd(reinterpret_cast<long long*>(ids.data_ptr()), w.data_ptr(), out.data_ptr(), (int)ids.numel(), (int)w.size(1),
+                            (int)w.size(0), cur_stream()),
+           "vb_embedding_fwd");
+  return out;
+}
+void embedding_bwd_(const Tensor& ids, const Tensor& dout, Tensor dw) {
+  CHECK_BF16(dout);
+  CHECK_F32(dw);
+  TORCH_CHECK(dout.is_contiguous() && dw.is_contiguous());
+  const c10::cuda::CUDAGuard guard(dw.device());
+  CHECK_RC(vb_embedding_bwd(reinterpret_cast<long long*>(ids.data_ptr()), dout.data_ptr(), dw.data_ptr<float>(), (int)ids.numel(),
+                            (int)dw.size(1), (int)dw.size(0), cur_stream()),
+           "vb_embedding_bwd");
+}
+
+void sumsq_(const Tensor& g, Tensor ctrl) {
+  CHECK_F32(g);
+  CHECK_F32(ctrl);
+  TORCH_CHECK(g.is_contiguous());
+  const c10::cuda::CUDAGuard guard(g.device());
+  CHECK_RC(vb_sumsq(g.data_ptr<float>(), g.numel(), ctrl.data_ptr<float>(), cur_stream()), "vb_sumsq");
+}
+void clip_coef_(Tensor ctrl, double max_norm) {
+  const c10::cuda::CUDAGuard guard(ctrl.device());
+  CHECK_RC(vb_clip_coef(ctrl.data_ptr<float>(), (float)max_norm, cur_stream()), "vb_clip_coef");
+}
+void adamw_(Tensor master, Tensor grad, Tensor m, Tensor v, const OptTensor& out_bf16, const OptTensor& ctrl, double lr,
+            double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale, bool zero_grad) {
+  CHECK_F32(master);
+  CHECK_F32(grad);
+  CHECK_F32(m);
+  CHECK_F32(v);
+  TORCH_CHECK(master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous());
+  const c10::cuda::CUDAGuard guard(master.device());
+  void* ob = out_bf16.has_value() ? out_bf16->data_ptr() : nullptr;
+  CHECK_RC(vb_adamw(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), ob,
+                    master.numel(), fptr(ctrl), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
+                    (float)grad_scale, zero_grad, cur_stream()),
+           "vb_adamw");
+}
+void cast_f32_bf16_(const Tensor& in, Tensor out, double scale) {
+  CHECK_F32(in);
+  CHECK_BF16(out);
+  const c10::cuda::CUDAGuard guard(in.device());
+  CHECK_RC(vb_cast_f32_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), (float)scale, cur_stream()), "vb_cast");
+}
+void accum_bf16_f32_(const Tensor& in, Tensor out, double scale, bool accumulate) {
+  CHECK_BF16(in);
+  CHECK_F32(out);
+  const c10::cuda::CUDAGuard guard(in.device());
+  CHECK_RC(vb_accum_bf16_f32(in.data_ptr(), out.data_ptr<float>(), in.numel(), (float)scale, accumulate, cur_stream()),
+           "vb_accum");
+}
+
+// k, v: [T, nkv, hd] views (row stride = stride(0)); slot: int64 [T]; caches: [num_slots, nkv, hd]
+void kv_append_(const Tensor& k, const Tensor& v, const Tensor& slot, Tensor kc, Tensor vc) {
+  CHECK_BF16(k);
+  CHECK_BF16(v);
+  TORCH_CHECK(k.dim() == 3 && k.stride(2) == 1 && k.stride(1) == k.size(2) && v.stride(1) == v.size(2));
+  TORCH_CHECK(slot.scalar_type() == at::kLong && slot.is_contiguous() && kc.is_contiguous() && vc.is_contiguous());
+  const c10::cuda::CUDAGuard guard(k.device());
+  CHECK_RC(vb_kv_append(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), reinterpret_cast<long long*>(slot.data_ptr()), kc.data_ptr(),
+                        vc.data_ptr(), (int)k.size(0), (int)k.size(1), (int)k.size(2), cur_stream()),
+           "vb_kv_append");
+}
+
+// q: [B, nh, hd] view; caches [num_blocks, block_size, nkv, hd]; block_table int32 [B, max_blocks]; ctx_len int32 [B]
+Tensor paged_decode(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_table,
+                    const Tensor& ctx_len, double scale) {
+  CHECK_BF16(q);
+  CHECK_BF16(kc);
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2) && kc.dim() == 4);
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && ctx_len.scalar_type() == at::kInt);
+  TORCH_CHECK(block_table.is_contiguous() && ctx_len.is_contiguous() && kc.is_contiguous() && vc.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), nh = q.size(1), hd = q.size(2);
+  Tensor out = at::empty({B, nh, hd}, q.options());
+  CHECK_RC(vb_paged_decode(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), block_table.data_ptr<int>(),
+                           (int)block_table.size(1), ctx_len.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)B,
+                           (int)nh, (int)kc.size(2), (int)hd, (int)kc.size(1), (float)scale, cur_stream()),
+           "vb_paged_decode");
+  return out;
+}
+
+// logits bf16 [B, V]; seeds int64 [B]. Returns (tokens int64 [B], logprobs fp32 [B]).
+std::tuple<Tensor, Tensor> sample(const Tensor& logits, int64_t valid_vocab, double inv_temp, const Tensor& seeds,
+                                  int64_t step) {
+  CHECK_BF16(logits);
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && seeds.scalar_type() == at::kLong);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t B = logits.size(0);
+  Tensor tok = at::empty({B}, logits.options().dtype(at::kLong));
+  Tensor lp = at::empty({B}, logits.options().dtype(at::kFloat));
+  CHECK_RC(vb_sample(logits.data_ptr(), logits.stride(0), (int)B, (int)logits.size(1), (int)valid_vocab,
+                     (float)inv_temp, reinterpret_cast<long long*>(seeds.data_ptr()), step, reinterpret_cast<long long*>(tok.data_ptr()), lp.data_ptr<float>(),
+                     cur_stream()),
+           "vb_sample");
+  return {tok, lp};
+}
+
+// rewards/mask fp32 [B, L]; group int32 [B] in [0, num_groups). Returns (advantages [B,L], scores [B]).
+std::tuple<Tensor, Tensor> grpo_advantage(const Tensor& rewards, const Tensor& mask, const Tensor& group,
+                                          int64_t num_groups, double eps, bool norm_by_std) {
+  CHECK_F32(rewards);
+  CHECK_F32(mask);
+  TORCH_CHECK(group.scalar_type() == at::kInt && rewards.is_contiguous() && mask.is_contiguous());
+  const c10::cuda::CUDAGuard guard(rewards.device());
+  const int64_t B = rewards.size(0), L = rewards.size(1);
+  Tensor adv = at::empty_like(rewards);
+  Tensor scores = at::empty({B}, rewards.options());
+  Tensor stats = at::empty({num_groups, 3}, rewards.options());
+  CHECK_RC(vb_grpo_advantage(rewards.data_ptr<float>(), mask.data_ptr<float>(), group.data_ptr<int>(), (int)B, (int)L,
+                             (int)num_groups, (float)eps, norm_by_std, scores.data_ptr<float>(),
+                             stats.data_ptr<float>(), adv.data_ptr<float>(), cur_stream()),
+           "vb_grpo_advantage");
+  return {adv, scores};
+}
+
+std::tuple<Tensor, Tensor> gae(const Tensor& rewards, const Tensor& values, const Tensor& mask, double gamma,
+                               double lam, bool whiten) {
+  CHECK_F32(rewards);
+  CHECK_F32(values);
+  CHECK_F32(mask);
+  TORCH_CHECK(rewards.is_contiguous() && values.is_contiguous() && mask.is_contiguous());
+  const c10::cuda::CUDAGuard guard(rewards.device());
+  Tensor adv = at::empty_like(rewards), ret = at::empty_like(rewards);
+  Tensor acc = at::empty({4}, rewards.options());
+  CHECK_RC(vb_gae(rewards.data_ptr<float>(), values.data_ptr<float>(), mask.data_ptr<float>(), (int)rewards.size(0),
+                  (int)rewards.size(1), (float)gamma, (float)lam, whiten, adv.data_ptr<float>(), ret.data_ptr<float>(),
+                  acc.data_ptr<float>(), cur_stream()),
+           "vb_gae");
+  return {adv, ret};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
+  m.def("lmhead_fwd", &lmhead_fwd);
+  m.def("lmhead_dlogits", &lmhead_dlogits);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_", &rope_);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd_", &embedding_bwd_);
+  m.def("sumsq_", &sumsq_);
+  m.def("clip_coef_", &clip_coef_);
+  m.def("adamw_", &adamw_);
+  m.def("cast_f32_bf16_", &cast_f32_bf16_);
+  m.def("accum_bf16_f32_", &accum_bf16_f32_);
+  m.def("kv_append_", &kv_append_);
+  m.def("paged_decode", &paged_decode);
+  m.def("sample", &sample);
+  m.def("grpo_advantage", &grpo_advantage);
+  m.def("gae", &gae);
 }

@@ -18,6 +18,7 @@
 // The epilogue of tile i overlaps the main loop of tile i+1 through the double-buffered accumulator.
 #include "tcgen05_common.cuh"
 
+#include <math.h>
 #include <stdio.h>
 
 namespace vb {
@@ -27,6 +28,14 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int GEMM_THREADS = 192;
 
+// Epilogue kinds.
+//  EPI_STORE    D = acc (+bias) as bf16 or fp32 (optionally +=)
+//  EPI_LSE      LM head forward: per (row, 256-column tile) online-softmax partials (max, sum exp,
+//               sum x*exp) of x = acc * inv_temp, plus the label logit; the [T, V] logits never exist.
+//  EPI_DLOGITS  LM head backward: D = d loss / d acc for the recomputed tile, written as bf16:
+//               inv_temp * ( g_lp * (onehot - p) - g_ent * p * (x - E[x]) ),  p = exp(x - lse).
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2 };
+
 struct GemmParams {
   int M, N, K;
   void* D;
@@ -35,6 +44,16 @@ struct GemmParams {
   int out_f32;
   int accumulate;
   int* status;
+  // LM-head epilogues
+  const long long* labels;  // [M]; label column in the full vocabulary
+  int label_offset;         // first vocabulary column covered by this launch
+  float inv_temp;
+  float* partial;           // EPI_LSE: [3][num_n_tiles][M]
+  float* label_logit;       // EPI_LSE: [M]
+  const float* lse;         // EPI_DLOGITS: [M]
+  const float* ex;          // EPI_DLOGITS: [M]  E[x] = lse - entropy (may be null when g_ent is null)
+  const float* g_lp;        // EPI_DLOGITS: [M]
+  const float* g_ent;       // EPI_DLOGITS: [M] or null
 };
 
 __device__ int g_gemm_status[4];
@@ -47,7 +66,7 @@ struct GemmSmem {
   static constexpr int TOTAL = RING + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN, bool A_MN, bool B_MN, int STAGES>
+template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmParams p) {
@@ -210,6 +229,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      // per-row state of the LM-head epilogues (thread == row)
+      float run_m = -INFINITY, run_l = 0.f, run_s = 0.f;
+      long long label = -1;
+      float r_lse = 0.f, r_ex = 0.f, r_glp = 0.f, r_gent = 0.f;
+      if constexpr (EPI != EPI_STORE) {
+        if (row_ok) {
+          label = p.labels[row] - p.label_offset;
+          if constexpr (EPI == EPI_DLOGITS) {
+            r_lse = p.lse[row];
+            r_glp = p.g_lp[row];
+            if (p.g_ent != nullptr) {
+              r_gent = p.g_ent[row];
+              r_ex = p.ex[row];
+            }
+          }
+        }
+      }
+      constexpr float LOG2E = 1.4426950408889634f;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -217,8 +254,60 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
-        if (row_ok) {
-          const int ncols = min(32, p.N - col0);  // multiple of 8
+        const int ncols = min(32, p.N - col0);  // multiple of 8
+        if constexpr (EPI == EPI_LSE) {
+          float x[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            x[j] = (j < ncols) ? __uint_as_float(r[j]) * p.inv_temp : -INFINITY;
+            cmax = fmaxf(cmax, x[j]);
+          }
+          const float new_m = fmaxf(run_m, cmax);
+          const float resc = exp2f((run_m - new_m) * LOG2E);  // 0 on the first chunk (run_m = -inf)
+          float cl = 0.f, cs = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float e = exp2f((x[j] - new_m) * LOG2E);
+            cl += e;
+            cs += (j < ncols) ? e * x[j] : 0.f;
+          }
+          run_l = run_l * resc + cl;
+          run_s = run_s * resc + cs;
+          run_m = new_m;
+          const long long rel = label - col0;
+          if (rel >= 0 && rel < ncols && row_ok) {
+            float lab = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) lab = (j == rel) ? x[j] : lab;
+            p.label_logit[row] = lab;
+          }
+        } else if constexpr (EPI == EPI_DLOGITS) {
+          if (row_ok) {
+            const long long rel = label - col0;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            float d[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = __uint_as_float(r[j]) * p.inv_temp;
+              const float pj = exp2f((x - r_lse) * LOG2E);
+              float g = r_glp * (((j == rel) ? 1.f : 0.f) - pj);
+              g -= r_gent * pj * (x - r_ex);
+              d[j] = g * p.inv_temp;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (j < ncols) {
+                uint4 v;
+                v.x = pack_bf16x2(d[j], d[j + 1]);
+                v.y = pack_bf16x2(d[j + 2], d[j + 3]);
+                v.z = pack_bf16x2(d[j + 4], d[j + 5]);
+                v.w = pack_bf16x2(d[j + 6], d[j + 7]);
+                *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            }
+          }
+        } else if (row_ok) {
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -255,6 +344,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
         }
       }
+      if constexpr (EPI == EPI_LSE) {
+        if (row_ok) {
+          const long long plane = static_cast<long long>(num_n) * p.M;
+          const long long o = static_cast<long long>(n_idx) * p.M + row;
+          p.partial[o] = run_m;
+          p.partial[plane + o] = run_l;
+          p.partial[2 * plane + o] = run_s;
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -275,10 +373,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 }
 
 // --------------------------------------------------------------------------- launcher
-template <int BN, bool A_MN, bool B_MN, int STAGES>
+template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI = EPI_STORE>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
                                   cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGES, EPI>;
   constexpr int smem = GemmSmem<BN, STAGES>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -303,8 +401,8 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
                             long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
                             int accumulate, int max_ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldd % (out_f32 ? 4 : 8))) return -1;
-  if (a_mn && (M % 8)) return -1;
+  // TMA needs 16-byte aligned bases and row strides; the epilogue stores 8-column vectors.
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % (out_f32 ? 4 : 8))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
   int sms = num_sms();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
@@ -320,7 +418,10 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
   if (!ok) return -3;
   int* status = nullptr;
   cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
-  GemmParams p{M, N, K, D, ldd, reinterpret_cast<const __nv_bfloat16*>(bias), out_f32, accumulate, status};
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_f32 = out_f32; p.accumulate = accumulate; p.status = status;
   cudaError_t e;
 #define VB_LAUNCH(BN_, AM, BMJ, ST) e = launch_variant<BN_, AM, BMJ, ST>(ta, tb, p, sms, stream)
   if (wide) {
@@ -347,4 +448,75 @@ extern "C" int vb_gemm_status() {
     cudaMemcpyToSymbol(g_gemm_status, z, sizeof(z));
   }
   return h[0];
+}
+
+namespace vb {
+
+// logprob / entropy from the per-tile partials written by EPI_LSE.
+__global__ void lmhead_merge_kernel(const float* __restrict__ partial, const float* __restrict__ label_logit,
+                                    float* __restrict__ logprob, float* __restrict__ entropy,
+                                    float* __restrict__ lse_out, int T, int num_n) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T) return;
+  const long long plane = static_cast<long long>(num_n) * T;
+  float M = -INFINITY;
+  for (int n = 0; n < num_n; ++n) M = fmaxf(M, partial[static_cast<long long>(n) * T + row]);
+  float L = 0.f, S = 0.f;
+  for (int n = 0; n < num_n; ++n) {
+    const long long o = static_cast<long long>(n) * T + row;
+    const float w = __expf(partial[o] - M);
+    L += partial[plane + o] * w;
+    S += partial[2 * plane + o] * w;
+  }
+  const float lse = M + __logf(L);
+  if (logprob) logprob[row] = label_logit[row] - lse;
+  if (entropy) entropy[row] = lse - S / L;
+  if (lse_out) lse_out[row] = lse;
+}
+
+}  // namespace vb
+
+// Number of 256-column tiles (rows of the partial buffer) for a vocabulary of V columns.
+extern "C" int vb_lmhead_num_tiles(int V) { return (V + 255) / 256; }
+
+// Forward: hidden [T,H] bf16, weight [V,H] bf16, labels [T] int64 -> logprob/entropy/lse [T] fp32.
+// partial: scratch of 3 * num_tiles(V) * T floats; label_logit: scratch of T floats.
+extern "C" int vb_lmhead_fwd(const void* hidden, const void* weight, const long long* labels, float inv_temp,
+                             float* partial, float* label_logit, float* logprob, float* entropy, float* lse, int T,
+                             int V, int H, long long ldh, long long ldw, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((V % 8) || (H % 8) || (ldh % 8) || (ldw % 8)) return -1;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, hidden, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, H, ldh, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!make_tmap_2d(&tb, weight, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, V, H, ldw, BK, 256, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  int* status = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
+  GemmParams p{};
+  p.M = T; p.N = V; p.K = H; p.status = status;
+  p.labels = labels; p.label_offset = 0; p.inv_temp = inv_temp; p.partial = partial; p.label_logit = label_logit;
+  cudaError_t e = launch_variant<256, false, false, 4, EPI_LSE>(ta, tb, p, num_sms(), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  lmhead_merge_kernel<<<(T + 127) / 128, 128, 0, stream>>>(partial, label_logit, logprob, entropy, lse, T,
+                                                         vb_lmhead_num_tiles(V));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward, one vocabulary chunk [v0, v0+Vc): writes dlogits [T, Vc] bf16 (row stride ldd).
+extern "C" int vb_lmhead_dlogits(const void* hidden, const void* weight_chunk, const long long* labels, int v0,
+                                 float inv_temp, const float* lse, const float* ex, const float* g_lp,
+                                 const float* g_ent, void* dlogits, int T, int Vc, int H, long long ldh, long long ldw,
+                                 long long ldd, cudaStream_t stream) {
+  if (T <= 0 || Vc <= 0) return 0;
+  if ((Vc % 8) || (H % 8) || (ldh % 8) || (ldw % 8) || (ldd % 8)) return -1;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, hidden, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, H, ldh, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!make_tmap_2d(&tb, weight_chunk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Vc, H, ldw, BK, 256, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  int* status = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
+  GemmParams p{};
+  p.M = T; p.N = Vc; p.K = H; p.D = dlogits; p.ldd = ldd; p.status = status;
+  p.labels = labels; p.label_offset = v0; p.inv_temp = inv_temp;
+  p.lse = lse; p.ex = ex; p.g_lp = g_lp; p.g_ent = g_ent;
+  cudaError_t e = launch_variant<256, false, false, 4, EPI_DLOGITS>(ta, tb, p, num_sms(), stream);
+  return static_cast<int>(e);
 }

@@ -4,8 +4,47 @@
 #include <stdint.h>
 
 extern "C" {
+// gemm_tcgen05.cu
 int vb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldd, int a_mn, int b_mn, int out_f32, int accumulate, int max_ctas,
                  cudaStream_t stream);
 int vb_gemm_status();
+int vb_lmhead_num_tiles(int V);
+int vb_lmhead_fwd(const void* hidden, const void* weight, const long long* labels, float inv_temp, float* partial,
+                  float* label_logit, float* logprob, float* entropy, float* lse, int T, int V, int H, long long ldh,
+                  long long ldw, cudaStream_t stream);
+int vb_lmhead_dlogits(const void* hidden, const void* weight_chunk, const long long* labels, int v0, float inv_temp,
+                      const float* lse, const float* ex, const float* g_lp, const float* g_ent, void* dlogits, int T,
+                      int Vc, int H, long long ldh, long long ldw, long long ldd, cudaStream_t stream);
+// elementwise.cu
+int vb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* res_out, float* rstd, int T,
+                   int H, float eps, cudaStream_t s);
+int vb_rmsnorm_bwd_blocks(int T);
+int vb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
+                   float* dw, float* scratch, int T, int H, int accumulate_dw, cudaStream_t s);
+int vb_rope(void* x, const int* pos, const float* cos_t, const float* sin_t, int T, int nheads, int hd, long long ld,
+            int backward, cudaStream_t s);
+int vb_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t s);
+int vb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int I, cudaStream_t s);
+int vb_embedding_fwd(const long long* ids, const void* w, void* out, int T, int H, int V, cudaStream_t s);
+int vb_embedding_bwd(const long long* ids, const void* dout, float* dw, int T, int H, int V, cudaStream_t s);
+int vb_sumsq(const float* g, long long n, float* ctrl, cudaStream_t s);
+int vb_clip_coef(float* ctrl, float max_norm, cudaStream_t s);
+int vb_adamw(float* master, float* grad, float* m, float* v, void* out_bf16, long long n, const float* ctrl, float lr,
+             float beta1, float beta2, float eps, float wd, int step, float grad_scale, int zero_grad, cudaStream_t s);
+int vb_cast_f32_bf16(const float* in, void* out, long long n, float scale, cudaStream_t s);
+int vb_accum_bf16_f32(const void* in, float* out, long long n, float scale, int accumulate, cudaStream_t s);
+// rollout_kernels.cu
+int vb_kv_append(const void* k, const void* v, long long ldk, long long ldv, const long long* slot, void* kc, void* vc,
+                 int T, int nkv, int hd, cudaStream_t s);
+int vb_paged_decode(const void* q, long long ldq, const void* kc, const void* vc, const int* block_table,
+                    int max_blocks, const int* ctx_len, void* out, long long ldo, int B, int nh, int nkv, int hd,
+                    int block_size, float scale, cudaStream_t s);
+int vb_sample(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, const long long* seeds,
+              long long step, long long* tokens, float* logprobs, cudaStream_t s);
+// advantage.cu
+int vb_grpo_advantage(const float* rewards, const float* mask, const int* group, int B, int L, int num_groups,
+                      float eps, int norm_by_std, float* scores, float* stats, float* adv, cudaStream_t s);
+int vb_gae(const float* rewards, const float* values, const float* mask, int B, int L, float gamma, float lam,
+           int whiten, float* adv, float* ret, float* acc, cudaStream_t s);
 }

@@ -1,0 +1,405 @@
+"""Functional front-end of the native kernels.
+
+Every function dispatches on the device of its input: CUDA tensors go to the hand-written sm_100a
+kernels (bf16 activations, fp32 statistics); CPU tensors take a plain PyTorch path that doubles as the
+fp32 oracle in the tests.  Nothing here silently falls back on a GPU: a missing native library raises.
+
+Weight gradients follow the "main_grad" convention: when a parameter carries an fp32 ``main_grad``
+buffer, backward GEMMs accumulate straight into it (tcgen05 wgrad with a read-modify-write epilogue) and
+autograd sees ``None`` for that parameter.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+__all__ = [
+    "gemm",
+    "linear",
+    "rms_norm",
+    "rms_norm_bwd",
+    "rope_table",
+    "apply_rope_",
+    "swiglu",
+    "swiglu_bwd",
+    "embedding",
+    "embedding_bwd_",
+    "lmhead_logprob_entropy",
+    "lmhead_backward",
+    "attention_varlen",
+    "attention_varlen_bwd",
+    "paged_decode_attention",
+    "kv_append_",
+    "sample_tokens",
+    "grpo_advantage",
+    "gae_advantage",
+]
+
+
+def _ops():
+    return native.ops()
+
+
+# ----------------------------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         a_mn: bool = False, b_mn: bool = False, out_f32: bool = False, accumulate: bool = False,
+         max_ctas: int = 0) -> torch.Tensor:
+    """``D = A @ B^T (+bias)``; ``a_mn``/``b_mn`` mean the operand is stored transposed ([K, M] / [K, N])."""
+    if a.is_cuda:
+        return _ops().gemm(a, b, bias, out, a_mn, b_mn, out_f32, accumulate, max_ctas)
+    A = a.t() if a_mn else a
+    Bt = b if b_mn else b.t()
+    d = A.float() @ Bt.float()
+    if bias is not None:
+        d = d + bias.float()
+    if out is not None:
+        if accumulate:
+            out.add_(d.to(out.dtype))
+        else:
+            out.copy_(d.to(out.dtype))
+        return out
+    return d if out_f32 else d.to(a.dtype)
+
+
+def _accumulate_wgrad(param: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor) -> Optional[torch.Tensor]:
+    """dW += dy^T x into ``param.main_grad`` when present (returns None) else returns the gradient."""
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        gemm(dy2, x2, out=mg, a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+        return None
+    return gemm(dy2, x2, a_mn=True, b_mn=True, out_f32=True).to(param.dtype)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
+        ctx.in_shape = x.shape
+        y = gemm(x2, weight, bias)
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, weight, b_mn=True).reshape(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        dw = _accumulate_wgrad(weight, dy2, x2) if ctx.needs_input_grad[1] else None
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            s = dy2.float().sum(0)
+            mg = getattr(ctx.bias_ref, "main_grad", None)
+            if mg is not None:
+                mg.add_(s)
+            else:
+                db = s.to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if x.is_cuda:
+        return _Linear.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+# ----------------------------------------------------------------------------------------------- RMSNorm
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
+    """Returns ``(y, x_eff, rstd)`` with ``x_eff = x (+ residual)`` (no autograd; see models.native)."""
+    if x.is_cuda:
+        return _ops().rmsnorm_fwd(x, residual, weight, eps)
+    xe = x if residual is None else (x + residual)
+    xf = xe.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1) + eps)
+    y = (xf * rstd.unsqueeze(-1) * weight.float()).to(x.dtype)
+    return y, xe, rstd.reshape(-1)
+
+
+def rms_norm_bwd(dy, x, weight, rstd, dres_in, dw_out: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+    if x.is_cuda:
+        return _ops().rmsnorm_bwd(dy, x, weight, rstd, dres_in, dw_out, accumulate)
+    H = x.shape[-1]
+    xf, dyf, wf = x.float().reshape(-1, H), dy.float().reshape(-1, H), weight.float()
+    rs = rstd.reshape(-1, 1)
+    dot = (dyf * wf * xf).sum(-1, keepdim=True)
+    dx = rs * dyf * wf - xf * (dot * rs.pow(3) / H)
+    if dres_in is not None:
+        dx = dx + dres_in.float().reshape(-1, H)
+    dw = (dyf * xf * rs).sum(0)
+    if accumulate:
+        dw_out.add_(dw)
+    else:
+        dw_out.copy_(dw)
+    return dx.to(x.dtype).reshape(x.shape)
+
+
+# ----------------------------------------------------------------------------------------------- RoPE
+def rope_table(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables [max_pos, head_dim/2] in fp32 (HF rotate-half convention)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float64).unsqueeze(1) * inv.unsqueeze(0)
+    return ang.cos().float().to(device), ang.sin().float().to(device)
+
+
+def apply_rope_(x: torch.Tensor, positions: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
+                backward: bool = False) -> torch.Tensor:
+    """In-place rotation of ``x`` [T, heads, hd] (a strided view is fine)."""
+    if x.is_cuda:
+        _ops().rope_(x, positions.to(torch.int32), cos_t, sin_t, backward)
+        return x
+    half = x.shape[-1] // 2
+    c = cos_t[positions.long()].unsqueeze(1).to(torch.float32)
+    s = sin_t[positions.long()].unsqueeze(1).to(torch.float32)
+    if backward:
+        s = -s
+    a, b = x[..., :half].float().clone(), x[..., half:].float().clone()
+    x[..., :half] = (a * c - b * s).to(x.dtype)
+    x[..., half:] = (b * c + a * s).to(x.dtype)
+    return x
+
+
+# ----------------------------------------------------------------------------------------------- SwiGLU
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    if gate_up.is_cuda:
+        return _ops().swiglu_fwd(gate_up)
+    g, u = gate_up.chunk(2, dim=-1)
+    return F.silu(g) * u
+
+
+def swiglu_bwd(dout: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    if gate_up.is_cuda:
+        return _ops().swiglu_bwd(dout, gate_up)
+    g, u = gate_up.float().chunk(2, dim=-1)
+    d = dout.float()
+    sg = torch.sigmoid(g)
+    return torch.cat([d * u * sg * (1 + g * (1 - sg)), d * g * sg], dim=-1).to(gate_up.dtype)
+
+
+# ----------------------------------------------------------------------------------------------- embedding
+def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if weight.is_cuda:
+        return _ops().embedding_fwd(ids.reshape(-1).contiguous(), weight)
+    return F.embedding(ids.reshape(-1), weight)
+
+
+def embedding_bwd_(ids: torch.Tensor, dout: torch.Tensor, dweight: torch.Tensor) -> None:
+    if dout.is_cuda:
+        _ops().embedding_bwd_(ids.reshape(-1).contiguous(), dout.contiguous(), dweight)
+    else:
+        dweight.index_add_(0, ids.reshape(-1), dout.to(dweight.dtype))
+
+
+# ----------------------------------------------------------------------------------------------- LM head
+def _torch_logprob_entropy(hidden, weight, labels, inv_temp: float, chunk: int = 2048):
+    lps, ents, lses = [], [], []
+    for s in range(0, hidden.shape[0], chunk):
+        logits = (hidden[s : s + chunk].float() @ weight.float().t()) * inv_temp
+        lse = torch.logsumexp(logits, -1)
+        p = torch.softmax(logits, -1)
+        lps.append(logits.gather(-1, labels[s : s + chunk].unsqueeze(-1)).squeeze(-1) - lse)
+        ents.append(lse - (p * logits).sum(-1))
+        lses.append(lse)
+    return torch.cat(lps), torch.cat(ents), torch.cat(lses)
+
+
+def lmhead_logprob_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                           temperature: float = 1.0):
+    """(logprob, entropy, lse), each fp32 [T], of ``labels`` under ``softmax(hidden @ weight^T / T)``."""
+    inv_temp = 1.0 / max(float(temperature), 1e-8)
+    if hidden.is_cuda:
+        return _ops().lmhead_fwd(hidden, weight, labels.contiguous(), inv_temp)
+    return _torch_logprob_entropy(hidden, weight, labels, inv_temp)
+
+
+def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_ent, dweight_out: torch.Tensor,
+                    vocab_chunk: int = 9728):
+    """Returns d_hidden (same dtype as hidden) and accumulates d_weight into ``dweight_out`` (fp32 [V, H])."""
+    inv_temp = 1.0 / max(float(temperature), 1e-8)
+    T, H = hidden.shape
+    V = weight.shape[0]
+    if not hidden.is_cuda:
+        logits = (hidden.float() @ weight.float().t()) * inv_temp
+        p = torch.softmax(logits, -1)
+        onehot = torch.zeros_like(p).scatter_(1, labels.unsqueeze(1), 1.0)
+        dl = g_lp.unsqueeze(1) * (onehot - p)
+        if g_ent is not None:
+            ex = (lse - entropy).unsqueeze(1)
+            dl = dl - g_ent.unsqueeze(1) * p * (logits - ex)
+        dl = dl * inv_temp
+        dweight_out.add_(dl.t() @ hidden.float())
+        return (dl @ weight.float()).to(hidden.dtype)
+    ops = _ops()
+    ex = (lse - entropy).contiguous() if g_ent is not None else None
+    g_lp = g_lp.float().contiguous()
+    g_ent = g_ent.float().contiguous() if g_ent is not None else None
+    dh = torch.zeros(T, H, device=hidden.device, dtype=torch.float32)
+    buf = torch.empty(T, min(vocab_chunk, V), device=hidden.device, dtype=hidden.dtype)
+    for v0 in range(0, V, vocab_chunk):
+        v1 = min(V, v0 + vocab_chunk)
+        wc = weight[v0:v1]
+        dl = buf[:, : v1 - v0]
+        ops.lmhead_dlogits(hidden, wc, labels, v0, inv_temp, lse, ex, g_lp, g_ent, dl)
+        # d_hidden += dl @ W[v0:v1]      (B stored [K=Vc, N=H] -> MN-major)
+        gemm(dl, wc, out=dh, b_mn=True, out_f32=True, accumulate=True)
+        # d_W[v0:v1] += dl^T @ hidden
+        gemm(dl, hidden, out=dweight_out[v0:v1], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+    return dh.to(hidden.dtype)
+
+
+# ----------------------------------------------------------------------------------------------- attention
+def _sdpa_varlen(q, k, v, cu_seqlens, scale):
+    """Causal attention over packed sequences through torch SDPA (per equal-length group)."""
+    T, nh, hd = q.shape
+    nkv = k.shape[1]
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
+    out = torch.empty_like(q)
+    uniform = len(set(lens)) == 1
+    if uniform and len(lens) > 0:
+        B, S = len(lens), lens[0]
+        qq = q.reshape(B, S, nh, hd).transpose(1, 2)
+        kk = k.reshape(B, S, nkv, hd).transpose(1, 2)
+        vv = v.reshape(B, S, nkv, hd).transpose(1, 2)
+        o = F.scaled_dot_product_attention(qq, kk, vv, is_causal=True, scale=scale, enable_gqa=nkv != nh)
+        return o.transpose(1, 2).reshape(T, nh, hd)
+    s0 = 0
+    for n in lens:
+        qq = q[s0 : s0 + n].transpose(0, 1).unsqueeze(0)
+        kk = k[s0 : s0 + n].transpose(0, 1).unsqueeze(0)
+        vv = v[s0 : s0 + n].transpose(0, 1).unsqueeze(0)
+        o = F.scaled_dot_product_attention(qq, kk, vv, is_causal=True, scale=scale, enable_gqa=nkv != nh)
+        out[s0 : s0 + n] = o.squeeze(0).transpose(0, 1)
+        s0 += n
+    return out
+
+
+_ATTN_IMPL = {"fwd": None, "bwd": None}
+
+
+def register_attention_impl(fwd=None, bwd=None) -> None:
+    """Install native varlen attention kernels (called by ops.attention when the library provides them)."""
+    if fwd is not None:
+        _ATTN_IMPL["fwd"] = fwd
+    if bwd is not None:
+        _ATTN_IMPL["bwd"] = bwd
+
+
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
+    """Causal GQA attention over packed sequences. q [T, nh, hd], k/v [T, nkv, hd]. Returns (out, lse|None)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and _ATTN_IMPL["fwd"] is not None:
+        return _ATTN_IMPL["fwd"](q, k, v, cu_seqlens, max_seqlen, scale)
+    return _sdpa_varlen(q, k, v, cu_seqlens, scale), None
+
+
+def attention_varlen_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
+    """Returns (dq, dk, dv)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and _ATTN_IMPL["bwd"] is not None and lse is not None:
+        return _ATTN_IMPL["bwd"](dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale)
+    with torch.enable_grad():
+        q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o = _sdpa_varlen(q_, k_, v_, cu_seqlens, scale)
+        return torch.autograd.grad(o, (q_, k_, v_), dout)
+
+
+def kv_append_(k, v, slots, k_cache, v_cache) -> None:
+    if k.is_cuda:
+        _ops().kv_append_(k, v, slots, k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1]),
+                          v_cache.view(-1, v_cache.shape[-2], v_cache.shape[-1]))
+        return
+    kc = k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1])
+    vc = v_cache.view(-1, v_cache.shape[-2], v_cache.shape[-1])
+    ok = slots >= 0
+    kc[slots[ok]] = k[ok]
+    vc[slots[ok]] = v[ok]
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_table, ctx_len, scale: Optional[float] = None):
+    """One query token per sequence against a paged cache [num_blocks, block_size, nkv, hd]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda:
+        return _ops().paged_decode(q, k_cache, v_cache, block_table, ctx_len, scale)
+    B, nh, hd = q.shape
+    bs, nkv = k_cache.shape[1], k_cache.shape[2]
+    out = torch.empty_like(q)
+    for b in range(B):
+        n = int(ctx_len[b])
+        idx = torch.arange(n)
+        rows = block_table[b, idx // bs].long() * bs + idx % bs
+        kk = k_cache.view(-1, nkv, hd)[rows].float()
+        vv = v_cache.view(-1, nkv, hd)[rows].float()
+        g = nh // nkv
+        kk = kk.repeat_interleave(g, dim=1)
+        vv = vv.repeat_interleave(g, dim=1)
+        s = torch.einsum("hd,thd->ht", q[b].float(), kk) * scale
+        p = torch.softmax(s, -1)
+        out[b] = torch.einsum("ht,thd->hd", p, vv).to(q.dtype)
+    return out
+
+
+# ----------------------------------------------------------------------------------------------- sampling
+def sample_tokens(logits: torch.Tensor, temperature: float, seeds: torch.Tensor, step: int, valid_vocab: int = 0,
+                  top_k: int = -1, top_p: float = 1.0):
+    """Returns (tokens int64 [B], logprobs fp32 [B]) — the log-prob is of the processed distribution."""
+    B, V = logits.shape
+    vv = valid_vocab if 0 < valid_vocab <= V else V
+    if logits.is_cuda and top_k <= 0 and top_p >= 1.0 and logits.dtype == torch.bfloat16:
+        inv_temp = 0.0 if temperature <= 0 else 1.0 / temperature
+        return _ops().sample(logits, vv, inv_temp, seeds, step)
+    x = logits[:, :vv].float()
+    if temperature <= 0:
+        tok = x.argmax(-1)
+        return tok, torch.log_softmax(x, -1).gather(-1, tok.unsqueeze(-1)).squeeze(-1)
+    x = x / temperature
+    if top_k > 0:
+        kth = torch.topk(x, min(top_k, vv), dim=-1).values[:, -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    if top_p < 1.0:
+        sx, si = torch.sort(x, dim=-1, descending=True)
+        cp = torch.softmax(sx, -1).cumsum(-1)
+        drop = cp - torch.softmax(sx, -1) > top_p
+        sx = sx.masked_fill(drop, float("-inf"))
+        x = torch.full_like(x, float("-inf")).scatter(1, si, sx)
+    lp = torch.log_softmax(x, -1)
+    gen = torch.Generator(device=x.device)
+    gen.manual_seed(int(seeds[0].item()) * 1000003 + int(step))
+    tok = torch.multinomial(lp.exp(), 1, generator=gen).squeeze(-1)
+    return tok, lp.gather(-1, tok.unsqueeze(-1)).squeeze(-1)
+
+
+# ----------------------------------------------------------------------------------------------- advantages
+def grpo_advantage(rewards: torch.Tensor, mask: torch.Tensor, group: torch.Tensor, num_groups: int,
+                   eps: float = 1e-6, norm_by_std: bool = True):
+    """Device GRPO outcome advantage. ``group`` is an int tensor of group ids in [0, num_groups)."""
+    if rewards.is_cuda:
+        return _ops().grpo_advantage(rewards.float().contiguous(), mask.float().contiguous(),
+                                     group.to(torch.int32).contiguous(), num_groups, eps, norm_by_std)
+    scores = rewards.float().sum(-1)
+    adv = torch.zeros_like(scores)
+    for g in range(num_groups):
+        sel = group == g
+        n = int(sel.sum())
+        if n == 0:
+            continue
+        mean = scores[sel].mean() if n > 1 else scores.new_zeros(())
+        std = scores[sel].std() if n > 1 else scores.new_ones(())
+        adv[sel] = (scores[sel] - mean) / (std + eps) if norm_by_std else scores[sel] - mean
+    return adv.unsqueeze(-1) * mask.float(), scores
+
+
+def gae_advantage(rewards, values, mask, gamma: float, lam: float, whiten: bool = True):
+    if rewards.is_cuda:
+        return _ops().gae(rewards.float().contiguous(), values.float().contiguous(), mask.float().contiguous(),
+                          gamma, lam, whiten)
+    from ..trainer.ppo import core_algos
+
+    return core_algos.compute_gae_advantage_return(rewards, values, mask, gamma, lam)
