@@ -84,6 +84,7 @@ class DecoderModel:
         self.recompute = recompute
         self.pre_layer_hook = pre_layer_hook
         self.post_layer_backward_hook = post_layer_backward_hook
+        self.kv_hook: Optional[Callable[[int, torch.Tensor, torch.Tensor], None]] = None  # prefill: receives rotated K, V
         self.device = params.flat.device
         self._rope_len = 0
         self._cos = self._sin = None
@@ -109,7 +110,7 @@ class DecoderModel:
         return batch.cu_seqlens_cpu
 
     # ------------------------------------------------------------------------------------ attention block
-    def _attn_fwd(self, W, h1, batch: PackedBatch, S: Optional[dict]):
+    def _attn_fwd(self, W, h1, batch: PackedBatch, S: Optional[dict], layer_idx: int = -1):
         cfg = self.cfg
         T = h1.shape[0]
         nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
@@ -127,6 +128,8 @@ class DecoderModel:
                 S.update(q_pre=qp, k_pre=kp, rstd_q=rq, rstd_k=rk)
         F.apply_rope_(q, batch.positions, self._cos, self._sin)
         F.apply_rope_(k, batch.positions, self._cos, self._sin)
+        if self.kv_hook is not None:
+            self.kv_hook(layer_idx, k, v)
         cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["fwd"] is not None else self._cu_cpu(batch)
         attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
         attn2 = attn.reshape(T, Q)
@@ -281,7 +284,7 @@ class DecoderModel:
         W = self.params.layer(i)
         eps = self.cfg.rms_norm_eps
         h1, x, rstd1 = F.rms_norm(a, W["input_layernorm.weight"], eps, residual=r)
-        o = self._attn_fwd(W, h1, batch, S)
+        o = self._attn_fwd(W, h1, batch, S, i)
         h2, x2, rstd2 = F.rms_norm(o, W["post_attention_layernorm.weight"], eps, residual=x)
         d = self._mlp_fwd(W, h2, S)
         if S is not None:

@@ -372,6 +372,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
+// Device address of the status word, resolved once (outside any stream capture).
+static int* status_ptr() {
+  static int* p = nullptr;
+  if (p == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_gemm_status);
+  return p;
+}
+
 // --------------------------------------------------------------------------- launcher
 template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI = EPI_STORE>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
@@ -416,8 +423,7 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
   if (!b_mn) ok = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
   else       ok = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return -3;
-  int* status = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
+  int* status = status_ptr();
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
@@ -489,8 +495,7 @@ extern "C" int vb_lmhead_fwd(const void* hidden, const void* weight, const long 
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, hidden, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, H, ldh, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
   if (!make_tmap_2d(&tb, weight, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, V, H, ldw, BK, 256, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
-  int* status = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
+  int* status = status_ptr();
   GemmParams p{};
   p.M = T; p.N = V; p.K = H; p.status = status;
   p.labels = labels; p.label_offset = 0; p.inv_temp = inv_temp; p.partial = partial; p.label_logit = label_logit;
@@ -511,8 +516,7 @@ extern "C" int vb_lmhead_dlogits(const void* hidden, const void* weight_chunk, c
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, hidden, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, H, ldh, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
   if (!make_tmap_2d(&tb, weight_chunk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Vc, H, ldw, BK, 256, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
-  int* status = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status);
+  int* status = status_ptr();
   GemmParams p{};
   p.M = T; p.N = Vc; p.K = H; p.D = dlogits; p.ldd = ldd; p.status = status;
   p.labels = labels; p.label_offset = v0; p.inv_temp = inv_temp;

@@ -371,7 +371,7 @@ def sample_tokens(logits: torch.Tensor, temperature: float, seeds: torch.Tensor,
         x = torch.full_like(x, float("-inf")).scatter(1, si, sx)
     lp = torch.log_softmax(x, -1)
     gen = torch.Generator(device=x.device)
-    gen.manual_seed(int(seeds[0].item()) * 1000003 + int(step))
+    gen.manual_seed((int(seeds[0].item()) * 1000003 + int(step)) % (2**63 - 1))
     tok = torch.multinomial(lp.exp(), 1, generator=gen).squeeze(-1)
     return tok, lp.gather(-1, tok.unsqueeze(-1)).squeeze(-1)
 

@@ -1,0 +1,1 @@
+from .base import *  # noqa: F401,F403

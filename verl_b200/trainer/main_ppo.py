@@ -1,0 +1,120 @@
+"""Command-line entry point of the PPO-family trainers.
+
+    python -m verl_b200.trainer.main_ppo key=value ...                       # one process: controller + workers
+    torchrun --nproc-per-node 8 -m verl_b200.trainer.main_ppo key=value ...   # one process per GPU (SPMD controller)
+
+Parity target: ``verl/trainer/main_ppo.py`` (:34-196) and ``main_ppo_v0.py`` (``TaskRunner.run`` :151-234).
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from typing import Optional, Sequence
+
+from ..utils.config import DictConfig, load_config, validate_config
+from ..utils.device import auto_set_device, get_device_name
+from .config import CONFIG_DIR
+from .ppo.utils import Role, need_critic, need_reference_policy
+
+__all__ = ["main", "run_ppo", "TaskRunner", "create_rl_dataset", "create_rl_sampler"]
+
+from ..utils.dataset.rl_dataset import create_rl_dataset, create_rl_sampler  # noqa: E402  (re-exported like the reference)
+
+
+def _select_worker_group(config):
+    from ..single_controller.local import InProcessWorkerGroup, MultiprocessWorkerGroup, SPMDWorkerGroup
+
+    kind = config.trainer.get("worker_group", "auto")
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    n = int(config.trainer.n_gpus_per_node) * int(config.trainer.nnodes)
+    if kind == "auto":
+        kind = "spmd" if (world_env > 1 or n == 1) else "multiprocess"
+    if kind == "spmd":
+        return SPMDWorkerGroup, {}
+    if kind == "multiprocess":
+        return MultiprocessWorkerGroup, {"device": get_device_name()}
+    if kind == "inprocess":
+        return InProcessWorkerGroup, {}
+    if kind == "ray":
+        from ..single_controller.ray import RayWorkerGroup
+
+        return RayWorkerGroup, {}
+    raise ValueError(f"unknown trainer.worker_group={kind}")
+
+
+class TaskRunner:
+    """Builds tokenizer, reward functions, datasets, resource pools and the trainer, then runs ``fit``."""
+
+    def __init__(self):
+        self.role_worker_mapping = {}
+        self.mapping = {}
+
+    def add_actor_rollout_worker(self, config):
+        from ..workers.engine_workers import ActorRolloutRefWorker
+
+        self.role_worker_mapping[Role.ActorRollout] = ActorRolloutRefWorker
+        self.mapping[Role.ActorRollout] = "global_pool"
+        return ActorRolloutRefWorker
+
+    def add_critic_worker(self, config):
+        from ..workers.engine_workers import CriticWorker
+
+        self.role_worker_mapping[Role.Critic] = CriticWorker
+        self.mapping[Role.Critic] = "global_pool"
+
+    def init_resource_pool_mgr(self, config):
+        from .ppo.ray_trainer import ResourcePoolManager
+
+        spec = {"global_pool": [int(config.trainer.n_gpus_per_node)] * int(config.trainer.nnodes)}
+        return ResourcePoolManager(resource_pool_spec=spec, mapping=self.mapping)
+
+    def run(self, config):
+        from ..utils.tokenizer import hf_tokenizer
+        from .ppo.ray_trainer import RayPPOTrainer
+        from .ppo.reward import load_reward_manager
+
+        auto_set_device(config)
+        validate_config(config, use_reference_policy=need_reference_policy(config), use_critic=need_critic(config))
+        self.add_actor_rollout_worker(config)
+        if need_critic(config):
+            self.add_critic_worker(config)
+        path = config.actor_rollout_ref.model.path
+        tokenizer = hf_tokenizer(path, trust_remote_code=config.data.get("trust_remote_code", False)) if os.path.isdir(str(path)) else None
+        reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
+        val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
+        wg_cls, wg_kwargs = _select_worker_group(config)
+        pool_mgr = self.init_resource_pool_mgr(config)
+        if getattr(wg_cls, "is_spmd", False):
+            from ..utils.distributed import initialize_global_process_group
+
+            initialize_global_process_group()
+        trainer = RayPPOTrainer(config=config, tokenizer=tokenizer, role_worker_mapping=self.role_worker_mapping,
+                                resource_pool_manager=pool_mgr, ray_worker_group_cls=wg_cls, reward_fn=reward_fn,
+                                val_reward_fn=val_reward_fn, device_name=config.trainer.device, worker_group_kwargs=wg_kwargs)
+        trainer.init_workers()
+        trainer.fit()
+        return trainer
+
+
+def run_ppo(config, task_runner_class=None):
+    runner = (task_runner_class or TaskRunner)()
+    return runner.run(config)
+
+
+def main(argv: Optional[Sequence[str]] = None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    cfg_dir, cfg_name, overrides = CONFIG_DIR, "ppo_trainer", []
+    for a in argv:
+        if a.startswith("--config-path="):
+            cfg_dir = a.split("=", 1)[1]
+        elif a.startswith("--config-name="):
+            cfg_name = a.split("=", 1)[1]
+        else:
+            overrides.append(a)
+    config = load_config(cfg_dir, cfg_name, overrides)
+    return run_ppo(config)
+
+
+if __name__ == "__main__":
+    main()

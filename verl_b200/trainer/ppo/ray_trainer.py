@@ -1,0 +1,539 @@
+"""PPO / GRPO / REINFORCE++ / RLOO trainer: the single-controller dataflow.
+
+The class keeps the reference's name although Ray is only one of the worker-group backends: the driver logic is
+backend-agnostic and talks to worker groups through ``@register``-ed methods carrying ``DataProto`` batches.
+Under ``torchrun`` the controller-replicated ``SPMDWorkerGroup`` keeps every batch on the GPU that produced it.
+
+Parity target: ``verl/trainer/ppo/ray_trainer.py`` (``apply_kl_penalty`` :78, ``compute_response_mask`` :120,
+``compute_advantage`` :187-282, ``RayPPOTrainer`` :286: ``_validate`` :596, ``init_workers`` :772,
+``_save_checkpoint`` :983, ``_load_checkpoint`` :1052, ``_balance_batch`` :1182, ``fit`` :1405-1823).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import time
+import uuid
+from collections import defaultdict
+from copy import deepcopy
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ...protocol import DataProto, pad_dataproto_to_divisor, unpad_dataproto
+from ...single_controller.base import ClassWithInitArgs, ResourcePool
+from ...utils import torch_functional as VF
+from ...utils.checkpoint.checkpoint_manager import find_latest_ckpt_path, should_save_ckpt_esi
+from ...utils.profiler import marked_timer
+from ...utils.seqlen_balancing import calculate_workload, get_seqlen_balanced_partitions, log_seqlen_unbalance
+from ...utils.tracking import Tracking, ValidationGenerationsLogger
+from . import core_algos
+from .core_algos import AdvantageEstimator, agg_loss
+from .metric_utils import (compute_data_metrics, compute_throughout_metrics, compute_timing_metrics,
+                           process_validation_metrics, reduce_metrics)
+from .utils import Role, need_critic, need_reference_policy
+
+__all__ = ["RayPPOTrainer", "ResourcePoolManager", "apply_kl_penalty", "compute_response_mask", "compute_advantage"]
+
+
+@dataclass
+class ResourcePoolManager:
+    """Named resource pools and the role -> pool mapping."""
+
+    resource_pool_spec: dict
+    mapping: dict
+    resource_pool_dict: dict = field(default_factory=dict)
+
+    def create_resource_pool(self) -> None:
+        for name, procs in self.resource_pool_spec.items():
+            self.resource_pool_dict[name] = ResourcePool(process_on_nodes=list(procs), max_colocate_count=3)
+
+    def get_resource_pool(self, role) -> ResourcePool:
+        return self.resource_pool_dict[self.mapping[role]]
+
+    def get_n_gpus(self) -> int:
+        return sum(n for procs in self.resource_pool_spec.values() for n in procs)
+
+
+def apply_kl_penalty(data: DataProto, kl_ctrl, kl_penalty: str = "kl"):
+    """token_level_rewards = token_level_scores - beta * KL(old || ref); updates the adaptive controller."""
+    mask = data.batch["response_mask"]
+    scores = data.batch["token_level_scores"]
+    bsz = data.batch.batch_size[0]
+    kld = core_algos.kl_penalty(data.batch["old_log_probs"], data.batch["ref_log_prob"], kl_penalty=kl_penalty) * mask
+    beta = kl_ctrl.value
+    data.batch["token_level_rewards"] = scores - beta * kld
+    current = torch.mean(VF.masked_mean(kld, mask=mask, axis=-1), dim=0).item()
+    kl_ctrl.update(current_kl=current, n_steps=bsz)
+    return data, {"actor/reward_kl_penalty": current, "actor/reward_kl_penalty_coeff": beta}
+
+
+def compute_response_mask(data: DataProto) -> torch.Tensor:
+    R = data.batch["responses"].size(1)
+    return data.batch["attention_mask"][:, -R:]
+
+
+def compute_advantage(data: DataProto, adv_estimator, gamma: float = 1.0, lam: float = 1.0, num_repeat: int = 1,
+                      norm_adv_by_std_in_grpo: bool = True, config=None) -> DataProto:
+    """Fill ``advantages`` / ``returns`` with the configured estimator (device kernels for GAE and GRPO when the
+    batch lives on a GPU)."""
+    if "response_mask" not in data.batch.keys():
+        data.batch["response_mask"] = compute_response_mask(data)
+    mask = data.batch["response_mask"]
+    rewards = data.batch["token_level_rewards"]
+    name = adv_estimator.value if isinstance(adv_estimator, AdvantageEstimator) else str(adv_estimator)
+    if name == "gae":
+        if rewards.is_cuda:
+            from ...ops import functional as OF
+
+            adv, ret = OF.gae_advantage(rewards, data.batch["values"], mask, gamma, lam, whiten=True)
+        else:
+            adv, ret = core_algos.compute_gae_advantage_return(rewards, data.batch["values"], mask.to(rewards.dtype), gamma, lam)
+        data.batch["advantages"], data.batch["returns"] = adv, ret
+        if config is not None and config.get("use_pf_ppo", False):
+            data = core_algos.compute_pf_ppo_reweight_data(data, config.pf_ppo.get("reweight_method"),
+                                                           config.pf_ppo.get("weight_pow"))
+        return data
+    if name == "grpo" and rewards.is_cuda:
+        from ...ops import functional as OF
+        from ...utils.groupwise import as_torch_index
+
+        g = as_torch_index(data.non_tensor_batch["uid"], device=rewards.device)
+        adv, _ = OF.grpo_advantage(rewards, mask, g, int(g.max().item()) + 1, 1e-6, norm_adv_by_std_in_grpo)
+        data.batch["advantages"], data.batch["returns"] = adv, adv
+        return data
+    fn = core_algos.get_adv_estimator_fn(name)
+    kwargs: dict[str, Any] = dict(token_level_rewards=rewards, response_mask=mask.to(rewards.dtype), config=config)
+    if "uid" in data.non_tensor_batch:
+        kwargs["index"] = data.non_tensor_batch["uid"]
+    if "reward_baselines" in data.batch.keys():
+        kwargs["reward_baselines"] = data.batch["reward_baselines"]
+    if name in ("grpo", "grpo_vectorized", "gdpo", "grpo_passk"):
+        kwargs["norm_adv_by_std_in_grpo"] = norm_adv_by_std_in_grpo
+    if name == "gdpo":
+        kwargs["non_tensor_batch"] = data.non_tensor_batch
+    if name in ("optimal_token_baseline", "tir_optimal_token_baseline"):
+        kwargs["old_log_probs"] = data.batch["old_log_probs"]
+        kwargs["sum_pi_squared"] = data.batch["sum_pi_squared"]
+        if "rollout_is_weights" in data.batch.keys():
+            kwargs["rollout_is_weights"] = data.batch["rollout_is_weights"]
+    if name in ("reinforce_plus_plus", "remax"):
+        kwargs.pop("index", None)
+    adv, ret = fn(**kwargs)
+    data.batch["advantages"], data.batch["returns"] = adv, ret
+    return data
+
+
+class RayPPOTrainer:
+    def __init__(self, config, tokenizer=None, role_worker_mapping: Optional[dict] = None,
+                 resource_pool_manager: Optional[ResourcePoolManager] = None, ray_worker_group_cls=None, processor=None,
+                 reward_fn=None, val_reward_fn=None, train_dataset=None, val_dataset=None, collate_fn=None,
+                 train_sampler=None, device_name: Optional[str] = None, worker_group_kwargs: Optional[dict] = None):
+        self.config = config
+        self.tokenizer = tokenizer
+        self.processor = processor
+        self.reward_fn = reward_fn
+        self.val_reward_fn = val_reward_fn
+        self.role_worker_mapping = role_worker_mapping or {}
+        self.resource_pool_manager = resource_pool_manager
+        if ray_worker_group_cls is None:
+            from ...single_controller.local import SPMDWorkerGroup
+
+            ray_worker_group_cls = SPMDWorkerGroup
+        self.ray_worker_group_cls = ray_worker_group_cls
+        self.worker_group_kwargs = worker_group_kwargs or {}
+        self.spmd = bool(getattr(ray_worker_group_cls, "is_spmd", False))
+        self.device_name = device_name or config.trainer.get("device", "cuda")
+        self.use_reference_policy = need_reference_policy(config)
+        self.use_critic = need_critic(config)
+        self.use_rm = False
+        self.ref_in_actor = False
+        self.hybrid_engine = True
+        self.global_steps = 0
+        self.validation_generations_logger = ValidationGenerationsLogger(
+            project_name=config.trainer.get("project_name", "verl_b200"), experiment_name=config.trainer.get("experiment_name", "run"))
+        if config.algorithm.get("use_kl_in_reward", False):
+            self.kl_ctrl_in_reward = core_algos.get_kl_controller(config.algorithm.kl_ctrl)
+        self._create_dataloader(train_dataset, val_dataset, collate_fn, train_sampler)
+
+    # ------------------------------------------------------------------------------------ data
+    def _dp_rank_world(self):
+        if self.spmd and dist.is_initialized():
+            return dist.get_rank(), dist.get_world_size()
+        return 0, 1
+
+    def _create_dataloader(self, train_dataset, val_dataset, collate_fn, train_sampler) -> None:
+        from ...utils.dataset.rl_dataset import collate_fn as default_collate
+        from ...utils.dataset.rl_dataset import create_rl_dataset, create_rl_sampler
+        from ...utils.dataset.stateful import StatefulDataLoader
+
+        cfg = self.config
+        if train_dataset is None:
+            train_dataset = create_rl_dataset(cfg.data.get("train_files"), cfg.data, self.tokenizer, self.processor, is_train=True)
+        if val_dataset is None and cfg.data.get("val_files"):
+            val_dataset = create_rl_dataset(cfg.data.get("val_files"), cfg.data, self.tokenizer, self.processor, is_train=False)
+        self.train_dataset, self.val_dataset = train_dataset, val_dataset
+        collate_fn = collate_fn or default_collate
+        rank, world = self._dp_rank_world()
+        gbs = int(cfg.data.get("gen_batch_size", cfg.data.train_batch_size))
+        assert gbs % world == 0, f"train_batch_size {gbs} must be divisible by the data-parallel world {world}"
+        if train_sampler is None:
+            train_sampler = create_rl_sampler(cfg.data, train_dataset, rank=rank, world=world)
+        self.train_dataloader = StatefulDataLoader(train_dataset, batch_size=gbs // world, sampler=train_sampler,
+                                                   collate_fn=collate_fn, drop_last=True,
+                                                   num_workers=int(cfg.data.get("dataloader_num_workers", 0)))
+        self.val_dataloader = None
+        if val_dataset is not None and len(val_dataset) > 0:
+            vbs = cfg.data.get("val_batch_size") or len(val_dataset)
+            self.val_dataloader = StatefulDataLoader(val_dataset, batch_size=int(vbs), shuffle=bool(cfg.data.get("validation_shuffle", False)),
+                                                     collate_fn=collate_fn, drop_last=False)
+        assert len(self.train_dataloader) >= 1, "Train dataloader is empty!"
+        total = len(self.train_dataloader) * cfg.trainer.total_epochs
+        if cfg.trainer.get("total_training_steps") is not None:
+            total = int(cfg.trainer.total_training_steps)
+        self.total_training_steps = total
+        for path in ("actor_rollout_ref.actor.optim", "critic.optim"):
+            node = cfg.select(path) if hasattr(cfg, "select") else None
+            if node is not None:
+                node["total_training_steps"] = total
+
+    # ------------------------------------------------------------------------------------ workers
+    def init_workers(self) -> None:
+        """Create the worker groups (actor/rollout/ref fused in one worker per GPU; critic optional)."""
+        cfg = self.config
+        if self.resource_pool_manager is not None:
+            self.resource_pool_manager.create_resource_pool()
+        pool = (self.resource_pool_manager.get_resource_pool(Role.ActorRollout)
+                if self.resource_pool_manager is not None and Role.ActorRollout in self.resource_pool_manager.mapping else None)
+        role = "actor_rollout_ref" if self.use_reference_policy else "actor_rollout"
+        actor_cls = self.role_worker_mapping.get(Role.ActorRollout) or self.role_worker_mapping.get(Role.ActorRolloutRef)
+        if actor_cls is None:
+            from ...workers.engine_workers import ActorRolloutRefWorker as actor_cls
+        self.actor_rollout_wg = self.ray_worker_group_cls(pool, ClassWithInitArgs(actor_cls, config=cfg.actor_rollout_ref, role=role),
+                                                          **self.worker_group_kwargs)
+        self.actor_rollout_wg.init_model()
+        self.ref_policy_wg = self.actor_rollout_wg
+        self.ref_in_actor = True
+        self.critic_wg = None
+        if self.use_critic:
+            critic_cls = self.role_worker_mapping.get(Role.Critic)
+            if critic_cls is None:
+                from ...workers.engine_workers import CriticWorker as critic_cls
+            cpool = (self.resource_pool_manager.get_resource_pool(Role.Critic)
+                     if self.resource_pool_manager is not None and Role.Critic in self.resource_pool_manager.mapping else pool)
+            self.critic_wg = self.ray_worker_group_cls(cpool, ClassWithInitArgs(critic_cls, config=cfg.critic), **self.worker_group_kwargs)
+            self.critic_wg.init_model()
+        self.async_rollout_mode = False
+
+    # ------------------------------------------------------------------------------------ checkpoint
+    def _save_checkpoint(self) -> None:
+        cfg = self.config.trainer
+        root = os.path.join(cfg.default_local_dir, f"global_step_{self.global_steps}")
+        os.makedirs(root, exist_ok=True)
+        self.actor_rollout_wg.save_checkpoint(os.path.join(root, "actor"), None, self.global_steps,
+                                              cfg.get("max_actor_ckpt_to_keep"))
+        if self.use_critic:
+            self.critic_wg.save_checkpoint(os.path.join(root, "critic"), None, self.global_steps,
+                                           cfg.get("max_critic_ckpt_to_keep"))
+        rank, _ = self._dp_rank_world()
+        torch.save(self.train_dataloader.state_dict(), os.path.join(root, f"data_rank{rank}.pt" if self.spmd and rank else "data.pt"))
+        if rank == 0:
+            with open(os.path.join(cfg.default_local_dir, "latest_checkpointed_iteration.txt"), "w") as f:
+                f.write(str(self.global_steps))
+            keep = cfg.get("max_actor_ckpt_to_keep")
+            if keep:
+                from ...utils.checkpoint.checkpoint_manager import rotate_checkpoints
+
+                rotate_checkpoints(cfg.default_local_dir, int(keep))
+
+    def _load_checkpoint(self) -> int:
+        cfg = self.config.trainer
+        mode = cfg.get("resume_mode", "auto")
+        if mode == "disable":
+            return 0
+        folder = None
+        if mode == "auto":
+            folder = find_latest_ckpt_path(cfg.default_local_dir)
+        elif mode == "resume_path":
+            folder = cfg.get("resume_from_path")
+            assert folder and "global_step_" in folder, "resume ckpt must specify the global_steps"
+        if folder is None:
+            if mode == "auto":
+                print("Training from scratch")
+            return 0
+        print(f"Load from checkpoint folder: {folder}")
+        self.global_steps = int(str(folder).split("global_step_")[-1])
+        self.actor_rollout_wg.load_checkpoint(os.path.join(folder, "actor"), None, cfg.get("del_local_ckpt_after_load", False))
+        if self.use_critic:
+            self.critic_wg.load_checkpoint(os.path.join(folder, "critic"), None, cfg.get("del_local_ckpt_after_load", False))
+        rank, _ = self._dp_rank_world()
+        dpath = os.path.join(folder, f"data_rank{rank}.pt" if self.spmd and rank else "data.pt")
+        if os.path.exists(dpath):
+            self.train_dataloader.load_state_dict(torch.load(dpath, weights_only=False))
+        return self.global_steps
+
+    # ------------------------------------------------------------------------------------ helpers
+    def _balance_batch(self, batch: DataProto, metrics: dict, logging_prefix: str = "global_seqlen") -> None:
+        """Reorder so that equal-sized data-parallel chunks carry equal attention+linear workload."""
+        world = self.actor_rollout_wg.world_size
+        if world <= 1:
+            return
+        lens = batch.batch["attention_mask"].view(len(batch), -1).sum(-1)
+        cost = calculate_workload(lens).tolist()
+        parts = get_seqlen_balanced_partitions(cost, k_partitions=world, equal_size=True)
+        for p in parts:
+            p.sort(key=lambda i: cost[i])
+        idx = torch.tensor([j for p in parts for j in p])
+        batch.reorder(idx)
+        metrics.update(log_seqlen_unbalance(lens.tolist(), parts, logging_prefix))
+
+    def _get_gen_batch(self, batch: DataProto) -> DataProto:
+        reward_keys = {"data_source", "reward_model", "extra_info", "uid"} & set(batch.non_tensor_batch)
+        pop_keys = [k for k in ("input_ids", "attention_mask", "position_ids") if k in batch.batch.keys()]
+        non_pop = [k for k in batch.non_tensor_batch if k not in reward_keys]
+        gen = batch.pop(batch_keys=pop_keys, non_tensor_batch_keys=non_pop)
+        for k in reward_keys:
+            gen.non_tensor_batch[k] = batch.non_tensor_batch[k]
+        return gen
+
+    def _compute_reward(self, batch: DataProto, fn) -> tuple[torch.Tensor, dict]:
+        if "rm_scores" in batch.batch.keys():
+            return batch.batch["rm_scores"], {}
+        res = fn(batch, return_dict=True)
+        if isinstance(res, dict):
+            return res["reward_tensor"], res.get("reward_extra_info", {})
+        return res, {}
+
+    def _allreduce_metrics(self, metrics: dict) -> dict:
+        """SPMD mode: every rank holds metrics of its shard; average them so all ranks log the global value."""
+        _, world = self._dp_rank_world()
+        if world <= 1 or not metrics:
+            return metrics
+        keys = sorted(k for k, v in metrics.items() if isinstance(v, (int, float, np.floating, np.integer)))
+        dev = "cuda" if self.device_name == "cuda" and torch.cuda.is_available() else "cpu"
+        t = torch.tensor([float(metrics[k]) for k in keys], dtype=torch.float64, device=dev)
+        mx, mn = t.clone(), t.clone()
+        dist.all_reduce(t)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        out = dict(metrics)
+        for i, k in enumerate(keys):
+            leaf = k.split("/")[-1]
+            out[k] = float(mx[i]) if leaf == "max" or k.startswith("timing_s/") or k == "perf/time_per_step" else \
+                float(mn[i]) if leaf == "min" else float(t[i]) if k == "perf/total_num_tokens" else float(t[i] / world)
+        return out
+
+    # ------------------------------------------------------------------------------------ validation
+    def _validate(self) -> dict:
+        if self.val_dataloader is None or self.val_reward_fn is None:
+            return {}
+        rewards_all, sources, uids = [], [], []
+        extra: dict[str, list] = defaultdict(list)
+        n = int(self.config.actor_rollout_ref.rollout.val_kwargs.get("n", 1))
+        for batch_dict in self.val_dataloader:
+            batch = DataProto.from_single_dict(batch_dict)
+            if "uid" not in batch.non_tensor_batch:
+                batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
+            batch = batch.repeat(n, interleave=True)
+            gen = self._get_gen_batch(batch)
+            gen.meta_info = {"do_sample": bool(self.config.actor_rollout_ref.rollout.val_kwargs.get("do_sample", False)),
+                             "validate": True, "global_steps": self.global_steps}
+            gen = self._to_device(gen)
+            padded, pad = pad_dataproto_to_divisor(gen, max(1, self.actor_rollout_wg.world_size))
+            out = unpad_dataproto(self.actor_rollout_wg.generate_sequences(padded), pad)
+            batch = batch.union(out)
+            reward, info = self._compute_reward(batch, self.val_reward_fn)
+            scores = reward.sum(-1).cpu().tolist()
+            rewards_all.extend(scores)
+            extra["reward"].extend(scores)
+            for k, v in info.items():
+                extra[k].extend(list(v))
+            sources.extend(batch.non_tensor_batch.get("data_source", np.array(["unknown"] * len(scores), dtype=object)).tolist())
+            uids.extend(batch.non_tensor_batch["uid"].tolist())
+        stats = process_validation_metrics(sources, uids, dict(extra))
+        out = {}
+        for ds, by_var in stats.items():
+            core = "acc" if "acc" in by_var else "reward"
+            for var, ms in by_var.items():
+                for name, val in ms.items():
+                    sec = "val-core" if var == core and (name.startswith("mean@") or name.startswith("maj@") or name.startswith("best@")) else "val-aux"
+                    out[f"{sec}/{ds}/{var}/{name}"] = val
+        return out
+
+    def _to_device(self, data: DataProto) -> DataProto:
+        """Stage a host batch onto this rank's GPU (pinned host memory, asynchronous copy)."""
+        if self.device_name != "cuda" or not torch.cuda.is_available() or not self.spmd or data.batch is None:
+            return data
+        dev = torch.device("cuda", torch.cuda.current_device())
+        for k in list(data.batch.keys()):
+            v = data.batch[k]
+            if isinstance(v, torch.Tensor) and not v.is_cuda:
+                data.batch[k] = v.pin_memory().to(dev, non_blocking=True)
+        return data
+
+    # ------------------------------------------------------------------------------------ main loop
+    def fit(self) -> None:
+        cfg = self.config
+        rank, world = self._dp_rank_world()
+        logger = Tracking(project_name=cfg.trainer.get("project_name", "verl_b200"),
+                          experiment_name=cfg.trainer.get("experiment_name", "run"),
+                          default_backend=cfg.trainer.get("logger", ["console"]) if rank == 0 else [],
+                          config=cfg)
+        self.global_steps = 0
+        self._load_checkpoint()
+        self.actor_rollout_wg.update_weights(self.global_steps)
+        if self.val_reward_fn is not None and cfg.trainer.get("val_before_train", False):
+            val = self._validate()
+            if val:
+                logger.log(data=val, step=self.global_steps)
+            if cfg.trainer.get("val_only", False):
+                return
+        self.global_steps += 1
+        last_val = None
+        for epoch in range(cfg.trainer.total_epochs):
+            for batch_dict in self.train_dataloader:
+                metrics, timing_raw = self.train_step(batch_dict)
+                is_last = self.global_steps >= self.total_training_steps
+                tf = cfg.trainer.get("test_freq", -1)
+                if self.val_reward_fn is not None and tf and tf > 0 and (is_last or self.global_steps % tf == 0):
+                    with marked_timer("testing", timing_raw):
+                        last_val = self._validate()
+                    metrics.update(last_val)
+                sf = cfg.trainer.get("save_freq", -1)
+                esi = should_save_ckpt_esi(max_steps_duration=timing_raw.get("step", 0.0),
+                                           redundant_time=cfg.trainer.get("esi_redundant_time", 0))
+                if sf and sf > 0 and (is_last or self.global_steps % sf == 0 or esi):
+                    with marked_timer("save_checkpoint", timing_raw):
+                        self._save_checkpoint()
+                metrics["training/global_step"] = self.global_steps
+                metrics["training/epoch"] = epoch
+                logger.log(data=metrics, step=self.global_steps)
+                self.global_steps += 1
+                if is_last:
+                    if last_val:
+                        print(f"Final validation metrics: {last_val}")
+                    return
+
+    def train_step(self, batch_dict: dict) -> tuple[dict, dict]:
+        """One PPO/GRPO step on one batch of prompts: rollout -> reward -> log-probs -> advantage -> updates."""
+        cfg = self.config
+        algo = cfg.algorithm
+        rank, world = self._dp_rank_world()
+        metrics: dict[str, Any] = {}
+        timing_raw: dict[str, float] = {}
+        n_gpus = self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager is not None else world
+        rollout_cfg = cfg.actor_rollout_ref.rollout
+        with marked_timer("step", timing_raw):
+            batch = DataProto.from_single_dict(batch_dict)
+            batch.meta_info["temperature"] = rollout_cfg.temperature
+            if "uid" not in batch.non_tensor_batch:
+                batch.non_tensor_batch["uid"] = np.array([f"{rank}-{self.global_steps}-{i}" for i in range(len(batch))], dtype=object)
+            gen_batch = self._get_gen_batch(batch)
+            gen_batch.meta_info = {"global_steps": self.global_steps, "temperature": rollout_cfg.temperature}
+            gen_batch = gen_batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
+            gen_batch = self._to_device(gen_batch)
+            with marked_timer("gen", timing_raw, color="red"):
+                gen_out = self.actor_rollout_wg.generate_sequences(gen_batch)
+                timing_raw.update({f"gen/{k}": v for k, v in gen_out.meta_info.pop("timing", {}).items()})
+                gen_out.meta_info.pop("rollout_stats", None)
+            if str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX"):
+                with marked_timer("gen_max", timing_raw, color="purple"):
+                    base = deepcopy(gen_batch)
+                    base.meta_info["do_sample"] = False
+                    base_out = self.actor_rollout_wg.generate_sequences(base)
+                    tmp = batch.repeat(rollout_cfg.n, interleave=True).union(base_out)
+                    rb, _ = self._compute_reward(tmp, self.reward_fn)
+                    batch.batch = None
+                    baseline = rb.sum(-1)
+            batch = batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
+            batch = batch.union(gen_out)
+            if str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX"):
+                batch.batch["reward_baselines"] = baseline
+            if "response_mask" not in batch.batch.keys():
+                batch.batch["response_mask"] = compute_response_mask(batch)
+            if cfg.trainer.get("balance_batch", True) and not self.spmd:
+                self._balance_batch(batch, metrics)
+            batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
+            with marked_timer("reward", timing_raw, color="yellow"):
+                reward_tensor, reward_extra = self._compute_reward(batch, self.reward_fn)
+                batch.batch["token_level_scores"] = reward_tensor
+                for k, v in reward_extra.items():
+                    batch.non_tensor_batch[k] = np.asarray(v)
+            with marked_timer("old_log_prob", timing_raw, color="blue"):
+                old = self.actor_rollout_wg.compute_log_prob(batch)
+                ent = old.batch["entropys"]
+                metrics["actor/entropy"] = agg_loss(ent, batch.batch["response_mask"].to(ent.dtype),
+                                                    cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean")).item()
+                old.batch.pop("entropys")
+                batch = batch.union(old)
+                if "rollout_log_probs" in batch.batch.keys():
+                    m = batch.batch["response_mask"].bool()
+                    diff = (torch.exp(batch.batch["rollout_log_probs"]) - torch.exp(batch.batch["old_log_probs"])).abs()
+                    sel = diff[m]
+                    if sel.numel():
+                        metrics.update({"training/rollout_probs_diff_max": sel.max().item(),
+                                        "training/rollout_probs_diff_mean": sel.mean().item()})
+            if self.use_reference_policy:
+                with marked_timer("ref", timing_raw, color="olive"):
+                    batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
+            if self.use_critic:
+                with marked_timer("values", timing_raw, color="cyan"):
+                    batch = batch.union(self.critic_wg.compute_values(batch))
+            with marked_timer("adv", timing_raw, color="brown"):
+                if algo.get("use_kl_in_reward", False):
+                    batch, kl_m = apply_kl_penalty(batch, kl_ctrl=self.kl_ctrl_in_reward, kl_penalty=algo.get("kl_penalty", "kl"))
+                    metrics.update(kl_m)
+                else:
+                    batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
+                rc = algo.get("rollout_correction")
+                if rc is not None and "rollout_log_probs" in batch.batch.keys() and (rc.get("rollout_is") or rc.get("rollout_rs")):
+                    from .rollout_corr_helper import compute_rollout_correction_and_add_to_batch
+
+                    batch, rc_m = compute_rollout_correction_and_add_to_batch(batch, rc)
+                    metrics.update(rc_m)
+                batch = compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
+                                          lam=algo.get("lam", 1.0), num_repeat=rollout_cfg.n,
+                                          norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo)
+            if self.use_critic:
+                with marked_timer("update_critic", timing_raw, color="pink"):
+                    cout = self.critic_wg.update_critic(batch)
+                metrics.update(reduce_metrics(cout.meta_info["metrics"]))
+            if cfg.trainer.get("critic_warmup", 0) <= self.global_steps:
+                with marked_timer("update_actor", timing_raw, color="red"):
+                    aout = self.actor_rollout_wg.update_actor(batch)
+                metrics.update(reduce_metrics(aout.meta_info["metrics"]))
+            with marked_timer("update_weights", timing_raw, color="red"):
+                res = self.actor_rollout_wg.update_weights(self.global_steps)
+                res = res[0] if isinstance(res, list) else res
+                metrics["timing_s/update_weights_worker"] = float((res or {}).get("timing_s/update_weights", 0.0))
+            if cfg.trainer.get("rollout_data_dir"):
+                self._dump_generations(batch, cfg.trainer.rollout_data_dir)
+        metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
+        metrics.update(compute_timing_metrics(batch=batch, timing_raw=timing_raw))
+        metrics.update(compute_throughout_metrics(batch=batch, timing_raw=timing_raw, n_gpus=max(1, n_gpus if not self.spmd else 1)))
+        metrics = self._allreduce_metrics(metrics)
+        if self.spmd and world > 1:
+            metrics["perf/throughput"] = metrics["perf/total_num_tokens"] / (metrics["perf/time_per_step"] * world)
+        self.last_batch = batch
+        return metrics, timing_raw
+
+    def _dump_generations(self, batch: DataProto, dump_path: str) -> None:
+        os.makedirs(dump_path, exist_ok=True)
+        rank, _ = self._dp_rank_world()
+        scores = batch.batch["token_level_scores"].sum(-1).cpu().tolist()
+        ids_in = batch.batch["prompts"].cpu()
+        ids_out = batch.batch["responses"].cpu()
+        with open(os.path.join(dump_path, f"{self.global_steps}_rank{rank}.jsonl"), "w") as f:
+            for i in range(len(batch)):
+                rec = {"step": self.global_steps, "score": scores[i]}
+                if self.tokenizer is not None:
+                    rec["input"] = self.tokenizer.decode(ids_in[i], skip_special_tokens=True)
+                    rec["output"] = self.tokenizer.decode(ids_out[i], skip_special_tokens=True)
+                else:
+                    rec["input_ids"] = ids_in[i].tolist()
+                    rec["output_ids"] = ids_out[i].tolist()
+                f.write(json.dumps(rec, ensure_ascii=False) + "\n")

@@ -1,0 +1,78 @@
+"""Optimizer configuration. Parity target: ``verl/workers/config/optimizer.py:298-351``."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+from ...base_config import BaseConfig
+
+__all__ = ["OptimizerConfig", "FSDPOptimizerConfig", "McoreOptimizerConfig", "build_optimizer", "lr_at_step"]
+
+
+@dataclass
+class OptimizerConfig(BaseConfig):
+    _mutable_fields = {"clip_grad", "total_training_steps", "lr_warmup_steps"}
+    lr: float = 1e-6
+    lr_warmup_steps_ratio: float = 0.0
+    lr_warmup_steps: Optional[int] = -1
+    total_training_steps: int = -1
+    weight_decay: float = 0.01
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    clip_grad: float = 1.0
+    optimizer: str = "AdamW"
+    optimizer_impl: str = "verl_b200.fused"
+    lr_scheduler_type: str = "constant"  # constant | cosine | wsd
+    min_lr_ratio: float = 0.0
+    num_cycles: float = 0.5
+    override_optimizer_config: Optional[dict] = None
+
+    def __post_init__(self):
+        assert self.lr != "???", "optimizer lr must be set"
+        assert self.lr_scheduler_type in ("constant", "cosine", "wsd")
+
+
+@dataclass
+class FSDPOptimizerConfig(OptimizerConfig):
+    warmup_style: Optional[str] = None  # deprecated alias of lr_scheduler_type
+
+    def __post_init__(self):
+        if self.warmup_style is not None:
+            object.__setattr__(self, "lr_scheduler_type", self.warmup_style)
+        super().__post_init__()
+
+
+@dataclass
+class McoreOptimizerConfig(OptimizerConfig):
+    lr_warmup_init: float = 0.0
+    lr_decay_steps: Optional[int] = None
+    lr_decay_style: str = "constant"
+    min_lr: float = 0.0
+    use_distributed_optimizer: bool = True
+
+
+def lr_at_step(cfg: OptimizerConfig, step: int) -> float:
+    """Learning rate for optimizer step ``step`` (0-based)."""
+    from ...utils.torch_functional import cosine_factor, wsd_factor
+
+    total = cfg.total_training_steps if cfg.total_training_steps and cfg.total_training_steps > 0 else 1
+    warm = cfg.lr_warmup_steps if (cfg.lr_warmup_steps is not None and cfg.lr_warmup_steps >= 0) else int(
+        cfg.lr_warmup_steps_ratio * total)
+    if cfg.lr_scheduler_type == "cosine":
+        return cfg.lr * cosine_factor(step, warm, total, cfg.min_lr_ratio, cfg.num_cycles)
+    if cfg.lr_scheduler_type == "wsd":
+        return cfg.lr * wsd_factor(step, warm, total, min_ratio=cfg.min_lr_ratio)
+    return cfg.lr * (min(1.0, step / max(1, warm)) if warm > 0 else 1.0)
+
+
+def build_optimizer(parameters, config: OptimizerConfig):
+    """torch optimizer for plain ``nn.Parameter`` lists (used by the CPU reference path and LoRA adapters)."""
+    import torch
+
+    cls = getattr(torch.optim, config.optimizer)
+    kw = dict(lr=config.lr, weight_decay=config.weight_decay)
+    if "Adam" in config.optimizer:
+        kw.update(betas=tuple(config.betas), eps=config.eps)
+    kw.update(config.override_optimizer_config or {})
+    return cls(parameters, **kw)

@@ -1,0 +1,390 @@
+"""Sharded data-parallel training engine on the native sm_100a kernels.
+
+Memory plan per GPU (sized for 180 GB HBM3e):
+
+* bf16 working parameters in one flat buffer (``zero_stage=2``: full replica, shared in place with the
+  rollout engine; no parameter gather anywhere in forward/backward),
+* fp32 main-gradient flat buffer that the wgrad GEMMs accumulate into across micro-batches,
+* this rank's 1/W shard of the fp32 master weights and Adam moments.
+
+One optimizer step = reduce-scatter of the main-grad buffer (fp32, mean over data-parallel ranks) ->
+global grad-norm (one scalar all-reduce) -> fused AdamW on the shard, which also writes the new bf16
+values into the working buffer -> all-gather of the working buffer.  With ``fused_comm`` and symmetric
+memory available the reduce-scatter/AdamW/all-gather run as peer-memory kernels
+(:mod:`verl_b200.parallel.fused_optim`); otherwise the same steps use NCCL (GPU) or gloo (CPU).
+
+On CPU the engine runs the same code in fp32 over gloo, which is the oracle configuration.
+
+Parity target: ``verl/workers/engine/fsdp/transformer_impl.py`` (``FSDPEngine`` :87-1117: initialise,
+``forward_backward_batch`` :700-753, ``optimizer_step`` :764-810 with clip + non-finite skip,
+``get_per_tensor_param`` :954-1038, value-head variant :1567-1617) and the checkpoint file layout of
+``verl/utils/checkpoint/fsdp_checkpoint_manager.py:213-417``.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Any, Callable, Generator, Optional
+
+import torch
+import torch.distributed as dist
+
+from ....models.config import ModelConfig
+from ....models.decoder import DecoderModel, PackedBatch
+from ....models.weights import ALIGN, FlatParams
+from ....ops import functional as F
+from ....ops import native
+from ....utils.device import get_device_name
+from ...config.optimizer import lr_at_step
+from ..base import BaseEngine, EngineRegistry
+
+__all__ = ["NativeEngine", "NativeEngineWithLMHead", "NativeEngineWithValueHead", "pack_padded_batch"]
+
+
+def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: Optional[torch.Tensor],
+                      response_length: int):
+    """Remove padding from a [b, P+R] batch (left-padded prompt, right-padded response).
+
+    Returns ``(packed_batch, labels, resp_index, resp_valid)`` where ``labels[t]`` is the next token of packed
+    position ``t`` and ``resp_index`` [b, R] are the packed positions whose outputs predict the response
+    tokens (column ``P-1+j`` of each row), valid where ``resp_valid``.
+    """
+    b, L = input_ids.shape
+    mask = attention_mask.bool()
+    lens = mask.sum(-1)
+    lens_list = lens.tolist()  # one host sync per micro-batch
+    ids = input_ids[mask]
+    labels = torch.roll(input_ids, shifts=-1, dims=1)[mask]
+    if position_ids is None:
+        pos = (torch.cumsum(mask.to(torch.int32), -1) - 1)[mask]
+    else:
+        pos = position_ids[mask]
+    cu = torch.zeros(b + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(lens_list, dtype=torch.int32), 0)
+    batch = PackedBatch(input_ids=ids.contiguous(), positions=pos.to(torch.int32).contiguous(),
+                        cu_seqlens=cu.to(input_ids.device), max_seqlen=max(lens_list) if lens_list else 0,
+                        cu_seqlens_cpu=cu)
+    flat_index = (torch.cumsum(mask.reshape(-1).to(torch.int64), 0) - 1).view(b, L)
+    P = L - response_length
+    resp_index = flat_index[:, P - 1 : L - 1]
+    resp_valid = mask[:, P:]
+    return batch, labels.contiguous(), resp_index, resp_valid
+
+
+class NativeEngine(BaseEngine):
+    value_head = False
+
+    def __init__(self, model_config, engine_config, optimizer_config=None, checkpoint_config=None, **kwargs):
+        self.model_config = model_config
+        self.engine_config = engine_config
+        self.optimizer_config = optimizer_config
+        self.checkpoint_config = checkpoint_config
+        self.arch: ModelConfig = model_config.arch if hasattr(model_config, "arch") else model_config
+        self.device_name = get_device_name()
+        self.forward_only = bool(getattr(engine_config, "forward_only", False)) or optimizer_config is None
+        self.opt_step_count = 0
+        self.sched_step = 0
+        self._initialized = False
+        self._shared_params: Optional[FlatParams] = kwargs.get("shared_params")
+
+    # ------------------------------------------------------------------------------------ setup
+    def initialize(self) -> None:
+        if self._initialized:
+            return
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if self.device_name == "cuda":
+            self.device = torch.device("cuda", torch.cuda.current_device())
+            self.dtype = torch.bfloat16
+            native.load()
+        else:
+            self.device = torch.device("cpu")
+            self.dtype = torch.float32
+        ec = self.engine_config
+        seed = int(getattr(ec, "seed", 42))
+        if self._shared_params is not None:
+            self.params = self._shared_params
+        else:
+            self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
+                                     pad_to=self.world)
+            self._load_or_init(seed)
+        recompute = "full" if getattr(ec, "enable_gradient_checkpointing", True) else "none"
+        self.model = DecoderModel(self.arch, self.params, recompute=recompute)
+        self.shard_numel = self.params.numel // self.world
+        self.shard_lo = self.rank * self.shard_numel
+        if not self.forward_only:
+            self.params.attach_main_grad()
+            sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+            self.master = self.params.flat[sl].float().clone()
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
+            self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+            self.ctrl = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self._initialized = True
+
+    def _load_or_init(self, seed: int) -> None:
+        mc = self.model_config
+        path = getattr(mc, "local_path", None) or getattr(mc, "path", None)
+        load = bool(getattr(mc, "load_weights", True)) and path and os.path.isdir(str(path))
+        if load and self.rank == 0:
+            from ....utils.model import load_hf_weights_into
+
+            load_hf_weights_into(self.params, path)
+        elif not load:
+            self.params.init_weights(seed=seed)
+        if self.world > 1:
+            dist.broadcast(self.params.flat, src=0)
+
+    # ------------------------------------------------------------------------------------ topology
+    def get_data_parallel_size(self) -> int:
+        return self.world
+
+    def get_data_parallel_rank(self) -> int:
+        return self.rank
+
+    def get_data_parallel_group(self):
+        return None
+
+    # ------------------------------------------------------------------------------------ batching
+    def _micro_batches(self, data: dict, forward_only: bool) -> list[dict]:
+        ec = self.engine_config
+        ids = data["input_ids"]
+        n = ids.shape[0]
+        dyn = bool(data.get("use_dynamic_bsz", getattr(ec, "use_dynamic_bsz", False)))
+        if dyn:
+            budget = int(data.get("max_token_len_per_gpu") or (ec.infer_max_token_len_per_gpu if forward_only
+                                                               else ec.max_token_len_per_gpu))
+            from ....utils.seqlen_balancing import get_seqlen_balanced_partitions
+
+            lens = data["attention_mask"].sum(-1).tolist()
+            k = max(1, min(n, math.ceil(sum(lens) / budget)))
+            parts = get_seqlen_balanced_partitions(lens, k, equal_size=False)
+        else:
+            mb = data.get("micro_batch_size_per_gpu") or (ec.infer_micro_batch_size_per_gpu if forward_only
+                                                          else ec.micro_batch_size_per_gpu) or n
+            parts = [list(range(s, min(n, s + int(mb)))) for s in range(0, n, int(mb))]
+        out = []
+        for p in parts:
+            idx = torch.tensor(p, dtype=torch.int64, device=ids.device)
+            out.append({k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v)
+                        for k, v in data.items()} | {"_rows": p})
+        return out
+
+    def forward_backward_batch(self, data, loss_function: Optional[Callable] = None, forward_only: bool = False) -> dict:
+        """``data``: dict-like with padded ``input_ids``/``attention_mask``/``position_ids`` [b, P+R], ``responses``
+        [b, R] and whatever the loss function needs.  Returns ``{"model_output": {...}, "loss": ..., "metrics": ...}``
+        with per-row outputs restored to the input order."""
+        data = dict(data.items()) if not isinstance(data, dict) else data
+        data = {k: (v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in data.items()}
+        R = data["responses"].shape[1]
+        n = data["input_ids"].shape[0]
+        temperature = float(data.get("temperature", 1.0))
+        calc_entropy = bool(data.get("calculate_entropy", False))
+        # global normalisation constants for agg_loss
+        if loss_function is not None and not forward_only:
+            mask = data.get("response_mask", data["attention_mask"][:, -R:])
+            tok = mask.sum().float()
+            seqs = torch.tensor(float(n), device=self.device)
+            if self.world > 1:
+                pack = torch.stack([tok, seqs])
+                dist.all_reduce(pack)
+                tok, seqs = pack[0], pack[1]
+            data["global_batch_info"] = dict(dp_size=self.world, batch_num_tokens=tok, global_batch_size=seqs,
+                                             loss_scale_factor=data.get("loss_scale_factor"))
+        mbs = self._micro_batches(data, forward_only)
+        outs: dict[str, list] = {}
+        rows: list[int] = []
+        losses, metrics = [], {}
+        for mb in mbs:
+            out = self._forward_micro(mb, R, temperature, calc_entropy, need_grad=not forward_only)
+            rows.extend(mb["_rows"])
+            if loss_function is not None:
+                loss, m = loss_function(model_output=out, data=mb, dp_group=None)
+                if not forward_only:
+                    loss.backward()
+                losses.append(loss.detach())
+                for k, v in m.items():
+                    metrics.setdefault(k, []).append(v)
+            for k, v in out.items():
+                outs.setdefault(k, []).append(v.detach())
+        inv = torch.empty(n, dtype=torch.int64, device=self.device)
+        inv[torch.tensor(rows, dtype=torch.int64, device=self.device)] = torch.arange(n, device=self.device)
+        model_output = {k: torch.cat(v, 0)[inv] for k, v in outs.items()}
+        result = {"model_output": model_output, "metrics": metrics}
+        if losses:
+            result["loss"] = torch.stack(losses).sum()
+        return result
+
+    def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
+        batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
+                                                                  mb.get("position_ids"), R)
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad)
+        zero = torch.zeros((), dtype=lp.dtype, device=lp.device)
+        out = {"log_probs": torch.where(resp_valid, lp[resp_index], zero)}
+        if calc_entropy or need_grad:
+            out["entropy"] = torch.where(resp_valid, ent[resp_index], zero)
+        return out
+
+    # ------------------------------------------------------------------------------------ optimizer
+    def optimizer_zero_grad(self) -> None:
+        if not self.forward_only:
+            self.params.zero_grad()
+
+    def optimizer_step(self) -> float:
+        """Gradient mean over DP ranks, global-norm clip, AdamW on this rank's shard, publish new bf16 weights.
+        A non-finite gradient norm skips the update. Returns the gradient norm."""
+        oc = self.optimizer_config
+        W = self.world
+        mg = self.params.main_grad
+        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        if W > 1:
+            if self.device.type == "cuda":
+                dist.reduce_scatter_tensor(self.grad_shard, mg, op=dist.ReduceOp.AVG)
+            else:  # gloo has no reduce-scatter: all-reduce and keep this rank's slice
+                dist.all_reduce(mg)
+                self.grad_shard.copy_(mg[sl]).div_(W)
+        self.ctrl.zero_()
+        lr = lr_at_step(oc, self.sched_step)
+        self.opt_step_count += 1
+        if self.device.type == "cuda":
+            ops = native.ops()
+            ops.sumsq_(self.grad_shard, self.ctrl)
+            if W > 1:
+                dist.all_reduce(self.ctrl[:1])
+            ops.clip_coef_(self.ctrl, float(oc.clip_grad))
+            ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.params.flat[sl], self.ctrl,
+                       lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
+                       self.opt_step_count, 1.0, False)
+            norm = self.ctrl[3]
+        else:
+            ss = self.grad_shard.double().pow(2).sum()
+            if W > 1:
+                dist.all_reduce(ss)
+            norm = ss.sqrt().float()
+            if torch.isfinite(norm):
+                coef = min(1.0, float(oc.clip_grad) / (float(norm) + 1e-6)) if oc.clip_grad and oc.clip_grad > 0 else 1.0
+                g = self.grad_shard * coef
+                b1, b2 = oc.betas
+                self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+                self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+                bc1 = 1 - b1 ** self.opt_step_count
+                bc2 = 1 - b2 ** self.opt_step_count
+                self.master.mul_(1 - lr * oc.weight_decay)
+                denom = (self.exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(oc.eps)
+                self.master.addcdiv_(self.exp_avg, denom, value=-lr / bc1)
+                self.params.flat[sl].copy_(self.master.to(self.dtype))
+        self._publish_shard()
+        return float(norm)
+
+    def _publish_shard(self) -> None:
+        """All-gather this rank's updated slice of the working weights into every replica."""
+        if self.world == 1:
+            return
+        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        if self.device.type == "cuda":
+            dist.all_gather_into_tensor(self.params.flat, self.params.flat[sl].clone())
+        else:
+            parts = [self.params.flat[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
+            dist.all_gather(parts, self.params.flat[sl].clone())
+
+    def lr_scheduler_step(self) -> float:
+        self.sched_step += 1
+        return lr_at_step(self.optimizer_config, self.sched_step)
+
+    # ------------------------------------------------------------------------------------ weights
+    def get_per_tensor_param(self, **kwargs) -> Generator[tuple[str, torch.Tensor], None, None]:
+        """HF-named views of the working weights (zero-copy; every rank holds the full replica)."""
+        yield from self.params.hf_views()
+
+    def to(self, device: str, model: bool = True, optimizer: bool = True, grad: bool = True) -> None:
+        """Move optimizer state (and optionally gradients) between GPU and pinned host memory."""
+        if self.forward_only or self.device.type != "cuda":
+            return
+        tgt = torch.device(device) if device != "cuda" else self.device
+        if optimizer:
+            for name in ("master", "exp_avg", "exp_avg_sq"):
+                t = getattr(self, name)
+                if t.device != tgt:
+                    setattr(self, name, t.to(tgt, non_blocking=True))
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------------------------ checkpoint
+    def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
+                        max_ckpt_to_keep: Optional[int] = None, **kwargs) -> None:
+        os.makedirs(local_path, exist_ok=True)
+        W, r = self.world, self.rank
+        contents = list(getattr(self.checkpoint_config, "save_contents", ["model", "optimizer", "extra"]) or [])
+        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        if "model" in contents:
+            src = self.master if not self.forward_only else self.params.flat[sl].float()
+            torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.params.numel,
+                        "offsets": self.params.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
+        if "optimizer" in contents and not self.forward_only:
+            torch.save({"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "step": self.opt_step_count},
+                       os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt"))
+        if "extra" in contents:
+            torch.save({"sched_step": self.sched_step, "rng": torch.get_rng_state(),
+                        "cuda_rng": torch.cuda.get_rng_state() if self.device.type == "cuda" else None},
+                       os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt"))
+        if r == 0:
+            with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
+                json.dump({"FSDP_version": 2, "world_size": W, "layout": "verl_b200.flat", "value_head": self.value_head}, f)
+            hf_dir = os.path.join(local_path, "huggingface")
+            self.arch.save_pretrained(hf_dir)
+            if "hf_model" in contents:
+                from ....utils.model import save_hf_weights
+
+                save_hf_weights(self.params, hf_dir)
+        if W > 1:
+            dist.barrier()
+
+    def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, del_local_after_load: bool = False,
+                        **kwargs) -> None:
+        if local_path is None:
+            return
+        W, r = self.world, self.rank
+        contents = list(getattr(self.checkpoint_config, "load_contents", ["model", "optimizer", "extra"]) or [])
+        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        mp = os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt")
+        if "model" in contents and os.path.exists(mp):
+            st = torch.load(mp, map_location="cpu", weights_only=False)
+            assert st["numel"] == self.params.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
+            if not self.forward_only:
+                self.master.copy_(st["flat_shard"])
+            self.params.flat[sl].copy_(st["flat_shard"].to(self.dtype))
+            self._publish_shard()
+        op = os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt")
+        if "optimizer" in contents and not self.forward_only and os.path.exists(op):
+            st = torch.load(op, map_location="cpu", weights_only=False)
+            self.exp_avg.copy_(st["exp_avg"])
+            self.exp_avg_sq.copy_(st["exp_avg_sq"])
+            self.opt_step_count = int(st["step"])
+        ep = os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt")
+        if "extra" in contents and os.path.exists(ep):
+            st = torch.load(ep, map_location="cpu", weights_only=False)
+            self.sched_step = int(st["sched_step"])
+            torch.set_rng_state(st["rng"])
+            if st.get("cuda_rng") is not None and self.device.type == "cuda":
+                torch.cuda.set_rng_state(st["cuda_rng"])
+
+
+@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "fsdp_turbo", "native"],
+                         device=["cuda", "cpu"])
+class NativeEngineWithLMHead(NativeEngine):
+    value_head = False
+
+
+@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "fsdp_turbo", "native"],
+                         device=["cuda", "cpu"])
+class NativeEngineWithValueHead(NativeEngine):
+    """Same trunk with a scalar head; ``model_output`` carries ``values`` [b, R] aligned with the responses."""
+
+    value_head = True
+
+    def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
+        batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
+                                                                  mb.get("position_ids"), R)
+        vals = self.model.forward_values(batch, need_grad=need_grad)
+        return {"values": torch.where(resp_valid, vals[resp_index], torch.zeros((), dtype=vals.dtype, device=vals.device))}

@@ -1,0 +1,423 @@
+"""In-process rollout engine: continuous batching over a paged KV cache with a device-resident decode loop.
+
+Design (one engine per GPU, or per tensor-parallel group):
+
+* **Shared weights.** The engine reads the trainer's bf16 working parameters in place (``FlatParams``);
+  a weight update is visible to the next generation call without any copy or re-layout.
+* **Slots.** ``max_num_seqs`` sequence slots with static per-slot state tensors on the device (current
+  token, position, context length, generated count, active flag, block-table row).  A decode step runs
+  over *all* slots with static shapes, so the whole step (28 layers + LM head + sampler + state update)
+  is one CUDA graph; inactive slots cost nothing in attention (context length 0) and their GEMM rows
+  are ignored.
+* **Device-resident loop.** Sampled tokens feed the next step on the device; EOS / length termination
+  is evaluated on the device.  The host synchronises only every ``sync_interval`` steps to retire
+  finished sequences and admit waiting ones (continuous batching at that granularity).
+* **Paged KV.** Blocks of ``block_size`` tokens from one pool ``[layers, 2, blocks, block_size, kv_heads,
+  head_dim]``; a sequence reserves the blocks for ``prompt + max_new_tokens`` at admission and returns
+  them when it retires.  ``release_kv_cache`` / ``resume_kv_cache`` hand the pool's memory back to the
+  trainer between rollout phases.
+* **Prefill** runs the packed varlen forward of the training model with a hook that scatters rotated
+  K/V into the cache, in chunks of at most ``max_num_batched_tokens`` tokens.
+
+Feature parity target: how the reference drives vLLM (``verl/workers/rollout/vllm_rollout/
+vllm_async_server.py:254-720``: token-in/token-out generate, sampling params, log-probs of sampled tokens,
+max_num_seqs / max_num_batched_tokens, dummy-weight start, KV release/resume, abort).
+"""
+
+from __future__ import annotations
+
+import math
+import time
+import zlib
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from ....models.config import ModelConfig
+from ....models.decoder import DecoderModel, PackedBatch
+from ....models.weights import FlatParams
+from ....ops import functional as F
+
+__all__ = ["SamplingParams", "RequestOutput", "RolloutEngine"]
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    max_tokens: int = 128
+    ignore_eos: bool = False
+    stop_token_ids: Sequence[int] = ()
+    logprobs: bool = True
+    seed: Optional[int] = None
+    repetition_penalty: float = 1.0
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_ids: list[int]
+    token_ids: list[int]
+    log_probs: Optional[list[float]]
+    stop_reason: str  # completed | length | aborted
+    num_preempted: int = 0
+    extra_fields: dict = field(default_factory=dict)
+
+
+@dataclass
+class _Request:
+    rid: str
+    prompt: list[int]
+    params: SamplingParams
+    slot: int = -1
+    blocks: list[int] = field(default_factory=list)
+    arrival: float = 0.0
+
+
+class RolloutEngine:
+    def __init__(self, cfg: ModelConfig, params: FlatParams, *, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
+                 num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
+                 valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0):
+        self.cfg = cfg
+        self.params = params
+        self.device = params.flat.device
+        self.is_cuda = self.device.type == "cuda"
+        self.S = int(max_num_seqs)
+        self.max_batched = int(max_num_batched_tokens)
+        self.max_model_len = int(max_model_len)
+        self.bs = int(block_size)
+        self.max_blocks_per_seq = (self.max_model_len + self.bs - 1) // self.bs
+        self.eos = eos_token_id if eos_token_id is not None else cfg.eos_token_id
+        self.valid_vocab = valid_vocab_size or cfg.vocab_size
+        self.use_graph = bool(use_cuda_graph) and self.is_cuda
+        self.sync_interval = max(1, int(sync_interval))
+        self.gpu_memory_utilization = gpu_memory_utilization
+        self._num_blocks_req = num_blocks
+        self.model = DecoderModel(cfg, params, max_positions=self.max_model_len + 1)
+        self.model.kv_hook = self._prefill_kv_hook
+        self.kv: Optional[torch.Tensor] = None
+        self.free_blocks: list[int] = []
+        self._graph = None
+        self._graph_key = None
+        self._seed = seed
+        self._rid = 0
+        self.waiting: deque[_Request] = deque()
+        self.running: dict[int, _Request] = {}
+        self.finished: list[RequestOutput] = []
+        self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
+        self._alloc_state()
+        self.resume_kv_cache()
+
+    # ------------------------------------------------------------------------------------ memory
+    def kv_bytes_per_block(self) -> int:
+        c = self.cfg
+        return c.num_hidden_layers * 2 * self.bs * c.kv_size * self.params.flat.element_size()
+
+    def resume_kv_cache(self) -> None:
+        if self.kv is not None:
+            return
+        c = self.cfg
+        n = self._num_blocks_req
+        if n is None:
+            if self.is_cuda:
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = min(free - (2 << 30), int(total * self.gpu_memory_utilization))
+                n = max(self.max_blocks_per_seq, int(budget // self.kv_bytes_per_block()))
+            else:
+                n = self.S * self.max_blocks_per_seq
+            n = min(n, self.S * self.max_blocks_per_seq + 1)
+        self.num_blocks = int(n)
+        self.kv = torch.zeros(c.num_hidden_layers, 2, self.num_blocks, self.bs, c.num_key_value_heads, c.head_dim,
+                              dtype=self.params.flat.dtype, device=self.device)
+        self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
+        self._graph = None  # cache addresses changed
+
+    def release_kv_cache(self) -> None:
+        assert not self.running, "cannot release the KV cache with sequences in flight"
+        self.kv = None
+        self._graph = None
+        self.free_blocks = []
+        if self.is_cuda:
+            torch.cuda.empty_cache()
+
+    def clear_kv_cache(self) -> None:
+        """Forget all cached content (called after every weight update)."""
+        assert not self.running
+        if self.kv is not None:
+            self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
+
+    def _alloc_state(self) -> None:
+        S, dev = self.S, self.device
+        z = lambda dt: torch.zeros(S, dtype=dt, device=dev)
+        self.tok, self.pos, self.ctx, self.gen = z(torch.int64), z(torch.int32), z(torch.int32), z(torch.int32)
+        self.max_new = z(torch.int32)
+        self.active = z(torch.bool)
+        self.ignore_eos = z(torch.bool)
+        self.seeds = z(torch.int64)
+        self.block_table = torch.zeros(S, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
+        self.out_cap = 0
+        self.out_tok = self.out_lp = None
+        self.temperature = 1.0
+        self.top_k, self.top_p = -1, 1.0
+        self.free_slots = list(range(S - 1, -1, -1))
+
+    def _ensure_out(self, cap: int) -> None:
+        if cap > self.out_cap:
+            assert not self.running, "output capacity can only grow while idle"
+            self.out_cap = int(cap)
+            self.out_tok = torch.zeros(self.S, self.out_cap, dtype=torch.int64, device=self.device)
+            self.out_lp = torch.zeros(self.S, self.out_cap, dtype=torch.float32, device=self.device)
+            self._graph = None
+
+    # ------------------------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids: Sequence[int], params: SamplingParams, request_id: Optional[str] = None) -> str:
+        rid = request_id if request_id is not None else f"req-{self._rid}"
+        self._rid += 1
+        prompt = list(map(int, prompt_ids))
+        assert 0 < len(prompt) < self.max_model_len, f"prompt of {len(prompt)} tokens does not fit max_model_len"
+        p = SamplingParams(**{**params.__dict__})
+        p.max_tokens = max(1, min(p.max_tokens, self.max_model_len - len(prompt)))
+        self.waiting.append(_Request(rid, prompt, p, arrival=time.time()))
+        return rid
+
+    def abort(self, request_id: Optional[str] = None) -> list[RequestOutput]:
+        """Abort one request (or all): running sequences are retired with what they generated so far."""
+        out = []
+        if self.running:
+            self._sync_retire(force_rids=None if request_id is None else {request_id}, abort=True)
+        keep = deque()
+        for r in self.waiting:
+            if request_id is None or r.rid == request_id:
+                out.append(RequestOutput(r.rid, r.prompt, [], [], "aborted"))
+            else:
+                keep.append(r)
+        self.waiting = keep
+        self.finished.extend(out)
+        return out
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------------------------ prefill
+    def _prefill_kv_hook(self, layer: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        if self._prefill_slots is not None:
+            F.kv_append_(k, v, self._prefill_slots, self.kv[layer, 0], self.kv[layer, 1])
+
+    _prefill_slots: Optional[torch.Tensor] = None
+
+    def _admit(self) -> list[_Request]:
+        """Move waiting requests into free slots while blocks and the token budget last."""
+        batch, tokens = [], 0
+        while self.waiting and self.free_slots:
+            r = self.waiting[0]
+            need = (len(r.prompt) + r.params.max_tokens + self.bs - 1) // self.bs
+            if need > len(self.free_blocks) or (batch and tokens + len(r.prompt) > self.max_batched):
+                break
+            want = (r.params.temperature, r.params.top_k, r.params.top_p)
+            idle = not self.running and not batch
+            if idle:
+                self.temperature, self.top_k, self.top_p = want  # one sampling configuration per running wave
+                self._ensure_out(r.params.max_tokens)
+            elif want != (self.temperature, self.top_k, self.top_p) or r.params.max_tokens > self.out_cap:
+                break
+            self.waiting.popleft()
+            r.slot = self.free_slots.pop()
+            r.blocks = [self.free_blocks.pop() for _ in range(need)]
+            batch.append(r)
+            tokens += len(r.prompt)
+        return batch
+
+    @torch.no_grad()
+    def _prefill(self, reqs: list[_Request]) -> None:
+        t0 = time.time()
+        dev = self.device
+        lens = [len(r.prompt) for r in reqs]
+        ids = torch.tensor([t for r in reqs for t in r.prompt], dtype=torch.int64)
+        slot_rows, bt_rows = [], torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            bt_rows[i, : len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
+            p = torch.arange(lens[i])
+            slot_rows.append(bt_rows[i, p // self.bs].long() * self.bs + p % self.bs)
+        if self.is_cuda:
+            ids, slot_map = ids.pin_memory().to(dev, non_blocking=True), torch.cat(slot_rows).pin_memory().to(dev, non_blocking=True)
+        else:
+            slot_map = torch.cat(slot_rows)
+        batch = PackedBatch.from_lengths(ids, lens, device=dev)
+        self._prefill_slots = slot_map
+        try:
+            h = self.model.forward_hidden(batch)
+        finally:
+            self._prefill_slots = None
+        last = (batch.cu_seqlens[1:].long() - 1)
+        logits = F.gemm(h[last].contiguous(), self.params.lm_head_weight)
+        slots = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=dev)
+        seeds = torch.tensor([(r.params.seed if r.params.seed is not None else self._seed * 1000003 + zlib.crc32(r.rid.encode()))
+                              for r in reqs], dtype=torch.int64, device=dev)
+        tok, lp = F.sample_tokens(logits, self.temperature, seeds, 0, self.valid_vocab, self.top_k, self.top_p)
+        n = torch.tensor(lens, dtype=torch.int32, device=dev)
+        self.block_table[slots] = bt_rows.to(dev)
+        self.tok[slots] = tok
+        self.pos[slots] = n
+        self.ctx[slots] = n + 1
+        self.gen[slots] = 1
+        self.max_new[slots] = torch.tensor([r.params.max_tokens for r in reqs], dtype=torch.int32, device=dev)
+        self.ignore_eos[slots] = torch.tensor([r.params.ignore_eos for r in reqs], dtype=torch.bool, device=dev)
+        self.seeds[slots] = seeds * 6364136223846793005 + 1442695040888963407
+        self.out_tok[slots, 0] = tok
+        self.out_lp[slots, 0] = lp
+        done = (self.gen[slots] >= self.max_new[slots])
+        if self.eos is not None:
+            done |= (tok == self.eos) & ~self.ignore_eos[slots]
+        self.active[slots] = ~done
+        for r in reqs:
+            self.running[r.slot] = r
+        self.stats["prefill_tokens"] += sum(lens)
+        self.stats["prefill_s"] += time.time() - t0
+
+    # ------------------------------------------------------------------------------------ decode
+    def _decode_body(self) -> None:
+        """One decode step over all slots (static shapes; capturable)."""
+        cfg, P = self.cfg, self.params
+        S = self.S
+        act = self.active
+        acti = act.to(torch.int32)
+        pos_l = self.pos.long()
+        blk = torch.gather(self.block_table, 1, (pos_l // self.bs).unsqueeze(1)).squeeze(1).long()
+        slot_map = torch.where(act, blk * self.bs + pos_l % self.bs, torch.full_like(pos_l, -1))
+        ctx_eff = self.ctx * acti
+        nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
+        a = F.embedding(self.tok, P["embed_tokens.weight"])
+        r = None
+        cos, sin = self.model._cos, self.model._sin
+        for i in range(cfg.num_hidden_layers):
+            W = P.layer(i)
+            h1, x, _ = F.rms_norm(a, W["input_layernorm.weight"], cfg.rms_norm_eps, residual=r)
+            qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+            q = qkv[:, :Q].view(S, nh, hd)
+            k = qkv[:, Q : Q + KV].view(S, nkv, hd)
+            v = qkv[:, Q + KV :].view(S, nkv, hd)
+            if cfg.qk_norm:
+                qn = F.rms_norm(q.reshape(S * nh, hd).contiguous(), W["self_attn.q_norm.weight"], cfg.rms_norm_eps)[0]
+                kn = F.rms_norm(k.reshape(S * nkv, hd).contiguous(), W["self_attn.k_norm.weight"], cfg.rms_norm_eps)[0]
+                q.copy_(qn.view(S, nh, hd))
+                k.copy_(kn.view(S, nkv, hd))
+            F.apply_rope_(q, self.pos, cos, sin)
+            F.apply_rope_(k, self.pos, cos, sin)
+            F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
+            attn = F.paged_decode_attention(q, self.kv[i, 0], self.kv[i, 1], self.block_table, ctx_eff)
+            o = F.gemm(attn.reshape(S, Q), W["self_attn.o_proj.weight"])
+            h2, x2, _ = F.rms_norm(o, W["post_attention_layernorm.weight"], cfg.rms_norm_eps, residual=x)
+            a = self.model._mlp_fwd(W, h2, None)
+            r = x2
+        hN = F.rms_norm(a, P["norm.weight"], cfg.rms_norm_eps, residual=r)[0]
+        logits = F.gemm(hN, P.lm_head_weight)
+        tok, lp = F.sample_tokens(logits, self.temperature, self.seeds, 0, self.valid_vocab, self.top_k, self.top_p)
+        # ---- state update (all on device)
+        rows = torch.arange(S, device=self.device)
+        col = self.gen.long().clamp(max=self.out_cap - 1)
+        self.out_tok[rows, col] = torch.where(act, tok, self.out_tok[rows, col])
+        self.out_lp[rows, col] = torch.where(act, lp, self.out_lp[rows, col])
+        self.gen.add_(acti)
+        done = self.gen >= self.max_new
+        if self.eos is not None:
+            done = done | ((tok == self.eos) & ~self.ignore_eos)
+        self.tok.copy_(torch.where(act, tok, self.tok))
+        self.pos.add_(acti)
+        self.ctx.add_(acti)
+        self.active.copy_(act & ~done)
+        self.seeds.copy_(self.seeds * 6364136223846793005 + 1442695040888963407)
+
+    @torch.no_grad()
+    def _decode_steps(self, n: int) -> None:
+        t0 = time.time()
+        if not self.use_graph or self.cfg.is_moe:
+            for _ in range(n):
+                self._decode_body()
+        else:
+            key = (self.temperature, self.top_k, self.top_p, self.out_cap, id(self.kv))
+            if self._graph is None or self._graph_key != key:
+                snap = [t.clone() for t in (self.tok, self.pos, self.ctx, self.gen, self.active, self.seeds, self.out_tok, self.out_lp)]
+                side = torch.cuda.Stream(device=self.device)
+                side.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(side):
+                    self._decode_body()  # warm-up (allocator, lazy init) outside capture
+                torch.cuda.current_stream(self.device).wait_stream(side)
+                for dst, src in zip((self.tok, self.pos, self.ctx, self.gen, self.active, self.seeds, self.out_tok, self.out_lp), snap):
+                    dst.copy_(src)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._decode_body()
+                for dst, src in zip((self.tok, self.pos, self.ctx, self.gen, self.active, self.seeds, self.out_tok, self.out_lp), snap):
+                    dst.copy_(src)
+                self._graph, self._graph_key = g, key
+            for _ in range(n):
+                self._graph.replay()
+        self.stats["decode_steps"] += n
+        self.stats["decode_s"] += time.time() - t0
+
+    # ------------------------------------------------------------------------------------ retire
+    def _sync_retire(self, force_rids=None, abort: bool = False) -> None:
+        if not self.running:
+            return
+        active = self.active.cpu()
+        gen = self.gen.cpu()
+        done_slots = [s for s, r in self.running.items()
+                      if (not bool(active[s])) or (abort and (force_rids is None or r.rid in force_rids))]
+        if not done_slots:
+            return
+        idx = torch.tensor(done_slots, dtype=torch.int64, device=self.device)
+        toks = self.out_tok[idx].cpu()
+        lps = self.out_lp[idx].cpu()
+        for j, s in enumerate(done_slots):
+            r = self.running.pop(s)
+            n = int(gen[s])
+            t = toks[j, :n].tolist()
+            still_active = bool(active[s])
+            if still_active:
+                reason = "aborted"
+            elif self.eos is not None and n > 0 and t[-1] == self.eos and not r.params.ignore_eos:
+                reason = "completed"
+            else:
+                reason = "length"
+            self.finished.append(RequestOutput(r.rid, r.prompt, t, lps[j, :n].tolist() if r.params.logprobs else None, reason))
+            self.stats["generated_tokens"] += n
+            self.free_blocks.extend(r.blocks)
+            self.free_slots.append(s)
+        self.active[idx] = False
+        self.ctx[idx] = 0
+
+    # ------------------------------------------------------------------------------------ driver loops
+    def step(self) -> list[RequestOutput]:
+        """Admit + prefill what fits, run ``sync_interval`` decode steps, retire; returns newly finished."""
+        assert self.kv is not None, "KV cache released; call resume_kv_cache() first"
+        if self.waiting and not self.running:
+            self._ensure_out(max(r.params.max_tokens for r in self.waiting))
+        while True:
+            reqs = self._admit()
+            if not reqs:
+                break
+            self._prefill(reqs)
+        if self.running:
+            self._decode_steps(self.sync_interval)
+            self._sync_retire()
+        out, self.finished = self.finished, []
+        return out
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams]) -> list[RequestOutput]:
+        """Blocking batch generation; outputs are returned in prompt order."""
+        plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        if not self.running:
+            self._ensure_out(max(p.max_tokens for p in plist))
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        results: dict[str, RequestOutput] = {}
+        while len(results) < len(rids):
+            progressed = self.step()
+            for o in progressed:
+                results[o.request_id] = o
+            if not progressed and not self.has_unfinished():
+                break
+        return [results[r] for r in rids]
