@@ -1,0 +1,258 @@
+#!/usr/bin/env python
+"""Headline benchmark: GRPO step tokens/s on the Qwen2.5-7B architecture (random-init bf16, synthetic prompts).
+
+    python bench.py --gpus 1 --steps 1 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus 8 --steps K --warmup W
+
+One GRPO step = rollout (prefill + decode of every response) + rule reward + old-policy and reference log-probs +
+GRPO advantages + actor update (forward, backward, grad reduction, clipped AdamW) + weight hand-over to the
+rollout engine.  Weak scaling: every GPU owns ``--prompts-per-gpu`` prompts x ``--n`` samples (64 x 5 by default,
+i.e. 512 x 5 on 8 GPUs), prompts of 1024 uniform random tokens, responses of up to 2048 tokens.
+
+Two timings are taken over the same K steps each, both bracketed by barrier + synchronize and CUDA events, max
+over ranks: ``value`` with the step inputs already resident on the device, and ``e2e`` through the public trainer
+API with every step's prompts staged host->device from pinned memory and the step's metrics read back.
+
+``--impl reference`` reports why the reference cannot run in this environment (its import needs packages that are
+not installed and cannot be installed offline).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=1)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="native", choices=["native", "reference"])
+    p.add_argument("--model", default="qwen2.5-7b")
+    p.add_argument("--prompts-per-gpu", type=int, default=64)
+    p.add_argument("--n", type=int, default=5)
+    p.add_argument("--prompt-len", type=int, default=1024)
+    p.add_argument("--response-len", type=int, default=2048)
+    p.add_argument("--max-token-len", type=int, default=16384, help="token budget of a training micro-batch")
+    p.add_argument("--max-num-seqs", type=int, default=320)
+    p.add_argument("--no-recompute", action="store_true")
+    p.add_argument("--skip-e2e", action="store_true", help="development only: skip the second (end-to-end) timing pass")
+    p.add_argument("--rollout-tp", type=int, default=0, help="rollout tensor-parallel size (0 = 2 when gpus >= 2 else 1)")
+    return p.parse_args()
+
+
+def reference_arm(args) -> None:
+    """The unmodified reference lives in baseline/_ref (installed with --no-deps). Importing it needs ray, tensordict,
+    hydra-core and omegaconf, none of which is installed or present in the offline wheelhouse."""
+    sys.path.insert(0, os.path.join(REPO, "baseline", "_ref"))
+    why = None
+    try:
+        import verl  # noqa: F401
+        from verl.trainer import main_ppo  # noqa: F401
+    except Exception as e:  # ModuleNotFoundError: ray / tensordict / hydra / omegaconf
+        why = f"{type(e).__name__}: {e}"
+    if why is None:
+        why = "reference imports, but its PPO entry point needs a Ray cluster and vLLM server actors that are not provisioned here"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference cannot run offline on this image ({why})"}))
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "500",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in sm if c > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_config(args, world: int):
+    from verl_b200.trainer.config import CONFIG_DIR
+    from verl_b200.utils.config import load_config
+
+    gbs = args.prompts_per_gpu * world
+    ov = [
+        f"data.train_batch_size={gbs}", f"data.max_prompt_length={args.prompt_len}",
+        f"data.max_response_length={args.response_len}", f"data.synthetic.num_prompts={gbs * 16}",
+        f"data.synthetic.prompt_length={args.prompt_len}", "data.synthetic.vocab_low=3", "data.shuffle=false",
+        f"actor_rollout_ref.model.path={args.model}", "actor_rollout_ref.model.load_weights=false",
+        f"actor_rollout_ref.model.enable_gradient_checkpointing={'false' if args.no_recompute else 'true'}",
+        f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
+        f"actor_rollout_ref.rollout.max_num_seqs={min(args.max_num_seqs, args.prompts_per_gpu * args.n)}",
+        "actor_rollout_ref.rollout.gpu_memory_utilization=0.45", "actor_rollout_ref.rollout.sync_interval=32",
+        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp or (2 if world >= 2 else 1)}",
+        f"actor_rollout_ref.actor.ppo_mini_batch_size={gbs}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
+        f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}",
+        "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.kl_loss_coef=0.001",
+        "actor_rollout_ref.actor.optim.lr=1e-6", "algorithm.adv_estimator=grpo", "reward_model.reward_manager=token_rule",
+        f"trainer.n_gpus_per_node={world}", "trainer.nnodes=1", "trainer.total_epochs=1000", "trainer.val_before_train=false",
+        "trainer.resume_mode=disable", "trainer.save_freq=-1", "trainer.test_freq=-1", "trainer.logger=[]",
+        "trainer.worker_group=spmd", "trainer.device=cuda",
+    ]
+    cfg = load_config(CONFIG_DIR, "ppo_trainer", ov)
+    cfg.data.synthetic["vocab_high"] = None
+    return cfg
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from verl_b200.models.config import get_preset
+    from verl_b200.ops import native
+    from verl_b200.trainer.ppo.ray_trainer import RayPPOTrainer
+    from verl_b200.trainer.ppo.reward import load_reward_manager
+    from verl_b200.single_controller.local import SPMDWorkerGroup
+    from verl_b200.utils.distributed import initialize_global_process_group
+
+    local_rank, rank, world = initialize_global_process_group()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    native.load()
+
+    cfg = build_config(args, world)
+    cfg.data.synthetic["vocab_high"] = get_preset(args.model).vocab_size
+    reward_fn = load_reward_manager(cfg, None)
+    trainer = RayPPOTrainer(config=cfg, tokenizer=None, ray_worker_group_cls=SPMDWorkerGroup, reward_fn=reward_fn,
+                            val_reward_fn=None, device_name="cuda")
+    trainer.init_workers()
+    trainer.global_steps = 1
+    it = iter(trainer.train_dataloader)
+
+    def next_batch():
+        nonlocal it
+        try:
+            return next(it)
+        except StopIteration:
+            it = iter(trainer.train_dataloader)
+            return next(it)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def to_pinned(batch):
+        return {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+
+    def to_device(batch):
+        return {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+
+    last_metrics = {}
+    for _ in range(args.warmup):
+        last_metrics, _ = trainer.train_step(next_batch())
+        trainer.global_steps += 1
+    native.check_status()
+
+    def timed(batches, staged_on_device: bool):
+        """K steps between barrier+synchronize; returns (ms per step max over ranks, tokens this rank, launches)."""
+        nonlocal last_metrics
+        tokens = 0
+        sync()
+        n0 = native.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for b in batches:
+            last_metrics, _ = trainer.train_step(b)
+            trainer.global_steps += 1
+            tokens += int(sum(trainer.last_batch.meta_info["global_token_num"]))
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        tok = torch.tensor([float(tokens)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tok)
+        return float(ms) / len(batches), float(tok), native.launch_count() - n0
+
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    dev_batches = [to_device(next_batch()) for _ in range(args.steps)]
+    ms_step, tokens, launches = timed(dev_batches, True)
+    value = tokens / (ms_step * args.steps / 1e3)
+    e2e = None
+    if not args.skip_e2e:
+        host_batches = [to_pinned(next_batch()) for _ in range(args.steps)]
+        h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values() if isinstance(v, torch.Tensor)) * args.n
+        ms_e2e, tok_e2e, _ = timed(host_batches, False)
+        d2h = 8 * len([v for v in last_metrics.values() if isinstance(v, (int, float))])
+        e2e = {"value": tok_e2e / (ms_e2e * args.steps / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+    clocks = sampler.stop() if sampler else None
+    native.check_status()
+    if rank == 0:
+        gbs = args.prompts_per_gpu * world
+        out = {
+            "metric": "GRPO step tokens/sec (prompt+response tokens of the step / step time, whole job)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (uniform random-token prompts, mod-7 rule reward, random-init weights)",
+            "config": {"model": args.model, "global_batch": gbs * args.n, "prompts": gbs, "samples_per_prompt": args.n,
+                       "seq_len": args.prompt_len + args.response_len, "prompt_len": args.prompt_len,
+                       "response_len": args.response_len,
+                       "parallelism": f"dp{world} (sharded optimizer, replicated bf16 weights) + in-process rollout dp{world}",
+                       "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
+                       "mean_response_len": last_metrics.get("response_length/mean")},
+            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "phases_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last_metrics.items()
+                         if k.startswith("timing_s/") and isinstance(v, (int, float))},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

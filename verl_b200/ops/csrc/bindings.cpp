@@ -6,7 +6,15 @@
 
 #include "launchers.h"
 
+#include <atomic>
+
 namespace {
+
+// Number of kernels of this library launched (or captured into a CUDA graph) by this process.
+std::atomic<int64_t> g_launches{0};
+inline void count(int64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+void add_launches(int64_t n) { count(n); }
 
 using at::Tensor;
 using OptTensor = c10::optional<at::Tensor>;
@@ -46,6 +54,7 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
     bias_ptr = bias->data_ptr();
   }
   if (M == 0 || N == 0) return d;
+  count(1);
   const int rc = vb_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
                               b.stride(0), d.stride(0), a_mn, b_mn, out_f32, accumulate, (int)max_ctas, cur_stream());
   TORCH_CHECK(rc == 0, "vb_gemm_bf16 failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
@@ -69,6 +78,7 @@ std::tuple<Tensor, Tensor, Tensor> lmhead_fwd(const Tensor& hidden, const Tensor
   if (T == 0) return {lp, ent, lse};
   Tensor partial = at::empty({3, (int64_t)vb_lmhead_num_tiles((int)V), T}, fo);
   Tensor lab = at::zeros({T}, fo);
+  count(2);
   const int rc = vb_lmhead_fwd(hidden.data_ptr(), weight.data_ptr(), reinterpret_cast<long long*>(labels.data_ptr()), (float)inv_temp,
                                partial.data_ptr<float>(), lab.data_ptr<float>(), lp.data_ptr<float>(),
                                ent.data_ptr<float>(), lse.data_ptr<float>(), (int)T, (int)V, (int)H, hidden.stride(0),
@@ -89,6 +99,7 @@ Tensor lmhead_dlogits(const Tensor& hidden, const Tensor& weight_chunk, const Te
   const int64_t T = hidden.size(0), H = hidden.size(1), Vc = weight_chunk.size(0);
   Tensor d = out.has_value() ? *out : at::empty({T, Vc}, hidden.options());
   TORCH_CHECK(d.size(0) == T && d.size(1) == Vc && d.stride(1) == 1);
+  count(1);
   const int rc = vb_lmhead_dlogits(hidden.data_ptr(), weight_chunk.data_ptr(), reinterpret_cast<long long*>(labels.data_ptr()), (int)v0,
                                    (float)inv_temp, lse.data_ptr<float>(), fptr(ex), g_lp.data_ptr<float>(),
                                    fptr(g_ent), d.data_ptr(), (int)T, (int)Vc, (int)H, hidden.stride(0),
@@ -109,6 +120,7 @@ std::tuple<Tensor, Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor&
   Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
   Tensor res_out = residual.has_value() ? at::empty_like(x) : x;
   if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->sizes() == x.sizes());
+  count(1);
   const int rc = vb_rmsnorm_fwd(x.data_ptr(), optr(residual), w.data_ptr(), y.data_ptr(),
                                 residual.has_value() ? res_out.data_ptr() : nullptr, rstd.data_ptr<float>(), (int)T,
                                 (int)H, (float)eps, cur_stream());
@@ -128,6 +140,7 @@ Tensor rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Ten
   Tensor dx = at::empty_like(x);
   if (T == 0) return dx;
   Tensor scratch = at::empty({(int64_t)vb_rmsnorm_bwd_blocks((int)T), H}, x.options().dtype(at::kFloat));
+  count(2);
   const int rc = vb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), optr(dres_in),
                                 dx.data_ptr(), dw.data_ptr<float>(), scratch.data_ptr<float>(), (int)T, (int)H,
                                 accumulate, cur_stream());
@@ -142,6 +155,7 @@ void rope_(Tensor x, const Tensor& pos, const Tensor& cos_t, const Tensor& sin_t
   TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: [T, nheads, hd] with packed heads");
   TORCH_CHECK(pos.scalar_type() == at::kInt && pos.is_contiguous(), "rope: int32 positions");
   const c10::cuda::CUDAGuard guard(x.device());
+  count(1);
   const int rc = vb_rope(x.data_ptr(), pos.data_ptr<int>(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
                          (int)x.size(0), (int)x.size(1), (int)x.size(2), x.stride(0), backward, cur_stream());
   CHECK_RC(rc, "vb_rope");
@@ -153,6 +167,7 @@ Tensor swiglu_fwd(const Tensor& gu) {
   const c10::cuda::CUDAGuard guard(gu.device());
   const int64_t T = gu.size(0), I = gu.size(1) / 2;
   Tensor out = at::empty({T, I}, gu.options());
+  count(1);
   CHECK_RC(vb_swiglu_fwd(gu.data_ptr(), out.data_ptr(), T, (int)I, cur_stream()), "vb_swiglu_fwd");
   return out;
 }
@@ -162,6 +177,7 @@ Tensor swiglu_bwd(const Tensor& dout, const Tensor& gu) {
   TORCH_CHECK(gu.is_contiguous() && dout.is_contiguous());
   const c10::cuda::CUDAGuard guard(gu.device());
   Tensor dgu = at::empty_like(gu);
+  count(1);
   CHECK_RC(vb_swiglu_bwd(dout.data_ptr(), gu.data_ptr(), dgu.data_ptr(), gu.size(0), (int)(gu.size(1) / 2), cur_stream()),
            "vb_swiglu_bwd");
   return dgu;
@@ -172,6 +188,7 @@ Tensor embedding_fwd(const Tensor& ids, const Tensor& w) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && w.is_contiguous());
   const c10::cuda::CUDAGuard guard(w.device());
   Tensor out = at::empty({ids.numel(), w.size(1)}, w.options());
+  count(1);
   CHECK_RC(vb_embedding_fwd(reinterpret_cast<long long*>(ids.data_ptr()), w.data_ptr(), out.data_ptr(), (int)ids.numel(), (int)w.size(1),
                             (int)w.size(0), cur_stream()),
            "vb_embedding_fwd");
@@ -182,6 +199,7 @@ void embedding_bwd_(const Tensor& ids, const Tensor& dout, Tensor dw) {
   CHECK_F32(dw);
   TORCH_CHECK(dout.is_contiguous() && dw.is_contiguous());
   const c10::cuda::CUDAGuard guard(dw.device());
+  count(1);
   CHECK_RC(vb_embedding_bwd(reinterpret_cast<long long*>(ids.data_ptr()), dout.data_ptr(), dw.data_ptr<float>(), (int)ids.numel(),
                             (int)dw.size(1), (int)dw.size(0), cur_stream()),
            "vb_embedding_bwd");
@@ -192,10 +210,12 @@ void sumsq_(const Tensor& g, Tensor ctrl) {
   CHECK_F32(ctrl);
   TORCH_CHECK(g.is_contiguous());
   const c10::cuda::CUDAGuard guard(g.device());
+  count(1);
   CHECK_RC(vb_sumsq(g.data_ptr<float>(), g.numel(), ctrl.data_ptr<float>(), cur_stream()), "vb_sumsq");
 }
 void clip_coef_(Tensor ctrl, double max_norm) {
   const c10::cuda::CUDAGuard guard(ctrl.device());
+  count(1);
   CHECK_RC(vb_clip_coef(ctrl.data_ptr<float>(), (float)max_norm, cur_stream()), "vb_clip_coef");
 }
 void adamw_(Tensor master, Tensor grad, Tensor m, Tensor v, const OptTensor& out_bf16, const OptTensor& ctrl, double lr,
@@ -207,6 +227,7 @@ void adamw_(Tensor master, Tensor grad, Tensor m, Tensor v, const OptTensor& out
   TORCH_CHECK(master.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous());
   const c10::cuda::CUDAGuard guard(master.device());
   void* ob = out_bf16.has_value() ? out_bf16->data_ptr() : nullptr;
+  count(1);
   CHECK_RC(vb_adamw(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), ob,
                     master.numel(), fptr(ctrl), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
                     (float)grad_scale, zero_grad, cur_stream()),
@@ -216,12 +237,14 @@ void cast_f32_bf16_(const Tensor& in, Tensor out, double scale) {
   CHECK_F32(in);
   CHECK_BF16(out);
   const c10::cuda::CUDAGuard guard(in.device());
+  count(1);
   CHECK_RC(vb_cast_f32_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), (float)scale, cur_stream()), "vb_cast");
 }
 void accum_bf16_f32_(const Tensor& in, Tensor out, double scale, bool accumulate) {
   CHECK_BF16(in);
   CHECK_F32(out);
   const c10::cuda::CUDAGuard guard(in.device());
+  count(1);
   CHECK_RC(vb_accum_bf16_f32(in.data_ptr(), out.data_ptr<float>(), in.numel(), (float)scale, accumulate, cur_stream()),
            "vb_accum");
 }
@@ -233,6 +256,7 @@ void kv_append_(const Tensor& k, const Tensor& v, const Tensor& slot, Tensor kc,
   TORCH_CHECK(k.dim() == 3 && k.stride(2) == 1 && k.stride(1) == k.size(2) && v.stride(1) == v.size(2));
   TORCH_CHECK(slot.scalar_type() == at::kLong && slot.is_contiguous() && kc.is_contiguous() && vc.is_contiguous());
   const c10::cuda::CUDAGuard guard(k.device());
+  count(1);
   CHECK_RC(vb_kv_append(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), reinterpret_cast<long long*>(slot.data_ptr()), kc.data_ptr(),
                         vc.data_ptr(), (int)k.size(0), (int)k.size(1), (int)k.size(2), cur_stream()),
            "vb_kv_append");
@@ -249,6 +273,7 @@ Tensor paged_decode(const Tensor& q, const Tensor& kc, const Tensor& vc, const T
   const c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), nh = q.size(1), hd = q.size(2);
   Tensor out = at::empty({B, nh, hd}, q.options());
+  count(1);
   CHECK_RC(vb_paged_decode(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), block_table.data_ptr<int>(),
                            (int)block_table.size(1), ctx_len.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)B,
                            (int)nh, (int)kc.size(2), (int)hd, (int)kc.size(1), (float)scale, cur_stream()),
@@ -265,6 +290,7 @@ std::tuple<Tensor, Tensor> sample(const Tensor& logits, int64_t valid_vocab, dou
   const int64_t B = logits.size(0);
   Tensor tok = at::empty({B}, logits.options().dtype(at::kLong));
   Tensor lp = at::empty({B}, logits.options().dtype(at::kFloat));
+  count(1);
   CHECK_RC(vb_sample(logits.data_ptr(), logits.stride(0), (int)B, (int)logits.size(1), (int)valid_vocab,
                      (float)inv_temp, reinterpret_cast<long long*>(seeds.data_ptr()), step, reinterpret_cast<long long*>(tok.data_ptr()), lp.data_ptr<float>(),
                      cur_stream()),
@@ -283,6 +309,7 @@ std::tuple<Tensor, Tensor> grpo_advantage(const Tensor& rewards, const Tensor& m
   Tensor adv = at::empty_like(rewards);
   Tensor scores = at::empty({B}, rewards.options());
   Tensor stats = at::empty({num_groups, 3}, rewards.options());
+  count(2);
   CHECK_RC(vb_grpo_advantage(rewards.data_ptr<float>(), mask.data_ptr<float>(), group.data_ptr<int>(), (int)B, (int)L,
                              (int)num_groups, (float)eps, norm_by_std, scores.data_ptr<float>(),
                              stats.data_ptr<float>(), adv.data_ptr<float>(), cur_stream()),
@@ -299,6 +326,7 @@ std::tuple<Tensor, Tensor> gae(const Tensor& rewards, const Tensor& values, cons
   const c10::cuda::CUDAGuard guard(rewards.device());
   Tensor adv = at::empty_like(rewards), ret = at::empty_like(rewards);
   Tensor acc = at::empty({4}, rewards.options());
+  count(3);
   CHECK_RC(vb_gae(rewards.data_ptr<float>(), values.data_ptr<float>(), mask.data_ptr<float>(), (int)rewards.size(0),
                   (int)rewards.size(1), (float)gamma, (float)lam, whiten, adv.data_ptr<float>(), ret.data_ptr<float>(),
                   acc.data_ptr<float>(), cur_stream()),
@@ -311,6 +339,8 @@ std::tuple<Tensor, Tensor> gae(const Tensor& rewards, const Tensor& values, cons
 TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
+  m.def("launch_count", &launch_count);
+  m.def("add_launches", &add_launches);
   m.def("lmhead_fwd", &lmhead_fwd);
   m.def("lmhead_dlogits", &lmhead_dlogits);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

@@ -63,3 +63,12 @@ def check_status() -> None:
     code = int(ops().gemm_status())
     if code != 0:
         raise RuntimeError(f"verl_b200 native kernel reported status {code} (a bounded in-kernel wait ran out)")
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (graph replays are added by their owners)."""
+    return int(ops().launch_count()) if _loaded or available() else 0
+
+
+def add_launches(n: int) -> None:
+    ops().add_launches(int(n))

@@ -114,14 +114,18 @@ class NativeEngine(BaseEngine):
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.shard_numel = self.params.numel // self.world
         self.shard_lo = self.rank * self.shard_numel
+        # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
+        # memory (4 bytes/param) is available to the rollout KV cache in between.
+        self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda"))
         if not self.forward_only:
-            self.params.attach_main_grad()
             sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
             self.master = self.params.flat[sl].float().clone()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
-            self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+            self.grad_shard = None
             self.ctrl = torch.zeros(4, dtype=torch.float32, device=self.device)
+            if not self.lazy_grad:
+                self._alloc_grads()
         self._initialized = True
 
     def _load_or_init(self, seed: int) -> None:
@@ -228,8 +232,17 @@ class NativeEngine(BaseEngine):
         return out
 
     # ------------------------------------------------------------------------------------ optimizer
+    def _alloc_grads(self) -> None:
+        self.params.attach_main_grad()
+        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+
     def optimizer_zero_grad(self) -> None:
-        if not self.forward_only:
+        if self.forward_only:
+            return
+        if self.params.main_grad is None:
+            self._alloc_grads()
+        else:
             self.params.zero_grad()
 
     def optimizer_step(self) -> float:
@@ -276,7 +289,11 @@ class NativeEngine(BaseEngine):
                 self.master.addcdiv_(self.exp_avg, denom, value=-lr / bc1)
                 self.params.flat[sl].copy_(self.master.to(self.dtype))
         self._publish_shard()
-        return float(norm)
+        norm = float(norm)
+        if self.lazy_grad:
+            self.params.detach_main_grad()
+            self.grad_shard = None
+        return norm
 
     def _publish_shard(self) -> None:
         """All-gather this rank's updated slice of the working weights into every replica."""

@@ -348,14 +348,22 @@ class RolloutEngine:
                 torch.cuda.current_stream(self.device).wait_stream(side)
                 for dst, src in zip((self.tok, self.pos, self.ctx, self.gen, self.active, self.seeds, self.out_tok, self.out_lp), snap):
                     dst.copy_(src)
+                from ....ops import native
+
                 g = torch.cuda.CUDAGraph()
+                n0 = native.launch_count()
                 with torch.cuda.graph(g):
                     self._decode_body()
+                self._graph_kernels = native.launch_count() - n0
+                native.add_launches(-self._graph_kernels)  # captured, not launched
                 for dst, src in zip((self.tok, self.pos, self.ctx, self.gen, self.active, self.seeds, self.out_tok, self.out_lp), snap):
                     dst.copy_(src)
                 self._graph, self._graph_key = g, key
             for _ in range(n):
                 self._graph.replay()
+            from ....ops import native
+
+            native.add_launches(self._graph_kernels * n)
         self.stats["decode_steps"] += n
         self.stats["decode_s"] += time.time() - t0
 
