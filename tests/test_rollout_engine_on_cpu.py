@@ -1,0 +1,76 @@
+"""Continuous batching + paged KV: generation must equal token-by-token greedy decoding of the full model."""
+import torch
+
+from verl_b200.models import DecoderModel, FlatParams, PackedBatch, get_preset
+from verl_b200.workers.rollout.native.engine import RolloutEngine, SamplingParams
+
+
+def _greedy_reference(model, prompt, n):
+    ids, out, lps = list(prompt), [], []
+    for _ in range(n):
+        lg = model.forward_logits(PackedBatch.from_lengths(torch.tensor(ids), [len(ids)]))[-1].float()
+        t = int(lg.argmax())
+        lps.append(float(torch.log_softmax(lg, -1)[t]))
+        out.append(t)
+        ids.append(t)
+    return out, lps
+
+
+def test_greedy_matches_full_forward_with_more_requests_than_slots():
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    eng = RolloutEngine(cfg, P, max_num_seqs=3, max_model_len=64, block_size=8, sync_interval=3, eos_token_id=-1)
+    prompts = [[5, 6, 7, 8, 9], [10, 11, 12], [20, 21, 22, 23, 24, 25, 26], [3, 4], [7, 7, 7, 7]]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=9))
+    model = DecoderModel(cfg, P)
+    for p, o in zip(prompts, outs):
+        ref, lps = _greedy_reference(model, p, 9)
+        assert o.token_ids == ref and o.stop_reason == "length"
+        assert torch.allclose(torch.tensor(o.log_probs), torch.tensor(lps), atol=1e-4)
+    assert not eng.running and len(eng.free_slots) == 3 and len(eng.free_blocks) == eng.num_blocks
+
+
+def test_eos_stops_and_sampling_logprobs_are_consistent():
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=4, std=0.2)
+    eng = RolloutEngine(cfg, P, max_num_seqs=4, max_model_len=48, block_size=4, sync_interval=2)
+    eng.eos = -1
+    first = eng.generate([[9, 9, 9]], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    # stop at the first position whose greedy token has not occurred before it (j = 0 if all tokens repeat)
+    j = next((i for i in range(1, 6) if first.token_ids[i] not in first.token_ids[:i]), 0)
+    eng.eos = first.token_ids[j]
+    again = eng.generate([[9, 9, 9]], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    assert again.token_ids == first.token_ids[: j + 1] and again.stop_reason == "completed"
+    ign = eng.generate([[9, 9, 9]], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))[0]
+    assert ign.token_ids == first.token_ids
+    samp = eng.generate([[4, 5, 6]] * 3, SamplingParams(temperature=1.0, max_tokens=5, ignore_eos=True))
+    model = DecoderModel(cfg, P)
+    for o in samp:
+        ids = [4, 5, 6]
+        for t, lp in zip(o.token_ids, o.log_probs):
+            lg = model.forward_logits(PackedBatch.from_lengths(torch.tensor(ids), [len(ids)]))[-1].float()
+            assert abs(float(torch.log_softmax(lg, -1)[t]) - lp) < 1e-4
+            ids.append(t)
+
+
+def test_kv_release_resume_and_abort():
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=5, std=0.1)
+    eng = RolloutEngine(cfg, P, max_num_seqs=2, max_model_len=32, block_size=4, sync_interval=2, eos_token_id=-1)
+    a = eng.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=4))[0].token_ids
+    eng.release_kv_cache()
+    assert eng.kv is None
+    eng.resume_kv_cache()
+    assert eng.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=4))[0].token_ids == a
+    for p in ([1, 2], [3, 4], [5, 6]):
+        eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=20))
+    eng.step()
+    aborted = eng.abort()
+    done = eng.finished + aborted
+    assert not eng.has_unfinished() and any(o.stop_reason == "aborted" for o in done)
+    assert len(eng.free_slots) == 2 and len(eng.free_blocks) == eng.num_blocks

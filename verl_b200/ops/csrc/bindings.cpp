@@ -6,6 +6,7 @@
 
 #include "launchers.h"
 
+#include <algorithm>
 #include <atomic>
 
 namespace {
@@ -54,14 +55,46 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
     bias_ptr = bias->data_ptr();
   }
   if (M == 0 || N == 0) return d;
-  count(1);
-  const int rc = vb_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
-                              b.stride(0), d.stride(0), a_mn, b_mn, out_f32, accumulate, (int)max_ctas, cur_stream());
+  // skinny GEMMs (decode: few output tiles, deep K) are split along K so that every SM streams weights
+  const int splits = (max_ctas == 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
+  Tensor ws;
+  if (splits > 1) ws = at::empty({splits, M, N}, a.options().dtype(at::kFloat));
+  count(splits > 1 ? 2 : 1);
+  const int rc = vb_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
+                                 b.stride(0), d.stride(0), a_mn, b_mn, out_f32, accumulate, (int)max_ctas, splits,
+                                 splits > 1 ? ws.data_ptr<float>() : nullptr, cur_stream());
   TORCH_CHECK(rc == 0, "vb_gemm_bf16 failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
   return d;
 }
 
-int64_t gemm_status() { return vb_gemm_status(); }
+int64_t gemm_status() {
+  const int a = vb_gemm_status();
+  const int b = vb_attn_status();
+  const int c = vb_pd_status();
+  return a != 0 ? a : (b != 0 ? 100 + b : (c != 0 ? 200 + c : 0));
+}
+
+// Causal GQA attention over packed sequences. q [T, nh, hd], k/v [T, nkv, hd] (strided views), cu_seqlens int32 [B+1].
+// Returns (out [T, nh, hd] bf16, lse [nh, T] fp32).
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_seqlens,
+                                    double scale) {
+  CHECK_BF16(q);
+  CHECK_BF16(k);
+  CHECK_BF16(v);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(1) == k.size(2) &&
+              v.stride(1) == v.size(2), "attn_fwd: [T, heads, hd] views with packed heads");
+  TORCH_CHECK(cu_seqlens.is_cuda() && cu_seqlens.scalar_type() == at::kInt && cu_seqlens.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t T = q.size(0), nh = q.size(1), hd = q.size(2), nkv = k.size(1);
+  Tensor out = at::empty({T, nh, hd}, q.options());
+  Tensor lse = at::empty({nh, T}, q.options().dtype(at::kFloat));
+  count(1);
+  const int rc = vb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                             cu_seqlens.data_ptr<int>(), (int)cu_seqlens.numel() - 1, (int)T, (int)nh, (int)nkv, (int)hd,
+                             (float)scale, out.data_ptr(), out.stride(0), lse.data_ptr<float>(), cur_stream());
+  CHECK_RC(rc, "vb_attn_fwd");
+  return {out, lse};
+}
 
 // (logprob, entropy, lse) of labels under softmax(hidden @ weight^T / temperature); [T,V] logits never exist.
 std::tuple<Tensor, Tensor, Tensor> lmhead_fwd(const Tensor& hidden, const Tensor& weight, const Tensor& labels,
@@ -273,6 +306,26 @@ Tensor paged_decode(const Tensor& q, const Tensor& kc, const Tensor& vc, const T
   const c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), nh = q.size(1), hd = q.size(2);
   Tensor out = at::empty({B, nh, hd}, q.options());
+  const int64_t nkv = kc.size(2), bs = kc.size(1);
+  if (bs == 64 && (hd == 64 || hd == 128) && nh / nkv <= 16) {
+    // TMA + tensor-core kernel; split the KV range when the grid would not fill the GPU
+    int64_t nsplit = 1;
+    const int64_t ctas = B * nkv;
+    if (ctas < 296) nsplit = std::min<int64_t>(8, (296 + ctas - 1) / ctas);
+    Tensor po, pml;
+    if (nsplit > 1) {
+      po = at::empty({B, nh, nsplit, hd}, q.options().dtype(at::kFloat));
+      pml = at::empty({B, nh, nsplit, 2}, q.options().dtype(at::kFloat));
+    }
+    count(nsplit > 1 ? 2 : 1);
+    const int rc = vb_paged_decode_v2(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), kc.size(0) * bs,
+                                      block_table.data_ptr<int>(), (int)block_table.size(1), ctx_len.data_ptr<int>(),
+                                      out.data_ptr(), out.stride(0), (int)B, (int)nh, (int)nkv, (int)hd, (int)bs,
+                                      (float)scale, (int)nsplit, nsplit > 1 ? po.data_ptr<float>() : nullptr,
+                                      nsplit > 1 ? pml.data_ptr<float>() : nullptr, cur_stream());
+    CHECK_RC(rc, "vb_paged_decode_v2");
+    return out;
+  }
   count(1);
   CHECK_RC(vb_paged_decode(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), block_table.data_ptr<int>(),
                            (int)block_table.size(1), ctx_len.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)B,
@@ -341,6 +394,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_status", &gemm_status);
   m.def("launch_count", &launch_count);
   m.def("add_launches", &add_launches);
+  m.def("attn_fwd", &attn_fwd);
   m.def("lmhead_fwd", &lmhead_fwd);
   m.def("lmhead_dlogits", &lmhead_dlogits);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

@@ -44,6 +44,7 @@ struct GemmParams {
   int out_f32;
   int accumulate;
   int* status;
+  int k_splits;        // > 1: tile t also selects a K range; partials go to `D` as fp32 [k_splits][M][N]
   // LM-head epilogues
   const long long* labels;  // [M]; label column in the full vocabulary
   int label_offset;         // first vocabulary column covered by this launch
@@ -88,8 +89,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int num_mn = num_m * num_n;
+  const int num_tiles = num_mn * splits;
+  const int num_kb_total = (p.K + BK - 1) / BK;
+  const int kb_per = (num_kb_total + splits - 1) / splits;
   constexpr int GROUP_M = 8;
 
   if (threadIdx.x == 0) {
@@ -114,7 +118,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  auto k_range = [&](int t, int& kb0, int& kb1) {
+    const int sp = t / num_mn;
+    kb0 = sp * kb_per;
+    kb1 = min(num_kb_total, kb0 + kb_per);
+  };
   auto tile_coords = [&](int t, int& m_idx, int& n_idx) {
+    t = t % num_mn;
     const int per_group = GROUP_M * num_n;
     const int g = t / per_group;
     const int first_m = g * GROUP_M;
@@ -134,7 +144,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         int m_idx, n_idx;
         tile_coords(t, m_idx, n_idx);
         const int m0 = m_idx * BM, n0 = n_idx * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb0, kb1;
+        k_range(t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, ST_TIMEOUT_PRODUCER);
             ok = false;
@@ -180,7 +192,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb0, kb1;
+        k_range(t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             atomicExch(p.status, ST_TIMEOUT_MMA);
             ok = false;
@@ -195,7 +209,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
@@ -315,7 +329,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
           if (p.out_f32) {
-            float* out = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            float* out = reinterpret_cast<float*>(p.D) + static_cast<long long>(t / num_mn) * p.M * p.ldd +
+                         static_cast<long long>(row) * p.ldd + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (j < ncols) {
@@ -391,7 +406,7 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.k_splits > 1 ? p.k_splits : 1);
   const int grid = tiles < sms ? tiles : sms;
   kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   return cudaGetLastError();
@@ -404,9 +419,64 @@ using namespace vb;
 // Returns 0 on success, a negative code for bad arguments, a positive cudaError_t otherwise.
 //  a_mn / b_mn: operand is stored [K, M|N] (MN contiguous) instead of [M|N, K].
 //  lda / ldb / ldd: row stride in elements of the stored matrix.
+namespace vb {
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __nv_bfloat16* __restrict__ bias, void* D,
+                                     long long ldd, int M, int N, int splits, int out_f32, int accumulate) {
+  const long long i4 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long total4 = static_cast<long long>(M) * N / 4;
+  if (i4 >= total4) return;
+  const long long e = i4 * 4;
+  const int row = static_cast<int>(e / N), col = static_cast<int>(e % N);
+  float4 a = reinterpret_cast<const float4*>(ws)[i4];
+  for (int s = 1; s < splits; ++s) {
+    const float4 b = reinterpret_cast<const float4*>(ws + static_cast<long long>(s) * M * N)[i4];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  if (bias != nullptr) {
+    a.x += __bfloat162float(bias[col]); a.y += __bfloat162float(bias[col + 1]);
+    a.z += __bfloat162float(bias[col + 2]); a.w += __bfloat162float(bias[col + 3]);
+  }
+  if (out_f32) {
+    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(D) + static_cast<long long>(row) * ldd + col);
+    if (accumulate) { const float4 c = *o; a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; }
+    *o = a;
+  } else {
+    uint2 v;
+    v.x = pack_bf16x2(a.x, a.y);
+    v.y = pack_bf16x2(a.z, a.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(D) + static_cast<long long>(row) * ldd + col) = v;
+  }
+}
+}  // namespace vb
+
+// Suggested number of K splits for a skinny GEMM (few output tiles, deep K); 1 = no split.
+extern "C" int vb_gemm_suggest_splits(int M, int N, int K) {
+  const int BN = N > 128 ? 256 : 128;
+  const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
+  const int sms = num_sms();
+  if (tiles * 2 > sms || K < 2048) return 1;
+  int s = sms / tiles;
+  const int by_k = K / 1024;
+  if (s > by_k) s = by_k;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : s;
+}
+
+extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
+                               int accumulate, int max_ctas, int k_splits, float* splitk_ws, cudaStream_t stream);
+
 extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                             long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
                             int accumulate, int max_ctas, cudaStream_t stream) {
+  return vb_gemm_bf16_ex(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, accumulate, max_ctas, 1, nullptr,
+                         stream);
+}
+
+// k_splits > 1 needs splitk_ws of k_splits * M * N floats.
+extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
+                               int accumulate, int max_ctas, int k_splits, float* splitk_ws, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row strides; the epilogue stores 8-column vectors.
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % (out_f32 ? 4 : 8))) return -1;
@@ -428,6 +498,11 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_f32 = out_f32; p.accumulate = accumulate; p.status = status;
+  p.k_splits = 1;
+  if (splitk_ws != nullptr && k_splits > 1) {
+    // partial sums as fp32 [k_splits][M][N] in the workspace; vb_splitk_reduce folds them (+bias) into D
+    p.k_splits = k_splits; p.D = splitk_ws; p.ldd = N; p.bias = nullptr; p.out_f32 = 1; p.accumulate = 0;
+  }
   cudaError_t e;
 #define VB_LAUNCH(BN_, AM, BMJ, ST) e = launch_variant<BN_, AM, BMJ, ST>(ta, tb, p, sms, stream)
   if (wide) {
@@ -442,6 +517,12 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
     else VB_LAUNCH(128, true, false, 6);
   }
 #undef VB_LAUNCH
+  if (e == cudaSuccess && p.k_splits > 1) {
+    const long long total4 = static_cast<long long>(M) * N / 4;
+    splitk_reduce_kernel<<<static_cast<int>((total4 + 255) / 256), 256, 0, stream>>>(
+        splitk_ws, reinterpret_cast<const __nv_bfloat16*>(bias), D, ldd, M, N, p.k_splits, out_f32, accumulate);
+    e = cudaGetLastError();
+  }
   return static_cast<int>(e);
 }
 

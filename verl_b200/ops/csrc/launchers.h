@@ -8,6 +8,10 @@ extern "C" {
 int vb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldd, int a_mn, int b_mn, int out_f32, int accumulate, int max_ctas,
                  cudaStream_t stream);
+int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
+                    long long ldb, long long ldd, int a_mn, int b_mn, int out_f32, int accumulate, int max_ctas, int k_splits,
+                    float* splitk_ws, cudaStream_t stream);
+int vb_gemm_suggest_splits(int M, int N, int K);
 int vb_gemm_status();
 int vb_lmhead_num_tiles(int V);
 int vb_lmhead_fwd(const void* hidden, const void* weight, const long long* labels, float inv_temp, float* partial,
@@ -42,6 +46,17 @@ int vb_paged_decode(const void* q, long long ldq, const void* kc, const void* vc
                     int block_size, float scale, cudaStream_t s);
 int vb_sample(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, const long long* seeds,
               long long step, long long* tokens, float* logprobs, cudaStream_t s);
+// attention_fwd_tcgen05.cu
+int vb_attn_fwd(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
+                const int* cu_seqlens, int num_seqs, int total_tokens, int nh, int nkv, int hd, float scale, void* out,
+                long long ldo, float* lse, cudaStream_t stream);
+int vb_attn_status();
+// paged_decode_tma.cu
+int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, const void* vc, long long num_slots,
+                       const int* block_table, int max_blocks, const int* ctx_len, void* out, long long ldo, int B, int nh,
+                       int nkv, int hd, int block_size, float scale, int nsplit, float* part_o, float* part_ml,
+                       cudaStream_t stream);
+int vb_pd_status();
 // advantage.cu
 int vb_grpo_advantage(const float* rewards, const float* mask, const int* group, int B, int L, int num_groups,
                       float eps, int norm_by_std, float* scores, float* stats, float* adv, cudaStream_t s);

@@ -403,3 +403,25 @@ def gae_advantage(rewards, values, mask, gamma: float, lam: float, whiten: bool 
     from ..trainer.ppo import core_algos
 
     return core_algos.compute_gae_advantage_return(rewards, values, mask, gamma, lam)
+
+
+# ----------------------------------------------------------------------------------------------- native attention
+def _native_attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale):
+    out, lse = _ops().attn_fwd(q, k, v, cu_seqlens.to(torch.int32), float(scale))
+    return out, lse
+
+
+def enable_native_attention(forward: bool = True, backward: bool = True) -> None:
+    """Route varlen attention on CUDA through the tcgen05 kernels (forward; backward when available)."""
+    if forward:
+        _ATTN_IMPL["fwd"] = _native_attn_fwd
+    if backward and hasattr(torch.ops.verl_b200, "attn_bwd"):
+        _ATTN_IMPL["bwd"] = _native_attn_bwd
+
+
+if torch.cuda.is_available():  # the tcgen05 forward kernel is the default attention path on a GPU
+    _ATTN_IMPL["fwd"] = _native_attn_fwd
+
+
+def _native_attn_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale):
+    return _ops().attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_seqlens.to(torch.int32), int(max_seqlen), float(scale))

@@ -293,6 +293,8 @@ class NativeEngine(BaseEngine):
         if self.lazy_grad:
             self.params.detach_main_grad()
             self.grad_shard = None
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
         return norm
 
     def _publish_shard(self) -> None:

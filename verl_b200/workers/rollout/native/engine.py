@@ -124,6 +124,7 @@ class RolloutEngine:
         n = self._num_blocks_req
         if n is None:
             if self.is_cuda:
+                torch.cuda.empty_cache()  # cached-but-unused allocator blocks would otherwise count as occupied
                 free, total = torch.cuda.mem_get_info(self.device)
                 budget = min(free - (2 << 30), int(total * self.gpu_memory_utilization))
                 n = max(self.max_blocks_per_seq, int(budget // self.kv_bytes_per_block()))
