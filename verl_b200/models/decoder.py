@@ -130,7 +130,8 @@ class DecoderModel:
         F.apply_rope_(k, batch.positions, self._cos, self._sin)
         if self.kv_hook is not None:
             self.kv_hook(layer_idx, k, v)
-        cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["fwd"] is not None else self._cu_cpu(batch)
+        native_ok = q.is_cuda and F._ATTN_IMPL["fwd"] is not None and hd in (64, 128)
+        cu = batch.cu_seqlens if native_ok else self._cu_cpu(batch)
         attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
         attn2 = attn.reshape(T, Q)
         if S is not None:

@@ -295,8 +295,8 @@ def register_attention_impl(fwd=None, bwd=None) -> None:
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
     """Causal GQA attention over packed sequences. q [T, nh, hd], k/v [T, nkv, hd]. Returns (out, lse|None)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if q.is_cuda and _ATTN_IMPL["fwd"] is not None:
-        return _ATTN_IMPL["fwd"](q, k, v, cu_seqlens, max_seqlen, scale)
+    if q.is_cuda and _ATTN_IMPL["fwd"] is not None and q.shape[-1] in (64, 128) and q.dtype == torch.bfloat16:
+        return _ATTN_IMPL["fwd"](q, k, v, cu_seqlens.to(q.device), max_seqlen, scale)
     return _sdpa_varlen(q, k, v, cu_seqlens, scale), None
 
 
