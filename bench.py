@@ -41,7 +41,7 @@ def parse_args():
     p.add_argument("--impl", default="native", choices=["native", "reference"])
     p.add_argument("--model", default="qwen2.5-7b")
     p.add_argument("--prompts-per-gpu", type=int, default=64)
-    p.add_argument("--n", type=int, default=5)
+    p.add_argument("--samples-per-prompt", dest="n", type=int, default=5)
     p.add_argument("--prompt-len", type=int, default=1024)
     p.add_argument("--response-len", type=int, default=2048)
     p.add_argument("--max-token-len", type=int, default=16384, help="token budget of a training micro-batch")

@@ -1,0 +1,119 @@
+"""Two-rank GPU tests (NCCL + peer memory): fused reduce-scatter/AdamW/all-gather vs the NCCL path, one-shot peer
+all-reduce, and a peer barrier whose wait runs out and reports a status instead of hanging.
+Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    try:
+        _worker_body(rank, world, port, out)
+    except Exception:  # report instead of leaving the parent waiting
+        import traceback
+
+        out.put((rank, {"error": traceback.format_exc()}))
+
+
+def _worker_body(rank, world, port, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.utils.distributed import initialize_global_process_group
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+    from functools import partial
+
+    initialize_global_process_group()
+    dev = torch.device("cuda", rank)
+    ops = native.ops()
+    res = {}
+    # ---- one-shot peer all-reduce
+    buf = SymmetricBuffer.allocate(4096, torch.bfloat16, dev)
+    bar = PeerBarrier(dev)
+    buf.tensor.copy_((torch.arange(4096, device=dev) % 7 + rank).bfloat16())
+    bar()
+    outt = torch.empty(4096, device=dev, dtype=torch.bfloat16)
+    ops.allreduce_peer_(buf.ptrs, outt, rank)
+    bar()
+    expect = sum((torch.arange(4096, device=dev) % 7 + r).float() for r in range(world))
+    res["allreduce_err"] = (outt.float() - expect).abs().max().item()
+    # ---- engines: fused peer-memory optimizer vs NCCL
+    arch = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=64, eos_token_id=2, pad_token_id=0)
+    finals = {}
+    for fused in (True, False):
+        os.environ["VERL_B200_FUSED_COMM"] = "1" if fused else "0"
+        torch.manual_seed(0)
+        eng = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2),
+                                     OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        assert eng.fused_comm == fused
+        g = torch.Generator().manual_seed(100 + rank)
+        ids = torch.randint(3, 1024, (4, 48), generator=g)
+        am = torch.ones(4, 48, dtype=torch.int64)
+        data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 16:].to(dev),
+                "response_mask": am[:, 16:].to(dev)}
+        norms = []
+        for _ in range(2):
+            out = eng.train_batch(dict(data), partial(sft_loss, None))
+            norms.append(out["metrics"]["grad_norm"])
+        finals[fused] = (eng.params.flat.float().clone(), norms)
+        # all replicas hold identical weights after the update
+        other = eng.params.flat.clone()
+        dist.broadcast(other, src=0)
+        res[f"replica_diff_{fused}"] = (other.float() - eng.params.flat.float()).abs().max().item()
+    res["param_diff"] = (finals[True][0] - finals[False][0]).abs().max().item()
+    res["norm_diff"] = max(abs(a - b) for a, b in zip(finals[True][1], finals[False][1]))
+    res["norm"] = finals[True][1]
+    # ---- a barrier that nobody else joins runs out after its limit and reports through the status word
+    lonely = PeerBarrier(dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        lonely(limit_s=0.3)
+        torch.cuda.synchronize()
+        res["timeout_status"] = int(ops.comm_status())
+        res["alive_after_timeout"] = float(torch.ones(4, device=dev).sum())
+    dist.barrier()
+    out.put((rank, res))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_fused_optimizer_and_peer_collectives():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    for r in (0, 1):
+        assert "error" not in results[r], results[r]["error"]
+    for r in (0, 1):
+        res = results[r]
+        assert res["allreduce_err"] == 0.0
+        assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
+        assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
+        assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res
+    assert results[0]["timeout_status"] == 4 and results[0]["alive_after_timeout"] == 4.0

@@ -387,9 +387,60 @@ std::tuple<Tensor, Tensor> gae(const Tensor& rewards, const Tensor& values, cons
   return {adv, ret};
 }
 
+// ---- peer-memory collectives. `ptrs`: int64 CPU tensor of device addresses, one per rank (symmetric buffers).
+inline const unsigned long long* uptr(const Tensor& t) {
+  TORCH_CHECK(!t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "pointer table: int64 CPU tensor");
+  return reinterpret_cast<const unsigned long long*>(t.data_ptr());
+}
+
+void peer_barrier(const Tensor& pad_ptrs, int64_t rank, int64_t epoch, double limit_s) {
+  count(1);
+  CHECK_RC(vb_peer_barrier(uptr(pad_ptrs), (int)rank, (int)pad_ptrs.numel(), (unsigned int)epoch, limit_s, cur_stream()),
+           "vb_peer_barrier");
+}
+
+void rs_sumsq_(const Tensor& grad_ptrs, int64_t mc_ptr, Tensor out, int64_t lo, int64_t rank, double scale, Tensor ctrl) {
+  CHECK_F32(out);
+  CHECK_F32(ctrl);
+  const c10::cuda::CUDAGuard guard(out.device());
+  count(1);
+  CHECK_RC(vb_rs_sumsq(uptr(grad_ptrs), (unsigned long long)mc_ptr, out.data_ptr<float>(), lo, out.numel(),
+                       (int)grad_ptrs.numel(), (int)rank, (float)scale, ctrl.data_ptr<float>(), cur_stream()),
+           "vb_rs_sumsq");
+}
+
+void adamw_allgather_(Tensor master, const Tensor& grad, Tensor m, Tensor v, const Tensor& param_ptrs, int64_t mc_ptr,
+                      int64_t lo, int64_t rank, const Tensor& ctrl, double lr, double beta1, double beta2, double eps,
+                      double wd, int64_t step) {
+  CHECK_F32(master);
+  CHECK_F32(grad);
+  const c10::cuda::CUDAGuard guard(master.device());
+  count(1);
+  CHECK_RC(vb_adamw_allgather(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                              uptr(param_ptrs), (unsigned long long)mc_ptr, lo, master.numel(), (int)param_ptrs.numel(),
+                              (int)rank, ctrl.data_ptr<float>(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd,
+                              (int)step, cur_stream()),
+           "vb_adamw_allgather");
+}
+
+void allreduce_peer_(const Tensor& buf_ptrs, Tensor out, int64_t rank) {
+  CHECK_BF16(out);
+  const c10::cuda::CUDAGuard guard(out.device());
+  count(1);
+  CHECK_RC(vb_allreduce_peer(uptr(buf_ptrs), out.data_ptr(), out.numel(), (int)buf_ptrs.numel(), (int)rank, cur_stream()),
+           "vb_allreduce_peer");
+}
+
+int64_t comm_status() { return vb_comm_status(); }
+
 }  // namespace
 
 TORCH_LIBRARY(verl_b200, m) {
+  m.def("peer_barrier", &peer_barrier);
+  m.def("rs_sumsq_", &rs_sumsq_);
+  m.def("adamw_allgather_", &adamw_allgather_);
+  m.def("allreduce_peer_", &allreduce_peer_);
+  m.def("comm_status", &comm_status);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
   m.def("launch_count", &launch_count);

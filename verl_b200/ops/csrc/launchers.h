@@ -57,6 +57,15 @@ int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, const void*
                        int nkv, int hd, int block_size, float scale, int nsplit, float* part_o, float* part_ml,
                        cudaStream_t stream);
 int vb_pd_status();
+// comm_fused.cu
+int vb_peer_barrier(const unsigned long long* pad_ptrs, int rank, int W, unsigned int epoch, double limit_s, cudaStream_t s);
+int vb_rs_sumsq(const unsigned long long* grad_ptrs, unsigned long long mc_ptr, float* out, long long lo, long long n, int W,
+                int rank, float scale, float* ctrl, cudaStream_t s);
+int vb_adamw_allgather(float* master, const float* grad, float* m, float* v, const unsigned long long* param_ptrs,
+                       unsigned long long mc_ptr, long long lo, long long n, int W, int rank, const float* ctrl, float lr,
+                       float beta1, float beta2, float eps, float wd, int step, cudaStream_t s);
+int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n, int W, int rank, cudaStream_t s);
+int vb_comm_status();
 // advantage.cu
 int vb_grpo_advantage(const float* rewards, const float* mask, const int* group, int B, int L, int num_groups,
                       float eps, int norm_by_std, float* scores, float* stats, float* adv, cudaStream_t s);

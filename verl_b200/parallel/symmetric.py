@@ -1,0 +1,73 @@
+"""Symmetric (peer-mapped) device buffers for in-kernel NVLink communication.
+
+Every rank allocates the same-sized buffer, exchanges handles once (``torch.distributed._symmetric_memory``
+rendezvous over the bootstrap process group) and from then on holds a table of device addresses — one per peer —
+that the fused kernels dereference directly (peer loads / stores over NVLink 5 through the NVSwitch), plus, when
+the fabric supports it, a multicast address for ``multimem`` instructions.  A per-rank signal pad of uint32 slots
+carries the epoch flags of :func:`peer_barrier`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available"]
+
+
+def symmetric_available() -> bool:
+    if not (torch.cuda.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+        return False
+    try:
+        from torch.distributed import _symmetric_memory  # noqa: F401
+
+        return True
+    except Exception:
+        return False
+
+
+@dataclass
+class SymmetricBuffer:
+    tensor: torch.Tensor          # this rank's buffer
+    ptrs: torch.Tensor            # int64 CPU tensor [world]: device address of every rank's buffer
+    multicast_ptr: int            # 0 when no multicast mapping exists
+    handle: object
+
+    @classmethod
+    def allocate(cls, numel: int, dtype: torch.dtype, device, group=None, zero: bool = True) -> "SymmetricBuffer":
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        t = symm_mem.empty(numel, dtype=dtype, device=device)
+        if zero:
+            t.zero_()
+        h = symm_mem.rendezvous(t, group)
+        ptrs = torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64)
+        mc = 0
+        try:
+            mc = int(h.multicast_ptr) if h.has_multicast_support(h.device.type if hasattr(h.device, "type") else "cuda", torch.cuda.current_device()) else 0
+        except Exception:
+            try:
+                mc = int(h.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        return cls(tensor=t, ptrs=ptrs, multicast_ptr=mc, handle=h)
+
+
+class PeerBarrier:
+    """Cross-GPU barrier on the current stream: monotonically increasing epochs through symmetric signal pads."""
+
+    def __init__(self, device, group=None, slots: int = 64):
+        self.buf = SymmetricBuffer.allocate(slots, torch.int32, device, group, zero=True)
+        self.rank = dist.get_rank(group)
+        self.epoch = 0
+        dist.barrier(group)  # pads are zero everywhere before the first device-side epoch is written
+
+    def __call__(self, limit_s: float = 20.0) -> None:
+        from ..ops import native
+
+        self.epoch += 1
+        native.ops().peer_barrier(self.buf.ptrs, self.rank, self.epoch, float(limit_s))

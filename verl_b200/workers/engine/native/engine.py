@@ -104,11 +104,26 @@ class NativeEngine(BaseEngine):
             self.dtype = torch.float32
         ec = self.engine_config
         seed = int(getattr(ec, "seed", 42))
+        self.fused_comm = False
+        self._sym_params = self._sym_grads = self._peer_barrier = None
         if self._shared_params is not None:
             self.params = self._shared_params
         else:
+            want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
+                          and self.world > 1 and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
+            buf = None
+            if want_fused:
+                from ....parallel.symmetric import PeerBarrier, SymmetricBuffer, symmetric_available
+
+                if symmetric_available():
+                    probe = FlatParams(self.arch, dtype=self.dtype, device="meta", value_head=self.value_head, pad_to=self.world)
+                    self._sym_params = SymmetricBuffer.allocate(probe.numel, self.dtype, self.device)
+                    self._sym_grads = SymmetricBuffer.allocate(probe.numel, torch.float32, self.device)
+                    self._peer_barrier = PeerBarrier(self.device)
+                    buf = self._sym_params.tensor
+                    self.fused_comm = True
             self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
-                                     pad_to=self.world)
+                                     pad_to=self.world, buffer=buf)
             self._load_or_init(seed)
         recompute = "full" if getattr(ec, "enable_gradient_checkpointing", True) else "none"
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
@@ -116,7 +131,7 @@ class NativeEngine(BaseEngine):
         self.shard_lo = self.rank * self.shard_numel
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
         # memory (4 bytes/param) is available to the rollout KV cache in between.
-        self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda"))
+        self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
         if not self.forward_only:
             sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
             self.master = self.params.flat[sl].float().clone()
@@ -233,7 +248,7 @@ class NativeEngine(BaseEngine):
 
     # ------------------------------------------------------------------------------------ optimizer
     def _alloc_grads(self) -> None:
-        self.params.attach_main_grad()
+        self.params.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
 
@@ -252,6 +267,8 @@ class NativeEngine(BaseEngine):
         W = self.world
         mg = self.params.main_grad
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        if self.fused_comm:
+            return self._fused_optimizer_step()
         if W > 1:
             if self.device.type == "cuda":
                 dist.reduce_scatter_tensor(self.grad_shard, mg, op=dist.ReduceOp.AVG)
@@ -295,6 +312,31 @@ class NativeEngine(BaseEngine):
             self.grad_shard = None
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
+        return norm
+
+    def _fused_optimizer_step(self) -> float:
+        """Peer-memory path: barrier -> reduce-scatter+mean+sumsq kernel (peer loads of this rank's shard of every
+        gradient buffer) -> scalar norm all-reduce -> AdamW + all-gather kernel (stores the new bf16 weights into every
+        rank's working buffer) -> barrier."""
+        oc = self.optimizer_config
+        ops = native.ops()
+        use_mc = os.environ.get("VERL_B200_MULTIMEM", "0") == "1"
+        lr = lr_at_step(oc, self.sched_step)
+        self.opt_step_count += 1
+        self._peer_barrier()
+        self.ctrl.zero_()
+        ops.rs_sumsq_(self._sym_grads.ptrs, self._sym_grads.multicast_ptr if use_mc else 0, self.grad_shard, self.shard_lo,
+                      self.rank, 1.0 / self.world, self.ctrl)
+        dist.all_reduce(self.ctrl[:1])
+        ops.clip_coef_(self.ctrl, float(oc.clip_grad))
+        ops.adamw_allgather_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self._sym_params.ptrs,
+                             self._sym_params.multicast_ptr if use_mc else 0, self.shard_lo, self.rank, self.ctrl, lr,
+                             float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay), self.opt_step_count)
+        self._peer_barrier()
+        norm = float(self.ctrl[3])
+        code = int(ops.comm_status())
+        if code != 0:
+            raise RuntimeError(f"peer barrier timed out (status {code}): a rank did not reach the optimizer step")
         return norm
 
     def _publish_shard(self) -> None:
