@@ -16,16 +16,16 @@ def _port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, queue):
     try:
-        _worker_body(rank, world, port, out)
+        _worker_body(rank, world, port, queue)
     except Exception:  # report instead of leaving the parent waiting
         import traceback
 
-        out.put((rank, {"error": traceback.format_exc()}))
+        queue.put((rank, {"error": traceback.format_exc()}))
 
 
-def _worker_body(rank, world, port, out):
+def _worker_body(rank, world, port, queue):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -91,7 +91,7 @@ def _worker_body(rank, world, port, out):
         res["timeout_status"] = int(ops.comm_status())
         res["alive_after_timeout"] = float(torch.ones(4, device=dev).sum())
     dist.barrier()
-    out.put((rank, res))
+    queue.put((rank, res))
     dist.destroy_process_group()
 
 
