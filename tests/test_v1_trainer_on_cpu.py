@@ -1,0 +1,85 @@
+"""v1 trainers end to end on CPU with the tiny model: sync and colocate_async both train for two steps."""
+import os
+
+import pytest
+
+ARGS = ['data.train_batch_size=4', 'data.max_prompt_length=16', 'data.max_response_length=12', 'data.synthetic.num_prompts=32',
+        'data.synthetic.prompt_length=16', 'data.synthetic.vocab_high=512', 'actor_rollout_ref.model.path=tiny-qwen2',
+        'actor_rollout_ref.rollout.n=2', 'actor_rollout_ref.actor.ppo_mini_batch_size=4',
+        'actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8', 'actor_rollout_ref.actor.use_kl_loss=true',
+        'actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=16', 'actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=16',
+        'algorithm.adv_estimator=grpo', 'reward_model.reward_manager=token_rule', 'trainer.n_gpus_per_node=1', 'trainer.total_epochs=4',
+        'trainer.total_training_steps=2', 'trainer.device=cpu', 'trainer.val_before_train=false', 'actor_rollout_ref.rollout.max_num_seqs=16',
+        'actor_rollout_ref.rollout.block_size=8', 'trainer.resume_mode=disable', 'trainer.use_v1=true', 'trainer.worker_group=inprocess']
+
+
+@pytest.mark.parametrize("mode", ["sync", "colocate_async"])
+def test_v1_modes_train(mode, monkeypatch):
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.trainer.main_ppo import main
+
+    t = main(ARGS + [f"trainer.v1.trainer_mode={mode}"])
+    assert type(t).trainer_mode == mode
+    assert t.global_steps == 3 and t.param_version == 2
+    assert t.last_batch.batch["advantages"].shape == (8, 12)
+    if mode == "colocate_async":
+        # the warm-up batch was generated under older weights and is still usable (threshold 1)
+        assert t.replay_buffer.inflight() + t.replay_buffer.count("finished") > 0
+
+
+def test_separate_async_single_pool_and_switch_controller(monkeypatch):
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.trainer.main_ppo import main
+    from verl_b200.trainer.ppo.v1.trainer_separate_async import SwitchController
+
+    t = main(ARGS + ["trainer.v1.trainer_mode=separate_async", "trainer.v1.parameter_sync_step=2", "trainer.total_training_steps=1"])
+    assert t.param_version == 1 and t.topo.R == 0  # two optimizer rounds, one weight hand-over
+    sc = SwitchController(enabled=True, ratio=2.0)
+    assert sc.should_switch(0.0)  # no cost measured yet: switching is free
+    sc.record_switch_cost(1.0)
+    assert not sc.should_switch(1.0) and sc.should_switch(2.5)
+    sc.record_wait(3.0)
+    assert not sc.should_switch(2.5)  # on average only 0.5 s of waiting is left: below 2 x cost
+    assert not SwitchController(enabled=False).should_switch(100.0)
+
+
+def _split_proc(rank, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      VERL_ENGINE_DEVICE="cpu")
+    try:
+        from verl_b200.trainer.main_ppo import main
+
+        args = [a for a in ARGS if not a.startswith("trainer.worker_group")] + [
+            "trainer.worker_group=spmd", "trainer.v1.trainer_mode=separate_async", "trainer.v1.rollout_ranks=1",
+            "trainer.v1.hybrid_switch=false", "trainer.total_training_steps=2"]
+        res = main(args)
+        if isinstance(res, dict):
+            q.put((rank, res))
+        else:
+            q.put((rank, {"param_version": res.param_version, "steps": res.global_steps}))
+    except Exception:
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+def test_separate_async_two_processes_trainer_and_rollout_rank():
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_split_proc, args=(r, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    assert "error" not in res[0], res[0]["error"]
+    assert "error" not in res[1], res[1]["error"]
+    assert res[0]["param_version"] == 2 and res[0]["steps"] == 3
+    assert res[1]["groups"] >= 8 and res[1]["weight_syncs"] >= 1  # all samples came from the rollout rank

@@ -64,3 +64,19 @@ class NCCLCheckpointEngine(CheckpointEngine):
             dist.broadcast(bucket, src=self.src, group=self.group)
             for name, t in asm.feed(bucket, metas):
                 yield name, t
+
+    # ---- identical-layout fast path: both sides hold the same flat parameter buffer, so the buffer itself is
+    # broadcast in place, slice by slice (no packing, no staging copy, no metadata)
+    def send_flat(self, flat: torch.Tensor) -> None:
+        self._bcast_flat(flat)
+
+    def receive_flat(self, flat: torch.Tensor) -> None:
+        self._bcast_flat(flat)
+
+    def _bcast_flat(self, flat: torch.Tensor) -> None:
+        step = max(1, self.bucket_size // flat.element_size())
+        works = []
+        for lo in range(0, flat.numel(), step):
+            works.append(dist.broadcast(flat[lo : lo + step], src=self.src, group=self.group, async_op=True))
+        for w in works:
+            w.wait()

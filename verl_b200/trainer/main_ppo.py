@@ -89,12 +89,51 @@ class TaskRunner:
             from ..utils.distributed import initialize_global_process_group
 
             initialize_global_process_group()
-        trainer = RayPPOTrainer(config=config, tokenizer=tokenizer, role_worker_mapping=self.role_worker_mapping,
-                                resource_pool_manager=pool_mgr, ray_worker_group_cls=wg_cls, reward_fn=reward_fn,
-                                val_reward_fn=val_reward_fn, device_name=config.trainer.device, worker_group_kwargs=wg_kwargs)
-        trainer.init_workers()
+        trainer_cls, v1, extra = RayPPOTrainer, False, {}
+        in_process = wg_cls.__name__ in ("InProcessWorkerGroup", "SPMDWorkerGroup")
+        if config.trainer.get("use_v1", False) and in_process:
+            from .ppo.v1.trainer_base import get_trainer_cls
+
+            v1cfg = config.trainer.get("v1") or {}
+            mode = v1cfg.get("trainer_mode", "sync")
+            trainer_cls, v1 = get_trainer_cls(mode), True
+            if mode == "separate_async":
+                res = self._split_job(config, int(v1cfg.get("rollout_ranks", 0) or 0), tokenizer)
+                if not hasattr(res, "T"):
+                    return res  # this rank served rollout until the trainers finished
+                extra["topology"] = res
+        trainer = trainer_cls(config=config, tokenizer=tokenizer, role_worker_mapping=self.role_worker_mapping,
+                              resource_pool_manager=pool_mgr, ray_worker_group_cls=wg_cls, reward_fn=reward_fn,
+                              val_reward_fn=val_reward_fn, device_name=config.trainer.device, worker_group_kwargs=wg_kwargs,
+                              **extra)
+        if v1:
+            trainer.init()
+        else:
+            trainer.init_workers()
         trainer.fit()
         return trainer
+
+
+def _split_job_impl(config, rollout_ranks: int, tokenizer):
+    """separate_async: build the rank layout; rollout-only ranks serve until told to stop and return their stats,
+    trainer ranks get the topology back."""
+    from ..utils.distributed import set_data_parallel_group
+    from ..workers.engine_workers import ActorRolloutRefWorker
+    from .ppo.v1.trainer_separate_async import RolloutService, SeparateTopology
+
+    topo = SeparateTopology(rollout_ranks)
+    if topo.R == 0:
+        return topo
+    if not topo.is_rollout_rank:
+        set_data_parallel_group(topo.trainer_group)
+        return topo
+    set_data_parallel_group(topo.rollout_group)
+    worker = ActorRolloutRefWorker(config=config.actor_rollout_ref, role="rollout")
+    worker.init_model()
+    return RolloutService(config, worker, topo, tokenizer).run()
+
+
+TaskRunner._split_job = staticmethod(_split_job_impl)
 
 
 def run_ppo(config, task_runner_class=None):

@@ -21,12 +21,23 @@ __all__ = ["reduce_metrics", "compute_data_metrics", "compute_timing_metrics", "
            "_compute_response_info"]
 
 
+def _flatten(v):
+    """Leaves of arbitrarily nested lists/tuples/arrays (per-worker lists of per-micro-batch lists)."""
+    if isinstance(v, np.ndarray):
+        v = v.reshape(-1).tolist()
+    for x in v:
+        if isinstance(x, (list, tuple, np.ndarray)):
+            yield from _flatten(x)
+        else:
+            yield x
+
+
 def reduce_metrics(metrics: dict[str, Any]) -> dict[str, float]:
     """Mean of list-valued metrics; keys containing 'max'/'min' reduce with max/min."""
     out = {}
     for k, v in metrics.items():
         if isinstance(v, (list, tuple, np.ndarray)):
-            vals = [float(x) for x in (np.asarray(v).reshape(-1).tolist() if isinstance(v, np.ndarray) else v)]
+            vals = [float(x) for x in _flatten(v)]
             if not vals:
                 continue
             out[k] = float(np.max(vals)) if "max" in k.split("/")[-1] else float(np.min(vals)) if "min" in k.split("/")[-1] else float(np.mean(vals))

@@ -163,7 +163,10 @@ class RayPPOTrainer:
     # ------------------------------------------------------------------------------------ data
     def _dp_rank_world(self):
         if self.spmd and dist.is_initialized():
-            return dist.get_rank(), dist.get_world_size()
+            from ...utils.distributed import get_data_parallel_group
+
+            g = get_data_parallel_group()
+            return dist.get_rank(g), dist.get_world_size(g)
         return 0, 1
 
     def _create_dataloader(self, train_dataset, val_dataset, collate_fn, train_sampler) -> None:
@@ -317,9 +320,12 @@ class RayPPOTrainer:
         dev = "cuda" if self.device_name == "cuda" and torch.cuda.is_available() else "cpu"
         t = torch.tensor([float(metrics[k]) for k in keys], dtype=torch.float64, device=dev)
         mx, mn = t.clone(), t.clone()
-        dist.all_reduce(t)
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        from ...utils.distributed import get_data_parallel_group
+
+        g = get_data_parallel_group()
+        dist.all_reduce(t, group=g)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=g)
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN, group=g)
         out = dict(metrics)
         for i, k in enumerate(keys):
             leaf = k.split("/")[-1]
@@ -428,6 +434,18 @@ class RayPPOTrainer:
         n_gpus = self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager is not None else world
         rollout_cfg = cfg.actor_rollout_ref.rollout
         with marked_timer("step", timing_raw):
+            batch = self.rollout_phase(batch_dict, metrics, timing_raw)
+            batch = self.learn_phase(batch, metrics, timing_raw)
+            self.sync_phase(batch, metrics, timing_raw)
+        return self.finish_step(batch, metrics, timing_raw)
+
+    def rollout_phase(self, batch_dict: dict, metrics: dict, timing_raw: dict) -> DataProto:
+        """Prompts -> n sampled responses per prompt, merged with the prompt-side fields."""
+        cfg = self.config
+        algo = cfg.algorithm
+        rank, world = self._dp_rank_world()
+        rollout_cfg = cfg.actor_rollout_ref.rollout
+        if True:
             batch = DataProto.from_single_dict(batch_dict)
             batch.meta_info["temperature"] = rollout_cfg.temperature
             if "uid" not in batch.non_tensor_batch:
@@ -455,6 +473,14 @@ class RayPPOTrainer:
                 batch.batch["reward_baselines"] = baseline
             if "response_mask" not in batch.batch.keys():
                 batch.batch["response_mask"] = compute_response_mask(batch)
+        return batch
+
+    def learn_phase(self, batch: DataProto, metrics: dict, timing_raw: dict) -> DataProto:
+        """Reward -> old/ref log-probs (-> values) -> advantages -> critic/actor updates on a generated batch."""
+        cfg = self.config
+        algo = cfg.algorithm
+        rollout_cfg = cfg.actor_rollout_ref.rollout
+        if True:
             if cfg.trainer.get("balance_batch", True) and not self.spmd:
                 self._balance_batch(batch, metrics)
             batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
@@ -506,12 +532,22 @@ class RayPPOTrainer:
                 with marked_timer("update_actor", timing_raw, color="red"):
                     aout = self.actor_rollout_wg.update_actor(batch)
                 metrics.update(reduce_metrics(aout.meta_info["metrics"]))
+        return batch
+
+    def sync_phase(self, batch: Optional[DataProto], metrics: dict, timing_raw: dict) -> None:
+        """Make the rollout side see the freshly updated weights (in place when colocated)."""
+        cfg = self.config
+        if True:
             with marked_timer("update_weights", timing_raw, color="red"):
                 res = self.actor_rollout_wg.update_weights(self.global_steps)
                 res = res[0] if isinstance(res, list) else res
                 metrics["timing_s/update_weights_worker"] = float((res or {}).get("timing_s/update_weights", 0.0))
-            if cfg.trainer.get("rollout_data_dir"):
+            if batch is not None and cfg.trainer.get("rollout_data_dir"):
                 self._dump_generations(batch, cfg.trainer.rollout_data_dir)
+
+    def finish_step(self, batch: DataProto, metrics: dict, timing_raw: dict) -> tuple[dict, dict]:
+        rank, world = self._dp_rank_world()
+        n_gpus = self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager is not None else world
         metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
         metrics.update(compute_timing_metrics(batch=batch, timing_raw=timing_raw))
         metrics.update(compute_throughout_metrics(batch=batch, timing_raw=timing_raw, n_gpus=max(1, n_gpus if not self.spmd else 1)))

@@ -15,7 +15,21 @@ import torch.distributed as dist
 from .device import get_device_name
 
 __all__ = ["initialize_global_process_group", "initialize_global_process_group_ray", "destroy_global_process_group",
-           "set_numa_affinity", "stateless_init_process_group", "get_world_size", "get_rank"]
+           "set_numa_affinity", "stateless_init_process_group", "get_world_size", "get_rank", "set_data_parallel_group",
+           "get_data_parallel_group"]
+
+_DP_GROUP = None
+
+
+def set_data_parallel_group(group) -> None:
+    """Restrict the training engines created afterwards to ``group`` (e.g. the trainer ranks of a job whose other
+    ranks only serve rollout). ``None`` restores the default: all ranks."""
+    global _DP_GROUP
+    _DP_GROUP = group
+
+
+def get_data_parallel_group():
+    return _DP_GROUP
 
 
 def initialize_global_process_group(timeout_second: int = 600, spmd: bool = False):

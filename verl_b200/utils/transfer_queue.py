@@ -1,0 +1,121 @@
+"""In-process key/value sample store with tags ("TransferQueue" role of the v1 trainer).
+
+Values are per-key field dictionaries (tensors, lists, scalars); tags are small metadata dictionaries that can be
+listed and filtered without touching the values. Keys live in partitions (``train`` / ``val``). All methods are
+thread-safe so a producer thread (rollout) and a consumer (trainer) may share one store. A cross-process variant
+backed by a ``torch.distributed`` store is in ``verl_b200.experimental.fully_async_policy.message_queue``.
+
+Parity target: the external TransferQueue package as used by ``verl/trainer/ppo/v1/replay_buffer.py`` and
+``verl/protocol.py:1231-1331`` (``KVBatchMeta``).
+"""
+
+from __future__ import annotations
+
+import threading
+from dataclasses import dataclass, field
+from typing import Any, Callable, Iterable, Optional
+
+__all__ = ["KVBatchMeta", "TransferQueue", "get_default_queue"]
+
+
+@dataclass
+class KVBatchMeta:
+    """Handle on a set of keys (and optionally a subset of fields) of one partition; cheap to pass around."""
+
+    keys: list[str]
+    partition_id: str = "train"
+    fields: Optional[list[str]] = None
+    tags: list[dict] = field(default_factory=list)
+
+    def __len__(self) -> int:
+        return len(self.keys)
+
+    def chunk(self, n: int) -> list["KVBatchMeta"]:
+        size = (len(self.keys) + n - 1) // n
+        return [KVBatchMeta(self.keys[i * size:(i + 1) * size], self.partition_id, self.fields, self.tags[i * size:(i + 1) * size])
+                for i in range(n)]
+
+    @staticmethod
+    def concat(metas: Iterable["KVBatchMeta"]) -> "KVBatchMeta":
+        metas = list(metas)
+        out = KVBatchMeta([], metas[0].partition_id if metas else "train", metas[0].fields if metas else None, [])
+        for m in metas:
+            out.keys += m.keys
+            out.tags += m.tags
+        return out
+
+
+class TransferQueue:
+    def __init__(self):
+        self._lock = threading.RLock()
+        self._values: dict[str, dict[str, dict[str, Any]]] = {}
+        self._tags: dict[str, dict[str, dict]] = {}
+        self._cond = threading.Condition(self._lock)
+
+    def put(self, key: str, fields: Optional[dict] = None, tags: Optional[dict] = None, partition_id: str = "train") -> None:
+        with self._cond:
+            self._values.setdefault(partition_id, {}).setdefault(key, {}).update(fields or {})
+            self._tags.setdefault(partition_id, {}).setdefault(key, {}).update(tags or {})
+            self._cond.notify_all()
+
+    def set_tags(self, key: str, tags: dict, partition_id: str = "train") -> None:
+        self.put(key, None, tags, partition_id)
+
+    def get_tags(self, key: str, partition_id: str = "train") -> dict:
+        with self._lock:
+            return dict(self._tags.get(partition_id, {}).get(key, {}))
+
+    def list_keys(self, partition_id: str = "train", where: Optional[Callable[[str, dict], bool]] = None) -> list[str]:
+        with self._lock:
+            tags = self._tags.get(partition_id, {})
+            return [k for k, t in tags.items() if where is None or where(k, t)]
+
+    def get(self, keys: Iterable[str], fields: Optional[list[str]] = None, partition_id: str = "train") -> list[dict]:
+        with self._lock:
+            part = self._values.get(partition_id, {})
+            out = []
+            for k in keys:
+                v = part[k]
+                out.append(dict(v) if fields is None else {f: v[f] for f in fields if f in v})
+            return out
+
+    def get_meta(self, keys: Iterable[str], fields=None, partition_id: str = "train") -> KVBatchMeta:
+        keys = list(keys)
+        with self._lock:
+            tags = [dict(self._tags.get(partition_id, {}).get(k, {})) for k in keys]
+        return KVBatchMeta(keys, partition_id, fields, tags)
+
+    def get_data(self, meta: KVBatchMeta) -> list[dict]:
+        return self.get(meta.keys, meta.fields, meta.partition_id)
+
+    def delete(self, keys: Iterable[str], partition_id: str = "train") -> None:
+        with self._lock:
+            for k in keys:
+                self._values.get(partition_id, {}).pop(k, None)
+                self._tags.get(partition_id, {}).pop(k, None)
+
+    def clear(self, partition_id: Optional[str] = None) -> None:
+        with self._lock:
+            for store in (self._values, self._tags):
+                if partition_id is None:
+                    store.clear()
+                else:
+                    store.pop(partition_id, None)
+
+    def size(self, partition_id: str = "train") -> int:
+        with self._lock:
+            return len(self._tags.get(partition_id, {}))
+
+    def wait(self, predicate: Callable[[], bool], timeout: Optional[float] = None) -> bool:
+        with self._cond:
+            return self._cond.wait_for(predicate, timeout)
+
+
+_default: Optional[TransferQueue] = None
+
+
+def get_default_queue() -> TransferQueue:
+    global _default
+    if _default is None:
+        _default = TransferQueue()
+    return _default

@@ -93,8 +93,12 @@ class NativeEngine(BaseEngine):
     def initialize(self) -> None:
         if self._initialized:
             return
-        self.rank = dist.get_rank() if dist.is_initialized() else 0
-        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        from ....utils.distributed import get_data_parallel_group
+
+        self.group = get_data_parallel_group()  # None = the default (world) group
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self._src0 = dist.get_global_rank(self.group, 0) if (self.group is not None and dist.is_initialized()) else 0
         if self.device_name == "cuda":
             self.device = torch.device("cuda", torch.cuda.current_device())
             self.dtype = torch.bfloat16
@@ -110,7 +114,8 @@ class NativeEngine(BaseEngine):
             self.params = self._shared_params
         else:
             want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
-                          and self.world > 1 and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
+                          and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
+                          and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
             buf = None
             if want_fused:
                 from ....parallel.symmetric import PeerBarrier, SymmetricBuffer, symmetric_available
@@ -154,7 +159,7 @@ class NativeEngine(BaseEngine):
         elif not load:
             self.params.init_weights(seed=seed)
         if self.world > 1:
-            dist.broadcast(self.params.flat, src=0)
+            dist.broadcast(self.params.flat, src=self._src0, group=self.group)
 
     # ------------------------------------------------------------------------------------ topology
     def get_data_parallel_size(self) -> int:
@@ -164,7 +169,7 @@ class NativeEngine(BaseEngine):
         return self.rank
 
     def get_data_parallel_group(self):
-        return None
+        return self.group
 
     # ------------------------------------------------------------------------------------ batching
     def _micro_batches(self, data: dict, forward_only: bool) -> list[dict]:
@@ -208,7 +213,7 @@ class NativeEngine(BaseEngine):
             seqs = torch.tensor(float(n), device=self.device)
             if self.world > 1:
                 pack = torch.stack([tok, seqs])
-                dist.all_reduce(pack)
+                dist.all_reduce(pack, group=self.group)
                 tok, seqs = pack[0], pack[1]
             data["global_batch_info"] = dict(dp_size=self.world, batch_num_tokens=tok, global_batch_size=seqs,
                                              loss_scale_factor=data.get("loss_scale_factor"))
@@ -271,9 +276,9 @@ class NativeEngine(BaseEngine):
             return self._fused_optimizer_step()
         if W > 1:
             if self.device.type == "cuda":
-                dist.reduce_scatter_tensor(self.grad_shard, mg, op=dist.ReduceOp.AVG)
+                dist.reduce_scatter_tensor(self.grad_shard, mg, op=dist.ReduceOp.AVG, group=self.group)
             else:  # gloo has no reduce-scatter: all-reduce and keep this rank's slice
-                dist.all_reduce(mg)
+                dist.all_reduce(mg, group=self.group)
                 self.grad_shard.copy_(mg[sl]).div_(W)
         self.ctrl.zero_()
         lr = lr_at_step(oc, self.sched_step)
@@ -282,7 +287,7 @@ class NativeEngine(BaseEngine):
             ops = native.ops()
             ops.sumsq_(self.grad_shard, self.ctrl)
             if W > 1:
-                dist.all_reduce(self.ctrl[:1])
+                dist.all_reduce(self.ctrl[:1], group=self.group)
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
             ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.params.flat[sl], self.ctrl,
                        lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
@@ -291,7 +296,7 @@ class NativeEngine(BaseEngine):
         else:
             ss = self.grad_shard.double().pow(2).sum()
             if W > 1:
-                dist.all_reduce(ss)
+                dist.all_reduce(ss, group=self.group)
             norm = ss.sqrt().float()
             if torch.isfinite(norm):
                 coef = min(1.0, float(oc.clip_grad) / (float(norm) + 1e-6)) if oc.clip_grad and oc.clip_grad > 0 else 1.0
@@ -327,7 +332,7 @@ class NativeEngine(BaseEngine):
         self.ctrl.zero_()
         ops.rs_sumsq_(self._sym_grads.ptrs, self._sym_grads.multicast_ptr if use_mc else 0, self.grad_shard, self.shard_lo,
                       self.rank, 1.0 / self.world, self.ctrl)
-        dist.all_reduce(self.ctrl[:1])
+        dist.all_reduce(self.ctrl[:1], group=self.group)
         ops.clip_coef_(self.ctrl, float(oc.clip_grad))
         ops.adamw_allgather_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self._sym_params.ptrs,
                              self._sym_params.multicast_ptr if use_mc else 0, self.shard_lo, self.rank, self.ctrl, lr,
@@ -345,10 +350,10 @@ class NativeEngine(BaseEngine):
             return
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if self.device.type == "cuda":
-            dist.all_gather_into_tensor(self.params.flat, self.params.flat[sl].clone())
+            dist.all_gather_into_tensor(self.params.flat, self.params.flat[sl].clone(), group=self.group)
         else:
             parts = [self.params.flat[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
-            dist.all_gather(parts, self.params.flat[sl].clone())
+            dist.all_gather(parts, self.params.flat[sl].clone(), group=self.group)
 
     def lr_scheduler_step(self) -> float:
         self.sched_step += 1
@@ -399,7 +404,7 @@ class NativeEngine(BaseEngine):
 
                 save_hf_weights(self.params, hf_dir)
         if W > 1:
-            dist.barrier()
+            dist.barrier(group=self.group)
 
     def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, del_local_after_load: bool = False,
                         **kwargs) -> None:

@@ -254,7 +254,11 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             rc = cfg.rollout if isinstance(cfg.rollout, RolloutConfig) else omega_conf_to_dataclass(cfg.rollout, RolloutConfig)
             self.rollout_config = rc
             src = self.actor if self.actor is not None else self.ref
-            assert src is not None, "a rollout-only worker needs weights: use role 'actor_rollout' or load a checkpoint"
+            if src is None:  # rollout-only rank: a forward-only engine holds the weights that weight sync overwrites
+                self.rollout_weights = EngineRegistry.new("language_model", "fsdp", model_config=mc,
+                                                          engine_config=FSDPEngineConfig(forward_only=True), optimizer_config=None)
+                self.rollout_weights.initialize()
+                src = self.rollout_weights
             arch = mc.arch
             max_len = rc.max_model_len or (rc.prompt_length + rc.response_length)
             self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs,
