@@ -83,3 +83,13 @@ def test_separate_async_two_processes_trainer_and_rollout_rank():
     assert "error" not in res[1], res[1]["error"]
     assert res[0]["param_version"] == 2 and res[0]["steps"] == 3
     assert res[1]["groups"] >= 8 and res[1]["weight_syncs"] >= 1  # all samples came from the rollout rank
+
+
+def test_one_step_off_single_pool(monkeypatch):
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.experimental.one_step_off_policy.main_ppo import main
+
+    t = main(ARGS + ["trainer.total_training_steps=3"])
+    assert type(t).__name__ == "OneStepOffRayTrainer" and t.param_version == 3
+    ages = t.last_batch  # batches after the first were generated one version earlier
+    assert ages is not None

@@ -1,0 +1,122 @@
+"""Streaming sample producer of the fully-asynchronous pipeline.
+
+Owns the prompt stream. Keeps up to ``max_concurrent_samples`` prompts in flight on the rollout replicas, packs each
+finished group into a ``RolloutSample`` and puts it on the message queue. Production pauses while the number of
+samples that would be stale when consumed reaches the budget
+``required_samples x trigger_parameter_sync_step x (1 + staleness_threshold)`` counted since the last weight sync
+(finished-but-unconsumed + in flight), and resumes after the next sync. Replicas can be added, removed and
+rebalanced while requests are running.
+
+Parity target: ``verl/experimental/fully_async_policy/fully_async_rollouter.py`` (``_feed_samples`` :859,
+``_processor_worker`` :902, ``_streaming_generation_main`` :1017, ``_should_pause_generation`` :1142,
+``add_replicas/remove_replicas/rebalance_requests`` :144-264, :1199-1274).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import time
+import uuid
+from typing import Callable, Iterator, Optional
+
+from .detach_utils import RolloutSample
+from .message_queue import MessageQueue
+
+__all__ = ["FullyAsyncRollouter"]
+
+
+class FullyAsyncRollouter:
+    def __init__(self, agent_worker, server_manager, message_queue: MessageQueue, prompt_source: Callable[[int], list[dict]],
+                 n: int, sampling_params: dict, required_samples: int, trigger_parameter_sync_step: int = 1,
+                 staleness_threshold: float = 1.0, max_concurrent_samples: Optional[int] = None, total_samples: Optional[int] = None):
+        self.w, self.sm, self.mq = agent_worker, server_manager, message_queue
+        self.prompt_source, self.n, self.sp = prompt_source, int(n), dict(sampling_params)
+        self.required_samples = int(required_samples)
+        self.trigger = max(1, int(trigger_parameter_sync_step))
+        self.staleness_threshold = float(staleness_threshold)
+        self.max_concurrent = int(max_concurrent_samples or 2 * required_samples)
+        self.total_samples = total_samples
+        self.param_version = 0
+        self.submitted = self.produced = self.produced_since_sync = 0
+        self.paused = False
+        self.running: dict[str, asyncio.Task] = {}
+        self.stats = {"pauses": 0, "failed": 0}
+
+    # ---- staleness control
+    def max_samples_per_version(self) -> int:
+        return int(self.required_samples * self.trigger * (1.0 + self.staleness_threshold))
+
+    def _should_pause_generation(self) -> bool:
+        if self.total_samples is not None and self.submitted >= self.total_samples:
+            return True
+        return self.produced_since_sync + len(self.running) >= self.max_samples_per_version()
+
+    def update_param_version(self, version: int) -> None:
+        """Called by the parameter synchroniser after a weight sync: the budget starts over."""
+        self.param_version = int(version)
+        self.produced_since_sync = self.mq.get_queue_size()  # what is still queued was made under older weights
+        self.paused = False
+
+    # ---- production
+    async def _one_sample(self, prompt: dict) -> None:
+        uid = str(prompt.get("uid") or uuid.uuid4().hex)
+        t0, v0 = time.time(), self.param_version
+        name = str(prompt.get("agent_name", self.w.default_loop))
+        outs = await asyncio.gather(*[self.w._run_one(name, self.sp, prompt) for _ in range(self.n)], return_exceptions=True)
+        bad = [o for o in outs if isinstance(o, BaseException)]
+        good = [o for o in outs if not isinstance(o, BaseException)]
+        self.stats["failed"] += len(bad)
+        sample = RolloutSample(sample_id=f"{uid}@{v0}", uid=uid, trajectories=good, prompt=prompt, param_version_start=v0,
+                               param_version_end=self.param_version, processing_time=time.time() - t0, failed=bool(bad))
+        self.running.pop(uid, None)
+        if good:
+            self.mq.put_sample(sample, self.param_version)
+            self.produced += 1
+            self.produced_since_sync += 1
+
+    def feed(self) -> int:
+        """Admit prompts up to the concurrency and staleness limits; returns how many were started."""
+        started = 0
+        while len(self.running) < self.max_concurrent:
+            if self._should_pause_generation():
+                if not self.paused:
+                    self.paused = True
+                    self.stats["pauses"] += 1
+                break
+            got = self.prompt_source(1)
+            if not got:
+                break
+            p = dict(got[0])
+            p.setdefault("uid", uuid.uuid4().hex)
+            self.running[p["uid"]] = asyncio.ensure_future(self._one_sample(p))
+            self.submitted += 1
+            started += 1
+        return started
+
+    async def run(self, stop: Callable[[], bool], idle_sleep: float = 0.0) -> None:
+        """Streaming main loop (for a dedicated event loop / thread)."""
+        while not stop():
+            self.feed()
+            await asyncio.sleep(idle_sleep)
+
+    # ---- elastic replicas
+    async def add_replicas(self, replicas: list) -> None:
+        await self.sm.add_replicas(replicas)
+
+    async def remove_replicas(self, replicas: list) -> None:
+        """Stop routing to the replicas, abort what they run (clients re-issue elsewhere with the partial output)."""
+        self.sm.lb.remove_servers([r.server_address for r in replicas])
+        for r in replicas:
+            await r.server_handle.abort_all_requests()
+            await r.server_handle.resume_generation()
+            self.sm.servers.pop(r.server_address, None)
+            if r in self.sm.replicas:
+                self.sm.replicas.remove(r)
+
+    def rebalance_requests(self) -> dict:
+        return self.sm.lb.snapshot()
+
+    def statistics(self) -> dict:
+        return {"rollouter/submitted": self.submitted, "rollouter/produced": self.produced, "rollouter/running": len(self.running),
+                "rollouter/pauses": self.stats["pauses"], "rollouter/failed_sessions": self.stats["failed"],
+                "rollouter/param_version": self.param_version, "rollouter/queue_size": self.mq.get_queue_size()}

@@ -1,0 +1,186 @@
+"""Consumer side of the fully-asynchronous pipeline and the in-process composition of both sides.
+
+``FullyAsyncTrainer.fit`` repeats: pull ``require_batches x ppo_mini_batch_size`` samples from the message queue
+(driving the rollouter while it waits), assemble the batch, run the learning phase, and after every
+``trigger_parameter_sync_step`` local updates synchronise weights, which also resets the rollouter's staleness
+budget. Rollouter and trainer share one process and one event loop here; with a separate rollout pool the same
+classes sit on the two sides of a ``StoreMessageQueue``.
+
+Parity target: ``verl/experimental/fully_async_policy/fully_async_trainer.py`` (``_get_samples_from_queue`` :375,
+``fit_step`` :536, ``_fit_update_weights`` :690) and ``fully_async_main.py``.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import time
+from typing import Any, Optional
+
+import numpy as np
+import torch
+
+from ...protocol import DataProto
+from ...trainer.ppo.ray_trainer import compute_response_mask
+from ...trainer.ppo.v1.trainer_base import PPOTrainer
+from ...utils.profiler import marked_timer
+from ...utils.tracking import Tracking
+from .detach_utils import MetricsAggregator, RolloutSample
+from .fully_async_rollouter import FullyAsyncRollouter
+from .message_queue import MessageQueue
+from .param_sync import ParameterSynchronizer
+
+__all__ = ["FullyAsyncTrainer", "assemble_batch_from_rollout_samples"]
+
+
+def assemble_batch_from_rollout_samples(samples: list[RolloutSample], postprocess, to_device) -> DataProto:
+    outs, uids, v0, v1 = [], [], [], []
+    for s in samples:
+        for o in s.trajectories:
+            outs.append(o)
+            uids.append(s.uid)
+            v0.append(s.param_version_start)
+            v1.append(s.param_version_end)
+    shell = DataProto.from_dict(tensors={"dummy": torch.zeros(len(outs), 1)}, meta_info={})
+    batch = postprocess(outs, shell)
+    batch.meta_info.pop("timing", None)
+    batch.meta_info.pop("reward_extra_keys", None)
+    batch.non_tensor_batch["uid"] = np.array(uids, dtype=object)
+    batch.non_tensor_batch["param_version_start"] = np.array(v0, dtype=np.int64)
+    batch.non_tensor_batch["param_version_end"] = np.array(v1, dtype=np.int64)
+    keys = sorted({k for s in samples for k in s.prompt if k not in ("uid", "raw_prompt_ids")})
+    for k in keys:
+        arr = np.empty(len(uids), dtype=object)
+        arr[:] = [s.prompt.get(k) for s in samples for _ in s.trajectories]
+        batch.non_tensor_batch.setdefault(k, arr)
+    if "response_mask" not in batch.batch.keys():
+        batch.batch["response_mask"] = compute_response_mask(batch)
+    return to_device(batch)
+
+
+class FullyAsyncTrainer(PPOTrainer):
+    trainer_mode = "fully_async"
+    fully_async_client = True
+
+    def _ac(self, key: str, default=None):
+        ac = self.config.get("async_training") if hasattr(self.config, "get") else None
+        return default if ac is None or ac.get(key) is None else ac.get(key)
+
+    def on_init_end(self) -> None:
+        rc = self.config.actor_rollout_ref.rollout
+        mini = int(self.config.actor_rollout_ref.actor.ppo_mini_batch_size)
+        self.required_samples = int(self._ac("require_batches", 1)) * mini
+        self.trigger = int(self._ac("trigger_parameter_sync_step", 1))
+        self.mq = MessageQueue(max_queue_size=int(self._ac("max_queue_size", 16 * self.required_samples)))
+        sp = dict(temperature=float(rc.temperature), top_p=float(rc.get("top_p", 1.0)), top_k=int(rc.get("top_k", -1)), logprobs=True)
+        total = self._ac("total_rollout_samples")
+
+        def prompt_source(k: int) -> list[dict]:
+            out = []
+            for p in self._next_prompts(k):
+                kw = {a: b for a, b in p.items() if not isinstance(b, torch.Tensor)}
+                if "raw_prompt" not in kw and "input_ids" in p:
+                    ids, am = p["input_ids"], p.get("attention_mask")
+                    kw["raw_prompt_ids"] = (ids[am.bool()] if am is not None else ids).tolist()
+                out.append(kw)
+            return out
+
+        self.rollouter = FullyAsyncRollouter(self.worker_tq, self.server_manager, self.mq, prompt_source, n=int(rc.n),
+                                             sampling_params=sp, required_samples=self.required_samples,
+                                             trigger_parameter_sync_step=self.trigger,
+                                             staleness_threshold=float(self._ac("staleness_threshold", 1.0)),
+                                             max_concurrent_samples=self._ac("max_concurrent_samples"), total_samples=total)
+        self.synchronizer = ParameterSynchronizer(
+            pause_fn=lambda: (self._each_server("abort_all_requests"), self._pump()),
+            resume_fn=lambda: self._each_server("resume_generation"),
+            transfer_fn=lambda v: self.actor_rollout_wg.update_weights(v),
+            message_queue=self.mq,
+            set_version_fn=lambda v: (self.rollouter.update_param_version(v), self._each_server("set_global_steps", v)))
+        self.aggregator = MetricsAggregator()
+        self.local_updates = 0
+
+    def _drive(self) -> None:
+        async def go():
+            self.rollouter.feed()
+            await asyncio.sleep(0)
+
+        self._loop.run_until_complete(go())
+
+    def _get_samples_from_queue(self, timing_raw: dict) -> Optional[list[RolloutSample]]:
+        got: list[RolloutSample] = []
+        idle0 = time.time()
+        while len(got) < self.required_samples:
+            item = self.mq.get_sample(timeout=0.0)
+            if item is not None:
+                got.append(item[0])
+                continue
+            self._drive()
+            if not self.rollouter.running and self.mq.get_queue_size() == 0 and self.rollouter._should_pause_generation():
+                if self.rollouter.total_samples is not None and self.rollouter.submitted >= self.rollouter.total_samples:
+                    return None  # the stream ended
+                # paused on staleness with nothing in flight: only a weight sync can make progress
+                break
+        timing_raw["wait_samples"] = time.time() - idle0
+        return got or None
+
+    def fit_step(self) -> Optional[tuple[dict, dict]]:
+        metrics: dict[str, Any] = {}
+        timing_raw: dict[str, float] = {}
+        with marked_timer("step", timing_raw):
+            self._each_server("resume_generation")
+            with marked_timer("gen", timing_raw, color="red"):
+                samples = self._get_samples_from_queue(timing_raw)
+            if not samples:
+                return None
+            self._each_server("abort_all_requests")  # the GPU is time-shared: generation rests while we train
+            self._pump()
+            batch = assemble_batch_from_rollout_samples(samples, self.worker_tq._postprocess, self._to_device)
+            batch.meta_info["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+            spans = [s.staleness_span for s in samples]
+            age = [self.param_version - s.param_version_start for s in samples]
+            metrics.update({"fully_async/staleness_span/mean": float(np.mean(spans)), "fully_async/staleness_span/max": float(np.max(spans)),
+                            "fully_async/sample_age/mean": float(np.mean(age)), "fully_async/sample_age/max": float(np.max(age)),
+                            "fully_async/queue_size": float(self.mq.get_queue_size())})
+            batch = self.learn_phase(batch, metrics, timing_raw)
+            self.local_updates += 1
+            if self.local_updates % self.trigger == 0:
+                self._fit_update_weights(metrics, timing_raw)
+        metrics.update(self.rollouter.statistics())
+        return self.finish_step(batch, metrics, timing_raw)
+
+    def _fit_update_weights(self, metrics: dict, timing_raw: dict) -> None:
+        with marked_timer("update_weights", timing_raw, color="red"):
+            self.param_version += 1
+            res = self.synchronizer.sync_weights(self.param_version)
+        res = res if isinstance(res, dict) else {}
+        metrics["timing_s/param_sync"] = float(res.get("timing_s/param_sync", 0.0))
+        metrics["fully_async/param_version"] = self.param_version
+
+    def step(self):
+        return self.fit_step()
+
+    def fit(self) -> None:
+        cfg = self.config
+        logger = Tracking(project_name=cfg.trainer.get("project_name", "verl_b200"), experiment_name=cfg.trainer.get("experiment_name", "run"),
+                          default_backend=cfg.trainer.get("logger", ["console"]), config=cfg)
+        if not hasattr(self, "replay_buffer"):
+            self.init()
+        self.global_steps = 0
+        self._load_checkpoint()
+        self.sync_phase(None, {}, {})
+        self._each_server("wake_up")
+        self.global_steps = 1
+        while self.global_steps <= self.total_training_steps:
+            res = self.fit_step()
+            if res is None:
+                break
+            metrics, _ = res
+            self.aggregator.add_step_metrics(metrics, self.required_samples)
+            if self.local_updates % self.trigger == 0:
+                agg = self.aggregator.get_aggregated_metrics()
+                agg["training/global_step"] = self.global_steps
+                logger.log(data=agg, step=self.global_steps)
+                self.aggregator.reset()
+            self.global_steps += 1
+        for t in list(self.rollouter.running.values()):
+            t.cancel()
+        self.shutdown()

@@ -97,7 +97,7 @@ class TaskRunner:
             v1cfg = config.trainer.get("v1") or {}
             mode = v1cfg.get("trainer_mode", "sync")
             trainer_cls, v1 = get_trainer_cls(mode), True
-            if mode == "separate_async":
+            if mode in ("separate_async", "separation", "one_step_off"):
                 res = self._split_job(config, int(v1cfg.get("rollout_ranks", 0) or 0), tokenizer)
                 if not hasattr(res, "T"):
                     return res  # this rank served rollout until the trainers finished

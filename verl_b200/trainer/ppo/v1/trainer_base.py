@@ -49,6 +49,8 @@ def register_trainer(mode: str):
 def get_trainer_cls(mode: str) -> type:
     from . import trainer_colocate_async, trainer_separate_async, trainer_sync  # noqa: F401  (self-registering)
 
+    if mode not in _TRAINERS and mode in ("separation", "one_step_off"):
+        from ....experimental.one_step_off_policy import ray_trainer  # noqa: F401
     if mode not in _TRAINERS:
         raise ValueError(f"unknown trainer mode '{mode}' (known: {sorted(_TRAINERS)})")
     return _TRAINERS[mode]
