@@ -1,0 +1,70 @@
+"""Distillation: forward-KL top-k loss against a dense reference, hidden-state path, teacher batching and routing."""
+import asyncio
+
+import torch
+
+from verl_b200.experimental.teacher_loop import AsyncTeacherLLMServerManager, MultiTeacherModelManager, TeacherModelManager
+from verl_b200.models import DecoderModel, FlatParams, PackedBatch, get_preset
+from verl_b200.trainer.distillation.losses import (DistillationConfig, DistillationLossConfig, compute_forward_kl_topk,
+                                                   distillation_loss, student_topk_log_probs)
+
+
+def test_forward_kl_topk_matches_dense_kl_when_k_is_vocab():
+    torch.manual_seed(0)
+    s, t = torch.randn(2, 5, 11), torch.randn(2, 5, 11)
+    lp_t = torch.log_softmax(t, -1)
+    ids = torch.arange(11).expand(2, 5, 11)
+    cfg = DistillationLossConfig(log_prob_min_clamp=None)
+    out = compute_forward_kl_topk(s, lp_t, ids, cfg)
+    dense = torch.nn.functional.kl_div(torch.log_softmax(s, -1), lp_t, log_target=True, reduction="none").sum(-1)
+    assert torch.allclose(out["distillation_losses"], dense, atol=1e-5)
+    assert torch.allclose(out["teacher_mass"], torch.ones(2, 5), atol=1e-5)
+    v, i = torch.topk(lp_t, 3, -1)  # k < V with the tail term: still non-negative and below the dense KL + tail
+    out3 = compute_forward_kl_topk(s, v, i, DistillationLossConfig(log_prob_min_clamp=None, use_tail_term=True))
+    assert (out3["distillation_losses"] > -1e-6).all() and (out3["distillation_losses"] <= dense + 1e-5).all()
+
+
+def test_hidden_path_and_scalar_loss_backward():
+    torch.manual_seed(0)
+    h = torch.randn(7, 16, requires_grad=True)
+    W = torch.randn(32, 16, requires_grad=True)
+    ids = torch.randint(0, 32, (7, 4))
+    lq = student_topk_log_probs(h, W, ids, chunk=3)
+    ref = torch.log_softmax(h @ W.t(), -1).gather(-1, ids)
+    assert torch.allclose(lq, ref, atol=1e-5)
+    lp_t = torch.log_softmax(torch.randn(7, 4), -1)
+    data = {"teacher_logprobs": lp_t.view(1, 7, 4), "teacher_ids": ids.view(1, 7, 4), "response_mask": torch.ones(1, 7)}
+    dc = DistillationConfig(enabled=True)
+    loss, m = distillation_loss({"loss_agg_mode": "token-mean"}, dc, {"topk_log_probs": lq.view(1, 7, 4)}, data)
+    loss.backward()
+    assert h.grad.abs().sum() > 0 and "distillation/loss_max" in m and "distillation/student_mass" in m
+    dc2 = DistillationConfig(enabled=True, distillation_loss=DistillationLossConfig(loss_mode="k3"))
+    lp = torch.randn(1, 7).clamp(-3, 0).requires_grad_()
+    loss2, _ = distillation_loss({"loss_agg_mode": "token-mean"}, dc2, {"log_probs": lp}, {"teacher_logprobs": lp.detach() - 0.1, "response_mask": torch.ones(1, 7)})
+    assert loss2.item() > 0
+
+
+def test_teacher_servers_batch_requests_and_route_by_key():
+    cfg = get_preset("tiny-qwen2")
+    models = []
+    for seed in (1, 2):
+        P = FlatParams(cfg, dtype=torch.float32)
+        P.init_weights(seed=seed, std=0.1)
+        models.append(DecoderModel(cfg, P))
+    a = TeacherModelManager.from_models("math", [models[0]], topk=4)
+    b = TeacherModelManager.from_models("code", [models[1]], topk=4)
+    mgr = AsyncTeacherLLMServerManager(MultiTeacherModelManager({"math": a, "code": b}), response_length=6)
+
+    async def go():
+        return await asyncio.gather(*[mgr.compute_teacher_logprobs(f"r{i}", [5, 6, 7], [8, 9, 10, 11], key)
+                                      for i, key in enumerate(["math", "math", "code", "unknown"])])
+
+    outs = asyncio.run(go())
+    assert outs[0]["teacher_ids"].shape == (6, 4) and (outs[0]["teacher_logprobs"][4:] == 0).all()
+    assert torch.equal(outs[0]["teacher_ids"], outs[1]["teacher_ids"]) and torch.equal(outs[0]["teacher_ids"], outs[3]["teacher_ids"])
+    assert not torch.equal(outs[0]["teacher_logprobs"], outs[2]["teacher_logprobs"])
+    assert list(a.servers.values())[0].num_forwards == 1  # three concurrent requests shared one forward
+    # the record agrees with a dense forward of the teacher
+    lg = models[0].forward_logits(PackedBatch.from_lengths(torch.tensor([5, 6, 7, 8, 9, 10, 11]), [7])).float()
+    v, i = torch.topk(torch.log_softmax(lg, -1)[2:6], 4, -1)
+    assert torch.equal(outs[0]["teacher_ids"][:4], i) and torch.allclose(outs[0]["teacher_logprobs"][:4], v, atol=1e-5)
