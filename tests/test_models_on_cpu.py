@@ -7,13 +7,14 @@ from verl_b200.models.reference import reference_logprobs, reference_values
 
 
 @pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-llama", "tiny-moe"])
-@pytest.mark.parametrize("recompute", ["none", "full"])
+@pytest.mark.parametrize("recompute", ["none", "full", "auto"])
 def test_manual_backward_matches_autograd(name, recompute):
     torch.manual_seed(0)
     cfg = get_preset(name)
     P = FlatParams(cfg, dtype=torch.float32, with_main_grad=True)
     P.init_weights(seed=1, std=0.05)
     model = DecoderModel(cfg, P, recompute=recompute)
+    model.keep_layers_fn = lambda num_tokens: 1  # "auto": the last layer keeps its activations, the others recompute
     lengths = [7, 12, 5]
     T = sum(lengths)
     ids = torch.randint(3, cfg.vocab_size, (T,))

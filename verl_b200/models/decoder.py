@@ -78,7 +78,8 @@ class DecoderModel:
     def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
                  post_layer_backward_hook: Optional[Callable[[int], None]] = None):
-        assert recompute in ("none", "full")
+        assert recompute in ("none", "full", "auto")
+        self.keep_layers_fn: Optional[Callable[[int], int]] = None
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -309,6 +310,25 @@ class DecoderModel:
         return g_x
 
     # ------------------------------------------------------------------------------------ trunk
+    def _first_kept_layer(self, num_tokens: int) -> int:
+        """Layers ``[0, k)`` are recomputed in the backward pass, layers ``[k, L)`` keep their activations.
+        ``recompute``: ``none`` -> k = 0, ``full`` -> k = L, ``auto`` -> as many kept layers as ``keep_layers_fn``
+        (set by the engine from the free device memory and the size of the micro-batch) allows."""
+        L = self.cfg.num_hidden_layers
+        if self.recompute == "full":
+            return L
+        if self.recompute == "auto":
+            keep = self.keep_layers_fn(num_tokens) if self.keep_layers_fn is not None else 0
+            return L - max(0, min(L, int(keep)))
+        return 0
+
+    def activation_bytes_per_layer(self, num_tokens: int) -> int:
+        """Bytes one kept layer pins until its backward: qkv, attention output, gate_up and the two residual streams."""
+        c = self.cfg
+        inter = c.moe_intermediate_size * c.num_experts_per_tok if c.is_moe else c.intermediate_size
+        per_tok = (c.q_size + 2 * c.kv_size) + c.q_size + 2 * inter + 2 * c.hidden_size
+        return int(num_tokens) * per_tok * self.params.flat.element_size() + int(num_tokens) * (c.num_attention_heads + 2) * 4
+
     def _trunk_fwd(self, batch: PackedBatch, save: bool):
         cfg = self.cfg
         self._ensure_rope(batch.max_seqlen + 1)
@@ -317,8 +337,9 @@ class DecoderModel:
         a = F.embedding(batch.input_ids, self.params["embed_tokens.weight"])
         r = None
         saved: list[Any] = []
+        keep_from = self._first_kept_layer(batch.num_tokens) if save else 0
         for i in range(cfg.num_hidden_layers):
-            if save and self.recompute == "full":
+            if save and i < keep_from:  # only the layer input is kept; the layer runs again in the backward pass
                 saved.append((a, r))
                 a, r = self._layer_fwd(i, a, r, batch, None)
             else:
@@ -342,7 +363,7 @@ class DecoderModel:
         g_d = g_x2 = g
         for i in reversed(range(cfg.num_hidden_layers)):
             S = state["layers"][i]
-            if self.recompute == "full":
+            if isinstance(S, tuple):
                 a, r = S
                 S = {}
                 self._layer_fwd(i, a, r, batch, S)

@@ -130,8 +130,12 @@ class NativeEngine(BaseEngine):
             self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
                                      pad_to=self.world, buffer=buf)
             self._load_or_init(seed)
-        recompute = "full" if getattr(ec, "enable_gradient_checkpointing", True) else "none"
+        # gradient checkpointing: "auto" keeps the activations of as many trailing layers as free memory allows and
+        # recomputes the rest (all of them when memory is short, none when everything fits)
+        recompute = "none" if not getattr(ec, "enable_gradient_checkpointing", True) else \
+            str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
+        self.model.keep_layers_fn = self._layers_that_fit
         self.shard_numel = self.params.numel // self.world
         self.shard_lo = self.rank * self.shard_numel
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
@@ -160,6 +164,21 @@ class NativeEngine(BaseEngine):
             self.params.init_weights(seed=seed)
         if self.world > 1:
             dist.broadcast(self.params.flat, src=self._src0, group=self.group)
+
+    def _layers_that_fit(self, num_tokens: int) -> int:
+        """How many layers can keep their activations for a micro-batch of ``num_tokens`` packed tokens: 60 % of what is
+        free now (driver-free plus the allocator's cached-but-unused blocks), the rest stays for the LM-head chunks,
+        attention workspaces and the gradient buffers that appear later in the step."""
+        per_layer = self.model.activation_bytes_per_layer(num_tokens)
+        if self.device.type != "cuda":
+            return self.arch.num_hidden_layers
+        free, _ = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        if self.lazy_grad and getattr(self.params, "main_grad", None) is None:
+            free -= self.params.numel * 4  # the fp32 gradient buffer is allocated on the first backward
+        keep = int(0.6 * max(0, free) // max(1, per_layer))
+        self.last_kept_layers = keep
+        return keep
 
     # ------------------------------------------------------------------------------------ topology
     def get_data_parallel_size(self) -> int:
