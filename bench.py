@@ -233,6 +233,7 @@ def main():
     native.check_status()
     if rank == 0:
         gbs = args.prompts_per_gpu * world
+        rollout_tp = int(getattr(trainer.actor_rollout_wg.worker, "rollout_tp", 1))
         out = {
             "metric": "GRPO step tokens/sec (prompt+response tokens of the step / step time, whole job)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -241,7 +242,8 @@ def main():
             "config": {"model": args.model, "global_batch": gbs * args.n, "prompts": gbs, "samples_per_prompt": args.n,
                        "seq_len": args.prompt_len + args.response_len, "prompt_len": args.prompt_len,
                        "response_len": args.response_len,
-                       "parallelism": f"dp{world} (sharded optimizer, replicated bf16 weights) + in-process rollout dp{world}",
+                       "parallelism": f"dp{world} (sharded optimizer, replicated bf16 weights) + colocated rollout "
+                                      f"tp{rollout_tp} x dp{world // rollout_tp} on in-place weight shards",
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
                        "mean_response_len": last_metrics.get("response_length/mean")},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,

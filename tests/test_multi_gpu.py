@@ -53,6 +53,27 @@ def _worker_body(rank, world, port, queue):
     bar()
     expect = sum((torch.arange(4096, device=dev) % 7 + r).float() for r in range(world))
     res["allreduce_err"] = (outt.float() - expect).abs().max().item()
+    # ---- row-parallel GEMM with the all-reduce inside the epilogue: three calls in a row (epochs, buffer halves)
+    from verl_b200.parallel.symmetric import FusedRowParallelLinear
+
+    fused = FusedRowParallelLinear(max_rows=3000, n=1024, device=dev)
+    errs, same = [], []
+    for call, M in enumerate((640, 3000, 77)):
+        g = torch.Generator(device="cpu").manual_seed(50 + call)
+        a_full = torch.randn(M, 1024, generator=g).bfloat16()
+        b_full = (torch.randn(1024, 1024, generator=g) * 0.05).bfloat16()
+        bias = torch.randn(1024, generator=g).bfloat16()
+        ks = slice(rank * 512, (rank + 1) * 512)
+        a, b = a_full[:, ks].contiguous().to(dev), b_full.to(dev)[:, ks]  # b: strided K-slice view of the full weight
+        y = fused(a, b, bias.to(dev))
+        ref = sum((a_full[:, r * 512:(r + 1) * 512].float() @ b_full[:, r * 512:(r + 1) * 512].float().t()) for r in range(world)) + bias.float()
+        errs.append(((y.float().cpu() - ref).norm() / ref.norm()).item())
+        other = y.clone()
+        dist.broadcast(other, src=0)
+        same.append(bool(torch.equal(other, y)))
+    res["gemm_ar_err"] = max(errs)
+    res["gemm_ar_identical"] = all(same)
+    res["gemm_status"] = int(ops.gemm_status())
     # ---- engines: fused peer-memory optimizer vs NCCL
     arch = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, eos_token_id=2, pad_token_id=0)
@@ -113,6 +134,7 @@ def test_two_rank_fused_optimizer_and_peer_collectives():
     for r in (0, 1):
         res = results[r]
         assert res["allreduce_err"] == 0.0
+        assert res["gemm_ar_err"] < 1e-2 and res["gemm_ar_identical"] and res["gemm_status"] == 0, res
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
         assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res

@@ -74,12 +74,28 @@ class _Anchor(torch.autograd.Function):
         return (torch.zeros((), device=dev), None, None) + tuple(None for _ in grads)
 
 
+class TensorParallelShard:
+    """Inference-time tensor parallelism over *views* of the replicated weights: rank ``r`` of ``size`` uses its heads'
+    rows of the fused QKV weight and its rows of gate/up (column-parallel, three plus two narrow GEMMs writing into one
+    activation buffer) and the matching K-slices of ``o_proj`` / ``down_proj`` (row-parallel). Nothing is copied: a
+    weight update of the full replica is visible to the shard at once. ``row_linear(a, w_kslice, bias)`` must return the
+    sum over ranks (on GPUs: the GEMM whose epilogue all-reduces over peer memory)."""
+
+    def __init__(self, rank: int, size: int, row_linear: Callable):
+        self.rank, self.size, self.row_linear = int(rank), int(size), row_linear
+
+    def rows(self, total: int) -> slice:
+        per = total // self.size
+        return slice(self.rank * per, (self.rank + 1) * per)
+
+
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
                  post_layer_backward_hook: Optional[Callable[[int], None]] = None):
         assert recompute in ("none", "full", "auto")
         self.keep_layers_fn: Optional[Callable[[int], int]] = None
+        self.tp: Optional[TensorParallelShard] = None  # set by the rollout engine; forward-only
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -115,7 +131,12 @@ class DecoderModel:
         cfg = self.cfg
         T = h1.shape[0]
         nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
-        qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+        if self.tp is not None:
+            assert S is None, "tensor-parallel shards are forward-only"
+            qkv = self.qkv_tp(W, h1)
+            nh, nkv, Q, KV = nh // self.tp.size, nkv // self.tp.size, Q // self.tp.size, KV // self.tp.size
+        else:
+            qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
         q = qkv[:, :Q].view(T, nh, hd)
         k = qkv[:, Q : Q + KV].view(T, nkv, hd)
         v = qkv[:, Q + KV :].view(T, nkv, hd)
@@ -137,7 +158,33 @@ class DecoderModel:
         attn2 = attn.reshape(T, Q)
         if S is not None:
             S.update(qkv=qkv, attn=attn2, lse=lse)
+        if self.tp is not None:
+            return self.tp.row_linear(attn2, W["self_attn.o_proj.weight"][:, self.tp.rows(cfg.q_size)], None)
         return F.gemm(attn2, W["self_attn.o_proj.weight"])
+
+    def qkv_tp(self, W, h1: torch.Tensor) -> torch.Tensor:
+        """[T, (Q + 2 KV) / size]: this rank's q | k | v columns."""
+        cfg, tp = self.cfg, self.tp
+        Q, KV = cfg.q_size, cfg.kv_size
+        Ql, KVl = Q // tp.size, KV // tp.size
+        w, b = W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias")
+        out = torch.empty(h1.shape[0], Ql + 2 * KVl, dtype=h1.dtype, device=h1.device)
+        col = 0
+        for base, width in ((0, Ql), (Q, KVl), (Q + KV, KVl)):
+            rows = slice(base + tp.rank * width, base + (tp.rank + 1) * width)
+            F.gemm(h1, w[rows], b[rows] if b is not None else None, out=out[:, col : col + width])
+            col += width
+        return out
+
+    def mlp_tp(self, W, h2: torch.Tensor) -> torch.Tensor:
+        cfg, tp = self.cfg, self.tp
+        I = cfg.intermediate_size
+        Il = I // tp.size
+        w = W["mlp.gate_up_proj.weight"]
+        gu = torch.empty(h2.shape[0], 2 * Il, dtype=h2.dtype, device=h2.device)
+        F.gemm(h2, w[tp.rank * Il : (tp.rank + 1) * Il], out=gu[:, :Il])
+        F.gemm(h2, w[I + tp.rank * Il : I + (tp.rank + 1) * Il], out=gu[:, Il:])
+        return tp.row_linear(F.swiglu(gu), W["mlp.down_proj.weight"][:, tp.rows(I)], None)
 
     def _attn_bwd(self, W, g_o, h1, batch: PackedBatch, S: dict):
         cfg = self.cfg
@@ -183,6 +230,9 @@ class DecoderModel:
     def _mlp_fwd(self, W, h2, S: Optional[dict]):
         if self.cfg.is_moe:
             return self._moe_fwd(W, h2, S)
+        if self.tp is not None:
+            assert S is None, "tensor-parallel shards are forward-only"
+            return self.mlp_tp(W, h2)
         gu = F.gemm(h2, W["mlp.gate_up_proj.weight"])
         if S is not None:
             S["gu"] = gu

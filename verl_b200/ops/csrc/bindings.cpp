@@ -431,6 +431,34 @@ void allreduce_peer_(const Tensor& buf_ptrs, Tensor out, int64_t rank) {
            "vb_allreduce_peer");
 }
 
+// Row-parallel linear + all-reduce in one kernel: out[M,N] = sum over ranks of a_r[M,K_r] @ b_r[N,K_r]^T (+bias).
+// part_ptrs / flag_ptrs: CPU int64 tensors [world] with every rank's partial buffer and flag array addresses.
+Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, const Tensor& part_ptrs, const Tensor& flag_ptrs,
+                      Tensor epoch, int64_t buf_elems, int64_t rank, double limit_s, const OptTensor& out) {
+  CHECK_BF16(a);
+  CHECK_BF16(b);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1),
+              "gemm_allreduce: K-major 2-D operands with equal K");
+  TORCH_CHECK(epoch.scalar_type() == at::kInt && epoch.numel() >= 2 && epoch.is_cuda(), "gemm_allreduce: int32 cuda epoch[2]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  Tensor d = out.has_value() ? *out : at::empty({M, N}, a.options());
+  TORCH_CHECK(d.scalar_type() == at::kBFloat16 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_allreduce: bad out");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm_allreduce: bad bias");
+    bias_ptr = bias->data_ptr();
+  }
+  if (M == 0) return d;
+  count(1);
+  const int rc = vb_gemm_bf16_allreduce(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
+                                        b.stride(0), d.stride(0), uptr(part_ptrs), uptr(flag_ptrs),
+                                        reinterpret_cast<unsigned int*>(epoch.data_ptr<int>()), buf_elems, (int)part_ptrs.numel(),
+                                        (int)rank, limit_s, cur_stream());
+  TORCH_CHECK(rc == 0, "vb_gemm_bf16_allreduce failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+  return d;
+}
+
 int64_t comm_status() { return vb_comm_status(); }
 
 }  // namespace
@@ -440,6 +468,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("rs_sumsq_", &rs_sumsq_);
   m.def("adamw_allgather_", &adamw_allgather_);
   m.def("allreduce_peer_", &allreduce_peer_);
+  m.def("gemm_allreduce", &gemm_allreduce);
   m.def("comm_status", &comm_status);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);

@@ -34,7 +34,12 @@ constexpr int GEMM_THREADS = 192;
 //               sum x*exp) of x = acc * inv_temp, plus the label logit; the [T, V] logits never exist.
 //  EPI_DLOGITS  LM head backward: D = d loss / d acc for the recomputed tile, written as bf16:
 //               inv_temp * ( g_lp * (onehot - p) - g_ent * p * (x - E[x]) ),  p = exp(x - lse).
-enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2 };
+//  EPI_ALLREDUCE  row-parallel (K-sharded) linear of a tensor-parallel group: every rank computes a partial tile,
+//               publishes it as bf16 in its own peer-visible buffer, raises a per-(tile, warp) flag, then sums
+//               the partials of all ranks in rank order (bitwise identical on every rank) and stores D.
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2, EPI_ALLREDUCE = 3 };
+
+constexpr int AR_MAX_RANKS = 8;
 
 struct GemmParams {
   int M, N, K;
@@ -55,7 +60,28 @@ struct GemmParams {
   const float* ex;          // EPI_DLOGITS: [M]  E[x] = lse - entropy (may be null when g_ent is null)
   const float* g_lp;        // EPI_DLOGITS: [M]
   const float* g_ent;       // EPI_DLOGITS: [M] or null
+  // EPI_ALLREDUCE
+  int ar_world, ar_rank;
+  unsigned long long ar_part[AR_MAX_RANKS];  // per rank: bf16 [2][ar_buf_elems] (two halves, selected by epoch parity)
+  unsigned long long ar_flag[AR_MAX_RANKS];  // per rank: uint32 [num_tiles * 4]
+  long long ar_buf_elems;
+  unsigned int* ar_epoch;   // this rank's [2]: {calls completed, CTAs finished in the running call}
+  unsigned long long ar_limit_ns;  // how long a slab waits for its peers before giving up
 };
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ar_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ int g_gemm_status[4];
 
@@ -117,6 +143,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  unsigned int ar_epoch_now = 0;
+  if constexpr (EPI == EPI_ALLREDUCE) ar_epoch_now = *reinterpret_cast<volatile unsigned int*>(p.ar_epoch) + 1u;
 
   auto k_range = [&](int t, int& kb0, int& kb1) {
     const int sp = t / num_mn;
@@ -321,6 +349,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               }
             }
           }
+        } else if constexpr (EPI == EPI_ALLREDUCE) {
+          // pass A: this rank's partial, rounded to bf16, into its own peer-visible buffer
+          if (row_ok) {
+            __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(p.ar_part[p.ar_rank]) +
+                                  static_cast<long long>(ar_epoch_now & 1u) * p.ar_buf_elems +
+                                  static_cast<long long>(row) * p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (j < ncols) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                *reinterpret_cast<uint4*>(mine + j) = v;
+              }
+            }
+          }
         } else if (row_ok) {
           if (p.bias != nullptr) {
 #pragma unroll
@@ -370,10 +416,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);  // the accumulator is free: the next tile's MMAs may start
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
+      }
+      if constexpr (EPI == EPI_ALLREDUCE) {
+        // publish: all 32 rows of this warp's slab are written -> raise flag (tile, q) with release semantics
+        __threadfence_system();
+        __syncwarp();
+        const int slot = (t % num_mn) * 4 + q;
+        if (lane == 0) st_release_sys_u32(reinterpret_cast<unsigned int*>(p.ar_flag[p.ar_rank]) + slot, ar_epoch_now);
+        // pass B: wait (bounded) for the same slab of every peer, then sum all partials in rank order
+        bool peers_ok = true;
+        const unsigned long long t_start = ar_now_ns();
+        for (int r = 0; r < p.ar_world; ++r) {
+          if (r == p.ar_rank) continue;
+          const unsigned int* f = reinterpret_cast<const unsigned int*>(p.ar_flag[r]) + slot;
+          while (static_cast<int>(ld_acquire_sys_u32(f) - ar_epoch_now) < 0) {
+            if (ar_now_ns() - t_start > p.ar_limit_ns) {  // the peer never arrived
+              peers_ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!peers_ok) break;
+        }
+        peers_ok = __all_sync(0xffffffffu, peers_ok);
+        if (!peers_ok) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_EPILOGUE + 10);
+        } else {
+          // lanes sweep the columns of one (BN = 256) or two (BN = 128) rows at a time: 16-byte pieces of a row are
+          // contiguous across lanes, so every peer read is a full 512-byte (256-byte) burst over NVLink
+          constexpr int LPR = BN / 8;   // lanes per row
+          constexpr int RPI = 32 / LPR;  // rows per iteration
+          const long long half = static_cast<long long>(ar_epoch_now & 1u) * p.ar_buf_elems;
+          const int col = n0 + (lane % LPR) * 8;
+#pragma unroll 1
+          for (int rr = 0; rr < 32; rr += RPI) {
+            const int orow = m0 + q * 32 + rr + lane / LPR;
+            if (orow >= p.M || col >= p.N) continue;
+            const long long off = half + static_cast<long long>(orow) * p.N + col;
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < p.ar_world; ++r) {
+              const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.ar_part[r]) + off);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f2 = __bfloat1622float2(h[j]);
+                acc8[2 * j] += f2.x;
+                acc8[2 * j + 1] += f2.y;
+              }
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc8[0], acc8[1]);
+            o.y = pack_bf16x2(acc8[2], acc8[3]);
+            o.z = pack_bf16x2(acc8[4], acc8[5]);
+            o.w = pack_bf16x2(acc8[6], acc8[7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow) * p.ldd + col) = o;
+          }
+        }
       }
     }
   }
@@ -384,6 +490,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+  if constexpr (EPI == EPI_ALLREDUCE) {
+    // the last CTA to finish closes the call: every CTA of this launch has read the epoch by now
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned int done = atomicAdd(p.ar_epoch + 1, 1u);
+      if (done == gridDim.x - 1) {
+        p.ar_epoch[1] = 0;
+        __threadfence();
+        atomicAdd(p.ar_epoch, 1u);
+      }
+    }
   }
 }
 
@@ -523,6 +641,46 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
         splitk_ws, reinterpret_cast<const __nv_bfloat16*>(bias), D, ldd, M, N, p.k_splits, out_f32, accumulate);
     e = cudaGetLastError();
   }
+  return static_cast<int>(e);
+}
+
+// Row-parallel linear of a tensor-parallel group with the all-reduce done inside the GEMM epilogue over peer memory:
+// D[M,N] = sum_r A_r[M,K_r] B_r[N,K_r]^T (+bias), identical bits on every rank. A and B are K-major.
+//  part_ptrs[r]  rank r's partial buffer (bf16, 2 * buf_elems elements, peer-mapped); buf_elems >= M*N
+//  flag_ptrs[r]  rank r's flags (uint32, >= 4 * ceil(M/128) * ceil(N/BN) entries, zero before the first call)
+//  epoch         this rank's two-word call counter (zero before the first call); all ranks must issue the same
+//                sequence of calls on these buffers. Waits on peers give up after limit_s seconds and report through
+//                vb_gemm_status() (code 13); the output is then undefined but the kernel returns.
+extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
+                                      const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
+                                      int world, int rank, double limit_s, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
+  if (world < 1 || world > AR_MAX_RANKS || rank < 0 || rank >= world) return -4;
+  if (static_cast<long long>(M) * N > buf_elems) return -5;
+  const int sms = num_sms();
+  // small M (decode): narrow tiles give more CTAs to hide the peer latency; large M (prefill): wide tiles
+  const bool wide = N > 128 && M > 1024;
+  const int BN = wide ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.status = status_ptr();
+  p.k_splits = 1;
+  p.ar_world = world; p.ar_rank = rank; p.ar_buf_elems = buf_elems; p.ar_epoch = epoch;
+  p.ar_limit_ns = static_cast<unsigned long long>((limit_s > 0.0 ? limit_s : 2.0) * 1e9);
+  for (int r = 0; r < world; ++r) {
+    p.ar_part[r] = part_ptrs[r];
+    p.ar_flag[r] = flag_ptrs[r];
+  }
+  cudaError_t e;
+  if (wide) e = launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
+  else e = launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   return static_cast<int>(e);
 }
 

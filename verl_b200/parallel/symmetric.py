@@ -71,3 +71,31 @@ class PeerBarrier:
 
         self.epoch += 1
         native.ops().peer_barrier(self.buf.ptrs, self.rank, self.epoch, float(limit_s))
+
+
+class FusedRowParallelLinear:
+    """Row-parallel (K-sharded) linear whose all-reduce runs inside the GEMM epilogue over peer memory.
+
+    Owns the peer-visible partial buffer (two halves, alternating per call), the per-tile flags and the call counter of
+    one tensor-parallel group. Every rank of the group must issue the same sequence of calls; the result is bitwise
+    identical on all ranks. ``max_rows`` bounds ``M`` of a call (rows of the activation)."""
+
+    def __init__(self, max_rows: int, n: int, device, group=None, limit_s: float = 20.0):
+        self.limit_s = float(limit_s)
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.n, self.max_rows = int(n), int(max_rows)
+        self.buf_elems = self.max_rows * self.n
+        self.part = SymmetricBuffer.allocate(2 * self.buf_elems, torch.bfloat16, device, group, zero=False)
+        tiles = ((self.max_rows + 127) // 128) * ((self.n + 127) // 128)
+        self.flags = SymmetricBuffer.allocate(4 * tiles, torch.int32, device, group, zero=True)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # flags are zero everywhere before anyone publishes epoch 1
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+        from ..ops import native
+
+        assert a.shape[0] <= self.max_rows and b.shape[0] == self.n
+        return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out)

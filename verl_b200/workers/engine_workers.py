@@ -261,11 +261,24 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 src = self.rollout_weights
             arch = mc.arch
             max_len = rc.max_model_len or (rc.prompt_length + rc.response_length)
-            self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs,
+            # rollout tensor parallelism: consecutive ranks form a group that serves the union of its members' prompts;
+            # every member shards the replicated weights in place, so the train -> rollout reshard moves no bytes
+            from ..utils.distributed import get_data_parallel_group
+
+            pool = get_data_parallel_group()  # the ranks that run this kind of worker (all ranks unless the job is split)
+            pool_ranks = dist.get_process_group_ranks(pool if pool is not None else dist.group.WORLD) if ws > 1 else [0]
+            n_pool, me = len(pool_ranks), (pool_ranks.index(dist.get_rank()) if ws > 1 else 0)
+            tp = int(rc.tensor_model_parallel_size or 1)
+            tp = tp if (n_pool > 1 and tp > 1 and n_pool % tp == 0 and not arch.is_moe and arch.num_key_value_heads % tp == 0) else 1
+            self.rollout_tp, self.rollout_tp_group = tp, None
+            if tp > 1:  # only the members take part in creating their group
+                g0 = me // tp * tp
+                self.rollout_tp_group = dist.new_group(pool_ranks[g0 : g0 + tp], use_local_synchronization=True)
+            self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs * tp, tp_group=self.rollout_tp_group,
                                          max_num_batched_tokens=rc.max_num_batched_tokens, max_model_len=max_len + 1,
                                          block_size=rc.block_size, gpu_memory_utilization=rc.gpu_memory_utilization,
                                          use_cuda_graph=not rc.enforce_eager, sync_interval=rc.sync_interval,
-                                         seed=1234 + self.rank, num_blocks=rc.engine_kwargs.get("num_blocks"),
+                                         seed=1234 + (me // tp if tp > 1 else self.rank), num_blocks=rc.engine_kwargs.get("num_blocks"),
                                          valid_vocab_size=rc.engine_kwargs.get("valid_vocab_size", 0))
             if rc.free_cache_engine:
                 self.rollout.release_kv_cache()
@@ -293,7 +306,15 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                             logprobs=True)
         ids_cpu, mask_cpu = ids.cpu(), mask.cpu()
         plist = [ids_cpu[i][mask_cpu[i]].tolist() for i in range(ids.shape[0])]
-        outs = self.rollout.generate(plist, sp)
+        if getattr(self, "rollout_tp", 1) > 1:
+            # the group generates the union of its members' prompts in lockstep; each member keeps its own slice
+            parts: list = [None] * self.rollout_tp
+            dist.all_gather_object(parts, plist, group=self.rollout_tp_group)
+            me = dist.get_rank(self.rollout_tp_group)
+            lo = sum(len(x) for x in parts[:me])
+            outs = self.rollout.generate([p for part in parts for p in part], sp)[lo : lo + len(plist)]
+        else:
+            outs = self.rollout.generate(plist, sp)
         R = sp.max_tokens
         pad = int(meta.get("pad_token_id", self.rollout.cfg.pad_token_id or 0))
         b = len(outs)

@@ -34,9 +34,10 @@ from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
 import torch
+import torch.distributed as dist
 
 from ....models.config import ModelConfig
-from ....models.decoder import DecoderModel, PackedBatch
+from ....models.decoder import DecoderModel, PackedBatch, TensorParallelShard
 from ....models.weights import FlatParams
 from ....ops import functional as F
 
@@ -81,8 +82,17 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, params: FlatParams, *, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
-                 valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0):
+                 valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0,
+                 tp_group=None):
+        """``tp_group``: process group of the ranks that serve the same requests tensor-parallel (each holds the
+        full replicated weights and uses its shard of them in place; see ``TensorParallelShard``). All ranks of the
+        group must be fed the same requests in the same order."""
         self.cfg = cfg
+        self.tp_group = tp_group
+        self.tp_size = dist.get_world_size(tp_group) if tp_group is not None else 1
+        self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
+        assert cfg.num_key_value_heads % self.tp_size == 0 and (cfg.is_moe or cfg.intermediate_size % (8 * self.tp_size) == 0), \
+            "tensor-parallel size must divide the KV heads and the MLP width"
         self.params = params
         self.device = params.flat.device
         self.is_cuda = self.device.type == "cuda"
@@ -99,6 +109,9 @@ class RolloutEngine:
         self._num_blocks_req = num_blocks
         self.model = DecoderModel(cfg, params, max_positions=self.max_model_len + 1)
         self.model.kv_hook = self._prefill_kv_hook
+        if self.tp_size > 1:
+            assert not cfg.is_moe, "tensor-parallel rollout of MoE models is not implemented (use expert parallelism)"
+            self.model.tp = TensorParallelShard(self.tp_rank, self.tp_size, self._make_row_linear())
         self.kv: Optional[torch.Tensor] = None
         self.free_blocks: list[int] = []
         self._graph = None
@@ -112,10 +125,29 @@ class RolloutEngine:
         self._alloc_state()
         self.resume_kv_cache()
 
+    def _make_row_linear(self):
+        """Row-parallel linear summed over the tensor-parallel group. GPUs: one kernel (GEMM with the all-reduce in its
+        epilogue over peer memory). CPU: GEMM followed by a gloo all-reduce (used by the multi-process tests)."""
+        if self.is_cuda:
+            from ....parallel.symmetric import FusedRowParallelLinear
+
+            fused = FusedRowParallelLinear(max(self.max_batched, self.S), self.cfg.hidden_size, self.device, self.tp_group)
+            self._fused_row = fused
+            return lambda a, w, bias: fused(a, w, bias)
+
+        def row_linear(a, w, bias):
+            y = a.float() @ w.float().t()
+            dist.all_reduce(y, group=self.tp_group)
+            if bias is not None:
+                y = y + bias.float()
+            return y.to(a.dtype)
+
+        return row_linear
+
     # ------------------------------------------------------------------------------------ memory
     def kv_bytes_per_block(self) -> int:
         c = self.cfg
-        return c.num_hidden_layers * 2 * self.bs * c.kv_size * self.params.flat.element_size()
+        return c.num_hidden_layers * 2 * self.bs * (c.kv_size // self.tp_size) * self.params.flat.element_size()
 
     def resume_kv_cache(self) -> None:
         if self.kv is not None:
@@ -131,8 +163,12 @@ class RolloutEngine:
             else:
                 n = self.S * self.max_blocks_per_seq
             n = min(n, self.S * self.max_blocks_per_seq + 1)
+        if self.tp_size > 1:  # identical admission decisions on every rank of the group need identical pool sizes
+            t = torch.tensor([int(n)], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp_group)
+            n = int(t.item())
         self.num_blocks = int(n)
-        self.kv = torch.zeros(c.num_hidden_layers, 2, self.num_blocks, self.bs, c.num_key_value_heads, c.head_dim,
+        self.kv = torch.zeros(c.num_hidden_layers, 2, self.num_blocks, self.bs, c.num_key_value_heads // self.tp_size, c.head_dim,
                               dtype=self.params.flat.dtype, device=self.device)
         self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
         self._graph = None  # cache addresses changed
@@ -290,14 +326,19 @@ class RolloutEngine:
         blk = torch.gather(self.block_table, 1, (pos_l // self.bs).unsqueeze(1)).squeeze(1).long()
         slot_map = torch.where(act, blk * self.bs + pos_l % self.bs, torch.full_like(pos_l, -1))
         ctx_eff = self.ctx * acti
-        nh, nkv, hd, Q, KV = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.q_size, cfg.kv_size
+        tp = self.model.tp
+        w_ = self.tp_size
+        nh, nkv, hd, Q, KV = cfg.num_attention_heads // w_, cfg.num_key_value_heads // w_, cfg.head_dim, cfg.q_size // w_, cfg.kv_size // w_
         a = F.embedding(self.tok, P["embed_tokens.weight"])
         r = None
         cos, sin = self.model._cos, self.model._sin
         for i in range(cfg.num_hidden_layers):
             W = P.layer(i)
             h1, x, _ = F.rms_norm(a, W["input_layernorm.weight"], cfg.rms_norm_eps, residual=r)
-            qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+            if tp is not None:
+                qkv = self.model.qkv_tp(W, h1)
+            else:
+                qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
             q = qkv[:, :Q].view(S, nh, hd)
             k = qkv[:, Q : Q + KV].view(S, nkv, hd)
             v = qkv[:, Q + KV :].view(S, nkv, hd)
@@ -310,7 +351,10 @@ class RolloutEngine:
             F.apply_rope_(k, self.pos, cos, sin)
             F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
             attn = F.paged_decode_attention(q, self.kv[i, 0], self.kv[i, 1], self.block_table, ctx_eff)
-            o = F.gemm(attn.reshape(S, Q), W["self_attn.o_proj.weight"])
+            if tp is not None:
+                o = tp.row_linear(attn.reshape(S, Q), W["self_attn.o_proj.weight"][:, tp.rows(cfg.q_size)], None)
+            else:
+                o = F.gemm(attn.reshape(S, Q), W["self_attn.o_proj.weight"])
             h2, x2, _ = F.rms_norm(o, W["post_attention_layernorm.weight"], cfg.rms_norm_eps, residual=x)
             a = self.model._mlp_fwd(W, h2, None)
             r = x2
