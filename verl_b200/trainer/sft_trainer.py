@@ -97,7 +97,9 @@ class SFTTrainer:
             return None
         loss = torch.stack(losses).mean()
         if self.world > 1:
-            dist.all_reduce(loss)
+            from ..utils.distributed import get_data_parallel_group
+
+            dist.all_reduce(loss, group=get_data_parallel_group())
             loss /= self.world
         return float(loss)
 

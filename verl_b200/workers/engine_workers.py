@@ -87,8 +87,11 @@ class TrainingWorker(Worker, DistProfilerExtension):
         if "loss" in out:
             loss = out["loss"].detach().float().clone()
             if dist.is_initialized() and dist.get_world_size() > 1:
-                dist.all_reduce(loss)
-                loss /= dist.get_world_size()
+                from ..utils.distributed import get_data_parallel_group
+
+                g = get_data_parallel_group()
+                dist.all_reduce(loss, group=g)
+                loss /= dist.get_world_size(g)
             metrics["loss"] = float(loss)
         if seconds > 0 and tokens > 0:
             est, promised = self.flops_counter.estimate_flops([tokens], seconds)
