@@ -162,6 +162,40 @@ def test_paged_decode_attention_and_kv_append(ops):
     assert torch.equal(flat[900], k[1]) and torch.equal(flat[0], k[6]) and flat[1].abs().sum() == 0
 
 
+def _attn_reference(q, k, v, lens, scale):
+    """fp32 causal GQA attention per sequence with autograd."""
+    outs, off = [], 0
+    G = q.shape[1] // k.shape[1]
+    for n in lens:
+        qs, ks, vs = (t[off:off + n].float() for t in (q, k, v))
+        ks, vs = ks.repeat_interleave(G, 1), vs.repeat_interleave(G, 1)
+        s = torch.einsum("qhd,khd->hqk", qs, ks) * scale
+        s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=q.device), 1), float("-inf"))
+        outs.append(torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vs))
+        off += n
+    return torch.cat(outs, 0)
+
+
+@pytest.mark.parametrize("lens,nh,nkv", [([300, 129, 64, 1], 4, 2), ([1000], 7, 1), ([130, 257], 2, 2)])
+def test_attention_forward_and_backward_tcgen05(ops, lens, nh, nkv):
+    torch.manual_seed(0)
+    T, hd = sum(lens), 128
+    scale = 1.0 / math.sqrt(hd)
+    q = (torch.randn(T, nh, hd, device=DEV) * 0.7).bfloat16()
+    k = (torch.randn(T, nkv, hd, device=DEV) * 0.7).bfloat16()
+    v = torch.randn(T, nkv, hd, device=DEV).bfloat16()
+    do = torch.randn(T, nh, hd, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    out, lse = ops.attn_fwd(q, k, v, cu, scale)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = _attn_reference(qr, kr, vr, lens, scale)
+    assert rel(out, ref) < 2e-2
+    dq_r, dk_r, dv_r = torch.autograd.grad(ref, (qr, kr, vr), do.float())
+    dq, dk, dv = ops.attn_bwd(do, q, k, v, out, lse, cu, max(lens), scale)
+    assert ops.gemm_status() == 0
+    assert rel(dv, dv_r) < 3e-2 and rel(dk, dk_r) < 3e-2 and rel(dq, dq_r) < 3e-2, (rel(dq, dq_r), rel(dk, dk_r), rel(dv, dv_r))
+
+
 def test_sampler_distribution_and_logprob(ops):
     from verl_b200.ops import functional as F
 

@@ -69,7 +69,8 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
 
 int64_t gemm_status() {
   const int a = vb_gemm_status();
-  const int b = vb_attn_status();
+  int b = vb_attn_status();
+  if (b == 0) b = vb_attn_bwd_status();
   const int c = vb_pd_status();
   return a != 0 ? a : (b != 0 ? 100 + b : (c != 0 ? 200 + c : 0));
 }
@@ -94,6 +95,38 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
                              (float)scale, out.data_ptr(), out.stride(0), lse.data_ptr<float>(), cur_stream());
   CHECK_RC(rc, "vb_attn_fwd");
   return {out, lse};
+}
+
+// (dq, dk, dv) of causal varlen GQA attention; q/out/dout: [T, nh, hd] views, k/v: [T, nkv, hd] views, lse [nh, T].
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& out, const Tensor& lse, const Tensor& cu_seqlens, int64_t max_seqlen,
+                                            double scale) {
+  CHECK_BF16(q);
+  CHECK_BF16(k);
+  CHECK_BF16(v);
+  CHECK_BF16(out);
+  CHECK_BF16(dout);
+  CHECK_F32(lse);
+  auto packed = [](const Tensor& t) { return t.dim() == 3 && t.stride(2) == 1 && t.stride(1) == t.size(2); };
+  TORCH_CHECK(packed(q) && packed(k) && packed(v) && packed(out) && packed(dout), "attn_bwd: [T, heads, hd] views with packed heads");
+  TORCH_CHECK(cu_seqlens.is_cuda() && cu_seqlens.scalar_type() == at::kInt && cu_seqlens.is_contiguous() && lse.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t T = q.size(0), nh = q.size(1), hd = q.size(2), nkv = k.size(1);
+  Tensor dq = at::empty({T, nh, hd}, q.options());
+  Tensor dk = at::empty({T, nkv, hd}, q.options());
+  Tensor dv = at::empty({T, nkv, hd}, q.options());
+  if (T == 0) return {dq, dk, dv};
+  auto fo = q.options().dtype(at::kFloat);
+  Tensor delta = at::empty({nh, T}, fo);
+  Tensor dq32 = at::empty({T, nh * hd}, fo);
+  count(4);
+  const int rc = vb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), q.stride(0), k.stride(0),
+                             v.stride(0), out.stride(0), dout.stride(0), lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
+                             (int)cu_seqlens.numel() - 1, (int)T, (int)nh, (int)nkv, (int)hd, (float)scale, dq.data_ptr(),
+                             dk.data_ptr(), dv.data_ptr(), dq.stride(0), dk.stride(0), dv.stride(0), delta.data_ptr<float>(),
+                             dq32.data_ptr<float>(), cur_stream());
+  CHECK_RC(rc, "vb_attn_bwd");
+  return {dq, dk, dv};
 }
 
 // (logprob, entropy, lse) of labels under softmax(hidden @ weight^T / temperature); [T,V] logits never exist.
@@ -475,6 +508,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("launch_count", &launch_count);
   m.def("add_launches", &add_launches);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
   m.def("lmhead_fwd", &lmhead_fwd);
   m.def("lmhead_dlogits", &lmhead_dlogits);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

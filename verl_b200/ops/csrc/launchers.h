@@ -55,6 +55,12 @@ int vb_attn_fwd(const void* q, const void* k, const void* v, long long ldq, long
                 const int* cu_seqlens, int num_seqs, int total_tokens, int nh, int nkv, int hd, float scale, void* out,
                 long long ldo, float* lse, cudaStream_t stream);
 int vb_attn_status();
+// attention_bwd_tcgen05.cu
+int vb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, long long ldq, long long ldk,
+                long long ldv, long long ldo, long long lddo, const float* lse, const int* cu_seqlens, int num_seqs,
+                int total_tokens, int nh, int nkv, int hd, float scale, void* dq, void* dk, void* dv, long long lddq,
+                long long lddk, long long lddv, float* delta_ws, float* dq32_ws, cudaStream_t stream);
+int vb_attn_bwd_status();
 // paged_decode_tma.cu
 int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, const void* vc, long long num_slots,
                        const int* block_table, int max_blocks, const int* ctx_len, void* out, long long ldo, int B, int nh,

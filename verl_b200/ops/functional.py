@@ -303,8 +303,8 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, scale: Optional[float
 def attention_varlen_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen: int, scale: Optional[float] = None):
     """Returns (dq, dk, dv)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if q.is_cuda and _ATTN_IMPL["bwd"] is not None and lse is not None:
-        return _ATTN_IMPL["bwd"](dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale)
+    if q.is_cuda and _ATTN_IMPL["bwd"] is not None and lse is not None and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
+        return _ATTN_IMPL["bwd"](dout, q, k, v, out, lse, cu_seqlens.to(q.device), max_seqlen, scale)
     with torch.enable_grad():
         q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
         o = _sdpa_varlen(q_, k_, v_, cu_seqlens, scale)
@@ -425,3 +425,10 @@ if torch.cuda.is_available():  # the tcgen05 forward kernel is the default atten
 
 def _native_attn_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale):
     return _ops().attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_seqlens.to(torch.int32), int(max_seqlen), float(scale))
+
+
+# the tcgen05 backward kernel (head_dim 128) is opt-in: VERL_B200_NATIVE_ATTN_BWD=1 or enable_native_attention()
+import os as _os
+
+if torch.cuda.is_available() and _os.environ.get("VERL_B200_NATIVE_ATTN_BWD", "0") == "1":
+    _ATTN_IMPL["bwd"] = _native_attn_bwd
