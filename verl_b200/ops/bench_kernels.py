@@ -1,0 +1,166 @@
+"""Micro-benchmarks of the native kernels with roofline fractions.
+
+    python -m verl_b200.ops.bench_kernels                 # all kernels, default (training-sized) shapes
+    python -m verl_b200.ops.bench_kernels --only gemm,attn_fwd --small   # a few hundred MB, for profiler captures
+
+Every case is timed with CUDA events after warm-up, with an L2 flush (a 256 MB write) between iterations, and printed
+as one JSON line: achieved TFLOP/s or GB/s and the fraction of the measured peak (``MEASURED_PEAKS.json`` at the
+repository root when present, else the stated fallback).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import native
+
+
+def _peaks() -> dict:
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            out = {"hbm_gbs": float(d.get("hbm_gbs", out["hbm_gbs"])), "bf16_tflops": float(d.get("bf16_tflops", out["bf16_tflops"])),
+                   "source": "measured"}
+        except Exception:
+            pass
+    return out
+
+
+class Timer:
+    def __init__(self, dev, iters: int, warmup: int):
+        self.dev, self.iters, self.warmup = dev, iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / self.iters
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    only = set(filter(None, a.only.split(",")))
+    want = lambda name: not only or name in only
+    dev = torch.device("cuda", 0)
+    ops = native.ops()
+    from . import functional as F
+
+    pk = _peaks()
+    T = Timer(dev, a.iters, a.warmup)
+    tag = "of measured" if pk["source"] == "measured" else "of fallback"
+
+    def report(name, shape, ms, flops=None, bytes_=None):
+        rec = {"kernel": name, "shape": shape, "ms": round(ms, 4)}
+        if flops is not None:
+            tf = flops / ms / 1e9
+            rec.update(tflops=round(tf, 1), frac=round(tf / pk["bf16_tflops"], 3), peak=f"{pk['bf16_tflops']} TFLOP/s {tag}")
+        if bytes_ is not None:
+            gbs = bytes_ / ms / 1e6
+            rec.update(gbs=round(gbs, 1), frac_hbm=round(gbs / pk["hbm_gbs"], 3), hbm_peak=f"{pk['hbm_gbs']} GB/s {tag}")
+        print(json.dumps(rec), flush=True)
+
+    tok = 4096 if a.small else 16384
+    H, I, V = 3584, 18944, 152064
+    rnd = lambda *s: (torch.randn(*s, device=dev) * 0.05).bfloat16()
+
+    if want("gemm"):
+        for name, (M, N, K, amn, bmn) in {"gemm_fwd_gate_up": (tok, 2 * I if not a.small else 8192, H, False, False),
+                                          "gemm_dgrad_down": (tok, I if not a.small else 8192, H, False, True),
+                                          "gemm_wgrad_qkv": (4608, H, tok, True, True),
+                                          "gemm_decode_skinny": (320, 4608, H, False, False)}.items():
+            A = rnd(K, M) if amn else rnd(M, K)
+            B = rnd(K, N) if bmn else rnd(N, K)
+            out = torch.empty(M, N, device=dev, dtype=torch.float32 if amn else torch.bfloat16)
+            ms = T(lambda: ops.gemm(A, B, None, out, amn, bmn, amn, False, 0))
+            report(name, [M, N, K], ms, flops=2.0 * M * N * K, bytes_=2.0 * (M * K + N * K) + out.element_size() * M * N)
+    if want("lmhead"):
+        Vs = 32768 if a.small else V
+        h, w = rnd(tok, H), rnd(Vs, H)
+        labels = torch.randint(0, Vs, (tok,), device=dev)
+        ms = T(lambda: ops.lmhead_fwd(h, w, labels, 1.0))
+        report("lmhead_fwd_logprob_entropy", [tok, Vs, H], ms, flops=2.0 * tok * Vs * H)
+    if want("attn_fwd") or want("attn_bwd"):
+        S = 1024 if a.small else 3072
+        nseq = max(1, tok // S)
+        nh, nkv, hd = 28, 4, 128
+        Tt = nseq * S
+        q, k, v = rnd(Tt, nh, hd), rnd(Tt, nkv, hd), rnd(Tt, nkv, hd)
+        cu = torch.arange(0, Tt + 1, S, dtype=torch.int32, device=dev)
+        fl = 4.0 * nseq * nh * hd * S * S / 2
+        if want("attn_fwd"):
+            ms = T(lambda: ops.attn_fwd(q, k, v, cu, 1.0 / math.sqrt(hd)))
+            report("attn_fwd_causal_gqa", [nseq, S, nh, nkv, hd], ms, flops=fl)
+        if want("attn_bwd"):
+            out, lse = ops.attn_fwd(q, k, v, cu, 1.0 / math.sqrt(hd))
+            do = rnd(Tt, nh, hd)
+            ms = T(lambda: ops.attn_bwd(do, q, k, v, out, lse, cu, S, 1.0 / math.sqrt(hd)))
+            report("attn_bwd_causal_gqa", [nseq, S, nh, nkv, hd], ms, flops=2.5 * fl)
+
+            def sdpa_bwd():
+                with torch.enable_grad():
+                    q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
+                    o = F._sdpa_varlen(q_, k_, v_, cu.cpu(), 1.0 / math.sqrt(hd))
+                    torch.autograd.grad(o, (q_, k_, v_), do)
+
+            ms = T(sdpa_bwd)
+            report("library_sdpa_fwd_plus_bwd_for_comparison", [nseq, S, nh, nkv, hd], ms, flops=3.5 * fl)
+    if want("paged_decode"):
+        B_, ctx, bs = (64, 1024, 64) if a.small else (320, 2048, 64)
+        nh, nkv, hd = 28, 4, 128
+        nb = B_ * (ctx // bs)
+        kc, vc = rnd(nb, bs, nkv, hd), rnd(nb, bs, nkv, hd)
+        bt = torch.arange(nb, dtype=torch.int32, device=dev).view(B_, ctx // bs)
+        cl = torch.full((B_,), ctx, dtype=torch.int32, device=dev)
+        q = rnd(B_, nh, hd)
+        ms = T(lambda: F.paged_decode_attention(q, kc, vc, bt, cl))
+        report("paged_decode_attention", [B_, ctx, nh, nkv, hd], ms, bytes_=2.0 * 2 * nb * bs * nkv * hd)
+    if want("rmsnorm"):
+        x, r, w = rnd(tok, H), rnd(tok, H), rnd(H)
+        ms = T(lambda: F.rms_norm(x, w, 1e-6, r))
+        report("rmsnorm_fwd_residual", [tok, H], ms, bytes_=2.0 * tok * H * 4)
+        y, xe, rs = F.rms_norm(x, w, 1e-6, r)
+        dw = torch.zeros(H, device=dev)
+        ms = T(lambda: F.rms_norm_bwd(x, xe, w, rs, r, dw, True))
+        report("rmsnorm_bwd", [tok, H], ms, bytes_=2.0 * tok * H * 4)
+    if want("swiglu"):
+        Is = 4096 if a.small else I
+        gu = rnd(tok, 2 * Is)
+        ms = T(lambda: F.swiglu(gu))
+        report("swiglu_fwd", [tok, Is], ms, bytes_=2.0 * tok * Is * 3)
+    if want("adamw"):
+        n = (64 << 20) if a.small else (512 << 20)
+        master, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
+        m, v2 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        outb = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        ctrl = torch.zeros(4, device=dev)
+        ctrl[1] = 1.0
+        ms = T(lambda: ops.adamw_(master, g, m, v2, outb, ctrl, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, False))
+        report("adamw_fused_cast", [n], ms, bytes_=n * (4 * 4 + 3 * 4 + 2.0))
+    native.check_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -40,7 +40,9 @@ struct AttnSmem {
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 128 + 1024;
+  // No alignment slack and no static shared memory: two CTAs (2 x (TOTAL + 1 KB reserved)) must fit the 228 KB of an
+  // SM; the dynamic window then starts 1024-byte aligned, which the kernel verifies before touching it.
+  static constexpr int TOTAL = OFF_BAR + 128;
 };
 
 template <int HD>
@@ -49,8 +51,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   using L = AttnSmem<HD>;
   constexpr int PANELS = HD / 64;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled TMA/MMA layouts need 1024-byte aligned tiles
+    if (threadIdx.x == 0) atomicExch(p.status, 9);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
@@ -63,7 +69,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_p = bars + 7;      // 1
   uint64_t* bar_o = bars + 8;      // 1
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
-  __shared__ int s_tile[4];  // seq start token, q0, seqlen, valid
+  int* s_tile = reinterpret_cast<int*>(bars + 10);  // seq start token, q0, seqlen, valid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
