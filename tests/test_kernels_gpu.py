@@ -196,6 +196,62 @@ def test_attention_forward_and_backward_tcgen05(ops, lens, nh, nkv):
     assert rel(dv, dv_r) < 3e-2 and rel(dk, dk_r) < 3e-2 and rel(dq, dq_r) < 3e-2, (rel(dq, dq_r), rel(dk, dk_r), rel(dv, dv_r))
 
 
+def test_moe_router_grouped_gemm_and_layer_match_reference(ops, monkeypatch):
+    from verl_b200.models import DecoderModel, FlatParams
+    from verl_b200.models.config import ModelConfig
+
+    torch.manual_seed(0)
+    # router kernel against softmax + topk
+    logits = torch.randn(700, 64, device=DEV).bfloat16()
+    w, idx, counts = ops.moe_route_topk(logits, 4, True)
+    pr = torch.softmax(logits.float(), -1)
+    rw, ri = torch.topk(pr, 4, -1)
+    rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(idx.long().sort(-1).values, ri.sort(-1).values) and rel(w.sort(-1).values, rw.sort(-1).values) < 1e-4
+    assert torch.equal(counts.long(), torch.bincount(ri.reshape(-1), minlength=64))
+    # one MoE layer: native (grouped tcgen05 GEMMs) against the per-expert fallback, forward and all gradients
+    cfg = ModelConfig(model_type="qwen3_moe", vocab_size=512, hidden_size=256, intermediate_size=256, num_hidden_layers=1,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=32, num_experts_per_tok=4,
+                      moe_intermediate_size=128, eos_token_id=2, pad_token_id=0)
+    outs = {}
+    for native_on in ("1", "0"):
+        monkeypatch.setenv("VERL_B200_MOE_NATIVE", native_on)
+        P = FlatParams(cfg, dtype=torch.bfloat16, device=DEV, with_main_grad=True)
+        P.init_weights(seed=4, std=0.05)
+        model = DecoderModel(cfg, P)
+        W = P.layer(0)
+        h2 = (torch.randn(700, 256, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1))).bfloat16()
+        g = (torch.randn(700, 256, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2))).bfloat16()
+        S = {}
+        out = model._moe_fwd(W, h2, S)
+        gh = model._moe_bwd(W, g, h2, S)
+        outs[native_on] = (out, gh, W["mlp.experts.gate_up_proj"].main_grad.clone(), W["mlp.experts.down_proj"].main_grad.clone(),
+                           W["mlp.gate.weight"].main_grad.clone())
+    assert ops.gemm_status() == 0
+    for a, b in zip(outs["1"], outs["0"]):
+        assert rel(a, b) < 3e-2, rel(a, b)
+
+
+@pytest.mark.parametrize("shape", [(320, 4608, 3584), (77, 136, 256), (1000, 1024, 1024)])
+def test_fp8_block_scaled_quant_and_gemm(ops, shape):
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    M, N, K = shape
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    xq, xs = F.fp8_quantize_1x128(x)
+    xq_c, xs_c = F.fp8_quantize_1x128(x.cpu())
+    assert rel(xs, xs_c) < 1e-6 and (xq.cpu() != xq_c).float().mean() < 1e-2  # identical up to rounding ties (reciprocal multiply vs division)
+    assert rel(F.fp8_dequantize_1x128(xq.cpu(), xs.cpu()), x.float()) < 0.07
+    wq, ws = F.fp8_quantize_1x128(w)
+    y = F.linear_fp8(x, wq, ws)
+    ref = F.fp8_dequantize_1x128(xq.cpu(), xs.cpu()) @ F.fp8_dequantize_1x128(wq.cpu(), ws.cpu()).t()
+    assert ops.gemm_status() == 0
+    assert rel(y, ref) < 1e-2  # same quantised operands: only accumulation order and the bf16 output rounding differ
+    assert rel(y, x.float().cpu() @ w.float().cpu().t()) < 0.06  # against the unquantised product
+
+
 def test_sampler_distribution_and_logprob(ops):
     from verl_b200.ops import functional as F
 

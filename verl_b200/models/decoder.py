@@ -19,6 +19,8 @@ log-prob / entropy from the LM head).
 
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any, Callable, Optional
@@ -251,15 +253,101 @@ class DecoderModel:
         return g_h2
 
     # -- mixture of experts: softmax router, top-k, tokens grouped by expert ------------------------
-    def _route(self, logits: torch.Tensor):
+    def _route(self, logits: torch.Tensor, idx: Optional[torch.Tensor] = None):
+        """Softmax over experts, top-k, optional renormalisation. With ``idx`` given the selection is taken as is and
+        only the weights are (differentiably) recomputed, so that forward and backward agree on exact ties."""
         cfg = self.cfg
         probs = torch.softmax(logits.float(), dim=-1)
-        w, idx = torch.topk(probs, cfg.num_experts_per_tok, dim=-1)
+        if idx is None:
+            if logits.is_cuda and logits.dtype == torch.bfloat16 and cfg.num_experts <= 1024:
+                idx = F._ops().moe_route_topk(logits, cfg.num_experts_per_tok, bool(cfg.norm_topk_prob))[1].long()
+            else:
+                idx = torch.topk(probs, cfg.num_experts_per_tok, dim=-1).indices
+        w = probs.gather(-1, idx.long())
         if cfg.norm_topk_prob:
             w = w / w.sum(-1, keepdim=True)
         return w, idx
 
+    # -- device path: router, expert-grouped layout and grouped tcgen05 GEMMs; no host synchronisation anywhere --------
+    @staticmethod
+    def _moe_plan(idx: torch.Tensor, counts: torch.Tensor, T: int, k: int, E: int) -> dict:
+        """Expert-grouped row layout in which every expert's rows start at a multiple of 128 (padding rows are zero).
+        ``slot[t, j]`` = row of the j-th expert copy of token t; ``src[row]`` = source token or -1 for padding."""
+        dev = idx.device
+        flat_e = idx.reshape(-1).long()
+        order = torch.argsort(flat_e, stable=True)
+        cnt = counts.long()
+        seg = torch.zeros(E + 1, dtype=torch.int64, device=dev)
+        seg[1:] = ((cnt + 127) // 128 * 128).cumsum(0)
+        first = cnt.cumsum(0) - cnt
+        e_sorted = flat_e[order]
+        slot_sorted = seg[e_sorted] + (torch.arange(T * k, device=dev) - first[e_sorted])
+        cap = ((T * k + 127) // 128 + E) * 128  # upper bound of the padded row count, known without reading `counts`
+        slot = torch.empty(T * k, dtype=torch.int32, device=dev)
+        slot[order] = slot_sorted.int()
+        src = torch.full((cap,), -1, dtype=torch.int32, device=dev)
+        src[slot_sorted] = torch.div(order, k, rounding_mode="floor").int()
+        tiles = torch.arange(cap // 128, device=dev) * 128
+        tile_expert = torch.searchsorted(seg[1:].contiguous(), tiles, right=True).clamp_(max=E - 1).int()
+        return dict(slot=slot.view(T, k), src=src, seg=seg.int(), tile_expert=tile_expert,
+                    num_mtiles=(seg[E:] // 128).int(), cap=cap)
+
+    def _moe_fwd_native(self, W, h2, S: Optional[dict]):
+        cfg = self.cfg
+        ops = F._ops()
+        T, H = h2.shape
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        logits = F.gemm(h2, W["mlp.gate.weight"])
+        w, idx, counts = ops.moe_route_topk(logits, k, bool(cfg.norm_topk_prob))
+        plan = self._moe_plan(idx, counts, T, k, E)
+        xp = ops.moe_gather_rows(h2, plan["src"], None)
+        gu = ops.gemm_grouped_rows(xp, W["mlp.experts.gate_up_proj"], False, plan["tile_expert"], plan["num_mtiles"])
+        y = ops.gemm_grouped_rows(F.swiglu(gu), W["mlp.experts.down_proj"], False, plan["tile_expert"], plan["num_mtiles"])
+        out = ops.moe_combine(y, plan["slot"], w)
+        if S is not None:
+            S.update(moe=dict(native=True, logits=logits, w=w, idx=idx, plan=plan, gu=gu, y=y))
+        return out
+
+    def _moe_bwd_native(self, W, g_d, h2, S: dict):
+        cfg = self.cfg
+        ops = F._ops()
+        M = S["moe"]
+        plan, w, gu, y = M["plan"], M["w"], M["gu"], M["y"]
+        T, H = h2.shape
+        k = cfg.num_experts_per_tok
+        g_d = g_d.contiguous()
+        g_w = ops.moe_combine_bwd_w(g_d, y, plan["slot"])
+        w_rows = torch.zeros(plan["cap"], dtype=torch.float32, device=h2.device)
+        w_rows[plan["slot"].reshape(-1).long()] = w.reshape(-1)
+        g_y = ops.moe_gather_rows(g_d, plan["src"], w_rows)
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        act = F.swiglu(gu)
+        g_act = ops.gemm_grouped_rows(g_y, Wd, True, plan["tile_expert"], plan["num_mtiles"])
+        if getattr(Wd, "main_grad", None) is not None:
+            ops.gemm_grouped_wgrad_(g_y, act, Wd.main_grad, plan["seg"], True)
+        g_gu = F.swiglu_bwd(g_act, gu)
+        g_xp = ops.gemm_grouped_rows(g_gu, Wgu, True, plan["tile_expert"], plan["num_mtiles"])
+        if getattr(Wgu, "main_grad", None) is not None:
+            xp = ops.moe_gather_rows(h2, plan["src"], None)
+            ops.gemm_grouped_wgrad_(g_gu, xp, Wgu.main_grad, plan["seg"], True)
+        g_h2 = ops.moe_combine(g_xp, plan["slot"], None).float()
+        with torch.enable_grad():
+            lg = M["logits"].detach().float().requires_grad_(True)
+            wr, _ = self._route(lg, idx=M["idx"])
+            (g_logits,) = torch.autograd.grad(wr, lg, g_w)
+        g_logits = g_logits.to(h2.dtype)
+        g_h2 += F.gemm(g_logits, W["mlp.gate.weight"], b_mn=True).float()
+        self._wgrad(W["mlp.gate.weight"], g_logits, h2)
+        return g_h2.to(h2.dtype)
+
+    def _moe_native_ok(self, h2) -> bool:
+        c = self.cfg
+        return (h2.is_cuda and h2.dtype == torch.bfloat16 and c.num_experts <= 1024 and c.hidden_size % 64 == 0
+                and c.moe_intermediate_size % 64 == 0 and os.environ.get("VERL_B200_MOE_NATIVE", "1") != "0")
+
     def _moe_fwd(self, W, h2, S: Optional[dict]):
+        if self._moe_native_ok(h2):
+            return self._moe_fwd_native(W, h2, S)
         cfg = self.cfg
         T, H = h2.shape
         E, k = cfg.num_experts, cfg.num_experts_per_tok
@@ -284,10 +372,12 @@ class DecoderModel:
         out = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
         out.index_add_(0, tok, (y * wp.unsqueeze(-1)).float())
         if S is not None:
-            S.update(moe=dict(logits=logits, order=order, tok=tok, counts=counts, gu=gu, y=y, wp=wp))
+            S.update(moe=dict(logits=logits, idx=idx, order=order, tok=tok, counts=counts, gu=gu, y=y, wp=wp))
         return out.to(h2.dtype)
 
     def _moe_bwd(self, W, g_d, h2, S: dict):
+        if S["moe"].get("native"):
+            return self._moe_bwd_native(W, g_d, h2, S)
         cfg = self.cfg
         M = S["moe"]
         order, tok, counts, gu, y, wp = M["order"], M["tok"], M["counts"], M["gu"], M["y"], M["wp"]
@@ -322,7 +412,7 @@ class DecoderModel:
         g_w[order] = g_wp
         with torch.enable_grad():
             lg = M["logits"].detach().float().requires_grad_(True)
-            w, _ = self._route(lg)
+            w, _ = self._route(lg, idx=M["idx"])
             (g_logits,) = torch.autograd.grad(w, lg, g_w.view(T, k))
         g_logits = g_logits.to(h2.dtype)
         g_h2 += F.gemm(g_logits, W["mlp.gate.weight"], b_mn=True).float()

@@ -71,6 +71,7 @@ int64_t gemm_status() {
   const int a = vb_gemm_status();
   int b = vb_attn_status();
   if (b == 0) b = vb_attn_bwd_status();
+  if (b == 0) b = vb_fp8_status();
   const int c = vb_pd_status();
   return a != 0 ? a : (b != 0 ? 100 + b : (c != 0 ? 200 + c : 0));
 }
@@ -494,6 +495,184 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
 
 int64_t comm_status() { return vb_comm_status(); }
 
+// ---- fp8 (e4m3) with 1x128 block scales
+// x [R, C] bf16 -> (q [R, C] uint8 holding e4m3, scales [C/128, R] fp32)
+std::tuple<Tensor, Tensor> fp8_quant_1x128(const Tensor& x) {
+  CHECK_BF16(x);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 128 == 0, "fp8_quant_1x128: [R, C] with C % 128 == 0");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), C = x.size(1);
+  Tensor q = at::empty({R, C}, x.options().dtype(at::kByte));
+  Tensor sc = at::empty({C / 128, R}, x.options().dtype(at::kFloat));
+  count(1);
+  CHECK_RC(vb_fp8_quant_1x128(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), sc.data_ptr<float>(), (int)R, (int)C, cur_stream()),
+           "vb_fp8_quant_1x128");
+  return {q, sc};
+}
+
+// out[M, N] bf16 = dequant(aq, sa) @ dequant(bq, sb)^T (+bias)
+Tensor gemm_fp8_blockscale(const Tensor& aq, const Tensor& sa, const Tensor& bq, const Tensor& sb, const OptTensor& bias) {
+  TORCH_CHECK(aq.scalar_type() == at::kByte && bq.scalar_type() == at::kByte && aq.is_cuda() && bq.is_cuda());
+  TORCH_CHECK(aq.dim() == 2 && bq.dim() == 2 && aq.stride(1) == 1 && bq.stride(1) == 1 && aq.size(1) == bq.size(1));
+  CHECK_F32(sa);
+  CHECK_F32(sb);
+  const int64_t M = aq.size(0), K = aq.size(1), N = bq.size(0);
+  TORCH_CHECK(sa.is_contiguous() && sb.is_contiguous() && sa.size(0) == K / 128 && sa.size(1) == M && sb.size(0) == K / 128 && sb.size(1) == N,
+              "gemm_fp8_blockscale: scales must be [K/128, M] and [K/128, N]");
+  const c10::cuda::CUDAGuard guard(aq.device());
+  Tensor d = at::empty({M, N}, aq.options().dtype(at::kBFloat16));
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous());
+    bias_ptr = bias->data_ptr();
+  }
+  if (M == 0) return d;
+  count(1);
+  CHECK_RC(vb_gemm_fp8_blockscale(aq.data_ptr(), sa.data_ptr<float>(), bq.data_ptr(), sb.data_ptr<float>(), d.data_ptr(), bias_ptr, (int)M,
+                                  (int)N, (int)K, aq.stride(0), bq.stride(0), d.stride(0), cur_stream()), "vb_gemm_fp8_blockscale");
+  return d;
+}
+
+// ---- mixture of experts
+// (weights [T,k] fp32, experts [T,k] int32, counts [E] int32) from router logits [T, E]
+std::tuple<Tensor, Tensor, Tensor> moe_route_topk(const Tensor& logits, int64_t k, bool renorm) {
+  CHECK_BF16(logits);
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  Tensor w = at::empty({T, k}, logits.options().dtype(at::kFloat));
+  Tensor idx = at::empty({T, k}, logits.options().dtype(at::kInt));
+  Tensor counts = at::zeros({E}, logits.options().dtype(at::kInt));
+  count(1);
+  CHECK_RC(vb_moe_route_topk(logits.data_ptr(), logits.stride(0), (int)T, (int)E, (int)k, renorm, w.data_ptr<float>(),
+                             idx.data_ptr<int>(), counts.data_ptr<int>(), cur_stream()), "vb_moe_route_topk");
+  return {w, idx, counts};
+}
+
+// dst[r] = src[map[r]] (* scale[r]) or zeros where map[r] < 0
+Tensor moe_gather_rows(const Tensor& src, const Tensor& map, const OptTensor& scale) {
+  CHECK_BF16(src);
+  TORCH_CHECK(src.dim() == 2 && src.stride(1) == 1 && map.scalar_type() == at::kInt && map.is_contiguous() && map.is_cuda());
+  const c10::cuda::CUDAGuard guard(src.device());
+  const int64_t rows = map.numel(), H = src.size(1);
+  Tensor dst = at::empty({rows, H}, src.options());
+  const float* sc = nullptr;
+  if (scale.has_value()) {
+    TORCH_CHECK(scale->scalar_type() == at::kFloat && scale->numel() == rows && scale->is_contiguous());
+    sc = scale->data_ptr<float>();
+  }
+  count(1);
+  CHECK_RC(vb_moe_gather_rows(src.data_ptr(), src.stride(0), map.data_ptr<int>(), sc, dst.data_ptr(), dst.stride(0), (int)rows,
+                              (int)H, cur_stream()), "vb_moe_gather_rows");
+  return dst;
+}
+
+// out[t] = sum_j w[t,j] * y[slot[t,j]]   (w optional: plain sum)
+Tensor moe_combine(const Tensor& y, const Tensor& slot, const OptTensor& w) {
+  CHECK_BF16(y);
+  TORCH_CHECK(y.dim() == 2 && y.stride(1) == 1 && slot.dim() == 2 && slot.scalar_type() == at::kInt && slot.is_contiguous());
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int64_t T = slot.size(0), k = slot.size(1), H = y.size(1);
+  Tensor out = at::empty({T, H}, y.options());
+  const float* wp = nullptr;
+  if (w.has_value()) {
+    TORCH_CHECK(w->scalar_type() == at::kFloat && w->numel() == T * k && w->is_contiguous());
+    wp = w->data_ptr<float>();
+  }
+  count(1);
+  CHECK_RC(vb_moe_combine(y.data_ptr(), y.stride(0), slot.data_ptr<int>(), wp, out.data_ptr(), out.stride(0), (int)T, (int)H, (int)k,
+                          cur_stream()), "vb_moe_combine");
+  return out;
+}
+
+Tensor moe_combine_bwd_w(const Tensor& g, const Tensor& y, const Tensor& slot) {
+  CHECK_BF16(g);
+  CHECK_BF16(y);
+  TORCH_CHECK(g.stride(1) == 1 && y.stride(1) == 1 && slot.scalar_type() == at::kInt && slot.is_contiguous());
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int64_t T = slot.size(0), k = slot.size(1), H = y.size(1);
+  Tensor gw = at::empty({T, k}, y.options().dtype(at::kFloat));
+  count(1);
+  CHECK_RC(vb_moe_combine_bwd_w(g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0), slot.data_ptr<int>(), gw.data_ptr<float>(),
+                                (int)T, (int)H, (int)k, cur_stream()), "vb_moe_combine_bwd_w");
+  return gw;
+}
+
+// pointer tables for the peer kernels live on the device: int64 CUDA tensors
+inline const unsigned long long* dptr(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "pointer table: int64 CUDA tensor");
+  return reinterpret_cast<const unsigned long long*>(t.data_ptr());
+}
+
+void moe_dispatch_peer_(const Tensor& src, const Tensor& dst_ptrs, const Tensor& dest_rank, const Tensor& dest_row, int64_t k) {
+  CHECK_BF16(src);
+  TORCH_CHECK(src.dim() == 2 && src.stride(1) == 1 && dest_rank.scalar_type() == at::kInt && dest_row.scalar_type() == at::kInt);
+  const c10::cuda::CUDAGuard guard(src.device());
+  count(1);
+  CHECK_RC(vb_moe_dispatch_peer(src.data_ptr(), src.stride(0), dptr(dst_ptrs), dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(),
+                                (int)dest_row.numel(), (int)k, (int)src.size(1), cur_stream()), "vb_moe_dispatch_peer");
+}
+
+Tensor moe_combine_peer(const Tensor& y_ptrs, const Tensor& src_rank, const Tensor& src_row, const OptTensor& w, int64_t H,
+                        const Tensor& like) {
+  TORCH_CHECK(src_rank.scalar_type() == at::kInt && src_row.scalar_type() == at::kInt && src_row.dim() == 2);
+  const c10::cuda::CUDAGuard guard(like.device());
+  const int64_t T = src_row.size(0), k = src_row.size(1);
+  Tensor out = at::empty({T, H}, like.options().dtype(at::kBFloat16));
+  const float* wp = nullptr;
+  if (w.has_value()) {
+    TORCH_CHECK(w->scalar_type() == at::kFloat && w->numel() == T * k && w->is_contiguous());
+    wp = w->data_ptr<float>();
+  }
+  count(1);
+  CHECK_RC(vb_moe_combine_peer(dptr(y_ptrs), src_rank.data_ptr<int>(), src_row.data_ptr<int>(), wp, out.data_ptr(), out.stride(0), (int)T,
+                               (int)H, (int)k, cur_stream()), "vb_moe_combine_peer");
+  return out;
+}
+
+void moe_publish_counts_(const Tensor& counts, const Tensor& table_ptrs, int64_t rank) {
+  TORCH_CHECK(counts.scalar_type() == at::kInt && counts.is_cuda() && counts.is_contiguous());
+  const c10::cuda::CUDAGuard guard(counts.device());
+  count(1);
+  CHECK_RC(vb_moe_publish_counts(counts.data_ptr<int>(), dptr(table_ptrs), (int)table_ptrs.numel(), (int)rank, (int)counts.numel(),
+                                 cur_stream()), "vb_moe_publish_counts");
+}
+
+// mode 1: out[rows, N] = a[rows, K] @ W_e^T per 128-row tile (w: [E, N, K], or [E, K, N] when b_mn)
+Tensor gemm_grouped_rows(const Tensor& a, const Tensor& w, bool b_mn, const Tensor& tile_expert, const Tensor& num_mtiles) {
+  CHECK_BF16(a);
+  CHECK_BF16(w);
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && w.dim() == 3 && w.is_contiguous() && a.size(0) % 128 == 0);
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.is_cuda() && num_mtiles.scalar_type() == at::kInt && num_mtiles.is_cuda());
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t rows = a.size(0), K = a.size(1), E = w.size(0);
+  const int64_t N = b_mn ? w.size(2) : w.size(1);
+  TORCH_CHECK((b_mn ? w.size(1) : w.size(2)) == K, "gemm_grouped_rows: contraction mismatch");
+  Tensor d = at::empty({rows, N}, a.options());
+  if (rows == 0) return d;
+  count(1);
+  CHECK_RC(vb_gemm_grouped(1, a.data_ptr(), w.data_ptr(), d.data_ptr(), (int)rows, (int)rows, (int)N, (int)K, a.stride(0), w.stride(1),
+                           d.stride(0), b_mn, 0, (int)E, tile_expert.data_ptr<int>(), num_mtiles.data_ptr<int>(), nullptr, cur_stream()),
+           "vb_gemm_grouped(rows)");
+  return d;
+}
+
+// mode 2: out[e] (+)= dy[seg_e]^T @ x[seg_e]   (out: fp32 [E, M, N])
+void gemm_grouped_wgrad_(const Tensor& dy, const Tensor& x, Tensor out, const Tensor& seg_start, bool accumulate) {
+  CHECK_BF16(dy);
+  CHECK_BF16(x);
+  CHECK_F32(out);
+  TORCH_CHECK(dy.stride(1) == 1 && x.stride(1) == 1 && out.dim() == 3 && out.is_contiguous() && dy.size(0) == x.size(0) && dy.size(0) % 128 == 0);
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_start.is_cuda() && seg_start.numel() == out.size(0) + 1);
+  const c10::cuda::CUDAGuard guard(dy.device());
+  if (dy.size(0) == 0) return;
+  if (!accumulate) out.zero_();
+  count(1);
+  CHECK_RC(vb_gemm_grouped(2, dy.data_ptr(), x.data_ptr(), out.data_ptr(), (int)dy.size(0), (int)out.size(1), (int)out.size(2), 0,
+                           dy.stride(0), x.stride(0), out.stride(1), 1, 1, (int)out.size(0), nullptr, nullptr, seg_start.data_ptr<int>(),
+                           cur_stream()), "vb_gemm_grouped(wgrad)");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(verl_b200, m) {
@@ -503,6 +682,17 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("comm_status", &comm_status);
+  m.def("fp8_quant_1x128", &fp8_quant_1x128);
+  m.def("gemm_fp8_blockscale", &gemm_fp8_blockscale);
+  m.def("moe_route_topk", &moe_route_topk);
+  m.def("moe_gather_rows", &moe_gather_rows);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd_w", &moe_combine_bwd_w);
+  m.def("moe_dispatch_peer_", &moe_dispatch_peer_);
+  m.def("moe_combine_peer", &moe_combine_peer);
+  m.def("moe_publish_counts_", &moe_publish_counts_);
+  m.def("gemm_grouped_rows", &gemm_grouped_rows);
+  m.def("gemm_grouped_wgrad_", &gemm_grouped_wgrad_);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
   m.def("launch_count", &launch_count);

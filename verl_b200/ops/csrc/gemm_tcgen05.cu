@@ -67,6 +67,15 @@ struct GemmParams {
   long long ar_buf_elems;
   unsigned int* ar_epoch;   // this rank's [2]: {calls completed, CTAs finished in the running call}
   unsigned long long ar_limit_ns;  // how long a slab waits for its peers before giving up
+  // grouped (mixture-of-experts) modes; all row segments are padded to multiples of 128 rows
+  //  1: rows grouped by expert  D[rows, N] = A[rows, K] * B_e^T, expert of each 128-row tile from grp_tile_expert
+  //  2: contraction grouped     D_e[M, N] (+)= A[seg_e, M]^T * B[seg_e, N] for every expert e (weight gradients)
+  int grp_mode;
+  const int* grp_tile_expert;
+  const int* grp_num_mtiles;
+  const int* grp_seg_start;  // [E + 1]
+  int grp_b_rows;            // rows one expert occupies in the stacked 2-D view of B
+  int grp_E;
 };
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
@@ -113,11 +122,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
+  const int num_m = (p.grp_mode == 1) ? *p.grp_num_mtiles : (p.M + BM - 1) / BM;
   const int splits = p.k_splits > 1 ? p.k_splits : 1;
   const int num_mn = num_m * num_n;
-  const int num_tiles = num_mn * splits;
+  const int num_tiles = (p.grp_mode == 2) ? num_mn * p.grp_E : num_mn * splits;
   const int num_kb_total = (p.K + BK - 1) / BK;
   const int kb_per = (num_kb_total + splits - 1) / splits;
   constexpr int GROUP_M = 8;
@@ -146,20 +155,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   unsigned int ar_epoch_now = 0;
   if constexpr (EPI == EPI_ALLREDUCE) ar_epoch_now = *reinterpret_cast<volatile unsigned int*>(p.ar_epoch) + 1u;
 
-  auto k_range = [&](int t, int& kb0, int& kb1) {
-    const int sp = t / num_mn;
-    kb0 = sp * kb_per;
-    kb1 = min(num_kb_total, kb0 + kb_per);
-  };
-  auto tile_coords = [&](int t, int& m_idx, int& n_idx) {
-    t = t % num_mn;
+  // tile t -> output tile origin (m0, n0), k-block range, row offset of the B tile in its stacked view, row offset of
+  // the output; returns false for a tile without work (an expert that received no rows)
+  auto decode_tile = [&](int t, int& m0, int& n0, int& kb0, int& kb1, int& b_off, long long& d_off) -> bool {
+    b_off = 0;
+    d_off = 0;
+    if (p.grp_mode == 1) {
+      const int m_idx = t / num_n;
+      m0 = m_idx * BM;
+      n0 = (t - m_idx * num_n) * BN;
+      kb0 = 0;
+      kb1 = num_kb_total;
+      b_off = p.grp_tile_expert[m_idx] * p.grp_b_rows;
+      return true;
+    }
+    int tt = t;
+    if (p.grp_mode == 2) {
+      const int e = t / num_mn;
+      tt = t - e * num_mn;
+      kb0 = p.grp_seg_start[e] / BK;
+      kb1 = p.grp_seg_start[e + 1] / BK;
+      d_off = static_cast<long long>(e) * p.M;
+    } else {
+      const int sp = t / num_mn;
+      tt = t - sp * num_mn;
+      kb0 = sp * kb_per;
+      kb1 = min(num_kb_total, kb0 + kb_per);
+      d_off = static_cast<long long>(sp) * p.M;  // split-K partials are stacked [splits][M][N]
+    }
     const int per_group = GROUP_M * num_n;
-    const int g = t / per_group;
+    const int g = tt / per_group;
     const int first_m = g * GROUP_M;
     const int gsize = min(num_m - first_m, GROUP_M);
-    const int r = t - g * per_group;
-    m_idx = first_m + (r % gsize);
-    n_idx = r / gsize;
+    const int r = tt - g * per_group;
+    m0 = (first_m + (r % gsize)) * BM;
+    n0 = (r / gsize) * BN;
+    return kb1 > kb0;
   };
 
   if (warp == 0) {
@@ -169,11 +200,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_idx, n_idx;
-        tile_coords(t, m_idx, n_idx);
-        const int m0 = m_idx * BM, n0 = n_idx * BN;
-        int kb0, kb1;
-        k_range(t, kb0, kb1);
+        int m0, n0, kb0, kb1, b_off;
+        long long d_off;
+        if (!decode_tile(t, m0, n0, kb0, kb1, b_off, d_off)) continue;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, ST_TIMEOUT_PRODUCER);
@@ -191,10 +220,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tma_a, &full_bar[stage], m0 + 64 * j, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tma_b, &full_bar[stage], k0, b_off + n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tma_b, &full_bar[stage], n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tma_b, &full_bar[stage], n0 + 64 * j, (p.grp_mode == 1 ? b_off : 0) + k0);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -213,6 +243,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m0_, n0_, kb0, kb1, b_off_;
+        long long d_off_;
+        if (!decode_tile(t, m0_, n0_, kb0, kb1, b_off_, d_off_)) continue;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
           atomicExch(p.status, ST_TIMEOUT_MMA);
           ok = false;
@@ -220,8 +253,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        int kb0, kb1;
-        k_range(t, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             atomicExch(p.status, ST_TIMEOUT_MMA);
@@ -260,9 +291,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int m_idx, n_idx;
-      tile_coords(t, m_idx, n_idx);
-      const int m0 = m_idx * BM, n0 = n_idx * BN;
+      int m0, n0, kb0_, kb1_, b_off_;
+      long long d_off;
+      if (!decode_tile(t, m0, n0, kb0_, kb1_, b_off_, d_off)) continue;
+      const int n_idx = n0 / BN;
       if (!mbar_wait(&acc_full[acc], acc_phase)) {
         if (lane == 0) atomicExch(p.status, ST_TIMEOUT_EPILOGUE);
         ok = false;
@@ -270,7 +302,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      const bool row_ok = (p.grp_mode == 1) ? true : row < p.M;  // grouped rows are padded to whole tiles
       // per-row state of the LM-head epilogues (thread == row)
       float run_m = -INFINITY, run_l = 0.f, run_s = 0.f;
       long long label = -1;
@@ -375,8 +407,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
           if (p.out_f32) {
-            float* out = reinterpret_cast<float*>(p.D) + static_cast<long long>(t / num_mn) * p.M * p.ldd +
-                         static_cast<long long>(row) * p.ldd + col0;
+            float* out = reinterpret_cast<float*>(p.D) + (d_off + row) * p.ldd + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (j < ncols) {
@@ -390,7 +421,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               }
             }
           } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + (d_off + row) * p.ldd + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (j < ncols) {
@@ -681,6 +712,74 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
   cudaError_t e;
   if (wide) e = launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   else e = launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
+  return static_cast<int>(e);
+}
+
+// Grouped GEMMs of a mixture-of-experts layer; every expert's rows start at a multiple of 128 (zero-padded).
+//  mode 1 (forward / dgrad):  D[rows, N] = A[rows, K] * B_e^T for the expert e of each 128-row tile.
+//      b_mn = 0: B stacked [E*N, K]; b_mn = 1: B stacked [E*K, N] (K % 64 == 0). tile_expert[i] = expert of tile i,
+//      num_mtiles (device scalar) = number of 128-row tiles in use; rows_cap bounds the rows of A and D.
+//  mode 2 (wgrad):  D_e[M, N] (+)= A[seg_e, M]^T * B[seg_e, N], D stacked fp32 [E*M, N], seg_start [E+1] (device).
+extern "C" int vb_gemm_grouped(int mode, const void* A, const void* B, void* D, int rows_cap, int M, int N, int K, long long lda,
+                               long long ldb, long long ldd, int b_mn, int accumulate, int E, const int* tile_expert,
+                               const int* num_mtiles, const int* seg_start, cudaStream_t stream) {
+  if (rows_cap <= 0 || N <= 0 || E <= 0) return 0;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (rows_cap % 128)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
+  const int sms = num_sms();
+  const bool wide = N > 128;
+  const int BN = wide ? 256 : 128;
+  CUtensorMap ta, tb;
+  GemmParams p{};
+  p.status = status_ptr();
+  p.k_splits = 1;
+  p.grp_mode = mode; p.grp_E = E; p.grp_tile_expert = tile_expert; p.grp_num_mtiles = num_mtiles; p.grp_seg_start = seg_start;
+  p.D = D; p.ldd = ldd; p.N = N;
+  cudaError_t e;
+  int max_tiles;
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (mode == 1) {
+    if ((ldd % 8) || (b_mn && (K % 64))) return -1;
+    p.M = rows_cap; p.K = K; p.out_f32 = 0; p.accumulate = 0;
+    p.grp_b_rows = b_mn ? K : N;
+    if (!make_tmap_2d(&ta, A, bf, 2, rows_cap, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+    const bool ok = b_mn ? make_tmap_2d(&tb, B, bf, 2, (uint64_t)E * K, N, ldb, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)
+                         : make_tmap_2d(&tb, B, bf, 2, (uint64_t)E * N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return -3;
+    max_tiles = (rows_cap / 128) * ((N + BN - 1) / BN);
+    const int grid = max_tiles < sms ? max_tiles : sms;
+    auto launch = [&](auto kern, int smem) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+    };
+    if (wide) {
+      if (b_mn) launch(gemm_bf16_kernel<256, false, true, 4, EPI_STORE>, GemmSmem<256, 4>::TOTAL);
+      else launch(gemm_bf16_kernel<256, false, false, 4, EPI_STORE>, GemmSmem<256, 4>::TOTAL);
+    } else {
+      if (b_mn) launch(gemm_bf16_kernel<128, false, true, 6, EPI_STORE>, GemmSmem<128, 6>::TOTAL);
+      else launch(gemm_bf16_kernel<128, false, false, 6, EPI_STORE>, GemmSmem<128, 6>::TOTAL);
+    }
+    e = cudaGetLastError();
+  } else if (mode == 2) {
+    if ((ldd % 4) || (M % 8)) return -1;
+    p.M = M; p.K = rows_cap; p.out_f32 = 1; p.accumulate = accumulate;
+    if (!make_tmap_2d(&ta, A, bf, 2, rows_cap, M, lda, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+    if (!make_tmap_2d(&tb, B, bf, 2, rows_cap, N, ldb, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+    max_tiles = E * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = max_tiles < sms ? max_tiles : sms;
+    if (wide) {
+      auto kern = gemm_bf16_kernel<256, true, true, 4, EPI_STORE>;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, 4>::TOTAL);
+      kern<<<grid, GEMM_THREADS, GemmSmem<256, 4>::TOTAL, stream>>>(ta, tb, p);
+    } else {
+      auto kern = gemm_bf16_kernel<128, true, true, 6, EPI_STORE>;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128, 6>::TOTAL);
+      kern<<<grid, GEMM_THREADS, GemmSmem<128, 6>::TOTAL, stream>>>(ta, tb, p);
+    }
+    e = cudaGetLastError();
+  } else {
+    return -4;
+  }
   return static_cast<int>(e);
 }
 

@@ -15,6 +15,9 @@ int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, const void* bi
                            long long ldb, long long ldd, const unsigned long long* part_ptrs,
                            const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
                            double limit_s, cudaStream_t stream);
+int vb_gemm_grouped(int mode, const void* A, const void* B, void* D, int rows_cap, int M, int N, int K, long long lda, long long ldb,
+                    long long ldd, int b_mn, int accumulate, int E, const int* tile_expert, const int* num_mtiles,
+                    const int* seg_start, cudaStream_t stream);
 int vb_gemm_suggest_splits(int M, int N, int K);
 int vb_gemm_status();
 int vb_lmhead_num_tiles(int V);
@@ -76,6 +79,25 @@ int vb_adamw_allgather(float* master, const float* grad, float* m, float* v, con
                        float beta1, float beta2, float eps, float wd, int step, cudaStream_t s);
 int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n, int W, int rank, cudaStream_t s);
 int vb_comm_status();
+// gemm_fp8_blockscale.cu
+int vb_fp8_quant_1x128(const void* x, long long ldx, void* q, long long ldq, float* scales, int R, int C, cudaStream_t s);
+int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, const void* bias, int M, int N,
+                           int K, long long lda, long long ldb, long long ldd, cudaStream_t stream);
+int vb_fp8_status();
+// moe_kernels.cu
+int vb_moe_route_topk(const void* logits, long long ld, int T, int E, int k, int renorm, float* weights, int* experts, int* counts,
+                      cudaStream_t s);
+int vb_moe_gather_rows(const void* src, long long lds, const int* map, const float* scale, void* dst, long long ldd, int rows, int H,
+                       cudaStream_t s);
+int vb_moe_combine(const void* y, long long ldy, const int* slot, const float* w, void* out, long long ldo, int T, int H, int k,
+                   cudaStream_t s);
+int vb_moe_combine_bwd_w(const void* g, long long ldg, const void* y, long long ldy, const int* slot, float* gw, int T, int H, int k,
+                         cudaStream_t s);
+int vb_moe_dispatch_peer(const void* src, long long lds, const unsigned long long* dst_ptrs_dev, const int* dest_rank, const int* dest_row,
+                         int pairs, int k, int H, cudaStream_t s);
+int vb_moe_combine_peer(const unsigned long long* y_ptrs_dev, const int* src_rank, const int* src_row, const float* w, void* out,
+                        long long ldo, int T, int H, int k, cudaStream_t s);
+int vb_moe_publish_counts(const int* counts, const unsigned long long* table_ptrs_dev, int W, int rank, int E, cudaStream_t s);
 // advantage.cu
 int vb_grpo_advantage(const float* rewards, const float* mask, const int* group, int B, int L, int num_groups,
                       float eps, int norm_by_std, float* scores, float* stats, float* adv, cudaStream_t s);

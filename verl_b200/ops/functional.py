@@ -432,3 +432,35 @@ import os as _os
 
 if torch.cuda.is_available() and _os.environ.get("VERL_B200_NATIVE_ATTN_BWD", "0") == "1":
     _ATTN_IMPL["bwd"] = _native_attn_bwd
+
+
+# ----------------------------------------------------------------------------------------------- fp8 block scaling
+def fp8_quantize_1x128(x: torch.Tensor):
+    """``x`` [R, C] (C % 128 == 0) -> (``q`` uint8 [R, C] holding e4m3 bits, ``scales`` fp32 [C/128, R]) with
+    ``x ~= q * scale`` per 1x128 block, ``scale = amax / 448``. Parity target: ``verl/utils/kernel/fp8_kernel.py``
+    (blockwise cast to fp8) with the 1x128 block shape for both operands."""
+    if x.is_cuda:
+        return _ops().fp8_quant_1x128(x.contiguous())
+    R, C = x.shape
+    xb = x.float().view(R, C // 128, 128)
+    scale = xb.abs().amax(-1).clamp_min(1e-12) / 448.0
+    q = (xb / scale.unsqueeze(-1)).to(torch.float8_e4m3fn).view(R, C)
+    return q.view(torch.uint8), scale.t().contiguous()
+
+
+def fp8_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    R, C = q.shape
+    return (q.view(torch.float8_e4m3fn).float().view(R, C // 128, 128) * scales.t().unsqueeze(-1)).view(R, C)
+
+
+def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scales: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ dequant(wq)^T`` with on-the-fly 1x128 quantisation of the activation and a block-scaled e4m3 tensor-core
+    GEMM (fp32 accumulation per 128-wide K block)."""
+    if x.is_cuda:
+        xq, xs = _ops().fp8_quant_1x128(x.contiguous())
+        return _ops().gemm_fp8_blockscale(xq, xs, wq, w_scales, bias)
+    xq, xs = fp8_quantize_1x128(x)
+    y = fp8_dequantize_1x128(xq, xs) @ fp8_dequantize_1x128(wq, w_scales).t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
