@@ -74,6 +74,28 @@ def _worker_body(rank, world, port, queue):
     res["gemm_ar_err"] = max(errs)
     res["gemm_ar_identical"] = all(same)
     res["gemm_status"] = int(ops.gemm_status())
+    # ---- expert-parallel MoE layer (dispatch / combine over peer memory) against the single-GPU layer
+    from verl_b200.models import DecoderModel, FlatParams
+    from verl_b200.parallel.expert_parallel import ExpertParallelMoE
+
+    moe_cfg = ModelConfig(model_type="qwen3_moe", vocab_size=512, hidden_size=256, intermediate_size=256, num_hidden_layers=1,
+                          num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=32, num_experts_per_tok=4,
+                          moe_intermediate_size=128, eos_token_id=2, pad_token_id=0)
+    MP = FlatParams(moe_cfg, dtype=torch.bfloat16, device=dev)
+    MP.init_weights(seed=4, std=0.05)
+    Wm = MP.layer(0)
+    h2 = torch.randn(300 + 50 * rank, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(10 + rank)).bfloat16()
+    ref_out = DecoderModel(moe_cfg, MP)._moe_fwd(Wm, h2, None)
+    ep = ExpertParallelMoE(32, 4, 256, max_tokens=400, device=dev)
+    El = 32 // world
+    ep_out = ep.forward(h2, Wm["mlp.gate.weight"], Wm["mlp.experts.gate_up_proj"][rank * El:(rank + 1) * El].contiguous(),
+                        Wm["mlp.experts.down_proj"][rank * El:(rank + 1) * El].contiguous())
+    ep_out2 = ep.forward(h2, Wm["mlp.gate.weight"], Wm["mlp.experts.gate_up_proj"][rank * El:(rank + 1) * El].contiguous(),
+                         Wm["mlp.experts.down_proj"][rank * El:(rank + 1) * El].contiguous())
+    res["ep_err"] = ((ep_out.float() - ref_out.float()).abs().max() / ref_out.float().abs().max()).item()
+    res["ep_repeat_equal"] = bool(torch.equal(ep_out, ep_out2))
+    res["ep_dropped"] = int(ep.dropped)
+    res["ep_status"] = int(ops.comm_status())
     # ---- engines: fused peer-memory optimizer vs NCCL
     arch = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, eos_token_id=2, pad_token_id=0)
@@ -134,6 +156,7 @@ def test_two_rank_fused_optimizer_and_peer_collectives():
     for r in (0, 1):
         res = results[r]
         assert res["allreduce_err"] == 0.0
+        assert res["ep_err"] < 2e-2 and res["ep_repeat_equal"] and res["ep_dropped"] == 0 and res["ep_status"] == 0, res
         assert res["gemm_ar_err"] < 1e-2 and res["gemm_ar_identical"] and res["gemm_status"] == 0, res
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates

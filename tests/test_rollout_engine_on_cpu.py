@@ -74,3 +74,26 @@ def test_kv_release_resume_and_abort():
     done = eng.finished + aborted
     assert not eng.has_unfinished() and any(o.stop_reason == "aborted" for o in done)
     assert len(eng.free_slots) == 2 and len(eng.free_blocks) == eng.num_blocks
+
+
+def test_fp8_rollout_weights_stay_close_to_bf16_and_refresh_after_updates():
+    torch.manual_seed(0)
+    from verl_b200.models.config import ModelConfig
+
+    cfg = ModelConfig(model_type="qwen2", vocab_size=256, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, eos_token_id=-1, pad_token_id=0)
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    ref = RolloutEngine(cfg, P, max_num_seqs=2, max_model_len=32, block_size=8, eos_token_id=-1)
+    q8 = RolloutEngine(cfg, P, max_num_seqs=2, max_model_len=32, block_size=8, eos_token_id=-1, quantization="fp8")
+    assert len(q8.model.fp8_weights) == 2 * 4
+    prompts = [[5, 6, 7, 8], [9, 10, 11]]
+    a = ref.generate(prompts, SamplingParams(temperature=0.0, max_tokens=4))
+    b = q8.generate(prompts, SamplingParams(temperature=0.0, max_tokens=4))
+    lp = max(abs(x - y) for o, p in zip(a, b) for x, y in zip(o.log_probs[:1], p.log_probs[:1]))
+    assert lp < 0.6  # first-token log-prob under e4m3 weights and activations stays near the full-precision one
+    old = next(iter(q8.model.fp8_weights.values()))[0].clone()
+    P.flat.mul_(1.5)
+    q8.clear_kv_cache()
+    new = next(iter(q8.model.fp8_weights.values()))
+    assert torch.equal(new[0], old) and new[1].mean() > 0  # same e4m3 codes, larger scales: the copy was rebuilt

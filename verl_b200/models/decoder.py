@@ -98,6 +98,7 @@ class DecoderModel:
         assert recompute in ("none", "full", "auto")
         self.keep_layers_fn: Optional[Callable[[int], int]] = None
         self.tp: Optional[TensorParallelShard] = None  # set by the rollout engine; forward-only
+        self.fp8_weights: Optional[dict] = None         # data_ptr of a bf16 weight -> (e4m3 copy, block scales)
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -138,7 +139,7 @@ class DecoderModel:
             qkv = self.qkv_tp(W, h1)
             nh, nkv, Q, KV = nh // self.tp.size, nkv // self.tp.size, Q // self.tp.size, KV // self.tp.size
         else:
-            qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+            qkv = self._lin(W, "self_attn.qkv_proj.weight", h1, S)
         q = qkv[:, :Q].view(T, nh, hd)
         k = qkv[:, Q : Q + KV].view(T, nkv, hd)
         v = qkv[:, Q + KV :].view(T, nkv, hd)
@@ -162,7 +163,7 @@ class DecoderModel:
             S.update(qkv=qkv, attn=attn2, lse=lse)
         if self.tp is not None:
             return self.tp.row_linear(attn2, W["self_attn.o_proj.weight"][:, self.tp.rows(cfg.q_size)], None)
-        return F.gemm(attn2, W["self_attn.o_proj.weight"])
+        return self._lin(W, "self_attn.o_proj.weight", attn2, S)
 
     def qkv_tp(self, W, h1: torch.Tensor) -> torch.Tensor:
         """[T, (Q + 2 KV) / size]: this rank's q | k | v columns."""
@@ -224,6 +225,31 @@ class DecoderModel:
             b.main_grad.add_(g_qkv.float().sum(0))
         return g_h1
 
+    def _lin(self, W, name: str, x: torch.Tensor, S: Optional[dict] = None) -> torch.Tensor:
+        """``x @ W[name]^T (+ bias)``; forward-only calls use the fp8 copy of the weight when one is installed."""
+        w = W[name]
+        b = W.get(name[: -len("weight")] + "bias")
+        if S is None and self.fp8_weights is not None:
+            q = self.fp8_weights.get(w.data_ptr())
+            if q is not None:
+                return F.linear_fp8(x, q[0], q[1], b)
+        return F.gemm(x, w, b)
+
+    def quantize_linear_weights_fp8(self) -> int:
+        """(Re)build e4m3 copies with 1x128 block scales of every dense projection (rollout precision of the MoE
+        recipe; call after each weight update). Returns the bytes held by the copies."""
+        self.fp8_weights = {}
+        total = 0
+        names = ("self_attn.qkv_proj.weight", "self_attn.o_proj.weight", "mlp.gate_up_proj.weight", "mlp.down_proj.weight")
+        for i in range(self.cfg.num_hidden_layers):
+            W = self.params.layer(i)
+            for n in names:
+                if n in W and W[n].dim() == 2 and W[n].shape[1] % 128 == 0:
+                    q, sc = F.fp8_quantize_1x128(W[n])
+                    self.fp8_weights[W[n].data_ptr()] = (q, sc)
+                    total += q.numel() + sc.numel() * 4
+        return total
+
     def _grad_of(self, w: torch.Tensor) -> torch.Tensor:
         mg = getattr(w, "main_grad", None)
         return mg if mg is not None else torch.zeros_like(w, dtype=torch.float32)
@@ -235,10 +261,10 @@ class DecoderModel:
         if self.tp is not None:
             assert S is None, "tensor-parallel shards are forward-only"
             return self.mlp_tp(W, h2)
-        gu = F.gemm(h2, W["mlp.gate_up_proj.weight"])
+        gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
         if S is not None:
             S["gu"] = gu
-        return F.gemm(F.swiglu(gu), W["mlp.down_proj.weight"])
+        return self._lin(W, "mlp.down_proj.weight", F.swiglu(gu), S)
 
     def _mlp_bwd(self, W, g_d, h2, S: dict):
         if self.cfg.is_moe:

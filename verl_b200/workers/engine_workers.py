@@ -278,6 +278,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 g0 = me // tp * tp
                 self.rollout_tp_group = dist.new_group(pool_ranks[g0 : g0 + tp], use_local_synchronization=True)
             self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs * tp, tp_group=self.rollout_tp_group,
+                                         quantization=(rc.get("quantization") if tp == 1 else None),
                                          max_num_batched_tokens=rc.max_num_batched_tokens, max_model_len=max_len + 1,
                                          block_size=rc.block_size, gpu_memory_utilization=rc.gpu_memory_utilization,
                                          use_cuda_graph=not rc.enforce_eager, sync_interval=rc.sync_interval,

@@ -83,11 +83,13 @@ class RolloutEngine:
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
                  valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0,
-                 tp_group=None):
+                 tp_group=None, quantization: Optional[str] = None):
         """``tp_group``: process group of the ranks that serve the same requests tensor-parallel (each holds the
         full replicated weights and uses its shard of them in place; see ``TensorParallelShard``). All ranks of the
         group must be fed the same requests in the same order."""
         self.cfg = cfg
+        assert quantization in (None, "", "fp8"), f"unsupported rollout quantization: {quantization}"
+        self.quantization = quantization or None
         self.tp_group = tp_group
         self.tp_size = dist.get_world_size(tp_group) if tp_group is not None else 1
         self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
@@ -124,6 +126,8 @@ class RolloutEngine:
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         self._alloc_state()
         self.resume_kv_cache()
+        if self.quantization == "fp8":
+            self.model.quantize_linear_weights_fp8()
 
     def _make_row_linear(self):
         """Row-parallel linear summed over the tensor-parallel group. GPUs: one kernel (GEMM with the all-reduce in its
@@ -184,6 +188,9 @@ class RolloutEngine:
     def clear_kv_cache(self) -> None:
         """Forget all cached content (called after every weight update)."""
         assert not self.running
+        if self.quantization == "fp8":
+            self.model.quantize_linear_weights_fp8()  # the bf16 weights changed: refresh the e4m3 copies
+            self._graph = None
         if self.kv is not None:
             self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
 
@@ -338,7 +345,7 @@ class RolloutEngine:
             if tp is not None:
                 qkv = self.model.qkv_tp(W, h1)
             else:
-                qkv = F.gemm(h1, W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias"))
+                qkv = self.model._lin(W, "self_attn.qkv_proj.weight", h1)
             q = qkv[:, :Q].view(S, nh, hd)
             k = qkv[:, Q : Q + KV].view(S, nkv, hd)
             v = qkv[:, Q + KV :].view(S, nkv, hd)
@@ -354,7 +361,7 @@ class RolloutEngine:
             if tp is not None:
                 o = tp.row_linear(attn.reshape(S, Q), W["self_attn.o_proj.weight"][:, tp.rows(cfg.q_size)], None)
             else:
-                o = F.gemm(attn.reshape(S, Q), W["self_attn.o_proj.weight"])
+                o = self.model._lin(W, "self_attn.o_proj.weight", attn.reshape(S, Q))
             h2, x2, _ = F.rms_norm(o, W["post_attention_layernorm.weight"], cfg.rms_norm_eps, residual=x)
             a = self.model._mlp_fwd(W, h2, None)
             r = x2
