@@ -455,7 +455,12 @@ class RayPPOTrainer:
             gen_batch = gen_batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
             gen_batch = self._to_device(gen_batch)
             with marked_timer("gen", timing_raw, color="red"):
-                gen_out = self.actor_rollout_wg.generate_sequences(gen_batch)
+                from ...utils.skip import SkipManager
+
+                if cfg.get("skip") and not SkipManager.skip_instances and SkipManager.config is None:
+                    SkipManager.init(cfg)
+                SkipManager.set_step(self.global_steps)
+                gen_out = SkipManager.annotate("rollout")(lambda prompts: self.actor_rollout_wg.generate_sequences(prompts))(gen_batch)
                 timing_raw.update({f"gen/{k}": v for k, v in gen_out.meta_info.pop("timing", {}).items()})
                 gen_out.meta_info.pop("rollout_stats", None)
             if str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX"):
