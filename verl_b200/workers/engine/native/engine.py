@@ -300,7 +300,7 @@ class NativeEngine(BaseEngine):
                 dist.all_reduce(mg, group=self.group)
                 self.grad_shard.copy_(mg[sl]).div_(W)
         self.ctrl.zero_()
-        lr = lr_at_step(oc, self.sched_step)
+        lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
         self.opt_step_count += 1
         if self.device.type == "cuda":
             ops = native.ops()
@@ -345,7 +345,7 @@ class NativeEngine(BaseEngine):
         oc = self.optimizer_config
         ops = native.ops()
         use_mc = os.environ.get("VERL_B200_MULTIMEM", "0") == "1"
-        lr = lr_at_step(oc, self.sched_step)
+        lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
         self.opt_step_count += 1
         self._peer_barrier()
         self.ctrl.zero_()
