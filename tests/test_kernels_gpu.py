@@ -319,6 +319,30 @@ def test_model_gpu_matches_cpu(ops, name):
         assert rel(Pg.main_grad, P.main_grad) < 0.05
 
 
+def test_activation_offload_gives_identical_gradients(ops):
+    from verl_b200.models import DecoderModel, FlatParams, PackedBatch, get_preset
+    from verl_b200.utils.activation_offload import ActivationOffloader
+
+    cfg = get_preset("tiny-llama")
+    grads = []
+    for use in (False, True):
+        P = FlatParams(cfg, dtype=torch.bfloat16, device=DEV, with_main_grad=True)
+        P.init_weights(seed=1, std=0.05)
+        model = DecoderModel(cfg, P, recompute="full")
+        if use:
+            model.offloader = ActivationOffloader(DEV)
+        g = torch.Generator().manual_seed(0)
+        ids = torch.randint(3, cfg.vocab_size, (300,), generator=g).to(DEV)
+        labels = torch.randint(3, cfg.vocab_size, (300,), generator=g).to(DEV)
+        lp, ent = model.forward_logprobs(PackedBatch.from_lengths(ids, [120, 100, 80], device=DEV), labels, 1.0)
+        (-lp.sum()).backward()
+        torch.cuda.synchronize()
+        grads.append(P.main_grad.clone())
+        if use:
+            assert model.offloader.bytes_offloaded > 0
+    assert torch.equal(grads[0], grads[1])
+
+
 def test_bounded_wait_reports_status_instead_of_hanging(ops):
     """The status word is readable and clear after the tests above (no kernel wait ran out)."""
     assert int(ops.gemm_status()) == 0

@@ -15,6 +15,10 @@ def test_manual_backward_matches_autograd(name, recompute):
     P.init_weights(seed=1, std=0.05)
     model = DecoderModel(cfg, P, recompute=recompute)
     model.keep_layers_fn = lambda num_tokens: 1  # "auto": the last layer keeps its activations, the others recompute
+    if recompute == "full":
+        from verl_b200.utils.activation_offload import ActivationOffloader
+
+        model.offloader = ActivationOffloader("cpu")  # host device: handles pass tensors through
     lengths = [7, 12, 5]
     T = sum(lengths)
     ids = torch.randint(3, cfg.vocab_size, (T,))

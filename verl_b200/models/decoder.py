@@ -99,6 +99,7 @@ class DecoderModel:
         self.keep_layers_fn: Optional[Callable[[int], int]] = None
         self.tp: Optional[TensorParallelShard] = None  # set by the rollout engine; forward-only
         self.fp8_weights: Optional[dict] = None         # data_ptr of a bf16 weight -> (e4m3 copy, block scales)
+        self.offloader = None                           # ActivationOffloader: inputs of recomputed layers live on the host
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -506,7 +507,7 @@ class DecoderModel:
         keep_from = self._first_kept_layer(batch.num_tokens) if save else 0
         for i in range(cfg.num_hidden_layers):
             if save and i < keep_from:  # only the layer input is kept; the layer runs again in the backward pass
-                saved.append((a, r))
+                saved.append(self.offloader.offload(i, (a, r)) if self.offloader is not None else (a, r))
                 a, r = self._layer_fwd(i, a, r, batch, None)
             else:
                 S = {} if save else None
@@ -529,6 +530,11 @@ class DecoderModel:
         g_d = g_x2 = g
         for i in reversed(range(cfg.num_hidden_layers)):
             S = state["layers"][i]
+            if self.offloader is not None and not isinstance(S, (tuple, dict)):
+                nxt = state["layers"][i - 1] if i > 0 else None
+                if nxt is not None and not isinstance(nxt, (tuple, dict)):
+                    self.offloader.prefetch(nxt)  # the previous layer's input travels back while this layer computes
+                S = self.offloader.wait(S)
             if isinstance(S, tuple):
                 a, r = S
                 S = {}

@@ -136,6 +136,10 @@ class NativeEngine(BaseEngine):
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
+        if bool(getattr(ec, "enable_activation_offload", False)) and not self.forward_only:
+            from ....utils.activation_offload import ActivationOffloader
+
+            self.model.offloader = ActivationOffloader(self.device)
         self.shard_numel = self.params.numel // self.world
         self.shard_lo = self.rank * self.shard_numel
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
