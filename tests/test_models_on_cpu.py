@@ -76,3 +76,24 @@ def test_param_counts_match_known_sizes():
     assert abs(get_preset("qwen2.5-0.5b").num_parameters() / 1e9 - 0.494) < 0.01
     assert abs(get_preset("llama-3.1-8b").num_parameters() / 1e9 - 8.03) < 0.02
     assert abs(get_preset("qwen3-30b-a3b").num_parameters() / 1e9 - 30.5) < 0.3
+
+
+def test_lm_head_on_selected_positions_matches_full_head():
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    lengths = [9, 6]
+    T = sum(lengths)
+    ids, labels = torch.randint(3, cfg.vocab_size, (T,)), torch.randint(3, cfg.vocab_size, (T,))
+    pos = torch.tensor([2, 3, 4, 7, 11, 12])
+    w = torch.randn(len(pos))
+    grads = []
+    for use_pos in (True, False):
+        P = FlatParams(cfg, dtype=torch.float32, with_main_grad=True)
+        P.init_weights(seed=1, std=0.05)
+        model = DecoderModel(cfg, P, recompute="none")
+        lp, ent = model.forward_logprobs(PackedBatch.from_lengths(ids, lengths), labels, 1.0, positions=pos if use_pos else None)
+        if not use_pos:
+            lp, ent = lp[pos], ent[pos]
+        ((lp * w).sum() + 0.3 * ent.sum()).backward()
+        grads.append((lp.detach().clone(), P.main_grad.clone()))
+    assert torch.allclose(grads[0][0], grads[1][0], atol=1e-6) and torch.allclose(grads[0][1], grads[1][1], atol=1e-6)

@@ -552,15 +552,21 @@ class DecoderModel:
 
     # ------------------------------------------------------------------------------------ heads
     def forward_logprobs(self, batch: PackedBatch, labels: torch.Tensor, temperature: float = 1.0,
-                         need_grad: Optional[bool] = None):
-        """(log_probs, entropy) per packed position of ``labels`` (fp32 [T]); differentiable when grads are on."""
+                         need_grad: Optional[bool] = None, positions: Optional[torch.Tensor] = None):
+        """(log_probs, entropy) per packed position of ``labels`` (fp32 [T]); differentiable when grads are on.
+        With ``positions`` (int64, increasing) the LM head runs only on those packed positions (the ones whose next
+        token is a response token) and the outputs have ``len(positions)`` entries."""
         need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
         with torch.no_grad():
             hN, state = self._trunk_fwd(batch, save=need_grad)
-            lp, ent, lse = F.lmhead_logprob_entropy(hN, self.params.lm_head_weight, labels, temperature)
+            if positions is not None:
+                hS, labels = hN.index_select(0, positions), labels.index_select(0, positions)
+            else:
+                hS = hN
+            lp, ent, lse = F.lmhead_logprob_entropy(hS, self.params.lm_head_weight, labels, temperature)
         if not need_grad:
             return lp, ent
-        state.update(kind="lm", labels=labels, temperature=temperature, lse=lse, ent=ent)
+        state.update(kind="lm", labels=labels, temperature=temperature, lse=lse, ent=ent, positions=positions, hS=hS)
         return _Anchor.apply(self._anchor, self, state, lp, ent)
 
     def forward_values(self, batch: PackedBatch, need_grad: Optional[bool] = None) -> torch.Tensor:
@@ -590,8 +596,14 @@ class DecoderModel:
             if g_lp is None:
                 g_lp = torch.zeros_like(state["lse"])
             head = self.params.lm_head_weight
-            g_hN = F.lmhead_backward(hN, head, state["labels"], state["temperature"], state["lse"], state["ent"],
+            g_hS = F.lmhead_backward(state["hS"], head, state["labels"], state["temperature"], state["lse"], state["ent"],
                                      g_lp.float(), g_ent.float() if g_ent is not None else None, self._grad_of(head))
+            if state.get("positions") is not None:
+                g_hN = torch.zeros_like(hN)
+                g_hN.index_copy_(0, state["positions"], g_hS.to(hN.dtype))
+            else:
+                g_hN = g_hS
+            state["hS"] = None
         else:
             (g_v,) = grads
             wv = self.params["v_head.weight"]

@@ -267,11 +267,13 @@ class NativeEngine(BaseEngine):
     def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
         batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
                                                                   mb.get("position_ids"), R)
-        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad)
-        zero = torch.zeros((), dtype=lp.dtype, device=lp.device)
-        out = {"log_probs": torch.where(resp_valid, lp[resp_index], zero)}
+        # the LM head (a third of a 7B forward's head+tail work at vocabulary 152k) runs only where a response token is
+        # predicted: prompt positions never enter a loss or a returned log-prob
+        positions = resp_index[resp_valid]
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions)
+        out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
         if calc_entropy or need_grad:
-            out["entropy"] = torch.where(resp_valid, ent[resp_index], zero)
+            out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
         return out
 
     # ------------------------------------------------------------------------------------ optimizer
