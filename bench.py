@@ -48,7 +48,9 @@ def parse_args():
     p.add_argument("--max-num-seqs", type=int, default=320)
     p.add_argument("--no-recompute", action="store_true")
     p.add_argument("--skip-e2e", action="store_true", help="development only: skip the second (end-to-end) timing pass")
-    p.add_argument("--rollout-tp", type=int, default=0, help="rollout tensor-parallel size (0 = 2 when gpus >= 2 else 1)")
+    p.add_argument("--rollout-tp", type=int, default=0,
+                   help="rollout tensor-parallel size; 0 = 1: every GPU holds the full bf16 weights, and data-parallel rollout "
+                        "measured faster than TP=2 for this model (gen 32.5 s vs 41.1 s per step); 2 reproduces the TP=2 layout")
     return p.parse_args()
 
 
@@ -126,7 +128,7 @@ def build_config(args, world: int):
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
         f"actor_rollout_ref.rollout.max_num_seqs={min(args.max_num_seqs, args.prompts_per_gpu * args.n)}",
         "actor_rollout_ref.rollout.gpu_memory_utilization=0.45", "actor_rollout_ref.rollout.sync_interval=32",
-        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp or (2 if world >= 2 else 1)}",
+        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp or 1}",
         f"actor_rollout_ref.actor.ppo_mini_batch_size={gbs}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
         f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}",
         "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.kl_loss_coef=0.001",
