@@ -43,6 +43,10 @@ class ModelConfig:
     pad_token_id: Optional[int] = None
     initializer_range: float = 0.02
     extra: dict = field(default_factory=dict)
+    # model-parallel shard description (a full model has both ends and local = global expert count)
+    has_embedding: bool = True    # pipeline stage owns the token embedding
+    has_head: bool = True         # pipeline stage owns the final norm and the LM/value head
+    num_local_experts: int = 0    # expert-parallel shard: experts stored on this rank (0 = all)
 
     def __post_init__(self):
         if self.head_dim is None:
@@ -51,6 +55,24 @@ class ModelConfig:
             self.attention_bias = True
         if self.model_type in ("qwen3", "qwen3_moe"):
             self.qk_norm = True
+
+    def local_shard(self, tp: int = 1, num_layers: Optional[int] = None, has_embedding: bool = True, has_head: bool = True,
+                    ep: int = 1) -> "ModelConfig":
+        """Configuration of what ONE rank of a tensor x pipeline (x expert) parallel layout stores and computes: 1/tp of the
+        attention heads and of the MLP width (column-parallel QKV / gate-up, row-parallel O / down), ``num_layers``
+        consecutive layers, the embedding only on the first and the head only on the last stage, 1/ep of the experts."""
+        import dataclasses
+
+        assert self.num_attention_heads % tp == 0 and self.num_key_value_heads % tp == 0, "tp must divide the head counts"
+        assert self.is_moe or self.intermediate_size % tp == 0
+        c = dataclasses.replace(self, num_attention_heads=self.num_attention_heads // tp,
+                                num_key_value_heads=self.num_key_value_heads // tp,
+                                intermediate_size=self.intermediate_size // tp if not self.is_moe else self.intermediate_size,
+                                num_hidden_layers=self.num_hidden_layers if num_layers is None else num_layers,
+                                head_dim=self.head_dim, has_embedding=has_embedding, has_head=has_head,
+                                num_local_experts=(self.num_experts // ep if self.is_moe and ep > 1 else 0),
+                                tie_word_embeddings=self.tie_word_embeddings and has_embedding and has_head, extra=dict(self.extra))
+        return c
 
     # ------------------------------------------------------------------ derived sizes
     @property

@@ -100,6 +100,10 @@ class DecoderModel:
         self.tp: Optional[TensorParallelShard] = None  # set by the rollout engine; forward-only
         self.fp8_weights: Optional[dict] = None         # data_ptr of a bf16 weight -> (e4m3 copy, block scales)
         self.offloader = None                           # ActivationOffloader: inputs of recomputed layers live on the host
+        # tensor-parallel training (this model is one shard: 1/tp of heads and MLP width): ``reduce(x)`` must sum x over the
+        # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
+        # gradients of the column-parallel qkv_proj / gate_up_proj.
+        self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -164,7 +168,8 @@ class DecoderModel:
             S.update(qkv=qkv, attn=attn2, lse=lse)
         if self.tp is not None:
             return self.tp.row_linear(attn2, W["self_attn.o_proj.weight"][:, self.tp.rows(cfg.q_size)], None)
-        return self._lin(W, "self_attn.o_proj.weight", attn2, S)
+        o = self._lin(W, "self_attn.o_proj.weight", attn2, S)
+        return self.tp_reduce(o) if self.tp_reduce is not None else o
 
     def qkv_tp(self, W, h1: torch.Tensor) -> torch.Tensor:
         """[T, (Q + 2 KV) / size]: this rank's q | k | v columns."""
@@ -220,6 +225,8 @@ class DecoderModel:
             gq.copy_(dqp.view(T, nh, hd))
             gk.copy_(dkp.view(T, nkv, hd))
         g_h1 = F.gemm(g_qkv, W["self_attn.qkv_proj.weight"], b_mn=True)
+        if self.tp_reduce is not None:
+            g_h1 = self.tp_reduce(g_h1)
         self._wgrad(W["self_attn.qkv_proj.weight"], g_qkv, h1)
         b = W.get("self_attn.qkv_proj.bias")
         if b is not None and getattr(b, "main_grad", None) is not None:
@@ -265,7 +272,8 @@ class DecoderModel:
         gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
         if S is not None:
             S["gu"] = gu
-        return self._lin(W, "mlp.down_proj.weight", F.swiglu(gu), S)
+        d = self._lin(W, "mlp.down_proj.weight", F.swiglu(gu), S)
+        return self.tp_reduce(d) if self.tp_reduce is not None else d
 
     def _mlp_bwd(self, W, g_d, h2, S: dict):
         if self.cfg.is_moe:
@@ -276,6 +284,8 @@ class DecoderModel:
         self._wgrad(W["mlp.down_proj.weight"], g_d, act)
         g_gu = F.swiglu_bwd(g_act, gu)
         g_h2 = F.gemm(g_gu, W["mlp.gate_up_proj.weight"], b_mn=True)
+        if self.tp_reduce is not None:
+            g_h2 = self.tp_reduce(g_h2)
         self._wgrad(W["mlp.gate_up_proj.weight"], g_gu, h2)
         return g_h2
 
@@ -496,12 +506,16 @@ class DecoderModel:
         per_tok = (c.q_size + 2 * c.kv_size) + c.q_size + 2 * inter + 2 * c.hidden_size
         return int(num_tokens) * per_tok * self.params.flat.element_size() + int(num_tokens) * (c.num_attention_heads + 2) * 4
 
-    def _trunk_fwd(self, batch: PackedBatch, save: bool):
+    def _trunk_fwd(self, batch: PackedBatch, save: bool, stage_input: Optional[torch.Tensor] = None):
         cfg = self.cfg
         self._ensure_rope(batch.max_seqlen + 1)
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(-1, "forward")
-        a = F.embedding(batch.input_ids, self.params["embed_tokens.weight"])
+        if cfg.has_embedding:
+            a = F.embedding(batch.input_ids, self.params["embed_tokens.weight"])
+        else:
+            a = stage_input  # hidden stream handed over by the previous pipeline stage
+            assert a is not None, "a pipeline stage without embedding needs stage_input"
         r = None
         saved: list[Any] = []
         keep_from = self._first_kept_layer(batch.num_tokens) if save else 0
@@ -516,15 +530,24 @@ class DecoderModel:
                     saved.append(S)
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(cfg.num_hidden_layers, "forward")
+        if not cfg.has_head:
+            # stage boundary: the next stage continues from the summed stream (its first norm sees residual None)
+            out = a if r is None else a + r
+            return out, (dict(batch=batch, layers=saved, boundary=True) if save else None)
         hN, xN, rstdN = F.rms_norm(a, self.params["norm.weight"], cfg.rms_norm_eps, residual=r)
         state = dict(batch=batch, layers=saved, xN=xN, rstdN=rstdN, hN=hN) if save else None
         return hN, state
 
-    def _trunk_bwd(self, state: dict, g_hN: torch.Tensor) -> None:
+    def _trunk_bwd(self, state: dict, g_hN: torch.Tensor) -> Optional[torch.Tensor]:
+        """Backward through this model's layers. ``g_hN``: gradient of the head input (last stage) or of the boundary
+        stream (other stages). Returns the gradient of ``stage_input`` when the model has no embedding, else None."""
         cfg = self.cfg
         batch = state["batch"]
-        wn = self.params["norm.weight"]
-        g = F.rms_norm_bwd(g_hN, state["xN"], wn, state["rstdN"], None, self._grad_of(wn), True)
+        if state.get("boundary"):
+            g = g_hN
+        else:
+            wn = self.params["norm.weight"]
+            g = F.rms_norm_bwd(g_hN, state["xN"], wn, state["rstdN"], None, self._grad_of(wn), True)
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(cfg.num_hidden_layers)
         g_d = g_x2 = g
@@ -542,6 +565,10 @@ class DecoderModel:
             g = self._layer_bwd(i, g_d, g_x2, batch, S)
             state["layers"][i] = None
             g_d = g_x2 = g
+        if not cfg.has_embedding:
+            if self.post_layer_backward_hook is not None:
+                self.post_layer_backward_hook(-1)
+            return g
         emb = self.params["embed_tokens.weight"]
         if getattr(emb, "main_grad", None) is not None:
             if self.pre_layer_hook is not None:
@@ -552,13 +579,14 @@ class DecoderModel:
 
     # ------------------------------------------------------------------------------------ heads
     def forward_logprobs(self, batch: PackedBatch, labels: torch.Tensor, temperature: float = 1.0,
-                         need_grad: Optional[bool] = None, positions: Optional[torch.Tensor] = None):
+                         need_grad: Optional[bool] = None, positions: Optional[torch.Tensor] = None,
+                         stage_input: Optional[torch.Tensor] = None):
         """(log_probs, entropy) per packed position of ``labels`` (fp32 [T]); differentiable when grads are on.
         With ``positions`` (int64, increasing) the LM head runs only on those packed positions (the ones whose next
         token is a response token) and the outputs have ``len(positions)`` entries."""
         need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
         with torch.no_grad():
-            hN, state = self._trunk_fwd(batch, save=need_grad)
+            hN, state = self._trunk_fwd(batch, save=need_grad, stage_input=stage_input)
             if positions is not None:
                 hS, labels = hN.index_select(0, positions), labels.index_select(0, positions)
             else:
@@ -567,17 +595,20 @@ class DecoderModel:
         if not need_grad:
             return lp, ent
         state.update(kind="lm", labels=labels, temperature=temperature, lse=lse, ent=ent, positions=positions, hS=hS)
+        self.last_state = state  # after backward: last_state["g_input"] is the gradient of stage_input
         return _Anchor.apply(self._anchor, self, state, lp, ent)
 
-    def forward_values(self, batch: PackedBatch, need_grad: Optional[bool] = None) -> torch.Tensor:
+    def forward_values(self, batch: PackedBatch, need_grad: Optional[bool] = None,
+                       stage_input: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Scalar value per packed position (fp32 [T]) from the value head."""
         need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
         with torch.no_grad():
-            hN, state = self._trunk_fwd(batch, save=need_grad)
+            hN, state = self._trunk_fwd(batch, save=need_grad, stage_input=stage_input)
             vals = F.gemm(hN, self.params["v_head.weight"])[:, 0].float()
         if not need_grad:
             return vals
         state.update(kind="value")
+        self.last_state = state
         return _Anchor.apply(self._anchor, self, state, vals)[0]
 
     def forward_hidden(self, batch: PackedBatch) -> torch.Tensor:
@@ -587,6 +618,18 @@ class DecoderModel:
     def forward_logits(self, batch: PackedBatch) -> torch.Tensor:
         with torch.no_grad():
             return F.gemm(self._trunk_fwd(batch, save=False)[0], self.params.lm_head_weight)
+
+    # ------------------------------------------------------------------------------------ pipeline stages
+    @torch.no_grad()
+    def forward_stage(self, batch: PackedBatch, stage_input: Optional[torch.Tensor] = None, save: bool = True):
+        """A stage without head: returns (boundary stream [T, H], state for ``backward_stage``)."""
+        assert not self.cfg.has_head
+        return self._trunk_fwd(batch, save=save, stage_input=stage_input)
+
+    @torch.no_grad()
+    def backward_stage(self, state: dict, g_out: torch.Tensor) -> Optional[torch.Tensor]:
+        """Backward of ``forward_stage``; returns the gradient of its ``stage_input`` (None on the first stage)."""
+        return self._trunk_bwd(state, g_out)
 
     @torch.no_grad()
     def _backward(self, state: dict, grads) -> None:
@@ -604,6 +647,8 @@ class DecoderModel:
             else:
                 g_hN = g_hS
             state["hS"] = None
+            state["g_input"] = self._trunk_bwd(state, g_hN)  # gradient of stage_input (pipeline stages after the first)
+            return
         else:
             (g_v,) = grads
             wv = self.params["v_head.weight"]
@@ -611,4 +656,4 @@ class DecoderModel:
             dl[:, 0] = g_v.to(hN.dtype)
             g_hN = F.gemm(dl, wv, b_mn=True)
             self._wgrad(wv, dl, hN)
-        self._trunk_bwd(state, g_hN)
+        state["g_input"] = self._trunk_bwd(state, g_hN)

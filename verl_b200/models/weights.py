@@ -43,7 +43,9 @@ class ParamSpec:
 def build_param_specs(cfg: ModelConfig, value_head: bool = False) -> list[ParamSpec]:
     h = cfg.hidden_size
     L = cfg.num_hidden_layers
-    specs = [ParamSpec("embed_tokens.weight", (cfg.vocab_size, h), "normal", True, -1)]
+    specs = []
+    if cfg.has_embedding:
+        specs.append(ParamSpec("embed_tokens.weight", (cfg.vocab_size, h), "normal", True, -1))
     for i in range(L):
         p = f"layers.{i}."
         specs.append(ParamSpec(p + "input_layernorm.weight", (h,), "ones", False, i))
@@ -57,12 +59,15 @@ def build_param_specs(cfg: ModelConfig, value_head: bool = False) -> list[ParamS
         specs.append(ParamSpec(p + "post_attention_layernorm.weight", (h,), "ones", False, i))
         if cfg.is_moe:
             E, ie = cfg.num_experts, cfg.moe_intermediate_size
+            El = cfg.num_local_experts or E  # expert-parallel shards store their own experts only; the router is replicated
             specs.append(ParamSpec(p + "mlp.gate.weight", (E, h), "normal", True, i))
-            specs.append(ParamSpec(p + "mlp.experts.gate_up_proj", (E, 2 * ie, h), "normal", True, i))
-            specs.append(ParamSpec(p + "mlp.experts.down_proj", (E, h, ie), "normal", True, i))
+            specs.append(ParamSpec(p + "mlp.experts.gate_up_proj", (El, 2 * ie, h), "normal", True, i))
+            specs.append(ParamSpec(p + "mlp.experts.down_proj", (El, h, ie), "normal", True, i))
         else:
             specs.append(ParamSpec(p + "mlp.gate_up_proj.weight", (2 * cfg.intermediate_size, h), "normal", True, i))
             specs.append(ParamSpec(p + "mlp.down_proj.weight", (h, cfg.intermediate_size), "normal", True, i))
+    if not cfg.has_head:
+        return specs
     specs.append(ParamSpec("norm.weight", (h,), "ones", False, L))
     if value_head:
         # scalar head stored with 8 rows (row 0 is the value) so the GEMM's N % 8 == 0 rule holds

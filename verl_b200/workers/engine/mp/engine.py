@@ -1,0 +1,268 @@
+"""Tensor x pipeline x data parallel training engine (``strategy=megatron``).
+
+Every rank trains the local shard model of ``ModelParallelTopology.local_config`` with the native engine's machinery
+(flat buffers, hand-written backward, sharded optimizer over the data-parallel group). What this class adds:
+
+* the tensor-parallel all-reduces inside the layer (``DecoderModel.tp_reduce``);
+* the pipeline schedule: all micro-batches flow forward through the stages (hidden stream [T, H] sent with
+  point-to-point messages), the last stage evaluates the loss, then the gradients flow back in the same order. Model
+  outputs and the loss are broadcast from the last stage so that every rank of a replica returns the same result;
+* a gradient norm that counts tensor-parallel-replicated parameters once and sums over the model-parallel group;
+* weights initialised / loaded in the full HuggingFace layout and cut into shards with ``ShardMap`` (identical on every
+  data-parallel replica), and the reverse gather for checkpoints and for handing weights to a rollout engine.
+
+Parity target: ``verl/workers/engine/megatron/transformer_impl.py`` (engine class, ``forward_backward_batch`` with the
+pipeline schedule, ``get_per_tensor_param`` export) and ``verl/utils/megatron_utils.py``.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Callable, Generator, Optional
+
+import torch
+import torch.distributed as dist
+
+from ....models.weights import FlatParams
+from ....parallel.model_parallel import ModelParallelTopology, build_shard_map, copy_full_to_local, copy_local_to_full
+from ....utils.distributed import get_data_parallel_group, set_data_parallel_group
+from ..base import EngineRegistry
+from ..native.engine import NativeEngine, pack_padded_batch
+
+__all__ = ["ModelParallelEngine", "ModelParallelEngineWithLMHead", "ModelParallelEngineWithValueHead"]
+
+_TOPOLOGIES: dict = {}
+
+
+def get_topology(tp: int, pp: int) -> ModelParallelTopology:
+    """One topology (set of process groups) per (tp, pp) and process: actor, critic and reference engines share it."""
+    key = (tp, pp)
+    if key not in _TOPOLOGIES:
+        _TOPOLOGIES[key] = ModelParallelTopology(tp, pp)
+    return _TOPOLOGIES[key]
+
+
+class ModelParallelEngine(NativeEngine):
+    def __init__(self, model_config, engine_config, optimizer_config=None, checkpoint_config=None, **kwargs):
+        super().__init__(model_config, engine_config, optimizer_config, checkpoint_config, **kwargs)
+        g = lambda k, d: int(getattr(engine_config, k, None) or d)
+        self.tp_size = g("tensor_model_parallel_size", 1)
+        self.pp_size = g("pipeline_model_parallel_size", 1)
+        self.full_arch = self.arch
+
+    # ------------------------------------------------------------------------------------ setup
+    def initialize(self) -> None:
+        if self._initialized:
+            return
+        self.topo = get_topology(self.tp_size, self.pp_size)
+        self.arch = self.topo.local_config(self.full_arch)
+        self.maps = build_shard_map(self.full_arch, self.topo, self.value_head)
+        outer = get_data_parallel_group()
+        set_data_parallel_group(self.topo.dp_group)
+        try:
+            object.__setattr__(self.engine_config, "fused_comm", False) if hasattr(self.engine_config, "fused_comm") else None
+            super().initialize()
+        finally:
+            set_data_parallel_group(outer)
+        if self.topo.tp > 1:
+            grp = self.topo.tp_group
+
+            def reduce(x: torch.Tensor) -> torch.Tensor:
+                dist.all_reduce(x, group=grp)
+                return x
+
+            self.model.tp_reduce = reduce
+        # replicated-parameter mask for the gradient norm (embedding, norms, head, biases of row-parallel layers)
+        self._rep_ranges = [(self.params.offsets[m.local_name], self.params.views[m.local_name].numel())
+                            for m in self.maps if m.kind == "rep"]
+
+    def _load_or_init(self, seed: int) -> None:
+        """Build (or load) the full model on the host with the same seed everywhere and keep this rank's shard."""
+        mc = self.model_config
+        path = getattr(mc, "local_path", None) or getattr(mc, "path", None)
+        load = bool(getattr(mc, "load_weights", True)) and path and os.path.isdir(str(path))
+        full = FlatParams(self.full_arch, dtype=torch.float32 if self.dtype == torch.float32 else torch.bfloat16, device="cpu",
+                          value_head=self.value_head)
+        if load:
+            from ....utils.model import load_hf_weights_into
+
+            load_hf_weights_into(full, path)
+        else:
+            full.init_weights(seed=seed)
+        copy_full_to_local(full, self.params, self.maps, self.topo.tp, self.topo.tp_rank)
+        del full
+
+    # ------------------------------------------------------------------------------------ topology facts for the worker
+    def get_data_parallel_size(self) -> int:
+        return self.topo.dp
+
+    def get_data_parallel_rank(self) -> int:
+        return self.topo.dp_rank
+
+    def is_collection_rank(self) -> bool:
+        """The rank of a replica whose outputs the controller keeps (all ranks return identical outputs)."""
+        return self.topo.tp_rank == 0 and self.topo.is_last_stage
+
+    # ------------------------------------------------------------------------------------ pipeline schedule
+    def _stage_recv(self, T: int) -> torch.Tensor:
+        x = torch.empty(T, self.full_arch.hidden_size, dtype=self.dtype, device=self.device)
+        dist.recv(x, src=self.topo.prev_rank)
+        return x
+
+    def _run_micro_batches(self, mbs: list[dict], R: int, temperature: float, calc_entropy: bool, loss_function, forward_only: bool):
+        topo = self.topo
+        if topo.pp == 1:
+            return super()._run_micro_batches(mbs, R, temperature, calc_entropy, loss_function, forward_only)
+        need_grad = not forward_only
+        outs: dict[str, list] = {}
+        rows: list[int] = []
+        losses, metrics = [], {}
+        pending = []  # per micro-batch: what the backward pass needs
+        # ---- all forwards
+        for mb in mbs:
+            batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R)
+            T = batch.num_tokens
+            x_in = None if topo.is_first_stage else self._stage_recv(T)
+            rows.extend(mb["_rows"])
+            if not topo.is_last_stage:
+                x_out, st = self.model.forward_stage(batch, x_in, save=need_grad)
+                dist.send(x_out.contiguous(), dst=topo.next_rank)
+                pending.append((st, None, T))
+                out = None
+            else:
+                out = self._head_outputs(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in)
+                st = getattr(self.model, "last_state", None) if need_grad else None
+                loss = None
+                if loss_function is not None:
+                    loss, m = loss_function(model_output=out, data=mb, dp_group=None)
+                    losses.append(loss.detach())
+                    for k, v in m.items():
+                        metrics.setdefault(k, []).append(v)
+                pending.append((st, loss, T))
+            # every stage returns the outputs of the last stage
+            out = self._broadcast_outputs(out, resp_valid.shape, calc_entropy or need_grad)
+            for k, v in out.items():
+                outs.setdefault(k, []).append(v.detach())
+        # ---- all backwards, same order
+        if need_grad and loss_function is not None:
+            for st, loss, T in pending:
+                if topo.is_last_stage:
+                    loss.backward()
+                    g_in = st.get("g_input")
+                else:
+                    g_out = torch.empty(T, self.full_arch.hidden_size, dtype=self.dtype, device=self.device)
+                    dist.recv(g_out, src=topo.next_rank)
+                    g_in = self.model.backward_stage(st, g_out)
+                if not topo.is_first_stage:
+                    dist.send(g_in.contiguous(), dst=topo.prev_rank)
+        # the loss and its metrics live on the last stage: share them inside the pipeline group
+        losses, metrics = self._broadcast_loss(losses, metrics, len(mbs), loss_function is not None)
+        return outs, rows, losses, metrics
+
+    def _head_outputs(self, batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in) -> dict:
+        positions = resp_index[resp_valid]
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions, stage_input=x_in)
+        out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
+        if calc_entropy or need_grad:
+            out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
+        return out
+
+    def _broadcast_outputs(self, out: Optional[dict], shape, with_entropy: bool) -> dict:
+        keys = ["log_probs"] + (["entropy"] if with_entropy else [])
+        res = {}
+        for k in keys:
+            t = out[k].detach().float().contiguous() if out is not None else torch.empty(shape, dtype=torch.float32, device=self.device)
+            dist.broadcast(t, src=self.topo.last_stage_rank, group=self.topo.pp_group)
+            res[k] = out[k] if out is not None else t
+        return res
+
+    def _broadcast_loss(self, losses: list, metrics: dict, n_mb: int, has_loss: bool):
+        if not has_loss:
+            return losses, metrics
+        box = [(torch.stack(losses).cpu(), metrics) if self.topo.is_last_stage else None]
+        dist.broadcast_object_list(box, src=self.topo.last_stage_rank, group=self.topo.pp_group)
+        l, m = box[0]
+        return ([x.to(self.device) for x in l] if not self.topo.is_last_stage else losses), m
+
+    def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
+        assert self.topo.pp == 1
+        return super()._forward_micro(mb, R, temperature, calc_entropy, need_grad)
+
+    # ------------------------------------------------------------------------------------ optimizer
+    def _global_sumsq_correction(self) -> None:
+        """``ctrl[0]`` holds the sum of squares of this rank's gradient shard over its DP group. Turn it into the model's
+        global value: replicated tensors are counted on tensor-parallel rank 0 only, then summed over TP x PP."""
+        if self.topo.tp * self.topo.pp == 1:
+            return
+        if self.topo.tp > 1 and self.topo.tp_rank != 0:
+            sl_lo, sl_hi = self.shard_lo, self.shard_lo + self.shard_numel
+            dup = torch.zeros((), dtype=torch.float32, device=self.device)
+            for off, n in self._rep_ranges:
+                a, b = max(off, sl_lo), min(off + n, sl_hi)
+                if a < b:
+                    dup += self.grad_shard[a - sl_lo : b - sl_lo].float().pow(2).sum()
+            dist.all_reduce(dup, group=self.topo.dp_group) if self.topo.dp > 1 else None
+            self.ctrl[0] -= dup
+        dist.all_reduce(self.ctrl[:1], group=self.topo.mp_group)
+
+    # ------------------------------------------------------------------------------------ weights out
+    def gather_full_params(self, dtype=None) -> FlatParams:
+        """The full model assembled on every rank of the replica (host of the train -> rollout reshard and of merged
+        checkpoints): each rank writes its shard into a zeroed full-layout buffer, the buffers are summed over the
+        model-parallel group, replicated tensors are divided by their multiplicity."""
+        dtype = dtype or self.dtype
+        full = FlatParams(self.full_arch, dtype=torch.float32, device=self.device, value_head=self.value_head)
+        copy_local_to_full(self.params, full, self.maps, self.topo.tp, self.topo.tp_rank)
+        if self.topo.mp_group is not None:
+            if self.topo.tp > 1 and self.topo.tp_rank != 0:  # replicated tensors are contributed by tp rank 0 only
+                for m in self.maps:
+                    if m.kind == "rep" and m.full_name in full.views:
+                        full.views[m.full_name].zero_()
+            dist.all_reduce(full.flat, group=self.topo.mp_group)
+        if dtype != torch.float32:
+            out = FlatParams(self.full_arch, dtype=dtype, device=self.device, value_head=self.value_head)
+            out.flat.copy_(full.flat.to(dtype))
+            return out
+        return full
+
+    def get_per_tensor_param(self, **kwargs) -> Generator[tuple[str, torch.Tensor], None, None]:
+        full = self.gather_full_params()
+        yield from full.hf_views()
+
+    def local_named_tensors(self):
+        """(full-model name of the shard, local tensor) pairs: what the model-parallel checkpoint layout stores."""
+        for m in self.maps:
+            yield m.full_name, self.params.views[m.local_name]
+
+    def load_local_named_tensors(self, tensors: dict) -> None:
+        for m in self.maps:
+            if m.full_name in tensors:
+                self.params.views[m.local_name].copy_(tensors[m.full_name].to(self.dtype))
+
+
+@EngineRegistry.register(model_type="language_model", backend=["megatron", "mp"], device=["cuda", "cpu"])
+class ModelParallelEngineWithLMHead(ModelParallelEngine):
+    value_head = False
+
+
+@EngineRegistry.register(model_type="value_model", backend=["megatron", "mp"], device=["cuda", "cpu"])
+class ModelParallelEngineWithValueHead(ModelParallelEngine):
+    """Critic: the last stage ends in a scalar head; ``model_output`` carries ``values`` [b, R]."""
+
+    value_head = True
+
+    def _head_outputs(self, batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in) -> dict:
+        vals = self.model.forward_values(batch, need_grad=need_grad, stage_input=x_in)
+        zero = torch.zeros((), dtype=vals.dtype, device=vals.device)
+        return {"values": torch.where(resp_valid, vals[resp_index], zero)}
+
+    def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
+        batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R)
+        return self._head_outputs(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, None)
+
+    def _broadcast_outputs(self, out, shape, with_entropy: bool) -> dict:
+        t = out["values"].detach().float().contiguous() if out is not None else torch.empty(shape, dtype=torch.float32, device=self.device)
+        dist.broadcast(t, src=self.topo.last_stage_rank, group=self.topo.pp_group)
+        return {"values": out["values"] if out is not None else t}
+
+

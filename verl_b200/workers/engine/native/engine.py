@@ -241,6 +241,17 @@ class NativeEngine(BaseEngine):
             data["global_batch_info"] = dict(dp_size=self.world, batch_num_tokens=tok, global_batch_size=seqs,
                                              loss_scale_factor=data.get("loss_scale_factor"))
         mbs = self._micro_batches(data, forward_only)
+        outs, rows, losses, metrics = self._run_micro_batches(mbs, R, temperature, calc_entropy, loss_function, forward_only)
+        inv = torch.empty(n, dtype=torch.int64, device=self.device)
+        inv[torch.tensor(rows, dtype=torch.int64, device=self.device)] = torch.arange(n, device=self.device)
+        model_output = {k: torch.cat(v, 0)[inv] for k, v in outs.items()}
+        result = {"model_output": model_output, "metrics": metrics}
+        if losses:
+            result["loss"] = torch.stack(losses).sum()
+        return result
+
+    def _run_micro_batches(self, mbs: list[dict], R: int, temperature: float, calc_entropy: bool, loss_function, forward_only: bool):
+        """Forward (+ loss + backward) of every micro-batch; model-parallel engines override this with their schedule."""
         outs: dict[str, list] = {}
         rows: list[int] = []
         losses, metrics = [], {}
@@ -256,13 +267,7 @@ class NativeEngine(BaseEngine):
                     metrics.setdefault(k, []).append(v)
             for k, v in out.items():
                 outs.setdefault(k, []).append(v.detach())
-        inv = torch.empty(n, dtype=torch.int64, device=self.device)
-        inv[torch.tensor(rows, dtype=torch.int64, device=self.device)] = torch.arange(n, device=self.device)
-        model_output = {k: torch.cat(v, 0)[inv] for k, v in outs.items()}
-        result = {"model_output": model_output, "metrics": metrics}
-        if losses:
-            result["loss"] = torch.stack(losses).sum()
-        return result
+        return outs, rows, losses, metrics
 
     def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
         batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
@@ -281,6 +286,11 @@ class NativeEngine(BaseEngine):
         self.params.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+
+    def _global_sumsq_correction(self) -> None:
+        """Hook for model-parallel engines: ``ctrl[0]`` (sum of squared gradients over the data-parallel group) becomes
+        the sum over the whole model."""
+        return None
 
     def optimizer_zero_grad(self) -> None:
         if self.forward_only:
@@ -313,6 +323,7 @@ class NativeEngine(BaseEngine):
             ops.sumsq_(self.grad_shard, self.ctrl)
             if W > 1:
                 dist.all_reduce(self.ctrl[:1], group=self.group)
+            self._global_sumsq_correction()
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
             ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.params.flat[sl], self.ctrl,
                        lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
@@ -322,6 +333,9 @@ class NativeEngine(BaseEngine):
             ss = self.grad_shard.double().pow(2).sum()
             if W > 1:
                 dist.all_reduce(ss, group=self.group)
+            self.ctrl[0] = ss.float()
+            self._global_sumsq_correction()
+            ss = self.ctrl[0].double()
             norm = ss.sqrt().float()
             if torch.isfinite(norm):
                 coef = min(1.0, float(oc.clip_grad) / (float(norm) + 1e-6)) if oc.clip_grad and oc.clip_grad > 0 else 1.0
