@@ -166,8 +166,19 @@ class RayPPOTrainer:
             from ...utils.distributed import get_data_parallel_group
 
             g = get_data_parallel_group()
+            if g is None:
+                mp = self._model_parallel_size()
+                if mp > 1:  # before the workers exist: replicas are blocks of tp*pp consecutive ranks
+                    return dist.get_rank() // mp, dist.get_world_size() // mp
             return dist.get_rank(g), dist.get_world_size(g)
         return 0, 1
+
+    def _model_parallel_size(self) -> int:
+        a = self.config.actor_rollout_ref.actor
+        if str(a.get("strategy", "fsdp")) != "megatron":
+            return 1
+        m = a.get("megatron") or {}
+        return int(m.get("tensor_model_parallel_size", 1) or 1) * int(m.get("pipeline_model_parallel_size", 1) or 1)
 
     def _create_dataloader(self, train_dataset, val_dataset, collate_fn, train_sampler) -> None:
         from ...utils.dataset.rl_dataset import collate_fn as default_collate

@@ -250,7 +250,9 @@ def load_config(config_dir: str, config_name: str, overrides: Optional[Iterable[
     rest = []
     for ov in overrides:
         k, sep, v = ov.partition("=")
-        if sep and "." not in k and os.path.isdir(os.path.join(config_dir, k.split("@")[0].lstrip("+"))):
+        group = k.split("@")[0].lstrip("+")  # "actor@actor_rollout_ref.actor=megatron_actor": group "actor" packaged at a path
+        if sep and "." not in group and os.path.isdir(os.path.join(config_dir, group)) and \
+                os.path.exists(os.path.join(config_dir, group, v + ".yaml")):
             choices[k.lstrip("+")] = v
         else:
             rest.append(ov)

@@ -153,6 +153,13 @@ class TrainingWorker(Worker, DistProfilerExtension):
         self.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
 
 
+def _dp_world(engine=None) -> int:
+    """Number of data-parallel replicas that split a global batch (model-parallel engines: world / (tp * pp))."""
+    if engine is not None and hasattr(engine, "get_data_parallel_size") and getattr(engine, "_initialized", False):
+        return int(engine.get_data_parallel_size())
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
 class CriticWorker(TrainingWorker):
     """Value model worker: ``compute_values`` and ``update_critic`` on top of :class:`TrainingWorker`."""
 
@@ -160,8 +167,13 @@ class CriticWorker(TrainingWorker):
         if not isinstance(config, TrainingWorkerConfig):
             critic = config
             mc = omega_conf_to_dataclass(critic.get("model"), HFModelConfig) if not isinstance(critic.get("model"), HFModelConfig) else critic.model
-            ec = critic.get("fsdp_config") or critic.get("engine") or FSDPEngineConfig()
-            ec = omega_conf_to_dataclass(ec, FSDPEngineConfig)
+            if str(critic.get("strategy", "fsdp")) == "megatron":
+                from .config import McoreEngineConfig
+
+                ec = omega_conf_to_dataclass(critic.get("megatron") or critic.get("engine") or McoreEngineConfig(), McoreEngineConfig)
+            else:
+                ec = critic.get("fsdp_config") or critic.get("engine") or FSDPEngineConfig()
+                ec = omega_conf_to_dataclass(ec, FSDPEngineConfig)
             object.__setattr__(ec, "micro_batch_size_per_gpu", critic.get("ppo_micro_batch_size_per_gpu"))
             object.__setattr__(ec, "infer_micro_batch_size_per_gpu", critic.get("forward_micro_batch_size_per_gpu") or critic.get("ppo_micro_batch_size_per_gpu"))
             self.critic_config = critic
@@ -182,7 +194,7 @@ class CriticWorker(TrainingWorker):
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("train"))
     def update_critic(self, data: DataProto) -> DataProto:
         cc = getattr(self, "critic_config", None)
-        ws = dist.get_world_size() if dist.is_initialized() else 1
+        ws = _dp_world(self.engine)
         if cc is not None:
             data.meta_info.setdefault("mini_batch_size", max(1, cc.ppo_mini_batch_size * cc.get("rollout_n", 1) // ws))
             data.meta_info.setdefault("epochs", cc.ppo_epochs)
@@ -218,7 +230,14 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         mc = self._model_config()
         ws = dist.get_world_size() if dist.is_initialized() else 1
         if self._is_actor:
-            ac = cfg.actor if isinstance(cfg.actor, ActorConfig) else omega_conf_to_dataclass(cfg.actor, FSDPActorConfig)
+            if isinstance(cfg.actor, ActorConfig):
+                ac = cfg.actor
+            elif str(cfg.actor.get("strategy", "fsdp")) == "megatron":
+                from .config import McoreActorConfig
+
+                ac = omega_conf_to_dataclass(cfg.actor, McoreActorConfig)
+            else:
+                ac = omega_conf_to_dataclass(cfg.actor, FSDPActorConfig)
             self.actor_config = ac
             ec = ac.engine if ac.engine is not None else FSDPEngineConfig()
             for k_src, k_dst in (("ppo_micro_batch_size_per_gpu", "micro_batch_size_per_gpu"),
@@ -247,7 +266,16 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 object.__setattr__(rec, "use_dynamic_bsz", bool(rcfg.get("log_prob_use_dynamic_bsz", False)))
                 if rcfg.get("log_prob_max_token_len_per_gpu"):
                     object.__setattr__(rec, "infer_max_token_len_per_gpu", rcfg.get("log_prob_max_token_len_per_gpu"))
-            self.ref = EngineRegistry.new("language_model", "fsdp", model_config=mc, engine_config=rec, optimizer_config=None)
+            if self.actor is not None and getattr(self.actor, "topo", None) is not None:  # same model-parallel layout as the actor
+                from .config import McoreEngineConfig
+
+                mrec = McoreEngineConfig(tensor_model_parallel_size=self.actor.tp_size, pipeline_model_parallel_size=self.actor.pp_size,
+                                         forward_only=True)
+                for k in ("infer_micro_batch_size_per_gpu", "use_dynamic_bsz", "infer_max_token_len_per_gpu"):
+                    object.__setattr__(mrec, k, getattr(rec, k))
+                self.ref = EngineRegistry.new("language_model", "megatron", model_config=mc, engine_config=mrec, optimizer_config=None)
+            else:
+                self.ref = EngineRegistry.new("language_model", "fsdp", model_config=mc, engine_config=rec, optimizer_config=None)
             self.ref.initialize()
             if self.actor is not None:  # the reference policy starts as an exact copy of the actor
                 self.ref.params.flat.copy_(self.actor.params.flat)
@@ -257,6 +285,20 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             rc = cfg.rollout if isinstance(cfg.rollout, RolloutConfig) else omega_conf_to_dataclass(cfg.rollout, RolloutConfig)
             self.rollout_config = rc
             src = self.actor if self.actor is not None else self.ref
+            self._mp_actor = src is not None and getattr(src, "topo", None) is not None and (src.topo.tp * src.topo.pp > 1)
+            if self._mp_actor:
+                # the trainer holds 1/(tp*pp) of the model: the rollout engine gets a full replica that update_weights()
+                # re-assembles from the shards after every optimizer step; trainer data-parallel group = replicas
+                from ..utils.distributed import set_data_parallel_group
+
+                self._mp_engine = src
+                self.rollout_params = src.gather_full_params()
+                set_data_parallel_group(src.topo.dp_group)
+
+                class _Holder:
+                    params = self.rollout_params
+
+                src = _Holder()
             if src is None:  # rollout-only rank: a forward-only engine holds the weights that weight sync overwrites
                 self.rollout_weights = EngineRegistry.new("language_model", "fsdp", model_config=mc,
                                                           engine_config=FSDPEngineConfig(forward_only=True), optimizer_config=None)
@@ -268,7 +310,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             # every member shards the replicated weights in place, so the train -> rollout reshard moves no bytes
             from ..utils.distributed import get_data_parallel_group
 
-            pool = get_data_parallel_group()  # the ranks that run this kind of worker (all ranks unless the job is split)
+            pool = None if getattr(self, "_mp_actor", False) else get_data_parallel_group()  # ranks that run this kind of worker
             pool_ranks = dist.get_process_group_ranks(pool if pool is not None else dist.group.WORLD) if ws > 1 else [0]
             n_pool, me = len(pool_ranks), (pool_ranks.index(dist.get_rank()) if ws > 1 else 0)
             tp = int(rc.tensor_model_parallel_size or 1)
@@ -310,7 +352,9 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                             logprobs=True)
         ids_cpu, mask_cpu = ids.cpu(), mask.cpu()
         plist = [ids_cpu[i][mask_cpu[i]].tolist() for i in range(ids.shape[0])]
-        if getattr(self, "rollout_tp", 1) > 1:
+        if getattr(self, "_mp_actor", False):
+            outs = self._generate_in_replica(plist, sp)
+        elif getattr(self, "rollout_tp", 1) > 1:
             # the group generates the union of its members' prompts in lockstep; each member keeps its own slice
             parts: list = [None] * self.rollout_tp
             dist.all_gather_object(parts, plist, group=self.rollout_tp_group)
@@ -345,6 +389,28 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                        "rollout_stats": dict(self.rollout.stats)})
         return out
 
+    def _generate_in_replica(self, plist: list, sp) -> list:
+        """All ranks of a model-parallel training replica hold the same prompts. Its rollout groups (``rollout_tp`` consecutive
+        ranks each) take interleaved slices of them, generate, and the replica exchanges the results so that every rank
+        ends up with the outputs of all prompts in the original order."""
+        topo = self._mp_engine.topo
+        mp = topo.tp * topo.pp
+        me = topo.pp_rank * topo.tp + topo.tp_rank          # position inside the replica
+        tp = max(1, getattr(self, "rollout_tp", 1))
+        groups = mp // tp
+        mine = me // tp
+        idx = list(range(mine, len(plist), groups))
+        local = self.rollout.generate([plist[i] for i in idx], sp) if idx else []
+        box = [None] * mp
+        dist.all_gather_object(box, (mine, idx, local if me % tp == 0 else None), group=topo.mp_group)
+        outs: list = [None] * len(plist)
+        for g, ids_, res in box:
+            if res is None:
+                continue
+            for i, o in zip(ids_, res):
+                outs[i] = o
+        return outs
+
     # ------------------------------------------------------------------ log-probs
     def _dev(self, data: DataProto) -> DataProto:
         eng = self.actor or self.ref
@@ -377,7 +443,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
     def update_actor(self, data: DataProto) -> DataProto:
         ac = self.actor_config
         data = self._dev(data)
-        ws = dist.get_world_size() if dist.is_initialized() else 1
+        ws = _dp_world(self.actor)
         n = len(data)
         mini = int(data.meta_info.get("mini_batch_size") or max(1, ac.ppo_mini_batch_size * ac.rollout_n // ws))
         mini = min(mini, n)
@@ -402,6 +468,10 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         """Make the latest actor weights visible to the rollout engine. The engine reads the trainer's working
         buffer in place, so this only invalidates cached KV; returns the device time spent."""
         t0 = time.time()
+        if getattr(self, "_mp_actor", False) and self.rollout is not None:
+            fresh = self._mp_engine.gather_full_params()
+            self.rollout_params.flat.copy_(fresh.flat)
+            del fresh
         if self.rollout is not None:
             self.rollout.clear_kv_cache()
         if get_device_name() == "cuda":
