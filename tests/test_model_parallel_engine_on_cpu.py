@@ -144,3 +144,52 @@ def test_grpo_end_to_end_with_tensor_parallel_actor_and_rollout():
         assert res[r]["steps"] == 3 and res[r]["adv_shape"] == (8, 12)
         assert res[r]["prob_diff"] < 1e-3  # TP-sharded trainer and TP rollout on gathered weights agree on token probabilities
     assert (res[0]["resp"] == res[1]["resp"]).all()  # one replica: both ranks hold the same batch
+
+
+def _ppo_critic_proc(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      VERL_ENGINE_DEVICE="cpu")
+    try:
+        from verl_b200.trainer.main_ppo import main
+
+        t = main(['actor@actor_rollout_ref.actor=megatron_actor', 'actor_rollout_ref.actor.megatron.pipeline_model_parallel_size=2',
+                  'critic@critic=megatron_critic', 'critic.megatron.pipeline_model_parallel_size=2', 'critic.model.path=tiny-llama',
+                  'critic.ppo_micro_batch_size_per_gpu=4', 'critic.ppo_mini_batch_size=4',
+                  'data.train_batch_size=4', 'data.max_prompt_length=16', 'data.max_response_length=12', 'data.synthetic.num_prompts=16',
+                  'data.synthetic.prompt_length=16', 'data.synthetic.vocab_high=512', 'actor_rollout_ref.model.path=tiny-llama',
+                  'actor_rollout_ref.rollout.n=1', 'actor_rollout_ref.actor.ppo_mini_batch_size=4',
+                  'actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=2', 'actor_rollout_ref.actor.use_kl_loss=false',
+                  'actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=2', 'actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=2',
+                  'actor_rollout_ref.rollout.tensor_model_parallel_size=1', 'algorithm.adv_estimator=gae',
+                  'reward_model.reward_manager=token_rule', 'trainer.n_gpus_per_node=2', 'trainer.total_epochs=2',
+                  'trainer.total_training_steps=2', 'trainer.device=cpu', 'trainer.val_before_train=false',
+                  'actor_rollout_ref.rollout.max_num_seqs=8', 'actor_rollout_ref.rollout.block_size=8', 'trainer.resume_mode=disable',
+                  'trainer.worker_group=spmd', 'trainer.logger=[]'])
+        b = t.last_batch.batch
+        q.put((rank, {"steps": t.global_steps, "keys": sorted(b.keys()), "resp": b["responses"].numpy(), "values": b["values"].numpy(),
+                      "critic": type(t.critic_wg.worker.engine).__name__, "pp": t.critic_wg.worker.engine.topo.pp}))
+    except Exception:
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+def test_ppo_with_critic_under_pipeline_parallelism():
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_ppo_critic_proc, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=400) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    for r in (0, 1):
+        assert "error" not in res[r], res[r]["error"]
+        assert res[r]["steps"] == 3 and "values" in res[r]["keys"] and "returns" in res[r]["keys"]
+        assert res[r]["critic"] == "ModelParallelEngineWithValueHead" and res[r]["pp"] == 2
+    assert (res[0]["resp"] == res[1]["resp"]).all() and abs(res[0]["values"] - res[1]["values"]).max() < 1e-5

@@ -55,6 +55,9 @@ class ModelParallelEngine(NativeEngine):
         if self._initialized:
             return
         self.topo = get_topology(self.tp_size, self.pp_size)
+        if self.full_arch.tie_word_embeddings and self.pp_size > 1:
+            raise NotImplementedError("pipeline parallelism with tied input/output embeddings needs the embedding shared between "
+                                      "the first and the last stage; use pipeline_model_parallel_size=1 for this model")
         self.arch = self.topo.local_config(self.full_arch)
         self.maps = build_shard_map(self.full_arch, self.topo, self.value_head)
         outer = get_data_parallel_group()
@@ -81,8 +84,10 @@ class ModelParallelEngine(NativeEngine):
         mc = self.model_config
         path = getattr(mc, "local_path", None) or getattr(mc, "path", None)
         load = bool(getattr(mc, "load_weights", True)) and path and os.path.isdir(str(path))
-        full = FlatParams(self.full_arch, dtype=torch.float32 if self.dtype == torch.float32 else torch.bfloat16, device="cpu",
-                          value_head=self.value_head)
+        # random init happens on the device (per-tensor seeded generators: identical on every rank, and fast for 8B+
+        # models); checkpoints are read on the host
+        full = FlatParams(self.full_arch, dtype=torch.float32 if self.dtype == torch.float32 else torch.bfloat16,
+                          device="cpu" if load else self.device, value_head=self.value_head)
         if load:
             from ....utils.model import load_hf_weights_into
 
