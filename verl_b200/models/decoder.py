@@ -43,6 +43,13 @@ class PackedBatch:
     cu_seqlens: torch.Tensor  # [B+1] int32 (device) ...
     max_seqlen: int
     cu_seqlens_cpu: Optional[torch.Tensor] = None  # host copy (avoids syncs in fallbacks)
+    # Shared-prefix batches: sequences of one group have the same prompt. The token stream then holds the prompt ONCE per
+    # group followed by the members' responses; every token-wise op (norms, projections, MLP, head) runs on that
+    # de-duplicated stream. Only attention needs whole sequences: ``expand_index`` [T_e] gathers the stream into the
+    # per-member (prompt + response) layout that ``cu_seqlens`` describes, ``collapse_index`` [T] picks one representative of
+    # every stream token back out of it.
+    expand_index: Optional[torch.Tensor] = None
+    collapse_index: Optional[torch.Tensor] = None
 
     @property
     def num_tokens(self) -> int:
@@ -162,10 +169,18 @@ class DecoderModel:
             self.kv_hook(layer_idx, k, v)
         native_ok = q.is_cuda and F._ATTN_IMPL["fwd"] is not None and hd in (64, 128)
         cu = batch.cu_seqlens if native_ok else self._cu_cpu(batch)
-        attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
-        attn2 = attn.reshape(T, Q)
-        if S is not None:
-            S.update(qkv=qkv, attn=attn2, lse=lse)
+        if batch.expand_index is not None:
+            ex = batch.expand_index
+            qe, ke, ve = q.index_select(0, ex), k.index_select(0, ex), v.index_select(0, ex)
+            attn_e, lse = F.attention_varlen(qe, ke, ve, cu, batch.max_seqlen)
+            attn2 = attn_e.index_select(0, batch.collapse_index).reshape(T, Q)
+            if S is not None:
+                S.update(qkv=qkv, attn=attn2, lse=lse, attn_e=attn_e)
+        else:
+            attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
+            attn2 = attn.reshape(T, Q)
+            if S is not None:
+                S.update(qkv=qkv, attn=attn2, lse=lse)
         if self.tp is not None:
             return self.tp.row_linear(attn2, W["self_attn.o_proj.weight"][:, self.tp.rows(cfg.q_size)], None)
         o = self._lin(W, "self_attn.o_proj.weight", attn2, S)
@@ -206,8 +221,21 @@ class DecoderModel:
         k = qkv[:, Q : Q + KV].view(T, nkv, hd)
         v = qkv[:, Q + KV :].view(T, nkv, hd)
         cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["bwd"] is not None and lse is not None else self._cu_cpu(batch)
-        dq, dk, dv = F.attention_varlen_bwd(g_attn.view(T, nh, hd), q, k, v, attn2.view(T, nh, hd), lse, cu,
-                                            batch.max_seqlen)
+        if batch.expand_index is not None:
+            # gradients of the per-member layout: only the representative copies carry an output gradient; the prompt's
+            # key/value gradients are the sums over all members of its group
+            ex, col = batch.expand_index, batch.collapse_index
+            attn_e = S["attn_e"]
+            g_e = torch.zeros_like(attn_e)
+            g_e.index_copy_(0, col, g_attn.view(T, nh, hd))
+            dq_e, dk_e, dv_e = F.attention_varlen_bwd(g_e, q.index_select(0, ex), k.index_select(0, ex), v.index_select(0, ex),
+                                                      attn_e, lse, cu, batch.max_seqlen)
+            dq = torch.zeros(T, nh, hd, dtype=torch.float32, device=q.device).index_add_(0, ex, dq_e.float()).to(q.dtype)
+            dk = torch.zeros(T, nkv, hd, dtype=torch.float32, device=q.device).index_add_(0, ex, dk_e.float()).to(q.dtype)
+            dv = torch.zeros(T, nkv, hd, dtype=torch.float32, device=q.device).index_add_(0, ex, dv_e.float()).to(q.dtype)
+        else:
+            dq, dk, dv = F.attention_varlen_bwd(g_attn.view(T, nh, hd), q, k, v, attn2.view(T, nh, hd), lse, cu,
+                                                batch.max_seqlen)
         g_qkv = torch.empty_like(qkv)
         gq = g_qkv[:, :Q].view(T, nh, hd)
         gk = g_qkv[:, Q : Q + KV].view(T, nkv, hd)
@@ -580,7 +608,7 @@ class DecoderModel:
     # ------------------------------------------------------------------------------------ heads
     def forward_logprobs(self, batch: PackedBatch, labels: torch.Tensor, temperature: float = 1.0,
                          need_grad: Optional[bool] = None, positions: Optional[torch.Tensor] = None,
-                         stage_input: Optional[torch.Tensor] = None):
+                         stage_input: Optional[torch.Tensor] = None, position_labels: Optional[torch.Tensor] = None):
         """(log_probs, entropy) per packed position of ``labels`` (fp32 [T]); differentiable when grads are on.
         With ``positions`` (int64, increasing) the LM head runs only on those packed positions (the ones whose next
         token is a response token) and the outputs have ``len(positions)`` entries."""
@@ -588,7 +616,10 @@ class DecoderModel:
         with torch.no_grad():
             hN, state = self._trunk_fwd(batch, save=need_grad, stage_input=stage_input)
             if positions is not None:
-                hS, labels = hN.index_select(0, positions), labels.index_select(0, positions)
+                # ``position_labels``: one label per entry of ``positions`` (a shared last prompt token predicts a different
+                # first response token for every member of its group, so positions may repeat)
+                hS = hN.index_select(0, positions)
+                labels = position_labels if position_labels is not None else labels.index_select(0, positions)
             else:
                 hS = hN
             lp, ent, lse = F.lmhead_logprob_entropy(hS, self.params.lm_head_weight, labels, temperature)
@@ -642,8 +673,9 @@ class DecoderModel:
             g_hS = F.lmhead_backward(state["hS"], head, state["labels"], state["temperature"], state["lse"], state["ent"],
                                      g_lp.float(), g_ent.float() if g_ent is not None else None, self._grad_of(head))
             if state.get("positions") is not None:
-                g_hN = torch.zeros_like(hN)
-                g_hN.index_copy_(0, state["positions"], g_hS.to(hN.dtype))
+                g_hN = torch.zeros(hN.shape, dtype=torch.float32, device=hN.device)
+                g_hN.index_add_(0, state["positions"], g_hS.float())  # positions may repeat (shared prefixes)
+                g_hN = g_hN.to(hN.dtype)
             else:
                 g_hN = g_hS
             state["hS"] = None

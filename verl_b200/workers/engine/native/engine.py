@@ -73,6 +73,69 @@ def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, pos
     return batch, labels.contiguous(), resp_index, resp_valid
 
 
+def prompt_group_ids(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int) -> list[int]:
+    """Group id per row: consecutive rows with an identical (left-padded) prompt belong to one group."""
+    P = input_ids.shape[1] - response_length
+    if input_ids.shape[0] <= 1:
+        return [0] * input_ids.shape[0]
+    same = (input_ids[1:, :P] == input_ids[:-1, :P]).all(-1) & (attention_mask[1:, :P] == attention_mask[:-1, :P]).all(-1)
+    gid = torch.cat([torch.zeros(1, dtype=torch.int64, device=same.device), (~same).to(torch.int64).cumsum(0)])
+    return gid.tolist()
+
+
+def pack_shared_prefix_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: Optional[torch.Tensor],
+                             response_length: int, gids: list[int]):
+    """Packing with the prompt of every group stored once (see ``PackedBatch.expand_index``).
+
+    Returns ``(packed_batch, positions_sel, labels_sel, resp_valid)``: ``positions_sel[n]`` is the stream position whose
+    output predicts the n-th valid response token (row-major over ``resp_valid``) and ``labels_sel[n]`` that token."""
+    b, L = input_ids.shape
+    P = L - response_length
+    dev = input_ids.device
+    mask = attention_mask.bool()
+    plen = mask[:, :P].sum(-1).tolist()
+    rlen = mask[:, P:].sum(-1).tolist()
+    src, expand, collapse, pos_sel, lab_src, lens_e = [], [], [], [], [], []
+    t_d = t_e = 0
+    i = 0
+    while i < b:
+        j = i
+        while j + 1 < b and gids[j + 1] == gids[i]:
+            j += 1
+        p = plen[i]
+        prompt_lo = t_d
+        src.append(torch.arange(i * L + P - p, i * L + P))              # the leader's prompt tokens
+        collapse.append(torch.arange(t_e, t_e + p))                      # represented by the leader's copy
+        t_d += p
+        for m in range(i, j + 1):
+            r = rlen[m]
+            src.append(torch.arange(m * L + P, m * L + P + r))
+            expand.append(torch.arange(prompt_lo, prompt_lo + p))
+            expand.append(torch.arange(t_d, t_d + r))
+            collapse.append(torch.arange(t_e + p, t_e + p + r))
+            if r > 0:
+                pos_sel.append(torch.tensor([prompt_lo + p - 1], dtype=torch.int64))
+                pos_sel.append(torch.arange(t_d, t_d + r - 1))
+                lab_src.append(torch.arange(m * L + P, m * L + P + r))
+            lens_e.append(p + r)
+            t_d += r
+            t_e += p + r
+        i = j + 1
+    cat = lambda xs: (torch.cat(xs) if xs else torch.zeros(0, dtype=torch.int64)).to(dev)
+    src_t, lab_t = cat(src), cat(lab_src)
+    flat_ids = input_ids.reshape(-1)
+    ids_d = flat_ids[src_t]
+    if position_ids is None:
+        pos_full = (torch.cumsum(mask.to(torch.int32), -1) - 1).reshape(-1)
+    else:
+        pos_full = position_ids.reshape(-1)
+    cu = torch.zeros(len(lens_e) + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(lens_e, dtype=torch.int32), 0)
+    batch = PackedBatch(input_ids=ids_d.contiguous(), positions=pos_full[src_t].to(torch.int32).contiguous(), cu_seqlens=cu.to(dev),
+                        max_seqlen=max(lens_e) if lens_e else 0, cu_seqlens_cpu=cu, expand_index=cat(expand), collapse_index=cat(collapse))
+    return batch, cat(pos_sel), flat_ids[lab_t].contiguous(), mask[:, P:]
+
+
 class NativeEngine(BaseEngine):
     value_head = False
 
@@ -136,6 +199,8 @@ class NativeEngine(BaseEngine):
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
+        # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
+        self._share_prefix = bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
         if bool(getattr(ec, "enable_activation_offload", False)) and not self.forward_only:
             from ....utils.activation_offload import ActivationOffloader
 
@@ -200,7 +265,37 @@ class NativeEngine(BaseEngine):
         ids = data["input_ids"]
         n = ids.shape[0]
         dyn = bool(data.get("use_dynamic_bsz", getattr(ec, "use_dynamic_bsz", False)))
-        if dyn:
+        share = self._share_prefix and "responses" in data and not self.value_head
+        gids_all = prompt_group_ids(ids, data["attention_mask"], data["responses"].shape[1]) if share else None
+        if share and len(set(gids_all)) == len(gids_all):
+            share, gids_all = False, None  # no two rows share a prompt
+        if share:
+            # whole groups per micro-batch, in order, under the token budget counted on the de-duplicated stream
+            P = ids.shape[1] - data["responses"].shape[1]
+            pl = data["attention_mask"][:, :P].sum(-1).tolist()
+            rl = data["attention_mask"][:, P:].sum(-1).tolist()
+            budget = int(data.get("max_token_len_per_gpu") or (ec.infer_max_token_len_per_gpu if forward_only else ec.max_token_len_per_gpu)) \
+                if dyn else None
+            cap_rows = None if dyn else int(data.get("micro_batch_size_per_gpu") or (ec.infer_micro_batch_size_per_gpu if forward_only
+                                                                                    else ec.micro_batch_size_per_gpu) or n)
+            parts, cur, cur_tok = [], [], 0
+            i = 0
+            while i < n:
+                j = i
+                while j + 1 < n and gids_all[j + 1] == gids_all[i]:
+                    j += 1
+                rows_g = list(range(i, j + 1))
+                tok_g = pl[i] + sum(rl[i : j + 1])
+                full = (budget is not None and cur and cur_tok + tok_g > budget) or (cap_rows is not None and cur and len(cur) + len(rows_g) > cap_rows)
+                if full:
+                    parts.append(cur)
+                    cur, cur_tok = [], 0
+                cur += rows_g
+                cur_tok += tok_g
+                i = j + 1
+            if cur:
+                parts.append(cur)
+        elif dyn:
             budget = int(data.get("max_token_len_per_gpu") or (ec.infer_max_token_len_per_gpu if forward_only
                                                                else ec.max_token_len_per_gpu))
             from ....utils.seqlen_balancing import get_seqlen_balanced_partitions
@@ -216,7 +311,7 @@ class NativeEngine(BaseEngine):
         for p in parts:
             idx = torch.tensor(p, dtype=torch.int64, device=ids.device)
             out.append({k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v)
-                        for k, v in data.items()} | {"_rows": p})
+                        for k, v in data.items()} | {"_rows": p} | ({"_gids": [gids_all[r] for r in p]} if share else {}))
         return out
 
     def forward_backward_batch(self, data, loss_function: Optional[Callable] = None, forward_only: bool = False) -> dict:
@@ -275,7 +370,14 @@ class NativeEngine(BaseEngine):
         # the LM head (a third of a 7B forward's head+tail work at vocabulary 152k) runs only where a response token is
         # predicted: prompt positions never enter a loss or a returned log-prob
         positions = resp_index[resp_valid]
-        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions)
+        position_labels = None
+        gids = mb.get("_gids")
+        if gids is not None and len(set(gids)) < len(gids) and self.model.tp is None:
+            # members of a group share their prompt: it is embedded, projected and fed through the MLPs once
+            batch, positions, position_labels, resp_valid = pack_shared_prefix_batch(mb["input_ids"], mb["attention_mask"],
+                                                                                     mb.get("position_ids"), R, gids)
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions,
+                                              position_labels=position_labels)
         out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
         if calc_entropy or need_grad:
             out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
