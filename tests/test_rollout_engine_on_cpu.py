@@ -97,3 +97,20 @@ def test_fp8_rollout_weights_stay_close_to_bf16_and_refresh_after_updates():
     q8.clear_kv_cache()
     new = next(iter(q8.model.fp8_weights.values()))
     assert torch.equal(new[0], old) and new[1].mean() > 0  # same e4m3 codes, larger scales: the copy was rebuilt
+
+
+def test_identical_prompts_are_prefilled_once_and_match_unshared_generation():
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    prompts = [[5, 6, 7, 8, 9, 10, 11, 12, 13]] * 3 + [[20, 21, 22]] * 2 + [[30, 31]]
+    outs = {}
+    for share in (True, False):
+        eng = RolloutEngine(cfg, P, max_num_seqs=8, max_model_len=64, block_size=4, eos_token_id=-1, share_prefill=share)
+        outs[share] = eng.generate(prompts, SamplingParams(temperature=1.0, max_tokens=6, seed=None))
+        if share:
+            assert eng.stats["prefill_tokens_shared"] == 2 * 9 + 3 and eng.stats["prefill_tokens"] == 9 * 3 + 3 * 2 + 2
+    for a, b in zip(outs[True], outs[False]):
+        assert a.token_ids == b.token_ids and max(abs(x - y) for x, y in zip(a.log_probs, b.log_probs)) < 1e-5
+    assert outs[True][0].token_ids != outs[True][1].token_ids  # same prompt, different seeds: different samples

@@ -83,13 +83,14 @@ class RolloutEngine:
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
                  valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0,
-                 tp_group=None, quantization: Optional[str] = None):
+                 tp_group=None, quantization: Optional[str] = None, share_prefill: bool = True):
         """``tp_group``: process group of the ranks that serve the same requests tensor-parallel (each holds the
         full replicated weights and uses its shard of them in place; see ``TensorParallelShard``). All ranks of the
         group must be fed the same requests in the same order."""
         self.cfg = cfg
         assert quantization in (None, "", "fp8"), f"unsupported rollout quantization: {quantization}"
         self.quantization = quantization or None
+        self.share_prefill = bool(share_prefill)
         self.tp_group = tp_group
         self.tp_size = dist.get_world_size(tp_group) if tp_group is not None else 1
         self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
@@ -280,17 +281,30 @@ class RolloutEngine:
         t0 = time.time()
         dev = self.device
         lens = [len(r.prompt) for r in reqs]
-        ids = torch.tensor([t for r in reqs for t in r.prompt], dtype=torch.int64)
-        slot_rows, bt_rows = [], torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
+        # requests with the same prompt (the n samples of a group) are prefilled once: the leader's prompt runs through
+        # the model, the followers get a copy of its KV blocks and sample their own first token from the same logits
+        first_of: dict = {}
+        leaders: list[int] = []   # request index of each distinct prompt's first occurrence
+        lead_idx: list[int] = []  # per request: index into ``leaders``
+        for i, r in enumerate(reqs):
+            key = tuple(r.prompt) if self.share_prefill else i
+            if key not in first_of:
+                first_of[key] = len(leaders)
+                leaders.append(i)
+            lead_idx.append(first_of[key])
+        bt_rows = torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
         for i, r in enumerate(reqs):
             bt_rows[i, : len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
+        ids = torch.tensor([t for i in leaders for t in reqs[i].prompt], dtype=torch.int64)
+        slot_rows = []
+        for i in leaders:
             p = torch.arange(lens[i])
             slot_rows.append(bt_rows[i, p // self.bs].long() * self.bs + p % self.bs)
         if self.is_cuda:
             ids, slot_map = ids.pin_memory().to(dev, non_blocking=True), torch.cat(slot_rows).pin_memory().to(dev, non_blocking=True)
         else:
             slot_map = torch.cat(slot_rows)
-        batch = PackedBatch.from_lengths(ids, lens, device=dev)
+        batch = PackedBatch.from_lengths(ids, [lens[i] for i in leaders], device=dev)
         self._prefill_slots = slot_map
         try:
             h = self.model.forward_hidden(batch)
@@ -298,6 +312,17 @@ class RolloutEngine:
             self._prefill_slots = None
         last = (batch.cu_seqlens[1:].long() - 1)
         logits = F.gemm(h[last].contiguous(), self.params.lm_head_weight)
+        if len(leaders) < len(reqs):
+            logits = logits[torch.tensor(lead_idx, dtype=torch.int64, device=dev)]
+            for i, r in enumerate(reqs):
+                li = leaders[lead_idx[i]]
+                if li == i:
+                    continue
+                nb = (lens[i] + self.bs - 1) // self.bs
+                src = torch.tensor(reqs[li].blocks[:nb], dtype=torch.int64, device=dev)
+                dst = torch.tensor(r.blocks[:nb], dtype=torch.int64, device=dev)
+                self.kv[:, :, dst] = self.kv[:, :, src]
+            self.stats["prefill_tokens_shared"] = self.stats.get("prefill_tokens_shared", 0) + sum(lens) - sum(lens[i] for i in leaders)
         slots = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=dev)
         seeds = torch.tensor([(r.params.seed if r.params.seed is not None else self._seed * 1000003 + zlib.crc32(r.rid.encode()))
                               for r in reqs], dtype=torch.int64, device=dev)
