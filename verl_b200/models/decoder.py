@@ -98,6 +98,45 @@ class TensorParallelShard:
         return slice(self.rank * per, (self.rank + 1) * per)
 
 
+class UlyssesSequenceParallel:
+    """Sequence parallelism over ``size`` ranks that hold the same micro-batch: every rank runs the token-wise layers on a
+    contiguous 1/size slice of the packed token stream; around attention an all-to-all trades the sequence split for a
+    head split (each rank attends over whole sequences with 1/size of the heads) and back.
+
+    Parity target: ``verl/utils/ulysses.py:137-195`` (``gather_seq_scatter_heads`` / ``gather_heads_scatter_seq``) and
+    ``verl/models/transformers/monkey_patch.py:87-155``."""
+
+    def __init__(self, group, rank: int, size: int):
+        self.group, self.rank, self.size = group, int(rank), int(size)
+
+    def local_slice(self, total: int) -> slice:
+        assert total % self.size == 0, "the packed stream must be padded to a multiple of the sequence-parallel size"
+        n = total // self.size
+        return slice(self.rank * n, (self.rank + 1) * n)
+
+    def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
+        """[T/size, heads, hd] (my tokens, all heads) -> [T, heads/size, hd] (all tokens, my heads)."""
+        import torch.distributed as dist
+
+        tl, h, d = x.shape
+        hs = h // self.size
+        send = x.view(tl, self.size, hs, d).permute(1, 0, 2, 3).contiguous()  # [size, tl, hs, d]: block j goes to rank j
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)                  # block i came from rank i: its tokens, my heads
+        return recv.view(self.size * tl, hs, d)
+
+    def heads_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, heads/size, hd] -> [T/size, heads, hd] (inverse of ``seq_to_heads``)."""
+        import torch.distributed as dist
+
+        t, hs, d = x.shape
+        tl = t // self.size
+        send = x.view(self.size, tl, hs, d).contiguous()                      # block j: rank j's tokens, my heads
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)                  # block i: my tokens, rank i's heads
+        return recv.permute(1, 0, 2, 3).reshape(tl, self.size * hs, d)
+
+
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
@@ -111,6 +150,7 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.sp: Optional[UlyssesSequenceParallel] = None  # sequence parallelism (token-wise layers on a slice of the stream)
         self.cfg = cfg
         self.params = params
         self.recompute = recompute
@@ -163,13 +203,21 @@ class DecoderModel:
             k.copy_(kn.view(T, nkv, hd))
             if S is not None:
                 S.update(q_pre=qp, k_pre=kp, rstd_q=rq, rstd_k=rk)
-        F.apply_rope_(q, batch.positions, self._cos, self._sin)
-        F.apply_rope_(k, batch.positions, self._cos, self._sin)
+        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_slice(batch.num_tokens)]
+        F.apply_rope_(q, pos, self._cos, self._sin)
+        F.apply_rope_(k, pos, self._cos, self._sin)
         if self.kv_hook is not None:
             self.kv_hook(layer_idx, k, v)
         native_ok = q.is_cuda and F._ATTN_IMPL["fwd"] is not None and hd in (64, 128)
         cu = batch.cu_seqlens if native_ok else self._cu_cpu(batch)
-        if batch.expand_index is not None:
+        if self.sp is not None:
+            assert batch.expand_index is None, "sequence parallelism and shared-prefix packing are exclusive"
+            qf, kf, vf = self.sp.seq_to_heads(q.contiguous()), self.sp.seq_to_heads(k.contiguous()), self.sp.seq_to_heads(v.contiguous())
+            attn_f, lse = F.attention_varlen(qf, kf, vf, cu, batch.max_seqlen)
+            attn2 = self.sp.heads_to_seq(attn_f.contiguous()).reshape(T, Q)
+            if S is not None:
+                S.update(qkv=qkv, attn=attn2, lse=lse, sp_full=(qf, kf, vf, attn_f))
+        elif batch.expand_index is not None:
             ex = batch.expand_index
             qe, ke, ve = q.index_select(0, ex), k.index_select(0, ex), v.index_select(0, ex)
             attn_e, lse = F.attention_varlen(qe, ke, ve, cu, batch.max_seqlen)
@@ -221,7 +269,12 @@ class DecoderModel:
         k = qkv[:, Q : Q + KV].view(T, nkv, hd)
         v = qkv[:, Q + KV :].view(T, nkv, hd)
         cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["bwd"] is not None and lse is not None else self._cu_cpu(batch)
-        if batch.expand_index is not None:
+        if self.sp is not None:
+            qf, kf, vf, attn_f = S["sp_full"]
+            g_f = self.sp.seq_to_heads(g_attn.view(T, nh, hd).contiguous())
+            dq_f, dk_f, dv_f = F.attention_varlen_bwd(g_f, qf, kf, vf, attn_f, lse, cu, batch.max_seqlen)
+            dq, dk, dv = (self.sp.heads_to_seq(t.contiguous()) for t in (dq_f, dk_f, dv_f))
+        elif batch.expand_index is not None:
             # gradients of the per-member layout: only the representative copies carry an output gradient; the prompt's
             # key/value gradients are the sums over all members of its group
             ex, col = batch.expand_index, batch.collapse_index
@@ -242,8 +295,9 @@ class DecoderModel:
         gq.copy_(dq)
         gk.copy_(dk)
         g_qkv[:, Q + KV :].view(T, nkv, hd).copy_(dv)
-        F.apply_rope_(gq, batch.positions, self._cos, self._sin, backward=True)
-        F.apply_rope_(gk, batch.positions, self._cos, self._sin, backward=True)
+        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_slice(batch.num_tokens)]
+        F.apply_rope_(gq, pos, self._cos, self._sin, backward=True)
+        F.apply_rope_(gk, pos, self._cos, self._sin, backward=True)
         if cfg.qk_norm:
             wq, wk = W["self_attn.q_norm.weight"], W["self_attn.k_norm.weight"]
             dqp = F.rms_norm_bwd(gq.reshape(T * nh, hd).contiguous(), S["q_pre"], wq, S["rstd_q"], None,
@@ -540,7 +594,8 @@ class DecoderModel:
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(-1, "forward")
         if cfg.has_embedding:
-            a = F.embedding(batch.input_ids, self.params["embed_tokens.weight"])
+            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
+            a = F.embedding(ids, self.params["embed_tokens.weight"])
         else:
             a = stage_input  # hidden stream handed over by the previous pipeline stage
             assert a is not None, "a pipeline stage without embedding needs stage_input"
@@ -601,7 +656,8 @@ class DecoderModel:
         if getattr(emb, "main_grad", None) is not None:
             if self.pre_layer_hook is not None:
                 self.pre_layer_hook(-1, "backward")
-            F.embedding_bwd_(batch.input_ids, g, emb.main_grad)
+            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
+            F.embedding_bwd_(ids, g, emb.main_grad)
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(-1)
 

@@ -199,8 +199,23 @@ class NativeEngine(BaseEngine):
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
+        # Ulysses sequence parallelism: blocks of ``sp`` consecutive ranks work on the same micro-batches
+        self.sp_size = int(getattr(ec, "ulysses_sequence_parallel_size", 1) or 1)
+        self.sp_group, self.sp_rank = None, 0
+        if self.sp_size > 1:
+            assert self.world % self.sp_size == 0 and not self.value_head, "sequence parallel size must divide the data-parallel world"
+            assert self.arch.num_key_value_heads % self.sp_size == 0, "sequence parallel size must divide the KV heads"
+            from ....models.decoder import UlyssesSequenceParallel
+
+            pool = dist.get_process_group_ranks(self.group if self.group is not None else dist.group.WORLD)
+            for g0 in range(0, self.world, self.sp_size):  # collective: every rank creates every group, in the same order
+                grp = dist.new_group(pool[g0 : g0 + self.sp_size])
+                if g0 <= self.rank < g0 + self.sp_size:
+                    self.sp_group, self.sp_rank = grp, self.rank - g0
+            self.model.sp = UlyssesSequenceParallel(self.sp_group, self.sp_rank, self.sp_size)
         # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
-        self._share_prefix = bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
+        self._share_prefix = (bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
+                              and self.sp_size == 1)
         if bool(getattr(ec, "enable_activation_offload", False)) and not self.forward_only:
             from ....utils.activation_offload import ActivationOffloader
 
@@ -332,7 +347,7 @@ class NativeEngine(BaseEngine):
             if self.world > 1:
                 pack = torch.stack([tok, seqs])
                 dist.all_reduce(pack, group=self.group)
-                tok, seqs = pack[0], pack[1]
+                tok, seqs = pack[0] / self.sp_size, pack[1] / self.sp_size  # the ranks of a sequence-parallel block hold the same rows
             data["global_batch_info"] = dict(dp_size=self.world, batch_num_tokens=tok, global_batch_size=seqs,
                                              loss_scale_factor=data.get("loss_scale_factor"))
         mbs = self._micro_batches(data, forward_only)
@@ -369,6 +384,8 @@ class NativeEngine(BaseEngine):
                                                                   mb.get("position_ids"), R)
         # the LM head (a third of a 7B forward's head+tail work at vocabulary 152k) runs only where a response token is
         # predicted: prompt positions never enter a loss or a returned log-prob
+        if self.sp_size > 1:
+            return self._forward_micro_sp(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad)
         positions = resp_index[resp_valid]
         position_labels = None
         gids = mb.get("_gids")
@@ -381,6 +398,39 @@ class NativeEngine(BaseEngine):
         out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
         if calc_entropy or need_grad:
             out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
+        return out
+
+    def _forward_micro_sp(self, batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad) -> dict:
+        """Sequence-parallel micro-batch: this rank evaluates the head on the response positions inside its slice of the
+        (padded) token stream; the [b, R] outputs are completed by a sum over the block. Gradients flow only into the
+        locally computed entries, which is exactly this rank's share of the block's loss."""
+        sp, T = self.sp_size, batch.num_tokens
+        pad = (-T) % sp
+        if pad:
+            dev = batch.input_ids.device
+            ids = torch.cat([batch.input_ids, batch.input_ids.new_zeros(pad)])
+            pos = torch.cat([batch.positions, torch.arange(pad, dtype=batch.positions.dtype, device=dev)])
+            cu_cpu = torch.cat([batch.cu_seqlens_cpu, torch.tensor([T + pad], dtype=torch.int32)])
+            batch = PackedBatch(input_ids=ids, positions=pos, cu_seqlens=cu_cpu.to(dev), max_seqlen=max(batch.max_seqlen, pad),
+                                cu_seqlens_cpu=cu_cpu)
+            labels = torch.cat([labels, labels.new_zeros(pad)])
+        sl = self.model.sp.local_slice(batch.num_tokens)
+        positions = resp_index[resp_valid]
+        mine = (positions >= sl.start) & (positions < sl.stop)
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions[mine] - sl.start,
+                                              position_labels=labels[positions[mine]])
+        flat_idx = resp_valid.reshape(-1).nonzero().squeeze(-1)[mine]
+        n_out = resp_valid.numel()
+
+        def complete(local: torch.Tensor) -> torch.Tensor:
+            part = torch.zeros(n_out, dtype=local.dtype, device=local.device).index_copy(0, flat_idx, local)
+            total = part.detach().clone()
+            dist.all_reduce(total, group=self.sp_group)
+            return (part + (total - part.detach())).view(resp_valid.shape)
+
+        out = {"log_probs": complete(lp)}
+        if calc_entropy or need_grad:
+            out["entropy"] = complete(ent)
         return out
 
     # ------------------------------------------------------------------------------------ optimizer
