@@ -166,17 +166,17 @@ class RayPPOTrainer:
             from ...utils.distributed import get_data_parallel_group
 
             g = get_data_parallel_group()
-            if g is None:
-                mp = self._model_parallel_size()
-                if mp > 1:  # before the workers exist: replicas are blocks of tp*pp consecutive ranks
-                    return dist.get_rank() // mp, dist.get_world_size() // mp
+            mp = self._model_parallel_size()
+            if mp > 1 and (g is None or str(self.config.actor_rollout_ref.actor.get("strategy", "fsdp")) != "megatron"):
+                # replicas are blocks of tp*pp (or sequence-parallel) consecutive ranks
+                return dist.get_rank(g) // mp, dist.get_world_size(g) // mp
             return dist.get_rank(g), dist.get_world_size(g)
         return 0, 1
 
     def _model_parallel_size(self) -> int:
         a = self.config.actor_rollout_ref.actor
         if str(a.get("strategy", "fsdp")) != "megatron":
-            return 1
+            return int(a.get("ulysses_sequence_parallel_size", 1) or 1)  # a sequence-parallel block shares its data
         m = a.get("megatron") or {}
         return int(m.get("tensor_model_parallel_size", 1) or 1) * int(m.get("pipeline_model_parallel_size", 1) or 1)
 

@@ -251,12 +251,17 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             if rc is not None and rc.get("log_prob_max_token_len_per_gpu"):
                 object.__setattr__(ec, "infer_max_token_len_per_gpu", rc.get("log_prob_max_token_len_per_gpu"))
             object.__setattr__(ec, "enable_gradient_checkpointing", bool(mc.enable_gradient_checkpointing))
+            sp_size = int(ac.get("ulysses_sequence_parallel_size", 1) or 1)
+            if sp_size > 1 and hasattr(ec, "ulysses_sequence_parallel_size"):
+                object.__setattr__(ec, "ulysses_sequence_parallel_size", sp_size)
             tw = TrainingWorkerConfig(model_type="language_model", model_config=mc, engine_config=ec,
                                       optimizer_config=ac.optim, checkpoint_config=ac.checkpoint)
             self.actor = EngineRegistry.new("language_model", getattr(ec, "strategy", "fsdp"), model_config=mc, engine_config=ec,
                                             optimizer_config=ac.optim, checkpoint_config=ac.checkpoint)
             self.actor.initialize()
             self.actor_loss = partial(ppo_loss, ac)
+            # the ranks of a sequence-parallel block see the same prompts: they split the generation work among them
+            self._sp_replica = getattr(self.actor, "sp_size", 1) > 1
         if self._is_ref:
             rcfg = cfg.get("ref") if hasattr(cfg, "get") else None
             rec = FSDPEngineConfig(forward_only=True)
@@ -352,7 +357,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                             logprobs=True)
         ids_cpu, mask_cpu = ids.cpu(), mask.cpu()
         plist = [ids_cpu[i][mask_cpu[i]].tolist() for i in range(ids.shape[0])]
-        if getattr(self, "_mp_actor", False):
+        if getattr(self, "_mp_actor", False) or getattr(self, "_sp_replica", False):
             outs = self._generate_in_replica(plist, sp)
         elif getattr(self, "rollout_tp", 1) > 1:
             # the group generates the union of its members' prompts in lockstep; each member keeps its own slice
@@ -393,16 +398,20 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         """All ranks of a model-parallel training replica hold the same prompts. Its rollout groups (``rollout_tp`` consecutive
         ranks each) take interleaved slices of them, generate, and the replica exchanges the results so that every rank
         ends up with the outputs of all prompts in the original order."""
-        topo = self._mp_engine.topo
-        mp = topo.tp * topo.pp
-        me = topo.pp_rank * topo.tp + topo.tp_rank          # position inside the replica
+        if getattr(self, "_sp_replica", False):
+            eng = self.actor
+            mp, me, group = eng.sp_size, eng.sp_rank, eng.sp_group
+        else:
+            topo = self._mp_engine.topo
+            mp, group = topo.tp * topo.pp, topo.mp_group
+            me = topo.pp_rank * topo.tp + topo.tp_rank      # position inside the replica
         tp = max(1, getattr(self, "rollout_tp", 1))
         groups = mp // tp
         mine = me // tp
         idx = list(range(mine, len(plist), groups))
         local = self.rollout.generate([plist[i] for i in idx], sp) if idx else []
         box = [None] * mp
-        dist.all_gather_object(box, (mine, idx, local if me % tp == 0 else None), group=topo.mp_group)
+        dist.all_gather_object(box, (mine, idx, local if me % tp == 0 else None), group=group)
         outs: list = [None] * len(plist)
         for g, ids_, res in box:
             if res is None:
