@@ -53,6 +53,9 @@ def parse_args():
                         "measured faster than TP=2 for this model (gen 32.5 s vs 41.1 s per step); 2 reproduces the TP=2 layout")
     p.add_argument("--train-tp", type=int, default=1, help="tensor-parallel size of the training engine (strategy=megatron when tp*pp > 1)")
     p.add_argument("--train-pp", type=int, default=1, help="pipeline-parallel size of the training engine")
+    p.add_argument("--no-prefix-sharing", action="store_true",
+                   help="pack every sample's prompt separately in the log-prob / training passes and prefill it separately "
+                        "(default: the n samples of a prompt share its tokens; results are identical)")
     p.add_argument("--critic", action="store_true", help="PPO with a critic of the same architecture and GAE instead of GRPO")
     return p.parse_args()
 
@@ -118,6 +121,8 @@ class ClockSampler:
 
 
 def build_config(args, world: int):
+    if args.no_prefix_sharing:
+        os.environ["VERL_B200_SHARE_PREFIX"] = "0"
     from verl_b200.trainer.config import CONFIG_DIR
     from verl_b200.utils.config import load_config
 
@@ -266,6 +271,7 @@ def main():
                        else (f"train tp{args.train_tp} x pp{args.train_pp} x dp{world // (args.train_tp * args.train_pp)} + rollout tp{rollout_tp} "
                              f"on weights gathered from the shards each step"),
                        "algorithm": "ppo+critic+gae" if args.critic else "grpo",
+                       "shared_prompt_packing": not args.no_prefix_sharing,
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
                        "mean_response_len": last_metrics.get("response_length/mean")},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
