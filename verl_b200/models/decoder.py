@@ -170,6 +170,18 @@ class DecoderModel:
             self._cos, self._sin = F.rope_table(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, self.device)
 
     def _wgrad(self, w: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> None:
+        lora = getattr(w, "lora", None)
+        if lora is not None:
+            # the weight in use is W0 + s * B A (merged): its own gradient is never formed; the adapter gradients are
+            #   dB += s * dy^T (x A^T)   [out, r]        dA += s * (dy B)^T x   [r, in]
+            A, B, scale = lora
+            if getattr(A, "main_grad", None) is None:
+                return
+            u = F.gemm(x, A)
+            F.gemm(dy, u * scale, out=B.main_grad, a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            t = F.gemm(dy, B, b_mn=True)
+            F.gemm(t * scale, x, out=A.main_grad, a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            return
         mg = getattr(w, "main_grad", None)
         if mg is None:
             return
@@ -727,7 +739,7 @@ class DecoderModel:
                 g_lp = torch.zeros_like(state["lse"])
             head = self.params.lm_head_weight
             g_hS = F.lmhead_backward(state["hS"], head, state["labels"], state["temperature"], state["lse"], state["ent"],
-                                     g_lp.float(), g_ent.float() if g_ent is not None else None, self._grad_of(head))
+                                     g_lp.float(), g_ent.float() if g_ent is not None else None, getattr(head, "main_grad", None))
             if state.get("positions") is not None:
                 g_hN = torch.zeros(hN.shape, dtype=torch.float32, device=hN.device)
                 g_hN.index_add_(0, state["positions"], g_hS.float())  # positions may repeat (shared prefixes)

@@ -220,9 +220,10 @@ def lmhead_logprob_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: t
     return _torch_logprob_entropy(hidden, weight, labels, inv_temp)
 
 
-def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_ent, dweight_out: torch.Tensor,
+def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_ent, dweight_out: Optional[torch.Tensor],
                     vocab_chunk: int = 9728):
-    """Returns d_hidden (same dtype as hidden) and accumulates d_weight into ``dweight_out`` (fp32 [V, H])."""
+    """Returns d_hidden (same dtype as hidden) and accumulates d_weight into ``dweight_out`` (fp32 [V, H]); a frozen head
+    (``dweight_out`` None) skips the weight-gradient GEMMs."""
     inv_temp = 1.0 / max(float(temperature), 1e-8)
     T, H = hidden.shape
     V = weight.shape[0]
@@ -235,7 +236,8 @@ def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_e
             ex = (lse - entropy).unsqueeze(1)
             dl = dl - g_ent.unsqueeze(1) * p * (logits - ex)
         dl = dl * inv_temp
-        dweight_out.add_(dl.t() @ hidden.float())
+        if dweight_out is not None:
+            dweight_out.add_(dl.t() @ hidden.float())
         return (dl @ weight.float()).to(hidden.dtype)
     ops = _ops()
     ex = (lse - entropy).contiguous() if g_ent is not None else None
@@ -251,7 +253,8 @@ def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_e
         # d_hidden += dl @ W[v0:v1]      (B stored [K=Vc, N=H] -> MN-major)
         gemm(dl, wc, out=dh, b_mn=True, out_f32=True, accumulate=True)
         # d_W[v0:v1] += dl^T @ hidden
-        gemm(dl, hidden, out=dweight_out[v0:v1], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+        if dweight_out is not None:
+            gemm(dl, hidden, out=dweight_out[v0:v1], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
     return dh.to(hidden.dtype)
 
 

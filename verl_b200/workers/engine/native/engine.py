@@ -177,6 +177,7 @@ class NativeEngine(BaseEngine):
             self.params = self._shared_params
         else:
             want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
+                          and not int(getattr(self.model_config, "lora_rank", 0) or 0)
                           and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
                           and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
             buf = None
@@ -199,6 +200,17 @@ class NativeEngine(BaseEngine):
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
+        # trainable parameters: the whole model, or low-rank adapters on a frozen base (``model.lora_rank`` > 0)
+        self.tparams = self.params
+        self.lora = None
+        lora_rank = int(getattr(self.model_config, "lora_rank", 0) or 0)
+        if lora_rank > 0 and not self.forward_only:
+            from ....models.lora import LoRAParams
+
+            assert not self.fused_comm, "LoRA uses the collective-library optimizer path (set fused_comm=false)"
+            self.lora = LoRAParams(self.params, lora_rank, float(getattr(self.model_config, "lora_alpha", 16) or 16),
+                                   getattr(self.model_config, "target_modules", None), pad_to=self.world, seed=seed)
+            self.tparams = self.lora
         # Ulysses sequence parallelism: blocks of ``sp`` consecutive ranks work on the same micro-batches
         self.sp_size = int(getattr(ec, "ulysses_sequence_parallel_size", 1) or 1)
         self.sp_group, self.sp_rank = None, 0
@@ -220,14 +232,14 @@ class NativeEngine(BaseEngine):
             from ....utils.activation_offload import ActivationOffloader
 
             self.model.offloader = ActivationOffloader(self.device)
-        self.shard_numel = self.params.numel // self.world
+        self.shard_numel = self.tparams.numel // self.world
         self.shard_lo = self.rank * self.shard_numel
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
         # memory (4 bytes/param) is available to the rollout KV cache in between.
         self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
         if not self.forward_only:
             sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-            self.master = self.params.flat[sl].float().clone()
+            self.master = self.tparams.flat[sl].float().clone()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
             self.grad_shard = None
@@ -258,8 +270,8 @@ class NativeEngine(BaseEngine):
             return self.arch.num_hidden_layers
         free, _ = torch.cuda.mem_get_info(self.device)
         free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-        if self.lazy_grad and getattr(self.params, "main_grad", None) is None:
-            free -= self.params.numel * 4  # the fp32 gradient buffer is allocated on the first backward
+        if self.lazy_grad and getattr(self.tparams, "main_grad", None) is None:
+            free -= self.tparams.numel * 4  # the fp32 gradient buffer is allocated on the first backward
         keep = int(0.6 * max(0, free) // max(1, per_layer))
         self.last_kept_layers = keep
         return keep
@@ -435,9 +447,9 @@ class NativeEngine(BaseEngine):
 
     # ------------------------------------------------------------------------------------ optimizer
     def _alloc_grads(self) -> None:
-        self.params.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
+        self.tparams.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-        self.grad_shard = self.params.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+        self.grad_shard = self.tparams.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
 
     def _global_sumsq_correction(self) -> None:
         """Hook for model-parallel engines: ``ctrl[0]`` (sum of squared gradients over the data-parallel group) becomes
@@ -447,17 +459,17 @@ class NativeEngine(BaseEngine):
     def optimizer_zero_grad(self) -> None:
         if self.forward_only:
             return
-        if self.params.main_grad is None:
+        if self.tparams.main_grad is None:
             self._alloc_grads()
         else:
-            self.params.zero_grad()
+            self.tparams.zero_grad()
 
     def optimizer_step(self) -> float:
         """Gradient mean over DP ranks, global-norm clip, AdamW on this rank's shard, publish new bf16 weights.
         A non-finite gradient norm skips the update. Returns the gradient norm."""
         oc = self.optimizer_config
         W = self.world
-        mg = self.params.main_grad
+        mg = self.tparams.main_grad
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if self.fused_comm:
             return self._fused_optimizer_step()
@@ -477,7 +489,7 @@ class NativeEngine(BaseEngine):
                 dist.all_reduce(self.ctrl[:1], group=self.group)
             self._global_sumsq_correction()
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
-            ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.params.flat[sl], self.ctrl,
+            ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.tparams.flat[sl], self.ctrl,
                        lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
                        self.opt_step_count, 1.0, False)
             norm = self.ctrl[3]
@@ -500,11 +512,13 @@ class NativeEngine(BaseEngine):
                 self.master.mul_(1 - lr * oc.weight_decay)
                 denom = (self.exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(oc.eps)
                 self.master.addcdiv_(self.exp_avg, denom, value=-lr / bc1)
-                self.params.flat[sl].copy_(self.master.to(self.dtype))
+                self.tparams.flat[sl].copy_(self.master.to(self.dtype))
         self._publish_shard()
+        if self.lora is not None:
+            self.lora.merge()  # the working weights (shared with the rollout engine) follow the adapters
         norm = float(norm)
         if self.lazy_grad:
-            self.params.detach_main_grad()
+            self.tparams.detach_main_grad()
             self.grad_shard = None
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
@@ -541,10 +555,10 @@ class NativeEngine(BaseEngine):
             return
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if self.device.type == "cuda":
-            dist.all_gather_into_tensor(self.params.flat, self.params.flat[sl].clone(), group=self.group)
+            dist.all_gather_into_tensor(self.tparams.flat, self.tparams.flat[sl].clone(), group=self.group)
         else:
-            parts = [self.params.flat[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
-            dist.all_gather(parts, self.params.flat[sl].clone(), group=self.group)
+            parts = [self.tparams.flat[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
+            dist.all_gather(parts, self.tparams.flat[sl].clone(), group=self.group)
 
     def lr_scheduler_step(self) -> float:
         self.sched_step += 1
@@ -575,9 +589,9 @@ class NativeEngine(BaseEngine):
         contents = list(getattr(self.checkpoint_config, "save_contents", ["model", "optimizer", "extra"]) or [])
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if "model" in contents:
-            src = self.master if not self.forward_only else self.params.flat[sl].float()
-            torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.params.numel,
-                        "offsets": self.params.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
+            src = self.master if not self.forward_only else self.tparams.flat[sl].float()
+            torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.tparams.numel,
+                        "offsets": self.tparams.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
         if "optimizer" in contents and not self.forward_only:
             torch.save({"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "step": self.opt_step_count},
                        os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt"))
@@ -590,6 +604,8 @@ class NativeEngine(BaseEngine):
                 json.dump({"FSDP_version": 2, "world_size": W, "layout": "verl_b200.flat", "value_head": self.value_head}, f)
             hf_dir = os.path.join(local_path, "huggingface")
             self.arch.save_pretrained(hf_dir)
+            if self.lora is not None:
+                self.lora.save_adapter(os.path.join(local_path, "lora_adapter"), str(getattr(self.model_config, "path", "")))
             if "hf_model" in contents:
                 from ....utils.model import save_hf_weights
 
@@ -607,11 +623,13 @@ class NativeEngine(BaseEngine):
         mp = os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt")
         if "model" in contents and os.path.exists(mp):
             st = torch.load(mp, map_location="cpu", weights_only=False)
-            assert st["numel"] == self.params.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
+            assert st["numel"] == self.tparams.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
             if not self.forward_only:
                 self.master.copy_(st["flat_shard"])
-            self.params.flat[sl].copy_(st["flat_shard"].to(self.dtype))
+            self.tparams.flat[sl].copy_(st["flat_shard"].to(self.dtype))
             self._publish_shard()
+            if self.lora is not None:
+                self.lora.merge()
         op = os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt")
         if "optimizer" in contents and not self.forward_only and os.path.exists(op):
             st = torch.load(op, map_location="cpu", weights_only=False)
