@@ -12,10 +12,17 @@
 //   dK  += dS^T Q            [128 keys, hd]     A = dS^T (K-major)   B = Q  (MN-major)       TMEM-resident
 //   dQ^T = K^T dS^T          [hd, 64 q]         A = K  (MN-major)    B = dS^T (MN-major)     -> fp32 atomics into dQ
 //
+// dQ^T has two TMEM buffers: the atomics of step i run after the softmax warps have handed P^T / dS^T of step i + 1 to
+// the MMA warp, i.e. under the tensor-core work of step i + 1 instead of in front of it.
+// Grid = (KV head, sequence, key block counted from the END of the sequence, longest first): blocks are handed out in
+// order of decreasing work (the first key block meets every query block, the last one only its own), which keeps the
+// tail of the launch short.
+//
 //   warp 0      TMA: K, V once; Q and dO tiles through a 2-stage ring
 //   warp 1      MMA issue (one elected thread)
-//   warps 2..5  thread == key row: tcgen05.ld S^T / dP^T -> P^T, dS^T -> swizzled shared memory; drain dQ^T with
-//               coalesced red.add (lanes = 32 consecutive head-dim elements of one query); final dK / dV store
+//   warps 2..9  two threads per key row (32 of the step's 64 queries each): tcgen05.ld S^T / dP^T -> P^T, dS^T ->
+//               swizzled shared memory; drain dQ^T with coalesced red.add (lanes = 32 consecutive head-dim elements of
+//               one query); final dV (warps 2..5) / dK (warps 6..9) store
 // D[q] = sum_d dO[q,d] O[q,d] comes from a small pre-pass; dQ is accumulated in fp32 and converted afterwards.
 #include "tcgen05_common.cuh"
 
@@ -25,11 +32,11 @@ namespace vb {
 
 constexpr int AB_BK = 128;  // keys per CTA
 constexpr int AB_BQ = 64;   // queries per step
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;  // TMA warp, MMA warp, eight softmax warps
 
 struct AttnBwdParams {
   const int* cu_seqlens;
-  int num_seqs, nh, nkv, total_tokens;
+  int num_seqs, nh, nkv, total_tokens, max_tiles;  // max_tiles: key blocks of the longest sequence
   const float* lse;    // [nh, T] natural log
   const float* delta;  // [nh, T]
   float* dq32;         // [T, nh*hd] fp32, zero on entry
@@ -51,8 +58,8 @@ struct AttnBwdSmem {
   static constexpr int OFF_DO = OFF_Q + 2 * QO_BYTES;     // 2 stages
   static constexpr int OFF_P = OFF_DO + 2 * QO_BYTES;
   static constexpr int OFF_DS = OFF_P + PS_BYTES;
-  static constexpr int OFF_VEC = OFF_DS + PS_BYTES;       // per softmax warp: [2 steps][lse2 | delta][64] fp32
-  static constexpr int OFF_BAR = OFF_VEC + 4 * 2 * 2 * AB_BQ * 4;
+  static constexpr int OFF_VEC = OFF_DS + PS_BYTES;       // per softmax warp (8): [2 steps][lse2 | delta][32] fp32
+  static constexpr int OFF_BAR = OFF_VEC + 8 * 2 * 2 * 32 * 4;
   static constexpr int TOTAL = OFF_BAR + 128 + 1024;
 };
 
@@ -71,7 +78,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sDO = smem + L::OFF_DO;
   uint8_t* sP = smem + L::OFF_P;
   uint8_t* sDS = smem + L::OFF_DS;
-  float* sVec = reinterpret_cast<float*>(smem + L::OFF_VEC);  // [4 warps][2 steps][lse2 | delta][64]
+  float* sVec = reinterpret_cast<float*>(smem + L::OFF_VEC);  // [8 warps][2 steps][lse2 | delta][32]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars;        // 1
   uint64_t* qdo_full = bars + 1;   // 2
@@ -80,24 +87,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_pds = bars + 6;    // P^T, dS^T written (4 warps)
   uint64_t* bar_dq = bars + 7;     // dV, dK, dQ^T MMAs of a step done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
-  __shared__ int s_tile[4];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x;
   const int G = p.nh / p.nkv;
+  const int seq_start = p.cu_seqlens[blockIdx.y];
+  const int seqlen = p.cu_seqlens[blockIdx.y + 1] - seq_start;
+  const int from_end = p.max_tiles - 1 - static_cast<int>(blockIdx.z);
+  const int ntiles = (seqlen + AB_BK - 1) / AB_BK;
+  if (from_end >= ntiles) return;  // shorter sequence: uniform over the CTA, nothing allocated yet
+  if (ntiles > p.max_tiles && blockIdx.z == 0 && threadIdx.x == 0) atomicExch(p.status, ST_BAD_ARGS);  // max_seqlen too small
+  const int k0 = (ntiles - 1 - from_end) * AB_BK;
 
   if (threadIdx.x == 0) {
-    int t = blockIdx.x, found = 0, start = 0, k0 = 0, len = 0;
-    for (int s = 0; s < p.num_seqs; ++s) {
-      const int a = p.cu_seqlens[s], b = p.cu_seqlens[s + 1];
-      const int nt = (b - a + AB_BK - 1) / AB_BK;
-      if (t < nt) {
-        start = a; len = b - a; k0 = t * AB_BK; found = 1;  // early key blocks (most query blocks) come first
-        break;
-      }
-      t -= nt;
-    }
-    s_tile[0] = start; s_tile[1] = k0; s_tile[2] = len; s_tile[3] = found;
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -108,7 +110,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&qdo_empty[i], 1);
     }
     mbar_init(bar_sdp, 1);
-    mbar_init(bar_pds, 4);
+    mbar_init(bar_pds, 8);
     mbar_init(bar_dq, 1);
     mbar_fence_init();
   }
@@ -120,17 +122,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const int seq_start = s_tile[0], k0 = s_tile[1], seqlen = s_tile[2];
-  const bool valid_tile = s_tile[3] != 0;
   const int i0 = k0 / AB_BQ;                                    // first query block at or below the diagonal
-  const int nqb = valid_tile ? (seqlen + AB_BQ - 1) / AB_BQ : 0;
-  const int per_head = valid_tile ? nqb - i0 : 0;
+  const int nqb = (seqlen + AB_BQ - 1) / AB_BQ;
+  const int per_head = nqb - i0;
   const int n_it = per_head * G;
   constexpr uint32_t TM_DV = 0, TM_DK = HD, TM_S = 2 * HD, TM_DP = 2 * HD + AB_BQ, TM_DQ = 2 * HD + 2 * AB_BQ;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_it > 0) {
+    if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
 #pragma unroll
       for (int c = 0; c < PANELS; ++c) {
@@ -202,7 +202,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int k = 0; k < AB_BK / 16; ++k) {  // contraction over the 128 keys
           const uint64_t da = make_smem_desc_sw128(aK + k * 2048, AB_BK * 128, 1024);
           const uint64_t db = make_smem_desc_sw128(aDS + k * 2048, AB_BK * 128, 1024);
-          tc_mma_f16_ss(tmem_base + TM_DQ, da, db, idesc_dq, k > 0 ? 1u : 0u);
+          tc_mma_f16_ss(tmem_base + TM_DQ + (it & 1) * AB_BQ, da, db, idesc_dq, k > 0 ? 1u : 0u);
         }
         tc_commit(&qdo_empty[st]);
         tc_commit(bar_dq);
@@ -210,96 +210,112 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!ok) atomicExch(p.status, ST_TIMEOUT_MMA);
     }
   } else if (n_it > 0) {
-    // ------------------------------------------------------------------ softmax backward / drains (thread == key row)
+    // ------------------------------------------------------------------ softmax backward / drains
+    // Eight warps: warp w serves TMEM lane quarter w % 4 (thread == key row) and the query columns of half (w - 2) / 4,
+    // so every key row is shared by two threads that never need each other's values.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;   // 0: query columns 0..31 of the step, 1: columns 32..63
     const int r = q * 32 + lane;
     const int key = k0 + r;  // key index inside the sequence; also the head-dim index when draining dQ^T
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    const int cbase = half * 32;
     bool ok = true;
     constexpr float LOG2E = 1.4426950408889634f;
 
     auto drain_dq = [&](int it) {
       const int head = kvh * G + it / per_head;
-      const int q0 = (i0 + it % per_head) * AB_BQ;
-      float* base = p.dq32 + static_cast<long long>(seq_start + q0) * (static_cast<long long>(p.nh) * HD) +
-                    static_cast<long long>(head) * HD + r;
-#pragma unroll 1
-      for (int c = 0; c < AB_BQ / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + TM_DQ + c * 32 + lane_off, v);
-        tmem_ld_wait();
+      const int q0 = (i0 + it % per_head) * AB_BQ + cbase;
+      const long long row_stride = static_cast<long long>(p.nh) * HD;
+      float* base = p.dq32 + static_cast<long long>(seq_start + q0) * row_stride + static_cast<long long>(head) * HD + r;
+      uint32_t v[32];
+      tmem_ld_32x32(tmem_base + TM_DQ + (it & 1) * AB_BQ + cbase + lane_off, v);
+      tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (q0 + c * 32 + j < seqlen)
-            atomicAdd(base + static_cast<long long>(c * 32 + j) * (static_cast<long long>(p.nh) * HD), __uint_as_float(v[j]));
-        }
+      for (int j = 0; j < 32; ++j) {
+        if (q0 + j < seqlen) atomicAdd(base + j * row_stride, __uint_as_float(v[j]));
       }
     };
 
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int head = kvh * G + it / per_head;
-      const int q0 = (i0 + it % per_head) * AB_BQ;
-      // stage lse (log2 domain) and delta of the 64 queries of this step: every warp keeps its own copy, so no
-      // barrier across warps is needed (a warp that gave up on a wait cannot leave the others stuck)
-      float* vL = sVec + ((q * 2 + (it & 1)) * 2) * AB_BQ;
-      float* vD = vL + AB_BQ;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int c = lane + 32 * u;
-        float l2 = 0.f, de = 0.f;
-        if (q0 + c < seqlen) {
-          const long long o = static_cast<long long>(head) * p.total_tokens + seq_start + q0 + c;
-          l2 = p.lse[o] * LOG2E;
-          de = p.delta[o];
-        }
-        vL[c] = l2;
-        vD[c] = de;
+    // lse (log2 domain) and delta of this warp's 32 queries of a step, one query per lane; fetched one step ahead
+    float nl2 = 0.f, nde = 0.f;
+    auto fetch_vec = [&](int it) {
+      const int qi = (i0 + it % per_head) * AB_BQ + cbase + lane;
+      nl2 = 0.f;
+      nde = 0.f;
+      if (it < n_it && qi < seqlen) {
+        const long long o = static_cast<long long>(kvh * G + it / per_head) * p.total_tokens + seq_start + qi;
+        nl2 = p.lse[o] * LOG2E;
+        nde = p.delta[o] * p.scale;
       }
+    };
+    fetch_vec(0);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int q0 = (i0 + it % per_head) * AB_BQ;
+      // a private copy per warp, so no barrier across warps is needed (a warp that gave up on a wait cannot leave the
+      // others stuck)
+      float* vL = sVec + (((warp - 2) * 2 + (it & 1)) * 2) * 32;
+      float* vD = vL + 32;
+      vL[lane] = nl2;
+      vD[lane] = nde;
       __syncwarp();
+      fetch_vec(it + 1);
       if (!mbar_wait(bar_sdp, it & 1)) { ok = false; break; }
       tc_fence_after();
-      uint32_t pk[32], dk[32];  // packed bf16 pairs of P^T and dS^T for this key row (64 queries)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      uint32_t pk[16], dk[16];  // packed bf16 pairs of P^T and dS^T: this key row, this warp's 32 queries
+      {
         uint32_t s[32], dp[32];
-        tmem_ld_32x32(tmem_base + TM_S + h * 32 + lane_off, s);
-        tmem_ld_32x32(tmem_base + TM_DP + h * 32 + lane_off, dp);
+        tmem_ld_32x32(tmem_base + TM_S + cbase + lane_off, s);
+        tmem_ld_32x32(tmem_base + TM_DP + cbase + lane_off, dp);
         tmem_ld_wait();
+        // only the blocks on the diagonal and the last (partial) query block of the sequence need the mask
+        const bool masked = (q0 < k0 + AB_BK) || (q0 + AB_BQ > seqlen);
+        const float4* vL4 = reinterpret_cast<const float4*>(vL);
+        const float4* vD4 = reinterpret_cast<const float4*>(vD);
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dsv[2];
+        for (int c = 0; c < 32; c += 4) {
+          const float4 l4 = vL4[c >> 2], d4 = vD4[c >> 2];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv_[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dsv[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = h * 32 + c + u;
-            const int qi = q0 + col;
-            const bool live = (key <= qi) && (qi < seqlen);
-            const float pe = live ? exp2f(__uint_as_float(s[c + u]) * p.scale_log2 - vL[col]) : 0.f;
+          for (int u = 0; u < 4; ++u) {
+            float pe = exp2f(fmaf(__uint_as_float(s[c + u]), p.scale_log2, -lv[u]));
+            if (masked) {
+              const int qi = q0 + cbase + c + u;
+              if (!((key <= qi) && (qi < seqlen))) pe = 0.f;
+            }
             pv[u] = pe;
-            dsv[u] = pe * (__uint_as_float(dp[c + u]) - vD[col]) * p.scale;
+            dsv[u] = pe * fmaf(__uint_as_float(dp[c + u]), p.scale, -dv_[u]);  // delta is stored pre-multiplied by scale
           }
-          pk[h * 16 + (c >> 1)] = pack_bf16x2(pv[0], pv[1]);
-          dk[h * 16 + (c >> 1)] = pack_bf16x2(dsv[0], dsv[1]);
+          pk[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pk[(c >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
+          dk[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+          dk[(c >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
       }
       tc_fence_before();
       if (it > 0) {
-        // P^T / dS^T buffers and the dQ^T columns are still in use by the MMAs of the previous step
+        // the P^T / dS^T buffers are still read by the MMAs of the previous step
         if (!mbar_wait(bar_dq, (it - 1) & 1)) { ok = false; break; }
         tc_fence_after();
-        drain_dq(it - 1);
       }
       uint8_t* prow = sP + r * 128;
       uint8_t* drow = sDS + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const int sw = (ch ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dk[ch * 4], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
+      for (int c4 = 0; c4 < 4; ++c4) {  // this warp's four 16-byte chunks of the 128-byte row
+        const int sw = ((half * 4 + c4) ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk[c4 * 4], pk[c4 * 4 + 1], pk[c4 * 4 + 2], pk[c4 * 4 + 3]);
+        *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dk[c4 * 4], dk[c4 * 4 + 1], dk[c4 * 4 + 2], dk[c4 * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
+      if (it > 0) {
+        // dQ^T of the previous step sits in the other TMEM buffer; its next writer is the MMA of step it + 1, which
+        // waits for this warp's next arrival
+        drain_dq(it - 1);
+        tc_fence_before();
+      }
     }
     if (ok) ok = mbar_wait(bar_dq, (n_it - 1) & 1);
     if (!ok) {
@@ -307,28 +323,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else {
       tc_fence_after();
       drain_dq(n_it - 1);
-      // dK, dV of this key block: exclusive to this CTA, plain stores (the TMEM loads are warp-wide, the stores are
-      // predicated on the key being inside the sequence)
+      // dV (first four warps) and dK (last four) of this key block: exclusive to this CTA, plain stores; the TMEM loads
+      // are warp-wide, the stores are predicated on the key being inside the sequence
       const bool key_ok = key < seqlen;
       const long long tok = static_cast<long long>(seq_start) + key;
+      __nv_bfloat16* dst = (half == 0 ? p.dv + tok * p.lddv : p.dk + tok * p.lddk) + static_cast<long long>(kvh) * HD;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dv + tok * p.lddv : p.dk + tok * p.lddk) + static_cast<long long>(kvh) * HD;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32(tmem_base + (which == 0 ? TM_DV : TM_DK) + c * 32 + lane_off, o);
-          tmem_ld_wait();
-          if (key_ok) {
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_base + (half == 0 ? TM_DV : TM_DK) + c * 32 + lane_off, o);
+        tmem_ld_wait();
+        if (key_ok) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
-              v.y = pack_bf16x2(__uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
-              v.z = pack_bf16x2(__uint_as_float(o[i + 4]), __uint_as_float(o[i + 5]));
-              v.w = pack_bf16x2(__uint_as_float(o[i + 6]), __uint_as_float(o[i + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
-            }
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[i]), __uint_as_float(o[i + 1]));
+            v.y = pack_bf16x2(__uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
+            v.z = pack_bf16x2(__uint_as_float(o[i + 4]), __uint_as_float(o[i + 5]));
+            v.w = pack_bf16x2(__uint_as_float(o[i + 6]), __uint_as_float(o[i + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
           }
         }
       }
@@ -390,8 +403,9 @@ extern "C" int vb_attn_bwd(const void* q, const void* k, const void* v, const vo
                            long long ldk, long long ldv, long long ldo, long long lddo, const float* lse,
                            const int* cu_seqlens, int num_seqs, int total_tokens, int nh, int nkv, int hd, float scale,
                            void* dq, void* dk, void* dv, long long lddq, long long lddk, long long lddv, float* delta_ws,
-                           float* dq32_ws, cudaStream_t stream) {
+                           float* dq32_ws, int max_seqlen, cudaStream_t stream) {
   if (total_tokens <= 0 || num_seqs <= 0) return 0;
+  if (max_seqlen <= 0 || num_seqs > 65535) return -4;
   if (hd != 128) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || (lddo % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8) || (nh % nkv)) return -1;
   CUtensorMap tq, tk, tv, tdo;
@@ -421,7 +435,9 @@ extern "C" int vb_attn_bwd(const void* q, const void* k, const void* v, const vo
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid((total_tokens + AB_BK - 1) / AB_BK + num_seqs, nkv);
+  p.max_tiles = (max_seqlen + AB_BK - 1) / AB_BK;
+  if (p.max_tiles > 65535) return -4;
+  dim3 grid(nkv, num_seqs, p.max_tiles);
   kern<<<grid, AB_THREADS, smem, stream>>>(tq, tk, tv, tdo, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);

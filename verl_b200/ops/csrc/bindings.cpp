@@ -125,7 +125,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& dout, const Tensor& q,
                              v.stride(0), out.stride(0), dout.stride(0), lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
                              (int)cu_seqlens.numel() - 1, (int)T, (int)nh, (int)nkv, (int)hd, (float)scale, dq.data_ptr(),
                              dk.data_ptr(), dv.data_ptr(), dq.stride(0), dk.stride(0), dv.stride(0), delta.data_ptr<float>(),
-                             dq32.data_ptr<float>(), cur_stream());
+                             dq32.data_ptr<float>(), (int)max_seqlen, cur_stream());
   CHECK_RC(rc, "vb_attn_bwd");
   return {dq, dk, dv};
 }

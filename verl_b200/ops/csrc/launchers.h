@@ -62,7 +62,7 @@ int vb_attn_status();
 int vb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, long long ldq, long long ldk,
                 long long ldv, long long ldo, long long lddo, const float* lse, const int* cu_seqlens, int num_seqs,
                 int total_tokens, int nh, int nkv, int hd, float scale, void* dq, void* dk, void* dv, long long lddq,
-                long long lddk, long long lddv, float* delta_ws, float* dq32_ws, cudaStream_t stream);
+                long long lddk, long long lddv, float* delta_ws, float* dq32_ws, int max_seqlen, cudaStream_t stream);
 int vb_attn_bwd_status();
 // paged_decode_tma.cu
 int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, const void* vc, long long num_slots,

@@ -422,19 +422,18 @@ def enable_native_attention(forward: bool = True, backward: bool = True) -> None
         _ATTN_IMPL["bwd"] = _native_attn_bwd
 
 
-if torch.cuda.is_available():  # the tcgen05 forward kernel is the default attention path on a GPU
-    _ATTN_IMPL["fwd"] = _native_attn_fwd
-
-
 def _native_attn_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale):
     return _ops().attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_seqlens.to(torch.int32), int(max_seqlen), float(scale))
 
 
-# the tcgen05 backward kernel (head_dim 128) is opt-in: VERL_B200_NATIVE_ATTN_BWD=1 or enable_native_attention()
+# On a GPU the tcgen05 kernels are the attention path: forward for head_dim 64 / 128, backward for head_dim 128 (other
+# head sizes differentiate through the reference formulation). VERL_B200_NATIVE_ATTN_BWD=0 keeps the backward off.
 import os as _os
 
-if torch.cuda.is_available() and _os.environ.get("VERL_B200_NATIVE_ATTN_BWD", "0") == "1":
-    _ATTN_IMPL["bwd"] = _native_attn_bwd
+if torch.cuda.is_available():
+    _ATTN_IMPL["fwd"] = _native_attn_fwd
+    if _os.environ.get("VERL_B200_NATIVE_ATTN_BWD", "1") != "0":
+        _ATTN_IMPL["bwd"] = _native_attn_bwd
 
 
 # ----------------------------------------------------------------------------------------------- fp8 block scaling
