@@ -135,7 +135,7 @@ class EngineRegistry:
         from ...utils.device import get_device_name
 
         device = device or get_device_name()
-        if backend in ("megatron", "mp") and backend not in cls._engines.get(model_type, {}):
+        if backend in ("megatron", "mp", "mindspeed") and backend not in cls._engines.get(model_type, {}):
             from . import mp  # noqa: F401  (registers the tensor x pipeline parallel engines)
         try:
             return cls._engines[model_type][backend][device]

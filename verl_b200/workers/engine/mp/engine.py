@@ -245,12 +245,12 @@ class ModelParallelEngine(NativeEngine):
                 self.params.views[m.local_name].copy_(tensors[m.full_name].to(self.dtype))
 
 
-@EngineRegistry.register(model_type="language_model", backend=["megatron", "mp"], device=["cuda", "cpu"])
+@EngineRegistry.register(model_type="language_model", backend=["megatron", "mp", "mindspeed"], device=["cuda", "cpu"])
 class ModelParallelEngineWithLMHead(ModelParallelEngine):
     value_head = False
 
 
-@EngineRegistry.register(model_type="value_model", backend=["megatron", "mp"], device=["cuda", "cpu"])
+@EngineRegistry.register(model_type="value_model", backend=["megatron", "mp", "mindspeed"], device=["cuda", "cpu"])
 class ModelParallelEngineWithValueHead(ModelParallelEngine):
     """Critic: the last stage ends in a scalar head; ``model_output`` carries ``values`` [b, R]."""
 
