@@ -483,32 +483,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           constexpr int RPI = 32 / LPR;  // rows per iteration
           const long long half = static_cast<long long>(ar_epoch_now & 1u) * p.ar_buf_elems;
           const int col = n0 + (lane % LPR) * 8;
+          // eight row groups are fetched per round trip: a peer read costs microseconds of latency, so the loads of a
+          // rank are all issued before the first one is consumed
+          constexpr int UNR = 8;
+          const bool col_ok = col < p.N;
 #pragma unroll 1
-          for (int rr = 0; rr < 32; rr += RPI) {
-            const int orow = m0 + q * 32 + rr + lane / LPR;
-            if (orow >= p.M || col >= p.N) continue;
-            const long long off = half + static_cast<long long>(orow) * p.N + col;
-            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int r = 0; r < p.ar_world; ++r) {
-              const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.ar_part[r]) + off);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+          for (int rr = 0; rr < 32; rr += RPI * UNR) {
+            long long off[UNR];
+            bool ok[UNR];
+            float acc8[UNR][8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f2 = __bfloat1622float2(h[j]);
-                acc8[2 * j] += f2.x;
-                acc8[2 * j + 1] += f2.y;
+            for (int u = 0; u < UNR; ++u) {
+              const int orow = m0 + q * 32 + rr + u * RPI + lane / LPR;
+              ok[u] = col_ok && orow < p.M;
+              off[u] = half + static_cast<long long>(orow) * p.N + col;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc8[u][j] = 0.f;
+            }
+            for (int r = 0; r < p.ar_world; ++r) {
+              const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.ar_part[r]);
+              uint4 v[UNR];
+#pragma unroll
+              for (int u = 0; u < UNR; ++u) v[u] = ok[u] ? __ldcg(reinterpret_cast<const uint4*>(src + off[u])) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int u = 0; u < UNR; ++u) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f2 = __bfloat1622float2(h[j]);
+                  acc8[u][2 * j] += f2.x;
+                  acc8[u][2 * j + 1] += f2.y;
+                }
               }
             }
-            if (p.bias != nullptr) {
+            float bias8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (p.bias != nullptr && col_ok) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+              for (int j = 0; j < 8; ++j) bias8[j] = __bfloat162float(p.bias[col + j]);
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc8[0], acc8[1]);
-            o.y = pack_bf16x2(acc8[2], acc8[3]);
-            o.z = pack_bf16x2(acc8[4], acc8[5]);
-            o.w = pack_bf16x2(acc8[6], acc8[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow) * p.ldd + col) = o;
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+              if (!ok[u]) continue;
+              const int orow = m0 + q * 32 + rr + u * RPI + lane / LPR;
+              uint4 o;
+              o.x = pack_bf16x2(acc8[u][0] + bias8[0], acc8[u][1] + bias8[1]);
+              o.y = pack_bf16x2(acc8[u][2] + bias8[2], acc8[u][3] + bias8[3]);
+              o.z = pack_bf16x2(acc8[u][4] + bias8[4], acc8[u][5] + bias8[5]);
+              o.w = pack_bf16x2(acc8[u][6] + bias8[6], acc8[u][7] + bias8[7]);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow) * p.ldd + col) = o;
+            }
           }
         }
       }

@@ -1,0 +1,183 @@
+"""Micro-benchmarks of the fused compute + collective kernels against their NCCL formulation (2 to 8 GPUs of one node).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 -m verl_b200.parallel.bench_fused
+
+Every case is timed with CUDA events on the launching stream after warm-up, the time of an iteration is the MAX over
+ranks, and rank 0 prints one JSON line per case with the roofline of the fused path: the slower of (FLOPs / measured
+GEMM peak), (HBM bytes / measured copy bandwidth) and (bytes that must cross NVLink per GPU and direction / the measured
+peer-copy bandwidth, 770 GB/s).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0  # measured peer copy, one direction, per GPU
+
+
+def _peaks() -> dict:
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        d = json.load(open(os.path.join(here, "MEASURED_PEAKS.json")))
+        out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        pass
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--numel", type=int, default=1 << 28, help="elements of the gradient / parameter buffer (cases rs, ag)")
+    a = ap.parse_args(argv)
+    only = set(filter(None, a.only.split(",")))
+    want = lambda name: not only or name in only
+
+    from ..ops import native
+    from ..ops import functional as F
+    from ..utils.distributed import initialize_global_process_group
+    from .symmetric import FusedRowParallelLinear, PeerBarrier, SymmetricBuffer
+
+    initialize_global_process_group()
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    ops = native.ops()
+    pk = _peaks()
+    tag = "of measured" if pk["source"] == "measured" else "of fallback"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bar = PeerBarrier(dev)
+
+    def timed(fn) -> float:
+        """Mean over iterations of the max over ranks of the device time of ``fn`` (ms)."""
+        for _ in range(a.warmup):
+            fn()
+        torch.cuda.synchronize()
+        per_iter = []
+        for _ in range(a.iters):
+            flush.zero_()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            per_iter.append(e0.elapsed_time(e1))
+        t = torch.tensor(per_iter, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.mean())
+
+    def report(name, shape, ms_fused, ms_nccl, flops=0.0, hbm_bytes=0.0, link_bytes=0.0):
+        floor_ms = max(flops / (pk["bf16_tflops"] * 1e9), hbm_bytes / (pk["hbm_gbs"] * 1e6), link_bytes / (NVLINK_GBS * 1e6))
+        if rank == 0:
+            print(json.dumps({"case": name, "world": world, "shape": shape, "ms_fused": round(ms_fused, 4),
+                              "ms_nccl_formulation": None if ms_nccl is None else round(ms_nccl, 4),
+                              "speedup": None if ms_nccl is None else round(ms_nccl / ms_fused, 3),
+                              "roofline_ms": round(floor_ms, 4), "frac_of_roofline": round(floor_ms / ms_fused, 3),
+                              "link_gbs": round(link_bytes / ms_fused / 1e6, 1),
+                              "denominators": f"{pk['bf16_tflops']} TFLOP/s, {pk['hbm_gbs']} GB/s {tag}; NVLink {NVLINK_GBS} GB/s per direction"}),
+                  flush=True)
+
+    n = (a.numel // (world * 1024)) * world * 1024
+    shard = n // world
+    lo = rank * shard
+
+    if want("rs"):
+        # gradient mean reduce-scatter + sum of squares of the reduced shard
+        grads = SymmetricBuffer.allocate(n, torch.float32, dev)
+        grads.tensor.normal_()
+        out = torch.empty(shard, device=dev)
+        ctrl = torch.zeros(4, device=dev)
+
+        def fused():
+            bar()
+            ops.rs_sumsq_(grads.ptrs, 0, out, lo, rank, 1.0 / world, ctrl)
+            bar()
+
+        def nccl():
+            dist.reduce_scatter_tensor(out, grads.tensor, op=dist.ReduceOp.AVG)
+            ops.sumsq_(out, ctrl)
+
+        report("grad_reduce_scatter_sumsq", [n], timed(fused), timed(nccl), hbm_bytes=4.0 * shard * (world + 1),
+               link_bytes=4.0 * shard * (world - 1))
+        del grads
+    if want("ag"):
+        # AdamW on the shard + publication of the new bf16 weights into every replica
+        params = SymmetricBuffer.allocate(n, torch.bfloat16, dev)
+        master, g = torch.randn(shard, device=dev), torch.randn(shard, device=dev)
+        m, v = torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+        ctrl = torch.zeros(4, device=dev)
+        ctrl[1] = 1.0
+        flat = params.tensor
+
+        def fused():
+            bar()
+            ops.adamw_allgather_(master, g, m, v, params.ptrs, 0, lo, rank, ctrl, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1)
+            bar()
+
+        def nccl():
+            ops.adamw_(master, g, m, v, flat[lo : lo + shard], ctrl, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, False)
+            dist.all_gather_into_tensor(flat, flat[lo : lo + shard].clone())
+
+        report("adamw_allgather_bf16", [n], timed(fused), timed(nccl), hbm_bytes=shard * (4.0 * 7 + 2.0 * world),
+               link_bytes=2.0 * shard * (world - 1))
+        del params
+    if want("gemm_ar"):
+        # row-parallel linear (down projection of Qwen2.5-7B): partial GEMM + all-reduce
+        N, K = 3584, 18944
+        Kl = (K // world) // 64 * 64
+        for M in (320, 8192):
+            x = (torch.randn(M, Kl, device=dev) * 0.05).bfloat16()
+            w = (torch.randn(N, Kl, device=dev) * 0.05).bfloat16()
+            fl = FusedRowParallelLinear(max_rows=M, n=N, device=dev)
+            y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+
+            def fused():
+                fl(x, w, None, out=y)
+
+            def nccl():
+                F.gemm(x, w, out=y)
+                dist.all_reduce(y)
+
+            report("row_parallel_gemm_allreduce", [M, N, Kl], timed(fused), timed(nccl), flops=2.0 * M * N * Kl,
+                   hbm_bytes=2.0 * (M * Kl + N * Kl + 2 * M * N), link_bytes=2.0 * M * N * (world - 1))
+            del fl
+    if want("moe_ep"):
+        # expert-parallel MoE layer of Qwen3-30B-A3B: router + dispatch + grouped GEMMs + combine
+        from .expert_parallel import ExpertParallelMoE
+
+        E, top_k, H, I, T = 128, 8, 2048, 768, 8192
+        El = E // world
+        h = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+        gate = (torch.randn(E, H, device=dev) * 0.05).bfloat16()
+        wgu = (torch.randn(El, 2 * I, H, device=dev) * 0.05).bfloat16()
+        wd = (torch.randn(El, H, I, device=dev) * 0.05).bfloat16()
+        ep = ExpertParallelMoE(E, top_k, H, max_tokens=T, device=dev)
+
+        def fused():
+            ep.forward(h, gate, wgu, wd)
+
+        t_f = timed(fused)
+        # every routed copy whose expert lives on another GPU crosses the link twice (dispatch and combine)
+        link = 2.0 * T * top_k * H * (world - 1) / world
+        report("moe_expert_parallel_layer_fwd", [T, H, E, top_k, I], t_f, None, flops=2.0 * T * top_k * 3 * H * I,
+               hbm_bytes=2.0 * (El * 3 * H * I + 4 * T * top_k * H), link_bytes=link)
+        if rank == 0 and int(ep.dropped) != 0:
+            print(json.dumps({"case": "moe_expert_parallel_layer_fwd", "dropped_copies": int(ep.dropped)}))
+    code_g, code_c = int(ops.gemm_status()), int(ops.comm_status())
+    if code_g or code_c:
+        raise RuntimeError(f"kernel status: gemm {code_g}, comm {code_c}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
