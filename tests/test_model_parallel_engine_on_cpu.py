@@ -14,7 +14,7 @@ def _data(seed=0, b=4, L=24, R=16, V=500):
     return {"input_ids": ids, "attention_mask": am, "responses": ids[:, -R:], "response_mask": am[:, -R:]}
 
 
-def _proc(rank, world, port, tp, pp, q):
+def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama"):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                           VERL_ENGINE_DEVICE="cpu")
@@ -27,8 +27,9 @@ def _proc(rank, world, port, tp, pp, q):
         from verl_b200.workers.utils.losses import sft_loss
 
         initialize_global_process_group()
-        ec = McoreEngineConfig(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp, seed=7, micro_batch_size_per_gpu=2)
-        eng = EngineRegistry.new("language_model", "megatron", get_preset("tiny-llama"), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
+        ec = McoreEngineConfig(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp, expert_model_parallel_size=ep, seed=7,
+                               micro_batch_size_per_gpu=2 if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
+        eng = EngineRegistry.new("language_model", "megatron", get_preset(preset), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
         eng.initialize()
         dp = eng.topo.dp
         data = _data()
@@ -48,7 +49,7 @@ def _proc(rank, world, port, tp, pp, q):
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-def _run(world, tp, pp):
+def _run(world, tp, pp, ep=1, preset="tiny-llama"):
     import torch.multiprocessing as mp
 
     with socket.socket() as s:
@@ -56,7 +57,7 @@ def _run(world, tp, pp):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q)) for r in range(world)]
+    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset)) for r in range(world)]
     for p in ps:
         p.start()
     res = dict(q.get(timeout=300) for _ in range(world))
@@ -67,7 +68,7 @@ def _run(world, tp, pp):
     return res
 
 
-def _reference():
+def _reference(preset="tiny-llama"):
     os.environ["VERL_ENGINE_DEVICE"] = "cpu"
     from functools import partial
 
@@ -76,7 +77,7 @@ def _reference():
     from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
     from verl_b200.workers.utils.losses import sft_loss
 
-    eng = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
+    eng = NativeEngineWithLMHead(get_preset(preset), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
     eng.initialize()
     out = eng.train_batch(dict(_data()), partial(sft_loss, None))
     lp = eng.infer_batch(dict(_data()))["model_output"]["log_probs"]
@@ -96,6 +97,20 @@ def test_model_parallel_engine_matches_unsharded(world, tp, pp):
     for r in range(world):
         d = r // (tp * pp)
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[d], atol=1e-4), r
+
+
+def test_expert_parallel_engine_matches_unsharded():
+    """Two ranks, each with half of the experts and half of the batch: same gradient norm, same updated full model and the
+    same log-probs as one process that holds every expert and sees the whole batch."""
+    ref_norm, ref_lp, ref_flat = _reference("tiny-moe")
+    res = _run(2, 1, 1, ep=2, preset="tiny-moe")
+    rows = ref_lp.chunk(2)
+    for r in range(2):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert got.shape == ref_flat.shape
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r], atol=1e-4), r
 
 
 def _ppo_proc(rank, world, port, q):

@@ -137,6 +137,38 @@ class UlyssesSequenceParallel:
         return recv.permute(1, 0, 2, 3).reshape(tl, self.size * hs, d)
 
 
+class ExpertParallelGroup:
+    """Expert parallelism for training: ``size`` data-parallel ranks (each with its own tokens) store ``E / size`` experts
+    each. A layer sends every routed token copy to the owner of its expert, runs the owner's experts, and sends the
+    results back along the same path; the backward pass retraces it (the gradient of an exchange is the reverse
+    exchange). Expert parameters therefore receive gradient contributions from the tokens of all ranks and are never
+    reduced over the data-parallel group.
+
+    Parity target: Megatron's token dispatcher used through ``verl/workers/engine/megatron/transformer_impl.py``
+    (``expert_model_parallel_size``) and ``verl/models/mcore/model_forward.py``."""
+
+    def __init__(self, group, rank: int, size: int):
+        self.group, self.rank, self.size = group, int(rank), int(size)
+
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """``counts`` [size, E_local]: copies this rank sends to each (owner, local expert). Returns the same matrix seen
+        from the receiving side: row s = copies arriving from rank s per local expert."""
+        import torch.distributed as dist
+
+        send = counts.contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return recv
+
+    def exchange_rows(self, x: torch.Tensor, in_splits: list, out_splits: list) -> torch.Tensor:
+        """Rows of ``x`` go to the ranks in blocks of ``in_splits``; returns the ``sum(out_splits)`` rows received."""
+        import torch.distributed as dist
+
+        out = torch.empty(sum(out_splits), *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=self.group)
+        return out
+
+
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
@@ -150,6 +182,7 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.ep: Optional[ExpertParallelGroup] = None       # expert parallelism (this model stores E / size experts)
         self.sp: Optional[UlyssesSequenceParallel] = None  # sequence parallelism (token-wise layers on a slice of the stream)
         self.cfg = cfg
         self.params = params
@@ -476,7 +509,104 @@ class DecoderModel:
         return (h2.is_cuda and h2.dtype == torch.bfloat16 and c.num_experts <= 1024 and c.hidden_size % 64 == 0
                 and c.moe_intermediate_size % 64 == 0 and os.environ.get("VERL_B200_MOE_NATIVE", "1") != "0")
 
+    # -- expert-parallel path: token copies travel to the owner of their expert and back -------------------------------
+    def _experts_apply(self, W, x, counts: list, S: Optional[dict]):
+        """Rows of ``x`` sorted by local expert (``counts`` rows each) through gate_up -> SwiGLU -> down."""
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        gu = torch.empty(x.shape[0], Wgu.shape[1], dtype=x.dtype, device=x.device)
+        y = torch.empty(x.shape[0], Wd.shape[1], dtype=x.dtype, device=x.device)
+        s0 = 0
+        for e, n in enumerate(counts):
+            if n:
+                F.gemm(x[s0 : s0 + n], Wgu[e], out=gu[s0 : s0 + n])
+                F.gemm(F.swiglu(gu[s0 : s0 + n]), Wd[e], out=y[s0 : s0 + n])
+                s0 += n
+        if S is not None:
+            S["gu"] = gu
+        return y
+
+    def _experts_apply_bwd(self, W, g_y, x, gu, counts: list):
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        g_x = torch.empty_like(x)
+        s0 = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            sl = slice(s0, s0 + n)
+            g_act = F.gemm(g_y[sl], Wd[e], b_mn=True)
+            mg = getattr(Wd, "main_grad", None)
+            if mg is not None:
+                F.gemm(g_y[sl], F.swiglu(gu[sl]), out=mg[e], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            g_gu = F.swiglu_bwd(g_act, gu[sl])
+            F.gemm(g_gu, Wgu[e], b_mn=True, out=g_x[sl])
+            mg = getattr(Wgu, "main_grad", None)
+            if mg is not None:
+                F.gemm(g_gu, x[sl], out=mg[e], a_mn=True, b_mn=True, out_f32=True, accumulate=True)
+            s0 += n
+        return g_x
+
+    def _moe_fwd_ep(self, W, h2, S: Optional[dict]):
+        cfg, ep = self.cfg, self.ep
+        T, H = h2.shape
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        El = E // ep.size
+        logits = F.gemm(h2, W["mlp.gate.weight"])
+        w, idx = self._route(logits)
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)          # copies sorted by global expert = by (owner, local expert)
+        tok = torch.div(order, k, rounding_mode="floor")
+        send_counts = torch.bincount(flat_e, minlength=E).view(ep.size, El)
+        recv_counts = ep.exchange_counts(send_counts)       # [source rank, local expert]
+        both = torch.stack([send_counts, recv_counts]).cpu()  # the one host read of the layer: split sizes of the exchange
+        in_splits, out_splits = both[0].sum(1).tolist(), both[1].sum(1).tolist()
+        x_recv = ep.exchange_rows(h2[tok], in_splits, out_splits)
+        # received rows are grouped by source rank, then local expert: regroup by local expert
+        eid = torch.repeat_interleave(torch.arange(El, device=h2.device).repeat(ep.size), recv_counts.reshape(-1).to(h2.device))
+        perm = torch.argsort(eid, stable=True)
+        local_counts = both[1].sum(0).tolist()
+        St = {} if S is not None else None
+        x_sorted = x_recv[perm]
+        y_sorted = self._experts_apply(W, x_sorted, local_counts, St)
+        y_recv = torch.empty_like(y_sorted)
+        y_recv[perm] = y_sorted
+        y_send = ep.exchange_rows(y_recv, out_splits, in_splits)  # back to the ranks of the tokens, in `order`
+        wp = w.reshape(-1)[order].to(h2.dtype)
+        out = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
+        out.index_add_(0, tok, (y_send * wp.unsqueeze(-1)).float())
+        if S is not None:
+            S.update(moe=dict(ep=True, logits=logits, idx=idx, order=order, tok=tok, wp=wp, y=y_send, perm=perm, x=x_sorted,
+                              gu=St["gu"], counts=local_counts, in_splits=in_splits, out_splits=out_splits))
+        return out.to(h2.dtype)
+
+    def _moe_bwd_ep(self, W, g_d, h2, S: dict):
+        cfg, ep = self.cfg, self.ep
+        M = S["moe"]
+        order, tok, wp, perm = M["order"], M["tok"], M["wp"], M["perm"]
+        k = cfg.num_experts_per_tok
+        T, H = h2.shape
+        g_dp = g_d[tok]
+        g_wp = (g_dp.float() * M["y"].float()).sum(-1)
+        g_y_recv = ep.exchange_rows((g_dp * wp.unsqueeze(-1)).contiguous(), M["in_splits"], M["out_splits"])
+        g_x_sorted = self._experts_apply_bwd(W, g_y_recv[perm].contiguous(), M["x"], M["gu"], M["counts"])
+        g_x_recv = torch.empty_like(g_x_sorted)
+        g_x_recv[perm] = g_x_sorted
+        g_x_send = ep.exchange_rows(g_x_recv, M["out_splits"], M["in_splits"])
+        g_h2 = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
+        g_h2.index_add_(0, tok, g_x_send.float())
+        g_w = torch.empty(T * k, dtype=torch.float32, device=h2.device)
+        g_w[order] = g_wp
+        with torch.enable_grad():
+            lg = M["logits"].detach().float().requires_grad_(True)
+            wr, _ = self._route(lg, idx=M["idx"])
+            (g_logits,) = torch.autograd.grad(wr, lg, g_w.view(T, k))
+        g_logits = g_logits.to(h2.dtype)
+        g_h2 += F.gemm(g_logits, W["mlp.gate.weight"], b_mn=True).float()
+        self._wgrad(W["mlp.gate.weight"], g_logits, h2)
+        return g_h2.to(h2.dtype)
+
     def _moe_fwd(self, W, h2, S: Optional[dict]):
+        if self.ep is not None:
+            return self._moe_fwd_ep(W, h2, S)
         if self._moe_native_ok(h2):
             return self._moe_fwd_native(W, h2, S)
         cfg = self.cfg
@@ -507,6 +637,8 @@ class DecoderModel:
         return out.to(h2.dtype)
 
     def _moe_bwd(self, W, g_d, h2, S: dict):
+        if S["moe"].get("ep"):
+            return self._moe_bwd_ep(W, g_d, h2, S)
         if S["moe"].get("native"):
             return self._moe_bwd_native(W, g_d, h2, S)
         cfg = self.cfg

@@ -92,11 +92,22 @@ class FlatParams:
         self.value_head = value_head
         self.specs = build_param_specs(cfg, value_head)
         self.offsets: dict[str, int] = {}
+        # An expert-parallel shard keeps its own experts in a tail region [dense_numel, numel): that region is local to the
+        # rank (never reduced or gathered over the data-parallel group), the region in front of it is replicated.
+        ep_shard = cfg.is_moe and cfg.num_local_experts > 0
+        is_local = lambda s: ep_shard and ".mlp.experts." in s.name
         off = 0
         for s in self.specs:
-            self.offsets[s.name] = off
-            off += _round_up(s.numel, ALIGN)
-        self.numel = _round_up(off, ALIGN * max(1, pad_to))
+            if not is_local(s):
+                self.offsets[s.name] = off
+                off += _round_up(s.numel, ALIGN)
+        self.dense_numel = _round_up(off, ALIGN * max(1, pad_to))
+        off = self.dense_numel
+        for s in self.specs:
+            if is_local(s):
+                self.offsets[s.name] = off
+                off += _round_up(s.numel, ALIGN)
+        self.numel = off if ep_shard else self.dense_numel
         self.flat = buffer if buffer is not None else torch.zeros(self.numel, dtype=dtype, device=device)
         assert self.flat.numel() == self.numel
         self.main_grad: Optional[torch.Tensor] = None
@@ -135,7 +146,7 @@ class FlatParams:
 
     def layer_range(self, i: int) -> tuple[int, int]:
         """[start, end) element range of layer i in the flat buffer (-1: embeddings, L: norm/head)."""
-        names = [s for s in self.specs if s.layer == i]
+        names = [s for s in self.specs if s.layer == i and self.offsets[s.name] < self.dense_numel]
         start = self.offsets[names[0].name]
         last = names[-1]
         return start, self.offsets[last.name] + _round_up(last.numel, ALIGN)
@@ -143,7 +154,7 @@ class FlatParams:
     def decay_mask_ranges(self) -> list[tuple[int, int, bool]]:
         """(start, end, weight_decay?) ranges covering the flat buffer in order."""
         out = []
-        for s in self.specs:
+        for s in sorted(self.specs, key=lambda s: self.offsets[s.name]):
             o = self.offsets[s.name]
             out.append((o, o + _round_up(s.numel, ALIGN), s.decay))
         return out

@@ -36,11 +36,14 @@ __all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to
 class ModelParallelTopology:
     """Process groups of a TP x PP x DP job. Every rank of the job must construct it (group creation is collective)."""
 
-    def __init__(self, tp: int = 1, pp: int = 1, ranks: Optional[list[int]] = None):
+    def __init__(self, tp: int = 1, pp: int = 1, ranks: Optional[list[int]] = None, ep: int = 1):
         self.world_ranks = list(ranks) if ranks is not None else list(range(dist.get_world_size() if dist.is_initialized() else 1))
         n = len(self.world_ranks)
         assert n % (tp * pp) == 0, f"world size {n} is not a multiple of tp*pp = {tp * pp}"
         self.tp, self.pp, self.dp = tp, pp, n // (tp * pp)
+        # expert parallelism borrows the data-parallel dimension: the ranks of a data-parallel group split the experts
+        assert ep == 1 or (ep == self.dp and tp == 1), "expert parallelism: ep must equal the data-parallel size, with tp = 1"
+        self.ep = ep
         me = dist.get_rank() if dist.is_initialized() else 0
         self.index = self.world_ranks.index(me)
         self.tp_rank = self.index % tp
@@ -75,6 +78,8 @@ class ModelParallelTopology:
         self.prev_rank = g(self.dp_rank, self.pp_rank - 1, self.tp_rank) if self.pp_rank > 0 else None
         self.next_rank = g(self.dp_rank, self.pp_rank + 1, self.tp_rank) if self.pp_rank < pp - 1 else None
         self.last_stage_rank = g(self.dp_rank, pp - 1, self.tp_rank)
+        self.ep_rank = self.dp_rank if ep > 1 else 0
+        self.ep_group = self.dp_group if ep > 1 else None
 
     @property
     def is_first_stage(self) -> bool:
@@ -92,14 +97,15 @@ class ModelParallelTopology:
 
     def local_config(self, cfg: ModelConfig) -> ModelConfig:
         lo, hi = self.layer_range(cfg.num_hidden_layers)
-        return cfg.local_shard(tp=self.tp, num_layers=hi - lo, has_embedding=self.is_first_stage, has_head=self.is_last_stage)
+        return cfg.local_shard(tp=self.tp, num_layers=hi - lo, has_embedding=self.is_first_stage, has_head=self.is_last_stage,
+                               ep=self.ep)
 
 
 @dataclass
 class ShardMap:
     local_name: str
     full_name: str
-    kind: str              # rep | rows | cols
+    kind: str              # rep | rows | cols | experts (dim 0 cut over the expert-parallel group)
     blocks: tuple = ()     # rows: sizes of the stacked blocks of the FULL tensor, each block is cut into tp slices
 
 
@@ -118,7 +124,9 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
             full_name = f"layers.{int(i) + lo}.{rest}"
         else:
             rest = name
-        if rest.startswith("self_attn.qkv_proj"):
+        if rest.startswith("mlp.experts.") and topo.ep > 1:
+            out.append(ShardMap(name, full_name, "experts"))
+        elif rest.startswith("self_attn.qkv_proj"):
             out.append(ShardMap(name, full_name, "rows", (full_cfg.q_size, full_cfg.kv_size, full_cfg.kv_size)))
         elif rest.startswith("mlp.gate_up_proj"):
             out.append(ShardMap(name, full_name, "rows", (full_cfg.intermediate_size, full_cfg.intermediate_size)))
@@ -129,8 +137,11 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
     return out
 
 
-def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int) -> list[torch.Tensor]:
+def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int, ep: int = 1, ep_rank: int = 0) -> list[torch.Tensor]:
     """Views of the full tensor that, concatenated along the sharded dimension, form the local tensor."""
+    if m.kind == "experts":
+        n = full.shape[0] // ep
+        return [full[ep_rank * n : (ep_rank + 1) * n]]
     if m.kind == "rep" or tp == 1:
         return [full]
     if m.kind == "cols":
@@ -145,24 +156,26 @@ def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int) -> list[torc
 
 
 @torch.no_grad()
-def copy_full_to_local(full: FlatParams, local: FlatParams, maps: list[ShardMap], tp: int, tp_rank: int) -> None:
+def copy_full_to_local(full: FlatParams, local: FlatParams, maps: list[ShardMap], tp: int, tp_rank: int, ep: int = 1,
+                       ep_rank: int = 0) -> None:
     for m in maps:
         if m.full_name not in full.views:
             continue  # e.g. lm_head of a tied model
-        parts = _slices(m, full.views[m.full_name], tp, tp_rank)
+        parts = _slices(m, full.views[m.full_name], tp, tp_rank, ep, ep_rank)
         dim = 1 if m.kind == "cols" else 0
         src = parts[0] if len(parts) == 1 else torch.cat(parts, dim)
         local.views[m.local_name].copy_(src.to(local.views[m.local_name].dtype))
 
 
 @torch.no_grad()
-def copy_local_to_full(local: FlatParams, full: FlatParams, maps: list[ShardMap], tp: int, tp_rank: int) -> None:
+def copy_local_to_full(local: FlatParams, full: FlatParams, maps: list[ShardMap], tp: int, tp_rank: int, ep: int = 1,
+                       ep_rank: int = 0) -> None:
     """Write this rank's shard into its place of a full-layout buffer (merge / reshard building block)."""
     for m in maps:
         if m.full_name not in full.views:
             continue
         src = local.views[m.local_name]
-        parts = _slices(m, full.views[m.full_name], tp, tp_rank)
+        parts = _slices(m, full.views[m.full_name], tp, tp_rank, ep, ep_rank)
         if len(parts) == 1:
             parts[0].copy_(src.to(parts[0].dtype))
             continue

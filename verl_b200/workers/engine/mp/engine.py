@@ -34,11 +34,11 @@ __all__ = ["ModelParallelEngine", "ModelParallelEngineWithLMHead", "ModelParalle
 _TOPOLOGIES: dict = {}
 
 
-def get_topology(tp: int, pp: int) -> ModelParallelTopology:
-    """One topology (set of process groups) per (tp, pp) and process: actor, critic and reference engines share it."""
-    key = (tp, pp)
+def get_topology(tp: int, pp: int, ep: int = 1) -> ModelParallelTopology:
+    """One topology (set of process groups) per (tp, pp, ep) and process: actor, critic and reference engines share it."""
+    key = (tp, pp, ep)
     if key not in _TOPOLOGIES:
-        _TOPOLOGIES[key] = ModelParallelTopology(tp, pp)
+        _TOPOLOGIES[key] = ModelParallelTopology(tp, pp, ep=ep)
     return _TOPOLOGIES[key]
 
 
@@ -48,13 +48,16 @@ class ModelParallelEngine(NativeEngine):
         g = lambda k, d: int(getattr(engine_config, k, None) or d)
         self.tp_size = g("tensor_model_parallel_size", 1)
         self.pp_size = g("pipeline_model_parallel_size", 1)
+        self.ep_size = g("expert_model_parallel_size", 1) if self.arch.is_moe else 1
         self.full_arch = self.arch
 
     # ------------------------------------------------------------------------------------ setup
     def initialize(self) -> None:
         if self._initialized:
             return
-        self.topo = get_topology(self.tp_size, self.pp_size)
+        self.topo = get_topology(self.tp_size, self.pp_size, self.ep_size)
+        if self.full_arch.is_moe and self.tp_size > 1:
+            raise NotImplementedError("mixture-of-experts layers are not tensor-parallel; use expert_model_parallel_size")
         if self.full_arch.tie_word_embeddings and self.pp_size > 1:
             raise NotImplementedError("pipeline parallelism with tied input/output embeddings needs the embedding shared between "
                                       "the first and the last stage; use pipeline_model_parallel_size=1 for this model")
@@ -67,6 +70,10 @@ class ModelParallelEngine(NativeEngine):
             super().initialize()
         finally:
             set_data_parallel_group(outer)
+        if self.topo.ep > 1:
+            from ....models.decoder import ExpertParallelGroup
+
+            self.model.ep = ExpertParallelGroup(self.topo.ep_group, self.topo.ep_rank, self.topo.ep)
         if self.topo.tp > 1:
             grp = self.topo.tp_group
 
@@ -94,7 +101,7 @@ class ModelParallelEngine(NativeEngine):
             load_hf_weights_into(full, path)
         else:
             full.init_weights(seed=seed)
-        copy_full_to_local(full, self.params, self.maps, self.topo.tp, self.topo.tp_rank)
+        copy_full_to_local(full, self.params, self.maps, self.topo.tp, self.topo.tp_rank, self.topo.ep, self.topo.ep_rank)
         del full
 
     # ------------------------------------------------------------------------------------ topology facts for the worker
@@ -214,17 +221,29 @@ class ModelParallelEngine(NativeEngine):
     def gather_full_params(self, dtype=None) -> FlatParams:
         """The full model assembled on every rank of the replica (host of the train -> rollout reshard and of merged
         checkpoints): each rank writes its shard into a zeroed full-layout buffer, the buffers are summed over the
-        model-parallel group, replicated tensors are divided by their multiplicity."""
+        model-parallel group, replicated tensors are divided by their multiplicity. Expert-parallel shards are gathered
+        over the expert-parallel group. Without tensor / pipeline parallelism the buffer is built in ``dtype`` directly."""
         dtype = dtype or self.dtype
-        full = FlatParams(self.full_arch, dtype=torch.float32, device=self.device, value_head=self.value_head)
-        copy_local_to_full(self.params, full, self.maps, self.topo.tp, self.topo.tp_rank)
-        if self.topo.mp_group is not None:
-            if self.topo.tp > 1 and self.topo.tp_rank != 0:  # replicated tensors are contributed by tp rank 0 only
+        topo = self.topo
+        work = torch.float32 if topo.mp_group is not None else dtype
+        full = FlatParams(self.full_arch, dtype=work, device=self.device, value_head=self.value_head)
+        copy_local_to_full(self.params, full, self.maps, topo.tp, topo.tp_rank, topo.ep, topo.ep_rank)
+        if topo.mp_group is not None:
+            if topo.tp > 1 and topo.tp_rank != 0:  # replicated tensors are contributed by tp rank 0 only
                 for m in self.maps:
                     if m.kind == "rep" and m.full_name in full.views:
                         full.views[m.full_name].zero_()
-            dist.all_reduce(full.flat, group=self.topo.mp_group)
-        if dtype != torch.float32:
+            dist.all_reduce(full.flat, group=topo.mp_group)
+        if topo.ep > 1:
+            for m in self.maps:
+                if m.kind == "experts":
+                    dst = full.views[m.full_name]
+                    src = self.params.views[m.local_name].to(work).contiguous()
+                    if self.device.type == "cuda":
+                        dist.all_gather_into_tensor(dst, src, group=topo.ep_group)
+                    else:
+                        dist.all_gather(list(dst.chunk(topo.ep)), src, group=topo.ep_group)
+        if dtype != work:
             out = FlatParams(self.full_arch, dtype=dtype, device=self.device, value_head=self.value_head)
             out.flat.copy_(full.flat.to(dtype))
             return out

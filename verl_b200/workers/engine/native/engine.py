@@ -232,14 +232,18 @@ class NativeEngine(BaseEngine):
             from ....utils.activation_offload import ActivationOffloader
 
             self.model.offloader = ActivationOffloader(self.device)
-        self.shard_numel = self.tparams.numel // self.world
+        # The replicated region [0, dense_numel) is optimised in equal shards over the data-parallel group; a rank-local tail
+        # region (the experts of an expert-parallel shard) is optimised whole by its owner.
+        self.dense_numel = int(getattr(self.tparams, "dense_numel", self.tparams.numel))
+        self.local_numel = self.tparams.numel - self.dense_numel
+        self.shard_numel = self.dense_numel // self.world
         self.shard_lo = self.rank * self.shard_numel
+        assert self.local_numel == 0 or (self.world > 1 and not self.fused_comm and self.lora is None)
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
         # memory (4 bytes/param) is available to the rollout KV cache in between.
         self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
         if not self.forward_only:
-            sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-            self.master = self.tparams.flat[sl].float().clone()
+            self.master = self._owned(self.tparams.flat).float()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
             self.grad_shard = None
@@ -273,6 +277,11 @@ class NativeEngine(BaseEngine):
         if self.lazy_grad and getattr(self.tparams, "main_grad", None) is None:
             free -= self.tparams.numel * 4  # the fp32 gradient buffer is allocated on the first backward
         keep = int(0.6 * max(0, free) // max(1, per_layer))
+        if getattr(self.model, "ep", None) is not None:
+            # expert-parallel layers exchange tokens in forward, recompute and backward: every rank must make the same choice
+            t = torch.tensor([keep], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.model.ep.group)
+            keep = int(t.item())
         self.last_kept_layers = keep
         return keep
 
@@ -334,6 +343,16 @@ class NativeEngine(BaseEngine):
             mb = data.get("micro_batch_size_per_gpu") or (ec.infer_micro_batch_size_per_gpu if forward_only
                                                           else ec.micro_batch_size_per_gpu) or n
             parts = [list(range(s, min(n, s + int(mb)))) for s in range(0, n, int(mb))]
+        if getattr(self.model, "ep", None) is not None:
+            # every rank of an expert-parallel group must run the same number of micro-batches (each one is a round of
+            # collectives): split the largest parts until the counts agree
+            t = torch.tensor([len(parts)], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.model.ep.group)
+            assert n >= int(t.item()), "fewer rows than micro-batches on another rank of the expert-parallel group"
+            while len(parts) < int(t.item()):
+                j = max(range(len(parts)), key=lambda i: len(parts[i]))
+                big = parts.pop(j)
+                parts[j:j] = [big[: len(big) // 2], big[len(big) // 2 :]]
         out = []
         for p in parts:
             idx = torch.tensor(p, dtype=torch.int64, device=ids.device)
@@ -446,6 +465,17 @@ class NativeEngine(BaseEngine):
         return out
 
     # ------------------------------------------------------------------------------------ optimizer
+    def _owned(self, flat: torch.Tensor) -> torch.Tensor:
+        """Copy of the elements of a full-layout buffer that this rank optimises: its shard of the replicated region
+        followed by the rank-local region."""
+        sl = flat[self.shard_lo : self.shard_lo + self.shard_numel]
+        return torch.cat([sl, flat[self.dense_numel :]]) if self.local_numel else sl.clone()
+
+    def _scatter_owned(self, owned: torch.Tensor, flat: torch.Tensor) -> None:
+        flat[self.shard_lo : self.shard_lo + self.shard_numel].copy_(owned[: self.shard_numel].to(flat.dtype))
+        if self.local_numel:
+            flat[self.dense_numel :].copy_(owned[self.shard_numel :].to(flat.dtype))
+
     def _alloc_grads(self) -> None:
         self.tparams.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
@@ -473,12 +503,16 @@ class NativeEngine(BaseEngine):
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if self.fused_comm:
             return self._fused_optimizer_step()
+        D, n_sh = self.dense_numel, self.shard_numel
         if W > 1:
             if self.device.type == "cuda":
-                dist.reduce_scatter_tensor(self.grad_shard, mg, op=dist.ReduceOp.AVG, group=self.group)
+                dist.reduce_scatter_tensor(self.grad_shard[:n_sh], mg[:D], op=dist.ReduceOp.AVG, group=self.group)
             else:  # gloo has no reduce-scatter: all-reduce and keep this rank's slice
-                dist.all_reduce(mg, group=self.group)
-                self.grad_shard.copy_(mg[sl]).div_(W)
+                dist.all_reduce(mg[:D], group=self.group)
+                self.grad_shard[:n_sh].copy_(mg[sl]).div_(W)
+            if self.local_numel:
+                # rank-local parameters already hold the sum over every rank's tokens; 1/W makes it the same global mean
+                torch.mul(mg[D:], 1.0 / W, out=self.grad_shard[n_sh:])
         self.ctrl.zero_()
         lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
         self.opt_step_count += 1
@@ -489,9 +523,11 @@ class NativeEngine(BaseEngine):
                 dist.all_reduce(self.ctrl[:1], group=self.group)
             self._global_sumsq_correction()
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
-            ops.adamw_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self.tparams.flat[sl], self.ctrl,
-                       lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
-                       self.opt_step_count, 1.0, False)
+            for own, dst in ((slice(0, n_sh), sl), (slice(n_sh, n_sh + self.local_numel), slice(D, D + self.local_numel))):
+                if own.stop > own.start:
+                    ops.adamw_(self.master[own], self.grad_shard[own], self.exp_avg[own], self.exp_avg_sq[own], self.tparams.flat[dst],
+                               self.ctrl, lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
+                               self.opt_step_count, 1.0, False)
             norm = self.ctrl[3]
         else:
             ss = self.grad_shard.double().pow(2).sum()
@@ -512,7 +548,7 @@ class NativeEngine(BaseEngine):
                 self.master.mul_(1 - lr * oc.weight_decay)
                 denom = (self.exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(oc.eps)
                 self.master.addcdiv_(self.exp_avg, denom, value=-lr / bc1)
-                self.tparams.flat[sl].copy_(self.master.to(self.dtype))
+                self._scatter_owned(self.master, self.tparams.flat)
         self._publish_shard()
         if self.lora is not None:
             self.lora.merge()  # the working weights (shared with the rollout engine) follow the adapters
@@ -554,11 +590,12 @@ class NativeEngine(BaseEngine):
         if self.world == 1:
             return
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        dense = self.tparams.flat[: self.dense_numel]
         if self.device.type == "cuda":
-            dist.all_gather_into_tensor(self.tparams.flat, self.tparams.flat[sl].clone(), group=self.group)
+            dist.all_gather_into_tensor(dense, dense[sl].clone(), group=self.group)
         else:
-            parts = [self.tparams.flat[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
-            dist.all_gather(parts, self.tparams.flat[sl].clone(), group=self.group)
+            parts = [dense[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
+            dist.all_gather(parts, dense[sl].clone(), group=self.group)
 
     def lr_scheduler_step(self) -> float:
         self.sched_step += 1
@@ -589,7 +626,7 @@ class NativeEngine(BaseEngine):
         contents = list(getattr(self.checkpoint_config, "save_contents", ["model", "optimizer", "extra"]) or [])
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if "model" in contents:
-            src = self.master if not self.forward_only else self.tparams.flat[sl].float()
+            src = self.master if not self.forward_only else self._owned(self.tparams.flat).float()
             torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.tparams.numel,
                         "offsets": self.tparams.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
         if "optimizer" in contents and not self.forward_only:
@@ -626,7 +663,7 @@ class NativeEngine(BaseEngine):
             assert st["numel"] == self.tparams.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
             if not self.forward_only:
                 self.master.copy_(st["flat_shard"])
-            self.tparams.flat[sl].copy_(st["flat_shard"].to(self.dtype))
+            self._scatter_owned(st["flat_shard"].to(self.device), self.tparams.flat)
             self._publish_shard()
             if self.lora is not None:
                 self.lora.merge()
