@@ -53,6 +53,8 @@ def parse_args():
                         "measured faster than TP=2 for this model (gen 32.5 s vs 41.1 s per step); 2 reproduces the TP=2 layout")
     p.add_argument("--train-tp", type=int, default=1, help="tensor-parallel size of the training engine (strategy=megatron when tp*pp > 1)")
     p.add_argument("--train-pp", type=int, default=1, help="pipeline-parallel size of the training engine")
+    p.add_argument("--train-ep", type=int, default=1, help="expert-parallel size of the training engine (mixture-of-experts models; "
+                                                           "must equal the data-parallel size)")
     p.add_argument("--no-prefix-sharing", action="store_true",
                    help="pack every sample's prompt separately in the log-prob / training passes and prefill it separately "
                         "(default: the n samples of a prompt share its tokens; results are identical)")
@@ -146,10 +148,11 @@ def build_config(args, world: int):
         "trainer.worker_group=spmd", "trainer.device=cuda",
     ]
     mp = args.train_tp * args.train_pp
-    if mp > 1:
+    if mp * args.train_ep > 1:
         ov += ["actor@actor_rollout_ref.actor=megatron_actor",
                f"actor_rollout_ref.actor.megatron.tensor_model_parallel_size={args.train_tp}",
-               f"actor_rollout_ref.actor.megatron.pipeline_model_parallel_size={args.train_pp}"]
+               f"actor_rollout_ref.actor.megatron.pipeline_model_parallel_size={args.train_pp}",
+               f"actor_rollout_ref.actor.megatron.expert_model_parallel_size={args.train_ep}"]
     if args.critic:
         ov = [o for o in ov if not o.startswith(("algorithm.adv_estimator", "actor_rollout_ref.actor.use_kl_loss"))]
         ov += ["algorithm.adv_estimator=gae", "algorithm.gamma=1.0", "algorithm.lam=1.0", "actor_rollout_ref.actor.use_kl_loss=false",
@@ -267,8 +270,9 @@ def main():
                        "seq_len": args.prompt_len + args.response_len, "prompt_len": args.prompt_len,
                        "response_len": args.response_len,
                        "parallelism": (f"dp{world} (sharded optimizer, replicated bf16 weights) + colocated rollout "
-                                       f"tp{rollout_tp} x dp{world // rollout_tp} on in-place weight shards") if args.train_tp * args.train_pp == 1
-                       else (f"train tp{args.train_tp} x pp{args.train_pp} x dp{world // (args.train_tp * args.train_pp)} + rollout tp{rollout_tp} "
+                                       f"tp{rollout_tp} x dp{world // rollout_tp} on in-place weight shards") if args.train_tp * args.train_pp * args.train_ep == 1
+                       else (f"train tp{args.train_tp} x pp{args.train_pp} x dp{world // (args.train_tp * args.train_pp)}"
+                             f"{' x ep' + str(args.train_ep) + ' (experts sharded over dp)' if args.train_ep > 1 else ''} + rollout tp{rollout_tp} "
                              f"on weights gathered from the shards each step"),
                        "algorithm": "ppo+critic+gae" if args.critic else "grpo",
                        "shared_prompt_packing": not args.no_prefix_sharing,

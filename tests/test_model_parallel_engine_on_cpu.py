@@ -161,6 +161,55 @@ def test_grpo_end_to_end_with_tensor_parallel_actor_and_rollout():
     assert (res[0]["resp"] == res[1]["resp"]).all()  # one replica: both ranks hold the same batch
 
 
+def _ppo_ep_proc(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      VERL_ENGINE_DEVICE="cpu")
+    try:
+        from verl_b200.trainer.main_ppo import main
+
+        t = main(['actor@actor_rollout_ref.actor=megatron_actor', 'actor_rollout_ref.actor.megatron.expert_model_parallel_size=2',
+                  'data.train_batch_size=4', 'data.max_prompt_length=16', 'data.max_response_length=12', 'data.synthetic.num_prompts=16',
+                  'data.synthetic.prompt_length=16', 'data.synthetic.vocab_high=512', 'actor_rollout_ref.model.path=tiny-moe',
+                  'actor_rollout_ref.rollout.n=2', 'actor_rollout_ref.actor.ppo_mini_batch_size=4',
+                  'actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=4', 'actor_rollout_ref.actor.use_kl_loss=true',
+                  'actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=8', 'actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=8',
+                  'algorithm.adv_estimator=grpo', 'reward_model.reward_manager=token_rule', 'trainer.n_gpus_per_node=2',
+                  'trainer.total_epochs=2', 'trainer.total_training_steps=2', 'trainer.device=cpu', 'trainer.val_before_train=false',
+                  'actor_rollout_ref.rollout.max_num_seqs=8', 'actor_rollout_ref.rollout.block_size=8', 'trainer.resume_mode=disable',
+                  'trainer.worker_group=spmd', 'trainer.logger=[]'])
+        b = t.last_batch.batch
+        diff = (torch.exp(b["rollout_log_probs"]) - torch.exp(b["old_log_probs"])).abs()[b["response_mask"].bool()].max().item()
+        q.put((rank, {"steps": t.global_steps, "adv_shape": tuple(b["advantages"].shape), "prob_diff": diff,
+                      "resp": b["responses"].numpy()}))
+    except Exception:
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+def test_grpo_end_to_end_with_expert_parallel_actor():
+    """Mixture-of-experts actor with the experts split over the two data-parallel ranks; the rollout engine of each rank
+    runs on the full model gathered from the shards after every update."""
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_ppo_ep_proc, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=400) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    for r in (0, 1):
+        assert "error" not in res[r], res[r]["error"]
+        assert res[r]["steps"] == 3 and res[r]["adv_shape"] == (4, 12)   # two ranks x (2 prompts x 2 samples)
+        assert res[r]["prob_diff"] < 1e-3  # expert-sharded trainer and full-model rollout agree on token probabilities
+    assert not (res[0]["resp"] == res[1]["resp"]).all()  # data parallel: the ranks hold different prompts
+
+
 def _ppo_critic_proc(rank, world, port, q):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                       VERL_ENGINE_DEVICE="cpu")

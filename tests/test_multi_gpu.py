@@ -124,6 +124,29 @@ def _worker_body(rank, world, port, queue):
     res["param_diff"] = (finals[True][0] - finals[False][0]).abs().max().item()
     res["norm_diff"] = max(abs(a - b) for a, b in zip(finals[True][1], finals[False][1]))
     res["norm"] = finals[True][1]
+    # ---- expert-parallel training engine (experts split over the two ranks, NCCL token exchange) vs replicated experts
+    from verl_b200.workers.config import McoreEngineConfig
+    from verl_b200.workers.engine.base import EngineRegistry
+
+    moe_arch = ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,
+                           moe_intermediate_size=128, eos_token_id=2, pad_token_id=0, qk_norm=True)
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    g = torch.Generator().manual_seed(300 + rank)
+    ids = torch.randint(3, 1024, (4, 40 + 8 * rank), generator=g)
+    am = torch.ones_like(ids)
+    data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 16:].to(dev), "response_mask": am[:, 16:].to(dev)}
+    ep_res = {}
+    for name, backend, ec in (("rep", "fsdp", FSDPEngineConfig(seed=9, micro_batch_size_per_gpu=2)),
+                              ("ep", "megatron", McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, expert_model_parallel_size=2))):
+        eng = EngineRegistry.new("language_model", backend, moe_arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        out = eng.train_batch(dict(data), partial(sft_loss, None))
+        full = eng.gather_full_params().flat.float() if name == "ep" else eng.params.flat.float().clone()
+        ep_res[name] = (float(out["metrics"]["grad_norm"]), full)
+    res["ep_train_norms"] = (ep_res["rep"][0], ep_res["ep"][0])
+    res["ep_train_param_diff"] = (ep_res["rep"][1] - ep_res["ep"][1]).abs().max().item()
+    os.environ["VERL_B200_FUSED_COMM"] = "1"
     # ---- a barrier that nobody else joins runs out after its limit and reports through the status word
     lonely = PeerBarrier(dev)
     torch.cuda.synchronize()
@@ -161,4 +184,6 @@ def test_two_rank_fused_optimizer_and_peer_collectives():
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
         assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res
+        n_rep, n_ep = res["ep_train_norms"]
+        assert abs(n_rep - n_ep) < 1e-2 * max(1.0, n_rep) and res["ep_train_param_diff"] < 5e-3, res  # one AdamW step of lr 1e-3
     assert results[0]["timeout_status"] == 4 and results[0]["alive_after_timeout"] == 4.0

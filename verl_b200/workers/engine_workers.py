@@ -275,7 +275,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 from .config import McoreEngineConfig
 
                 mrec = McoreEngineConfig(tensor_model_parallel_size=self.actor.tp_size, pipeline_model_parallel_size=self.actor.pp_size,
-                                         forward_only=True)
+                                         expert_model_parallel_size=getattr(self.actor, "ep_size", 1), forward_only=True)
                 for k in ("infer_micro_batch_size_per_gpu", "use_dynamic_bsz", "infer_max_token_len_per_gpu"):
                     object.__setattr__(mrec, k, getattr(rec, k))
                 self.ref = EngineRegistry.new("language_model", "megatron", model_config=mc, engine_config=mrec, optimizer_config=None)
@@ -290,15 +290,19 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             rc = cfg.rollout if isinstance(cfg.rollout, RolloutConfig) else omega_conf_to_dataclass(cfg.rollout, RolloutConfig)
             self.rollout_config = rc
             src = self.actor if self.actor is not None else self.ref
-            self._mp_actor = src is not None and getattr(src, "topo", None) is not None and (src.topo.tp * src.topo.pp > 1)
-            if self._mp_actor:
-                # the trainer holds 1/(tp*pp) of the model: the rollout engine gets a full replica that update_weights()
-                # re-assembles from the shards after every optimizer step; trainer data-parallel group = replicas
+            topo = getattr(src, "topo", None) if src is not None else None
+            self._mp_actor = topo is not None and topo.tp * topo.pp > 1
+            self._regather = topo is not None and (self._mp_actor or topo.ep > 1)
+            if self._regather:
+                # the trainer holds a shard of the model (1/(tp*pp) of it, or 1/ep of the experts): the rollout engine gets a
+                # full replica that update_weights() re-assembles from the shards after every optimizer step; with tensor /
+                # pipeline parallelism the trainer's data-parallel group = the replicas
                 from ..utils.distributed import set_data_parallel_group
 
                 self._mp_engine = src
                 self.rollout_params = src.gather_full_params()
-                set_data_parallel_group(src.topo.dp_group)
+                if self._mp_actor:
+                    set_data_parallel_group(topo.dp_group)
 
                 class _Holder:
                     params = self.rollout_params
@@ -477,7 +481,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         """Make the latest actor weights visible to the rollout engine. The engine reads the trainer's working
         buffer in place, so this only invalidates cached KV; returns the device time spent."""
         t0 = time.time()
-        if getattr(self, "_mp_actor", False) and self.rollout is not None:
+        if getattr(self, "_regather", False) and self.rollout is not None:
             fresh = self._mp_engine.gather_full_params()
             self.rollout_params.flat.copy_(fresh.flat)
             del fresh
