@@ -1,0 +1,181 @@
+"""Small utilities: paths, time limits, dictionaries, dynamic enums, addresses, precision names, debug metrics."""
+import asyncio
+import os
+import time
+
+import pytest
+import torch
+
+
+def test_fs_and_hdfs_io_on_local_paths(tmp_path):
+    from verl_b200.utils import fs, hdfs_io
+
+    src = tmp_path / "src"
+    (src / "sub").mkdir(parents=True)
+    (src / "a.txt").write_text("hello")
+    (src / "sub" / "b.bin").write_bytes(b"\x00" * 100)
+    assert not fs.is_non_local(str(src)) and fs.is_non_local("hdfs://nn/path")
+    assert fs.copy_to_local(str(src)) == str(src)
+    dst = tmp_path / "dst"
+    assert hdfs_io.copy(str(src), str(dst)) and fs.verify_copy(str(src), str(dst))
+    (dst / "a.txt").write_text("hello!")
+    assert not fs.verify_copy(str(src), str(dst))
+    p1, p2 = fs.get_local_temp_path("hdfs://x/a/model", str(tmp_path)), fs.get_local_temp_path("hdfs://x/b/model", str(tmp_path))
+    assert p1 != p2 and os.path.basename(p1) == os.path.basename(p2) == "model"
+    shm = fs.copy_to_shm(str(src))
+    assert fs.verify_copy(str(src), shm)
+    assert hdfs_io.exists(str(src)) and not hdfs_io.exists(str(tmp_path / "nope"))
+    assert os.path.isdir(fs.local_mkdir_safe(str(tmp_path / "x" / "y")))
+
+
+def _slow(t):
+    time.sleep(t)
+    return t
+
+
+def test_timeout_limit_process_and_signal():
+    from verl_b200.utils.py_functional import timeout_limit
+
+    assert timeout_limit(5.0)(_slow)(0.01) == 0.01
+    with pytest.raises(TimeoutError):
+        timeout_limit(0.2)(_slow)(5.0)
+    with pytest.raises(TimeoutError):
+        timeout_limit(0.2, use_signals=True)(_slow)(5.0)
+
+    def boom():
+        raise ValueError("x")
+
+    with pytest.raises(ValueError):
+        timeout_limit(5.0)(boom)()
+
+
+from verl_b200.utils.py_functional import DynamicEnum as _DynamicEnum
+
+
+class _Role(_DynamicEnum):
+    _registry, _next_value = {}, 0
+
+
+def test_dict_helpers_and_dynamic_enum():
+    from verl_b200.utils.py_functional import (DynamicEnum, NestedNamespace, append_to_dict, list_of_dict_to_dict_of_list,
+                                                rename_dict, temp_env_var, union_two_dict)
+
+    assert union_two_dict({"a": 1}, {"b": 2}) == {"a": 1, "b": 2}
+    with pytest.raises(AssertionError):
+        union_two_dict({"a": 1}, {"a": 2})
+    d = {}
+    append_to_dict(d, {"x": 1, "y": [1, 2]}, prefix="m/")
+    append_to_dict(d, {"x": 2, "y": [3]}, prefix="m/")
+    assert d == {"m/x": [1, 2], "m/y": [1, 2, 3]} and rename_dict({"a": 1}, "p/") == {"p/a": 1}
+    ns = NestedNamespace({"a": {"b": [{"c": 3}]}})
+    assert ns.a.b[0].c == 3
+    assert list_of_dict_to_dict_of_list([{"a": 1}, {"a": 2}]) == {"a": [1, 2]}
+
+    Role = _Role
+    actor = Role.register("actor")
+    Role.register("critic")
+    assert Role.ACTOR is actor and Role["CRITIC"].value == 1 and Role.names() == ["ACTOR", "CRITIC"] and actor in Role
+    import pickle
+
+    assert pickle.loads(pickle.dumps(actor)) is actor
+    Role.remove("critic")
+    assert Role.from_name("critic") is None
+    with temp_env_var("VB_TEST_ENV", "1"):
+        assert os.environ["VB_TEST_ENV"] == "1"
+    assert "VB_TEST_ENV" not in os.environ
+
+
+def test_net_precision_logger_ray_utils(capsys):
+    from verl_b200.utils.logger import LocalLogger, concat_dict_to_str
+    from verl_b200.utils.net_utils import get_free_port, is_ipv4, is_ipv6
+    from verl_b200.utils.ray_utils import auto_await, ray_noset_visible_devices
+    from verl_b200.utils.torch_dtypes import PrecisionType
+
+    assert is_ipv4("10.0.0.1") and not is_ipv4("::1") and is_ipv6("[::1]") and not is_ipv6("host")
+    port, sock = get_free_port("127.0.0.1", with_alive_sock=True)
+    assert 0 < port < 65536 and sock is not None
+    sock.close()
+    assert PrecisionType.to_dtype("bf16") is torch.bfloat16 and PrecisionType.is_fp16(16) and PrecisionType.to_str(torch.float32) == "fp32"
+    assert concat_dict_to_str({"a": 1.0, "s": "x"}, 3) == "step:3 - a:1.000"
+    LocalLogger().log({"loss": 0.5}, 1)
+    assert "loss:0.500" in capsys.readouterr().out
+    assert ray_noset_visible_devices({"RAY_EXPERIMENTAL_NOSET_CUDA_VISIBLE_DEVICES": "1"}) and not ray_noset_visible_devices({})
+
+    @auto_await
+    async def f(x):
+        await asyncio.sleep(0)
+        return x + 1
+
+    assert f(1) == 2
+
+
+def test_debug_metrics_and_tracker(tmp_path, monkeypatch):
+    from verl_b200.protocol import DataProto
+    from verl_b200.utils.debug import calculate_debug_metrics, calculate_token_list_diff, dump_data, get_trajectory_tracker
+
+    lp = torch.log(torch.tensor([[0.5, 0.25, 0.1], [0.3, 0.3, 0.3]]))
+    lp2 = lp.clone()
+    lp2[0, 0] = torch.log(torch.tensor(0.4))
+    mask = torch.tensor([[1, 1, 0], [1, 1, 1]])
+    data = DataProto.from_dict({"rollout_log_probs": lp, "old_log_probs": lp2, "response_mask": mask, "responses": torch.zeros(2, 3, dtype=torch.long)})
+    m = calculate_debug_metrics(data)
+    assert abs(m["training/rollout_probs_diff_max"] - 0.1) < 1e-6 and m["training/rollout_actor_probs_pearson_corr"] > 0.9
+    d = calculate_token_list_diff(torch.tensor([[1, 2, 3]]), torch.tensor([[1, 5, 9]]), torch.tensor([[1, 1, 0]]))
+    assert abs(d.item() - 0.5) < 1e-6
+    monkeypatch.setenv("VERL_ENABLE_TRACKER", "1")
+    monkeypatch.setenv("VERL_TRACKER_HDFS_DIR", str(tmp_path / "trk"))
+    import verl_b200.utils.debug.trajectory_tracker as tt
+
+    tt._TRACKER = None
+    dump_data({"x": torch.ones(3)}, "step0")
+    (path,) = get_trajectory_tracker().wait_for_hdfs()
+    assert torch.equal(torch.load(path)["x"], torch.ones(3))
+    tt._TRACKER = None
+
+
+def _ulysses_proc(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        import torch.distributed as dist
+
+        from verl_b200.utils import ulysses as U
+
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        U.set_ulysses_sequence_parallel_group(dist.group.WORLD)
+        g = torch.Generator().manual_seed(0)
+        full = torch.randn(1, 6, 4, 8, generator=g)  # [b, seq, heads, dim]
+        local = U.slice_input_tensor(full, dim=1).clone().requires_grad_(True)
+        x = U.gather_seq_scatter_heads(local, seq_dim=1, head_dim=2)           # [1, 6, 2, 8]: all tokens, my heads
+        ok_fwd = torch.equal(x, full[:, :, rank * 2:(rank + 1) * 2])
+        back = U.gather_heads_scatter_seq(x, head_dim=2, seq_dim=1)
+        ok_rt = torch.equal(back, local)
+        out = U.gather_outputs_and_unpad(back.sum(-1), gather_dim=1, grad_scaler=False)  # [1, 6, 4]
+        out.pow(2).sum().backward()
+        expect = 2 * full.sum(-1, keepdim=True).expand_as(full)[:, rank * 3:(rank + 1) * 3]
+        q.put((rank, {"fwd": ok_fwd, "rt": ok_rt, "grad": torch.allclose(local.grad, expect, atol=1e-5)}))
+        dist.destroy_process_group()
+    except Exception:
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+def test_ulysses_functions_on_gloo():
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_ulysses_proc, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    for r in range(2):
+        assert "error" not in res[r], res[r]["error"]
+        assert res[r] == {"fwd": True, "rt": True, "grad": True}, res[r]
