@@ -93,3 +93,47 @@ def test_two_process_sync(backend):
     if backend == "delta_sharded":
         stats = next(r for r in res if isinstance(r, dict))
         assert stats["sent_elements"] == 1  # the second sync shipped exactly the one changed element
+
+
+def _ring_proc(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = CheckpointEngineRegistry.new("nixl", bucket_size=256, group=None, src=0)  # the relay chain under a transport's name
+    w = _weights()
+
+    async def run():
+        got = {}
+        if rank == 0:
+            await eng.send_weights(iter(w))
+        else:
+            async for n, t in eng.receive_weights():
+                got[n] = t.clone()
+        return got
+
+    got = asyncio.run(run())
+    q.put((rank, rank == 0 or all(torch.equal(got[n], t) for n, t in _weights())))
+    dist.destroy_process_group()
+
+
+def test_relay_chain_delivers_to_every_receiver():
+    import torch.multiprocessing as mp
+
+    from verl_b200.checkpoint_engine.ring_checkpoint_engine import RingCheckpointEngine
+
+    assert CheckpointEngineRegistry.get("mooncake") is RingCheckpointEngine and CheckpointEngineRegistry.get("kimi") is RingCheckpointEngine
+    tr, ro = RingCheckpointEngine.build_topology(2, 3, [])
+    assert tr["rank"] == [0, -1] and ro["rank"] == [1, 2, 3] and ro["world_size"] == [4, 4, 4]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_ring_proc, args=(r, 4, port, q)) for r in range(4)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(4))
+    for p in ps:
+        p.join(timeout=30)
+    assert res == {0: True, 1: True, 2: True, 3: True}

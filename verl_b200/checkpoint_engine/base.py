@@ -48,7 +48,7 @@ class CheckpointEngineRegistry:
     @classmethod
     def get(cls, backend: str) -> type["CheckpointEngine"]:
         if backend not in cls._registry:
-            from . import delta_checkpoint_engine, nccl_checkpoint_engine  # noqa: F401  (self-registering)
+            from . import delta_checkpoint_engine, nccl_checkpoint_engine, ring_checkpoint_engine  # noqa: F401  (self-registering)
         if backend not in cls._registry:
             raise ValueError(f"Checkpoint engine {backend} not registered (known: {sorted(cls._registry)})")
         return cls._registry[backend]

@@ -39,7 +39,13 @@ _ROLLOUT_REGISTRY: dict[tuple[str, str], str] = {
     ("native", "sync"): "verl_b200.workers.rollout.native.adapter.NativeRollout",
     ("hf", "sync"): "verl_b200.workers.rollout.hf_rollout.HFRollout",
     ("naive", "sync"): "verl_b200.workers.rollout.naive_rollout.NaiveRollout",
+    # optional library back-end (import-gated); the native engine is the default and the measured path
+    ("vllm", "async"): "verl_b200.workers.rollout.vllm_rollout.vllm_rollout.VLLMRollout",
+    ("vllm", "sync"): "verl_b200.workers.rollout.vllm_rollout.vllm_rollout.VLLMRollout",
 }
+
+# engines of the reference's registry that this framework replaces with the native engine and does not wrap
+_NOT_WRAPPED = {"sglang": "SGLang", "trtllm": "TensorRT-LLM"}
 
 
 def register_rollout(name: str, mode: str, fqn: str) -> None:
@@ -48,6 +54,10 @@ def register_rollout(name: str, mode: str, fqn: str) -> None:
 
 def get_rollout_class(rollout_name: str, mode: str = "async") -> type[BaseRollout]:
     key = (rollout_name, mode)
+    if rollout_name in _NOT_WRAPPED and key not in _ROLLOUT_REGISTRY:
+        raise ValueError(f"rollout.name={rollout_name}: {_NOT_WRAPPED[rollout_name]} is not wrapped by this framework; use "
+                         f"rollout.name=native (built-in engine: continuous batching, paged KV, CUDA-graph decode) or register "
+                         f"an adapter with register_rollout()")
     if key not in _ROLLOUT_REGISTRY:
         raise ValueError(f"Rollout {rollout_name} with mode {mode} is not supported (known: {sorted(_ROLLOUT_REGISTRY)})")
     import importlib
