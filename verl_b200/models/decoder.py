@@ -31,7 +31,7 @@ from ..ops import functional as F
 from .config import ModelConfig
 from .weights import FlatParams
 
-__all__ = ["PackedBatch", "DecoderModel"]
+__all__ = ["PackedBatch", "DecoderModel", "RouterReplay", "ExpertParallelGroup", "UlyssesSequenceParallel"]
 
 
 @dataclass
@@ -169,6 +169,27 @@ class ExpertParallelGroup:
         return out
 
 
+class RouterReplay:
+    """Expert choices of a token stream, per mixture-of-experts layer. ``record``: every router writes the experts it picked
+    (``store[layer]`` = [T, k]); ``replay``: every router takes its experts from the store and only recomputes their
+    weights from its own logits. Replaying the routing that produced the behaviour log-probs keeps the policy-gradient
+    ratio free of routing flips between the two passes.
+
+    Parity target: ``verl/utils/megatron/router_replay_utils.py`` and ``router_replay_patch.py`` (modes R2 / R3)."""
+
+    def __init__(self, mode: str, store: Optional[dict] = None):
+        assert mode in ("record", "replay")
+        self.mode, self.store = mode, ({} if store is None else store)
+
+    @classmethod
+    def from_tokens(cls, routed: torch.Tensor, moe_layers: list) -> "RouterReplay":
+        """``routed`` [T, n_moe_layers, k] -> replay object."""
+        return cls("replay", {l: routed[:, j].contiguous() for j, l in enumerate(moe_layers)})
+
+    def stacked(self, moe_layers: list) -> torch.Tensor:
+        return torch.stack([self.store[l] for l in moe_layers], dim=1)
+
+
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, params: FlatParams, recompute: str = "none", max_positions: int = 0,
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
@@ -182,6 +203,8 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.router_replay: Optional[RouterReplay] = None   # record / replay the experts every router picks
+        self._layer_idx = 0
         self.ep: Optional[ExpertParallelGroup] = None       # expert parallelism (this model stores E / size experts)
         self.sp: Optional[UlyssesSequenceParallel] = None  # sequence parallelism (token-wise layers on a slice of the stream)
         self.cfg = cfg
@@ -432,6 +455,23 @@ class DecoderModel:
             w = w / w.sum(-1, keepdim=True)
         return w, idx
 
+    def _routing(self, logits: torch.Tensor):
+        """(weights fp32 [T, k], experts int64 [T, k], per-expert counts) with record / replay of the choice."""
+        cfg, rr = self.cfg, self.router_replay
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        if rr is not None and rr.mode == "replay":
+            w, idx = self._route(logits, idx=rr.store[self._layer_idx].to(logits.device).long())
+            return w, idx, torch.bincount(idx.reshape(-1), minlength=E).int()
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and E <= 1024:
+            w, idx, counts = F._ops().moe_route_topk(logits, k, bool(cfg.norm_topk_prob))
+            idx = idx.long()
+        else:
+            w, idx = self._route(logits)
+            counts = torch.bincount(idx.reshape(-1), minlength=E).int()
+        if rr is not None:
+            rr.store[self._layer_idx] = idx.detach().clone()
+        return w, idx, counts
+
     # -- device path: router, expert-grouped layout and grouped tcgen05 GEMMs; no host synchronisation anywhere --------
     @staticmethod
     def _moe_plan(idx: torch.Tensor, counts: torch.Tensor, T: int, k: int, E: int) -> dict:
@@ -462,7 +502,8 @@ class DecoderModel:
         T, H = h2.shape
         E, k = cfg.num_experts, cfg.num_experts_per_tok
         logits = F.gemm(h2, W["mlp.gate.weight"])
-        w, idx, counts = ops.moe_route_topk(logits, k, bool(cfg.norm_topk_prob))
+        w, idx, counts = self._routing(logits)
+        w = w.float().contiguous()
         plan = self._moe_plan(idx, counts, T, k, E)
         xp = ops.moe_gather_rows(h2, plan["src"], None)
         gu = ops.gemm_grouped_rows(xp, W["mlp.experts.gate_up_proj"], False, plan["tile_expert"], plan["num_mtiles"])
@@ -551,11 +592,11 @@ class DecoderModel:
         E, k = cfg.num_experts, cfg.num_experts_per_tok
         El = E // ep.size
         logits = F.gemm(h2, W["mlp.gate.weight"])
-        w, idx = self._route(logits)
+        w, idx, counts = self._routing(logits)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)          # copies sorted by global expert = by (owner, local expert)
         tok = torch.div(order, k, rounding_mode="floor")
-        send_counts = torch.bincount(flat_e, minlength=E).view(ep.size, El)
+        send_counts = counts.long().view(ep.size, El)
         recv_counts = ep.exchange_counts(send_counts)       # [source rank, local expert]
         both = torch.stack([send_counts, recv_counts]).cpu()  # the one host read of the layer: split sizes of the exchange
         in_splits, out_splits = both[0].sum(1).tolist(), both[1].sum(1).tolist()
@@ -613,11 +654,11 @@ class DecoderModel:
         T, H = h2.shape
         E, k = cfg.num_experts, cfg.num_experts_per_tok
         logits = F.gemm(h2, W["mlp.gate.weight"])
-        w, idx = self._route(logits)
+        w, idx, counts = self._routing(logits)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = torch.div(order, k, rounding_mode="floor")
-        counts = torch.bincount(flat_e, minlength=E).tolist()
+        counts = counts.tolist()
         xp = h2[tok]
         Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
         gu = torch.empty(T * k, Wgu.shape[1], dtype=h2.dtype, device=h2.device)
@@ -687,6 +728,7 @@ class DecoderModel:
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(i, "forward")
         W = self.params.layer(i)
+        self._layer_idx = i
         eps = self.cfg.rms_norm_eps
         h1, x, rstd1 = F.rms_norm(a, W["input_layernorm.weight"], eps, residual=r)
         o = self._attn_fwd(W, h1, batch, S, i)

@@ -420,6 +420,18 @@ class NativeEngine(BaseEngine):
         positions = resp_index[resp_valid]
         position_labels = None
         gids = mb.get("_gids")
+        # router replay (mixture-of-experts): take every router's expert choice from the batch, or record it for the batch
+        replay = mb.get("routed_experts") if self.arch.is_moe else None
+        record = bool(mb.get("record_routing", False)) and self.arch.is_moe and not need_grad
+        self.model.router_replay = None
+        if replay is not None or record:
+            from ....models.decoder import RouterReplay
+
+            gids = None  # the stored choices are laid out per row: no shared-prefix packing for this micro-batch
+            moe_layers = list(range(self.arch.num_hidden_layers))
+            mask = mb["attention_mask"].bool()
+            self.model.router_replay = (RouterReplay.from_tokens(replay[mask], moe_layers) if replay is not None
+                                        else RouterReplay("record"))
         if gids is not None and len(set(gids)) < len(gids) and self.model.tp is None:
             # members of a group share their prompt: it is embedded, projected and fed through the MLPs once
             batch, positions, position_labels, resp_valid = pack_shared_prefix_batch(mb["input_ids"], mb["attention_mask"],
@@ -429,6 +441,12 @@ class NativeEngine(BaseEngine):
         out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
         if calc_entropy or need_grad:
             out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
+        if record:
+            routed = self.model.router_replay.stacked(moe_layers)  # [T, layers, k]
+            full = torch.zeros(*mask.shape, *routed.shape[1:], dtype=torch.int32, device=routed.device)
+            full[mask] = routed.int()
+            out["routed_experts"] = full
+            self.model.router_replay = None
         return out
 
     def _forward_micro_sp(self, batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad) -> dict:

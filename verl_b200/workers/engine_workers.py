@@ -431,10 +431,10 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             data = DataProto(batch=data.batch.to(eng.device), non_tensor_batch=data.non_tensor_batch, meta_info=data.meta_info)
         return data
 
-    def _infer(self, engine, data: DataProto, calculate_entropy: bool) -> dict:
+    def _infer(self, engine, data: DataProto, calculate_entropy: bool, replay_routing: bool = True) -> dict:
         data = self._dev(data)
-        d = {k: v for k, v in data.batch.items()}
-        d.update({k: v for k, v in data.meta_info.items() if k in ("temperature", "micro_batch_size_per_gpu",
+        d = {k: v for k, v in data.batch.items() if replay_routing or k != "routed_experts"}
+        d.update({k: v for k, v in data.meta_info.items() if k in ("temperature", "micro_batch_size_per_gpu", "record_routing",
                                                                    "max_token_len_per_gpu", "use_dynamic_bsz")})
         d["calculate_entropy"] = calculate_entropy
         with engine.eval_mode():
@@ -442,13 +442,31 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("train"))
     def compute_log_prob(self, data: DataProto) -> DataProto:
+        # router replay (mixture-of-experts actors): "R2" records the experts chosen in this pass so that the policy update
+        # replays them; "R3" replays the rollout engine's choices when the batch carries them (and records otherwise)
+        record = self._router_replay_mode() in ("R2", "R3") and "routed_experts" not in data.batch.keys()
+        if record:
+            data.meta_info["record_routing"] = True
         out = self._infer(self.actor, data, calculate_entropy=True)
-        return DataProto.from_dict(tensors={"old_log_probs": out["log_probs"].float(), "entropys": out["entropy"].float()},
-                                   meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
+        tensors = {"old_log_probs": out["log_probs"].float(), "entropys": out["entropy"].float()}
+        if record and "routed_experts" in out:
+            tensors["routed_experts"] = out["routed_experts"].to(torch.int32)
+        return DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info.get("temperature", 1.0)})
+
+    def _router_replay_mode(self) -> str:
+        ac = getattr(self, "actor_config", None)
+        for holder in (ac, getattr(ac, "megatron", None), getattr(ac, "engine", None)):
+            rr = getattr(holder, "router_replay", None) if holder is not None else None
+            if rr is None and hasattr(holder, "get"):
+                rr = holder.get("router_replay")
+            mode = (rr.get("mode") if hasattr(rr, "get") else getattr(rr, "mode", None)) if rr is not None else None
+            if mode and mode != "disabled":
+                return str(mode)
+        return "disabled"
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("train"))
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
-        out = self._infer(self.ref, data, calculate_entropy=False)
+        out = self._infer(self.ref, data, calculate_entropy=False, replay_routing=False)  # the reference policy routes by itself
         return DataProto.from_dict(tensors={"ref_log_prob": out["log_probs"].float()})
 
     # ------------------------------------------------------------------ training
