@@ -203,6 +203,7 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.mlp_tile_tokens = 0                            # > 0: sequence-tiled dense MLP (tokens per tile)
         self.router_replay: Optional[RouterReplay] = None   # record / replay the experts every router picks
         self._layer_idx = 0
         self.ep: Optional[ExpertParallelGroup] = None       # expert parallelism (this model stores E / size experts)
@@ -419,6 +420,17 @@ class DecoderModel:
         if self.tp is not None:
             assert S is None, "tensor-parallel shards are forward-only"
             return self.mlp_tp(W, h2)
+        tile = self.mlp_tile_tokens
+        if tile and h2.shape[0] > tile and self.fp8_weights is None:
+            # sequence-tiled MLP: the [tokens, 2 * intermediate] activation exists for one tile at a time and is recomputed
+            # tile by tile in the backward pass (nothing of it is saved)
+            d = torch.empty(h2.shape[0], W["mlp.down_proj.weight"].shape[0], dtype=h2.dtype, device=h2.device)
+            for s0 in range(0, h2.shape[0], tile):
+                gu = F.gemm(h2[s0 : s0 + tile], W["mlp.gate_up_proj.weight"])
+                F.gemm(F.swiglu(gu), W["mlp.down_proj.weight"], out=d[s0 : s0 + tile])
+            if S is not None:
+                S["gu"] = None
+            return self.tp_reduce(d) if self.tp_reduce is not None else d
         gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
         if S is not None:
             S["gu"] = gu
@@ -429,6 +441,18 @@ class DecoderModel:
         if self.cfg.is_moe:
             return self._moe_bwd(W, g_d, h2, S)
         gu = S["gu"]
+        if gu is None:  # sequence-tiled: recompute gate_up per tile, accumulate the weight gradients tile by tile
+            tile = self.mlp_tile_tokens
+            g_h2 = torch.empty_like(h2)
+            for s0 in range(0, h2.shape[0], tile):
+                sl = slice(s0, s0 + tile)
+                gu_t = F.gemm(h2[sl], W["mlp.gate_up_proj.weight"])
+                g_act = F.gemm(g_d[sl], W["mlp.down_proj.weight"], b_mn=True)
+                self._wgrad(W["mlp.down_proj.weight"], g_d[sl], F.swiglu(gu_t))
+                g_gu = F.swiglu_bwd(g_act, gu_t)
+                F.gemm(g_gu, W["mlp.gate_up_proj.weight"], b_mn=True, out=g_h2[sl])
+                self._wgrad(W["mlp.gate_up_proj.weight"], g_gu, h2[sl])
+            return self.tp_reduce(g_h2) if self.tp_reduce is not None else g_h2
         act = F.swiglu(gu)
         g_act = F.gemm(g_d, W["mlp.down_proj.weight"], b_mn=True)
         self._wgrad(W["mlp.down_proj.weight"], g_d, act)

@@ -200,6 +200,11 @@ class NativeEngine(BaseEngine):
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
         self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
+        tm = getattr(self.model_config, "tiled_mlp", None) or {}
+        if (tm.get("enabled") if hasattr(tm, "get") else getattr(tm, "enabled", False)):
+            shards = int((tm.get("num_shards") if hasattr(tm, "get") else getattr(tm, "num_shards", 4)) or 4)
+            budget = int(getattr(ec, "max_token_len_per_gpu", 0) or 8192)
+            self.model.mlp_tile_tokens = max(128, -(-budget // shards) // 128 * 128)
         # trainable parameters: the whole model, or low-rank adapters on a frozen base (``model.lora_rank`` > 0)
         self.tparams = self.params
         self.lora = None
