@@ -50,6 +50,7 @@ class ToolAgentLoop(AgentLoopBase):
             self.tools = {t.name: t for t in tools}
         self.tool_schemas = [t.tool_schema.model_dump(exclude_unset=True, exclude_none=True) for t in self.tools.values()]
         self.parser = ToolParser.get_tool_parser(mt.get("format", "hermes"), tokenizer)
+        self._ct_builder = None  # continuous-token builder, created on first use (False: template not supported)
 
     def _truncate(self, text: str) -> str:
         L = self.max_tool_response_length
@@ -68,6 +69,15 @@ class ToolAgentLoop(AgentLoopBase):
         if tok is None:
             text = "".join(f"\n<tool_response>{m['content']}</tool_response>" for m in messages) + "\n"
             return [ord(c) % 255 + 3 for c in text]
+        if self._ct_builder is None and hasattr(tok, "encode") and hasattr(tok, "convert_tokens_to_ids"):
+            from ...utils.tokenizer.continuous_token import build_continuous_token_builder
+
+            try:
+                self._ct_builder = build_continuous_token_builder(tok, getattr(tok, "name_or_path", None))
+            except Exception:
+                self._ct_builder = False  # template not prefix-stable for the synthetic base: plain difference below
+        if self._ct_builder:
+            return self._ct_builder.tokenize_non_assistant_incremental_messages(messages)
         base = tok.apply_chat_template([{"role": "system", "content": ""}], add_generation_prompt=False, tokenize=True)
         full = tok.apply_chat_template([{"role": "system", "content": ""}] + messages, add_generation_prompt=True, tokenize=True)
         return full[len(base):]
@@ -136,6 +146,10 @@ class ToolAgentLoop(AgentLoopBase):
                 msgs = [{"role": "tool", "content": r.text or ""} for r, _ in results]
                 tool_rewards += [rw for _, rw in results]
                 tool_ids = await self._encode_tool_messages(msgs)
+                if self._ct_builder:
+                    # junction repair: close a turn that was cut without its end marker, do not repeat template text
+                    merged = self._ct_builder.merge_non_assistant_tokens(prompt_ids + ids, tool_ids)
+                    tool_ids = merged.token_ids[len(prompt_ids) + len(ids):]
                 if len(ids) + len(tool_ids) >= self.response_length:
                     state = AgentState.TERMINATED
                     continue
