@@ -47,6 +47,7 @@ class ModelConfig:
     has_embedding: bool = True    # pipeline stage owns the token embedding
     has_head: bool = True         # pipeline stage owns the final norm and the LM/value head
     num_local_experts: int = 0    # expert-parallel shard: experts stored on this rank (0 = all)
+    head_vocab_size: int = 0      # vocabulary-parallel shard: rows of the LM head stored on this rank (0 = all)
 
     def __post_init__(self):
         if self.head_dim is None:
@@ -57,7 +58,7 @@ class ModelConfig:
             self.qk_norm = True
 
     def local_shard(self, tp: int = 1, num_layers: Optional[int] = None, has_embedding: bool = True, has_head: bool = True,
-                    ep: int = 1) -> "ModelConfig":
+                    ep: int = 1, vocab_parallel: bool = False) -> "ModelConfig":
         """Configuration of what ONE rank of a tensor x pipeline (x expert) parallel layout stores and computes: 1/tp of the
         attention heads and of the MLP width (column-parallel QKV / gate-up, row-parallel O / down), ``num_layers``
         consecutive layers, the embedding only on the first and the head only on the last stage, 1/ep of the experts."""
@@ -71,6 +72,8 @@ class ModelConfig:
                                 num_hidden_layers=self.num_hidden_layers if num_layers is None else num_layers,
                                 head_dim=self.head_dim, has_embedding=has_embedding, has_head=has_head,
                                 num_local_experts=(self.num_experts // ep if self.is_moe and ep > 1 else 0),
+                                head_vocab_size=(self.vocab_size // tp if vocab_parallel and tp > 1 and has_head
+                                                 and not self.tie_word_embeddings and self.vocab_size % (8 * tp) == 0 else 0),
                                 tie_word_embeddings=self.tie_word_embeddings and has_embedding and has_head, extra=dict(self.extra))
         return c
 

@@ -203,6 +203,7 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.vocab_parallel = None                          # (group, first vocabulary row) of a vocabulary-parallel LM head
         self.mlp_tile_tokens = 0                            # > 0: sequence-tiled dense MLP (tokens per tile)
         self.router_replay: Optional[RouterReplay] = None   # record / replay the experts every router picks
         self._layer_idx = 0
@@ -888,7 +889,11 @@ class DecoderModel:
                 labels = position_labels if position_labels is not None else labels.index_select(0, positions)
             else:
                 hS = hN
-            lp, ent, lse = F.lmhead_logprob_entropy(hS, self.params.lm_head_weight, labels, temperature)
+            if self.vocab_parallel is not None:
+                grp, v0 = self.vocab_parallel
+                lp, ent, lse = F.lmhead_logprob_entropy_vocab_parallel(hS, self.params.lm_head_weight, labels, temperature, v0, grp)
+            else:
+                lp, ent, lse = F.lmhead_logprob_entropy(hS, self.params.lm_head_weight, labels, temperature)
         if not need_grad:
             return lp, ent
         state.update(kind="lm", labels=labels, temperature=temperature, lse=lse, ent=ent, positions=positions, hS=hS)
@@ -937,7 +942,14 @@ class DecoderModel:
                 g_lp = torch.zeros_like(state["lse"])
             head = self.params.lm_head_weight
             g_hS = F.lmhead_backward(state["hS"], head, state["labels"], state["temperature"], state["lse"], state["ent"],
-                                     g_lp.float(), g_ent.float() if g_ent is not None else None, getattr(head, "main_grad", None))
+                                     g_lp.float(), g_ent.float() if g_ent is not None else None, getattr(head, "main_grad", None),
+                                     vocab_start=self.vocab_parallel[1] if self.vocab_parallel is not None else 0)
+            if self.vocab_parallel is not None:  # every rank holds the contribution of its vocabulary slice
+                import torch.distributed as dist
+
+                g_hS = g_hS.float()
+                dist.all_reduce(g_hS, group=self.vocab_parallel[0])
+                g_hS = g_hS.to(hN.dtype)
             if state.get("positions") is not None:
                 g_hN = torch.zeros(hN.shape, dtype=torch.float32, device=hN.device)
                 g_hN.index_add_(0, state["positions"], g_hS.float())  # positions may repeat (shared prefixes)

@@ -73,7 +73,7 @@ def build_param_specs(cfg: ModelConfig, value_head: bool = False) -> list[ParamS
         # scalar head stored with 8 rows (row 0 is the value) so the GEMM's N % 8 == 0 rule holds
         specs.append(ParamSpec("v_head.weight", (8, h), "normal", True, L))
     elif not cfg.tie_word_embeddings:
-        specs.append(ParamSpec("lm_head.weight", (cfg.vocab_size, h), "normal", True, L))
+        specs.append(ParamSpec("lm_head.weight", (cfg.head_vocab_size or cfg.vocab_size, h), "normal", True, L))
     return specs
 
 

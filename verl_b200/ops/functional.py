@@ -220,17 +220,48 @@ def lmhead_logprob_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: t
     return _torch_logprob_entropy(hidden, weight, labels, inv_temp)
 
 
+def lmhead_logprob_entropy_vocab_parallel(hidden: torch.Tensor, weight_shard: torch.Tensor, labels: torch.Tensor,
+                                          temperature: float, vocab_start: int, group):
+    """Vocabulary-parallel fused head: every rank of ``group`` holds rows ``[vocab_start, vocab_start + V_local)`` of the
+    head and runs the fused log-prob / entropy kernel on its slice; the slices are combined from three [T] vectors per rank
+    (local LSE, label logit, expected logit), so no logits ever cross the link. Returns the global (logprob, entropy, lse).
+
+    Parity target: ``verl/utils/megatron/tensor_parallel.py`` (``vocab_parallel_log_probs_from_logits``,
+    ``vocab_parallel_entropy``)."""
+    import torch.distributed as dist
+
+    Vl = weight_shard.shape[0]
+    local = labels - vocab_start
+    mine = (local >= 0) & (local < Vl)
+    lp_l, ent_l, lse_l = lmhead_logprob_entropy(hidden, weight_shard, torch.where(mine, local, torch.zeros_like(local)), temperature)
+    n = dist.get_world_size(group)
+    all_lse = torch.empty(n, lse_l.numel(), dtype=lse_l.dtype, device=lse_l.device)
+    if lse_l.is_cuda:
+        dist.all_gather_into_tensor(all_lse, lse_l.contiguous(), group=group)
+    else:
+        dist.all_gather(list(all_lse.unbind(0)), lse_l.contiguous(), group=group)
+    lse = torch.logsumexp(all_lse, dim=0)
+    share = torch.exp(lse_l - lse)                              # probability mass of this rank's slice
+    pack = torch.stack([torch.where(mine, lp_l + lse_l, torch.zeros_like(lp_l)), share * (lse_l - ent_l)])
+    dist.all_reduce(pack, group=group)
+    return pack[0] - lse, lse - pack[1], lse
+
+
 def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_ent, dweight_out: Optional[torch.Tensor],
-                    vocab_chunk: int = 9728):
+                    vocab_chunk: int = 9728, vocab_start: int = 0):
     """Returns d_hidden (same dtype as hidden) and accumulates d_weight into ``dweight_out`` (fp32 [V, H]); a frozen head
-    (``dweight_out`` None) skips the weight-gradient GEMMs."""
+    (``dweight_out`` None) skips the weight-gradient GEMMs. With a vocabulary-parallel head, ``weight`` is this rank's
+    slice starting at ``vocab_start`` while ``lse`` / ``entropy`` are the global values: the result is this rank's partial
+    d_hidden (to be summed over the group)."""
     inv_temp = 1.0 / max(float(temperature), 1e-8)
     T, H = hidden.shape
     V = weight.shape[0]
     if not hidden.is_cuda:
         logits = (hidden.float() @ weight.float().t()) * inv_temp
-        p = torch.softmax(logits, -1)
-        onehot = torch.zeros_like(p).scatter_(1, labels.unsqueeze(1), 1.0)
+        p = torch.exp(logits - lse.unsqueeze(1))
+        local = labels - vocab_start
+        mine = ((local >= 0) & (local < V)).unsqueeze(1)
+        onehot = torch.zeros_like(p).scatter_(1, local.clamp(0, V - 1).unsqueeze(1), 1.0) * mine
         dl = g_lp.unsqueeze(1) * (onehot - p)
         if g_ent is not None:
             ex = (lse - entropy).unsqueeze(1)
@@ -249,7 +280,7 @@ def lmhead_backward(hidden, weight, labels, temperature, lse, entropy, g_lp, g_e
         v1 = min(V, v0 + vocab_chunk)
         wc = weight[v0:v1]
         dl = buf[:, : v1 - v0]
-        ops.lmhead_dlogits(hidden, wc, labels, v0, inv_temp, lse, ex, g_lp, g_ent, dl)
+        ops.lmhead_dlogits(hidden, wc, labels, vocab_start + v0, inv_temp, lse, ex, g_lp, g_ent, dl)
         # d_hidden += dl @ W[v0:v1]      (B stored [K=Vc, N=H] -> MN-major)
         gemm(dl, wc, out=dh, b_mn=True, out_f32=True, accumulate=True)
         # d_W[v0:v1] += dl^T @ hidden

@@ -95,10 +95,10 @@ class ModelParallelTopology:
         lo = self.pp_rank * base + min(self.pp_rank, rem)
         return lo, lo + base + (1 if self.pp_rank < rem else 0)
 
-    def local_config(self, cfg: ModelConfig) -> ModelConfig:
+    def local_config(self, cfg: ModelConfig, vocab_parallel: bool = True) -> ModelConfig:
         lo, hi = self.layer_range(cfg.num_hidden_layers)
         return cfg.local_shard(tp=self.tp, num_layers=hi - lo, has_embedding=self.is_first_stage, has_head=self.is_last_stage,
-                               ep=self.ep)
+                               ep=self.ep, vocab_parallel=vocab_parallel)
 
 
 @dataclass
@@ -109,12 +109,13 @@ class ShardMap:
     blocks: tuple = ()     # rows: sizes of the stacked blocks of the FULL tensor, each block is cut into tp slices
 
 
-def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_head: bool = False) -> list[ShardMap]:
+def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_head: bool = False,
+                    vocab_parallel: bool = True) -> list[ShardMap]:
     """One entry per tensor of the local shard model, in the local parameter order."""
     from ..models.weights import build_param_specs
 
     lo, _ = topo.layer_range(full_cfg.num_hidden_layers)
-    local_cfg = topo.local_config(full_cfg)
+    local_cfg = topo.local_config(full_cfg, vocab_parallel and not value_head)
     out = []
     for spec in build_param_specs(local_cfg, value_head and topo.is_last_stage):
         name = spec.name
@@ -124,7 +125,9 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
             full_name = f"layers.{int(i) + lo}.{rest}"
         else:
             rest = name
-        if rest.startswith("mlp.experts.") and topo.ep > 1:
+        if name == "lm_head.weight" and local_cfg.head_vocab_size:
+            out.append(ShardMap(name, full_name, "rows", (full_cfg.vocab_size,)))
+        elif rest.startswith("mlp.experts.") and topo.ep > 1:
             out.append(ShardMap(name, full_name, "experts"))
         elif rest.startswith("self_attn.qkv_proj"):
             out.append(ShardMap(name, full_name, "rows", (full_cfg.q_size, full_cfg.kv_size, full_cfg.kv_size)))

@@ -61,8 +61,10 @@ class ModelParallelEngine(NativeEngine):
         if self.full_arch.tie_word_embeddings and self.pp_size > 1:
             raise NotImplementedError("pipeline parallelism with tied input/output embeddings needs the embedding shared between "
                                       "the first and the last stage; use pipeline_model_parallel_size=1 for this model")
-        self.arch = self.topo.local_config(self.full_arch)
-        self.maps = build_shard_map(self.full_arch, self.topo, self.value_head)
+        # vocabulary-parallel LM head (each tensor-parallel rank holds V / tp rows; the fused log-prob kernel runs per slice)
+        vp = bool(getattr(self.engine_config, "vocab_parallel_head", True)) and not self.value_head
+        self.arch = self.topo.local_config(self.full_arch, vocab_parallel=vp)
+        self.maps = build_shard_map(self.full_arch, self.topo, self.value_head, vocab_parallel=vp)
         outer = get_data_parallel_group()
         set_data_parallel_group(self.topo.dp_group)
         try:
@@ -70,6 +72,8 @@ class ModelParallelEngine(NativeEngine):
             super().initialize()
         finally:
             set_data_parallel_group(outer)
+        if self.arch.head_vocab_size:
+            self.model.vocab_parallel = (self.topo.tp_group, self.topo.tp_rank * self.arch.head_vocab_size)
         if self.topo.ep > 1:
             from ....models.decoder import ExpertParallelGroup
 
