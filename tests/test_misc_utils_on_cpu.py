@@ -179,3 +179,24 @@ def test_ulysses_functions_on_gloo():
     for r in range(2):
         assert "error" not in res[r], res[r]["error"]
         assert res[r] == {"fwd": True, "rt": True, "grad": True}, res[r]
+
+
+def test_rm_dataset_pairs(tmp_path):
+    import pandas as pd
+
+    from verl_b200.utils.dataset.rm_dataset import RMDataset
+
+    class Tok:
+        pad_token_id, eos_token_id = 0, 2
+
+        def __call__(self, t, add_special_tokens=False):
+            return {"input_ids": [ord(c) % 50 + 3 for c in t]}
+
+    f = tmp_path / "pairs.parquet"
+    pd.DataFrame({"prompt": ["hi", "yo"], "chosen": ["good", "fine"], "rejected": ["bad", "a much longer answer"]}).to_parquet(f)
+    ds = RMDataset(str(f), Tok(), max_length=8)
+    a, b = ds[0], ds[1]
+    assert len(ds) == 2 and a["input_ids"].shape == (2, 8)
+    assert a["attention_mask"].sum(-1).tolist() == [7, 6] and a["input_ids"][0, 6] == 2 and a["input_ids"][0, 7] == 0
+    assert b["attention_mask"][1].sum() == 8          # truncated to max_length
+    assert torch.equal(a["input_ids"][0, :2], a["input_ids"][1, :2])   # both rows start with the prompt

@@ -159,6 +159,33 @@ def main(argv=None):
         ctrl[1] = 1.0
         ms = T(lambda: ops.adamw_(master, g, m, v2, outb, ctrl, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, False))
         report("adamw_fused_cast", [n], ms, bytes_=n * (4 * 4 + 3 * 4 + 2.0))
+    if want("moe"):
+        # one mixture-of-experts MLP of Qwen3-30B-A3B (128 experts, top-8, H 2048, I 768) on one GPU: router kernel,
+        # expert-grouped layout, grouped tcgen05 GEMMs, weighted combine; backward adds grouped dgrad + wgrad
+        from ..models import DecoderModel, FlatParams
+        from ..models.config import ModelConfig
+
+        Tm = 2048 if a.small else 8192
+        cfg = ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=2048, intermediate_size=6144, num_hidden_layers=1,
+                          num_attention_heads=32, num_key_value_heads=4, head_dim=128, num_experts=128, num_experts_per_tok=8,
+                          moe_intermediate_size=768, eos_token_id=2, pad_token_id=0, qk_norm=True, norm_topk_prob=True)
+        P = FlatParams(cfg, dtype=torch.bfloat16, device=dev, with_main_grad=True)
+        P.init_weights(seed=1, std=0.02)
+        model = DecoderModel(cfg, P)
+        W = P.layer(0)
+        h2 = rnd(Tm, 2048) * 10
+        g = rnd(Tm, 2048)
+        fl = 2.0 * Tm * 8 * 3 * 2048 * 768
+        ms = T(lambda: model._moe_fwd(W, h2, None))
+        report("moe_layer_fwd_128e_top8", [Tm, 2048, 128, 8, 768], ms, flops=fl)
+
+        def fwd_bwd():
+            S = {}
+            model._moe_fwd(W, h2, S)
+            model._moe_bwd(W, g, h2, S)
+
+        ms = T(fwd_bwd)
+        report("moe_layer_fwd_bwd_128e_top8", [Tm, 2048, 128, 8, 768], ms, flops=3.0 * fl)
     native.check_status()
 
 
