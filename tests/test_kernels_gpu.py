@@ -363,3 +363,21 @@ def test_rollout_engine_cuda_graph_matches_eager(ops):
                             use_cuda_graph=graph, eos_token_id=-1)
         outs[graph] = [o.token_ids for o in eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=9))]
     assert outs[True] == outs[False] and all(len(t) == 9 for t in outs[True])
+
+
+def test_nvfp4_fake_quant_matches_reference():
+    """NVFP4 fake-quantisation kernel against the plain PyTorch formulation of the same op (fp32 math)."""
+    from verl_b200.utils.qat import nvfp4_fake_quantize, nvfp4_global_scale
+
+    torch.manual_seed(0)
+    x = (torch.randn(300, 1024, device="cuda") * 0.05).bfloat16()
+    x[5] *= 40                                   # a row with large magnitudes (block scales near the top of e4m3)
+    x[7, :32] = 0                                # all-zero blocks
+    gs = nvfp4_global_scale(x)
+    y = nvfp4_fake_quantize(x, gs)
+    ref = nvfp4_fake_quantize(x.cpu().float(), gs)
+    bad = (y.float().cpu() - ref).abs() > 1e-2 * ref.abs().clamp(min=1e-3)   # bf16 rounding of the output only
+    assert bad.float().mean() < 1e-3, bad.float().mean()
+    z = x.clone()
+    nvfp4_fake_quantize(z, gs, out=z)            # in place
+    assert torch.equal(z, y)

@@ -497,6 +497,18 @@ int64_t comm_status() { return vb_comm_status(); }
 
 // ---- fp8 (e4m3) with 1x128 block scales
 // x [R, C] bf16 -> (q [R, C] uint8 holding e4m3, scales [C/128, R] fp32)
+// NVFP4 fake quantisation (e2m1 values, 1x16 blocks, e4m3 block scales in units of global_scale); out may be x itself.
+void nvfp4_fake_quant_(const Tensor& x, Tensor out, double global_scale) {
+  CHECK_BF16(x);
+  CHECK_BF16(out);
+  TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 && x.sizes() == out.sizes() &&
+              x.size(1) % 16 == 0, "nvfp4_fake_quant_: [R, C] with C % 16 == 0");
+  const c10::cuda::CUDAGuard guard(x.device());
+  count(1);
+  CHECK_RC(vb_nvfp4_fake_quant(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), x.size(0), (int)x.size(1),
+                               (float)global_scale, cur_stream()), "vb_nvfp4_fake_quant");
+}
+
 std::tuple<Tensor, Tensor> fp8_quant_1x128(const Tensor& x) {
   CHECK_BF16(x);
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 128 == 0, "fp8_quant_1x128: [R, C] with C % 128 == 0");
@@ -683,6 +695,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
+  m.def("nvfp4_fake_quant_", &nvfp4_fake_quant_);
   m.def("gemm_fp8_blockscale", &gemm_fp8_blockscale);
   m.def("moe_route_topk", &moe_route_topk);
   m.def("moe_gather_rows", &moe_gather_rows);

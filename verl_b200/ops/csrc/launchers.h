@@ -80,6 +80,8 @@ int vb_adamw_allgather(float* master, const float* grad, float* m, float* v, con
 int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n, int W, int rank, cudaStream_t s);
 int vb_comm_status();
 // gemm_fp8_blockscale.cu
+int vb_nvfp4_fake_quant(const void* x, long long ldx, void* y, long long ldy, long long rows, int cols, float global_scale,
+                        cudaStream_t s);
 int vb_fp8_quant_1x128(const void* x, long long ldx, void* q, long long ldq, float* scales, int R, int C, cudaStream_t s);
 int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, const void* bias, int M, int N,
                            int K, long long lda, long long ldb, long long ldd, cudaStream_t stream);

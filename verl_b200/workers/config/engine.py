@@ -37,6 +37,8 @@ class EngineConfig(BaseConfig):
     use_torch_compile: bool = False
     entropy_from_logits_with_chunking: bool = False
     entropy_checkpointing: bool = False
+    qat: dict = field(default_factory=dict)            # {enable, mode: w4a16, group_size: 16, ignore_patterns}
+    router_replay: dict = field(default_factory=dict)  # {mode: disabled | R2 | R3}
 
 
 @dataclass

@@ -255,6 +255,14 @@ class NativeEngine(BaseEngine):
             self.ctrl = torch.zeros(4, dtype=torch.float32, device=self.device)
             if not self.lazy_grad:
                 self._alloc_grads()
+        # quantisation-aware training: working weights = fake-quantised master weights (master stays full precision)
+        from ....utils.qat import QATConfig
+
+        self.qat = QATConfig.from_any(getattr(ec, "qat", None))
+        self._qat_names = None
+        if self.qat.enable and self._shared_params is None:
+            assert self.lora is None, "QAT and LoRA are exclusive"
+            self._apply_qat()
         self._initialized = True
 
     def _load_or_init(self, seed: int) -> None:
@@ -575,6 +583,8 @@ class NativeEngine(BaseEngine):
         self._publish_shard()
         if self.lora is not None:
             self.lora.merge()  # the working weights (shared with the rollout engine) follow the adapters
+        if self.qat.enable:
+            self._apply_qat()  # fresh bf16 casts of the master weights -> their NVFP4 values
         norm = float(norm)
         if self.lazy_grad:
             self.tparams.detach_main_grad()
@@ -602,11 +612,20 @@ class NativeEngine(BaseEngine):
                              self._sym_params.multicast_ptr if use_mc else 0, self.shard_lo, self.rank, self.ctrl, lr,
                              float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay), self.opt_step_count)
         self._peer_barrier()
+        if self.qat.enable:
+            self._apply_qat()
         norm = float(self.ctrl[3])
         code = int(ops.comm_status())
         if code != 0:
             raise RuntimeError(f"peer barrier timed out (status {code}): a rank did not reach the optimizer step")
         return norm
+
+    def _apply_qat(self) -> None:
+        from ....utils.qat import apply_qat_to_params, qat_target_names
+
+        if self._qat_names is None:
+            self._qat_names = qat_target_names(self.params, self.qat)
+        apply_qat_to_params(self.params, self.qat, self._qat_names)
 
     def _publish_shard(self) -> None:
         """All-gather this rank's updated slice of the working weights into every replica."""
