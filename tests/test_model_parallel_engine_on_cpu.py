@@ -14,7 +14,7 @@ def _data(seed=0, b=4, L=24, R=16, V=500):
     return {"input_ids": ids, "attention_mask": am, "responses": ids[:, -R:], "response_mask": am[:, -R:]}
 
 
-def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama"):
+def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b"):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                           VERL_ENGINE_DEVICE="cpu")
@@ -28,7 +28,8 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama"):
 
         initialize_global_process_group()
         ec = McoreEngineConfig(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp, expert_model_parallel_size=ep, seed=7,
-                               micro_batch_size_per_gpu=2 if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
+                               micro_batch_size_per_gpu=mbs if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
+        object.__setattr__(ec, "pipeline_schedule", schedule)
         eng = EngineRegistry.new("language_model", "megatron", get_preset(preset), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
         eng.initialize()
         dp = eng.topo.dp
@@ -49,7 +50,7 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama"):
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-def _run(world, tp, pp, ep=1, preset="tiny-llama"):
+def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b"):
     import torch.multiprocessing as mp
 
     with socket.socket() as s:
@@ -57,7 +58,7 @@ def _run(world, tp, pp, ep=1, preset="tiny-llama"):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset)) for r in range(world)]
+    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset, mbs, schedule)) for r in range(world)]
     for p in ps:
         p.start()
     res = dict(q.get(timeout=300) for _ in range(world))
@@ -97,6 +98,18 @@ def test_model_parallel_engine_matches_unsharded(world, tp, pp):
     for r in range(world):
         d = r // (tp * pp)
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[d], atol=1e-4), r
+
+
+@pytest.mark.parametrize("world,pp,mbs,schedule", [(2, 2, 1, "1f1b"), (3, 3, 1, "1f1b"), (2, 2, 1, "gpipe")])
+def test_pipeline_schedules_with_more_micro_batches_than_stages(world, pp, mbs, schedule):
+    """Four micro-batches through two / three stages: warm-up, steady one-forward-one-backward and drain phases all run."""
+    ref_norm, ref_lp, ref_flat = _reference()
+    res = _run(world, 1, pp, mbs=mbs, schedule=schedule)
+    for r in range(world):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), ref_lp, atol=1e-4), r
 
 
 def test_expert_parallel_engine_matches_unsharded():

@@ -125,54 +125,120 @@ class ModelParallelEngine(NativeEngine):
         dist.recv(x, src=self.topo.prev_rank)
         return x
 
+    # ---- point-to-point helpers of the pipeline (shapes are known on both sides: every rank of a replica sees the batch)
+    def _hidden_buf(self, T: int) -> torch.Tensor:
+        return torch.empty(T, self.full_arch.hidden_size, dtype=self.dtype, device=self.device)
+
+    def _exchange(self, send: Optional[torch.Tensor], dst: Optional[int], recv_T: Optional[int], src: Optional[int]) -> Optional[torch.Tensor]:
+        """One batched point-to-point step: optionally send ``send`` to ``dst`` and/or receive a [recv_T, H] tensor from
+        ``src``. Issuing both directions as one batch is what keeps neighbouring stages, which talk to each other in both
+        directions during the steady state, from waiting on each other."""
+        ops, out = [], None
+        if send is not None:
+            ops.append(dist.P2POp(dist.isend, send.contiguous(), dst))
+        if recv_T is not None:
+            out = self._hidden_buf(recv_T)
+            ops.append(dist.P2POp(dist.irecv, out, src))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        return out
+
     def _run_micro_batches(self, mbs: list[dict], R: int, temperature: float, calc_entropy: bool, loss_function, forward_only: bool):
+        """Pipeline schedule. Training uses one-forward-one-backward (1F1B): stage s runs ``P - 1 - s`` warm-up forwards,
+        then alternates a forward with the backward of its oldest micro-batch in flight, then drains, so a stage never holds
+        the activations of more than ``P - s`` micro-batches (the all-forward-then-all-backward order holds all of them;
+        ``pipeline_schedule=gpipe`` selects it). Forward-only passes stream the micro-batches through the stages."""
         topo = self.topo
         if topo.pp == 1:
             return super()._run_micro_batches(mbs, R, temperature, calc_entropy, loss_function, forward_only)
-        need_grad = not forward_only
-        outs: dict[str, list] = {}
-        rows: list[int] = []
+        need_grad = not forward_only and loss_function is not None
+        first, last = topo.is_first_stage, topo.is_last_stage
+        packed = [pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R) for mb in mbs]
+        Ts = [p[0].num_tokens for p in packed]
+        M = len(mbs)
+        rows: list[int] = [r for mb in mbs for r in mb["_rows"]]
         losses, metrics = [], {}
-        pending = []  # per micro-batch: what the backward pass needs
-        # ---- all forwards
-        for mb in mbs:
-            batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R)
-            T = batch.num_tokens
-            x_in = None if topo.is_first_stage else self._stage_recv(T)
-            rows.extend(mb["_rows"])
-            if not topo.is_last_stage:
+        head_out: list = [None] * M
+        inflight: list = []  # (state, loss, index) of forwards whose backward has not run yet, oldest first
+
+        def forward(i: int, x_in):
+            batch, labels, resp_index, resp_valid = packed[i]
+            if not last:
                 x_out, st = self.model.forward_stage(batch, x_in, save=need_grad)
-                dist.send(x_out.contiguous(), dst=topo.next_rank)
-                pending.append((st, None, T))
-                out = None
+                inflight.append((st, None, i))
+                return x_out
+            out = self._head_outputs(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in)
+            st = getattr(self.model, "last_state", None) if need_grad else None
+            loss = None
+            if loss_function is not None:
+                loss, m = loss_function(model_output=out, data=mbs[i], dp_group=None)
+                losses.append(loss.detach())
+                for k, v in m.items():
+                    metrics.setdefault(k, []).append(v)
+            inflight.append((st, loss, i))
+            head_out[i] = {k: v.detach() for k, v in out.items()}
+            return None
+
+        def backward(g_out):
+            st, loss, _ = inflight.pop(0)
+            if last:
+                loss.backward()
+                return st.get("g_input")
+            return self.model.backward_stage(st, g_out)
+
+        schedule = str(getattr(self.engine_config, "pipeline_schedule", "1f1b") or "1f1b").lower()
+        if not need_grad or schedule == "gpipe":
+            for i in range(M):
+                x_in = None if first else self._exchange(None, None, Ts[i], topo.prev_rank)
+                x_out = forward(i, x_in)
+                if not last:
+                    self._exchange(x_out, topo.next_rank, None, None)
+            if need_grad:
+                for i in range(M):
+                    g_out = None if last else self._exchange(None, None, Ts[i], topo.next_rank)
+                    g_in = backward(g_out)
+                    if not first:
+                        self._exchange(g_in, topo.prev_rank, None, None)
             else:
-                out = self._head_outputs(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in)
-                st = getattr(self.model, "last_state", None) if need_grad else None
-                loss = None
-                if loss_function is not None:
-                    loss, m = loss_function(model_output=out, data=mb, dp_group=None)
-                    losses.append(loss.detach())
-                    for k, v in m.items():
-                        metrics.setdefault(k, []).append(v)
-                pending.append((st, loss, T))
-            # every stage returns the outputs of the last stage
-            out = self._broadcast_outputs(out, resp_valid.shape, calc_entropy or need_grad)
+                inflight.clear()
+        else:
+            warm = min(topo.pp - 1 - topo.pp_rank, M)
+            steady = M - warm
+            nf = 0  # forwards issued
+            x_in = None if first or M == 0 else self._exchange(None, None, Ts[0], topo.prev_rank)
+            for _ in range(warm):
+                x_out = forward(nf, x_in)
+                nf += 1
+                nxt = Ts[nf] if (nf < M and not first) else None
+                # the last stage has no warm-up, so x_out is never None here
+                self._exchange(x_out, topo.next_rank, None, None)
+                x_in = self._exchange(None, None, nxt, topo.prev_rank) if nxt is not None else None
+            for k in range(steady):
+                x_out = forward(nf, x_in)
+                nf += 1
+                oldest = inflight[0][2]
+                g_out = None if last else self._exchange(x_out, topo.next_rank, Ts[oldest], topo.next_rank)
+                g_in = backward(g_out)
+                more = nf < M
+                if first:
+                    x_in = None
+                else:
+                    x_in = self._exchange(g_in, topo.prev_rank, Ts[nf] if more else None, topo.prev_rank)
+            while inflight:
+                oldest = inflight[0][2]
+                g_out = None if last else self._exchange(None, None, Ts[oldest], topo.next_rank)
+                g_in = backward(g_out)
+                if not first:
+                    self._exchange(g_in, topo.prev_rank, None, None)
+        # every stage returns the outputs of the last stage
+        outs: dict[str, list] = {}
+        for i in range(M):
+            out = self._broadcast_outputs(head_out[i], packed[i][3].shape, calc_entropy or need_grad)
             for k, v in out.items():
                 outs.setdefault(k, []).append(v.detach())
-        # ---- all backwards, same order
-        if need_grad and loss_function is not None:
-            for st, loss, T in pending:
-                if topo.is_last_stage:
-                    loss.backward()
-                    g_in = st.get("g_input")
-                else:
-                    g_out = torch.empty(T, self.full_arch.hidden_size, dtype=self.dtype, device=self.device)
-                    dist.recv(g_out, src=topo.next_rank)
-                    g_in = self.model.backward_stage(st, g_out)
-                if not topo.is_first_stage:
-                    dist.send(g_in.contiguous(), dst=topo.prev_rank)
         # the loss and its metrics live on the last stage: share them inside the pipeline group
-        losses, metrics = self._broadcast_loss(losses, metrics, len(mbs), loss_function is not None)
+        losses, metrics = self._broadcast_loss(losses, metrics, M, loss_function is not None)
         return outs, rows, losses, metrics
 
     def _head_outputs(self, batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in) -> dict:
