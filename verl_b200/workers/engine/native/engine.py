@@ -162,6 +162,23 @@ class NativeEngine(BaseEngine):
         self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
         self._src0 = dist.get_global_rank(self.group, 0) if (self.group is not None and dist.is_initialized()) else 0
+        # Hybrid sharding (``fsdp_size`` = s, 0 < s < data-parallel size): optimizer state and gradient shards are split over
+        # blocks of s consecutive ranks and replicated across the blocks; gradients are reduce-scattered inside a block and
+        # all-reduced between the blocks. Default: one block = the whole data-parallel group.
+        self.sh_group, self.sh_rank, self.sh_world = self.group, self.rank, self.world
+        self.rep_group, self.rep_rank, self.rep_world = None, 0, 1
+        fs = int(getattr(self.engine_config, "fsdp_size", -1) or -1)
+        if 0 < fs < self.world:
+            assert self.world % fs == 0, "fsdp_size must divide the data-parallel size"
+            pool = dist.get_process_group_ranks(self.group if self.group is not None else dist.group.WORLD)
+            for b0 in range(0, self.world, fs):          # collective: every rank creates every group, in the same order
+                g = dist.new_group(pool[b0 : b0 + fs])
+                if b0 <= self.rank < b0 + fs:
+                    self.sh_group, self.sh_rank, self.sh_world = g, self.rank - b0, fs
+            for r0 in range(fs):
+                g = dist.new_group(pool[r0::fs])
+                if self.rank % fs == r0:
+                    self.rep_group, self.rep_rank, self.rep_world = g, self.rank // fs, self.world // fs
         if self.device_name == "cuda":
             self.device = torch.device("cuda", torch.cuda.current_device())
             self.dtype = torch.bfloat16
@@ -179,20 +196,21 @@ class NativeEngine(BaseEngine):
             want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
                           and not int(getattr(self.model_config, "lora_rank", 0) or 0)
                           and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
+                          and self.rep_world == 1
                           and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
             buf = None
             if want_fused:
                 from ....parallel.symmetric import PeerBarrier, SymmetricBuffer, symmetric_available
 
                 if symmetric_available():
-                    probe = FlatParams(self.arch, dtype=self.dtype, device="meta", value_head=self.value_head, pad_to=self.world)
+                    probe = FlatParams(self.arch, dtype=self.dtype, device="meta", value_head=self.value_head, pad_to=self.sh_world)
                     self._sym_params = SymmetricBuffer.allocate(probe.numel, self.dtype, self.device)
                     self._sym_grads = SymmetricBuffer.allocate(probe.numel, torch.float32, self.device)
                     self._peer_barrier = PeerBarrier(self.device)
                     buf = self._sym_params.tensor
                     self.fused_comm = True
             self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
-                                     pad_to=self.world, buffer=buf)
+                                     pad_to=self.sh_world, buffer=buf)
             self._load_or_init(seed)
         # gradient checkpointing: "auto" keeps the activations of as many trailing layers as free memory allows and
         # recomputes the rest (all of them when memory is short, none when everything fits)
@@ -214,7 +232,7 @@ class NativeEngine(BaseEngine):
 
             assert not self.fused_comm, "LoRA uses the collective-library optimizer path (set fused_comm=false)"
             self.lora = LoRAParams(self.params, lora_rank, float(getattr(self.model_config, "lora_alpha", 16) or 16),
-                                   getattr(self.model_config, "target_modules", None), pad_to=self.world, seed=seed)
+                                   getattr(self.model_config, "target_modules", None), pad_to=self.sh_world, seed=seed)
             self.tparams = self.lora
         # Ulysses sequence parallelism: blocks of ``sp`` consecutive ranks work on the same micro-batches
         self.sp_size = int(getattr(ec, "ulysses_sequence_parallel_size", 1) or 1)
@@ -241,9 +259,9 @@ class NativeEngine(BaseEngine):
         # region (the experts of an expert-parallel shard) is optimised whole by its owner.
         self.dense_numel = int(getattr(self.tparams, "dense_numel", self.tparams.numel))
         self.local_numel = self.tparams.numel - self.dense_numel
-        self.shard_numel = self.dense_numel // self.world
-        self.shard_lo = self.rank * self.shard_numel
-        assert self.local_numel == 0 or (self.world > 1 and not self.fused_comm and self.lora is None)
+        self.shard_numel = self.dense_numel // self.sh_world
+        self.shard_lo = self.sh_rank * self.shard_numel
+        assert self.local_numel == 0 or (self.world > 1 and not self.fused_comm and self.lora is None and self.rep_world == 1)
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
         # memory (4 bytes/param) is available to the rollout KV cache in between.
         self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
@@ -510,7 +528,7 @@ class NativeEngine(BaseEngine):
     def _alloc_grads(self) -> None:
         self.tparams.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-        self.grad_shard = self.tparams.main_grad[sl] if self.world == 1 else torch.zeros_like(self.master)
+        self.grad_shard = self.tparams.main_grad[sl] if self.sh_world == 1 else torch.zeros_like(self.master)
 
     def _global_sumsq_correction(self) -> None:
         """Hook for model-parallel engines: ``ctrl[0]`` (sum of squared gradients over the data-parallel group) becomes
@@ -537,10 +555,16 @@ class NativeEngine(BaseEngine):
         D, n_sh = self.dense_numel, self.shard_numel
         if W > 1:
             if self.device.type == "cuda":
-                dist.reduce_scatter_tensor(self.grad_shard[:n_sh], mg[:D], op=dist.ReduceOp.AVG, group=self.group)
-            else:  # gloo has no reduce-scatter: all-reduce and keep this rank's slice
+                if self.sh_world > 1:
+                    dist.reduce_scatter_tensor(self.grad_shard[:n_sh], mg[:D], op=dist.ReduceOp.AVG, group=self.sh_group)
+                if self.rep_world > 1:  # mean over the replicas of this shard
+                    dist.all_reduce(self.grad_shard[:n_sh], op=dist.ReduceOp.AVG, group=self.rep_group)
+            else:  # gloo has no reduce-scatter: all-reduce over everyone and keep this rank's slice
                 dist.all_reduce(mg[:D], group=self.group)
-                self.grad_shard[:n_sh].copy_(mg[sl]).div_(W)
+                if self.sh_world > 1:
+                    self.grad_shard[:n_sh].copy_(mg[sl]).div_(W)
+                else:
+                    mg[:D].div_(W)
             if self.local_numel:
                 # rank-local parameters already hold the sum over every rank's tokens; 1/W makes it the same global mean
                 torch.mul(mg[D:], 1.0 / W, out=self.grad_shard[n_sh:])
@@ -550,8 +574,8 @@ class NativeEngine(BaseEngine):
         if self.device.type == "cuda":
             ops = native.ops()
             ops.sumsq_(self.grad_shard, self.ctrl)
-            if W > 1:
-                dist.all_reduce(self.ctrl[:1], group=self.group)
+            if self.sh_world > 1:  # replicas hold identical shards: the norm is a sum over one block
+                dist.all_reduce(self.ctrl[:1], group=self.sh_group)
             self._global_sumsq_correction()
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
             for own, dst in ((slice(0, n_sh), sl), (slice(n_sh, n_sh + self.local_numel), slice(D, D + self.local_numel))):
@@ -562,8 +586,8 @@ class NativeEngine(BaseEngine):
             norm = self.ctrl[3]
         else:
             ss = self.grad_shard.double().pow(2).sum()
-            if W > 1:
-                dist.all_reduce(ss, group=self.group)
+            if self.sh_world > 1:
+                dist.all_reduce(ss, group=self.sh_group)
             self.ctrl[0] = ss.float()
             self._global_sumsq_correction()
             ss = self.ctrl[0].double()
@@ -629,15 +653,15 @@ class NativeEngine(BaseEngine):
 
     def _publish_shard(self) -> None:
         """All-gather this rank's updated slice of the working weights into every replica."""
-        if self.world == 1:
+        if self.sh_world == 1:
             return
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         dense = self.tparams.flat[: self.dense_numel]
         if self.device.type == "cuda":
-            dist.all_gather_into_tensor(dense, dense[sl].clone(), group=self.group)
+            dist.all_gather_into_tensor(dense, dense[sl].clone(), group=self.sh_group)
         else:
-            parts = [dense[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.world)]
-            dist.all_gather(parts, dense[sl].clone(), group=self.group)
+            parts = [dense[i * self.shard_numel : (i + 1) * self.shard_numel] for i in range(self.sh_world)]
+            dist.all_gather(parts, dense[sl].clone(), group=self.sh_group)
 
     def lr_scheduler_step(self) -> float:
         self.sched_step += 1
@@ -664,7 +688,11 @@ class NativeEngine(BaseEngine):
     def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
                         max_ckpt_to_keep: Optional[int] = None, **kwargs) -> None:
         os.makedirs(local_path, exist_ok=True)
-        W, r = self.world, self.rank
+        W, r = self.sh_world, self.sh_rank  # replicas of a block hold identical shards: block 0 writes, everyone reads
+        if self.rep_rank != 0:
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            return
         contents = list(getattr(self.checkpoint_config, "save_contents", ["model", "optimizer", "extra"]) or [])
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         if "model" in contents:
@@ -678,7 +706,7 @@ class NativeEngine(BaseEngine):
             torch.save({"sched_step": self.sched_step, "rng": torch.get_rng_state(),
                         "cuda_rng": torch.cuda.get_rng_state() if self.device.type == "cuda" else None},
                        os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt"))
-        if r == 0:
+        if self.rank == 0:
             with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
                 json.dump({"FSDP_version": 2, "world_size": W, "layout": "verl_b200.flat", "value_head": self.value_head}, f)
             hf_dir = os.path.join(local_path, "huggingface")
@@ -689,14 +717,14 @@ class NativeEngine(BaseEngine):
                 from ....utils.model import save_hf_weights
 
                 save_hf_weights(self.params, hf_dir)
-        if W > 1:
+        if self.world > 1:
             dist.barrier(group=self.group)
 
     def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, del_local_after_load: bool = False,
                         **kwargs) -> None:
         if local_path is None:
             return
-        W, r = self.world, self.rank
+        W, r = self.sh_world, self.sh_rank
         contents = list(getattr(self.checkpoint_config, "load_contents", ["model", "optimizer", "extra"]) or [])
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         mp = os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt")
