@@ -111,6 +111,8 @@ def test_identical_prompts_are_prefilled_once_and_match_unshared_generation():
         outs[share] = eng.generate(prompts, SamplingParams(temperature=1.0, max_tokens=6, seed=None))
         if share:
             assert eng.stats["prefill_tokens_shared"] == 2 * 9 + 3 and eng.stats["prefill_tokens"] == 9 * 3 + 3 * 2 + 2
+        # every block came back exactly once (prompt pages shared by a group are freed by their last user)
+        assert sorted(eng.free_blocks) == list(range(eng.num_blocks)) and not eng._block_users
     for a, b in zip(outs[True], outs[False]):
         assert a.token_ids == b.token_ids and max(abs(x - y) for x, y in zip(a.log_probs, b.log_probs)) < 1e-5
     assert outs[True][0].token_ids != outs[True][1].token_ids  # same prompt, different seeds: different samples

@@ -117,6 +117,7 @@ class RolloutEngine:
             self.model.tp = TensorParallelShard(self.tp_rank, self.tp_size, self._make_row_linear())
         self.kv: Optional[torch.Tensor] = None
         self.free_blocks: list[int] = []
+        self._block_users: dict[int, int] = {}  # prompt pages shared by several sequences -> number of users
         self._graph = None
         self._graph_key = None
         self._seed = seed
@@ -176,13 +177,28 @@ class RolloutEngine:
         self.kv = torch.zeros(c.num_hidden_layers, 2, self.num_blocks, self.bs, c.num_key_value_heads // self.tp_size, c.head_dim,
                               dtype=self.params.flat.dtype, device=self.device)
         self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
+        self._block_users = {}
         self._graph = None  # cache addresses changed
+
+    def _release_blocks(self, blocks: list[int]) -> None:
+        """Give blocks back; a prompt page shared by the samples of a group is free once its last user is done."""
+        shared = self._block_users
+        for b in blocks:
+            n = shared.get(b)
+            if n is None:
+                self.free_blocks.append(b)
+            elif n <= 1:
+                del shared[b]
+                self.free_blocks.append(b)
+            else:
+                shared[b] = n - 1
 
     def release_kv_cache(self) -> None:
         assert not self.running, "cannot release the KV cache with sequences in flight"
         self.kv = None
         self._graph = None
         self.free_blocks = []
+        self._block_users = {}
         if self.is_cuda:
             torch.cuda.empty_cache()
 
@@ -194,6 +210,7 @@ class RolloutEngine:
             self._graph = None
         if self.kv is not None:
             self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
+            self._block_users = {}
 
     def _alloc_state(self) -> None:
         S, dev = self.S, self.device
@@ -292,6 +309,19 @@ class RolloutEngine:
                 first_of[key] = len(leaders)
                 leaders.append(i)
             lead_idx.append(first_of[key])
+        # followers point at the leader's pages for every page the prompt fills completely (those are never written
+        # again); decode CTAs of a group then stream the same addresses at the same time and meet in L2
+        if len(leaders) < len(reqs):
+            for i, r in enumerate(reqs):
+                li = leaders[lead_idx[i]]
+                nfull = lens[i] // self.bs
+                if li == i or nfull == 0:
+                    continue
+                own, shared = r.blocks[:nfull], reqs[li].blocks[:nfull]
+                self.free_blocks.extend(own)
+                r.blocks[:nfull] = shared
+                for b in shared:
+                    self._block_users[b] = self._block_users.get(b, 1) + 1
         bt_rows = torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
         for i, r in enumerate(reqs):
             bt_rows[i, : len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
@@ -318,10 +348,11 @@ class RolloutEngine:
                 li = leaders[lead_idx[i]]
                 if li == i:
                     continue
-                nb = (lens[i] + self.bs - 1) // self.bs
-                src = torch.tensor(reqs[li].blocks[:nb], dtype=torch.int64, device=dev)
-                dst = torch.tensor(r.blocks[:nb], dtype=torch.int64, device=dev)
-                self.kv[:, :, dst] = self.kv[:, :, src]
+                nfull, nb = lens[i] // self.bs, (lens[i] + self.bs - 1) // self.bs
+                if nb > nfull:  # the partially filled last page is private: copy it
+                    src = torch.tensor(reqs[li].blocks[nfull:nb], dtype=torch.int64, device=dev)
+                    dst = torch.tensor(r.blocks[nfull:nb], dtype=torch.int64, device=dev)
+                    self.kv[:, :, dst] = self.kv[:, :, src]
             self.stats["prefill_tokens_shared"] = self.stats.get("prefill_tokens_shared", 0) + sum(lens) - sum(lens[i] for i in leaders)
         slots = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=dev)
         seeds = torch.tensor([(r.params.seed if r.params.seed is not None else self._seed * 1000003 + zlib.crc32(r.rid.encode()))
@@ -470,7 +501,7 @@ class RolloutEngine:
                 reason = "length"
             self.finished.append(RequestOutput(r.rid, r.prompt, t, lps[j, :n].tolist() if r.params.logprobs else None, reason))
             self.stats["generated_tokens"] += n
-            self.free_blocks.extend(r.blocks)
+            self._release_blocks(r.blocks)
             self.free_slots.append(s)
         self.active[idx] = False
         self.ctx[idx] = 0
