@@ -27,6 +27,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--eager", action="store_true", help="no CUDA graph (one launch per kernel, for launch lists)")
     ap.add_argument("--hbm-gbs", type=float, default=6545.6)
+    ap.add_argument("--group", type=int, default=1, help="consecutive sequences that share the pages of their first --shared-ctx tokens")
+    ap.add_argument("--shared-ctx", type=int, default=1024)
     a = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     cfg = get_preset(a.model)
@@ -39,6 +41,10 @@ def main(argv=None):
     eng.kv.normal_(0, 0.5)
     S = a.seqs
     eng.block_table[:, :blocks_per_seq] = torch.arange(S * blocks_per_seq, dtype=torch.int32, device=dev).view(S, blocks_per_seq)
+    if a.group > 1:  # the samples of a prompt point at the same pages for the prompt part of their context
+        shared_pages = min(a.shared_ctx, a.ctx) // bs
+        lead = (torch.arange(S, device=dev) // a.group) * a.group
+        eng.block_table[:, :shared_pages] = eng.block_table[lead, :shared_pages]
     eng.tok.fill_(5)
     eng.pos.fill_(a.ctx)
     eng.ctx.fill_(a.ctx + 1)
@@ -61,7 +67,8 @@ def main(argv=None):
     floor_ms = (weight_bytes + kv_bytes) / (a.hbm_gbs * 1e9) * 1e3
     print(json.dumps({"model": a.model, "seqs": S, "ctx": a.ctx, "graph": not a.eager, "ms_per_step": round(ms, 3),
                       "tokens_per_s": round(S / ms * 1e3, 1), "hbm_floor_ms": round(floor_ms, 3),
-                      "fraction_of_hbm_roofline": round(floor_ms / ms, 3)}))
+                      "fraction_of_hbm_roofline": round(floor_ms / ms, 3),
+                      "group": a.group, "shared_ctx": a.shared_ctx if a.group > 1 else 0}))
 
 
 if __name__ == "__main__":
