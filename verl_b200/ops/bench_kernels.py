@@ -61,6 +61,7 @@ def main(argv=None):
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--group", type=int, default=1, help="paged decode: sequences per group that share their prompt pages")
     a = ap.parse_args(argv)
     only = set(filter(None, a.only.split(",")))
     want = lambda name: not only or name in only
@@ -137,6 +138,15 @@ def main(argv=None):
         q = rnd(B_, nh, hd)
         ms = T(lambda: F.paged_decode_attention(q, kc, vc, bt, cl))
         report("paged_decode_attention", [B_, ctx, nh, nkv, hd], ms, bytes_=2.0 * 2 * nb * bs * nkv * hd)
+        if a.group > 1:
+            # the samples of a prompt share the pages of the first half of their context (one physical copy)
+            shared = (ctx // 2) // bs
+            lead = (torch.arange(B_, device=dev) // a.group) * a.group
+            bt2 = bt.clone()
+            bt2[:, :shared] = bt[lead, :shared]
+            ms = T(lambda: F.paged_decode_attention(q, kc, vc, bt2, cl))
+            uniq = 2.0 * 2 * bs * nkv * hd * ((B_ // a.group) * shared + B_ * (ctx // bs - shared))
+            report(f"paged_decode_attention_shared_prefix_group{a.group}", [B_, ctx, nh, nkv, hd], ms, bytes_=uniq)
     if want("rmsnorm"):
         x, r, w = rnd(tok, H), rnd(tok, H), rnd(H)
         ms = T(lambda: F.rms_norm(x, w, 1e-6, r))
