@@ -75,3 +75,27 @@ def test_length_cut_turn_gets_the_end_marker_and_bad_roles_are_rejected():
     assert r2.token_ids == r1.token_ids + [IM_END, NL] + inc
     with pytest.raises(ValueError):
         b.tokenize_non_assistant_incremental_messages([{"role": "assistant", "content": "x"}])
+
+
+def test_async_rollout_request_tracks_tokens_masks_and_states():
+    from verl_b200.workers.rollout.schemas import AsyncRolloutRequest, AsyncRolloutRequestStateEnum, FinishReasonTypeEnum
+
+    tok = ToyTokenizer()
+    req = AsyncRolloutRequest.create("r1", [{"role": "user", "content": "what is the answer"}], tok, max_response_len=64)
+    n0 = len(req.input_ids)
+    assert req.state == AsyncRolloutRequestStateEnum.PENDING and req.loss_mask == [0] * n0 and req.response_ids == []
+    sampled = tok.encode("call the tool") + [IM_END]
+    req.add_assistant_message("call the tool", sampled, logprobs=[-0.5] * len(sampled), tool_calls=[{"name": "calc"}])
+    assert req.state == AsyncRolloutRequestStateEnum.TOOL_CALLING and req.response_loss_mask == [1] * len(sampled)
+    req.add_tool_response_messages(["the result is 42"])
+    assert req.state == AsyncRolloutRequestStateEnum.RUNNING
+    full = tok.apply_chat_template([{"role": "user", "content": "what is the answer"}, {"role": "assistant", "content": "call the tool"},
+                                    {"role": "tool", "content": "the result is 42"}], add_generation_prompt=True)
+    assert req.input_ids == full and req.get_generation_prompt_ids() == full
+    assert sum(req.response_loss_mask) == len(sampled) and len(req.response_loss_mask) == len(full) - n0
+    final = tok.encode("42") + [IM_END]
+    req.add_assistant_message("42", final)
+    req.max_response_len = len(req.response_ids) - 1          # force a truncation by one token
+    req.finalize({"score": 1.0}, FinishReasonTypeEnum.from_str("stop"))
+    assert req.state == AsyncRolloutRequestStateEnum.COMPLETED and len(req.response_ids) == req.max_response_len
+    assert len(req.input_ids) == len(req.loss_mask) == n0 + req.max_response_len and req.reward_scores == {"score": 1.0}
