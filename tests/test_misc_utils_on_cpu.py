@@ -200,3 +200,29 @@ def test_rm_dataset_pairs(tmp_path):
     assert a["attention_mask"].sum(-1).tolist() == [7, 6] and a["input_ids"][0, 6] == 2 and a["input_ids"][0, 7] == 0
     assert b["attention_mask"][1].sum() == 8          # truncated to max_length
     assert torch.equal(a["input_ids"][0, :2], a["input_ids"][1, :2])   # both rows start with the prompt
+
+
+def test_precision_debugger_writes_per_layer_statistics(tmp_path):
+    import json
+
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    from verl_b200.models import get_preset
+    from verl_b200.utils.profiler.precision_debugger_profile import PrecisionDebuggerProfiler
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+
+    eng = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=1), OptimizerConfig(lr=1e-3))
+    eng.initialize()
+    ids = torch.randint(3, 500, (2, 12))
+    data = {"input_ids": ids, "attention_mask": torch.ones_like(ids), "responses": ids[:, -4:]}
+    dbg = PrecisionDebuggerProfiler({"enable": True, "stages": ["actor_compute_log_prob", "nonsense"], "steps": [3]}, rank=0,
+                                    save_path=str(tmp_path))
+    assert not dbg.start("actor_update", 3, eng.model) and not dbg.start("actor_compute_log_prob", 2, eng.model)
+    started = dbg.start("actor_compute_log_prob", 3, eng.model)
+    eng.infer_batch(dict(data))
+    path = dbg.stop(started)
+    rows = [json.loads(l) for l in open(path)]
+    L = eng.arch.num_hidden_layers
+    assert [r["name"] for r in rows] == [f"layers.{i}.{k}" for i in range(L) for k in ("attn_out", "mlp_out")]
+    assert all(r["nan"] == 0 and r["norm"] > 0 and r["shape"] == [24, eng.arch.hidden_size] for r in rows)
+    assert eng.model.stats_hook is None

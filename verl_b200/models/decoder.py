@@ -203,6 +203,7 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        self.stats_hook: Optional[Callable[[str, torch.Tensor], None]] = None  # called with (name, tensor) per layer output
         self.vocab_parallel = None                          # (group, first vocabulary row) of a vocabulary-parallel LM head
         self.mlp_tile_tokens = 0                            # > 0: sequence-tiled dense MLP (tokens per tile)
         self.router_replay: Optional[RouterReplay] = None   # record / replay the experts every router picks
@@ -759,6 +760,9 @@ class DecoderModel:
         o = self._attn_fwd(W, h1, batch, S, i)
         h2, x2, rstd2 = F.rms_norm(o, W["post_attention_layernorm.weight"], eps, residual=x)
         d = self._mlp_fwd(W, h2, S)
+        if self.stats_hook is not None:  # precision debugging: per-layer tensor statistics
+            self.stats_hook(f"layers.{i}.attn_out", o)
+            self.stats_hook(f"layers.{i}.mlp_out", d)
         if S is not None:
             S.update(x=x, rstd1=rstd1, x2=x2, rstd2=rstd2)
         return d, x2

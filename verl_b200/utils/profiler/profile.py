@@ -69,6 +69,7 @@ class DistProfiler:
         self.tool = self.config.tool if self.config.enable else None
         self.active = False
         self._prof = None
+        self._precision, self._precision_started = None, False
         self._step = 0
 
     def _selected(self) -> bool:
@@ -89,6 +90,14 @@ class DistProfiler:
             self._prof.__enter__()
         elif self.tool == "torch_memory" and get_device_name() == "cuda":
             torch.cuda.memory._record_memory_history(max_entries=int(self.config.tool_config.get("trace_alloc_max_entries", 100000)))
+        elif self.tool == "precision_debugger":
+            from .precision_debugger_profile import PrecisionDebuggerProfiler
+
+            if self._precision is None:
+                self._precision = PrecisionDebuggerProfiler(dict(self.config.tool_config or {}, enable=True), rank=self.rank,
+                                                            save_path=self.config.save_path)
+            self._precision_started = self._precision.start(kwargs.get("stage", "actor_update"), kwargs.get("global_step", self._step),
+                                                            kwargs.get("model"))
 
     def stop(self) -> None:
         if not self.active:
@@ -101,6 +110,8 @@ class DistProfiler:
             self._prof.__exit__(None, None, None)
             self._prof.export_chrome_trace(os.path.join(self.config.save_path, f"trace_rank{self.rank}_step{self._step}.json"))
             self._prof = None
+        elif self.tool == "precision_debugger" and self._precision is not None:
+            self._precision.stop(self._precision_started)
         elif self.tool == "torch_memory" and get_device_name() == "cuda":
             torch.cuda.memory._dump_snapshot(os.path.join(self.config.save_path, f"memory_rank{self.rank}_step{self._step}.pickle"))
             torch.cuda.memory._record_memory_history(enabled=None)
