@@ -381,3 +381,54 @@ def test_nvfp4_fake_quant_matches_reference():
     z = x.clone()
     nvfp4_fake_quantize(z, gs, out=z)            # in place
     assert torch.equal(z, y)
+
+
+def test_fp8_grouped_expert_gemm_and_moe_layer(ops):
+    """Grouped block-scaled fp8 GEMM against the same op on the host (dequantised fp32 product per 128-row tile), and the
+    mixture-of-experts layer with fp8 expert copies against its bf16 result."""
+    from verl_b200.models import DecoderModel, FlatParams
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    E, N, K = 6, 384, 256
+    counts = [130, 0, 128, 5, 250, 77]
+    segs = [(c + 127) // 128 * 128 for c in counts]
+    cap = sum(segs) + 256                                   # two unused tiles at the end
+    x = torch.zeros(cap, K, device=DEV, dtype=torch.bfloat16)
+    tile_expert, row = [], 0
+    for e, (c, s_) in enumerate(zip(counts, segs)):
+        x[row : row + c] = torch.randn(c, K, device=DEV).bfloat16()
+        tile_expert += [e] * (s_ // 128)
+        row += s_
+    n_tiles = len(tile_expert)
+    tile_expert += [E - 1] * (cap // 128 - n_tiles)
+    te = torch.tensor(tile_expert, dtype=torch.int32, device=DEV)
+    nt = torch.tensor([n_tiles], dtype=torch.int32, device=DEV)
+    w = (torch.randn(E, N, K, device=DEV) * 0.05).bfloat16()
+    wq, ws = F.fp8_quantize_1x128(w.reshape(E * N, K))
+    y = F.linear_fp8_grouped(x, wq, ws, N, te, nt)
+    # reference from the SAME quantised operands (host and device quantisers differ on rounding ties)
+    xq, xs = F.fp8_quantize_1x128(x)
+    xd = F.fp8_dequantize_1x128(xq.cpu(), xs.cpu())
+    wd = F.fp8_dequantize_1x128(wq.cpu(), ws.cpu()).view(E, N, K)
+    ref = torch.zeros(cap, N)
+    for t in range(n_tiles):
+        ref[t * 128 : (t + 1) * 128] = xd[t * 128 : (t + 1) * 128] @ wd[tile_expert[t]].t()
+    assert ops.gemm_status() == 0
+    assert rel(y, ref) < 1e-2
+    assert rel(y, F.linear_fp8_grouped(x.cpu(), wq.cpu(), ws.cpu(), N, te.cpu(), nt.cpu()).float()) < 0.04  # host formulation of the op
+    assert float(y[row:].abs().max()) == 0.0               # tiles beyond num_mtiles are not computed
+    # layer level
+    cfg = ModelConfig(model_type="qwen3_moe", vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=1,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=16, num_experts_per_tok=4,
+                      moe_intermediate_size=128, eos_token_id=2, pad_token_id=0)
+    P = FlatParams(cfg, dtype=torch.bfloat16, device=DEV)
+    P.init_weights(seed=4, std=0.05)
+    model = DecoderModel(cfg, P)
+    h2 = torch.randn(300, 256, device=DEV).bfloat16()
+    ref_out = model._moe_fwd(P.layer(0), h2, None)
+    assert model.quantize_linear_weights_fp8() > 0
+    q_out = model._moe_fwd(P.layer(0), h2, None)
+    assert ops.gemm_status() == 0
+    assert 0 < rel(q_out, ref_out.float()) < 0.08           # fp8 operands: close to, not identical with, the bf16 layer

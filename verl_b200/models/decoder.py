@@ -409,6 +409,11 @@ class DecoderModel:
                     q, sc = F.fp8_quantize_1x128(W[n])
                     self.fp8_weights[W[n].data_ptr()] = (q, sc)
                     total += q.numel() + sc.numel() * 4
+            for n in ("mlp.experts.gate_up_proj", "mlp.experts.down_proj"):  # stacked expert matrices [E, N, K] -> [E * N, K]
+                if n in W and W[n].shape[-1] % 128 == 0:
+                    q, sc = F.fp8_quantize_1x128(W[n].reshape(-1, W[n].shape[-1]))
+                    self.fp8_weights[W[n].data_ptr()] = (q, sc)
+                    total += q.numel() + sc.numel() * 4
         return total
 
     def _grad_of(self, w: torch.Tensor) -> torch.Tensor:
@@ -532,8 +537,15 @@ class DecoderModel:
         w = w.float().contiguous()
         plan = self._moe_plan(idx, counts, T, k, E)
         xp = ops.moe_gather_rows(h2, plan["src"], None)
-        gu = ops.gemm_grouped_rows(xp, W["mlp.experts.gate_up_proj"], False, plan["tile_expert"], plan["num_mtiles"])
-        y = ops.gemm_grouped_rows(F.swiglu(gu), W["mlp.experts.down_proj"], False, plan["tile_expert"], plan["num_mtiles"])
+        Wgu, Wd = W["mlp.experts.gate_up_proj"], W["mlp.experts.down_proj"]
+        q_gu = self.fp8_weights.get(Wgu.data_ptr()) if (S is None and self.fp8_weights is not None) else None
+        q_d = self.fp8_weights.get(Wd.data_ptr()) if (S is None and self.fp8_weights is not None) else None
+        if q_gu is not None and q_d is not None:  # forward-only with fp8 expert copies installed (rollout precision)
+            gu = F.linear_fp8_grouped(xp, q_gu[0], q_gu[1], Wgu.shape[1], plan["tile_expert"], plan["num_mtiles"])
+            y = F.linear_fp8_grouped(F.swiglu(gu), q_d[0], q_d[1], Wd.shape[1], plan["tile_expert"], plan["num_mtiles"])
+        else:
+            gu = ops.gemm_grouped_rows(xp, Wgu, False, plan["tile_expert"], plan["num_mtiles"])
+            y = ops.gemm_grouped_rows(F.swiglu(gu), Wd, False, plan["tile_expert"], plan["num_mtiles"])
         out = ops.moe_combine(y, plan["slot"], w)
         if S is not None:
             S.update(moe=dict(native=True, logits=logits, w=w, idx=idx, plan=plan, gu=gu, y=y))

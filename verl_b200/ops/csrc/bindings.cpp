@@ -545,6 +545,30 @@ Tensor gemm_fp8_blockscale(const Tensor& aq, const Tensor& sa, const Tensor& bq,
   return d;
 }
 
+// Grouped block-scaled fp8 GEMM of a mixture-of-experts layer: aq [rows_cap, K] (rows grouped by expert, 128-row aligned),
+// bq [E * N, K]; scales [K/128, rows_cap] and [K/128, E * N]. Rows of tiles beyond num_mtiles are left as allocated (zeroed).
+Tensor gemm_fp8_blockscale_grouped(const Tensor& aq, const Tensor& sa, const Tensor& bq, const Tensor& sb, int64_t N,
+                                   const Tensor& tile_expert, const Tensor& num_mtiles) {
+  TORCH_CHECK(aq.scalar_type() == at::kByte && bq.scalar_type() == at::kByte && aq.is_cuda() && bq.is_cuda());
+  TORCH_CHECK(aq.dim() == 2 && bq.dim() == 2 && aq.stride(1) == 1 && bq.stride(1) == 1 && aq.size(1) == bq.size(1));
+  CHECK_F32(sa);
+  CHECK_F32(sb);
+  const int64_t rows = aq.size(0), K = aq.size(1), EN = bq.size(0);
+  TORCH_CHECK(N > 0 && EN % N == 0 && rows % 128 == 0, "gemm_fp8_blockscale_grouped: bq must hold E stacked [N, K] matrices");
+  TORCH_CHECK(sa.is_contiguous() && sb.is_contiguous() && sa.size(0) == K / 128 && sa.size(1) == rows && sb.size(0) == K / 128 &&
+              sb.size(1) == EN, "gemm_fp8_blockscale_grouped: scales must be [K/128, rows] and [K/128, E*N]");
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.is_cuda() && tile_expert.numel() >= rows / 128 &&
+              num_mtiles.scalar_type() == at::kInt && num_mtiles.is_cuda());
+  const c10::cuda::CUDAGuard guard(aq.device());
+  Tensor d = at::zeros({rows, N}, aq.options().dtype(at::kBFloat16));
+  count(1);
+  CHECK_RC(vb_gemm_fp8_blockscale_grouped(aq.data_ptr(), sa.data_ptr<float>(), bq.data_ptr(), sb.data_ptr<float>(), d.data_ptr(), (int)rows,
+                                          (int)N, (int)K, (int)(EN / N), aq.stride(0), bq.stride(0), d.stride(0),
+                                          tile_expert.data_ptr<int>(), num_mtiles.data_ptr<int>(), cur_stream()),
+           "vb_gemm_fp8_blockscale_grouped");
+  return d;
+}
+
 // ---- mixture of experts
 // (weights [T,k] fp32, experts [T,k] int32, counts [E] int32) from router logits [T, E]
 std::tuple<Tensor, Tensor, Tensor> moe_route_topk(const Tensor& logits, int64_t k, bool renorm) {
@@ -695,6 +719,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
+  m.def("gemm_fp8_blockscale_grouped", &gemm_fp8_blockscale_grouped);
   m.def("nvfp4_fake_quant_", &nvfp4_fake_quant_);
   m.def("gemm_fp8_blockscale", &gemm_fp8_blockscale);
   m.def("moe_route_topk", &moe_route_topk);

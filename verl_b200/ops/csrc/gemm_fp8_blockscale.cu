@@ -28,6 +28,11 @@ struct Fp8GemmParams {
   long long ldd;
   const __nv_bfloat16* bias;
   int* status;
+  // grouped (mixture-of-experts) mode: A rows are grouped by expert in 128-row aligned segments, B holds E stacked [N, K]
+  // matrices and sb E stacked column-scale rows; the 128-row tile i belongs to expert grp_tile_expert[i]
+  const int* grp_tile_expert;  // nullptr = plain GEMM
+  const int* grp_num_mtiles;   // device scalar: tiles in use (tiles beyond it return at once)
+  long long ldsb;              // row stride of sb (N, or E * N when grouped)
 };
 
 struct Fp8Smem {
@@ -56,6 +61,11 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * F8_BN, m0 = blockIdx.y * F8_BM;
   const int num_kb = p.K / F8_BK;
+  int b_row0 = n0;  // first row of the B operand (and column of sb) of this tile
+  if (p.grp_tile_expert != nullptr) {
+    if (static_cast<int>(blockIdx.y) >= *p.grp_num_mtiles) return;  // uniform over the CTA; nothing allocated yet
+    b_row0 = p.grp_tile_expert[blockIdx.y] * p.N + n0;
+  }
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
@@ -89,7 +99,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         }
         mbar_expect_tx(&full_bar[st], 2 * Fp8Smem::TILE);
         tma_load_2d(smem_a + st * Fp8Smem::TILE, &tma_a, &full_bar[st], kb * F8_BK, m0);
-        tma_load_2d(smem_b + st * Fp8Smem::TILE, &tma_b, &full_bar[st], kb * F8_BK, n0);
+        tma_load_2d(smem_b + st * Fp8Smem::TILE, &tma_b, &full_bar[st], kb * F8_BK, b_row0);
       }
     }
   } else if (warp == 1) {
@@ -132,7 +142,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
 #pragma unroll
       for (int u = 0; u < F8_BN / 32; ++u) {
         const int n = n0 + lane + 32 * u;
-        csb[lane + 32 * u] = n < p.N ? p.sb[static_cast<long long>(kb) * p.N + n] : 0.f;
+        csb[lane + 32 * u] = n < p.N ? p.sb[static_cast<long long>(kb) * p.ldsb + (b_row0 - n0) + n] : 0.f;
       }
       const float ra = row_ok ? p.sa[static_cast<long long>(kb) * p.M + row] : 0.f;
       __syncwarp();
@@ -235,6 +245,7 @@ extern "C" int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const voi
   Fp8GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.sa = sa; p.sb = sb; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias); p.status = status;
+  p.ldsb = N;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fp8Smem::TOTAL);
@@ -242,6 +253,35 @@ extern "C" int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const voi
     configured = true;
   }
   dim3 grid((N + F8_BN - 1) / F8_BN, (M + F8_BM - 1) / F8_BM);
+  gemm_fp8_blockscale_kernel<<<grid, F8_THREADS, Fp8Smem::TOTAL, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped variant for mixture-of-experts layers: D[rows, N] = A[rows, K] * B_e^T for the expert e of each 128-row tile.
+//  Aq [rows_cap, K] e4m3 with scales sa [K/128, rows_cap]; Bq [E * N, K] e4m3 with scales sb [K/128, E * N];
+//  tile_expert[i] = expert of tile i, num_mtiles (device scalar) = tiles in use. Rows of unused tiles are not written.
+extern "C" int vb_gemm_fp8_blockscale_grouped(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, int rows_cap,
+                                              int N, int K, int E, long long lda, long long ldb, long long ldd, const int* tile_expert,
+                                              const int* num_mtiles, cudaStream_t stream) {
+  if (rows_cap <= 0 || N <= 0 || K <= 0 || E <= 0) return 0;
+  if ((K % 128) || (N % 8) || (rows_cap % F8_BM) || (lda % 16) || (ldb % 16) || (ldd % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, Aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows_cap, K, lda, F8_BK, F8_BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!make_tmap_2d(&tb, Bq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(E) * N, K, ldb, F8_BK, F8_BN, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  static int* status = nullptr;
+  if (status == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_fp8_status);
+  Fp8GemmParams p{};
+  p.M = rows_cap; p.N = N; p.K = K; p.sa = sa; p.sb = sb; p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.bias = nullptr; p.status = status;
+  p.grp_tile_expert = tile_expert; p.grp_num_mtiles = num_mtiles; p.ldsb = static_cast<long long>(E) * N;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fp8Smem::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid((N + F8_BN - 1) / F8_BN, rows_cap / F8_BM);
   gemm_fp8_blockscale_kernel<<<grid, F8_THREADS, Fp8Smem::TOTAL, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }

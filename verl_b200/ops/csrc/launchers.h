@@ -85,6 +85,9 @@ int vb_nvfp4_fake_quant(const void* x, long long ldx, void* y, long long ldy, lo
 int vb_fp8_quant_1x128(const void* x, long long ldx, void* q, long long ldq, float* scales, int R, int C, cudaStream_t s);
 int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, const void* bias, int M, int N,
                            int K, long long lda, long long ldb, long long ldd, cudaStream_t stream);
+int vb_gemm_fp8_blockscale_grouped(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, int rows_cap, int N, int K,
+                                   int E, long long lda, long long ldb, long long ldd, const int* tile_expert, const int* num_mtiles,
+                                   cudaStream_t s);
 int vb_fp8_status();
 // moe_kernels.cu
 int vb_moe_route_topk(const void* logits, long long ld, int T, int E, int k, int renorm, float* weights, int* experts, int* counts,

@@ -486,6 +486,23 @@ def fp8_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return (q.view(torch.float8_e4m3fn).float().view(R, C // 128, 128) * scales.t().unsqueeze(-1)).view(R, C)
 
 
+def linear_fp8_grouped(x_rows: torch.Tensor, wq: torch.Tensor, w_scales: torch.Tensor, n_out: int, tile_expert: torch.Tensor,
+                       num_mtiles: torch.Tensor) -> torch.Tensor:
+    """Grouped expert linear in block-scaled fp8: ``x_rows`` [rows, K] (rows grouped by expert in 128-row aligned segments,
+    padding rows zero), ``wq`` [E * n_out, K] e4m3 with scales [K/128, E * n_out]; the expert of every 128-row tile comes
+    from ``tile_expert``. Activations are quantised per row and 128-wide K block on the fly."""
+    if x_rows.is_cuda:
+        xq, xs = _ops().fp8_quant_1x128(x_rows.contiguous())
+        return _ops().gemm_fp8_blockscale_grouped(xq, xs, wq, w_scales, int(n_out), tile_expert, num_mtiles)
+    xq, xs = fp8_quantize_1x128(x_rows)
+    xd = fp8_dequantize_1x128(xq, xs)
+    wd = fp8_dequantize_1x128(wq, w_scales).view(-1, n_out, x_rows.shape[1])
+    out = torch.zeros(x_rows.shape[0], n_out, dtype=torch.float32)
+    for t in range(int(num_mtiles.reshape(-1)[0])):
+        out[t * 128 : (t + 1) * 128] = xd[t * 128 : (t + 1) * 128] @ wd[int(tile_expert[t])].t()
+    return out.to(x_rows.dtype)
+
+
 def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scales: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ dequant(wq)^T`` with on-the-fly 1x128 quantisation of the activation and a block-scaled e4m3 tensor-core
     GEMM (fp32 accumulation per 128-wide K block)."""
