@@ -432,3 +432,26 @@ def test_fp8_grouped_expert_gemm_and_moe_layer(ops):
     q_out = model._moe_fwd(P.layer(0), h2, None)
     assert ops.gemm_status() == 0
     assert 0 < rel(q_out, ref_out.float()) < 0.08           # fp8 operands: close to, not identical with, the bf16 layer
+
+
+def test_rollout_engine_moe_cuda_graph_and_fp8_experts(ops):
+    """Mixture-of-experts decoding under the CUDA graph equals eager decoding; with fp8 weight copies (dense projections and
+    experts) generation runs and the sampled-token log-probs stay close to the bf16 engine's."""
+    from verl_b200.models import FlatParams, ModelConfig
+    from verl_b200.workers.rollout.native.engine import RolloutEngine, SamplingParams
+
+    cfg = ModelConfig(model_type="qwen3_moe", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, num_experts=16, num_experts_per_tok=4,
+                      moe_intermediate_size=256, qk_norm=True, eos_token_id=-1, pad_token_id=0)
+    P = FlatParams(cfg, dtype=torch.bfloat16, device=DEV)
+    P.init_weights(seed=0, std=0.05)
+    prompts = [[5, 6, 7, 8, 9], [10, 11, 12], [20, 21, 22, 23, 24, 25, 26], [3, 4]]
+    outs = {}
+    for key, graph, quant in (("graph", True, None), ("eager", False, None), ("fp8", True, "fp8")):
+        eng = RolloutEngine(cfg, P, max_num_seqs=4, max_model_len=64, block_size=16, num_blocks=32, sync_interval=3,
+                            use_cuda_graph=graph, eos_token_id=-1, quantization=quant)
+        outs[key] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, logprobs=True))
+    assert [o.token_ids for o in outs["graph"]] == [o.token_ids for o in outs["eager"]]
+    assert all(len(o.token_ids) == 8 for o in outs["fp8"]) and ops.gemm_status() == 0
+    # first generated token comes from the prefill (bf16 in both engines): identical; later ones may differ under fp8
+    assert [o.token_ids[0] for o in outs["fp8"]] == [o.token_ids[0] for o in outs["graph"]]
