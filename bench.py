@@ -55,6 +55,8 @@ def parse_args():
     p.add_argument("--train-pp", type=int, default=1, help="pipeline-parallel size of the training engine")
     p.add_argument("--train-ep", type=int, default=1, help="expert-parallel size of the training engine (mixture-of-experts models; "
                                                            "must equal the data-parallel size)")
+    p.add_argument("--layers", type=int, default=0, help="development only: override the number of decoder layers (the result is "
+                                                         "marked as a reduced model and is not a measurement of the named config)")
     p.add_argument("--no-prefix-sharing", action="store_true",
                    help="pack every sample's prompt separately in the log-prob / training passes and prefill it separately "
                         "(default: the n samples of a prompt share its tokens; results are identical)")
@@ -147,6 +149,8 @@ def build_config(args, world: int):
         "trainer.resume_mode=disable", "trainer.save_freq=-1", "trainer.test_freq=-1", "trainer.logger=[]",
         "trainer.worker_group=spmd", "trainer.device=cuda",
     ]
+    if args.layers > 0:
+        ov += [f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}"]
     mp = args.train_tp * args.train_pp
     if mp * args.train_ep > 1:
         ov += ["actor@actor_rollout_ref.actor=megatron_actor",
@@ -275,6 +279,7 @@ def main():
                              f"{' x ep' + str(args.train_ep) + ' (experts sharded over dp)' if args.train_ep > 1 else ''} + rollout tp{rollout_tp} "
                              f"on weights gathered from the shards each step"),
                        "algorithm": "ppo+critic+gae" if args.critic else "grpo",
+                       **({"reduced_model_layers": args.layers} if args.layers > 0 else {}),
                        "shared_prompt_packing": not args.no_prefix_sharing,
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
                        "mean_response_len": last_metrics.get("response_length/mean")},
