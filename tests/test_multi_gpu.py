@@ -58,7 +58,7 @@ def _worker_body(rank, world, port, queue):
 
     fused = FusedRowParallelLinear(max_rows=3000, n=1024, device=dev)
     errs, same = [], []
-    for call, M in enumerate((640, 3000, 77)):
+    for call, M in enumerate((640, 3000, 77, 320, 320)):  # 77 / 320 rows with K = 512: tile path; see the K-split case below
         g = torch.Generator(device="cpu").manual_seed(50 + call)
         a_full = torch.randn(M, 1024, generator=g).bfloat16()
         b_full = (torch.randn(1024, 1024, generator=g) * 0.05).bfloat16()
@@ -71,6 +71,21 @@ def _worker_body(rank, world, port, queue):
         other = y.clone()
         dist.broadcast(other, src=0)
         same.append(bool(torch.equal(other, y)))
+    # decode-sized call with a deep K: K-split GEMM + fused reduce / all-reduce kernel (twice: both buffer halves)
+    fused_d = FusedRowParallelLinear(max_rows=320, n=1024, device=dev)
+    for call in range(3):
+        g = torch.Generator(device="cpu").manual_seed(70 + call)
+        a_full = torch.randn(320, 8192, generator=g).bfloat16()
+        b_full = (torch.randn(1024, 8192, generator=g) * 0.02).bfloat16()
+        bias = torch.randn(1024, generator=g).bfloat16()
+        ks = slice(rank * 4096, (rank + 1) * 4096)
+        y = fused_d(a_full[:, ks].contiguous().to(dev), b_full.to(dev)[:, ks], bias.to(dev))
+        ref = a_full.float() @ b_full.float().t() + bias.float()
+        errs.append(((y.float().cpu() - ref).norm() / ref.norm()).item())
+        other = y.clone()
+        dist.broadcast(other, src=0)
+        same.append(bool(torch.equal(other, y)))
+    res["gemm_ar_splitk_used"] = int(native.ops().gemm_suggest_splits(320, 1024, 4096)) if hasattr(native.ops(), "gemm_suggest_splits") else -1
     res["gemm_ar_err"] = max(errs)
     res["gemm_ar_identical"] = all(same)
     res["gemm_status"] = int(ops.gemm_status())
@@ -181,6 +196,7 @@ def test_two_rank_fused_optimizer_and_peer_collectives():
         assert res["allreduce_err"] == 0.0
         assert res["ep_err"] < 2e-2 and res["ep_repeat_equal"] and res["ep_dropped"] == 0 and res["ep_status"] == 0, res
         assert res["gemm_ar_err"] < 1e-2 and res["gemm_ar_identical"] and res["gemm_status"] == 0, res
+        assert res["gemm_ar_splitk_used"] > 1, res   # the decode-sized case went through the K-split path
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
         assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res

@@ -87,11 +87,13 @@ def main(argv=None):
     H, I, V = 3584, 18944, 152064
     rnd = lambda *s: (torch.randn(*s, device=dev) * 0.05).bfloat16()
 
-    if want("gemm"):
+    if want("gemm") or want("gemm_decode"):
         for name, (M, N, K, amn, bmn) in {"gemm_fwd_gate_up": (tok, 2 * I if not a.small else 8192, H, False, False),
                                           "gemm_dgrad_down": (tok, I if not a.small else 8192, H, False, True),
                                           "gemm_wgrad_qkv": (4608, H, tok, True, True),
                                           "gemm_decode_skinny": (320, 4608, H, False, False)}.items():
+            if not want("gemm") and name != "gemm_decode_skinny":
+                continue
             A = rnd(K, M) if amn else rnd(M, K)
             B = rnd(K, N) if bmn else rnd(N, K)
             out = torch.empty(M, N, device=dev, dtype=torch.float32 if amn else torch.bfloat16)

@@ -468,7 +468,8 @@ void allreduce_peer_(const Tensor& buf_ptrs, Tensor out, int64_t rank) {
 // Row-parallel linear + all-reduce in one kernel: out[M,N] = sum over ranks of a_r[M,K_r] @ b_r[N,K_r]^T (+bias).
 // part_ptrs / flag_ptrs: CPU int64 tensors [world] with every rank's partial buffer and flag array addresses.
 Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, const Tensor& part_ptrs, const Tensor& flag_ptrs,
-                      Tensor epoch, int64_t buf_elems, int64_t rank, double limit_s, const OptTensor& out) {
+                      Tensor epoch, int64_t buf_elems, int64_t rank, double limit_s, const OptTensor& out,
+                      const OptTensor& splitk_ws) {
   CHECK_BF16(a);
   CHECK_BF16(b);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1),
@@ -484,6 +485,19 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
     bias_ptr = bias->data_ptr();
   }
   if (M == 0) return d;
+  // decode-sized calls (few output tiles, deep K): K-split GEMM over all SMs + one fused reduce / all-reduce kernel
+  const int splits = splitk_ws.has_value() ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
+  if (splits > 1 && splitk_ws->numel() >= splits * M * N) {
+    CHECK_F32((*splitk_ws));
+    count(2);
+    const int rc2 = vb_gemm_bf16_splitk_allreduce(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
+                                                  b.stride(0), d.stride(0), uptr(part_ptrs), uptr(flag_ptrs),
+                                                  reinterpret_cast<unsigned int*>(epoch.data_ptr<int>()), buf_elems,
+                                                  (int)part_ptrs.numel(), (int)rank, limit_s, splits, splitk_ws->data_ptr<float>(),
+                                                  cur_stream());
+    TORCH_CHECK(rc2 == 0, "vb_gemm_bf16_splitk_allreduce failed with code ", rc2, " (M=", M, " N=", N, " K=", K, ")");
+    return d;
+  }
   count(1);
   const int rc = vb_gemm_bf16_allreduce(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
                                         b.stride(0), d.stride(0), uptr(part_ptrs), uptr(flag_ptrs),
@@ -717,6 +731,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("adamw_allgather_", &adamw_allgather_);
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
+  m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
   m.def("gemm_fp8_blockscale_grouped", &gemm_fp8_blockscale_grouped);

@@ -619,6 +619,112 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __nv_bf
     *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(D) + static_cast<long long>(row) * ldd + col) = v;
   }
 }
+
+// Split-K reduction fused with the tensor-parallel all-reduce (decode-sized row-parallel linears: few output tiles, deep
+// K). Every CTA owns 2048 consecutive output elements: it folds this rank's K-split partial sums, publishes the bf16
+// result in the rank's peer-visible buffer, raises the chunk's flag, waits (bounded) for the same chunk of every peer and
+// sums all ranks' chunks in rank order, so every rank obtains identical bits.
+struct SplitKAllReduceParams {
+  const float* ws;   // [splits][M*N] fp32 partial sums of this rank
+  int splits;
+  long long total;   // M * N
+  int N;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* D;
+  long long ldd;
+  unsigned long long part[AR_MAX_RANKS];
+  unsigned long long flag[AR_MAX_RANKS];
+  long long buf_elems;
+  unsigned int* epoch;
+  unsigned long long limit_ns;
+  int world, rank;
+  int* status;
+};
+
+constexpr int SKAR_THREADS = 256;
+
+__global__ void __launch_bounds__(SKAR_THREADS)
+splitk_reduce_allreduce_kernel(const SplitKAllReduceParams p) {
+  __shared__ int s_ok;
+  const unsigned int epoch_now = *reinterpret_cast<volatile unsigned int*>(p.epoch) + 1u;
+  const long long half = static_cast<long long>(epoch_now & 1u) * p.buf_elems;
+  const long long e = (blockIdx.x * static_cast<long long>(SKAR_THREADS) + threadIdx.x) * 8;
+  const bool live = e < p.total;
+  if (live) {
+    float a[8];
+    const float4* w0 = reinterpret_cast<const float4*>(p.ws + e);
+    float4 x = w0[0], y = w0[1];
+    a[0] = x.x; a[1] = x.y; a[2] = x.z; a[3] = x.w; a[4] = y.x; a[5] = y.y; a[6] = y.z; a[7] = y.w;
+    for (int s = 1; s < p.splits; ++s) {
+      const float4* w = reinterpret_cast<const float4*>(p.ws + static_cast<long long>(s) * p.total + e);
+      x = w[0]; y = w[1];
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w; a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+    uint4 v;
+    v.x = pack_bf16x2(a[0], a[1]); v.y = pack_bf16x2(a[2], a[3]); v.z = pack_bf16x2(a[4], a[5]); v.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.part[p.rank]) + half + e) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    st_release_sys_u32(reinterpret_cast<unsigned int*>(p.flag[p.rank]) + blockIdx.x, epoch_now);
+    int ok = 1;
+    const unsigned long long t0 = ar_now_ns();
+    for (int r = 0; r < p.world && ok; ++r) {
+      if (r == p.rank) continue;
+      const unsigned int* f = reinterpret_cast<const unsigned int*>(p.flag[r]) + blockIdx.x;
+      while (static_cast<int>(ld_acquire_sys_u32(f) - epoch_now) < 0) {
+        if (ar_now_ns() - t0 > p.limit_ns) {  // the peer never arrived
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    if (!ok) atomicExch(p.status, ST_TIMEOUT_EPILOGUE + 10);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok && live) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 v[AR_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < AR_MAX_RANKS; ++r) {  // all peers' loads in flight before the first is consumed
+      if (r < p.world) v[r] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.part[r]) + half + e));
+    }
+#pragma unroll
+    for (int r = 0; r < AR_MAX_RANKS; ++r) {
+      if (r < p.world) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f2 = __bfloat1622float2(h[j]);
+          acc[2 * j] += f2.x;
+          acc[2 * j + 1] += f2.y;
+        }
+      }
+    }
+    const long long row = e / p.N;
+    const int col = static_cast<int>(e % p.N);
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(p.bias[col + j]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(p.D + row * p.ldd + col) = o;
+  }
+  // the last CTA to finish closes the call: every CTA of this launch has read the epoch by now
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int done = atomicAdd(p.epoch + 1, 1u);
+    if (done == gridDim.x - 1) {
+      p.epoch[1] = 0;
+      __threadfence();
+      atomicAdd(p.epoch, 1u);
+    }
+  }
+}
 }  // namespace vb
 
 // Suggested number of K splits for a skinny GEMM (few output tiles, deep K); 1 = no split.
@@ -646,6 +752,8 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
 }
 
 // k_splits > 1 needs splitk_ws of k_splits * M * N floats.
+static bool g_partials_only = false;  // set by the all-reduce launcher: leave the K-split partial sums in the workspace
+
 extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                                long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
                                int accumulate, int max_ctas, int k_splits, float* splitk_ws, cudaStream_t stream) {
@@ -689,7 +797,7 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
     else VB_LAUNCH(128, true, false, 6);
   }
 #undef VB_LAUNCH
-  if (e == cudaSuccess && p.k_splits > 1) {
+  if (e == cudaSuccess && p.k_splits > 1 && !g_partials_only) {
     const long long total4 = static_cast<long long>(M) * N / 4;
     splitk_reduce_kernel<<<static_cast<int>((total4 + 255) / 256), 256, 0, stream>>>(
         splitk_ws, reinterpret_cast<const __nv_bfloat16*>(bias), D, ldd, M, N, p.k_splits, out_f32, accumulate);
@@ -736,6 +844,36 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
   if (wide) e = launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   else e = launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   return static_cast<int>(e);
+}
+
+// Decode-sized variant of the row-parallel linear: the GEMM runs K-split over all SMs into ``splitk_ws``
+// (k_splits * M * N floats), then one kernel folds the splits and performs the all-reduce over peer memory.
+// flag_ptrs need ceil(M * N / 2048) entries; part_ptrs / epoch / limit_s as for vb_gemm_bf16_allreduce.
+extern "C" int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                             long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
+                                             const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
+                                             int world, int rank, double limit_s, int k_splits, float* splitk_ws,
+                                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (ldd % 8) || k_splits < 2 || splitk_ws == nullptr) return -1;
+  if (world < 1 || world > AR_MAX_RANKS || rank < 0 || rank >= world) return -4;
+  if (static_cast<long long>(M) * N > buf_elems) return -5;
+  g_partials_only = true;
+  const int rc = vb_gemm_bf16_ex(A, B, splitk_ws, nullptr, M, N, K, lda, ldb, N, 0, 0, 1, 0, 0, k_splits, splitk_ws, stream);
+  g_partials_only = false;
+  if (rc != 0) return rc;
+  SplitKAllReduceParams p{};
+  p.ws = splitk_ws; p.splits = k_splits; p.total = static_cast<long long>(M) * N; p.N = N;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias); p.D = reinterpret_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.buf_elems = buf_elems; p.epoch = epoch; p.world = world; p.rank = rank; p.status = status_ptr();
+  p.limit_ns = static_cast<unsigned long long>((limit_s > 0.0 ? limit_s : 2.0) * 1e9);
+  for (int r = 0; r < world; ++r) {
+    p.part[r] = part_ptrs[r];
+    p.flag[r] = flag_ptrs[r];
+  }
+  const long long chunks = (p.total / 8 + SKAR_THREADS - 1) / SKAR_THREADS;
+  splitk_reduce_allreduce_kernel<<<static_cast<unsigned int>(chunks), SKAR_THREADS, 0, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // Grouped GEMMs of a mixture-of-experts layer; every expert's rows start at a multiple of 128 (zero-padded).

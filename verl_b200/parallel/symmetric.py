@@ -76,8 +76,9 @@ class PeerBarrier:
 class FusedRowParallelLinear:
     """Row-parallel (K-sharded) linear whose all-reduce runs inside the GEMM epilogue over peer memory.
 
-    Owns the peer-visible partial buffer (two halves, alternating per call), the per-tile flags and the call counter of
-    one tensor-parallel group. Every rank of the group must issue the same sequence of calls; the result is bitwise
+    Owns the peer-visible partial buffer (two halves, alternating per call), the flags and the call counter of one
+    tensor-parallel group. Large calls (prefill) reduce inside the GEMM epilogue tile by tile; decode-sized calls (few
+    output tiles, deep K) run the GEMM K-split over all SMs and fold the splits in the kernel that performs the all-reduce. Every rank of the group must issue the same sequence of calls; the result is bitwise
     identical on all ranks. ``max_rows`` bounds ``M`` of a call (rows of the activation)."""
 
     def __init__(self, max_rows: int, n: int, device, group=None, limit_s: float = 20.0):
@@ -89,7 +90,10 @@ class FusedRowParallelLinear:
         self.buf_elems = self.max_rows * self.n
         self.part = SymmetricBuffer.allocate(2 * self.buf_elems, torch.bfloat16, device, group, zero=False)
         tiles = ((self.max_rows + 127) // 128) * ((self.n + 127) // 128)
-        self.flags = SymmetricBuffer.allocate(4 * tiles, torch.int32, device, group, zero=True)
+        chunks = (self.buf_elems + 2047) // 2048  # flags of the decode-sized path (one per 2048 output elements)
+        self.flags = SymmetricBuffer.allocate(max(4 * tiles, chunks), torch.int32, device, group, zero=True)
+        # decode-sized calls run the GEMM K-split over all SMs and fold the splits inside the all-reduce kernel
+        self.splitk_ws = torch.empty(8 * self.buf_elems, dtype=torch.float32, device=device) if self.max_rows <= 1024 else None
         self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group)  # flags are zero everywhere before anyone publishes epoch 1
@@ -98,4 +102,5 @@ class FusedRowParallelLinear:
         from ..ops import native
 
         assert a.shape[0] <= self.max_rows and b.shape[0] == self.n
-        return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out)
+        return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
+                                           self.splitk_ws)
