@@ -455,3 +455,16 @@ def test_rollout_engine_moe_cuda_graph_and_fp8_experts(ops):
     assert all(len(o.token_ids) == 8 for o in outs["fp8"]) and ops.gemm_status() == 0
     # first generated token comes from the prefill (bf16 in both engines): identical; later ones may differ under fp8
     assert [o.token_ids[0] for o in outs["fp8"]] == [o.token_ids[0] for o in outs["graph"]]
+
+
+def test_fp8_weight_block_quantiser_128x128(ops):
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    w = (torch.randn(300, 520, device=DEV) * 0.05).bfloat16()      # ragged: 3 x 5 blocks with partial edges
+    w[130:140, 200:210] *= 30
+    q, sc = F.fp8_quantize_128x128(w)
+    q_c, sc_c = F.fp8_quantize_128x128(w.cpu())
+    assert q.shape == (300, 520) and sc.shape == (3, 5)
+    assert rel(sc, sc_c) < 1e-6 and (q.cpu() != q_c).float().mean() < 1e-2   # identical up to rounding ties
+    assert rel(F.fp8_dequantize_128x128(q.cpu(), sc.cpu()), w.float()) < 0.07

@@ -145,3 +145,27 @@ def test_separation_tables():
     rpm = create_resource_pool_manager(cfg, [Role.Actor, Role.Rollout, Role.RefPolicy])
     assert rpm.resource_pool_spec == {"trainer_pool": [4], "rollout_pool": [2]} and rpm.get_n_gpus() == 6
     assert rpm.mapping[Role.Rollout] == "rollout_pool" and rpm.mapping[Role.RefPolicy] == "trainer_pool"
+
+
+def test_linear_cross_entropy_autograd_matches_plain_torch():
+    from verl_b200.utils.experimental.torch_functional import FusedLinearForPPO
+    from verl_b200.utils.kernel import linear_cross_entropy
+
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn(2, 5, 16, generator=g, requires_grad=True)
+    w = (torch.randn(40, 16, generator=g) * 0.3).requires_grad_(True)
+    y = torch.randint(0, 40, (2, 5), generator=g)
+    lp, ent = linear_cross_entropy(h, w, y, temperature=0.7)
+    (lp.sum() * 1.3 + ent.sum() * 0.4).backward()
+    h2, w2 = h.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    logits = (h2 @ w2.t()) / 0.7
+    ls = torch.log_softmax(logits, -1)
+    lp_r = ls.gather(-1, y.unsqueeze(-1)).squeeze(-1)
+    ent_r = -(ls.exp() * ls).sum(-1)
+    (lp_r.sum() * 1.3 + ent_r.sum() * 0.4).backward()
+    assert torch.allclose(lp, lp_r, atol=1e-5) and torch.allclose(ent, ent_r, atol=1e-5)
+    assert torch.allclose(h.grad, h2.grad, atol=1e-5) and torch.allclose(w.grad, w2.grad, atol=1e-5)
+    m_lp, _ = linear_cross_entropy(h.detach(), w.detach(), y, 0.7, "mean")
+    assert torch.allclose(m_lp, lp_r.mean(), atol=1e-5)
+    lp2, ent2 = FusedLinearForPPO()(h.detach(), w.detach(), y, 0.7)
+    assert torch.allclose(lp2, lp_r, atol=1e-5) and lp2.shape == (2, 5)

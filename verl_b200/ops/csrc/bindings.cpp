@@ -559,6 +559,20 @@ Tensor gemm_fp8_blockscale(const Tensor& aq, const Tensor& sa, const Tensor& bq,
   return d;
 }
 
+// w [R, C] bf16 -> (q [R, C] uint8 holding e4m3, scale_inv [ceil(R/128), ceil(C/128)] fp32): 128 x 128 weight blocks
+std::tuple<Tensor, Tensor> fp8_quant_128x128(const Tensor& w) {
+  CHECK_BF16(w);
+  TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1 && w.size(1) % 4 == 0, "fp8_quant_128x128: [R, C] with C % 4 == 0");
+  const c10::cuda::CUDAGuard guard(w.device());
+  const int64_t R = w.size(0), C = w.size(1);
+  Tensor q = at::empty({R, C}, w.options().dtype(at::kByte));
+  Tensor sc = at::empty({(R + 127) / 128, (C + 127) / 128}, w.options().dtype(at::kFloat));
+  count(1);
+  CHECK_RC(vb_fp8_quant_128x128(w.data_ptr(), w.stride(0), q.data_ptr(), q.stride(0), sc.data_ptr<float>(), (int)R, (int)C, cur_stream()),
+           "vb_fp8_quant_128x128");
+  return {q, sc};
+}
+
 // Grouped block-scaled fp8 GEMM of a mixture-of-experts layer: aq [rows_cap, K] (rows grouped by expert, 128-row aligned),
 // bq [E * N, K]; scales [K/128, rows_cap] and [K/128, E * N]. Rows of tiles beyond num_mtiles are left as allocated (zeroed).
 Tensor gemm_fp8_blockscale_grouped(const Tensor& aq, const Tensor& sa, const Tensor& bq, const Tensor& sb, int64_t N,
@@ -734,6 +748,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
+  m.def("fp8_quant_128x128", &fp8_quant_128x128);
   m.def("gemm_fp8_blockscale_grouped", &gemm_fp8_blockscale_grouped);
   m.def("nvfp4_fake_quant_", &nvfp4_fake_quant_);
   m.def("gemm_fp8_blockscale", &gemm_fp8_blockscale);

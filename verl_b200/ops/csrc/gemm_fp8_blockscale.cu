@@ -217,6 +217,58 @@ __global__ void fp8_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long
   if (lane == 0) scales[static_cast<long long>(b) * R + r] = scale;
 }
 
+// w [R, C] bf16 -> q [R, C] e4m3 and scale_inv [ceil(R/128), ceil(C/128)] fp32: one scale per 128 x 128 block
+// (w ~= q * scale_inv, scale_inv = amax(block) / 448), the weight format of block-scaled fp8 checkpoints.
+// One CTA of 256 threads per block: pass 1 reduces |w| over the block, pass 2 converts.
+__global__ void fp8_quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* __restrict__ q, long long ldq,
+                                         float* __restrict__ scale_inv, int R, int C) {
+  __shared__ float s_red[8];
+  __shared__ float s_scale;
+  const int bc = blockIdx.x, br = blockIdx.y;
+  const int r0 = br * 128, c0 = bc * 128;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // thread t covers columns (t % 32) * 4 .. +3 of rows (t / 32) + 8 * i
+  const int col = c0 + (tid & 31) * 4;
+  float amax = 0.f;
+  float4 vals[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int row = r0 + (tid >> 5) + 8 * i;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < R && col < C) {  // C % 4 == 0: a 4-vector is inside or outside as a whole
+      const uint2 raw = *reinterpret_cast<const uint2*>(w + static_cast<long long>(row) * ldw + col);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+      v = make_float4(a.x, a.y, b.x, b.y);
+    }
+    vals[i] = v;
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) s_red[warp] = amax;
+  __syncthreads();
+  if (tid == 0) {
+    float m = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, s_red[i]);
+    const float sc = fmaxf(m, 1e-12f) / 448.f;
+    s_scale = sc;
+    scale_inv[static_cast<long long>(br) * gridDim.x + bc] = sc;
+  }
+  __syncthreads();
+  const float inv = 1.f / s_scale;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int row = r0 + (tid >> 5) + 8 * i;
+    if (row < R && col < C) {
+      const float4 v = vals[i];
+      __nv_fp8x4_e4m3 packed(make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv));
+      *reinterpret_cast<uint32_t*>(q + static_cast<long long>(row) * ldq + col) = *reinterpret_cast<uint32_t*>(&packed);
+    }
+  }
+}
+
 __device__ int g_fp8_status[4];
 
 }  // namespace vb
@@ -229,6 +281,15 @@ extern "C" int vb_fp8_quant_1x128(const void* x, long long ldx, void* q, long lo
   const long long threads = static_cast<long long>(R) * (C / 128) * 32;
   fp8_quant_1x128_kernel<<<static_cast<int>((threads + 255) / 256), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
                                                                                  reinterpret_cast<uint8_t*>(q), ldq, scales, R, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int vb_fp8_quant_128x128(const void* w, long long ldw, void* q, long long ldq, float* scale_inv, int R, int C, cudaStream_t s) {
+  if (R <= 0 || C <= 0) return 0;
+  if ((C % 4) || (ldw % 4) || (ldq % 4)) return -1;
+  dim3 grid((C + 127) / 128, (R + 127) / 128);
+  fp8_quant_128x128_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(w), ldw, reinterpret_cast<uint8_t*>(q), ldq,
+                                                scale_inv, R, C);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -92,6 +92,7 @@ int vb_gemm_fp8_blockscale(const void* Aq, const float* sa, const void* Bq, cons
 int vb_gemm_fp8_blockscale_grouped(const void* Aq, const float* sa, const void* Bq, const float* sb, void* D, int rows_cap, int N, int K,
                                    int E, long long lda, long long ldb, long long ldd, const int* tile_expert, const int* num_mtiles,
                                    cudaStream_t s);
+int vb_fp8_quant_128x128(const void* w, long long ldw, void* q, long long ldq, float* scale_inv, int R, int C, cudaStream_t s);
 int vb_fp8_status();
 // moe_kernels.cu
 int vb_moe_route_topk(const void* logits, long long ld, int T, int E, int k, int renorm, float* weights, int* experts, int* counts,

@@ -486,6 +486,28 @@ def fp8_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     return (q.view(torch.float8_e4m3fn).float().view(R, C // 128, 128) * scales.t().unsqueeze(-1)).view(R, C)
 
 
+def fp8_quantize_128x128(w: torch.Tensor):
+    """``w`` [R, C] -> (``q`` uint8 [R, C] holding e4m3 bits, ``scale_inv`` fp32 [ceil(R/128), ceil(C/128)]) with
+    ``w ~= q * scale_inv`` per 128 x 128 block: the weight layout of block-scaled fp8 checkpoints (what an external
+    inference engine loads). Parity target: ``verl/utils/kernel/fp8_kernel.py:53-108`` (blockwise cast)."""
+    if w.is_cuda and w.dtype == torch.bfloat16:
+        return _ops().fp8_quant_128x128(w.contiguous())
+    R, C = w.shape
+    Rb, Cb = (R + 127) // 128, (C + 127) // 128
+    pad = torch.zeros(Rb * 128, Cb * 128, dtype=torch.float32, device=w.device)
+    pad[:R, :C] = w.float()
+    blocks = pad.view(Rb, 128, Cb, 128)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp(min=1e-12) / 448.0
+    q = (blocks / scale[:, None, :, None]).to(torch.float8_e4m3fn).view(Rb * 128, Cb * 128)[:R, :C]
+    return q.contiguous().view(torch.uint8), scale
+
+
+def fp8_dequantize_128x128(q: torch.Tensor, scale_inv: torch.Tensor) -> torch.Tensor:
+    R, C = q.shape
+    s = scale_inv.repeat_interleave(128, 0)[:R].repeat_interleave(128, 1)[:, :C]
+    return q.view(torch.float8_e4m3fn).float() * s
+
+
 def linear_fp8_grouped(x_rows: torch.Tensor, wq: torch.Tensor, w_scales: torch.Tensor, n_out: int, tile_expert: torch.Tensor,
                        num_mtiles: torch.Tensor) -> torch.Tensor:
     """Grouped expert linear in block-scaled fp8: ``x_rows`` [rows, K] (rows grouped by expert in 128-row aligned segments,

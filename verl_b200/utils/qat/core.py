@@ -47,9 +47,16 @@ class QATConfig:
         return c
 
 
-def nvfp4_global_scale(x: torch.Tensor) -> float:
-    """Per-tensor scale that lets the largest block scale use the whole e4m3 range."""
-    return float(x.detach().abs().amax().float()) / (FP4_MAX * FP8_MAX)
+def nvfp4_global_scale(x: torch.Tensor, group=None) -> float:
+    """Per-tensor scale that lets the largest block scale use the whole e4m3 range. ``group``: the tensor is one shard of a
+    weight split over a (tensor-parallel) group, whose members must agree on the scale (maximum over the group)."""
+    amax = x.detach().abs().amax().float()
+    if group is not None:
+        import torch.distributed as dist
+
+        amax = amax.clone()
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    return float(amax) / (FP4_MAX * FP8_MAX)
 
 
 def _e2m1_round(a: torch.Tensor) -> torch.Tensor:
@@ -108,12 +115,13 @@ def qat_target_names(params, cfg: QATConfig) -> list[str]:
 
 
 @torch.no_grad()
-def apply_qat_to_params(params, cfg: QATConfig, names: Optional[list] = None) -> int:
-    """Replace every target weight of ``params`` (a ``FlatParams``) by its fake-quantised value, in place."""
+def apply_qat_to_params(params, cfg: QATConfig, names: Optional[list] = None, group=None) -> int:
+    """Replace every target weight of ``params`` (a ``FlatParams``) by its fake-quantised value, in place. ``group``: the
+    tensor-parallel group over which sharded weights agree on their per-tensor scale."""
     assert cfg.mode == "w4a16" and cfg.group_size == 16, "supported: NVFP4 weights (groups of 16), bf16 activations"
     names = qat_target_names(params, cfg) if names is None else names
     for n in names:
         w = params.views[n]
         w2 = w.view(-1, w.shape[-1])
-        nvfp4_fake_quantize(w2, out=w2)
+        nvfp4_fake_quantize(w2, nvfp4_global_scale(w2, group) if group is not None else None, out=w2)
     return len(names)

@@ -108,6 +108,10 @@ class ModelParallelEngine(NativeEngine):
         copy_full_to_local(full, self.params, self.maps, self.topo.tp, self.topo.tp_rank, self.topo.ep, self.topo.ep_rank)
         del full
 
+    def _qat_scale_group(self):
+        topo = getattr(self, "topo", None)
+        return topo.tp_group if topo is not None and topo.tp > 1 else None
+
     # ------------------------------------------------------------------------------------ topology facts for the worker
     def get_data_parallel_size(self) -> int:
         return self.topo.dp

@@ -644,12 +644,16 @@ class NativeEngine(BaseEngine):
             raise RuntimeError(f"peer barrier timed out (status {code}): a rank did not reach the optimizer step")
         return norm
 
+    def _qat_scale_group(self):
+        """Group over which sharded weights agree on their per-tensor quantisation scale (tensor-parallel engines)."""
+        return None
+
     def _apply_qat(self) -> None:
         from ....utils.qat import apply_qat_to_params, qat_target_names
 
         if self._qat_names is None:
             self._qat_names = qat_target_names(self.params, self.qat)
-        apply_qat_to_params(self.params, self.qat, self._qat_names)
+        apply_qat_to_params(self.params, self.qat, self._qat_names, group=self._qat_scale_group())
 
     def _publish_shard(self) -> None:
         """All-gather this rank's updated slice of the working weights into every replica."""
