@@ -1,0 +1,90 @@
+"""Numerical parity of the decoder with the HuggingFace implementations of the supported model families: same random
+weights (loaded through the HF-name mapping), same token ids, logits compared in fp32."""
+import os
+
+import pytest
+import torch
+
+os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+
+transformers = pytest.importorskip("transformers")
+
+COMMON = dict(vocab_size=160, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              max_position_embeddings=128, rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=False)
+
+FAMILIES = {
+    "llama": ("LlamaConfig", "LlamaForCausalLM", dict(COMMON, attention_bias=False)),
+    "mistral": ("MistralConfig", "MistralForCausalLM", dict(COMMON, sliding_window=None)),
+    "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict(COMMON, use_sliding_window=False)),
+    "qwen2_tied": ("Qwen2Config", "Qwen2ForCausalLM", dict(COMMON, tie_word_embeddings=True, use_sliding_window=False)),
+    "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(COMMON, head_dim=32, use_sliding_window=False)),
+    "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(COMMON, head_dim=16, num_experts=4, num_experts_per_tok=2,
+                                                                moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
+                                                                mlp_only_layers=[], use_sliding_window=False)),
+    "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(COMMON, num_local_experts=4, num_experts_per_tok=2, sliding_window=None)),
+    "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(COMMON, pad_token_id=0, sliding_window=None)),
+}
+
+
+def _load_into(P, sd):
+    """HF in-memory state dict (fused expert tensors in recent transformers) -> flat parameters."""
+    sd = dict(sd)
+    missing = P.load_hf_state_dict(sd, strict=False)
+    for name in missing:
+        # names of the on-disk checkpoint format that the in-memory model keeps fused (experts) or renames (Mixtral router)
+        if "experts" not in name and "block_sparse_moe" not in name:
+            raise KeyError(name)
+    for k, v in sd.items():
+        if k.endswith("mlp.experts.gate_up_proj") or k.endswith("mlp.experts.down_proj") or (k.endswith("mlp.gate.weight") and "model.layers" in k):
+            mine = P.views[k[len("model."):]]
+            assert mine.shape == v.shape, (k, mine.shape, v.shape)
+            mine.copy_(v)
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_logits_match_huggingface(family):
+    from verl_b200.models import DecoderModel, FlatParams
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.models.decoder import PackedBatch
+
+    cfg_cls, model_cls, kw = FAMILIES[family]
+    torch.manual_seed(0)
+    hf_cfg = getattr(transformers, cfg_cls)(**kw)
+    hf_cfg._attn_implementation = "eager"
+    hf = getattr(transformers, model_cls)(hf_cfg).float().eval()
+    for p in hf.parameters():          # biases and norms away from their trivial initial values
+        if p.dim() == 1:
+            p.data.add_(torch.randn_like(p) * 0.1)
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    P = FlatParams(cfg, dtype=torch.float32)
+    _load_into(P, hf.state_dict())
+    model = DecoderModel(cfg, P)
+    lens = [9, 5, 12]
+    ids = [torch.randint(0, 160, (n,)) for n in lens]
+    batch = PackedBatch.from_lengths(torch.cat(ids), lens, device="cpu")
+    mine = model.forward_logits(batch).float()
+    off = 0
+    for seq, n in zip(ids, lens):
+        with torch.no_grad():
+            ref = hf(input_ids=seq.unsqueeze(0)).logits[0].float()
+        got = mine[off : off + n]
+        assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (family, (got - ref).abs().max().item())
+        off += n
+
+
+def test_checkpoint_names_follow_each_family():
+    from verl_b200.models import FlatParams
+    from verl_b200.models.config import ModelConfig
+
+    mix = ModelConfig.from_hf_dict(dict(COMMON, model_type="mixtral", num_local_experts=4, num_experts_per_tok=2))
+    names = set(FlatParams(mix, dtype=torch.float32).hf_state_dict())
+    assert {"model.layers.0.block_sparse_moe.gate.weight", "model.layers.1.block_sparse_moe.experts.3.w1.weight",
+            "model.layers.1.block_sparse_moe.experts.3.w2.weight", "model.layers.1.block_sparse_moe.experts.3.w3.weight"} <= names
+    assert mix.to_hf_dict()["num_local_experts"] == 4 and ModelConfig.from_hf_dict(mix.to_hf_dict()).moe_intermediate_size == 112
+    phi = ModelConfig.from_hf_dict(dict(COMMON, model_type="phi3"))
+    names = set(FlatParams(phi, dtype=torch.float32).hf_state_dict())
+    assert "model.layers.0.self_attn.qkv_proj.weight" in names and "model.layers.0.mlp.gate_up_proj.weight" in names
+    assert not any("q_proj" in n for n in names)
+    q3 = ModelConfig.from_hf_dict(dict(COMMON, model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48))
+    names = set(FlatParams(q3, dtype=torch.float32).hf_state_dict())
+    assert "model.layers.0.mlp.experts.2.gate_proj.weight" in names and "model.layers.0.mlp.gate.weight" in names

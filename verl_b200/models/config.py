@@ -132,7 +132,8 @@ class ModelConfig:
             attention_bias=bool(d.get("attention_bias", mt == "qwen2")),
             num_experts=d.get("num_experts", d.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
-            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
+            # Mixtral names its expert width ``intermediate_size``
+            moe_intermediate_size=(d.get("moe_intermediate_size", 0) or 0) or (d.get("intermediate_size", 0) if mt == "mixtral" else 0),
             norm_topk_prob=bool(d.get("norm_topk_prob", True)),
             bos_token_id=d.get("bos_token_id"),
             eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
@@ -154,6 +155,8 @@ class ModelConfig:
             "qwen3_moe": "Qwen3MoeForCausalLM",
             "llama": "LlamaForCausalLM",
             "mistral": "MistralForCausalLM",
+            "mixtral": "MixtralForCausalLM",
+            "phi3": "Phi3ForCausalLM",
         }.get(self.model_type, "LlamaForCausalLM")
         d = {
             "architectures": [arch],
@@ -177,7 +180,10 @@ class ModelConfig:
             "pad_token_id": self.pad_token_id,
             "initializer_range": self.initializer_range,
         }
-        if self.is_moe:
+        if self.is_moe and self.model_type == "mixtral":
+            d.update(num_local_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     intermediate_size=self.moe_intermediate_size)
+        elif self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
         return d

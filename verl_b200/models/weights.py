@@ -187,6 +187,7 @@ class FlatParams:
         """HF-named tensors as zero-copy views of the fused storage."""
         cfg = self.cfg
         q, kv = cfg.q_size, cfg.kv_size
+        mixtral, phi3 = cfg.model_type == "mixtral", cfg.model_type == "phi3"
         for s in self.specs:
             v = self.views[s.name]
             n = s.name
@@ -194,6 +195,20 @@ class FlatParams:
                 yield "lm_head.weight", v
             elif n == "v_head.weight":
                 yield "v_head.weight", v[:1]
+            elif phi3 and (n.endswith("self_attn.qkv_proj.weight") or n.endswith("mlp.gate_up_proj.weight")):
+                yield prefix + n, v                      # Phi-3 checkpoints store these projections fused, in the same order
+            elif mixtral and n.endswith("mlp.gate.weight"):
+                yield prefix + n.replace("mlp.gate.weight", "block_sparse_moe.gate.weight"), v
+            elif mixtral and n.endswith("mlp.experts.gate_up_proj"):
+                base = n[: -len("mlp.experts.gate_up_proj")] + "block_sparse_moe.experts."
+                ie = cfg.moe_intermediate_size
+                for e in range(cfg.num_experts):
+                    yield f"{prefix}{base}{e}.w1.weight", v[e, :ie]   # gate
+                    yield f"{prefix}{base}{e}.w3.weight", v[e, ie:]   # up
+            elif mixtral and n.endswith("mlp.experts.down_proj"):
+                base = n[: -len("mlp.experts.down_proj")] + "block_sparse_moe.experts."
+                for e in range(cfg.num_experts):
+                    yield f"{prefix}{base}{e}.w2.weight", v[e]
             elif n.endswith("self_attn.qkv_proj.weight") or n.endswith("self_attn.qkv_proj.bias"):
                 base, kind = n.rsplit("qkv_proj.", 1)
                 yield f"{prefix}{base}q_proj.{kind}", v[:q]
