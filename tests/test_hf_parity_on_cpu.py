@@ -88,3 +88,48 @@ def test_checkpoint_names_follow_each_family():
     q3 = ModelConfig.from_hf_dict(dict(COMMON, model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48))
     names = set(FlatParams(q3, dtype=torch.float32).hf_state_dict())
     assert "model.layers.0.mlp.experts.2.gate_proj.weight" in names and "model.layers.0.mlp.gate.weight" in names
+
+
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "mixtral"])
+def test_gradients_match_huggingface_autograd(family):
+    """The hand-scheduled backward pass against HuggingFace + autograd: gradient of the summed label log-probs with
+    respect to every parameter."""
+    from verl_b200.models import DecoderModel, FlatParams
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.models.decoder import PackedBatch
+
+    cfg_cls, model_cls, kw = FAMILIES[family]
+    torch.manual_seed(1)
+    hf_cfg = getattr(transformers, cfg_cls)(**kw)
+    hf_cfg._attn_implementation = "eager"
+    hf = getattr(transformers, model_cls)(hf_cfg).float().train()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    P = FlatParams(cfg, dtype=torch.float32, with_main_grad=True)
+    _load_into(P, hf.state_dict())
+    model = DecoderModel(cfg, P)
+    lens = [7, 10]
+    ids = [torch.randint(0, 160, (n,)) for n in lens]
+    batch = PackedBatch.from_lengths(torch.cat(ids), lens, device="cpu")
+    labels = torch.cat([torch.roll(s, -1) for s in ids])
+    lp, _ = model.forward_logprobs(batch, labels, 1.0, need_grad=True)
+    lp.sum().backward()
+    total = 0.0
+    for s in ids:
+        logits = hf(input_ids=s.unsqueeze(0)).logits[0].float()
+        ref_lp = torch.log_softmax(logits, -1).gather(-1, torch.roll(s, -1).unsqueeze(-1)).squeeze(-1)
+        total = total + ref_lp.sum()
+    total.backward()
+    G = FlatParams(cfg, dtype=torch.float32, buffer=P.main_grad)      # the gradient buffer under the parameter names
+    mine = G.hf_state_dict()
+    checked = 0
+    for name, p in hf.named_parameters():
+        if name in mine:
+            got = mine[name]
+        elif name.endswith("mlp.experts.gate_up_proj") or name.endswith("mlp.experts.down_proj") or name.endswith("mlp.gate.weight"):
+            got = G.views[name[len("model."):]]
+        else:
+            raise KeyError(name)
+        scale = p.grad.abs().max().clamp(min=1e-6)
+        assert (got - p.grad).abs().max() / scale < 2e-3, (family, name, float((got - p.grad).abs().max() / scale))
+        checked += 1
+    assert checked == len(list(hf.named_parameters()))
