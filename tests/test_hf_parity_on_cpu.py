@@ -21,6 +21,9 @@ FAMILIES = {
     "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(COMMON, head_dim=16, num_experts=4, num_experts_per_tok=2,
                                                                 moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
                                                                 mlp_only_layers=[], use_sliding_window=False)),
+    "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM", dict(COMMON, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                                                                shared_expert_intermediate_size=80, norm_topk_prob=False,
+                                                                decoder_sparse_step=1, mlp_only_layers=[], use_sliding_window=False)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(COMMON, num_local_experts=4, num_experts_per_tok=2, sliding_window=None)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(COMMON, pad_token_id=0, sliding_window=None)),
 }
@@ -90,7 +93,7 @@ def test_checkpoint_names_follow_each_family():
     assert "model.layers.0.mlp.experts.2.gate_proj.weight" in names and "model.layers.0.mlp.gate.weight" in names
 
 
-@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "mixtral"])
+@pytest.mark.parametrize("family", ["qwen2", "qwen3", "qwen3_moe", "qwen2_moe", "mixtral"])
 def test_gradients_match_huggingface_autograd(family):
     """The hand-scheduled backward pass against HuggingFace + autograd: gradient of the summed label log-probs with
     respect to every parameter."""

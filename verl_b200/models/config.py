@@ -36,6 +36,7 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0   # > 0: a dense expert every token passes through, scaled by a sigmoid gate
     router_aux_loss_coef: float = 0.0
     # tokens
     bos_token_id: Optional[int] = None
@@ -52,7 +53,7 @@ class ModelConfig:
     def __post_init__(self):
         if self.head_dim is None:
             self.head_dim = self.hidden_size // self.num_attention_heads
-        if self.model_type in ("qwen2",) and "attention_bias" not in self.extra.get("_explicit", ()):
+        if self.model_type in ("qwen2", "qwen2_moe") and "attention_bias" not in self.extra.get("_explicit", ()):
             self.attention_bias = True
         if self.model_type in ("qwen3", "qwen3_moe"):
             self.qk_norm = True
@@ -103,6 +104,8 @@ class ModelConfig:
             per_layer += 2 * self.head_dim
         if self.is_moe:
             per_layer += self.num_experts * h + self.num_experts * 3 * h * self.moe_intermediate_size
+            if self.shared_expert_intermediate_size:
+                per_layer += 3 * h * self.shared_expert_intermediate_size + 8 * h
         else:
             per_layer += 3 * h * self.intermediate_size
         total = v * h + self.num_hidden_layers * per_layer + h
@@ -129,12 +132,13 @@ class ModelConfig:
             rope_theta=float(d.get("rope_theta", 10000.0)),
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            attention_bias=bool(d.get("attention_bias", mt == "qwen2")),
+            attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))),
             num_experts=d.get("num_experts", d.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             # Mixtral names its expert width ``intermediate_size``
             moe_intermediate_size=(d.get("moe_intermediate_size", 0) or 0) or (d.get("intermediate_size", 0) if mt == "mixtral" else 0),
-            norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            norm_topk_prob=bool(d.get("norm_topk_prob", mt != "qwen2_moe")),
+            shared_expert_intermediate_size=(d.get("shared_expert_intermediate_size", 0) or 0) if mt == "qwen2_moe" else 0,
             bos_token_id=d.get("bos_token_id"),
             eos_token_id=d.get("eos_token_id") if not isinstance(d.get("eos_token_id"), list) else d["eos_token_id"][0],
             pad_token_id=d.get("pad_token_id"),
@@ -153,6 +157,7 @@ class ModelConfig:
             "qwen2": "Qwen2ForCausalLM",
             "qwen3": "Qwen3ForCausalLM",
             "qwen3_moe": "Qwen3MoeForCausalLM",
+            "qwen2_moe": "Qwen2MoeForCausalLM",
             "llama": "LlamaForCausalLM",
             "mistral": "MistralForCausalLM",
             "mixtral": "MixtralForCausalLM",
@@ -186,6 +191,8 @@ class ModelConfig:
         elif self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+            if self.shared_expert_intermediate_size:
+                d.update(shared_expert_intermediate_size=self.shared_expert_intermediate_size, decoder_sparse_step=1, mlp_only_layers=[])
         return d
 
     def save_pretrained(self, path: str) -> None:

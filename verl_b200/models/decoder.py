@@ -683,7 +683,46 @@ class DecoderModel:
         self._wgrad(W["mlp.gate.weight"], g_logits, h2)
         return g_h2.to(h2.dtype)
 
+    # -- shared expert (Qwen2-MoE): a dense SwiGLU MLP applied to every token, scaled by sigmoid(h . w_gate) -------------
+    def _shared_expert_fwd(self, W, h2, S: Optional[dict]):
+        gu = F.gemm(h2, W["mlp.shared_expert.gate_up_proj.weight"])
+        y = F.gemm(F.swiglu(gu), W["mlp.shared_expert.down_proj.weight"])
+        z = F.gemm(h2, W["mlp.shared_expert_gate.weight"])[:, 0].float()
+        sg = torch.sigmoid(z)
+        if S is not None:
+            S["shared"] = dict(gu=gu, y=y, sg=sg)
+        return (y.float() * sg.unsqueeze(-1)).to(h2.dtype)
+
+    def _shared_expert_bwd(self, W, g_d, h2, S: dict):
+        Sh = S["shared"]
+        gu, y, sg = Sh["gu"], Sh["y"], Sh["sg"]
+        Wgu, Wd, Wg = W["mlp.shared_expert.gate_up_proj.weight"], W["mlp.shared_expert.down_proj.weight"], W["mlp.shared_expert_gate.weight"]
+        g_y = (g_d.float() * sg.unsqueeze(-1)).to(h2.dtype)
+        g_z = (g_d.float() * y.float()).sum(-1) * sg * (1.0 - sg)
+        g_act = F.gemm(g_y, Wd, b_mn=True)
+        self._wgrad(Wd, g_y, F.swiglu(gu))
+        g_gu = F.swiglu_bwd(g_act, gu)
+        g_h2 = F.gemm(g_gu, Wgu, b_mn=True).float()
+        self._wgrad(Wgu, g_gu, h2)
+        dl = torch.zeros(h2.shape[0], Wg.shape[0], dtype=h2.dtype, device=h2.device)
+        dl[:, 0] = g_z.to(h2.dtype)
+        g_h2 += F.gemm(dl, Wg, b_mn=True).float()
+        self._wgrad(Wg, dl, h2)
+        return g_h2
+
     def _moe_fwd(self, W, h2, S: Optional[dict]):
+        out = self._moe_routed_fwd(W, h2, S)
+        if self.cfg.shared_expert_intermediate_size:
+            out = out + self._shared_expert_fwd(W, h2, S)
+        return out
+
+    def _moe_bwd(self, W, g_d, h2, S: dict):
+        g_h2 = self._moe_routed_bwd(W, g_d, h2, S)
+        if self.cfg.shared_expert_intermediate_size:
+            g_h2 = (g_h2.float() + self._shared_expert_bwd(W, g_d.contiguous(), h2, S)).to(h2.dtype)
+        return g_h2
+
+    def _moe_routed_fwd(self, W, h2, S: Optional[dict]):
         if self.ep is not None:
             return self._moe_fwd_ep(W, h2, S)
         if self._moe_native_ok(h2):
@@ -715,7 +754,7 @@ class DecoderModel:
             S.update(moe=dict(logits=logits, idx=idx, order=order, tok=tok, counts=counts, gu=gu, y=y, wp=wp))
         return out.to(h2.dtype)
 
-    def _moe_bwd(self, W, g_d, h2, S: dict):
+    def _moe_routed_bwd(self, W, g_d, h2, S: dict):
         if S["moe"].get("ep"):
             return self._moe_bwd_ep(W, g_d, h2, S)
         if S["moe"].get("native"):

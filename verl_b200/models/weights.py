@@ -63,6 +63,12 @@ def build_param_specs(cfg: ModelConfig, value_head: bool = False) -> list[ParamS
             specs.append(ParamSpec(p + "mlp.gate.weight", (E, h), "normal", True, i))
             specs.append(ParamSpec(p + "mlp.experts.gate_up_proj", (El, 2 * ie, h), "normal", True, i))
             specs.append(ParamSpec(p + "mlp.experts.down_proj", (El, h, ie), "normal", True, i))
+            if cfg.shared_expert_intermediate_size:
+                se = cfg.shared_expert_intermediate_size
+                specs.append(ParamSpec(p + "mlp.shared_expert.gate_up_proj.weight", (2 * se, h), "normal", True, i))
+                specs.append(ParamSpec(p + "mlp.shared_expert.down_proj.weight", (h, se), "normal", True, i))
+                # scalar gate stored with 8 rows (row 0 is the gate) so the GEMM's N % 8 == 0 rule holds
+                specs.append(ParamSpec(p + "mlp.shared_expert_gate.weight", (8, h), "normal", True, i))
         else:
             specs.append(ParamSpec(p + "mlp.gate_up_proj.weight", (2 * cfg.intermediate_size, h), "normal", True, i))
             specs.append(ParamSpec(p + "mlp.down_proj.weight", (h, cfg.intermediate_size), "normal", True, i))
@@ -214,6 +220,13 @@ class FlatParams:
                 yield f"{prefix}{base}q_proj.{kind}", v[:q]
                 yield f"{prefix}{base}k_proj.{kind}", v[q : q + kv]
                 yield f"{prefix}{base}v_proj.{kind}", v[q + kv :]
+            elif n.endswith("mlp.shared_expert_gate.weight"):
+                yield prefix + n, v[:1]
+            elif n.endswith("mlp.shared_expert.gate_up_proj.weight"):
+                base = n[: -len("gate_up_proj.weight")]
+                se = cfg.shared_expert_intermediate_size
+                yield f"{prefix}{base}gate_proj.weight", v[:se]
+                yield f"{prefix}{base}up_proj.weight", v[se:]
             elif n.endswith("mlp.gate_up_proj.weight"):
                 base = n[: -len("gate_up_proj.weight")]
                 I = cfg.intermediate_size
