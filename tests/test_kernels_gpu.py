@@ -294,7 +294,7 @@ def test_advantage_kernels(ops):
     assert (ret.cpu() - ret2).abs().max() < 1e-4 and (a.cpu() - a2).abs().max() < 1e-3
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-llama"])
+@pytest.mark.parametrize("name", ["tiny-qwen2", "tiny-llama", "tiny-moe", "tiny-qwen2-moe"])
 def test_model_gpu_matches_cpu(ops, name):
     from verl_b200.models import DecoderModel, FlatParams, PackedBatch, get_preset
 
