@@ -476,3 +476,36 @@ def test_fp8_weight_block_quantiser_128x128(ops):
     assert rel(sc, sc_c) < 1e-6 and (q.cpu() != q_c).float().mean() < 3e-2
     assert rel(F.fp8_dequantize_128x128(q.cpu(), sc.cpu()), F.fp8_dequantize_128x128(q_c, sc_c)) < 1e-2
     assert rel(F.fp8_dequantize_128x128(q.cpu(), sc.cpu()), w.float()) < 0.07
+
+
+def test_training_step_is_bitwise_reproducible_on_gpu(ops):
+    """Deterministic mode: the same step run twice from the same seed gives identical bits (fixed reduction orders, no
+    atomics on the training path)."""
+    from functools import partial
+
+    from verl_b200.models import get_preset
+    from verl_b200.ops import functional as F
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.engine.utils import enable_full_determinism
+    from verl_b200.workers.utils.losses import sft_loss
+
+    saved = dict(F._ATTN_IMPL)
+    try:
+        def run():
+            enable_full_determinism(11)
+            eng = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=3, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2))
+            eng.initialize()
+            g = torch.Generator().manual_seed(5)
+            ids = torch.randint(3, 500, (4, 96), generator=g).to(DEV)
+            am = torch.ones_like(ids)
+            data = {"input_ids": ids, "attention_mask": am, "responses": ids[:, -40:], "response_mask": am[:, -40:]}
+            norms = [eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"] for _ in range(2)]
+            return norms, eng.params.flat.clone()
+
+        n1, w1 = run()
+        n2, w2 = run()
+        assert n1 == n2 and torch.equal(w1, w2)
+    finally:
+        F._ATTN_IMPL.update(saved)
+        torch.use_deterministic_algorithms(False)

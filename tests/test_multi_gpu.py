@@ -73,7 +73,12 @@ def _worker_body(rank, world, port, queue):
         same.append(bool(torch.equal(other, y)))
     # decode-sized call with a deep K: K-split GEMM + fused reduce / all-reduce kernel (twice: both buffer halves)
     fused_d = FusedRowParallelLinear(max_rows=320, n=1024, device=dev)
+    import random
+    import time as _time
+
+    rnd_delay = random.Random(1000 + rank)
     for call in range(3):
+        _time.sleep(rnd_delay.random() * 0.05)  # ranks reach the call at different times: the epoch flags must cope
         g = torch.Generator(device="cpu").manual_seed(70 + call)
         a_full = torch.randn(320, 8192, generator=g).bfloat16()
         b_full = (torch.randn(1024, 8192, generator=g) * 0.02).bfloat16()

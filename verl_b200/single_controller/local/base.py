@@ -118,6 +118,9 @@ def _free_port() -> int:
 
 def _worker_main(conn, cls_with_init, env: dict):
     os.environ.update(env)
+    from ...utils.process import set_death_signal
+
+    set_death_signal()  # a worker never outlives the controller that spawned it
     try:
         if env.get("VERL_WORKER_DEVICE") == "cuda":
             import torch

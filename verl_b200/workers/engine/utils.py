@@ -29,6 +29,9 @@ def enable_full_determinism(seed: int) -> None:
         torch.cuda.manual_seed_all(seed)
     os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
     os.environ["VERL_B200_NATIVE_ATTN_BWD"] = "0"  # the tcgen05 attention backward reduces dQ with fp32 atomics
+    from ...ops import functional as _F
+
+    _F._ATTN_IMPL["bwd"] = None                    # also when the kernels were selected before this call
     torch.backends.cudnn.deterministic = True
     torch.backends.cudnn.benchmark = False
     try:
