@@ -508,4 +508,5 @@ def test_training_step_is_bitwise_reproducible_on_gpu(ops):
         assert n1 == n2 and torch.equal(w1, w2)
     finally:
         F._ATTN_IMPL.update(saved)
+        F.DETERMINISTIC_ATTENTION = False
         torch.use_deterministic_algorithms(False)

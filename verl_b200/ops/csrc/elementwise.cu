@@ -260,6 +260,9 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __
 // ------------------------------------------------------------------------------------------ optimizer
 // ctrl[0] = sum of squared gradients (accumulated by sumsq_kernel), ctrl[1] = clip coefficient,
 // ctrl[2] = 1.0 when the step must be skipped (non-finite norm), ctrl[3] = grad norm.
+constexpr int SUMSQ_MAX_BLOCKS = 148 * 8;
+__device__ float g_sumsq_partial[SUMSQ_MAX_BLOCKS];  // scratch of the two-pass reduction (one call at a time per device)
+
 __global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ ctrl) {
   __shared__ float red[32];
   float s = 0.f;
@@ -272,7 +275,15 @@ __global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __
   for (long long i = (n4 << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
     s += g[i] * g[i];
   s = block_sum(s, red);
-  if (threadIdx.x == 0) atomicAdd(ctrl, s);
+  if (threadIdx.x == 0) g_sumsq_partial[blockIdx.x] = s;
+}
+// second pass: the block partials are folded in a fixed order (bitwise reproducible), then added to ctrl[0]
+__global__ void sumsq_final_kernel(int blocks, float* __restrict__ ctrl) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < blocks; i += blockDim.x) s += g_sumsq_partial[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) ctrl[0] += s;
 }
 __global__ void clip_coef_kernel(float* __restrict__ ctrl, float max_norm) {
   const float norm = sqrtf(ctrl[0]);
@@ -414,9 +425,10 @@ int vb_embedding_bwd(const long long* ids, const void* dout, float* dw, int T, i
 int vb_sumsq(const float* g, long long n, float* ctrl, cudaStream_t s) {
   if (n == 0) return 0;
   long long blocks = (n / 4 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > SUMSQ_MAX_BLOCKS) blocks = SUMSQ_MAX_BLOCKS;
   if (blocks < 1) blocks = 1;
   sumsq_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(g, n, ctrl);
+  sumsq_final_kernel<<<1, 256, 0, s>>>(static_cast<int>(blocks), ctrl);
   return static_cast<int>(cudaGetLastError());
 }
 int vb_clip_coef(float* ctrl, float max_norm, cudaStream_t s) {

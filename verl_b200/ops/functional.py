@@ -191,8 +191,14 @@ def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return F.embedding(ids.reshape(-1), weight)
 
 
+DETERMINISTIC_ATTENTION = False  # set by enable_full_determinism(): order-stable accumulation instead of atomics / fused library back-ends
+
+
 def embedding_bwd_(ids: torch.Tensor, dout: torch.Tensor, dweight: torch.Tensor) -> None:
-    if dout.is_cuda:
+    if dout.is_cuda and DETERMINISTIC_ATTENTION:
+        # deterministic mode: the kernel adds repeated token ids with atomics; the sorted accumulation is order-stable
+        dweight.index_add_(0, ids.reshape(-1), dout.to(dweight.dtype))
+    elif dout.is_cuda:
         _ops().embedding_bwd_(ids.reshape(-1).contiguous(), dout.contiguous(), dweight)
     else:
         dweight.index_add_(0, ids.reshape(-1), dout.to(dweight.dtype))
@@ -339,7 +345,14 @@ def attention_varlen_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen: int, s
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if q.is_cuda and _ATTN_IMPL["bwd"] is not None and lse is not None and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
         return _ATTN_IMPL["bwd"](dout, q, k, v, out, lse, cu_seqlens.to(q.device), max_seqlen, scale)
-    with torch.enable_grad():
+    import contextlib
+
+    ctx = contextlib.nullcontext()
+    if DETERMINISTIC_ATTENTION and q.is_cuda:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+
+        ctx = sdpa_kernel(SDPBackend.MATH)  # the fused library back-ends accumulate dQ / dK in a run-dependent order
+    with torch.enable_grad(), ctx:
         q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
         o = _sdpa_varlen(q_, k_, v_, cu_seqlens, scale)
         return torch.autograd.grad(o, (q_, k_, v_), dout)

@@ -32,6 +32,7 @@ def enable_full_determinism(seed: int) -> None:
     from ...ops import functional as _F
 
     _F._ATTN_IMPL["bwd"] = None                    # also when the kernels were selected before this call
+    _F.DETERMINISTIC_ATTENTION = True              # the autograd attention backward then runs on the math back-end
     torch.backends.cudnn.deterministic = True
     torch.backends.cudnn.benchmark = False
     try:
