@@ -116,3 +116,27 @@ def test_identical_prompts_are_prefilled_once_and_match_unshared_generation():
     for a, b in zip(outs[True], outs[False]):
         assert a.token_ids == b.token_ids and max(abs(x - y) for x, y in zip(a.log_probs, b.log_probs)) < 1e-5
     assert outs[True][0].token_ids != outs[True][1].token_ids  # same prompt, different seeds: different samples
+
+
+def test_stop_tokens_and_repetition_penalty():
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    prompt = [5, 6, 7, 8, 9]
+    eng = RolloutEngine(cfg, P, max_num_seqs=4, max_model_len=64, block_size=4, eos_token_id=-1)
+    base = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12))[0]
+    assert base.stop_reason == "length" and len(base.token_ids) == 12
+    # the 4th greedy token as a stop token: generation ends there, with the stop token as last token
+    stop = base.token_ids[3]
+    first = base.token_ids.index(stop)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[stop]))[0]
+    assert out.token_ids == base.token_ids[: first + 1] and out.stop_reason == "completed"
+    # a very large penalty under greedy decoding: no token of the prompt or of the output repeats
+    pen = eng.generate([prompt, prompt], SamplingParams(temperature=0.0, max_tokens=12, repetition_penalty=1e4))
+    for o in pen:
+        seq = prompt + o.token_ids
+        assert len(set(seq)) == len(seq), seq
+    # penalty 1.0 alongside: unchanged output for that request
+    again = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12))[0]
+    assert again.token_ids == base.token_ids

@@ -220,6 +220,10 @@ class RolloutEngine:
         self.active = z(torch.bool)
         self.ignore_eos = z(torch.bool)
         self.seeds = z(torch.int64)
+        self.stop_ids = torch.full((S, 8), -1, dtype=torch.int64, device=dev)  # per slot: extra tokens that end the sequence
+        self.rep_penalty = torch.ones(S, dtype=torch.float32, device=dev)
+        self.seen = None            # [S, vocab] bool, allocated when a request asks for a repetition penalty
+        self._use_penalty = False
         self.block_table = torch.zeros(S, self.max_blocks_per_seq, dtype=torch.int32, device=dev)
         self.out_cap = 0
         self.out_tok = self.out_lp = None
@@ -357,7 +361,25 @@ class RolloutEngine:
         slots = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=dev)
         seeds = torch.tensor([(r.params.seed if r.params.seed is not None else self._seed * 1000003 + zlib.crc32(r.rid.encode()))
                               for r in reqs], dtype=torch.int64, device=dev)
+        stop_rows = torch.full((len(reqs), 8), -1, dtype=torch.int64)
+        for i, r in enumerate(reqs):
+            st = list(r.params.stop_token_ids or ())[:8]
+            if st:
+                stop_rows[i, : len(st)] = torch.tensor(st, dtype=torch.int64)
+        self.stop_ids[slots] = stop_rows.to(dev)
+        pens = [float(r.params.repetition_penalty or 1.0) for r in reqs]
+        if any(p != 1.0 for p in pens) and not self._use_penalty:
+            self.seen = torch.zeros(self.S, self.cfg.vocab_size, dtype=torch.bool, device=dev)
+            self._use_penalty, self._graph = True, None  # the decode graph gains the penalty ops
+        self.rep_penalty[slots] = torch.tensor(pens, dtype=torch.float32, device=dev)
+        if self._use_penalty:
+            self.seen[slots] = False
+            for i, r in enumerate(reqs):
+                self.seen[r.slot, torch.tensor(r.prompt, dtype=torch.int64, device=dev)] = True
+            logits = self._penalise(logits, slots)
         tok, lp = F.sample_tokens(logits, self.temperature, seeds, 0, self.valid_vocab, self.top_k, self.top_p)
+        if self._use_penalty:
+            self.seen[slots, tok] = True
         n = torch.tensor(lens, dtype=torch.int32, device=dev)
         self.block_table[slots] = bt_rows.to(dev)
         self.tok[slots] = tok
@@ -372,11 +394,22 @@ class RolloutEngine:
         done = (self.gen[slots] >= self.max_new[slots])
         if self.eos is not None:
             done |= (tok == self.eos) & ~self.ignore_eos[slots]
+        done |= (tok.unsqueeze(1) == self.stop_ids[slots]).any(1)
         self.active[slots] = ~done
         for r in reqs:
             self.running[r.slot] = r
         self.stats["prefill_tokens"] += sum(lens)
         self.stats["prefill_s"] += time.time() - t0
+
+    def _penalise(self, logits: torch.Tensor, slots=None) -> torch.Tensor:
+        """Repetition penalty: logits of tokens that already occur in a sequence are divided (positive) or multiplied
+        (negative) by the sequence's penalty."""
+        seen = self.seen if slots is None else self.seen[slots]
+        pen = (self.rep_penalty if slots is None else self.rep_penalty[slots]).unsqueeze(1)
+        l = logits.float()
+        V = min(l.shape[1], seen.shape[1])
+        l[:, :V] = torch.where(seen[:, :V], torch.where(l[:, :V] > 0, l[:, :V] / pen, l[:, :V] * pen), l[:, :V])
+        return l.to(logits.dtype)
 
     # ------------------------------------------------------------------------------------ decode
     def _decode_body(self) -> None:
@@ -423,9 +456,13 @@ class RolloutEngine:
             r = x2
         hN = F.rms_norm(a, P["norm.weight"], cfg.rms_norm_eps, residual=r)[0]
         logits = F.gemm(hN, P.lm_head_weight)
+        if self._use_penalty:
+            logits = self._penalise(logits)
         tok, lp = F.sample_tokens(logits, self.temperature, self.seeds, 0, self.valid_vocab, self.top_k, self.top_p)
         # ---- state update (all on device)
         rows = torch.arange(S, device=self.device)
+        if self._use_penalty:
+            self.seen[rows, tok] = self.seen[rows, tok] | act
         col = self.gen.long().clamp(max=self.out_cap - 1)
         self.out_tok[rows, col] = torch.where(act, tok, self.out_tok[rows, col])
         self.out_lp[rows, col] = torch.where(act, lp, self.out_lp[rows, col])
@@ -433,6 +470,7 @@ class RolloutEngine:
         done = self.gen >= self.max_new
         if self.eos is not None:
             done = done | ((tok == self.eos) & ~self.ignore_eos)
+        done = done | (tok.unsqueeze(1) == self.stop_ids).any(1)
         self.tok.copy_(torch.where(act, tok, self.tok))
         self.pos.add_(acti)
         self.ctx.add_(acti)
@@ -495,7 +533,8 @@ class RolloutEngine:
             still_active = bool(active[s])
             if still_active:
                 reason = "aborted"
-            elif self.eos is not None and n > 0 and t[-1] == self.eos and not r.params.ignore_eos:
+            elif n > 0 and ((self.eos is not None and t[-1] == self.eos and not r.params.ignore_eos)
+                            or t[-1] in tuple(r.params.stop_token_ids or ())):
                 reason = "completed"
             else:
                 reason = "length"
