@@ -329,6 +329,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 g0 = me // tp * tp
                 self.rollout_tp_group = dist.new_group(pool_ranks[g0 : g0 + tp], use_local_synchronization=True)
             self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs * tp, tp_group=self.rollout_tp_group,
+                                         record_routing=(self._router_replay_mode() == "R3"),
                                          quantization=(rc.get("quantization") if tp == 1 else None),
                                          max_num_batched_tokens=rc.max_num_batched_tokens, max_model_len=max_len + 1,
                                          block_size=rc.block_size, gpu_memory_utilization=rc.gpu_memory_utilization,
@@ -391,9 +392,21 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         pos = VF.compute_position_id_with_mask(full_mask)
         if rc.free_cache_engine:
             self.rollout.release_kv_cache()
+        tensors = {"prompts": ids, "responses": resp, "input_ids": full_ids, "attention_mask": full_mask,
+                   "position_ids": pos, "response_mask": resp_mask, "rollout_log_probs": lps}
+        if outs and "routed_experts" in outs[0].extra_fields:
+            # router replay from the rollout (R3): experts per position of the padded [b, P + R] layout; the last generated
+            # token never went through the rollout model, its row stays zero (its output enters no loss)
+            P_len = ids.shape[1]
+            first = outs[0].extra_fields["routed_experts"]
+            routed = torch.zeros(b, P_len + R, first.shape[1], first.shape[2], dtype=torch.int32)
+            for i, o in enumerate(outs):
+                re_ = o.extra_fields["routed_experts"].to(torch.int32)
+                p_n = len(o.prompt_ids)
+                routed[i, P_len - p_n : P_len - p_n + re_.shape[0]] = re_
+            tensors["routed_experts"] = routed.to(dev)
         out = DataProto.from_dict(
-            tensors={"prompts": ids, "responses": resp, "input_ids": full_ids, "attention_mask": full_mask,
-                     "position_ids": pos, "response_mask": resp_mask, "rollout_log_probs": lps},
+            tensors=tensors,
             meta_info={"timing": {"generate_sequences": time.time() - t0},
                        "rollout_stats": dict(self.rollout.stats)})
         return out

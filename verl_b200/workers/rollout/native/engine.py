@@ -83,7 +83,7 @@ class RolloutEngine:
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
                  valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0,
-                 tp_group=None, quantization: Optional[str] = None, share_prefill: bool = True):
+                 tp_group=None, quantization: Optional[str] = None, share_prefill: bool = True, record_routing: bool = False):
         """``tp_group``: process group of the ranks that serve the same requests tensor-parallel (each holds the
         full replicated weights and uses its shard of them in place; see ``TensorParallelShard``). All ranks of the
         group must be fed the same requests in the same order."""
@@ -91,6 +91,10 @@ class RolloutEngine:
         assert quantization in (None, "", "fp8"), f"unsupported rollout quantization: {quantization}"
         self.quantization = quantization or None
         self.share_prefill = bool(share_prefill)
+        # mixture-of-experts models: return the experts every router picked for every token that went through the model
+        # (``RequestOutput.extra_fields["routed_experts"]``, [prompt + generated - 1, layers, k]) for router replay
+        self.record_routing = bool(record_routing) and cfg.is_moe
+        self.out_routed = None
         self.tp_group = tp_group
         self.tp_size = dist.get_world_size(tp_group) if tp_group is not None else 1
         self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
@@ -237,6 +241,9 @@ class RolloutEngine:
             self.out_cap = int(cap)
             self.out_tok = torch.zeros(self.S, self.out_cap, dtype=torch.int64, device=self.device)
             self.out_lp = torch.zeros(self.S, self.out_cap, dtype=torch.float32, device=self.device)
+            if self.record_routing:
+                self.out_routed = torch.zeros(self.S, self.out_cap, self.cfg.num_hidden_layers, self.cfg.num_experts_per_tok,
+                                              dtype=torch.int16, device=self.device)
             self._graph = None
 
     # ------------------------------------------------------------------------------------ requests
@@ -340,10 +347,23 @@ class RolloutEngine:
             slot_map = torch.cat(slot_rows)
         batch = PackedBatch.from_lengths(ids, [lens[i] for i in leaders], device=dev)
         self._prefill_slots = slot_map
+        if self.record_routing:
+            from ....models.decoder import RouterReplay
+
+            self.model.router_replay = RouterReplay("record")
         try:
             h = self.model.forward_hidden(batch)
         finally:
             self._prefill_slots = None
+        if self.record_routing:
+            routed = self.model.router_replay.stacked(list(range(self.cfg.num_hidden_layers))).to(torch.int16).cpu()
+            self.model.router_replay = None
+            cu = [0]
+            for i in leaders:
+                cu.append(cu[-1] + lens[i])
+            for i, r in enumerate(reqs):
+                j = lead_idx[i]
+                r.routed_prompt = routed[cu[j] : cu[j + 1]]
         last = (batch.cu_seqlens[1:].long() - 1)
         logits = F.gemm(h[last].contiguous(), self.params.lm_head_weight)
         if len(leaders) < len(reqs):
@@ -428,8 +448,13 @@ class RolloutEngine:
         a = F.embedding(self.tok, P["embed_tokens.weight"])
         r = None
         cos, sin = self.model._cos, self.model._sin
+        if self.record_routing:
+            from ....models.decoder import RouterReplay
+
+            self.model.router_replay = RouterReplay("record")
         for i in range(cfg.num_hidden_layers):
             W = P.layer(i)
+            self.model._layer_idx = i
             h1, x, _ = F.rms_norm(a, W["input_layernorm.weight"], cfg.rms_norm_eps, residual=r)
             if tp is not None:
                 qkv = self.model.qkv_tp(W, h1)
@@ -461,6 +486,12 @@ class RolloutEngine:
         tok, lp = F.sample_tokens(logits, self.temperature, self.seeds, 0, self.valid_vocab, self.top_k, self.top_p)
         # ---- state update (all on device)
         rows = torch.arange(S, device=self.device)
+        if self.record_routing:
+            # routing of the token that was fed in this step = generated token number gen - 1
+            step_routed = self.model.router_replay.stacked(list(range(cfg.num_hidden_layers))).to(torch.int16)
+            self.model.router_replay = None
+            prev = (self.gen.long() - 1).clamp(min=0, max=self.out_cap - 1)
+            self.out_routed[rows, prev] = torch.where(act.view(-1, 1, 1), step_routed, self.out_routed[rows, prev])
         if self._use_penalty:
             self.seen[rows, tok] = self.seen[rows, tok] | act
         col = self.gen.long().clamp(max=self.out_cap - 1)
@@ -526,6 +557,7 @@ class RolloutEngine:
         idx = torch.tensor(done_slots, dtype=torch.int64, device=self.device)
         toks = self.out_tok[idx].cpu()
         lps = self.out_lp[idx].cpu()
+        routed = self.out_routed[idx].cpu() if self.record_routing else None
         for j, s in enumerate(done_slots):
             r = self.running.pop(s)
             n = int(gen[s])
@@ -538,7 +570,12 @@ class RolloutEngine:
                 reason = "completed"
             else:
                 reason = "length"
-            self.finished.append(RequestOutput(r.rid, r.prompt, t, lps[j, :n].tolist() if r.params.logprobs else None, reason))
+            extra = {}
+            if routed is not None:
+                # prompt tokens, then every generated token that was fed back (all but the last one)
+                extra["routed_experts"] = torch.cat([r.routed_prompt, routed[j, : max(n - 1, 0)]], 0)
+            self.finished.append(RequestOutput(r.rid, r.prompt, t, lps[j, :n].tolist() if r.params.logprobs else None, reason,
+                                               extra_fields=extra))
             self.stats["generated_tokens"] += n
             self._release_blocks(r.blocks)
             self.free_slots.append(s)
