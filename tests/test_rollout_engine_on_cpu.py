@@ -140,3 +140,23 @@ def test_stop_tokens_and_repetition_penalty():
     # penalty 1.0 alongside: unchanged output for that request
     again = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12))[0]
     assert again.token_ids == base.token_ids
+
+
+def test_prometheus_export_of_engine_counters():
+    from prometheus_client import generate_latest
+
+    from verl_b200.workers.rollout.metrics import RolloutMetricsExporter
+
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    eng = RolloutEngine(cfg, P, max_num_seqs=4, max_model_len=64, block_size=4, eos_token_id=-1)
+    exp = RolloutMetricsExporter(replica="3")
+    eng.generate([[5, 6, 7], [8, 9]], SamplingParams(temperature=0.0, max_tokens=5))
+    exp.update(eng)
+    eng.generate([[5, 6, 7]], SamplingParams(temperature=0.0, max_tokens=4))
+    exp.update(eng)
+    text = generate_latest(exp.registry).decode()
+    assert 'verl_rollout_generated_tokens_total{replica="3"} 14.0' in text
+    assert 'verl_rollout_prefill_tokens_total{replica="3"} 8.0' in text
+    assert 'verl_rollout_running_requests{replica="3"} 0.0' in text and 'verl_rollout_kv_usage{replica="3"} 0.0' in text
