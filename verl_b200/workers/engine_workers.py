@@ -338,6 +338,13 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                                          valid_vocab_size=rc.engine_kwargs.get("valid_vocab_size", 0))
             if rc.free_cache_engine:
                 self.rollout.release_kv_cache()
+            prom = rc.prometheus or {}
+            self._rollout_metrics = None
+            if (prom.get("enable") if hasattr(prom, "get") else getattr(prom, "enable", False)):
+                from .rollout.metrics import RolloutMetricsExporter
+
+                port = (prom.get("port") if hasattr(prom, "get") else getattr(prom, "port", None))
+                self._rollout_metrics = RolloutMetricsExporter(replica=str(self.rank), port=(int(port) + self.rank) if port else None)
 
     # ------------------------------------------------------------------ rollout
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
@@ -390,6 +397,8 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         full_ids = torch.cat([ids, resp], dim=1)
         full_mask = torch.cat([prompts.batch["attention_mask"], resp_mask.to(prompts.batch["attention_mask"].dtype)], dim=1)
         pos = VF.compute_position_id_with_mask(full_mask)
+        if getattr(self, "_rollout_metrics", None) is not None:
+            self._rollout_metrics.update(self.rollout)
         if rc.free_cache_engine:
             self.rollout.release_kv_cache()
         tensors = {"prompts": ids, "responses": resp, "input_ids": full_ids, "attention_mask": full_mask,
