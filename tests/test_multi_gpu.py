@@ -94,6 +94,20 @@ def _worker_body(rank, world, port, queue):
     res["gemm_ar_err"] = max(errs)
     res["gemm_ar_identical"] = all(same)
     res["gemm_status"] = int(ops.gemm_status())
+    # ---- weight stored in row blocks on the ranks, read in place by the GEMM (no gather)
+    from verl_b200.parallel.symmetric import PeerShardedLinear
+
+    g = torch.Generator(device="cpu").manual_seed(90)
+    w_full = (torch.randn(1024, 512, generator=g) * 0.05).bfloat16()
+    bias_p = torch.randn(1024, generator=g).bfloat16()
+    psl = PeerShardedLinear(1024, 512, dev)
+    psl.load_shard(w_full[rank * 512:(rank + 1) * 512].to(dev))
+    psl.barrier()
+    xs = torch.randn(300 + 17 * rank, 512, generator=g).bfloat16().to(dev)   # every rank has its own tokens
+    yp = psl(xs, bias_p.to(dev))
+    refp = xs.float().cpu() @ w_full.float().t() + bias_p.float()
+    res["peer_b_err"] = ((yp.float().cpu() - refp).norm() / refp.norm()).item()
+    psl.barrier()
     # ---- expert-parallel MoE layer (dispatch / combine over peer memory) against the single-GPU layer
     from verl_b200.models import DecoderModel, FlatParams
     from verl_b200.parallel.expert_parallel import ExpertParallelMoE
@@ -202,6 +216,7 @@ def test_two_rank_fused_optimizer_and_peer_collectives():
         assert res["ep_err"] < 2e-2 and res["ep_repeat_equal"] and res["ep_dropped"] == 0 and res["ep_status"] == 0, res
         assert res["gemm_ar_err"] < 1e-2 and res["gemm_ar_identical"] and res["gemm_status"] == 0, res
         assert res["gemm_ar_splitk_used"] > 1, res   # the decode-sized case went through the K-split path
+        assert res["peer_b_err"] < 1e-2, res
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
         assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res

@@ -507,6 +507,28 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   return d;
 }
 
+// D = a @ B^T (+ bias) where B's row blocks [rows_per_rank, K] (K-major, contiguous) live on the ranks of a group and are read
+// in place over NVLink; b_ptrs: int64 CPU tensor with every rank's block address (peer-mapped on this device).
+Tensor gemm_peer_b(const Tensor& a, const Tensor& b_ptrs, int64_t rows_per_rank, const OptTensor& bias, const OptTensor& out) {
+  CHECK_BF16(a);
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1, "gemm_peer_b: K-major 2-D activation");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), K = a.size(1), world = b_ptrs.numel(), N = world * rows_per_rank;
+  Tensor d = out.has_value() ? *out : at::empty({M, N}, a.options());
+  TORCH_CHECK(d.scalar_type() == at::kBFloat16 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_peer_b: bad out");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm_peer_b: bad bias");
+    bias_ptr = bias->data_ptr();
+  }
+  if (M == 0) return d;
+  count(1);
+  const int rc = vb_gemm_bf16_peer_b(a.data_ptr(), uptr(b_ptrs), d.data_ptr(), bias_ptr, (int)M, (int)K, a.stride(0), K, d.stride(0),
+                                     (int)world, (int)rows_per_rank, cur_stream());
+  TORCH_CHECK(rc == 0, "vb_gemm_bf16_peer_b failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+  return d;
+}
+
 int64_t comm_status() { return vb_comm_status(); }
 
 // ---- fp8 (e4m3) with 1x128 block scales
@@ -745,6 +767,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("adamw_allgather_", &adamw_allgather_);
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
+  m.def("gemm_peer_b", &gemm_peer_b);
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);

@@ -76,6 +76,9 @@ struct GemmParams {
   const int* grp_seg_start;  // [E + 1]
   int grp_b_rows;            // rows one expert occupies in the stacked 2-D view of B
   int grp_E;
+  // peer-sharded B (weights split by rows over the ranks of a group, read in place over NVLink): rank r owns rows
+  // [r * peer_rows, (r + 1) * peer_rows) of B and has its own tensor map
+  int peer_rows, peer_world;
 };
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
@@ -102,10 +105,11 @@ struct GemmSmem {
   static constexpr int TOTAL = RING + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+// Kernel body. ``tma_bs`` holds one tensor map of B (PEERS == 1) or one per rank of a group whose members each store a
+// row block of B (PEERS > 1): the producer then fetches every B tile from the memory of the rank that owns it.
+template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI, int PEERS>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap* tma_bs, const GemmParams& p) {
+  const CUtensorMap& tma_b = tma_bs[0];
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int A_BYTES = GemmSmem<BN, STAGES>::A_BYTES;
@@ -134,6 +138,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if constexpr (PEERS > 1) {
+      for (int r = 1; r < p.peer_world; ++r) tma_prefetch_desc(&tma_bs[r]);
+    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -219,7 +226,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tma_a, &full_bar[stage], m0 + 64 * j, k0);
           }
-          if constexpr (!B_MN) {
+          if constexpr (PEERS > 1) {
+            const int owner = n0 / p.peer_rows;  // a tile never straddles two owners: peer_rows % BN == 0
+            tma_load_2d(sb, &tma_bs[owner], &full_bar[stage], k0, n0 - owner * p.peer_rows);
+          } else if constexpr (!B_MN) {
             tma_load_2d(sb, &tma_b, &full_bar[stage], k0, b_off + n0);
           } else {
 #pragma unroll
@@ -559,6 +569,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
+template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, STAGES, EPI, 1>(tma_a, &tma_b, p);
+}
+
+struct PeerMaps {
+  CUtensorMap m[AR_MAX_RANKS];
+};
+
+// D = A * B^T with B's row blocks living on the ranks of a group (sharded weights, no gather): K-major operands.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_peer_b_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ PeerMaps maps, const GemmParams p) {
+  gemm_body<BN, false, false, STAGES, EPI_STORE, AR_MAX_RANKS>(tma_a, maps.m, p);
+}
+
 // Device address of the status word, resolved once (outside any stream capture).
 static int* status_ptr() {
   static int* p = nullptr;
@@ -844,6 +872,64 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
   if (wide) e = launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   else e = launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   return static_cast<int>(e);
+}
+
+// D[M, N] = A[M, K] * B^T (+ bias) where B [N, K] is stored in row blocks of ``rows_per_rank`` on the ranks of a group and
+// read in place from their memory (TMA loads over NVLink, no all-gather): b_ptrs[r] = rank r's block (peer-mapped).
+// rows_per_rank must be a multiple of the tile width (256, or 128 when N <= 128 * world); N = world * rows_per_rank.
+extern "C" int vb_gemm_bf16_peer_b(const void* A, const unsigned long long* b_ptrs, void* D, const void* bias, int M, int K,
+                                   long long lda, long long ldb, long long ldd, int world, int rows_per_rank,
+                                   cudaStream_t stream) {
+  const int N = world * rows_per_rank;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -1;
+  if (world < 1 || world > AR_MAX_RANKS) return -4;
+  const bool wide = rows_per_rank % 256 == 0;
+  const int BN = wide ? 256 : 128;
+  if (rows_per_rank % BN) return -6;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
+  CUtensorMap ta;
+  PeerMaps maps{};
+  if (!make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  for (int r = 0; r < world; ++r) {
+    if (b_ptrs[r] & 15) return -2;
+    if (!make_tmap_2d(&maps.m[r], reinterpret_cast<const void*>(b_ptrs[r]), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, ldb,
+                      BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+      return -3;
+  }
+  for (int r = world; r < AR_MAX_RANKS; ++r) maps.m[r] = maps.m[0];
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.status = status_ptr();
+  p.k_splits = 1;
+  p.peer_rows = rows_per_rank; p.peer_world = world;
+  const int sms = num_sms();
+  const int tiles = ((M + BM - 1) / BM) * (N / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  cudaError_t e;
+  if (wide) {
+    auto kern = gemm_bf16_peer_b_kernel<256, 4>;
+    constexpr int smem = GemmSmem<256, 4>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, maps, p);
+  } else {
+    auto kern = gemm_bf16_peer_b_kernel<128, 6>;
+    constexpr int smem = GemmSmem<128, 6>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, maps, p);
+  }
+  return static_cast<int>(cudaGetLastError());
 }
 
 // Decode-sized variant of the row-parallel linear: the GEMM runs K-split over all SMs into ``splitk_ws``

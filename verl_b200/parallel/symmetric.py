@@ -104,3 +104,34 @@ class FusedRowParallelLinear:
         assert a.shape[0] <= self.max_rows and b.shape[0] == self.n
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
                                            self.splitk_ws)
+
+
+class PeerShardedLinear:
+    """Linear layer whose weight [N, K] is stored in equal row blocks on the ranks of a group (1 / world of the bytes per
+    GPU) and never gathered: the GEMM kernel fetches every weight tile by TMA from the memory of the rank that owns it,
+    over NVLink, while the tensor cores work on the previous tile. Every rank computes the full ``x @ W^T`` for its own
+    tokens. This is the parameter all-gather of a fully sharded layout folded into the consuming GEMM.
+
+    ``load_shard`` stores this rank's rows; call ``barrier()`` (or any collective) after a weight update so that no
+    rank reads rows that a peer is still writing."""
+
+    def __init__(self, n: int, k: int, device, group=None, dtype=torch.bfloat16):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        assert n % self.world == 0 and (n // self.world) % 128 == 0 and k % 8 == 0, "row blocks must be multiples of 128 rows"
+        self.n, self.k, self.rows = int(n), int(k), int(n) // self.world
+        self.buf = SymmetricBuffer.allocate(self.rows * self.k, dtype, device, group, zero=True)
+        self.shard = self.buf.tensor.view(self.rows, self.k)
+        self._barrier = PeerBarrier(device, group)
+
+    def load_shard(self, rows: torch.Tensor) -> None:
+        self.shard.copy_(rows)
+
+    def barrier(self) -> None:
+        self._barrier()
+
+    def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from ..ops import native
+
+        assert x.shape[-1] == self.k
+        return native.ops().gemm_peer_b(x, self.buf.ptrs, self.rows, bias, out)
