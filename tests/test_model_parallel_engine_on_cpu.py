@@ -112,6 +112,17 @@ def test_pipeline_schedules_with_more_micro_batches_than_stages(world, pp, mbs, 
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), ref_lp, atol=1e-4), r
 
 
+def test_tensor_parallel_with_per_head_norms_matches_unsharded():
+    """Qwen3-style q/k norms are applied per head: under tensor parallelism every rank sees a subset of the heads, so the
+    gradients of these (replicated) weights are partial sums that must be completed over the group."""
+    ref_norm, ref_lp, ref_flat = _reference("tiny-qwen3")
+    res = _run(2, 2, 1, preset="tiny-qwen3")
+    for r in range(2):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+
+
 def test_expert_parallel_engine_matches_unsharded():
     """Two ranks, each with half of the experts and half of the batch: same gradient norm, same updated full model and the
     same log-probs as one process that holds every expert and sees the whole batch."""

@@ -230,6 +230,8 @@ PRESETS: dict[str, ModelConfig] = {
                                   num_attention_heads=4, num_key_value_heads=2, num_experts=8, num_experts_per_tok=2,
                                   moe_intermediate_size=64, shared_expert_intermediate_size=128, norm_topk_prob=False,
                                   eos_token_id=2, pad_token_id=0),
+    "tiny-qwen3": ModelConfig(model_type="qwen3", vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                              num_attention_heads=4, num_key_value_heads=2, head_dim=32, eos_token_id=2, pad_token_id=0),
     "tiny-llama": ModelConfig(model_type="llama", vocab_size=512, hidden_size=128, intermediate_size=256,
                               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, eos_token_id=2,
                               pad_token_id=0),

@@ -275,6 +275,29 @@ class ModelParallelEngine(NativeEngine):
         return super()._forward_micro(mb, R, temperature, calc_entropy, need_grad)
 
     # ------------------------------------------------------------------------------------ optimizer
+    def _partial_grad_ranges(self) -> list:
+        """(offset, numel) of replicated tensors whose gradient is a partial sum on every tensor-parallel rank: the
+        per-head q / k norms (each rank sees its own heads)."""
+        if getattr(self, "_partial_ranges", None) is None:
+            names = [m.local_name for m in self.maps if m.kind == "rep" and m.local_name.endswith(("self_attn.q_norm.weight",
+                                                                                                   "self_attn.k_norm.weight"))]
+            self._partial_ranges = [(self.params.offsets[n], self.params.views[n].numel()) for n in names]
+        return self._partial_ranges
+
+    def _complete_partial_grads(self) -> None:
+        if self.topo.tp == 1 or self.tparams.main_grad is None:
+            return
+        ranges = self._partial_grad_ranges()
+        if not ranges:
+            return
+        mg = self.tparams.main_grad
+        buf = torch.cat([mg[o : o + n] for o, n in ranges])
+        dist.all_reduce(buf, group=self.topo.tp_group)
+        off = 0
+        for o, n in ranges:
+            mg[o : o + n].copy_(buf[off : off + n])
+            off += n
+
     def _global_sumsq_correction(self) -> None:
         """``ctrl[0]`` holds the sum of squares of this rank's gradient shard over its DP group. Turn it into the model's
         global value: replicated tensors are counted on tensor-parallel rank 0 only, then summed over TP x PP."""

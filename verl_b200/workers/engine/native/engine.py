@@ -530,6 +530,11 @@ class NativeEngine(BaseEngine):
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         self.grad_shard = self.tparams.main_grad[sl] if self.sh_world == 1 else torch.zeros_like(self.master)
 
+    def _complete_partial_grads(self) -> None:
+        """Hook for model-parallel engines: gradients of replicated parameters that every rank of a model-parallel group
+        computed from its own part of the work (heads, tokens) are summed over that group before the optimizer sees them."""
+        return None
+
     def _global_sumsq_correction(self) -> None:
         """Hook for model-parallel engines: ``ctrl[0]`` (sum of squared gradients over the data-parallel group) becomes
         the sum over the whole model."""
@@ -550,6 +555,7 @@ class NativeEngine(BaseEngine):
         W = self.world
         mg = self.tparams.main_grad
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        self._complete_partial_grads()
         if self.fused_comm:
             return self._fused_optimizer_step()
         D, n_sh = self.dense_numel, self.shard_numel
