@@ -14,7 +14,7 @@ def _data(seed=0, b=4, L=24, R=16, V=500):
     return {"input_ids": ids, "attention_mask": am, "responses": ids[:, -R:], "response_mask": am[:, -R:]}
 
 
-def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b"):
+def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                           VERL_ENGINE_DEVICE="cpu")
@@ -30,6 +30,7 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedu
         ec = McoreEngineConfig(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp, expert_model_parallel_size=ep, seed=7,
                                micro_batch_size_per_gpu=mbs if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
         object.__setattr__(ec, "pipeline_schedule", schedule)
+        object.__setattr__(ec, "sequence_parallel", sp)
         eng = EngineRegistry.new("language_model", "megatron", get_preset(preset), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
         eng.initialize()
         dp = eng.topo.dp
@@ -50,7 +51,7 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedu
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b"):
+def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False):
     import torch.multiprocessing as mp
 
     with socket.socket() as s:
@@ -58,7 +59,7 @@ def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b"):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset, mbs, schedule)) for r in range(world)]
+    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset, mbs, schedule, sp)) for r in range(world)]
     for p in ps:
         p.start()
     res = dict(q.get(timeout=300) for _ in range(world))
@@ -110,6 +111,21 @@ def test_pipeline_schedules_with_more_micro_batches_than_stages(world, pp, mbs, 
         got = torch.from_numpy(res[r]["full"])
         assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), ref_lp, atol=1e-4), r
+
+
+@pytest.mark.parametrize("world,tp,pp,preset", [(2, 2, 1, "tiny-llama"), (2, 2, 1, "tiny-qwen3"), (4, 2, 2, "tiny-llama")])
+def test_sequence_parallel_inside_tensor_parallel_matches_unsharded(world, tp, pp, preset):
+    """Token-sliced residual stream (all-gather / reduce-scatter around the projections); the packed batch has a token
+    count that is not a multiple of the group size, so the padded tail is exercised too."""
+    ref_norm, ref_lp, ref_flat = _reference(preset)
+    res = _run(world, tp, pp, preset=preset, sp=True)
+    dp = res[0]["dp"]
+    rows = ref_lp.chunk(dp)
+    for r in range(world):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r // (tp * pp)], atol=1e-4), r
 
 
 def test_tensor_parallel_with_per_head_norms_matches_unsharded():

@@ -31,7 +31,7 @@ from ..ops import functional as F
 from .config import ModelConfig
 from .weights import FlatParams
 
-__all__ = ["PackedBatch", "DecoderModel", "RouterReplay", "ExpertParallelGroup", "UlyssesSequenceParallel"]
+__all__ = ["PackedBatch", "DecoderModel", "RouterReplay", "ExpertParallelGroup", "UlyssesSequenceParallel", "TensorSequenceParallel"]
 
 
 @dataclass
@@ -137,6 +137,61 @@ class UlyssesSequenceParallel:
         return recv.permute(1, 0, 2, 3).reshape(tl, self.size * hs, d)
 
 
+class TensorSequenceParallel:
+    """Sequence parallelism inside a tensor-parallel group (Megatron style): the residual stream, the norms and everything
+    else that is token-wise live on a 1 / size slice of the (padded) token stream; an all-gather in front of every
+    column-parallel projection and a reduce-scatter behind every row-parallel one replace the all-reduce of plain tensor
+    parallelism (same bytes on the wire, 1 / size of the activation memory between the blocks).
+
+    Parity target: Megatron sequence parallelism as enabled by ``verl/workers/config/engine.py`` (``McoreEngineConfig``:
+    on whenever tensor parallelism is) and ``verl/utils/megatron/sequence_parallel.py:29`` (padding)."""
+
+    def __init__(self, group, rank: int, size: int):
+        self.group, self.rank, self.size = group, int(rank), int(size)
+
+    def local_rows(self, total: int) -> int:
+        return (int(total) + self.size - 1) // self.size
+
+    def slice(self, x: torch.Tensor) -> torch.Tensor:
+        """Rows of this rank out of a full [T, ...] tensor (zero rows where the padded stream runs past T)."""
+        n = self.local_rows(x.shape[0])
+        lo = self.rank * n
+        part = x[lo : lo + n]
+        if part.shape[0] == n:
+            return part.contiguous()
+        out = torch.zeros(n, *x.shape[1:], dtype=x.dtype, device=x.device)
+        out[: part.shape[0]] = part
+        return out
+
+    def gather(self, x_local: torch.Tensor, total: int) -> torch.Tensor:
+        import torch.distributed as dist
+
+        n = x_local.shape[0]
+        full = torch.empty(n * self.size, *x_local.shape[1:], dtype=x_local.dtype, device=x_local.device)
+        if x_local.is_cuda:
+            dist.all_gather_into_tensor(full, x_local.contiguous(), group=self.group)
+        else:
+            dist.all_gather(list(full.split(n)), x_local.contiguous(), group=self.group)
+        return full[:total]
+
+    def scatter_sum(self, x_full: torch.Tensor) -> torch.Tensor:
+        """Sum of every rank's [T, H] over the group, of which this rank keeps its rows."""
+        import torch.distributed as dist
+
+        T = x_full.shape[0]
+        n = self.local_rows(T)
+        if n * self.size != T:
+            pad = torch.zeros(n * self.size - T, *x_full.shape[1:], dtype=x_full.dtype, device=x_full.device)
+            x_full = torch.cat([x_full, pad])
+        if x_full.is_cuda:
+            out = torch.empty(n, *x_full.shape[1:], dtype=x_full.dtype, device=x_full.device)
+            dist.reduce_scatter_tensor(out, x_full.contiguous(), group=self.group)
+            return out
+        x_full = x_full.contiguous().clone()
+        dist.all_reduce(x_full, group=self.group)  # gloo has no reduce-scatter
+        return x_full[self.rank * n : (self.rank + 1) * n].contiguous()
+
+
 class ExpertParallelGroup:
     """Expert parallelism for training: ``size`` data-parallel ranks (each with its own tokens) store ``E / size`` experts
     each. A layer sends every routed token copy to the owner of its expert, runs the owner's experts, and sends the
@@ -208,6 +263,7 @@ class DecoderModel:
         self.mlp_tile_tokens = 0                            # > 0: sequence-tiled dense MLP (tokens per tile)
         self.router_replay: Optional[RouterReplay] = None   # record / replay the experts every router picks
         self._layer_idx = 0
+        self.tsp: Optional[TensorSequenceParallel] = None   # token-sliced residual stream inside a tensor-parallel group
         self.ep: Optional[ExpertParallelGroup] = None       # expert parallelism (this model stores E / size experts)
         self.sp: Optional[UlyssesSequenceParallel] = None  # sequence parallelism (token-wise layers on a slice of the stream)
         self.cfg = cfg
@@ -808,9 +864,12 @@ class DecoderModel:
         self._layer_idx = i
         eps = self.cfg.rms_norm_eps
         h1, x, rstd1 = F.rms_norm(a, W["input_layernorm.weight"], eps, residual=r)
-        o = self._attn_fwd(W, h1, batch, S, i)
+        tsp, T = self.tsp, batch.num_tokens
+        # sequence parallelism: the projections see every token (gathered), their row-parallel outputs come back
+        # reduce-scattered (``tp_reduce``), norms and residuals stay on this rank's slice
+        o = self._attn_fwd(W, h1 if tsp is None else tsp.gather(h1, T), batch, S, i)
         h2, x2, rstd2 = F.rms_norm(o, W["post_attention_layernorm.weight"], eps, residual=x)
-        d = self._mlp_fwd(W, h2, S)
+        d = self._mlp_fwd(W, h2 if tsp is None else tsp.gather(h2, T), S)
         if self.stats_hook is not None:  # precision debugging: per-layer tensor statistics
             self.stats_hook(f"layers.{i}.attn_out", o)
             self.stats_hook(f"layers.{i}.mlp_out", d)
@@ -824,11 +883,13 @@ class DecoderModel:
         W = self.params.layer(i)
         eps = self.cfg.rms_norm_eps
         w1, w2 = W["input_layernorm.weight"], W["post_attention_layernorm.weight"]
+        tsp, T = self.tsp, batch.num_tokens
+        full = (lambda t: t) if tsp is None else (lambda t: tsp.gather(t, T))  # gradient of a reduce-scatter = all-gather
         h2 = F.rms_norm(S["x2"], w2, eps)[0]
-        g_h2 = self._mlp_bwd(W, g_d, h2, S)
+        g_h2 = self._mlp_bwd(W, full(g_d), full(h2), S)
         g_x2t = F.rms_norm_bwd(g_h2, S["x2"], w2, S["rstd2"], g_x2, self._grad_of(w2), True)
         h1 = F.rms_norm(S["x"], w1, eps)[0]
-        g_h1 = self._attn_bwd(W, g_x2t, h1, batch, S)
+        g_h1 = self._attn_bwd(W, full(g_x2t), full(h1), batch, S)
         g_x = F.rms_norm_bwd(g_h1, S["x"], w1, S["rstd1"], g_x2t, self._grad_of(w1), True)
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(i)
@@ -862,6 +923,8 @@ class DecoderModel:
         if cfg.has_embedding:
             ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
             a = F.embedding(ids, self.params["embed_tokens.weight"])
+            if self.tsp is not None:
+                a = self.tsp.slice(a)
         else:
             a = stage_input  # hidden stream handed over by the previous pipeline stage
             assert a is not None, "a pipeline stage without embedding needs stage_input"
@@ -884,6 +947,8 @@ class DecoderModel:
             out = a if r is None else a + r
             return out, (dict(batch=batch, layers=saved, boundary=True) if save else None)
         hN, xN, rstdN = F.rms_norm(a, self.params["norm.weight"], cfg.rms_norm_eps, residual=r)
+        if self.tsp is not None:
+            hN = self.tsp.gather(hN, batch.num_tokens)  # the heads see every token
         state = dict(batch=batch, layers=saved, xN=xN, rstdN=rstdN, hN=hN) if save else None
         return hN, state
 
@@ -896,6 +961,8 @@ class DecoderModel:
             g = g_hN
         else:
             wn = self.params["norm.weight"]
+            if self.tsp is not None:
+                g_hN = self.tsp.slice(g_hN)  # every rank of the group holds the same head-input gradient
             g = F.rms_norm_bwd(g_hN, state["xN"], wn, state["rstdN"], None, self._grad_of(wn), True)
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(cfg.num_hidden_layers)
@@ -923,6 +990,8 @@ class DecoderModel:
             if self.pre_layer_hook is not None:
                 self.pre_layer_hook(-1, "backward")
             ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
+            if self.tsp is not None:
+                ids = self.tsp.slice(ids)  # padding rows carry a zero gradient
             F.embedding_bwd_(ids, g, emb.main_grad)
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(-1)

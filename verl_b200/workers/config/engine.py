@@ -77,6 +77,7 @@ class FSDPEngineConfig(EngineConfig):
 class McoreEngineConfig(EngineConfig):
     tensor_model_parallel_size: int = 1
     expert_model_parallel_size: int = 1
+    sequence_parallel: bool = False     # token-sliced residual stream inside the tensor-parallel group
     pipeline_schedule: str = "1f1b"   # 1f1b | gpipe (all forwards, then all backwards)
     vocab_parallel_head: bool = True    # LM head rows split over the tensor-parallel group
     expert_tensor_parallel_size: Optional[int] = None

@@ -86,6 +86,14 @@ class ModelParallelEngine(NativeEngine):
                 return x
 
             self.model.tp_reduce = reduce
+            if bool(getattr(self.engine_config, "sequence_parallel", False)):
+                # token-sliced residual stream: reduce-scatter behind the row-parallel projections, all-gather in front of
+                # the column-parallel ones
+                from ....models.decoder import TensorSequenceParallel
+
+                assert not self.full_arch.is_moe, "sequence parallelism covers dense blocks"
+                self.model.tsp = TensorSequenceParallel(grp, self.topo.tp_rank, self.topo.tp)
+                self.model.tp_reduce = self.model.tsp.scatter_sum
         # replicated-parameter mask for the gradient norm (embedding, norms, head, biases of row-parallel layers)
         self._rep_ranges = [(self.params.offsets[m.local_name], self.params.views[m.local_name].numel())
                             for m in self.maps if m.kind == "rep"]
@@ -159,7 +167,8 @@ class ModelParallelEngine(NativeEngine):
         need_grad = not forward_only and loss_function is not None
         first, last = topo.is_first_stage, topo.is_last_stage
         packed = [pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R) for mb in mbs]
-        Ts = [p[0].num_tokens for p in packed]
+        tsp = self.model.tsp
+        Ts = [p[0].num_tokens if tsp is None else tsp.local_rows(p[0].num_tokens) for p in packed]  # rows of a boundary tensor
         M = len(mbs)
         rows: list[int] = [r for mb in mbs for r in mb["_rows"]]
         losses, metrics = [], {}
@@ -279,8 +288,10 @@ class ModelParallelEngine(NativeEngine):
         """(offset, numel) of replicated tensors whose gradient is a partial sum on every tensor-parallel rank: the
         per-head q / k norms (each rank sees its own heads)."""
         if getattr(self, "_partial_ranges", None) is None:
-            names = [m.local_name for m in self.maps if m.kind == "rep" and m.local_name.endswith(("self_attn.q_norm.weight",
-                                                                                                   "self_attn.k_norm.weight"))]
+            partial = ("self_attn.q_norm.weight", "self_attn.k_norm.weight")
+            if self.model.tsp is not None:  # token-wise parameters see this rank's tokens only
+                partial += ("layernorm.weight", "norm.weight", "embed_tokens.weight")
+            names = [m.local_name for m in self.maps if m.kind == "rep" and m.local_name.endswith(partial)]
             self._partial_ranges = [(self.params.offsets[n], self.params.views[n].numel()) for n in names]
         return self._partial_ranges
 
