@@ -266,6 +266,10 @@ class NativeEngine(BaseEngine):
         # memory (4 bytes/param) is available to the rollout KV cache in between.
         self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
         if not self.forward_only:
+            opt_name = str(getattr(self.optimizer_config, "optimizer", "AdamW") or "AdamW")
+            if opt_name.lower() not in ("adamw", "adam", "fusedadam", "fused_adamw"):
+                raise NotImplementedError(f"optimizer {opt_name!r}: this engine implements the sharded fused AdamW only "
+                                          f"(decoupled weight decay; weight_decay=0 gives Adam)")
             self.master = self._owned(self.tparams.flat).float()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
