@@ -160,3 +160,23 @@ def test_prometheus_export_of_engine_counters():
     assert 'verl_rollout_generated_tokens_total{replica="3"} 14.0' in text
     assert 'verl_rollout_prefill_tokens_total{replica="3"} 8.0' in text
     assert 'verl_rollout_running_requests{replica="3"} 0.0' in text and 'verl_rollout_kv_usage{replica="3"} 0.0' in text
+
+
+def test_prefill_decode_disaggregation_matches_a_single_engine():
+    from verl_b200.workers.rollout.pd_disaggregation import DisaggregationConfig, PrefillDecodeRollout
+
+    torch.manual_seed(0)
+    cfg = get_preset("tiny-qwen2")
+    P = FlatParams(cfg, dtype=torch.float32)
+    P.init_weights(seed=3, std=0.1)
+    prompts = [[5, 6, 7, 8, 9, 10, 11], [20, 21, 22], [30, 31, 32, 33, 34], [5, 6, 7, 8, 9, 10, 11]]
+    sp = SamplingParams(temperature=1.0, max_tokens=7)
+    mk = lambda: RolloutEngine(cfg, P, max_num_seqs=4, max_model_len=64, block_size=4, eos_token_id=-1, seed=0)
+    ref = mk().generate(prompts, sp)
+    pd = PrefillDecodeRollout(mk(), mk(), DisaggregationConfig(enable=True, prefill_chunk=3))
+    out = pd.generate(prompts, sp)
+    for a, b in zip(out, ref):
+        assert a.token_ids == b.token_ids and max(abs(x - y) for x, y in zip(a.log_probs, b.log_probs)) < 1e-5
+    assert pd.stats["handoffs"] == 4 and pd.stats["kv_bytes_transferred"] > 0
+    for eng in (pd.prefill, pd.decode):   # both stages gave every block and slot back
+        assert sorted(eng.free_blocks) == list(range(eng.num_blocks)) and len(eng.free_slots) == eng.S

@@ -417,9 +417,15 @@ def sample_tokens(logits: torch.Tensor, temperature: float, seeds: torch.Tensor,
         sx = sx.masked_fill(drop, float("-inf"))
         x = torch.full_like(x, float("-inf")).scatter(1, si, sx)
     lp = torch.log_softmax(x, -1)
-    gen = torch.Generator(device=x.device)
-    gen.manual_seed((int(seeds[0].item()) * 1000003 + int(step)) % (2**63 - 1))
-    tok = torch.multinomial(lp.exp(), 1, generator=gen).squeeze(-1)
+    # one random stream per row, keyed by that row's seed (as in the device kernel): what a request samples does not depend
+    # on which other requests share its batch
+    gen = torch.Generator(device="cpu")
+    toks = []
+    for i, sd in enumerate(seeds.tolist()):
+        gen.manual_seed((int(sd) * 1000003 + int(step)) % (2**63 - 1))
+        u = torch.rand(lp.shape[1], generator=gen).clamp_(min=1e-20).to(lp.device)
+        toks.append(torch.argmax(lp[i] - torch.log(-torch.log(u))))   # Gumbel-max
+    tok = torch.stack(toks)
     return tok, lp.gather(-1, tok.unsqueeze(-1)).squeeze(-1)
 
 

@@ -76,6 +76,7 @@ class _Request:
     slot: int = -1
     blocks: list[int] = field(default_factory=list)
     arrival: float = 0.0
+    handoff: Optional[dict] = None  # prefilled elsewhere: KV content, first token and sampler state arrive with the request
 
 
 class RolloutEngine:
@@ -304,8 +305,100 @@ class RolloutEngine:
             tokens += len(r.prompt)
         return batch
 
+    # ------------------------------------------------------------------------------------ prefill / decode disaggregation
+    @torch.no_grad()
+    def prefill_only(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams]) -> list[dict]:
+        """Prefill stage of a disaggregated deployment: run the prompts, sample the first token, and hand back per prompt
+        what a decode engine needs to continue (``add_prefilled``): the KV content of the prompt's pages, the first token
+        with its log-prob and the sampler state. Nothing stays allocated here afterwards."""
+        plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        assert not self.running and not self.waiting, "prefill_only needs an idle engine"
+        self._ensure_out(max(p.max_tokens for p in plist))
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        out: dict[str, dict] = {}
+        while self.waiting:
+            reqs = self._admit()
+            assert reqs, "a prompt does not fit the prefill engine's cache"
+            self._prefill(reqs)
+            for r in reqs:
+                nb = (len(r.prompt) + self.bs - 1) // self.bs
+                blk = torch.tensor(r.blocks[:nb], dtype=torch.int64, device=self.device)
+                out[r.rid] = dict(prompt=list(r.prompt), kv=self.kv[:, :, blk].clone(), token=int(self.tok[r.slot]),
+                                  logprob=float(self.out_lp[r.slot, 0]), seed=int(self.seeds[r.slot]), block_size=self.bs,
+                                  routed_prompt=getattr(r, "routed_prompt", None))
+            idx = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=self.device)
+            for r in reqs:
+                self.running.pop(r.slot)
+                self._release_blocks(r.blocks)
+                self.free_slots.append(r.slot)
+            self.active[idx] = False
+            self.ctx[idx] = 0
+        return [out[r] for r in rids]
+
+    def add_prefilled(self, handoff: dict, params: SamplingParams, request_id: Optional[str] = None) -> str:
+        """Decode stage: queue a request whose prompt was prefilled by another engine (same model, same block size)."""
+        assert handoff["block_size"] == self.bs, "prefill and decode engines must use the same KV block size"
+        rid = self.add_request(handoff["prompt"], params, request_id)
+        self.waiting[-1].handoff = handoff
+        return rid
+
+    @torch.no_grad()
+    def _install_prefilled(self, reqs: list[_Request]) -> None:
+        dev = self.device
+        lens = [len(r.prompt) for r in reqs]
+        bt_rows = torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            bt_rows[i, : len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
+            nb = (lens[i] + self.bs - 1) // self.bs
+            dst = torch.tensor(r.blocks[:nb], dtype=torch.int64, device=dev)
+            self.kv[:, :, dst] = r.handoff["kv"].to(dev, dtype=self.kv.dtype)   # the KV transfer (a peer copy between GPUs)
+            if self.record_routing:
+                r.routed_prompt = r.handoff.get("routed_prompt")
+        slots = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=dev)
+        tok = torch.tensor([r.handoff["token"] for r in reqs], dtype=torch.int64, device=dev)
+        lp = torch.tensor([r.handoff["logprob"] for r in reqs], dtype=torch.float32, device=dev)
+        stop_rows = torch.full((len(reqs), 8), -1, dtype=torch.int64)
+        for i, r in enumerate(reqs):
+            st = list(r.params.stop_token_ids or ())[:8]
+            if st:
+                stop_rows[i, : len(st)] = torch.tensor(st, dtype=torch.int64)
+        self.stop_ids[slots] = stop_rows.to(dev)
+        pens = [float(r.params.repetition_penalty or 1.0) for r in reqs]
+        if any(p != 1.0 for p in pens) and not self._use_penalty:
+            self.seen = torch.zeros(self.S, self.cfg.vocab_size, dtype=torch.bool, device=dev)
+            self._use_penalty, self._graph = True, None
+        self.rep_penalty[slots] = torch.tensor(pens, dtype=torch.float32, device=dev)
+        if self._use_penalty:
+            self.seen[slots] = False
+            for r in reqs:
+                self.seen[r.slot, torch.tensor(r.prompt + [r.handoff["token"]], dtype=torch.int64, device=dev)] = True
+        n = torch.tensor(lens, dtype=torch.int32, device=dev)
+        self.block_table[slots] = bt_rows.to(dev)
+        self.tok[slots] = tok
+        self.pos[slots] = n
+        self.ctx[slots] = n + 1
+        self.gen[slots] = 1
+        self.max_new[slots] = torch.tensor([r.params.max_tokens for r in reqs], dtype=torch.int32, device=dev)
+        self.ignore_eos[slots] = torch.tensor([r.params.ignore_eos for r in reqs], dtype=torch.bool, device=dev)
+        self.seeds[slots] = torch.tensor([r.handoff["seed"] for r in reqs], dtype=torch.int64, device=dev)
+        self.out_tok[slots, 0] = tok
+        self.out_lp[slots, 0] = lp
+        done = (self.gen[slots] >= self.max_new[slots])
+        if self.eos is not None:
+            done |= (tok == self.eos) & ~self.ignore_eos[slots]
+        done |= (tok.unsqueeze(1) == self.stop_ids[slots]).any(1)
+        self.active[slots] = ~done
+        for r in reqs:
+            self.running[r.slot] = r
+
     @torch.no_grad()
     def _prefill(self, reqs: list[_Request]) -> None:
+        hand = [r for r in reqs if r.handoff is not None]
+        if hand:
+            self._install_prefilled(hand)
+            reqs = [r for r in reqs if r.handoff is None]
+            if not reqs:
+                return
         t0 = time.time()
         dev = self.device
         lens = [len(r.prompt) for r in reqs]
