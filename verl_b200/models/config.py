@@ -12,7 +12,11 @@ import os
 from dataclasses import asdict, dataclass, field
 from typing import Any, Optional
 
-__all__ = ["ModelConfig", "PRESETS", "get_preset"]
+__all__ = ["ModelConfig", "PRESETS", "get_preset", "NATIVE_FAMILIES"]
+
+# architectures with a hand-scheduled decoder (own kernels, own backward, paged rollout engine); every other causal language
+# model of the ``transformers`` library runs through ``models/generic.py``
+NATIVE_FAMILIES = ("llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "qwen2_moe", "mixtral", "phi3")
 
 
 @dataclass
@@ -84,6 +88,11 @@ class ModelConfig:
         return self.num_experts > 0
 
     @property
+    def is_generic(self) -> bool:
+        """True for architectures that run as a library module under autograd (no hand-scheduled decoder)."""
+        return bool(self.extra.get("generic"))
+
+    @property
     def q_size(self) -> int:
         return self.num_attention_heads * self.head_dim
 
@@ -119,6 +128,8 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict[str, Any]) -> "ModelConfig":
         mt = d.get("model_type", "llama")
+        if mt not in NATIVE_FAMILIES:
+            return cls._generic_from_hf_dict(d)
         kw = dict(
             model_type=mt,
             vocab_size=d["vocab_size"],
@@ -148,11 +159,32 @@ class ModelConfig:
         return cfg
 
     @classmethod
+    def _generic_from_hf_dict(cls, d: dict[str, Any]) -> "ModelConfig":
+        """Description of an architecture outside ``NATIVE_FAMILIES``: the sizes the framework reports and plans with
+        (FLOPs estimate, token ids) are read leniently; the complete library configuration travels in ``extra``."""
+        t = d.get("text_config") if isinstance(d.get("text_config"), dict) else d
+        heads = t.get("num_attention_heads", 1)
+        eos = d.get("eos_token_id", t.get("eos_token_id"))
+        # latent attention (DeepSeek-V2/V3): the score width is nope + rope dims
+        head_dim = t.get("head_dim") or ((t.get("qk_nope_head_dim", 0) + t.get("qk_rope_head_dim", 0)) or None)
+        return cls(model_type=d.get("model_type"), vocab_size=t.get("vocab_size", d.get("vocab_size", 0)),
+                   hidden_size=t.get("hidden_size", 0), intermediate_size=t.get("intermediate_size", 0) or 0,
+                   num_hidden_layers=t.get("num_hidden_layers", 0), num_attention_heads=heads,
+                   num_key_value_heads=t.get("num_key_value_heads", heads) or heads, head_dim=head_dim,
+                   rms_norm_eps=t.get("rms_norm_eps", 1e-6), max_position_embeddings=t.get("max_position_embeddings", 32768),
+                   tie_word_embeddings=bool(d.get("tie_word_embeddings", t.get("tie_word_embeddings", False))),
+                   bos_token_id=d.get("bos_token_id", t.get("bos_token_id")), eos_token_id=eos[0] if isinstance(eos, list) else eos,
+                   pad_token_id=d.get("pad_token_id", t.get("pad_token_id")), initializer_range=t.get("initializer_range", 0.02),
+                   extra={"generic": True, "hf_config": dict(d), "_explicit": ("attention_bias",)})
+
+    @classmethod
     def from_pretrained(cls, path: str) -> "ModelConfig":
         with open(os.path.join(path, "config.json")) as f:
             return cls.from_hf_dict(json.load(f))
 
     def to_hf_dict(self) -> dict[str, Any]:
+        if self.is_generic:
+            return dict(self.extra["hf_config"])
         arch = {
             "qwen2": "Qwen2ForCausalLM",
             "qwen3": "Qwen3ForCausalLM",

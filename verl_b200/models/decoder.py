@@ -250,6 +250,8 @@ class DecoderModel:
                  pre_layer_hook: Optional[Callable[[int, str], None]] = None,
                  post_layer_backward_hook: Optional[Callable[[int], None]] = None):
         assert recompute in ("none", "full", "auto")
+        assert not cfg.is_generic, (f"model_type={cfg.model_type!r} has no hand-scheduled decoder: it runs through "
+                                    f"verl_b200.models.generic (training engine and its cache-based rollout)")
         self.keep_layers_fn: Optional[Callable[[int], int]] = None
         self.tp: Optional[TensorParallelShard] = None  # set by the rollout engine; forward-only
         self.fp8_weights: Optional[dict] = None         # data_ptr of a bf16 weight -> (e4m3 copy, block scales)

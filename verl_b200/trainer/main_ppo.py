@@ -80,7 +80,10 @@ class TaskRunner:
         if need_critic(config):
             self.add_critic_worker(config)
         path = config.actor_rollout_ref.model.path
-        tokenizer = hf_tokenizer(path, trust_remote_code=config.data.get("trust_remote_code", False)) if os.path.isdir(str(path)) else None
+        # a model directory that holds only a configuration (random-initialised runs on token-level data) has no tokenizer
+        has_tok = os.path.isdir(str(path)) and any(os.path.exists(os.path.join(str(path), f))
+                                                   for f in ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "vocab.json"))
+        tokenizer = hf_tokenizer(path, trust_remote_code=config.data.get("trust_remote_code", False)) if has_tok else None
         reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
         val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
         wg_cls, wg_kwargs = _select_worker_group(config)

@@ -50,6 +50,10 @@ class ModelParallelEngine(NativeEngine):
         self.pp_size = g("pipeline_model_parallel_size", 1)
         self.ep_size = g("expert_model_parallel_size", 1) if self.arch.is_moe else 1
         self.full_arch = self.arch
+        if self.arch.is_generic:
+            raise NotImplementedError(f"model_type={self.arch.model_type!r} runs as a library module: tensor / pipeline / expert "
+                                      f"parallel training covers the natively supported families; use the data-parallel engine "
+                                      f"(strategy fsdp) with its sharded optimizer for this one")
 
     # ------------------------------------------------------------------------------------ setup
     def initialize(self) -> None:

@@ -194,6 +194,7 @@ class NativeEngine(BaseEngine):
             self.params = self._shared_params
         else:
             want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
+                          and not self.arch.is_generic
                           and not int(getattr(self.model_config, "lora_rank", 0) or 0)
                           and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
                           and self.rep_world == 1
@@ -209,14 +210,29 @@ class NativeEngine(BaseEngine):
                     self._peer_barrier = PeerBarrier(self.device)
                     buf = self._sym_params.tensor
                     self.fused_comm = True
-            self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
-                                     pad_to=self.sh_world, buffer=buf)
+            if self.arch.is_generic:
+                # an architecture without a hand-scheduled decoder: a library module whose parameters live in the flat buffer
+                from ....models.generic import ModuleFlatParams
+
+                self.params = ModuleFlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
+                                               pad_to=self.sh_world, seed=seed,
+                                               attn_implementation=getattr(self.model_config, "attn_implementation", None))
+            else:
+                self.params = FlatParams(self.arch, dtype=self.dtype, device=self.device, value_head=self.value_head,
+                                         pad_to=self.sh_world, buffer=buf)
             self._load_or_init(seed)
         # gradient checkpointing: "auto" keeps the activations of as many trailing layers as free memory allows and
         # recomputes the rest (all of them when memory is short, none when everything fits)
         recompute = "none" if not getattr(ec, "enable_gradient_checkpointing", True) else \
             str(os.environ.get("VERL_B200_RECOMPUTE", getattr(ec, "recompute_granularity", None) or "auto"))
-        self.model = DecoderModel(self.arch, self.params, recompute=recompute)
+        if self.arch.is_generic:
+            from ....models.generic import GenericCausalLM
+
+            assert int(getattr(self.model_config, "lora_rank", 0) or 0) == 0 and int(getattr(ec, "ulysses_sequence_parallel_size", 1) or 1) == 1, \
+                "LoRA and sequence parallelism need one of the natively supported model families"
+            self.model = GenericCausalLM(self.arch, self.params, recompute=recompute)
+        else:
+            self.model = DecoderModel(self.arch, self.params, recompute=recompute)
         self.model.keep_layers_fn = self._layers_that_fit
         tm = getattr(self.model_config, "tiled_mlp", None) or {}
         if (tm.get("enabled") if hasattr(tm, "get") else getattr(tm, "enabled", False)):
@@ -250,7 +266,7 @@ class NativeEngine(BaseEngine):
             self.model.sp = UlyssesSequenceParallel(self.sp_group, self.sp_rank, self.sp_size)
         # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
         self._share_prefix = (bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
-                              and self.sp_size == 1)
+                              and self.sp_size == 1 and not self.arch.is_generic)
         if bool(getattr(ec, "enable_activation_offload", False)) and not self.forward_only:
             from ....utils.activation_offload import ActivationOffloader
 

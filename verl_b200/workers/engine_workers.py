@@ -323,11 +323,16 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             pool_ranks = dist.get_process_group_ranks(pool if pool is not None else dist.group.WORLD) if ws > 1 else [0]
             n_pool, me = len(pool_ranks), (pool_ranks.index(dist.get_rank()) if ws > 1 else 0)
             tp = int(rc.tensor_model_parallel_size or 1)
-            tp = tp if (n_pool > 1 and tp > 1 and n_pool % tp == 0 and not arch.is_moe and arch.num_key_value_heads % tp == 0) else 1
+            tp = tp if (n_pool > 1 and tp > 1 and n_pool % tp == 0 and not arch.is_moe and not arch.is_generic
+                        and arch.num_key_value_heads % tp == 0) else 1
             self.rollout_tp, self.rollout_tp_group = tp, None
             if tp > 1:  # only the members take part in creating their group
                 g0 = me // tp * tp
                 self.rollout_tp_group = dist.new_group(pool_ranks[g0 : g0 + tp], use_local_synchronization=True)
+            if arch.is_generic:
+                # no hand-scheduled decoder for this family: sampling runs on the library module with its key/value cache
+                from ..models.generic import GenericRolloutEngine as RolloutEngine
+
             self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs * tp, tp_group=self.rollout_tp_group,
                                          record_routing=(self._router_replay_mode() == "R3"),
                                          quantization=(rc.get("quantization") if tp == 1 else None),
