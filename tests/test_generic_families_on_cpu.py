@@ -253,3 +253,28 @@ def test_sharded_optimizer_over_two_ranks_matches_one_rank():
         assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm)
         n = ref.params.numel
         assert torch.allclose(torch.from_numpy(res[r]["flat"])[:n], ref.params.flat, atol=2e-5)
+
+
+def test_flops_estimates_follow_the_library_configuration():
+    from verl_b200.utils.flops_counter import FlopsCounter, _causal_pairs
+
+    v3 = dict(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, intermediate_size=18432, moe_intermediate_size=2048,
+              num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, n_shared_experts=1, n_routed_experts=256,
+              kv_lora_rank=512, q_lora_rank=1536, qk_rope_head_dim=64, v_head_dim=128, qk_nope_head_dim=128,
+              num_experts_per_tok=8, first_k_dense_replace=3)
+    fc = FlopsCounter(ModelConfig.from_hf_dict(v3))
+    active = fc._dense_per_token()
+    assert 35e9 < active < 39e9, active            # ~37 B activated parameters per token
+    # attention: 61 global layers, 128 heads, score width 192 and value width 128
+    assert fc._attention_forward_flops([1000]) == 2.0 * 61 * 128 * (192 + 128) * _causal_pairs(1000)
+
+    oss = dict(model_type="gpt_oss", vocab_size=201088, hidden_size=2880, intermediate_size=2880, num_hidden_layers=24,
+               num_attention_heads=64, num_key_value_heads=8, head_dim=64, num_local_experts=32, num_experts_per_tok=4,
+               sliding_window=128, layer_types=["sliding_attention", "full_attention"] * 12)
+    fo = FlopsCounter(ModelConfig.from_hf_dict(oss))
+    assert 2.5e9 < fo._dense_per_token() < 4.0e9   # ~3.6 B active of 21 B
+    long, short = fo._attention_forward_flops([4096]), fo._attention_forward_flops([128])
+    full_only = 2.0 * 24 * 64 * 128 * _causal_pairs(4096)
+    assert 0.5 * full_only < long < 0.55 * full_only     # half of the layers see at most 128 keys
+    assert short == 2.0 * 24 * 64 * 128 * _causal_pairs(128)
+    assert _causal_pairs(10, 4) == 10 + 9 + 9 + 6      # 1+2+3+4 then 4 per query

@@ -36,35 +36,98 @@ def get_device_flops(unit: str = "T") -> float:
     return flops / div
 
 
+def _causal_pairs(s: int, window: int = 0) -> float:
+    """Number of (query, key) pairs a causal layer evaluates for a sequence of ``s`` tokens; ``window`` > 0 limits every
+    query to its ``window`` most recent keys."""
+    if window <= 0 or s <= window:
+        return s * (s + 1) / 2.0
+    return window * (window + 1) / 2.0 + (s - window) * float(window)
+
+
+def _terms_from_hf(d: dict) -> tuple[float, list[tuple[int, int, float]]]:
+    """(multiply-accumulates per token in the projections, MLPs, routers and LM head; attention layer classes as
+    ``(layers, window, heads * (score width + value width))``) of a library configuration. Covers latent attention with
+    dense-then-sparse stacks (DeepSeek-V2/V3), sliding / full layer patterns (GPT-OSS, Gemma-2/3, Mistral) and plain
+    grouped-query decoders; unknown fields fall back to the dense decoder reading of the configuration."""
+    t = d.get("text_config") if isinstance(d.get("text_config"), dict) else d
+    h, L, H = t["hidden_size"], t["num_hidden_layers"], t["num_attention_heads"]
+    kvh = t.get("num_key_value_heads") or H
+    if t.get("kv_lora_rank"):                                   # multi-head latent attention
+        nope, rope, vd, r = t["qk_nope_head_dim"], t["qk_rope_head_dim"], t["v_head_dim"], t["kv_lora_rank"]
+        qr = t.get("q_lora_rank") or 0
+        q = (h * qr + qr * H * (nope + rope)) if qr else h * H * (nope + rope)
+        attn_lin = q + h * (r + rope) + r * H * (nope + vd) + H * vd * h
+        width = H * (nope + rope + vd)
+    else:
+        hd = t.get("head_dim") or h // H
+        attn_lin = h * (H + 2 * kvh) * hd + H * hd * h
+        width = H * 2 * hd
+    experts = t.get("n_routed_experts") or t.get("num_local_experts") or t.get("num_experts") or 0
+    if experts:
+        top_k = t.get("num_experts_per_tok", 1)
+        ie = t.get("moe_intermediate_size") or t.get("intermediate_size")
+        shared = (t.get("n_shared_experts") or 0) * ie + (t.get("shared_expert_intermediate_size") or 0)
+        sparse = 3 * h * (ie * top_k + shared) + h * experts
+        n_dense = min(L, t.get("first_k_dense_replace") or 0)
+        mlp_total = n_dense * 3 * h * t.get("intermediate_size", ie) + (L - n_dense) * sparse
+    else:
+        mlp_total = L * 3 * h * t["intermediate_size"]
+    linear = L * attn_lin + mlp_total + t["vocab_size"] * h
+    window = int(t.get("sliding_window") or 0)
+    kinds = t.get("layer_types")
+    if kinds and window:
+        n_slide = sum(1 for k in kinds[:L] if "sliding" in str(k))
+    elif window and t.get("sliding_window_pattern"):           # every n-th layer is global
+        n_slide = L - L // int(t["sliding_window_pattern"])
+    elif window and t.get("model_type") in ("mistral", "gemma2"):
+        n_slide = L if t.get("model_type") == "mistral" else L // 2
+    else:
+        n_slide = 0
+    classes = [(L - n_slide, 0, float(width))] + ([(n_slide, window, float(width))] if n_slide else [])
+    return float(linear), classes
+
+
 class FlopsCounter:
-    """Training FLOPs (forward + backward = 3x forward) of one batch of sequences for the supported families."""
+    """Training FLOPs (forward + backward = 3x forward) of one batch of sequences. Natively supported families are read
+    from the architecture description; any other family from its library configuration (``_terms_from_hf``)."""
 
     def __init__(self, config):
         self.config = config
+        self._generic = None
+        if getattr(config, "is_generic", False):
+            try:
+                self._generic = _terms_from_hf(config.extra["hf_config"])
+            except (KeyError, TypeError):
+                self._generic = None
 
     def _dense_per_token(self) -> float:
+        if self._generic is not None:
+            return self._generic[0]
         c = self.config
         h = c.hidden_size
         attn_lin = h * (c.q_size + 2 * c.kv_size) + c.q_size * h
         if getattr(c, "is_moe", False) and c.is_moe:
             mlp = 3 * h * c.moe_intermediate_size * c.num_experts_per_tok + h * c.num_experts
+            if getattr(c, "shared_expert_intermediate_size", 0):
+                mlp += 3 * h * c.shared_expert_intermediate_size + h
         else:
             mlp = 3 * h * c.intermediate_size
         emb = c.vocab_size * h  # LM head (the embedding gather is free)
         return (attn_lin + mlp) * c.num_hidden_layers + emb
 
+    def _attention_forward_flops(self, batch_seqlens: Sequence[int]) -> float:
+        """QK^T and PV of the causal layers: 2 FLOPs per multiply-accumulate, (score + value width) per pair."""
+        if self._generic is not None:
+            return sum(2.0 * n * width * sum(_causal_pairs(int(s), w) for s in batch_seqlens) for n, w, width in self._generic[1])
+        c = self.config
+        sq = float(sum(int(s) ** 2 for s in batch_seqlens))
+        return 4.0 * sq * c.head_dim * c.num_attention_heads * c.num_hidden_layers / 2.0
+
     def estimate_flops(self, batch_seqlens: Sequence[int], delta_time: float):
         """Returns (achieved TFLOPS, promised TFLOPS). ``batch_seqlens``: valid tokens per sequence."""
-        c = self.config
-        tokens = float(sum(batch_seqlens))
-        dense = 6.0 * self._dense_per_token() * tokens
-        sq = float(sum(int(s) ** 2 for s in batch_seqlens))
-        attn = 12.0 * sq * c.head_dim * c.num_attention_heads * c.num_hidden_layers / 2.0  # causal
-        achieved = (dense + attn) / max(delta_time, 1e-9) / 1e12
-        return achieved, get_device_flops("T")
+        total = 3.0 * self.forward_flops(batch_seqlens)
+        return total / max(delta_time, 1e-9) / 1e12, get_device_flops("T")
 
     def forward_flops(self, batch_seqlens: Sequence[int]) -> float:
-        c = self.config
         tokens = float(sum(batch_seqlens))
-        sq = float(sum(int(s) ** 2 for s in batch_seqlens))
-        return 2.0 * self._dense_per_token() * tokens + 4.0 * sq * c.head_dim * c.num_attention_heads * c.num_hidden_layers / 2.0
+        return 2.0 * self._dense_per_token() * tokens + self._attention_forward_flops(batch_seqlens)
