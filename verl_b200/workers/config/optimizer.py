@@ -27,10 +27,34 @@ class OptimizerConfig(BaseConfig):
     min_lr_ratio: float = 0.0
     num_cycles: float = 0.5
     override_optimizer_config: Optional[dict] = None
+    # Muon (``optimizer: muon``): momentum + Newton-Schulz orthogonalisation for the 2-D weights of the layers, AdamW
+    # (with the fields above) for embeddings, heads, norms and biases
+    muon_momentum: float = 0.95
+    muon_nesterov: bool = False
+    muon_split_qkv: bool = True
+    muon_scale_mode: str = "spectral"          # spectral | shape_scaling | unit_rms_norm | none
+    muon_coefficient_type: str = "quintic"     # quintic | simple
+    muon_num_ns_steps: int = 5
+    muon_tp_mode: str = "blockwise"            # tensor-parallel shards are orthogonalised one by one
+    muon_extra_scale_factor: float = 1.0
+    muon_scalar_optimizer: str = "adam"
+    muon_match_adamw_update_rms: bool = False  # extra factor = sqrt((1 - beta1) / (1 + beta1)): reuse an AdamW learning rate
 
     def __post_init__(self):
         assert self.lr != "???", "optimizer lr must be set"
         assert self.lr_scheduler_type in ("constant", "cosine", "wsd")
+        if self.muon_match_adamw_update_rms:
+            assert self.muon_extra_scale_factor == 1.0, "muon_match_adamw_update_rms derives muon_extra_scale_factor: set only one"
+        assert self.muon_tp_mode == "blockwise" and str(self.muon_scalar_optimizer).lower() in ("adam", "adamw")
+
+    @property
+    def muon_update_scale(self) -> float:
+        """Factor on the learning rate of the orthogonalised updates."""
+        if self.muon_match_adamw_update_rms:
+            from ..engine.native.muon import adamw_rms_match_scale_factor
+
+            return adamw_rms_match_scale_factor(float(self.betas[0]))
+        return float(self.muon_extra_scale_factor)
 
 
 @dataclass

@@ -150,6 +150,7 @@ class NativeEngine(BaseEngine):
         self.opt_step_count = 0
         self.sched_step = 0
         self._initialized = False
+        self.muon = None
         self._shared_params: Optional[FlatParams] = kwargs.get("shared_params")
 
     # ------------------------------------------------------------------------------------ setup
@@ -195,6 +196,7 @@ class NativeEngine(BaseEngine):
         else:
             want_fused = (bool(getattr(ec, "fused_comm", True)) and not self.forward_only and self.device.type == "cuda"
                           and not self.arch.is_generic
+                          and str(getattr(self.optimizer_config, "optimizer", "AdamW") or "AdamW").lower() != "muon"
                           and not int(getattr(self.model_config, "lora_rank", 0) or 0)
                           and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
                           and self.rep_world == 1
@@ -283,9 +285,18 @@ class NativeEngine(BaseEngine):
         self.lazy_grad = bool(getattr(ec, "lazy_grad_buffer", self.device.type == "cuda")) and not self.fused_comm
         if not self.forward_only:
             opt_name = str(getattr(self.optimizer_config, "optimizer", "AdamW") or "AdamW")
-            if opt_name.lower() not in ("adamw", "adam", "fusedadam", "fused_adamw"):
-                raise NotImplementedError(f"optimizer {opt_name!r}: this engine implements the sharded fused AdamW only "
-                                          f"(decoupled weight decay; weight_decay=0 gives Adam)")
+            if opt_name.lower() not in ("adamw", "adam", "fusedadam", "fused_adamw", "muon"):
+                raise NotImplementedError(f"optimizer {opt_name!r}: this engine implements the sharded fused AdamW "
+                                          f"(decoupled weight decay; weight_decay=0 gives Adam) and Muon")
+            self.muon = None
+            if opt_name.lower() == "muon":
+                from .muon import MuonPlan
+
+                assert self.lora is None and not self.fused_comm and self.local_numel == 0 and self.rep_world == 1, \
+                    "Muon runs on the full-parameter, collective-library optimizer path without hybrid sharding"
+                self.muon = MuonPlan(self.tparams, world=self.sh_world,
+                                     split_qkv=bool(getattr(self.optimizer_config, "muon_split_qkv", True)))
+                self._muon_mask = self.muon.mask(self.shard_lo, self.shard_lo + self.shard_numel, self.device)
             self.master = self._owned(self.tparams.flat).float()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
@@ -597,7 +608,9 @@ class NativeEngine(BaseEngine):
         self.ctrl.zero_()
         lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
         self.opt_step_count += 1
-        if self.device.type == "cuda":
+        if self.muon is not None:
+            norm = self._muon_update(lr)
+        elif self.device.type == "cuda":
             ops = native.ops()
             ops.sumsq_(self.grad_shard, self.ctrl)
             if self.sh_world > 1:  # replicas hold identical shards: the norm is a sum over one block
@@ -641,6 +654,56 @@ class NativeEngine(BaseEngine):
             self.grad_shard = None
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
+        return norm
+
+    def _muon_update(self, lr: float) -> torch.Tensor:
+        """Muon on the matrix ranges and AdamW on the rest of this rank's range (``muon.py`` has the step's plan). Expects
+        the mean gradient of the owned range in ``grad_shard``; returns the global gradient norm."""
+        oc, n_sh, W = self.optimizer_config, self.shard_numel, self.sh_world
+        g, mask = self.grad_shard, self._muon_mask
+        ss = g.double().pow(2).sum() if self.device.type == "cpu" else g.float().pow(2).sum()
+        if W > 1:
+            dist.all_reduce(ss, group=self.sh_group)
+        self.ctrl[0] = ss.float()
+        self._global_sumsq_correction()
+        norm = self.ctrl[0].double().sqrt().float()
+        if not bool(torch.isfinite(norm)):
+            return norm  # skipped step: state and weights stay as they are
+        coef = min(1.0, float(oc.clip_grad) / (float(norm) + 1e-6)) if oc.clip_grad and oc.clip_grad > 0 else 1.0
+        if coef != 1.0:
+            g.mul_(coef)
+        b1, b2 = float(oc.betas[0]), float(oc.betas[1])
+        mu, nesterov = float(oc.muon_momentum), bool(oc.muon_nesterov)
+        # second moment (used on the AdamW ranges only), then one buffer for both kinds of first moment
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        self.exp_avg.mul_(torch.where(mask, mu, b1)).add_(g * torch.where(mask, 1.0, 1 - b1))
+        u = torch.where(mask, g + mu * self.exp_avg if nesterov else self.exp_avg, torch.zeros((), device=g.device))
+        # whole matrices for the orthogonalisation: gather into the idle full-size gradient buffer
+        mg = self.tparams.main_grad
+        full = mg[: self.dense_numel]
+        if W > 1:
+            if self.device.type == "cuda":
+                dist.all_gather_into_tensor(full, u.contiguous(), group=self.sh_group)
+            else:
+                dist.all_gather([full[i * n_sh : (i + 1) * n_sh] for i in range(W)], u.contiguous(), group=self.sh_group)
+        else:
+            full.copy_(u)
+        self.muon.orthogonalise_owned(full, self.sh_rank, int(oc.muon_num_ns_steps), str(oc.muon_coefficient_type),
+                                      str(oc.muon_scale_mode))
+        if W > 1:
+            if self.device.type == "cuda":
+                upd = torch.empty_like(u)
+                dist.reduce_scatter_tensor(upd, full, op=dist.ReduceOp.SUM, group=self.sh_group)
+            else:
+                dist.all_reduce(full, group=self.sh_group)
+                upd = full[self.shard_lo : self.shard_lo + n_sh]
+        else:
+            upd = full[self.shard_lo : self.shard_lo + n_sh]
+        bc1, bc2 = 1 - b1 ** self.opt_step_count, 1 - b2 ** self.opt_step_count
+        denom = (self.exp_avg_sq.sqrt() / math.sqrt(bc2)).add_(float(oc.eps))
+        step = torch.where(mask, upd * (lr * oc.muon_update_scale), self.exp_avg / denom * (lr / bc1))
+        self.master.mul_(1 - lr * float(oc.weight_decay)).sub_(step)
+        self._scatter_owned(self.master, self.tparams.flat)
         return norm
 
     def _fused_optimizer_step(self) -> float:
