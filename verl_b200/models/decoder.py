@@ -31,7 +31,8 @@ from ..ops import functional as F
 from .config import ModelConfig
 from .weights import FlatParams
 
-__all__ = ["PackedBatch", "DecoderModel", "RouterReplay", "ExpertParallelGroup", "UlyssesSequenceParallel", "TensorSequenceParallel"]
+__all__ = ["PackedBatch", "DecoderModel", "RouterReplay", "ExpertParallelGroup", "UlyssesSequenceParallel", "ContextParallel",
+           "TensorSequenceParallel"]
 
 
 @dataclass
@@ -135,6 +136,43 @@ class UlyssesSequenceParallel:
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=self.group)                  # block i: my tokens, rank i's heads
         return recv.permute(1, 0, 2, 3).reshape(tl, self.size * hs, d)
+
+
+class ContextParallel(UlyssesSequenceParallel):
+    """Context parallelism over ``size`` ranks that hold the same micro-batch: like sequence parallelism every rank runs
+    the token-wise layers on a contiguous 1/size slice of the packed token stream, but around attention the KEYS AND
+    VALUES are all-gathered (all tokens, all heads) and every rank attends with its own queries; in the backward the
+    key / value gradients are reduce-scattered back to the owners of the tokens. Unlike the head exchange this puts no
+    divisibility constraint on the number of key/value heads (grouped-query models with few KV heads, long contexts).
+
+    Parity target: Megatron context parallelism as configured by ``verl/workers/config/engine.py``
+    (``context_parallel_size``) with the contiguous token split of ``verl/models/mcore/util.py:62-211``; the zigzag
+    (load-balanced) split of that file is not implemented."""
+
+    def gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        """[T/size, ...] of every rank -> [T, ...] in stream order."""
+        import torch.distributed as dist
+
+        x = x.contiguous()
+        out = torch.empty(self.size * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        if x.is_cuda:
+            dist.all_gather_into_tensor(out, x, group=self.group)
+        else:
+            dist.all_gather(list(out.chunk(self.size, 0)), x, group=self.group)
+        return out
+
+    def scatter_sum(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of every rank's [T, ...] contribution, this rank's [T/size, ...] rows of it."""
+        import torch.distributed as dist
+
+        x = x.contiguous()
+        n = x.shape[0] // self.size
+        if x.is_cuda:
+            out = torch.empty(n, *x.shape[1:], dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+            return out
+        dist.all_reduce(x, group=self.group)
+        return x[self.rank * n : (self.rank + 1) * n].clone()
 
 
 class TensorSequenceParallel:
@@ -339,7 +377,15 @@ class DecoderModel:
             self.kv_hook(layer_idx, k, v)
         native_ok = q.is_cuda and F._ATTN_IMPL["fwd"] is not None and hd in (64, 128)
         cu = batch.cu_seqlens if native_ok else self._cu_cpu(batch)
-        if self.sp is not None:
+        if isinstance(self.sp, ContextParallel):
+            assert batch.expand_index is None, "context parallelism and shared-prefix packing are exclusive"
+            kf, vf = self.sp.gather_tokens(k), self.sp.gather_tokens(v)
+            lo = self.sp.local_slice(batch.num_tokens).start
+            attn = F.attention_query_slice(q.contiguous(), kf, vf, self._cu_cpu(batch), lo)
+            attn2, lse = attn.reshape(T, Q), None
+            if S is not None:
+                S.update(qkv=qkv, attn=attn2, lse=None, cp_full=(kf, vf, lo))
+        elif self.sp is not None:
             assert batch.expand_index is None, "sequence parallelism and shared-prefix packing are exclusive"
             qf, kf, vf = self.sp.seq_to_heads(q.contiguous()), self.sp.seq_to_heads(k.contiguous()), self.sp.seq_to_heads(v.contiguous())
             attn_f, lse = F.attention_varlen(qf, kf, vf, cu, batch.max_seqlen)
@@ -398,7 +444,12 @@ class DecoderModel:
         k = qkv[:, Q : Q + KV].view(T, nkv, hd)
         v = qkv[:, Q + KV :].view(T, nkv, hd)
         cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["bwd"] is not None and lse is not None else self._cu_cpu(batch)
-        if self.sp is not None:
+        if isinstance(self.sp, ContextParallel):
+            kf, vf, lo = S["cp_full"]
+            dq, dk_f, dv_f = F.attention_query_slice_bwd(g_attn.view(T, nh, hd), q.contiguous(), kf, vf, self._cu_cpu(batch), lo)
+            # every rank's queries contribute to the gradients of all the keys / values they saw
+            dk, dv = self.sp.scatter_sum(dk_f.float()).to(q.dtype), self.sp.scatter_sum(dv_f.float()).to(q.dtype)
+        elif self.sp is not None:
             qf, kf, vf, attn_f = S["sp_full"]
             g_f = self.sp.seq_to_heads(g_attn.view(T, nh, hd).contiguous())
             dq_f, dk_f, dv_f = F.attention_varlen_bwd(g_f, qf, kf, vf, attn_f, lse, cu, batch.max_seqlen)

@@ -358,6 +358,49 @@ def attention_varlen_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen: int, s
         return torch.autograd.grad(o, (q_, k_, v_), dout)
 
 
+def _attention_query_slice(q, k, v, cu_seqlens, q_start: int, scale: float):
+    T_q = q.shape[0]
+    nh, nkv = q.shape[1], k.shape[1]
+    cu = cu_seqlens.tolist()
+    parts = []
+    lo, hi = q_start, q_start + T_q
+    for s0, s1 in zip(cu[:-1], cu[1:]):
+        a, b = max(lo, s0), min(hi, s1)
+        if a >= b:
+            continue
+        qq = q[a - lo : b - lo].transpose(0, 1).unsqueeze(0)          # [1, nh, b - a, hd]
+        kk = k[s0:b].transpose(0, 1).unsqueeze(0)                     # keys from the start of the sequence to the last query
+        vv = v[s0:b].transpose(0, 1).unsqueeze(0)
+        # query i (stream position a + i) sees keys s0 .. a + i: a causal mask aligned to the bottom-right corner
+        mask = torch.ones(b - a, b - s0, dtype=torch.bool, device=q.device).tril(diagonal=a - s0)
+        o = F.scaled_dot_product_attention(qq, kk, vv, attn_mask=mask, scale=scale, enable_gqa=nkv != nh)
+        parts.append(o.squeeze(0).transpose(0, 1))
+    covered = sum(p.shape[0] for p in parts)
+    if covered < T_q:  # rows past the end of the packed stream (padding): no keys, zero output
+        parts.append(q.new_zeros(T_q - covered, nh, q.shape[2]) + 0 * q[covered:])
+    return torch.cat(parts, 0)
+
+
+def attention_query_slice(q, k, v, cu_seqlens, q_start: int, scale: Optional[float] = None):
+    """Causal GQA attention of a contiguous slice of the packed stream's queries (``q`` [Tq, nh, hd] = stream positions
+    ``q_start .. q_start + Tq``) against the keys / values of the WHOLE stream (``k``/``v`` [T, nkv, hd]): what one rank
+    of a context-parallel group computes after the keys and values have been gathered. Every query attends to the keys
+    of its own sequence up to itself. Library attention per sequence (a functional path, not a tuned kernel)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    with torch.no_grad():
+        return _attention_query_slice(q, k, v, cu_seqlens, int(q_start), scale)
+
+
+def attention_query_slice_bwd(dout, q, k, v, cu_seqlens, q_start: int, scale: Optional[float] = None):
+    """(dq [Tq, nh, hd], dk [T, nkv, hd], dv [T, nkv, hd]) of :func:`attention_query_slice`; dk / dv are this rank's
+    contributions for the whole stream and still have to be summed over the group."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    with torch.enable_grad():
+        q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o = _attention_query_slice(q_, k_, v_, cu_seqlens, int(q_start), scale)
+        return torch.autograd.grad(o, (q_, k_, v_), dout, allow_unused=True)
+
+
 def kv_append_(k, v, slots, k_cache, v_cache) -> None:
     if k.is_cuda:
         _ops().kv_append_(k, v, slots, k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1]),

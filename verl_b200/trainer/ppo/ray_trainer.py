@@ -176,7 +176,10 @@ class RayPPOTrainer:
     def _model_parallel_size(self) -> int:
         a = self.config.actor_rollout_ref.actor
         if str(a.get("strategy", "fsdp")) != "megatron":
-            return int(a.get("ulysses_sequence_parallel_size", 1) or 1)  # a sequence-parallel block shares its data
+            # a sequence-parallel or context-parallel block shares its data
+            fc = a.get("fsdp_config") or {}
+            cp = int((fc.get("context_parallel_size", 1) if hasattr(fc, "get") else getattr(fc, "context_parallel_size", 1)) or 1)
+            return max(int(a.get("ulysses_sequence_parallel_size", 1) or 1), cp)
         m = a.get("megatron") or {}
         return int(m.get("tensor_model_parallel_size", 1) or 1) * int(m.get("pipeline_model_parallel_size", 1) or 1)
 

@@ -59,6 +59,9 @@ class FSDPEngineConfig(EngineConfig):
     use_orig_params: bool = False
     mixed_precision: Optional[dict] = None
     ulysses_sequence_parallel_size: int = 1
+    # context parallelism: blocks of this many data-parallel ranks split the tokens of the same micro-batches and exchange
+    # keys / values around attention (no constraint on the number of KV heads; exclusive with Ulysses)
+    context_parallel_size: int = 1
     zero_stage: int = 2
     enable_gradient_checkpointing: bool = True
     enable_activation_offload: bool = False
@@ -77,14 +80,13 @@ class FSDPEngineConfig(EngineConfig):
 class McoreEngineConfig(EngineConfig):
     tensor_model_parallel_size: int = 1
     expert_model_parallel_size: int = 1
-    sequence_parallel: bool = False     # token-sliced residual stream inside the tensor-parallel group
     pipeline_schedule: str = "1f1b"   # 1f1b | gpipe (all forwards, then all backwards)
     vocab_parallel_head: bool = True    # LM head rows split over the tensor-parallel group
     expert_tensor_parallel_size: Optional[int] = None
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: Optional[int] = None
     context_parallel_size: int = 1
-    sequence_parallel: bool = True
+    sequence_parallel: bool = True      # token-sliced residual stream inside the tensor-parallel group (on with TP > 1)
     use_distributed_optimizer: bool = True
     use_dist_checkpointing: bool = False
     dist_checkpointing_path: Optional[str] = None

@@ -50,6 +50,9 @@ class ModelParallelEngine(NativeEngine):
         self.pp_size = g("pipeline_model_parallel_size", 1)
         self.ep_size = g("expert_model_parallel_size", 1) if self.arch.is_moe else 1
         self.full_arch = self.arch
+        if g("context_parallel_size", 1) > 1 and self.pp_size > 1:
+            raise NotImplementedError("context parallelism is combined with tensor and data parallelism; pipeline stages "
+                                      "exchange whole token streams (use pipeline_model_parallel_size=1 with it)")
         if self.arch.is_generic:
             raise NotImplementedError(f"model_type={self.arch.model_type!r} runs as a library module: tensor / pipeline / expert "
                                       f"parallel training covers the natively supported families; use the data-parallel engine "
@@ -90,7 +93,9 @@ class ModelParallelEngine(NativeEngine):
                 return x
 
             self.model.tp_reduce = reduce
-            if bool(getattr(self.engine_config, "sequence_parallel", False)):
+            if bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1:
+                # (with context parallelism the stream is already token-sliced over the context-parallel block, and the
+                # tensor-parallel group keeps the plain all-reduce form)
                 # token-sliced residual stream: reduce-scatter behind the row-parallel projections, all-gather in front of
                 # the column-parallel ones
                 from ....models.decoder import TensorSequenceParallel

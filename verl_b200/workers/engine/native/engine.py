@@ -254,18 +254,32 @@ class NativeEngine(BaseEngine):
             self.tparams = self.lora
         # Ulysses sequence parallelism: blocks of ``sp`` consecutive ranks work on the same micro-batches
         self.sp_size = int(getattr(ec, "ulysses_sequence_parallel_size", 1) or 1)
+        self.cp_size = int(getattr(ec, "context_parallel_size", 1) or 1)
+        assert self.sp_size == 1 or self.cp_size == 1, "Ulysses sequence parallelism and context parallelism are exclusive"
+        if self.cp_size > 1:
+            # same placement and micro-batch handling as Ulysses (a block of ranks shares its micro-batches and splits their
+            # tokens); only the exchange around attention differs
+            assert not self.arch.is_generic, "context parallelism needs one of the natively supported model families"
+            self.sp_size = self.cp_size
         self.sp_group, self.sp_rank = None, 0
         if self.sp_size > 1:
             assert self.world % self.sp_size == 0 and not self.value_head, "sequence parallel size must divide the data-parallel world"
-            assert self.arch.num_key_value_heads % self.sp_size == 0, "sequence parallel size must divide the KV heads"
-            from ....models.decoder import UlyssesSequenceParallel
+            assert self.cp_size > 1 or self.arch.num_key_value_heads % self.sp_size == 0, "sequence parallel size must divide the KV heads"
+            from ....models.decoder import ContextParallel, UlyssesSequenceParallel
 
             pool = dist.get_process_group_ranks(self.group if self.group is not None else dist.group.WORLD)
-            for g0 in range(0, self.world, self.sp_size):  # collective: every rank creates every group, in the same order
-                grp = dist.new_group(pool[g0 : g0 + self.sp_size])
-                if g0 <= self.rank < g0 + self.sp_size:
-                    self.sp_group, self.sp_rank = grp, self.rank - g0
-            self.model.sp = UlyssesSequenceParallel(self.sp_group, self.sp_rank, self.sp_size)
+            if self.group is None:
+                for g0 in range(0, self.world, self.sp_size):  # collective: every rank creates every group, in the same order
+                    grp = dist.new_group(pool[g0 : g0 + self.sp_size])
+                    if g0 <= self.rank < g0 + self.sp_size:
+                        self.sp_group, self.sp_rank = grp, self.rank - g0
+            else:
+                # the data-parallel group is itself a sub-group (model-parallel engines): other ranks of the job build
+                # different groups at this point, so only the members of a block take part in creating it
+                g0 = self.rank // self.sp_size * self.sp_size
+                self.sp_group = dist.new_group(pool[g0 : g0 + self.sp_size], use_local_synchronization=True)
+                self.sp_rank = self.rank - g0
+            self.model.sp = (ContextParallel if self.cp_size > 1 else UlyssesSequenceParallel)(self.sp_group, self.sp_rank, self.sp_size)
         # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
         self._share_prefix = (bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
                               and self.sp_size == 1 and not self.arch.is_generic)
