@@ -124,6 +124,11 @@ class ModelConfig:
             total += v * h
         return total
 
+    @property
+    def is_multimodal(self) -> bool:
+        """True for vision-language architectures (a vision tower feeds placeholder tokens of the text stream)."""
+        return self.is_generic and isinstance(self.extra.get("hf_config", {}).get("vision_config"), dict)
+
     # ------------------------------------------------------------------ HF interchange
     @classmethod
     def from_hf_dict(cls, d: dict[str, Any]) -> "ModelConfig":

@@ -35,7 +35,7 @@ def _round_up(n: int, a: int) -> int:
 def build_hf_module(cfg: ModelConfig, dtype: torch.dtype, seed: int = 0, value_head: bool = False,
                     attn_implementation: Optional[str] = None) -> torch.nn.Module:
     """Random-initialised library module for the architecture stored in ``cfg.extra['hf_config']``."""
-    from transformers import AutoConfig, AutoModelForCausalLM
+    from transformers import AutoConfig, AutoModelForCausalLM, AutoModelForImageTextToText
 
     d = dict(cfg.extra["hf_config"])
     mt = d.pop("model_type")
@@ -48,7 +48,8 @@ def build_hf_module(cfg: ModelConfig, dtype: torch.dtype, seed: int = 0, value_h
         # without an explicit choice the library picks its best supported attention (fused SDPA where the family has it)
         # ("native" names this framework's own attention kernels, which serve the hand-scheduled families only)
         kw = {"attn_implementation": attn_implementation} if attn_implementation and attn_implementation != "native" else {}
-        module = AutoModelForCausalLM.from_config(hf_cfg, dtype=dtype, **kw)
+        auto = AutoModelForImageTextToText if cfg.is_multimodal else AutoModelForCausalLM
+        module = auto.from_config(hf_cfg, dtype=dtype, **kw)
         if value_head:
             h = hf_cfg.get_text_config().hidden_size
             module.v_head = torch.nn.Linear(h, 1, bias=False, dtype=dtype)
@@ -191,7 +192,9 @@ class GenericCausalLM:
     def __init__(self, cfg: ModelConfig, params: ModuleFlatParams, recompute: str = "auto"):
         self.cfg, self.params = cfg, params
         self.module = params.module
-        self.trunk = self.module.get_decoder() if hasattr(self.module, "get_decoder") else self.module.model
+        # vision-language models: the trunk is the module that merges the vision tower's output into the text stream
+        self.multimodal = bool(cfg.is_multimodal)
+        self.trunk = self.module.model if self.multimodal or not hasattr(self.module, "get_decoder") else self.module.get_decoder()
         hf = self.module.config.get_text_config()
         self.softcap = float(getattr(hf, "final_logit_softcapping", 0.0) or 0.0)
         head = self.module.get_output_embeddings()
@@ -210,7 +213,7 @@ class GenericCausalLM:
         return 0  # recomputation is all-or-nothing here (the library's gradient checkpointing)
 
     # ------------------------------------------------------------------ forward
-    def _hidden(self, batch, need_grad: bool) -> torch.Tensor:
+    def _hidden(self, batch, need_grad: bool, mm_inputs: Optional[dict] = None) -> torch.Tensor:
         assert getattr(batch, "expand_index", None) is None, "shared-prefix packing needs the hand-written decoder"
         # gradient checkpointing and dropout follow the module's training flag
         self.module.train(bool(need_grad) and self.recompute != "none")
@@ -225,7 +228,14 @@ class GenericCausalLM:
         ids = torch.zeros(b, width, dtype=torch.int64, device=dev).index_put_((row, col), batch.input_ids.long())
         pos = torch.zeros(b, width, dtype=torch.int64, device=dev).index_put_((row, col), batch.positions.long())
         mask = torch.zeros(b, width, dtype=torch.int64, device=dev).index_put_((row, col), torch.ones_like(row))
-        out = self.trunk(input_ids=ids, attention_mask=mask, position_ids=pos, use_cache=False)
+        if self.multimodal:
+            # multi-axis rotary positions (time / height / width of the image patches) follow from the placeholder tokens and
+            # the grids: the library derives them from the mask; ``mm_inputs`` holds the processor's tensors of this
+            # micro-batch's rows, concatenated in row order (pixel_values, image_grid_thw, ...)
+            out = self.trunk(input_ids=ids, attention_mask=mask, use_cache=False, **(mm_inputs or {}))
+        else:
+            assert not mm_inputs, "multi-modal inputs for a text-only architecture"
+            out = self.trunk(input_ids=ids, attention_mask=mask, position_ids=pos, use_cache=False)
         return out.last_hidden_state[row, col]
 
     def _head(self, hS: torch.Tensor, labels: torch.Tensor, temperature: float):
@@ -240,21 +250,21 @@ class GenericCausalLM:
 
     def forward_logprobs(self, batch, labels: torch.Tensor, temperature: float = 1.0, need_grad: Optional[bool] = None,
                          positions: Optional[torch.Tensor] = None, stage_input=None,
-                         position_labels: Optional[torch.Tensor] = None):
+                         position_labels: Optional[torch.Tensor] = None, mm_inputs: Optional[dict] = None):
         """(log_probs, entropy) per packed position (fp32), or per entry of ``positions``."""
         need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
         with torch.set_grad_enabled(bool(need_grad)):
-            h = self._hidden(batch, need_grad)
+            h = self._hidden(batch, need_grad, mm_inputs)
             if positions is not None:
                 h = h.index_select(0, positions)
                 labels = position_labels if position_labels is not None else labels.index_select(0, positions)
             lp, ent = self._head(h, labels, temperature)
         return lp.float(), ent.float()
 
-    def forward_values(self, batch, need_grad: Optional[bool] = None, stage_input=None) -> torch.Tensor:
+    def forward_values(self, batch, need_grad: Optional[bool] = None, stage_input=None, mm_inputs: Optional[dict] = None) -> torch.Tensor:
         need_grad = torch.is_grad_enabled() if need_grad is None else need_grad
         with torch.set_grad_enabled(bool(need_grad)):
-            h = self._hidden(batch, need_grad)
+            h = self._hidden(batch, need_grad, mm_inputs)
             return self.module.v_head(h)[:, 0].float()
 
     @torch.no_grad()
@@ -262,8 +272,8 @@ class GenericCausalLM:
         return self._hidden(batch, False)
 
     @torch.no_grad()
-    def forward_logits(self, batch) -> torch.Tensor:
-        logits = self.module.get_output_embeddings()(self._hidden(batch, False)).float()
+    def forward_logits(self, batch, mm_inputs: Optional[dict] = None) -> torch.Tensor:
+        logits = self.module.get_output_embeddings()(self._hidden(batch, False, mm_inputs)).float()
         if self.softcap:
             logits = torch.tanh(logits / self.softcap) * self.softcap
         return logits

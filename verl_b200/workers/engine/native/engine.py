@@ -40,7 +40,8 @@ from ....utils.device import get_device_name
 from ...config.optimizer import lr_at_step
 from ..base import BaseEngine, EngineRegistry
 
-__all__ = ["NativeEngine", "NativeEngineWithLMHead", "NativeEngineWithValueHead", "pack_padded_batch"]
+__all__ = ["NativeEngine", "NativeEngineWithLMHead", "NativeEngineWithValueHead", "pack_padded_batch",
+           "collate_multi_modal_inputs"]
 
 
 def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: Optional[torch.Tensor],
@@ -71,6 +72,21 @@ def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, pos
     resp_index = flat_index[:, P - 1 : L - 1]
     resp_valid = mask[:, P:]
     return batch, labels.contiguous(), resp_index, resp_valid
+
+
+def collate_multi_modal_inputs(rows, device=None) -> dict:
+    """One dict of tensors for a micro-batch from its rows' processor outputs (``pixel_values``, ``image_grid_thw``,
+    ``pixel_values_videos``, ...): every key is concatenated along its first dimension in row order; rows without
+    images contribute nothing. Parity target: the reference's ``multi_modal_inputs`` handling in
+    ``verl/workers/utils/padding.py`` / ``verl/utils/model.py`` (``extract_multi_modal_inputs``)."""
+    out: dict[str, list] = {}
+    for r in rows:
+        if not r:
+            continue
+        for k, v in r.items():
+            if isinstance(v, torch.Tensor):
+                out.setdefault(k, []).append(v)
+    return {k: torch.cat(v, 0).to(device) if device is not None else torch.cat(v, 0) for k, v in out.items()}
 
 
 def prompt_group_ids(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int) -> list[int]:
@@ -432,8 +448,11 @@ class NativeEngine(BaseEngine):
         out = []
         for p in parts:
             idx = torch.tensor(p, dtype=torch.int64, device=ids.device)
-            out.append({k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v)
-                        for k, v in data.items()} | {"_rows": p} | ({"_gids": [gids_all[r] for r in p]} if share else {}))
+            mb = {k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v)
+                  for k, v in data.items()} | {"_rows": p} | ({"_gids": [gids_all[r] for r in p]} if share else {})
+            if mb.get("multi_modal_inputs") is not None:   # per-row processor outputs (vision-language models)
+                mb["multi_modal_inputs"] = [data["multi_modal_inputs"][r] for r in p]
+            out.append(mb)
         return out
 
     def forward_backward_batch(self, data, loss_function: Optional[Callable] = None, forward_only: bool = False) -> dict:
@@ -512,8 +531,12 @@ class NativeEngine(BaseEngine):
             # members of a group share their prompt: it is embedded, projected and fed through the MLPs once
             batch, positions, position_labels, resp_valid = pack_shared_prefix_batch(mb["input_ids"], mb["attention_mask"],
                                                                                      mb.get("position_ids"), R, gids)
+        extra = {}
+        if mb.get("multi_modal_inputs") is not None:
+            assert self.arch.is_multimodal, "multi_modal_inputs need a vision-language architecture"
+            extra["mm_inputs"] = collate_multi_modal_inputs(mb["multi_modal_inputs"], self.device)
         lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions,
-                                              position_labels=position_labels)
+                                              position_labels=position_labels, **extra)
         out = {"log_probs": torch.zeros(resp_valid.shape, dtype=lp.dtype, device=lp.device).masked_scatter(resp_valid, lp)}
         if calc_entropy or need_grad:
             out["entropy"] = torch.zeros(resp_valid.shape, dtype=ent.dtype, device=ent.device).masked_scatter(resp_valid, ent)
@@ -875,5 +898,8 @@ class NativeEngineWithValueHead(NativeEngine):
     def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
         batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
                                                                   mb.get("position_ids"), R)
-        vals = self.model.forward_values(batch, need_grad=need_grad)
+        extra = {}
+        if mb.get("multi_modal_inputs") is not None:
+            extra["mm_inputs"] = collate_multi_modal_inputs(mb["multi_modal_inputs"], self.device)
+        vals = self.model.forward_values(batch, need_grad=need_grad, **extra)
         return {"values": torch.where(resp_valid, vals[resp_index], torch.zeros((), dtype=vals.dtype, device=vals.device))}
