@@ -112,3 +112,147 @@ def test_text_only_families_refuse_images():
     data["input_ids"] = data["input_ids"].clamp_max(400)
     with pytest.raises(AssertionError, match="vision-language"):
         eng.infer_batch(data)
+
+
+def test_cached_sampling_with_images_matches_cache_free_greedy():
+    from verl_b200.models.generic import GenericRolloutEngine
+    from verl_b200.workers.rollout.native.engine import SamplingParams
+
+    arch = _arch()
+    eng = _engine(arch)
+    P = eng.params
+    ro = GenericRolloutEngine(arch, P, max_num_seqs=4, eos_token_id=-1)
+    data = _batch()
+    prompts = [data["input_ids"][i, :14][data["attention_mask"][i, :14].bool()].tolist() for i in range(3)]
+    mm = data["multi_modal_inputs"]
+    outs = ro.generate(prompts, SamplingParams(temperature=0.0, max_tokens=4), mm_inputs=mm)
+    mod = P.module.eval()
+    for p, o, m in zip(prompts, outs, mm):
+        seq = list(p)
+        for t in range(4):
+            x = torch.tensor([seq])
+            with torch.no_grad():
+                lg = mod(input_ids=x, attention_mask=torch.ones_like(x), use_cache=False, **(m or {})).logits[0, -1].float()
+            assert int(lg.argmax()) == o.token_ids[t], (t, o.token_ids)
+            assert abs(float(torch.log_softmax(lg, -1)[o.token_ids[t]]) - o.log_probs[t]) < 2e-4
+            seq.append(o.token_ids[t])
+
+
+def test_image_and_video_preparation():
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    from verl_b200.utils.dataset.vision_utils import process_image, process_video, smart_resize
+
+    assert smart_resize(100, 100, 28, 56 * 56, 10**6) == (112, 112)
+    h, w = smart_resize(2000, 1000, 28, 56 * 56, 200 * 200)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 200 * 200 and abs(h / w - 2.0) < 0.35
+    h, w = smart_resize(20, 30, 28, 56 * 56, 10**6)
+    assert h % 28 == 0 and w % 28 == 0 and h * w >= 56 * 56
+    with pytest.raises(ValueError):
+        smart_resize(1, 1000)
+    img = Image.fromarray((np.random.RandomState(0).rand(50, 70, 3) * 255).astype(np.uint8))
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    for src in (img, {"bytes": buf.getvalue()}, {"image": img, "max_pixels": 28 * 28 * 2}, np.asarray(img)):
+        out = process_image(src, image_patch_size=14)
+        assert out.mode == "RGB" and out.width % 28 == 0 and out.height % 28 == 0
+    assert process_image({"image": img, "max_pixels": 28 * 28 * 2}).width * process_image({"image": img, "max_pixels": 28 * 28 * 2}).height <= 28 * 28 * 2
+    frames = [np.full((40, 40, 3), i, dtype=np.uint8) for i in range(60)]       # two seconds at 30 fps
+    v = process_video(frames, image_patch_size=14)
+    assert v.shape == (4, 3, 28, 28) and v.dtype == torch.uint8 and int(v[0, 0, 0, 0]) == 0 and int(v[-1, 0, 0, 0]) == 59
+    assert process_video({"video": frames, "nframes": 7}).shape[0] == 6          # multiple of the temporal patch
+
+
+class _FakeProcessor:
+    """Stands in for a vision-language processor: one placeholder token per 2x2 patch block, patches of 96 numbers."""
+
+    def apply_chat_template(self, messages, add_generation_prompt=True, tokenize=False, **kw):
+        out = []
+        for m in messages:
+            for part in m["content"] if isinstance(m["content"], list) else [{"type": "text", "text": m["content"]}]:
+                out.append({"image": "<|img|>", "video": "<|vid|>"}.get(part["type"]) or part["text"])
+        return " ".join(out)
+
+    def __call__(self, text, images=None, videos=None, return_tensors="pt"):
+        ids, pix, grids = [], [], []
+        it = iter(images or [])
+        for word in text[0].split():
+            if word == "<|img|>":
+                im = next(it)
+                gh, gw = im.height // 14, im.width // 14
+                ids += [VSTART] + [IMG] * ((gh // 2) * (gw // 2)) + [VEND]
+                pix.append(torch.zeros(gh * gw, 96))
+                grids.append([1, gh, gw])
+            else:
+                ids.append(3 + sum(map(ord, word)) % 400)
+        enc = {"input_ids": torch.tensor([ids]), "attention_mask": torch.ones(1, len(ids), dtype=torch.int64)}
+        if pix:
+            enc.update(pixel_values=torch.cat(pix), image_grid_thw=torch.tensor(grids))
+        return enc
+
+
+def test_dataset_rows_with_images_carry_processor_outputs(tmp_path):
+    import numpy as np
+    import pandas as pd
+    from PIL import Image
+
+    from verl_b200.utils.dataset.rl_dataset import RLHFDataset, collate_fn
+
+    img = Image.fromarray(np.zeros((56, 84, 3), dtype=np.uint8))
+    rows = [{"prompt": [{"role": "user", "content": "look <image> and answer"}], "images": [{"image": img}], "data_source": "geo"},
+            {"prompt": [{"role": "user", "content": "no picture here"}], "images": [], "data_source": "geo"}]
+    f = tmp_path / "d.jsonl"
+    pd.DataFrame([{**r, "images": []} for r in rows]).to_json(f, orient="records", lines=True)
+
+    class Tok:
+        pad_token_id = 0
+        chat_template = None
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [3 + sum(map(ord, w)) % 400 for w in text.split()]}
+
+    ds = RLHFDataset(str(f), Tok(), {"max_prompt_length": 16, "filter_overlong_prompts": False}, processor=_FakeProcessor())
+    ds.rows = rows                                                   # (images do not survive a json round trip)
+    a, b = ds[0], ds[1]
+    assert a["input_ids"].shape == (16,) and int((a["input_ids"] == IMG).sum()) == (56 // 28) * (84 // 28)
+    assert a["multi_modal_inputs"]["pixel_values"].shape == (4 * 6, 96) and a["multi_modal_inputs"]["image_grid_thw"].tolist() == [[1, 4, 6]]
+    assert a["multi_modal_data"]["image"][0].size == (84, 56) and "images" not in a
+    assert b["multi_modal_inputs"] == {} and int((b["input_ids"] == IMG).sum()) == 0
+    batch = collate_fn([a, b])
+    assert batch["input_ids"].shape == (2, 16) and len(batch["multi_modal_inputs"]) == 2
+
+
+def _ppo_cfg(mdir, tmp):
+    return ['data.train_batch_size=4', 'data.max_prompt_length=12', 'data.max_response_length=6', 'data.synthetic.num_prompts=8',
+            'data.synthetic.prompt_length=12', 'data.synthetic.vocab_high=490',
+            '+data.synthetic.image.grid=[4,4]', '+data.synthetic.image.merge_size=2', '+data.synthetic.image.patch_dim=96',
+            '+data.synthetic.image.image_token_id=500', '+data.synthetic.image.vision_start_token_id=498',
+            '+data.synthetic.image.vision_end_token_id=499',
+            f'actor_rollout_ref.model.path={mdir}', 'actor_rollout_ref.rollout.n=2', 'actor_rollout_ref.actor.ppo_mini_batch_size=4',
+            'actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=4', 'actor_rollout_ref.actor.use_kl_loss=true',
+            'actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=8', 'actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=8',
+            'algorithm.adv_estimator=grpo', 'reward_model.reward_manager=token_rule', 'trainer.n_gpus_per_node=1',
+            'trainer.total_epochs=1', 'trainer.total_training_steps=2', 'trainer.device=cpu', 'trainer.val_before_train=false',
+            'actor_rollout_ref.rollout.max_num_seqs=8', 'trainer.resume_mode=disable', 'trainer.logger=[]',
+            f'trainer.default_local_dir={tmp}/ckpt', 'trainer.save_freq=-1']
+
+
+def test_grpo_end_to_end_with_images(tmp_path):
+    import json
+
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    arch = _arch()
+    mdir = tmp_path / "tiny-qwen2_5-vl"
+    mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(arch.to_hf_dict()))
+    from verl_b200.trainer.main_ppo import main
+
+    t = main(_ppo_cfg(mdir, tmp_path))
+    b = t.last_batch
+    assert b.batch["advantages"].shape == (8, 6) and len(b.non_tensor_batch["multi_modal_inputs"]) == 8
+    assert int((b.batch["input_ids"][:, :12] == IMG).sum()) == 8 * 4
+    diff = (torch.exp(b.batch["rollout_log_probs"]) - torch.exp(b.batch["old_log_probs"])).abs()[b.batch["response_mask"].bool()].max().item()
+    assert diff < 1e-3, diff     # the sampler and the training forward saw the same images

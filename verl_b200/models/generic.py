@@ -306,7 +306,9 @@ class GenericRolloutEngine:
         return None  # the cache of a generate() call dies with the call
 
     @torch.no_grad()
-    def generate(self, prompts, params):
+    def generate(self, prompts, params, mm_inputs=None):
+        """``mm_inputs``: per prompt, the processor's tensors of its images / videos (or None); the prompt ids already hold
+        the placeholder tokens."""
         from ..workers.rollout.native.engine import RequestOutput
         from ..workers.rollout.naive.naive_rollout import filter_logits
 
@@ -341,9 +343,24 @@ class GenericRolloutEngine:
             pos = (mask.cumsum(-1) - 1).clamp_min(0)
             cache, step_ids, step_pos = None, ids, pos
             self.stats["prefill_tokens"] += int(mask.sum())
+            multimodal = bool(self.cfg.is_multimodal)
+            first_kw = {}
+            if mm_inputs is not None and multimodal:
+                per_key: dict = {}
+                for i in rows:
+                    for k, v in (mm_inputs[i] or {}).items():
+                        if isinstance(v, torch.Tensor):
+                            per_key.setdefault(k, []).append(v)
+                first_kw = {k: torch.cat(v, 0).to(dev) for k, v in per_key.items()}
             for t in range(max_new):
-                out = self.module(input_ids=step_ids, attention_mask=mask, position_ids=step_pos, past_key_values=cache,
-                                  use_cache=True)
+                if multimodal:
+                    # multi-axis rotary positions: the library derives them from the mask and the grids at the prefill and
+                    # continues them from its stored offsets on the cached steps
+                    out = self.module(input_ids=step_ids, attention_mask=mask, past_key_values=cache, use_cache=True,
+                                      **(first_kw if t == 0 else {}))
+                else:
+                    out = self.module(input_ids=step_ids, attention_mask=mask, position_ids=step_pos, past_key_values=cache,
+                                      use_cache=True)
                 cache = out.past_key_values
                 logits = out.logits[:, -1].float()
                 scaled = logits / torch.where(greedy, torch.ones_like(temp), temp)[:, None]

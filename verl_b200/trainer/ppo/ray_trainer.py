@@ -309,7 +309,9 @@ class RayPPOTrainer:
         metrics.update(log_seqlen_unbalance(lens.tolist(), parts, logging_prefix))
 
     def _get_gen_batch(self, batch: DataProto) -> DataProto:
-        reward_keys = {"data_source", "reward_model", "extra_info", "uid"} & set(batch.non_tensor_batch)
+        # kept on the training batch as well: what the reward needs, and the processor outputs of images / videos that the
+        # log-prob and update passes feed to the vision tower again
+        reward_keys = {"data_source", "reward_model", "extra_info", "uid", "multi_modal_inputs"} & set(batch.non_tensor_batch)
         pop_keys = [k for k in ("input_ids", "attention_mask", "position_ids") if k in batch.batch.keys()]
         non_pop = [k for k in batch.non_tensor_batch if k not in reward_keys]
         gen = batch.pop(batch_keys=pop_keys, non_tensor_batch_keys=non_pop)

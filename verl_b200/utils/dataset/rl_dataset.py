@@ -40,20 +40,39 @@ class SyntheticPromptDataset(Dataset):
     """``num_prompts`` prompts of ``prompt_length`` token ids drawn uniformly from [low, high)."""
 
     def __init__(self, num_prompts: int, prompt_length: int, vocab_low: int = 3, vocab_high: int = 512, seed: int = 0,
-                 data_source: str = "synthetic/mod7"):
+                 data_source: str = "synthetic/mod7", image: Optional[dict] = None):
+        """``image`` (vision-language runs without data files): ``{grid: [h, w] patches, merge_size, patch_dim,
+        image_token_id, vision_start_token_id, vision_end_token_id}`` puts one random image in front of every prompt: its
+        placeholder tokens into the ids and its patches ([h * w, patch_dim]) + grid into ``multi_modal_inputs``."""
         g = torch.Generator()
         g.manual_seed(seed)
         self.ids = torch.randint(vocab_low, vocab_high, (num_prompts, prompt_length), generator=g)
         self.data_source = data_source
+        self.image = dict(image) if image else None
+        self.seed = seed
+        if self.image:
+            h, w = (int(x) for x in self.image.get("grid", (4, 4)))
+            m = int(self.image.get("merge_size", 2))
+            n_tok = (h // m) * (w // m)
+            assert n_tok + 2 < prompt_length, "the prompt is too short for the image placeholders"
+            head = [int(self.image["vision_start_token_id"])] + [int(self.image["image_token_id"])] * n_tok + [int(self.image["vision_end_token_id"])]
+            self.ids[:, : len(head)] = torch.tensor(head)
 
     def __len__(self) -> int:
         return self.ids.shape[0]
 
     def __getitem__(self, i: int) -> dict:
         ids = self.ids[i]
-        return {"input_ids": ids, "attention_mask": torch.ones_like(ids), "position_ids": torch.arange(ids.shape[0]),
-                "data_source": self.data_source, "index": i,
-                "reward_model": {"style": "rule", "ground_truth": int(ids[0]) % 7}}
+        out = {"input_ids": ids, "attention_mask": torch.ones_like(ids), "position_ids": torch.arange(ids.shape[0]),
+               "data_source": self.data_source, "index": i,
+               "reward_model": {"style": "rule", "ground_truth": int(ids[-1]) % 7 if self.image else int(ids[0]) % 7}}
+        if self.image:
+            h, w = (int(x) for x in self.image.get("grid", (4, 4)))
+            g = torch.Generator()
+            g.manual_seed(self.seed * 1000003 + i)
+            out["multi_modal_inputs"] = {"pixel_values": torch.randn(h * w, int(self.image.get("patch_dim", 1176)), generator=g),
+                                         "image_grid_thw": torch.tensor([[1, h, w]])}
+        return out
 
 
 class RLHFDataset(Dataset):
@@ -73,6 +92,10 @@ class RLHFDataset(Dataset):
         self.return_full_prompt = bool(g("return_full_prompt", False))
         self.apply_chat_template_kwargs = dict(g("apply_chat_template_kwargs", {}) or {})
         self.need_tools_kwargs = bool(g("need_tools_kwargs", False))
+        # vision-language rows: ``<image>`` / ``<video>`` marks in the prompt text refer to the entries of these columns
+        self.image_key = g("image_key", "images")
+        self.video_key = g("video_key", "videos")
+        self.image_patch_size = int(g("image_patch_size", 14))
         self.max_samples = max_samples
         self.seed = g("seed", None)
         self._read()
@@ -93,7 +116,7 @@ class RLHFDataset(Dataset):
         if self.max_samples and self.max_samples > 0:
             rng = np.random.RandomState(self.seed or 0)
             rows = [rows[i] for i in rng.permutation(len(rows))[: self.max_samples]]
-        if self.filter_overlong_prompts and self.tokenizer is not None:
+        if self.filter_overlong_prompts and self.tokenizer is not None and self.processor is None:
             rows = [r for r in rows if len(self._tokenize(self._messages(r))) <= self.max_prompt_length]
         self.rows = rows
 
@@ -116,14 +139,62 @@ class RLHFDataset(Dataset):
     def __len__(self) -> int:
         return len(self.rows)
 
+    def _has_media(self, row: dict) -> bool:
+        def some(v):
+            return v is not None and len(v) > 0
+
+        return self.processor is not None and (some(row.get(self.image_key)) or some(row.get(self.video_key)))
+
+    def _multimodal(self, row: dict, messages: list) -> tuple[torch.Tensor, torch.Tensor, dict, dict]:
+        """Prompt ids with the processor's placeholder tokens, its tensors (``multi_modal_inputs``) and the prepared raw
+        media (``multi_modal_data``, what an external inference server would be given)."""
+        from .vision_utils import process_image, process_video
+
+        structured = []
+        for m in messages:
+            content = m["content"]
+            if isinstance(content, str):   # "<image>" / "<video>" marks split the text into typed segments
+                parts = []
+                for seg in re.split(r"(<image>|<video>)", content):
+                    if seg == "<image>":
+                        parts.append({"type": "image"})
+                    elif seg == "<video>":
+                        parts.append({"type": "video"})
+                    elif seg:
+                        parts.append({"type": "text", "text": seg})
+                content = parts
+            structured.append({"role": m["role"], "content": content})
+        prompt = self.processor.apply_chat_template(structured, add_generation_prompt=True, tokenize=False,
+                                                    **self.apply_chat_template_kwargs)
+        data, kw = {}, {}
+        imgs, vids = row.get(self.image_key), row.get(self.video_key)
+        if imgs is not None and len(imgs) > 0:
+            data["image"] = [process_image(im, self.image_patch_size) for im in imgs]
+            kw["images"] = data["image"]
+        if vids is not None and len(vids) > 0:
+            data["video"] = [process_video(v, self.image_patch_size) for v in vids]
+            kw["videos"] = data["video"]
+        enc = dict(self.processor(text=[prompt], return_tensors="pt", **kw))
+        ids, mask = enc.pop("input_ids"), enc.pop("attention_mask")
+        enc.pop("second_per_grid_ts", None)
+        return ids, mask, {k: v for k, v in enc.items() if isinstance(v, torch.Tensor)}, data
+
     def __getitem__(self, i: int) -> dict:
         row = dict(self.rows[i])
         messages = self._messages(row)
-        ids = torch.tensor(self._tokenize(messages), dtype=torch.int64).unsqueeze(0)
-        mask = torch.ones_like(ids)
+        mm_inputs = mm_data = None
+        if self._has_media(row):
+            ids, mask, mm_inputs, mm_data = self._multimodal(row, messages)
+            assert ids.shape[1] <= self.max_prompt_length or self.truncation != "error", \
+                f"prompt with media placeholders has {ids.shape[1]} tokens > max_prompt_length {self.max_prompt_length}"
+        else:
+            ids = torch.tensor(self._tokenize(messages), dtype=torch.int64).unsqueeze(0)
+            mask = torch.ones_like(ids)
         pad = self.tokenizer.pad_token_id if getattr(self.tokenizer, "pad_token_id", None) is not None else 0
         ids, mask = VF.postprocess_data(ids, mask, self.max_prompt_length, pad, left_pad=True, truncation=self.truncation)
-        out = {k: v for k, v in row.items() if k != self.prompt_key}
+        out = {k: v for k, v in row.items() if k not in (self.prompt_key, self.image_key, self.video_key)}
+        if self.processor is not None:   # every row of a vision-language dataset carries the fields (empty for text-only rows)
+            out["multi_modal_inputs"], out["multi_modal_data"] = mm_inputs or {}, mm_data or {}
         out.update(input_ids=ids[0], attention_mask=mask[0], position_ids=VF.compute_position_id_with_mask(mask)[0])
         if self.return_raw_chat:
             out["raw_prompt"] = messages
@@ -147,7 +218,7 @@ def create_rl_dataset(data_paths, data_config, tokenizer, processor=None, is_tra
         n = int(syn.get("num_prompts", data_config.get("train_batch_size", 8) * (4 if is_train else 1)))
         return SyntheticPromptDataset(n, int(syn.get("prompt_length", data_config.get("max_prompt_length", 32))),
                                       int(syn.get("vocab_low", 3)), int(syn.get("vocab_high", 512)),
-                                      seed=int(syn.get("seed", 0)) + (0 if is_train else 7919))
+                                      seed=int(syn.get("seed", 0)) + (0 if is_train else 7919), image=syn.get("image"))
     return RLHFDataset(data_paths, tokenizer, data_config, processor, max_samples)
 
 

@@ -383,6 +383,9 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             me = dist.get_rank(self.rollout_tp_group)
             lo = sum(len(x) for x in parts[:me])
             outs = self.rollout.generate([p for part in parts for p in part], sp)[lo : lo + len(plist)]
+        elif "multi_modal_inputs" in prompts.non_tensor_batch:
+            # vision-language prompts: the placeholder tokens are in the prompt ids, the patches travel beside them
+            outs = self.rollout.generate(plist, sp, mm_inputs=list(prompts.non_tensor_batch["multi_modal_inputs"]))
         else:
             outs = self.rollout.generate(plist, sp)
         R = sp.max_tokens
@@ -461,6 +464,8 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
     def _infer(self, engine, data: DataProto, calculate_entropy: bool, replay_routing: bool = True) -> dict:
         data = self._dev(data)
         d = {k: v for k, v in data.batch.items() if replay_routing or k != "routed_experts"}
+        if "multi_modal_inputs" in data.non_tensor_batch:
+            d["multi_modal_inputs"] = list(data.non_tensor_batch["multi_modal_inputs"])
         d.update({k: v for k, v in data.meta_info.items() if k in ("temperature", "micro_batch_size_per_gpu", "record_routing",
                                                                    "max_token_len_per_gpu", "use_dynamic_bsz")})
         d["calculate_entropy"] = calculate_entropy
@@ -510,6 +515,8 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         for mb in data.make_iterator(mini_batch_size=mini, epochs=int(ac.ppo_epochs), seed=ac.data_loader_seed,
                                      dataloader_kwargs={"shuffle": bool(ac.shuffle)}):
             d = {k: v for k, v in mb.batch.items()}
+            if "multi_modal_inputs" in mb.non_tensor_batch:
+                d["multi_modal_inputs"] = list(mb.non_tensor_batch["multi_modal_inputs"])
             d.update(temperature=data.meta_info.get("temperature", 1.0), calculate_entropy=ac.entropy_coeff != 0,
                      loss_scale_factor=ac.loss_scale_factor)
             with self.actor.train_mode():
