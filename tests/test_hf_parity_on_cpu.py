@@ -26,6 +26,12 @@ FAMILIES = {
                                                                 decoder_sparse_step=1, mlp_only_layers=[], use_sliding_window=False)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(COMMON, num_local_experts=4, num_experts_per_tok=2, sliding_window=None)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(COMMON, pad_token_id=0, sliding_window=None)),
+    # context extensions of the rotary embedding (original context shorter than the test sequences' positions matter for)
+    "llama3_rope": ("LlamaConfig", "LlamaForCausalLM", dict(COMMON, attention_bias=False, rope_scaling=dict(
+        rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=16))),
+    "qwen2_yarn": ("Qwen2Config", "Qwen2ForCausalLM", dict(COMMON, use_sliding_window=False, rope_scaling=dict(
+        rope_type="yarn", factor=4.0, original_max_position_embeddings=32))),
+    "llama_linear": ("LlamaConfig", "LlamaForCausalLM", dict(COMMON, attention_bias=False, rope_scaling=dict(rope_type="linear", factor=2.0))),
 }
 
 
@@ -136,3 +142,24 @@ def test_gradients_match_huggingface_autograd(family):
         assert (got - p.grad).abs().max() / scale < 2e-3, (family, name, float((got - p.grad).abs().max() / scale))
         checked += 1
     assert checked == len(list(hf.named_parameters()))
+
+
+def test_rotary_settings_are_read_from_both_configuration_layouts():
+    from verl_b200.models.config import ModelConfig
+
+    old = dict(COMMON, model_type="llama", rope_theta=500000.0,
+               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192})
+    new = {k: v for k, v in old.items() if k not in ("rope_theta", "rope_scaling")}
+    new["rope_parameters"] = dict(old["rope_scaling"], rope_theta=500000.0)
+    a, b = ModelConfig.from_hf_dict(old), ModelConfig.from_hf_dict(new)
+    assert a.rope_theta == b.rope_theta == 500000.0 and a.rope_scaling == b.rope_scaling and a.rope_scaling["rope_type"] == "llama3"
+    assert a.to_hf_dict()["rope_scaling"]["factor"] == 8.0 and not a.is_generic
+    plain = ModelConfig.from_hf_dict(dict(COMMON, model_type="qwen2", rope_parameters={"rope_type": "default", "rope_theta": 1e6}))
+    assert plain.rope_theta == 1e6 and plain.rope_scaling is None
+    # rules without a hand-scheduled implementation are served by the library module instead of being ignored
+    assert ModelConfig.from_hf_dict(dict(COMMON, model_type="mistral", sliding_window=16)).is_generic
+    assert not ModelConfig.from_hf_dict(dict(COMMON, model_type="mistral", sliding_window=None)).is_generic
+    assert not ModelConfig.from_hf_dict(dict(COMMON, model_type="qwen2", sliding_window=16, use_sliding_window=False)).is_generic
+    assert ModelConfig.from_hf_dict(dict(COMMON, model_type="phi3", rope_scaling={"rope_type": "longrope", "short_factor": [1.0] * 8,
+                                                                                 "long_factor": [2.0] * 8})).is_generic

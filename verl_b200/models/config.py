@@ -31,6 +31,7 @@ class ModelConfig:
     head_dim: Optional[int] = None
     rms_norm_eps: float = 1e-6
     rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None   # context extension of the rotary embedding: {rope_type: linear | llama3 | yarn, factor, ...}
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
     attention_bias: bool = False
@@ -135,6 +136,19 @@ class ModelConfig:
         mt = d.get("model_type", "llama")
         if mt not in NATIVE_FAMILIES:
             return cls._generic_from_hf_dict(d)
+        # rotary settings: older configurations keep ``rope_theta`` + ``rope_scaling`` at the top level, newer ones one
+        # ``rope_parameters`` dict
+        rp, rs = d.get("rope_parameters") or {}, d.get("rope_scaling") or {}
+        theta = rp.get("rope_theta") or d.get("rope_theta") or 10000.0
+        scaling = {**rs, **{k: v for k, v in rp.items() if k != "rope_theta"}}
+        kind = scaling.get("rope_type") or scaling.get("type") or "default"
+        scaling = dict(scaling, rope_type=kind) if kind != "default" else None
+        window = d.get("sliding_window") if d.get("use_sliding_window", mt in ("mistral", "mixtral", "phi3")) else None
+        windowed = window is not None and int(window) < int(d.get("max_position_embeddings", 32768))
+        if kind not in ("default", "linear", "llama3", "yarn") or windowed or (d.get("partial_rotary_factor") or 1.0) != 1.0:
+            # rules the hand-scheduled decoder does not implement (sliding-window attention, other rotary variants): the
+            # library module is exact for them
+            return cls._generic_from_hf_dict(d)
         kw = dict(
             model_type=mt,
             vocab_size=d["vocab_size"],
@@ -145,7 +159,7 @@ class ModelConfig:
             num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
             head_dim=d.get("head_dim"),
             rms_norm_eps=d.get("rms_norm_eps", 1e-6),
-            rope_theta=float(d.get("rope_theta", 10000.0)),
+            rope_theta=float(theta), rope_scaling=scaling,
             max_position_embeddings=d.get("max_position_embeddings", 32768),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             attention_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))),
@@ -212,6 +226,7 @@ class ModelConfig:
             "head_dim": self.head_dim,
             "rms_norm_eps": self.rms_norm_eps,
             "rope_theta": self.rope_theta,
+            **({"rope_scaling": dict(self.rope_scaling)} if self.rope_scaling else {}),
             "max_position_embeddings": self.max_position_embeddings,
             "tie_word_embeddings": self.tie_word_embeddings,
             "attention_bias": self.attention_bias,

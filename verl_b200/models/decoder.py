@@ -322,7 +322,8 @@ class DecoderModel:
     def _ensure_rope(self, n: int) -> None:
         if n > self._rope_len:
             self._rope_len = int(2 ** math.ceil(math.log2(max(n, 16))))
-            self._cos, self._sin = F.rope_table(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, self.device)
+            self._cos, self._sin = F.rope_table(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, self.device, self.cfg.rope_scaling,
+                                                 self.cfg.max_position_embeddings)
 
     def _wgrad(self, w: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> None:
         lora = getattr(w, "lora", None)

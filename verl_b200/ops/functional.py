@@ -143,11 +143,57 @@ def rms_norm_bwd(dy, x, weight, rstd, dres_in, dw_out: torch.Tensor, accumulate:
 
 
 # ----------------------------------------------------------------------------------------------- RoPE
-def rope_table(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """cos/sin tables [max_pos, head_dim/2] in fp32 (HF rotate-half convention)."""
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, max_position_embeddings: int = 0):
+    """(inverse frequencies [head_dim/2] in fp64, factor on cos/sin) for plain rotary embeddings and their context
+    extensions: ``linear`` (positions divided by ``factor``), ``llama3`` (long wavelengths divided by ``factor``, a smooth
+    blend in the band between ``original / low_freq_factor`` and ``original / high_freq_factor``), ``yarn`` (interpolated
+    low frequencies, extrapolated high ones, blended by a ramp between the dimensions that complete ``beta_fast`` and
+    ``beta_slow`` turns inside the original context; cos/sin scaled by ``0.1 ln(factor) + 1`` unless given)."""
+    dims = torch.arange(0, head_dim, 2, dtype=torch.float64)
+    inv = 1.0 / (theta ** (dims / head_dim))
+    kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
+    if kind == "default":
+        return inv, 1.0
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return inv / factor, 1.0
+    original = int(scaling.get("original_max_position_embeddings") or max_position_embeddings)
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        wavelen = 2 * math.pi / inv
+        blend = ((original / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)   # 0: long wavelengths (scaled), 1: short ones (kept)
+        return (1 - blend) * inv / factor + blend * inv, 1.0
+    if kind == "yarn":
+        fast, slow = float(scaling.get("beta_fast") or 32.0), float(scaling.get("beta_slow") or 1.0)
+
+        def turns_dim(turns: float) -> float:   # dimension whose wavelength makes ``turns`` rotations over the original context
+            return head_dim * math.log(original / (turns * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = turns_dim(fast), turns_dim(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0.0, 1.0)
+        inv = inv / factor * ramp + inv * (1 - ramp)
+        att = scaling.get("attention_factor")
+        if att is None:
+            def mscale(f, m=1.0):
+                return 1.0 if f <= 1 else 0.1 * m * math.log(f) + 1.0
+
+            ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+            att = mscale(factor, ms) / mscale(factor, ms_all) if ms and ms_all else mscale(factor)
+        return inv, float(att)
+    raise NotImplementedError(f"rope scaling type {kind!r}")
+
+
+def rope_table(max_pos: int, head_dim: int, theta: float, device, scaling: Optional[dict] = None,
+               max_position_embeddings: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables [max_pos, head_dim/2] in fp32 (HF rotate-half convention), context-extension rules folded in."""
+    inv, att = rope_inv_freq(head_dim, theta, scaling, max_position_embeddings)
     ang = torch.arange(max_pos, dtype=torch.float64).unsqueeze(1) * inv.unsqueeze(0)
-    return ang.cos().float().to(device), ang.sin().float().to(device)
+    return (ang.cos() * att).float().to(device), (ang.sin() * att).float().to(device)
 
 
 def apply_rope_(x: torch.Tensor, positions: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
