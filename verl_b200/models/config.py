@@ -269,7 +269,10 @@ PRESETS: dict[str, ModelConfig] = {
                               eos_token_id=151645, pad_token_id=151643),
     "llama-3.1-8b": ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
                                 num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
-                                rope_theta=5e5, rms_norm_eps=1e-5, eos_token_id=128001, pad_token_id=128001),
+                                rope_theta=5e5, rms_norm_eps=1e-5, eos_token_id=128001, pad_token_id=128001,
+                                max_position_embeddings=131072,
+                                rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                              "original_max_position_embeddings": 8192}),
     "qwen3-30b-a3b": ModelConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
                                  num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
                                  rope_theta=1e6, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
