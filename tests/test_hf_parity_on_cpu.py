@@ -163,3 +163,17 @@ def test_rotary_settings_are_read_from_both_configuration_layouts():
     assert not ModelConfig.from_hf_dict(dict(COMMON, model_type="qwen2", sliding_window=16, use_sliding_window=False)).is_generic
     assert ModelConfig.from_hf_dict(dict(COMMON, model_type="phi3", rope_scaling={"rope_type": "longrope", "short_factor": [1.0] * 8,
                                                                                  "long_factor": [2.0] * 8})).is_generic
+
+
+def test_architecture_variants_without_a_native_implementation_use_the_library_module():
+    from verl_b200.models.config import ModelConfig
+
+    base = {k: v for k, v in COMMON.items() if k != "rope_theta"}
+    generic = lambda **kw: ModelConfig.from_hf_dict(dict(base, **kw)).is_generic
+    assert generic(model_type="llama", attention_bias=True)          # biases the output projection as well
+    assert not generic(model_type="qwen2", attention_bias=True)
+    assert generic(model_type="llama", mlp_bias=True) and generic(model_type="llama", hidden_act="gelu")
+    assert generic(model_type="qwen3_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, mlp_only_layers=[0])
+    assert generic(model_type="qwen2_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=2)
+    assert generic(model_type="phi3", partial_rotary_factor=0.5)
+    assert not generic(model_type="qwen3") and not generic(model_type="llama")

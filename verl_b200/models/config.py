@@ -145,7 +145,14 @@ class ModelConfig:
         scaling = dict(scaling, rope_type=kind) if kind != "default" else None
         window = d.get("sliding_window") if d.get("use_sliding_window", mt in ("mistral", "mixtral", "phi3")) else None
         windowed = window is not None and int(window) < int(d.get("max_position_embeddings", 32768))
-        if kind not in ("default", "linear", "llama3", "yarn") or windowed or (d.get("partial_rotary_factor") or 1.0) != 1.0:
+        odd = (
+            (d.get("partial_rotary_factor") or 1.0) != 1.0
+            or str(d.get("hidden_act", "silu")) not in ("silu", "swish")
+            or bool(d.get("mlp_bias", False))
+            or (bool(d.get("attention_bias", False)) and mt not in ("qwen2", "qwen2_moe"))   # these families bias the output projection too
+            or int(d.get("decoder_sparse_step", 1) or 1) != 1 or len(d.get("mlp_only_layers") or []) > 0  # dense layers among the sparse ones
+        )
+        if kind not in ("default", "linear", "llama3", "yarn") or windowed or odd:
             # rules the hand-scheduled decoder does not implement (sliding-window attention, other rotary variants): the
             # library module is exact for them
             return cls._generic_from_hf_dict(d)
