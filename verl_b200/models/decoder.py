@@ -312,6 +312,7 @@ class DecoderModel:
         self.pre_layer_hook = pre_layer_hook
         self.post_layer_backward_hook = post_layer_backward_hook
         self.kv_hook: Optional[Callable[[int, torch.Tensor, torch.Tensor], None]] = None  # prefill: receives rotated K, V
+        self.prefix_kv: Optional[Callable[[int], tuple]] = None  # prefill: (cached K, cached V, cached length per sequence) of a layer
         self.device = params.flat.device
         self._rope_len = 0
         self._cos = self._sin = None
@@ -400,6 +401,11 @@ class DecoderModel:
             attn2 = attn_e.index_select(0, batch.collapse_index).reshape(T, Q)
             if S is not None:
                 S.update(qkv=qkv, attn=attn2, lse=lse, attn_e=attn_e)
+        elif self.prefix_kv is not None:
+            # prefill behind a prefix-cache hit: the batch holds the uncached tail of every prompt
+            assert S is None, "cached prefixes are a forward-only (rollout) feature"
+            kp, vp, plens = self.prefix_kv(layer_idx)
+            attn2, lse = F.attention_with_prefix(q.contiguous(), k.contiguous(), v.contiguous(), kp, vp, self._cu_cpu(batch), plens).reshape(T, Q), None
         else:
             attn, lse = F.attention_varlen(q, k, v, cu, batch.max_seqlen)
             attn2 = attn.reshape(T, Q)

@@ -447,6 +447,29 @@ def attention_query_slice_bwd(dout, q, k, v, cu_seqlens, q_start: int, scale: Op
         return torch.autograd.grad(o, (q_, k_, v_), dout, allow_unused=True)
 
 
+def attention_with_prefix(q, k, v, k_prefix, v_prefix, cu_seqlens, prefix_lens, scale: Optional[float] = None):
+    """Causal GQA attention of packed sequences whose first ``prefix_lens[i]`` positions are already in a cache: ``q``/``k``/
+    ``v`` [T, heads, hd] hold the new tokens only (``cu_seqlens`` over them), ``k_prefix``/``v_prefix`` [sum(prefix_lens), nkv, hd]
+    the cached keys / values in sequence order. Every new token attends to its sequence's whole prefix and to the new tokens up
+    to itself. Library attention per sequence (the path of a prefix-cache hit at prefill; forward only)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    nh, nkv = q.shape[1], k.shape[1]
+    cu = cu_seqlens.tolist()
+    out = torch.empty_like(q)
+    p0 = 0
+    with torch.no_grad():
+        for i, (s0, s1) in enumerate(zip(cu[:-1], cu[1:])):
+            m, n = int(prefix_lens[i]), s1 - s0
+            kk = torch.cat([k_prefix[p0 : p0 + m], k[s0:s1]], 0).transpose(0, 1).unsqueeze(0)
+            vv = torch.cat([v_prefix[p0 : p0 + m], v[s0:s1]], 0).transpose(0, 1).unsqueeze(0)
+            qq = q[s0:s1].transpose(0, 1).unsqueeze(0)
+            mask = torch.ones(n, m + n, dtype=torch.bool, device=q.device).tril(diagonal=m)
+            o = F.scaled_dot_product_attention(qq, kk, vv, attn_mask=mask, scale=scale, enable_gqa=nkv != nh)
+            out[s0:s1] = o.squeeze(0).transpose(0, 1)
+            p0 += m
+    return out
+
+
 def kv_append_(k, v, slots, k_cache, v_cache) -> None:
     if k.is_cuda:
         _ops().kv_append_(k, v, slots, k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1]),

@@ -335,6 +335,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
 
             self.rollout = RolloutEngine(arch, src.params, max_num_seqs=rc.max_num_seqs * tp, tp_group=self.rollout_tp_group,
                                          record_routing=(self._router_replay_mode() == "R3"),
+                                         enable_prefix_caching=bool(rc.get("enable_prefix_caching", False)),
                                          quantization=(rc.get("quantization") if tp == 1 else None),
                                          max_num_batched_tokens=rc.max_num_batched_tokens, max_model_len=max_len + 1,
                                          block_size=rc.block_size, gpu_memory_utilization=rc.gpu_memory_utilization,

@@ -29,7 +29,7 @@ from __future__ import annotations
 import math
 import time
 import zlib
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -77,6 +77,7 @@ class _Request:
     blocks: list[int] = field(default_factory=list)
     arrival: float = 0.0
     handoff: Optional[dict] = None  # prefilled elsewhere: KV content, first token and sampler state arrive with the request
+    cached: int = 0                 # leading prompt tokens whose pages came from the prefix cache
 
 
 class RolloutEngine:
@@ -84,7 +85,8 @@ class RolloutEngine:
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 64,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, eos_token_id=None,
                  valid_vocab_size: int = 0, use_cuda_graph: bool = True, sync_interval: int = 16, seed: int = 0,
-                 tp_group=None, quantization: Optional[str] = None, share_prefill: bool = True, record_routing: bool = False):
+                 tp_group=None, quantization: Optional[str] = None, share_prefill: bool = True, record_routing: bool = False,
+                 enable_prefix_caching: bool = False):
         """``tp_group``: process group of the ranks that serve the same requests tensor-parallel (each holds the
         full replicated weights and uses its shard of them in place; see ``TensorParallelShard``). All ranks of the
         group must be fed the same requests in the same order."""
@@ -92,6 +94,14 @@ class RolloutEngine:
         assert quantization in (None, "", "fp8"), f"unsupported rollout quantization: {quantization}"
         self.quantization = quantization or None
         self.share_prefill = bool(share_prefill)
+        # Prefix cache across requests: full pages stay indexed by a chain hash of their tokens after their last user has
+        # finished (evicted least-recently-used when fresh pages run out); a new prompt that starts with cached pages (the
+        # next turn of a conversation, a shared system prompt) points at them and is prefilled from the first uncached token.
+        # Emptied with every weight update. Off with routing recording (a cached page has no routing record).
+        self.enable_prefix_caching = bool(enable_prefix_caching) and not (bool(record_routing) and cfg.is_moe)
+        self._page_of_hash: dict = {}      # chain hash -> page
+        self._hash_of_page: dict = {}      # page -> chain hash
+        self._idle_cached: "OrderedDict[int, None]" = OrderedDict()   # indexed pages without a user, oldest first
         # mixture-of-experts models: return the experts every router picked for every token that went through the model
         # (``RequestOutput.extra_fields["routed_experts"]``, [prompt + generated - 1, layers, k]) for router replay
         self.record_routing = bool(record_routing) and cfg.is_moe
@@ -190,13 +200,47 @@ class RolloutEngine:
         shared = self._block_users
         for b in blocks:
             n = shared.get(b)
-            if n is None:
-                self.free_blocks.append(b)
-            elif n <= 1:
-                del shared[b]
-                self.free_blocks.append(b)
-            else:
+            if n is not None and n > 1:
                 shared[b] = n - 1
+                continue
+            if n is not None:
+                del shared[b]
+            if b in self._hash_of_page:
+                self._idle_cached[b] = None      # content stays valid: reusable until evicted
+            else:
+                self.free_blocks.append(b)
+
+    def _take_block(self) -> int:
+        """A fresh page: from the free list, else the least recently used idle page of the prefix cache."""
+        if self.free_blocks:
+            return self.free_blocks.pop()
+        b, _ = self._idle_cached.popitem(last=False)
+        del self._page_of_hash[self._hash_of_page.pop(b)]
+        return b
+
+    def _page_hashes(self, tokens: Sequence[int], n_pages: int) -> list:
+        """Chain hash of each of the first ``n_pages`` full pages of ``tokens`` (a page's hash covers everything before it)."""
+        import hashlib
+        from array import array
+
+        out, h = [], b""
+        for i in range(n_pages):
+            h = hashlib.blake2b(h + array("q", tokens[i * self.bs : (i + 1) * self.bs]).tobytes(), digest_size=16).digest()
+            out.append(h)
+        return out
+
+    def _index_pages(self, tokens: Sequence[int], blocks: list[int], n_valid: int) -> None:
+        """Index the pages of ``blocks`` that ``tokens[:n_valid]`` fill completely (their content is final)."""
+        for i, h in enumerate(self._page_hashes(tokens, min(n_valid // self.bs, len(blocks)))):
+            b = blocks[i]
+            if h not in self._page_of_hash and b not in self._hash_of_page:
+                self._page_of_hash[h] = b
+                self._hash_of_page[b] = h
+
+    def _drop_prefix_cache(self) -> None:
+        self._page_of_hash.clear()
+        self._hash_of_page.clear()
+        self._idle_cached.clear()
 
     def release_kv_cache(self) -> None:
         assert not self.running, "cannot release the KV cache with sequences in flight"
@@ -204,6 +248,7 @@ class RolloutEngine:
         self._graph = None
         self.free_blocks = []
         self._block_users = {}
+        self._drop_prefix_cache()
         if self.is_cuda:
             torch.cuda.empty_cache()
 
@@ -213,6 +258,7 @@ class RolloutEngine:
         if self.quantization == "fp8":
             self.model.quantize_linear_weights_fp8()  # the bf16 weights changed: refresh the e4m3 copies
             self._graph = None
+        self._drop_prefix_cache()
         if self.kv is not None:
             self.free_blocks = list(range(self.num_blocks - 1, -1, -1))
             self._block_users = {}
@@ -289,7 +335,18 @@ class RolloutEngine:
         while self.waiting and self.free_slots:
             r = self.waiting[0]
             need = (len(r.prompt) + r.params.max_tokens + self.bs - 1) // self.bs
-            if need > len(self.free_blocks) or (batch and tokens + len(r.prompt) > self.max_batched):
+            hit: list[int] = []
+            if self.enable_prefix_caching and r.handoff is None:
+                # longest run of leading pages that is in the cache; the last prompt token is always computed (its output
+                # is the first sampling distribution)
+                for h in self._page_hashes(r.prompt, (len(r.prompt) - 1) // self.bs):
+                    b = self._page_of_hash.get(h)
+                    if b is None:
+                        break
+                    hit.append(b)
+            idle_hit = sum(1 for b in hit if b in self._idle_cached)
+            if need - len(hit) > len(self.free_blocks) + len(self._idle_cached) - idle_hit or \
+                    (batch and tokens + len(r.prompt) - len(hit) * self.bs > self.max_batched):
                 break
             want = (r.params.temperature, r.params.top_k, r.params.top_p)
             idle = not self.running and not batch
@@ -300,9 +357,15 @@ class RolloutEngine:
                 break
             self.waiting.popleft()
             r.slot = self.free_slots.pop()
-            r.blocks = [self.free_blocks.pop() for _ in range(need)]
+            for b in hit:                       # cached pages gain a user
+                if b in self._idle_cached:
+                    del self._idle_cached[b]
+                else:
+                    self._block_users[b] = self._block_users.get(b, 1) + 1
+            r.cached = len(hit) * self.bs
+            r.blocks = hit + [self._take_block() for _ in range(need - len(hit))]
             batch.append(r)
-            tokens += len(r.prompt)
+            tokens += len(r.prompt) - r.cached
         return batch
 
     # ------------------------------------------------------------------------------------ prefill / decode disaggregation
@@ -422,23 +485,33 @@ class RolloutEngine:
                 if li == i or nfull == 0:
                     continue
                 own, shared = r.blocks[:nfull], reqs[li].blocks[:nfull]
-                self.free_blocks.extend(own)
+                self._release_blocks(own)
                 r.blocks[:nfull] = shared
                 for b in shared:
                     self._block_users[b] = self._block_users.get(b, 1) + 1
         bt_rows = torch.zeros(len(reqs), self.max_blocks_per_seq, dtype=torch.int32)
         for i, r in enumerate(reqs):
             bt_rows[i, : len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
-        ids = torch.tensor([t for i in leaders for t in reqs[i].prompt], dtype=torch.int64)
+        skip = [reqs[i].cached for i in leaders]        # tokens whose pages came from the prefix cache: not recomputed
+        ids = torch.tensor([t for i in leaders for t in reqs[i].prompt[reqs[i].cached:]], dtype=torch.int64)
         slot_rows = []
         for i in leaders:
-            p = torch.arange(lens[i])
+            p = torch.arange(reqs[i].cached, lens[i])
             slot_rows.append(bt_rows[i, p // self.bs].long() * self.bs + p % self.bs)
         if self.is_cuda:
             ids, slot_map = ids.pin_memory().to(dev, non_blocking=True), torch.cat(slot_rows).pin_memory().to(dev, non_blocking=True)
         else:
             slot_map = torch.cat(slot_rows)
-        batch = PackedBatch.from_lengths(ids, [lens[i] for i in leaders], device=dev)
+        batch = PackedBatch.from_lengths(ids, [lens[i] - c for i, c in zip(leaders, skip)], device=dev)
+        if any(skip):
+            batch.positions = torch.cat([torch.arange(c, lens[i], dtype=torch.int32) for i, c in zip(leaders, skip)]).to(dev)
+            pages = torch.cat([bt_rows[i, : c // self.bs].long() for i, c in zip(leaders, skip)])
+            cached_slots = (pages.unsqueeze(1) * self.bs + torch.arange(self.bs).unsqueeze(0)).reshape(-1).to(dev)
+            nkv_l, hd = self.kv.shape[-2], self.kv.shape[-1]
+            self.model.prefix_kv = lambda layer: (self.kv[layer, 0].view(-1, nkv_l, hd)[cached_slots],
+                                                  self.kv[layer, 1].view(-1, nkv_l, hd)[cached_slots], skip)
+            self.model._ensure_rope(max(lens) + 1)
+            self.stats["prefix_cache_hit_tokens"] = self.stats.get("prefix_cache_hit_tokens", 0) + sum(skip)
         self._prefill_slots = slot_map
         if self.record_routing:
             from ....models.decoder import RouterReplay
@@ -448,6 +521,10 @@ class RolloutEngine:
             h = self.model.forward_hidden(batch)
         finally:
             self._prefill_slots = None
+            self.model.prefix_kv = None
+        if self.enable_prefix_caching:
+            for i in leaders:
+                self._index_pages(reqs[i].prompt, reqs[i].blocks, lens[i])
         if self.record_routing:
             routed = self.model.router_replay.stacked(list(range(self.cfg.num_hidden_layers))).to(torch.int16).cpu()
             self.model.router_replay = None
@@ -511,7 +588,7 @@ class RolloutEngine:
         self.active[slots] = ~done
         for r in reqs:
             self.running[r.slot] = r
-        self.stats["prefill_tokens"] += sum(lens)
+        self.stats["prefill_tokens"] += sum(lens) - sum(skip)
         self.stats["prefill_s"] += time.time() - t0
 
     def _penalise(self, logits: torch.Tensor, slots=None) -> torch.Tensor:
@@ -670,6 +747,10 @@ class RolloutEngine:
             self.finished.append(RequestOutput(r.rid, r.prompt, t, lps[j, :n].tolist() if r.params.logprobs else None, reason,
                                                extra_fields=extra))
             self.stats["generated_tokens"] += n
+            if self.enable_prefix_caching and n > 1:
+                # the next turn of a conversation starts with this prompt + response: every generated token but the last
+                # has gone through the model, its keys / values are in the pages
+                self._index_pages(r.prompt + t[:-1], r.blocks, len(r.prompt) + n - 1)
             self._release_blocks(r.blocks)
             self.free_slots.append(s)
         self.active[idx] = False
