@@ -53,9 +53,11 @@ class ReplayBuffer:
         return self.mode != "sync"
 
     # ---- producer side
-    def add_prompt(self, uid: str, payload: dict, model_version: int, partition_id: str = "train") -> None:
+    def add_prompt(self, uid: str, payload: dict, model_version: int, partition_id: str = "train", n: Optional[int] = None) -> None:
+        """``n``: sessions that complete this prompt's group (default: the buffer's group size; validation prompts usually
+        run one)."""
         self.q.put(uid, {"prompt": payload}, {"kind": "prompt", "status": PENDING, "start_version": int(model_version),
-                                               "done": 0, "failed": 0}, partition_id)
+                                               "done": 0, "failed": 0, "n": int(n or self.n)}, partition_id)
 
     def mark_running(self, uid: str, partition_id: str = "train") -> None:
         self.q.set_tags(uid, {"status": RUNNING}, partition_id)
@@ -70,7 +72,7 @@ class ReplayBuffer:
             t = self.q.get_tags(uid, partition_id)
             done, bad = t.get("done", 0) + 1, t.get("failed", 0) + int(failed)
             upd = {"done": done, "failed": bad, "end_version": max(int(model_version), t.get("end_version", 0))}
-            if done >= self.n:
+            if done >= int(t.get("n", self.n)):
                 upd["status"] = FAILURE if bad else FINISHED
             self.q.set_tags(uid, upd, partition_id)
         return key
