@@ -370,6 +370,17 @@ class ModelParallelEngine(NativeEngine):
         full = self.gather_full_params()
         yield from full.hf_views()
 
+    def export_hf_delta(self, update_snapshot: bool = True):
+        """What changed in this rank's shard since the previous call (or since the first call, which takes the snapshot), as
+        ``(hf_name, positions, values)`` records in full-tensor coordinates: the sparse alternative to
+        ``gather_full_params`` for keeping a remote copy of the weights current (``delta_export.py``)."""
+        if getattr(self, "_delta_exporter", None) is None:
+            from .delta_export import ShardDeltaExporter
+
+            self._delta_exporter = ShardDeltaExporter(self)
+            return []
+        return self._delta_exporter.export(update_snapshot)
+
     def local_named_tensors(self):
         """(full-model name of the shard, local tensor) pairs: what the model-parallel checkpoint layout stores."""
         for m in self.maps:
