@@ -29,7 +29,7 @@ def test_query_slice_attention_matches_full_attention():
     assert torch.allclose(dks, dk, atol=1e-5) and torch.allclose(dvs, dv, atol=1e-5)
 
 
-def _proc(rank, world, port, cp, q):
+def _proc(rank, world, port, cp, q, mode="zigzag"):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                           VERL_ENGINE_DEVICE="cpu")
@@ -43,10 +43,10 @@ def _proc(rank, world, port, cp, q):
         from verl_b200.workers.utils.losses import sft_loss
 
         initialize_global_process_group()
-        ec = FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2, context_parallel_size=cp)
+        ec = FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2, context_parallel_size=cp, context_parallel_mode=mode)
         eng = NativeEngineWithLMHead(get_preset("tiny-llama"), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05))
         eng.initialize()
-        assert isinstance(eng.model.sp, ContextParallel)
+        assert isinstance(eng.model.sp, ContextParallel) and eng.model.sp.zigzag == (mode == "zigzag")
         dp = world // cp
         shard = {k: v.chunk(dp)[rank // cp] for k, v in _data().items()}
         out = eng.train_batch(dict(shard), partial(sft_loss, None))
@@ -58,8 +58,8 @@ def _proc(rank, world, port, cp, q):
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-@pytest.mark.parametrize("world,cp", [(2, 2), (3, 3), (4, 2)])
-def test_context_parallel_matches_single_rank(world, cp):
+@pytest.mark.parametrize("world,cp,mode", [(2, 2, "zigzag"), (3, 3, "zigzag"), (4, 2, "zigzag"), (2, 2, "contiguous")])
+def test_context_parallel_matches_single_rank(world, cp, mode):
     import torch.multiprocessing as mp
 
     ref_norm, ref_lp, ref_flat = _reference()
@@ -68,7 +68,7 @@ def test_context_parallel_matches_single_rank(world, cp):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_proc, args=(r, world, port, cp, q)) for r in range(world)]
+    ps = [ctx.Process(target=_proc, args=(r, world, port, cp, q, mode)) for r in range(world)]
     for p in ps:
         p.start()
     res = dict(q.get(timeout=300) for _ in range(world))
@@ -183,3 +183,26 @@ def test_tensor_parallel_times_context_parallel():
     with pytest.raises(NotImplementedError, match="pipeline"):
         EngineRegistry.new("language_model", "megatron", model_config=get_preset("tiny-llama"),
                            engine_config=McoreEngineConfig(pipeline_model_parallel_size=2, context_parallel_size=2), optimizer_config=None)
+
+
+def test_zigzag_layout_bookkeeping():
+    from verl_b200.models.decoder import ContextParallel
+
+    total, size = 24, 3
+    seen = []
+    for r in range(size):
+        cp = ContextParallel(None, r, size)
+        assert cp.pad_multiple() == 6 and cp.chunks(total) == [(4 * r, 4 * r + 4), (4 * (5 - r), 4 * (5 - r) + 4)]
+        rows = cp.local_rows(total)
+        seen.append(rows)
+        pos = torch.tensor([0, 5, 9, 14, 19, 23])
+        mine, local = cp.local_of(pos, total)
+        assert torch.equal(rows[local], pos[mine])
+    assert torch.equal(torch.cat(seen).sort().values, torch.arange(total))         # every token has exactly one owner
+    # rank-major gathered rows -> stream order and back
+    cp = ContextParallel(None, 1, size)
+    gathered = torch.cat(seen)                                                    # what an all-gather of the rows delivers
+    order = cp._stream_order(total, "cpu")
+    assert torch.equal(gathered[order], torch.arange(total))
+    flat = ContextParallel(None, 1, size, zigzag=False)
+    assert flat.pad_multiple() == 3 and flat.chunks(total) == [(8, 16)] and flat._stream_order(total, "cpu") is None

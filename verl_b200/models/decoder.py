@@ -115,6 +115,20 @@ class UlyssesSequenceParallel:
         n = total // self.size
         return slice(self.rank * n, (self.rank + 1) * n)
 
+    def pad_multiple(self) -> int:
+        """The packed stream is padded to a multiple of this many tokens."""
+        return self.size
+
+    def local_rows(self, total: int, device=None):
+        """Stream positions of this rank's rows, in local order (a slice here; an index tensor for split layouts)."""
+        return self.local_slice(total)
+
+    def local_of(self, positions: torch.Tensor, total: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """(mask of the stream ``positions`` this rank holds, their local row numbers)."""
+        sl = self.local_slice(total)
+        mine = (positions >= sl.start) & (positions < sl.stop)
+        return mine, positions[mine] - sl.start
+
     def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
         """[T/size, heads, hd] (my tokens, all heads) -> [T, heads/size, hd] (all tokens, my heads)."""
         import torch.distributed as dist
@@ -146,8 +160,56 @@ class ContextParallel(UlyssesSequenceParallel):
     divisibility constraint on the number of key/value heads (grouped-query models with few KV heads, long contexts).
 
     Parity target: Megatron context parallelism as configured by ``verl/workers/config/engine.py``
-    (``context_parallel_size``) with the contiguous token split of ``verl/models/mcore/util.py:62-211``; the zigzag
-    (load-balanced) split of that file is not implemented."""
+    (``context_parallel_size``) with the zigzag (load-balanced) and contiguous token splits of
+    ``verl/models/mcore/util.py:62-211``."""
+
+    def __init__(self, group, rank: int, size: int, zigzag: bool = True):
+        super().__init__(group, rank, size)
+        # zigzag: the stream is cut into 2 * size chunks and rank i holds chunks i and 2 * size - 1 - i, which evens out the
+        # causal attention work (late tokens see more keys than early ones); contiguous: rank i holds the i-th 1/size
+        self.zigzag = bool(zigzag) and size > 1
+
+    def pad_multiple(self) -> int:
+        return 2 * self.size if self.zigzag else self.size
+
+    def chunks(self, total: int) -> list[tuple[int, int]]:
+        """[start, stop) stream ranges of this rank's rows, in local order."""
+        if not self.zigzag:
+            sl = self.local_slice(total)
+            return [(sl.start, sl.stop)]
+        assert total % (2 * self.size) == 0, "the packed stream must be padded to a multiple of twice the context-parallel size"
+        c = total // (2 * self.size)
+        a, b = self.rank, 2 * self.size - 1 - self.rank
+        return [(a * c, (a + 1) * c), (b * c, (b + 1) * c)]
+
+    def local_rows(self, total: int, device=None):
+        if not self.zigzag:
+            return self.local_slice(total)
+        return torch.cat([torch.arange(lo, hi, device=device) for lo, hi in self.chunks(total)])
+
+    def local_of(self, positions: torch.Tensor, total: int) -> tuple[torch.Tensor, torch.Tensor]:
+        if not self.zigzag:
+            return super().local_of(positions, total)
+        mine = torch.zeros_like(positions, dtype=torch.bool)
+        local = torch.zeros_like(positions)
+        off = 0
+        for lo, hi in self.chunks(total):
+            sel = (positions >= lo) & (positions < hi)
+            mine |= sel
+            local = torch.where(sel, positions - lo + off, local)
+            off += hi - lo
+        return mine, local[mine]
+
+    def _stream_order(self, total: int, device) -> Optional[torch.Tensor]:
+        """Row of the rank-major gathered tensor that holds stream chunk j, for every j (None: already in order)."""
+        if not self.zigzag:
+            return None
+        c = total // (2 * self.size)
+        src = []
+        for j in range(2 * self.size):
+            r, half = (j, 0) if j < self.size else (2 * self.size - 1 - j, 1)
+            src.append(torch.arange((2 * r + half) * c, (2 * r + half + 1) * c, device=device))
+        return torch.cat(src)
 
     def gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
         """[T/size, ...] of every rank -> [T, ...] in stream order."""
@@ -159,12 +221,18 @@ class ContextParallel(UlyssesSequenceParallel):
             dist.all_gather_into_tensor(out, x, group=self.group)
         else:
             dist.all_gather(list(out.chunk(self.size, 0)), x, group=self.group)
-        return out
+        order = self._stream_order(out.shape[0], x.device)
+        return out if order is None else out.index_select(0, order)
 
     def scatter_sum(self, x: torch.Tensor) -> torch.Tensor:
         """Sum of every rank's [T, ...] contribution, this rank's [T/size, ...] rows of it."""
         import torch.distributed as dist
 
+        order = self._stream_order(x.shape[0], x.device)
+        if order is not None:            # back to the rank-major layout the collective scatters
+            rank_major = torch.empty_like(x)
+            rank_major.index_copy_(0, order, x)
+            x = rank_major
         x = x.contiguous()
         n = x.shape[0] // self.size
         if x.is_cuda:
@@ -372,7 +440,7 @@ class DecoderModel:
             k.copy_(kn.view(T, nkv, hd))
             if S is not None:
                 S.update(q_pre=qp, k_pre=kp, rstd_q=rq, rstd_k=rk)
-        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_slice(batch.num_tokens)]
+        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_rows(batch.num_tokens, batch.positions.device)]
         F.apply_rope_(q, pos, self._cos, self._sin)
         F.apply_rope_(k, pos, self._cos, self._sin)
         if self.kv_hook is not None:
@@ -382,11 +450,14 @@ class DecoderModel:
         if isinstance(self.sp, ContextParallel):
             assert batch.expand_index is None, "context parallelism and shared-prefix packing are exclusive"
             kf, vf = self.sp.gather_tokens(k), self.sp.gather_tokens(v)
-            lo = self.sp.local_slice(batch.num_tokens).start
-            attn = F.attention_query_slice(q.contiguous(), kf, vf, self._cu_cpu(batch), lo)
-            attn2, lse = attn.reshape(T, Q), None
+            spans, cu_cpu, qc, row = self.sp.chunks(batch.num_tokens), self._cu_cpu(batch), q.contiguous(), 0
+            parts = []
+            for lo, hi in spans:         # one or two contiguous runs of stream positions
+                parts.append(F.attention_query_slice(qc[row : row + hi - lo], kf, vf, cu_cpu, lo))
+                row += hi - lo
+            attn2, lse = torch.cat(parts, 0).reshape(T, Q), None
             if S is not None:
-                S.update(qkv=qkv, attn=attn2, lse=None, cp_full=(kf, vf, lo))
+                S.update(qkv=qkv, attn=attn2, lse=None, cp_full=(kf, vf, spans))
         elif self.sp is not None:
             assert batch.expand_index is None, "sequence parallelism and shared-prefix packing are exclusive"
             qf, kf, vf = self.sp.seq_to_heads(q.contiguous()), self.sp.seq_to_heads(k.contiguous()), self.sp.seq_to_heads(v.contiguous())
@@ -452,8 +523,15 @@ class DecoderModel:
         v = qkv[:, Q + KV :].view(T, nkv, hd)
         cu = batch.cu_seqlens if q.is_cuda and F._ATTN_IMPL["bwd"] is not None and lse is not None else self._cu_cpu(batch)
         if isinstance(self.sp, ContextParallel):
-            kf, vf, lo = S["cp_full"]
-            dq, dk_f, dv_f = F.attention_query_slice_bwd(g_attn.view(T, nh, hd), q.contiguous(), kf, vf, self._cu_cpu(batch), lo)
+            kf, vf, spans = S["cp_full"]
+            ga, qc, cu_cpu, row = g_attn.view(T, nh, hd), q.contiguous(), self._cu_cpu(batch), 0
+            dqs, dk_f, dv_f = [], 0, 0
+            for lo, hi in spans:
+                a, b, c = F.attention_query_slice_bwd(ga[row : row + hi - lo], qc[row : row + hi - lo], kf, vf, cu_cpu, lo)
+                dqs.append(a)
+                dk_f, dv_f = dk_f + b, dv_f + c
+                row += hi - lo
+            dq = torch.cat(dqs, 0)
             # every rank's queries contribute to the gradients of all the keys / values they saw
             dk, dv = self.sp.scatter_sum(dk_f.float()).to(q.dtype), self.sp.scatter_sum(dv_f.float()).to(q.dtype)
         elif self.sp is not None:
@@ -482,7 +560,7 @@ class DecoderModel:
         gq.copy_(dq)
         gk.copy_(dk)
         g_qkv[:, Q + KV :].view(T, nkv, hd).copy_(dv)
-        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_slice(batch.num_tokens)]
+        pos = batch.positions if self.sp is None else batch.positions[self.sp.local_rows(batch.num_tokens, batch.positions.device)]
         F.apply_rope_(gq, pos, self._cos, self._sin, backward=True)
         F.apply_rope_(gk, pos, self._cos, self._sin, backward=True)
         if cfg.qk_norm:
@@ -981,7 +1059,7 @@ class DecoderModel:
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(-1, "forward")
         if cfg.has_embedding:
-            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
+            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_rows(batch.num_tokens, batch.input_ids.device)]
             a = F.embedding(ids, self.params["embed_tokens.weight"])
             if self.tsp is not None:
                 a = self.tsp.slice(a)
@@ -1049,7 +1127,7 @@ class DecoderModel:
         if getattr(emb, "main_grad", None) is not None:
             if self.pre_layer_hook is not None:
                 self.pre_layer_hook(-1, "backward")
-            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_slice(batch.num_tokens)]
+            ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_rows(batch.num_tokens, batch.input_ids.device)]
             if self.tsp is not None:
                 ids = self.tsp.slice(ids)  # padding rows carry a zero gradient
             F.embedding_bwd_(ids, g, emb.main_grad)

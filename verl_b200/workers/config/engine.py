@@ -62,6 +62,7 @@ class FSDPEngineConfig(EngineConfig):
     # context parallelism: blocks of this many data-parallel ranks split the tokens of the same micro-batches and exchange
     # keys / values around attention (no constraint on the number of KV heads; exclusive with Ulysses)
     context_parallel_size: int = 1
+    context_parallel_mode: str = "zigzag"   # zigzag (rank i holds chunks i and 2 cp - 1 - i of the stream: balanced causal work) | contiguous
     zero_stage: int = 2
     enable_gradient_checkpointing: bool = True
     enable_activation_offload: bool = False
@@ -86,6 +87,7 @@ class McoreEngineConfig(EngineConfig):
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: Optional[int] = None
     context_parallel_size: int = 1
+    context_parallel_mode: str = "zigzag"
     sequence_parallel: bool = True      # token-sliced residual stream inside the tensor-parallel group (on with TP > 1)
     use_distributed_optimizer: bool = True
     use_dist_checkpointing: bool = False

@@ -295,7 +295,12 @@ class NativeEngine(BaseEngine):
                 g0 = self.rank // self.sp_size * self.sp_size
                 self.sp_group = dist.new_group(pool[g0 : g0 + self.sp_size], use_local_synchronization=True)
                 self.sp_rank = self.rank - g0
-            self.model.sp = (ContextParallel if self.cp_size > 1 else UlyssesSequenceParallel)(self.sp_group, self.sp_rank, self.sp_size)
+            if self.cp_size > 1:
+                mode = str(getattr(ec, "context_parallel_mode", "zigzag") or "zigzag")
+                assert mode in ("zigzag", "contiguous"), f"context_parallel_mode {mode!r}"
+                self.model.sp = ContextParallel(self.sp_group, self.sp_rank, self.sp_size, zigzag=(mode == "zigzag"))
+            else:
+                self.model.sp = UlyssesSequenceParallel(self.sp_group, self.sp_rank, self.sp_size)
         # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
         self._share_prefix = (bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
                               and self.sp_size == 1 and not self.arch.is_generic)
@@ -552,7 +557,7 @@ class NativeEngine(BaseEngine):
         """Sequence-parallel micro-batch: this rank evaluates the head on the response positions inside its slice of the
         (padded) token stream; the [b, R] outputs are completed by a sum over the block. Gradients flow only into the
         locally computed entries, which is exactly this rank's share of the block's loss."""
-        sp, T = self.sp_size, batch.num_tokens
+        sp, T = self.model.sp.pad_multiple(), batch.num_tokens
         pad = (-T) % sp
         if pad:
             dev = batch.input_ids.device
@@ -562,10 +567,9 @@ class NativeEngine(BaseEngine):
             batch = PackedBatch(input_ids=ids, positions=pos, cu_seqlens=cu_cpu.to(dev), max_seqlen=max(batch.max_seqlen, pad),
                                 cu_seqlens_cpu=cu_cpu)
             labels = torch.cat([labels, labels.new_zeros(pad)])
-        sl = self.model.sp.local_slice(batch.num_tokens)
         positions = resp_index[resp_valid]
-        mine = (positions >= sl.start) & (positions < sl.stop)
-        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=positions[mine] - sl.start,
+        mine, local_pos = self.model.sp.local_of(positions, batch.num_tokens)
+        lp, ent = self.model.forward_logprobs(batch, labels, temperature, need_grad=need_grad, positions=local_pos,
                                               position_labels=labels[positions[mine]])
         flat_idx = resp_valid.reshape(-1).nonzero().squeeze(-1)[mine]
         n_out = resp_valid.numel()
