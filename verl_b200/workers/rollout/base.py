@@ -55,9 +55,10 @@ def register_rollout(name: str, mode: str, fqn: str) -> None:
 def get_rollout_class(rollout_name: str, mode: str = "async") -> type[BaseRollout]:
     key = (rollout_name, mode)
     if rollout_name in _NOT_WRAPPED and key not in _ROLLOUT_REGISTRY:
-        raise ValueError(f"rollout.name={rollout_name}: {_NOT_WRAPPED[rollout_name]} is not wrapped by this framework; use "
-                         f"rollout.name=native (built-in engine: continuous batching, paged KV, CUDA-graph decode) or register "
-                         f"an adapter with register_rollout()")
+        raise ValueError(f"rollout.name={rollout_name}: {_NOT_WRAPPED[rollout_name]} is not embedded in the trainer's process by "
+                         f"this framework; use rollout.name=native (built-in engine: continuous batching, paged KV, CUDA-graph "
+                         f"decode), connect to a running server through the HTTP replicas (rollout.server_urls, "
+                         f"workers/rollout/http_replica.py), or register an adapter with register_rollout()")
     if key not in _ROLLOUT_REGISTRY:
         raise ValueError(f"Rollout {rollout_name} with mode {mode} is not supported (known: {sorted(_ROLLOUT_REGISTRY)})")
     import importlib

@@ -140,7 +140,14 @@ class LLMServerManager:
         g = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
         replica_cls = get_rollout_replica_class(g("name", "native"))
         replicas = []
-        if engines is not None:
+        urls = list(g("server_urls", None) or [])
+        if urls and engines is None and g("name", "native") in ("sglang", "trtllm", "openai", "http"):
+            # servers that already run elsewhere: one replica per address, nothing to launch
+            for i in range(len(urls)):
+                r = replica_cls(i, config, model_config)
+                await r.init_standalone()
+                replicas.append(r)
+        elif engines is not None:
             for i, eng in enumerate(engines):
                 r = replica_cls(i, config, model_config, engine=eng)
                 await r.init_standalone()

@@ -199,5 +199,20 @@ class RolloutReplicaRegistry:
 RolloutReplicaRegistry.register("native", lambda: NativeReplica)
 
 
+def _http_replica(kind: str):
+    def load():
+        from . import http_replica
+
+        return http_replica.HTTPReplica if kind == "sglang" else http_replica.OpenAIReplica
+
+    return load
+
+
+# inference servers that run outside this process and are reached over HTTP (SGLang's native API; OpenAI-compatible
+# completion servers such as ``vllm serve`` and ``trtllm-serve``)
+for _name, _kind in (("sglang", "sglang"), ("http", "sglang"), ("trtllm", "openai"), ("openai", "openai")):
+    RolloutReplicaRegistry.register(_name, _http_replica(_kind))
+
+
 def get_rollout_replica_class(rollout: str) -> type[RolloutReplica]:
     return RolloutReplicaRegistry.get(rollout)
