@@ -278,3 +278,33 @@ def test_flops_estimates_follow_the_library_configuration():
     assert 0.5 * full_only < long < 0.55 * full_only     # half of the layers see at most 128 keys
     assert short == 2.0 * 24 * 64 * 128 * _causal_pairs(128)
     assert _causal_pairs(10, 4) == 10 + 9 + 9 + 6      # 1+2+3+4 then 4 per query
+
+
+def test_sharded_checkpoint_of_a_generic_family_merges_to_library_names(tmp_path):
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    from verl_b200.models import FlatParams, make_flat_params
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+
+    arch = _arch("deepseek_v3")
+    with pytest.raises(AssertionError, match="make_flat_params"):
+        FlatParams(arch)
+    eng = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=3), OptimizerConfig(lr=1e-3))
+    eng.initialize()
+    ck = tmp_path / "ckpt"
+    eng.save_checkpoint(str(ck))
+    hf_dir = tmp_path / "hf"
+    hf_dir.mkdir()
+    (hf_dir / "config.json").write_text(json.dumps(arch.to_hf_dict()))
+    from verl_b200.model_merger.base_model_merger import ModelMergerConfig
+    from verl_b200.model_merger.fsdp_model_merger import FSDPModelMerger
+
+    merger = FSDPModelMerger(ModelMergerConfig(operation="merge", backend="fsdp", local_dir=str(ck), target_dir=str(tmp_path / "out"),
+                                               hf_model_config_path=str(hf_dir)))
+    sd = merger.merge_state_dict()
+    want = eng.params.hf_state_dict()
+    assert set(sd) == set(want)
+    assert all(torch.allclose(sd[k].float(), want[k].float(), atol=1e-2) for k in want)       # bf16 copy of the fp32 weights
+    # storage over a given buffer keeps the buffer's content
+    P2 = make_flat_params(arch, dtype=torch.float32, buffer=eng.params.flat.clone())
+    assert torch.equal(P2.flat, eng.params.flat)

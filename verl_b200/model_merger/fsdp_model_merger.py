@@ -71,8 +71,10 @@ class FSDPModelMerger(BaseModelMerger):
         if os.path.exists(cfgp):
             with open(cfgp) as f:
                 value_head = bool(json.load(f).get("value_head", False))
-        params = FlatParams(arch, dtype=torch.float32, device="cpu", value_head=value_head or self.config.is_value_model,
-                            pad_to=len(shards), buffer=flat)
+        from ..models import make_flat_params
+
+        params = make_flat_params(arch, dtype=torch.float32, device="cpu", value_head=value_head or self.config.is_value_model,
+                                  pad_to=len(shards), buffer=flat)
         out = {}
         for name, v in params.hf_views():
             if name == "lm_head.weight" and (arch.tie_word_embeddings or self.config.tie_word_embedding):

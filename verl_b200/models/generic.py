@@ -85,7 +85,8 @@ class ModuleFlatParams:
         for (n, p), s in zip(named, self.specs):
             o = self.offsets[n]
             v = self.flat[o : o + s.numel].view(*s.shape)
-            v.copy_(p.data)
+            if buffer is None:
+                v.copy_(p.data)      # a buffer handed in is authoritative (merged checkpoints, shared storage)
             p.data = v
             self.views[n] = v
             p.register_post_accumulate_grad_hook(self._make_hook(n))

@@ -93,6 +93,9 @@ class FlatParams:
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", value_head: bool = False,
                  with_main_grad: bool = False, pad_to: int = 1, buffer: Optional[torch.Tensor] = None,
                  grad_buffer: Optional[torch.Tensor] = None):
+        assert not getattr(cfg, "is_generic", False), (
+            f"model_type={cfg.model_type!r} has no hand-scheduled parameter layout: use verl_b200.models.make_flat_params "
+            f"(library-module storage, models/generic.py)")
         self.cfg = cfg
         self.dtype = dtype
         self.value_head = value_head

@@ -101,7 +101,7 @@ def update_model_config(cfg, override: dict) -> None:
 
 def load_valuehead_model(model_config, device="cpu", dtype=torch.float32):
     """Flat parameter store with a scalar value head for critic / reward models."""
-    from ..models.weights import FlatParams
+    from ..models import make_flat_params
 
     arch = model_config.arch if hasattr(model_config, "arch") else model_config
-    return FlatParams(arch, dtype=dtype, device=device, value_head=True)
+    return make_flat_params(arch, dtype=dtype, device=device, value_head=True)
