@@ -256,3 +256,43 @@ def test_grpo_end_to_end_with_images(tmp_path):
     assert int((b.batch["input_ids"][:, :12] == IMG).sum()) == 8 * 4
     diff = (torch.exp(b.batch["rollout_log_probs"]) - torch.exp(b.batch["old_log_probs"])).abs()[b.batch["response_mask"].bool()].max().item()
     assert diff < 1e-3, diff     # the sampler and the training forward saw the same images
+
+
+def test_supervised_fine_tuning_batches_carry_images(tmp_path):
+    """SFT collate -> trainer batch -> training worker: per-row processor outputs reach the engine."""
+    import json
+
+    import numpy as np
+
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    from verl_b200.protocol import DataProto
+    from verl_b200.utils.dataset.multiturn_sft_dataset import sft_collate
+    from verl_b200.workers.config import FSDPEngineConfig, HFModelConfig, OptimizerConfig, TrainingWorkerConfig
+    from verl_b200.workers.engine_workers import TrainingWorker
+    from verl_b200.workers.utils.losses import sft_loss
+
+    arch = _arch()
+    mdir = tmp_path / "vl"
+    mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(arch.to_hf_dict()))
+    w = TrainingWorker(TrainingWorkerConfig(model_type="language_model", model_config=HFModelConfig(path=str(mdir), load_weights=False),
+                                            engine_config=FSDPEngineConfig(seed=1, micro_batch_size_per_gpu=2),
+                                            optimizer_config=OptimizerConfig(lr=3e-3)))
+    w.reset()
+    w.set_loss_fn(partial(sft_loss, None))
+    g = torch.Generator().manual_seed(0)
+    items = []
+    for k, (gh, gw) in enumerate(((4, 4), (2, 4), (0, 0))):
+        text = torch.randint(3, 490, (10 + k,), generator=g).tolist()
+        n_img = (gh // 2) * (gw // 2) if gh else 0
+        ids = text[:2] + ([VSTART] + [IMG] * n_img + [VEND] if n_img else []) + text[2:]
+        item = {"input_ids": torch.tensor(ids), "loss_mask": torch.tensor([0] * (len(ids) - 6) + [1] * 6)}
+        if gh:
+            item["multi_modal_inputs"] = _image(gh, gw, k)
+        items.append(item)
+    batch = sft_collate(items, pad_token_id=0)
+    assert len(batch["multi_modal_inputs"]) == 3 and batch["multi_modal_inputs"][2] == {}
+    non = {"multi_modal_inputs": np.array(batch.pop("multi_modal_inputs") + [None], dtype=object)[:-1]}
+    proto = DataProto.from_dict(tensors=batch, non_tensors=non)
+    losses = [w._train_batch(proto)["loss"] for _ in range(4)]
+    assert losses[-1] < losses[0], losses

@@ -83,7 +83,16 @@ class SFTTrainer:
                                                  sampler=ShardedRandomSampler(len(self.val_ds), 0, self.rank, self.world))
 
     def _proto(self, batch: dict) -> DataProto:
-        return DataProto.from_dict(tensors={k: v.to(self.device) for k, v in batch.items()})
+        import numpy as np
+
+        non = {}
+        for k, v in batch.items():
+            if not isinstance(v, torch.Tensor):
+                arr = np.empty(len(v), dtype=object)
+                arr[:] = list(v)
+                non[k] = arr
+        return DataProto.from_dict(tensors={k: v.to(self.device) for k, v in batch.items() if isinstance(v, torch.Tensor)},
+                                   non_tensors=non)
 
     def validate(self) -> Optional[float]:
         if self.val_loader is None:

@@ -110,5 +110,8 @@ def sft_collate(items: list[dict], pad_token_id: int = 0) -> dict:
         am[i, :n] = 1
         lm[i, :n] = x["loss_mask"]
     # response part = tokens 1..L-1 (their log-probs come from positions 0..L-2)
-    return {"input_ids": ids, "attention_mask": am, "position_ids": (am.cumsum(-1) - 1).clamp(min=0),
-            "responses": ids[:, 1:], "response_mask": lm[:, 1:] * am[:, 1:]}
+    out = {"input_ids": ids, "attention_mask": am, "position_ids": (am.cumsum(-1) - 1).clamp(min=0),
+           "responses": ids[:, 1:], "response_mask": lm[:, 1:] * am[:, 1:]}
+    if any("multi_modal_inputs" in x for x in items):   # vision-language samples: the processor's tensors stay per row
+        out["multi_modal_inputs"] = [x.get("multi_modal_inputs") or {} for x in items]
+    return out

@@ -79,6 +79,8 @@ class TrainingWorker(Worker, DistProfilerExtension):
         if isinstance(data, DataProto):
             d = {k: v for k, v in data.batch.items()}
             d.update(data.meta_info)
+            if "multi_modal_inputs" in data.non_tensor_batch:   # per-row processor outputs of vision-language samples
+                d["multi_modal_inputs"] = list(data.non_tensor_batch["multi_modal_inputs"])
             return d
         return dict(data.items()) if hasattr(data, "items") else dict(data)
 
