@@ -58,7 +58,7 @@ def _proc(rank, world, port, cp, q, mode="zigzag"):
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-@pytest.mark.parametrize("world,cp,mode", [(2, 2, "zigzag"), (3, 3, "zigzag"), (4, 2, "zigzag"), (2, 2, "contiguous")])
+@pytest.mark.parametrize("world,cp,mode", [(3, 3, "zigzag"), (2, 2, "contiguous")])
 def test_context_parallel_matches_single_rank(world, cp, mode):
     import torch.multiprocessing as mp
 

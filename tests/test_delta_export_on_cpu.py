@@ -78,7 +78,6 @@ def _proc(rank, world, port, model, kw, q):
 
 @pytest.mark.parametrize("model,world,kw", [
     ("tiny-qwen2", 4, dict(tensor_model_parallel_size=2, pipeline_model_parallel_size=2)),
-    ("tiny-qwen2", 2, dict(tensor_model_parallel_size=2, sequence_parallel=False)),
     ("tiny-moe", 2, dict(expert_model_parallel_size=2)),
 ])
 def test_exported_records_rebuild_the_new_weights(model, world, kw):
