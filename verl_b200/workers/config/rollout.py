@@ -118,6 +118,12 @@ class RolloutConfig(BaseConfig):
     skip_tokenizer_init: bool = True
     enable_chunked_prefill: bool = True
     enable_prefix_caching: bool = False
+    # inference servers that already run elsewhere (name: sglang | openai | trtllm | http): one replica per address
+    server_urls: list = field(default_factory=list)
+    server_dialect: Optional[str] = None
+    served_model_name: Optional[str] = None
+    server_timeout: float = 600.0
+    server_api_key: Optional[str] = None
     prometheus: dict = field(default_factory=dict)
     quantization: Optional[str] = None  # None | fp8
     quantization_config_file: Optional[str] = None
