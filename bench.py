@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: GRPO step tokens/s on the Qwen2.5-7B architecture (random-init bf16, synthetic prompts).
 
-    python bench.py --gpus 1 --steps 1 --warmup 3
+    python bench.py --gpus 1 --steps 2 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus 8 --steps K --warmup W
 
@@ -10,9 +10,11 @@ GRPO advantages + actor update (forward, backward, grad reduction, clipped AdamW
 rollout engine.  Weak scaling: every GPU owns ``--prompts-per-gpu`` prompts x ``--n`` samples (64 x 5 by default,
 i.e. 512 x 5 on 8 GPUs), prompts of 1024 uniform random tokens, responses of up to 2048 tokens.
 
-Two timings are taken over the same K steps each, both bracketed by barrier + synchronize and CUDA events, max
-over ranks: ``value`` with the step inputs already resident on the device, and ``e2e`` through the public trainer
-API with every step's prompts staged host->device from pinned memory and the step's metrics read back.
+One timed pass of K steps, bracketed by barrier + synchronize, CUDA events, max over ranks.  Every step's prompts
+are staged host->device from pinned memory and its scores and metrics are read back: ``e2e`` is the span of the
+whole loop, ``value`` the sum of per-step spans that start after the copy in and end before the read-back.  A
+wall-clock budget (``--time-budget-s``) cuts the numbers of warm-up and timed steps to what fits; the result line
+carries the numbers actually run, and a cumulative line is printed after every finished step.
 
 ``--impl reference`` reports why the reference cannot run in this environment (its import needs packages that are
 not installed and cannot be installed offline).
@@ -36,7 +38,7 @@ sys.path.insert(0, REPO)
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=1)
+    p.add_argument("--steps", type=int, default=2)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="native", choices=["native", "reference"])
     p.add_argument("--model", default="qwen2.5-7b")
@@ -47,10 +49,15 @@ def parse_args():
     p.add_argument("--max-token-len", type=int, default=16384, help="token budget of a training micro-batch")
     p.add_argument("--max-num-seqs", type=int, default=320)
     p.add_argument("--no-recompute", action="store_true")
-    p.add_argument("--skip-e2e", action="store_true", help="development only: skip the second (end-to-end) timing pass")
+    p.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                   help="cpu: development dry run of the control flow (gloo, fp32, host timers); not a measurement")
+    p.add_argument("--time-budget-s", type=float, default=720.0,
+                   help="wall-clock budget of the whole run in seconds, counted from process start (0 = none): after the first "
+                        "warm-up step the numbers of warm-up and timed steps are cut to what still fits, keeping three warm-up "
+                        "steps when that many were asked for; the result line reports the numbers actually run")
     p.add_argument("--rollout-tp", type=int, default=0,
-                   help="rollout tensor-parallel size; 0 = 1: every GPU holds the full bf16 weights, and data-parallel rollout "
-                        "measured faster than TP=2 for this model (gen 32.5 s vs 41.1 s per step); 2 reproduces the TP=2 layout")
+                   help="rollout tensor-parallel size; 0 = the named configuration: 2 on two or more GPUs (1 on one GPU). "
+                        "1 selects pure data-parallel rollout replicas")
     p.add_argument("--train-tp", type=int, default=1, help="tensor-parallel size of the training engine (strategy=megatron when tp*pp > 1)")
     p.add_argument("--train-pp", type=int, default=1, help="pipeline-parallel size of the training engine")
     p.add_argument("--train-ep", type=int, default=1, help="expert-parallel size of the training engine (mixture-of-experts models; "
@@ -80,6 +87,32 @@ def reference_arm(args) -> None:
         print(json.dumps({"impl": "reference", "unavailable": f"reference cannot run offline on this image ({why})"}))
 
 
+def _process_start_time() -> float:
+    """Wall-clock time at which this process was created (imports count against the time budget)."""
+    try:
+        import psutil
+
+        return psutil.Process().create_time()
+    except Exception:
+        return time.time()
+
+
+class _HostEvent:
+    """Host-clock stand-in for a CUDA event (``--device cpu`` dry runs)."""
+
+    def __init__(self):
+        self.t = 0.0
+
+    def record(self):
+        self.t = time.perf_counter()
+
+    def synchronize(self):
+        pass
+
+    def elapsed_time(self, other) -> float:
+        return (other.t - self.t) * 1e3
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
@@ -105,9 +138,15 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
+        return self.snapshot()
+
+    def snapshot(self) -> dict:
+        """Summary of the samples so far (the sampler keeps running)."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in list(self.lines):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -140,14 +179,14 @@ def build_config(args, world: int):
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
         f"actor_rollout_ref.rollout.max_num_seqs={min(args.max_num_seqs, args.prompts_per_gpu * args.n)}",
         "actor_rollout_ref.rollout.gpu_memory_utilization=0.45", "actor_rollout_ref.rollout.sync_interval=32",
-        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp or 1}",
+        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp or (2 if world >= 2 and world % 2 == 0 else 1)}",
         f"actor_rollout_ref.actor.ppo_mini_batch_size={gbs}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
         f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}",
         "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.kl_loss_coef=0.001",
         "actor_rollout_ref.actor.optim.lr=1e-6", "algorithm.adv_estimator=grpo", "reward_model.reward_manager=token_rule",
         f"trainer.n_gpus_per_node={world}", "trainer.nnodes=1", "trainer.total_epochs=1000", "trainer.val_before_train=false",
         "trainer.resume_mode=disable", "trainer.save_freq=-1", "trainer.test_freq=-1", "trainer.logger=[]",
-        "trainer.worker_group=spmd", "trainer.device=cuda",
+        "trainer.worker_group=spmd", f"trainer.device={args.device}",
     ]
     if args.layers > 0:
         ov += [f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}"]
@@ -186,16 +225,23 @@ def main():
     from verl_b200.single_controller.local import SPMDWorkerGroup
     from verl_b200.utils.distributed import initialize_global_process_group
 
+    on_gpu = args.device == "cuda"
+    if not on_gpu:
+        os.environ["VERL_ENGINE_DEVICE"] = "cpu"
     local_rank, rank, world = initialize_global_process_group()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1"
-    dev = torch.device("cuda", torch.cuda.current_device())
-    native.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+    if on_gpu:
+        native.load()
+    Event = (lambda: torch.cuda.Event(enable_timing=True)) if on_gpu else _HostEvent
+    launch_count = native.launch_count if on_gpu else (lambda: 0)
+    check_status = native.check_status if on_gpu else (lambda: None)
 
     cfg = build_config(args, world)
     cfg.data.synthetic["vocab_high"] = get_preset(args.model).vocab_size
     reward_fn = load_reward_manager(cfg, None)
     trainer = RayPPOTrainer(config=cfg, tokenizer=None, ray_worker_group_cls=SPMDWorkerGroup, reward_fn=reward_fn,
-                            val_reward_fn=None, device_name="cuda")
+                            val_reward_fn=None, device_name=args.device)
     trainer.init_workers()
     trainer.global_steps = 1
     it = iter(trainer.train_dataloader)
@@ -211,7 +257,8 @@ def main():
     def sync():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        if on_gpu:
+            torch.cuda.synchronize()
 
     def to_pinned(batch):
         return {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
@@ -219,62 +266,80 @@ def main():
     def to_device(batch):
         return {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
 
+    t_start = _process_start_time()
+
+    def agree_max(x: float) -> float:
+        """Same decision on every rank: the maximum over ranks of a host-side float."""
+        if world == 1:
+            return float(x)
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    # ---- warm-up: the first step is timed on the host to size the rest of the run against the wall-clock budget
     last_metrics = {}
-    for _ in range(args.warmup):
+    warmup, steps = max(args.warmup, 0), max(args.steps, 1)
+    done_warm = 0
+    step_s = 0.0
+    if warmup > 0:
+        sync()
+        t0 = time.time()
         last_metrics, _ = trainer.train_step(next_batch())
         trainer.global_steps += 1
-    native.check_status()
-
-    def timed(batches, staged_on_device: bool):
-        """K steps between barrier+synchronize; returns (ms per step max over ranks, tokens this rank, launches)."""
-        nonlocal last_metrics
-        tokens = 0
         sync()
-        n0 = native.launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for b in batches:
-            last_metrics, _ = trainer.train_step(b)
-            trainer.global_steps += 1
-            tokens += int(sum(trainer.last_batch.meta_info["global_token_num"]))
-        e1.record()
-        sync()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        tok = torch.tensor([float(tokens)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            dist.all_reduce(tok)
-        return float(ms) / len(batches), float(tok), native.launch_count() - n0
+        step_s = agree_max(time.time() - t0)
+        done_warm = 1
+    if args.time_budget_s > 0 and done_warm:
+        left = args.time_budget_s - agree_max(time.time() - t_start) - 20.0  # 20 s for the report and teardown
+        fit = max(1, int(left / (step_s * 1.03)))  # steps that still fit (the first one includes one-time captures)
+        w_min = max(0, min(warmup, 3) - done_warm)
+        steps = max(1, min(steps, fit - w_min))
+        warmup = done_warm + max(0, min(warmup - done_warm, fit - steps))
+    for _ in range(warmup - done_warm):
+        last_metrics, _ = trainer.train_step(next_batch())
+        trainer.global_steps += 1
+    check_status()
 
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    # ---- one timed pass.  Every step: prompts come from pinned host memory (H2D inside the end-to-end region), the
+    # step runs through the trainer's public ``train_step``, the per-sample scores and the metric scalars are read
+    # back (D2H inside the end-to-end region).  ``value`` sums per-step CUDA-event spans that start after the H2D copy
+    # and end before the read-back; ``e2e`` is the span of the whole loop.
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and on_gpu else None
     if sampler:
         sampler.start()
-    dev_batches = [to_device(next_batch()) for _ in range(args.steps)]
-    ms_step, tokens, launches = timed(dev_batches, True)
-    value = tokens / (ms_step * args.steps / 1e3)
-    e2e = None
-    if not args.skip_e2e:
-        host_batches = [to_pinned(next_batch()) for _ in range(args.steps)]
-        h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values() if isinstance(v, torch.Tensor)) * args.n
-        ms_e2e, tok_e2e, _ = timed(host_batches, False)
-        d2h = 8 * len([v for v in last_metrics.values() if isinstance(v, (int, float))])
-        e2e = {"value": tok_e2e / (ms_e2e * args.steps / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
-    clocks = sampler.stop() if sampler else None
-    native.check_status()
-    if rank == 0:
-        gbs = args.prompts_per_gpu * world
+    gbs = args.prompts_per_gpu * world
+    ev = [(Event(), Event()) for _ in range(steps)]
+    e_all0, e_all1 = Event(), Event()
+    pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
+    host_scores = pin(torch.empty(args.prompts_per_gpu * args.n, dtype=torch.float32))
+    tokens = h2d = d2h = 0
+    reshard_s, phase_sum = 0.0, {}
+
+    def report(k: int, partial: bool) -> None:
+        """Collective over ranks; rank 0 prints one JSON line for the first ``k`` timed steps."""
+        ms_dev = sum(ev[j][0].elapsed_time(ev[j][1]) for j in range(k))
+        ms_all = e_all0.elapsed_time(e_all1)
+        t = torch.tensor([ms_dev, ms_all], device=dev, dtype=torch.float64)
+        tok = torch.tensor([float(tokens)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tok)
+        if rank != 0:
+            return
+        ms_dev, ms_all, tok_all = float(t[0]), float(t[1]), float(tok)
         rollout_tp = int(getattr(trainer.actor_rollout_wg.worker, "rollout_tp", 1))
+        mp = args.train_tp * args.train_pp * args.train_ep
         out = {
             "metric": "GRPO step tokens/sec (prompt+response tokens of the step / step time, whole job)",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "value": tok_all / (ms_dev / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": k, "warmup": warmup,
+            "requested_steps": args.steps, "requested_warmup": args.warmup,
+            "ms_per_step": ms_dev / k, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if on_gpu else "fp32 (cpu dry run)",
             "data": "synthetic (uniform random-token prompts, mod-7 rule reward, random-init weights)",
             "config": {"model": args.model, "global_batch": gbs * args.n, "prompts": gbs, "samples_per_prompt": args.n,
                        "seq_len": args.prompt_len + args.response_len, "prompt_len": args.prompt_len,
                        "response_len": args.response_len,
                        "parallelism": (f"dp{world} (sharded optimizer, replicated bf16 weights) + colocated rollout "
-                                       f"tp{rollout_tp} x dp{world // rollout_tp} on in-place weight shards") if args.train_tp * args.train_pp * args.train_ep == 1
+                                       f"tp{rollout_tp} x dp{world // rollout_tp} on in-place weight shards") if mp == 1
                        else (f"train tp{args.train_tp} x pp{args.train_pp} x dp{world // (args.train_tp * args.train_pp)}"
                              f"{' x ep' + str(args.train_ep) + ' (experts sharded over dp)' if args.train_ep > 1 else ''} + rollout tp{rollout_tp} "
                              f"on weights gathered from the shards each step"),
@@ -282,12 +347,48 @@ def main():
                        **({"reduced_model_layers": args.layers} if args.layers > 0 else {}),
                        "shared_prompt_packing": not args.no_prefix_sharing,
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
+                       "time_budget_s": args.time_budget_s,
                        "mean_response_len": last_metrics.get("response_length/mean")},
-            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "phases_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last_metrics.items()
-                         if k.startswith("timing_s/") and isinstance(v, (int, float))},
+            "e2e": {"value": tok_all / (ms_all / 1e3), "unit": "tokens/s", "ms_per_step": ms_all / k,
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "api": "RayPPOTrainer.train_step on prompts staged from pinned host memory; scores and metrics read back"},
+            "reshard_ms_per_step": 1e3 * reshard_s / k,
+            "gpu_launches": int(launch_count() - n0),
+            "clocks": (sampler.stop() if not partial else sampler.snapshot()) if sampler else None,
+            "phases_s": {name: round(v / k, 3) for name, v in phase_sum.items()},
         }
-        print(json.dumps(out))
+        if partial:
+            out["partial"] = True
+        print(json.dumps(out), flush=True)
+
+    sync()
+    n0 = launch_count()
+    e_all0.record()
+    for i in range(steps):
+        host = {k: (pin(v) if isinstance(v, torch.Tensor) else v) for k, v in next_batch().items()}
+        batch = {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in host.items()}
+        h2d = sum(v.numel() * v.element_size() for v in host.values() if isinstance(v, torch.Tensor))
+        ev[i][0].record()
+        last_metrics, _ = trainer.train_step(batch)
+        trainer.global_steps += 1
+        ev[i][1].record()
+        scores = trainer.last_batch.batch["token_level_scores"].sum(-1).float()
+        host_scores[: scores.numel()].copy_(scores, non_blocking=True)
+        if on_gpu:
+            torch.cuda.current_stream().synchronize()
+        d2h = scores.numel() * 4 + 8 * len([v for v in last_metrics.values() if isinstance(v, (int, float))])
+        tokens += int(sum(trainer.last_batch.meta_info["global_token_num"]))
+        reshard_s += float(last_metrics.get("timing_s/update_weights", 0.0))
+        for k, v in last_metrics.items():
+            if k.startswith("timing_s/") and isinstance(v, (int, float)):
+                phase_sum[k.split("/", 1)[1]] = phase_sum.get(k.split("/", 1)[1], 0.0) + float(v)
+        if i + 1 < steps:  # cumulative line after every finished step: a run cut short still leaves a result
+            e_all1.record()
+            e_all1.synchronize()
+            report(i + 1, partial=True)
+    e_all1.record()
+    sync()
+    report(steps, partial=False)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
