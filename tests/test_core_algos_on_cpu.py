@@ -90,18 +90,117 @@ def test_reinforce_pp_remax_opo_gpg_passk():
     assert a.shape == (4, 3) and abs(a.mean().item()) < 1e-6
 
 
-def test_optimal_token_baseline_shapes():
-    torch.manual_seed(0)
-    r = torch.zeros(4, 5)
-    r[:, -1] = torch.rand(4)
-    m = torch.ones(4, 5)
-    olp = -torch.rand(4, 5)
-    s2 = torch.rand(4, 5) * 0.1
-    a, ret = ca.compute_optimal_token_baseline_advantage(r, m, np.array([0, 0, 1, 1]), olp, s2)
-    assert a.shape == (4, 5) and torch.isfinite(a).all()
-    # within a group the W-weighted advantages sum to ~0 per timestep
-    W = torch.cumsum((1 - 2 * olp.exp() + s2) * m, -1)
-    assert torch.allclose((a[:2] * W[:2]).sum(0), torch.zeros(5), atol=1e-4)
+def _otb_oracle(r, m, idx, olp, s2, isw=None, tail=True, eps=1e-8, compact=False):
+    """Loop form of the optimal-token-baseline estimators, one group and one time step at a time."""
+    bs, L = r.shape
+    ret = torch.zeros(bs, L)
+    W = torch.zeros(bs, L)
+    for i in range(bs):
+        acc = 0.0
+        for t in reversed(range(L)):
+            acc += float(r[i, t] * m[i, t])
+            ret[i, t] = acc
+        acc = 0.0
+        for t in range(L):
+            w = 1 - 2 * float(olp[i, t].exp()) + float(s2[i, t])
+            if isw is not None:
+                w *= float(isw[i, t]) ** 2
+            acc += w * float(m[i, t])
+            W[i, t] = acc
+    pos = [[t for t in range(L) if m[i, t] > 0] for i in range(bs)]
+    # frame: position t itself, or the t-th generated token when compacting
+    frame = [pos[i] if compact else [t if m[i, t] > 0 else None for t in range(L)] for i in range(bs)]
+    adv = torch.zeros(bs, L)
+    groups = {}
+    for i in range(bs):
+        if compact and not pos[i]:
+            continue
+        groups.setdefault(idx[i], []).append(i)
+    for members in groups.values():
+        lens = sorted(len(pos[i]) for i in members)
+        for i in members:
+            for k, t in enumerate(frame[i]):
+                if t is None:
+                    continue
+                base = 0.0
+                if len(members) > 1:
+                    num = den = 0.0
+                    for j in members:
+                        if k < len(frame[j]) and frame[j][k] is not None:
+                            tj = frame[j][k]
+                            num += float(ret[j, tj] * W[j, tj])
+                            den += float(W[j, tj])
+                    base = num / (den + eps)
+                    if tail and len(pos[i]) == lens[-1] and lens[-1] > lens[-2] and k >= lens[-2]:
+                        base = 0.0
+                adv[i, t] = ret[i, t] - base
+    return adv, ret
+
+
+def _otb_case(seed, masks, idx):
+    torch.manual_seed(seed)
+    m = torch.tensor(masks, dtype=torch.float32)
+    bs, L = m.shape
+    r = torch.rand(bs, L) * m
+    olp = -torch.rand(bs, L)
+    s2 = torch.rand(bs, L) * 0.2
+    isw = 0.5 + torch.rand(bs, L)
+    return r, m, np.array(idx, dtype=object), olp, s2, isw
+
+
+@pytest.mark.parametrize("tail", [True, False])
+def test_optimal_token_baseline_matches_loop_form(tail):
+    # ragged right-padded responses: a unique longest sample, a tie for longest, a singleton group
+    masks = [[1, 1, 1, 1, 1, 1], [1, 1, 1, 0, 0, 0], [1, 1, 0, 0, 0, 0],
+             [1, 1, 1, 1, 0, 0], [1, 1, 1, 1, 0, 0], [1, 0, 0, 0, 0, 0],
+             [1, 1, 1, 1, 1, 0]]
+    r, m, idx, olp, s2, isw = _otb_case(0, masks, ["a", "a", "a", "b", "b", "b", "solo"])
+    for w in (None, isw):
+        a, ret = ca.compute_optimal_token_baseline_advantage(r, m, idx, olp, s2, rollout_is_weights=w, handle_zero_tail=tail)
+        a0, ret0 = _otb_oracle(r, m, list(idx), olp, s2, w, tail)
+        assert torch.allclose(ret, ret0, atol=1e-5) and torch.allclose(a, a0, atol=1e-5)
+    # singleton group: the advantage is the reward-to-go itself
+    assert torch.allclose(a[6], ret[6] * m[6])
+    # the unique longest sample of group "a" has baseline zero beyond the second-longest length
+    if tail:
+        assert torch.allclose(a[0, 3:], ret[0, 3:])
+
+
+@pytest.mark.parametrize("tail", [True, False])
+def test_multi_turn_optimal_token_baseline_matches_loop_form(tail):
+    # tool / observation tokens (0) inside the trajectory, one sample with no generated token, one singleton group
+    masks = [[1, 1, 0, 0, 1, 1, 1, 0], [1, 0, 0, 1, 1, 0, 0, 0], [1, 1, 1, 0, 0, 0, 1, 1],
+             [0, 0, 0, 0, 0, 0, 0, 0], [1, 1, 0, 1, 0, 1, 0, 1], [1, 0, 1, 0, 0, 0, 0, 0]]
+    r, m, idx, olp, s2, isw = _otb_case(1, masks, [0, 0, 0, 1, 1, 2])
+    for w in (None, isw):
+        a, ret = ca.compute_multi_turn_optimal_token_baseline_advantage(r, m, idx, olp, s2, rollout_is_weights=w,
+                                                                        handle_zero_tail=tail)
+        a0, ret0 = _otb_oracle(r, m, list(idx), olp, s2, w, tail, compact=True)
+        assert torch.allclose(ret, ret0, atol=1e-5) and torch.allclose(a, a0, atol=1e-5)
+    assert (a[3] == 0).all() and torch.allclose(a[4], ret[4] * m[4])  # group 1 has one sample with tokens
+    assert (a * (1 - m) == 0).all()
+
+
+def test_gdpo_whitens_over_tokens():
+    torch.manual_seed(2)
+    m = torch.tensor([[1, 1, 1, 1], [1, 0, 0, 0], [1, 1, 0, 0], [1, 1, 1, 0]], dtype=torch.float32)
+    r = torch.zeros(4, 4)
+    r[torch.arange(4), (m.sum(-1) - 1).long()] = torch.tensor([1.0, 0.0, 0.5, 2.0])
+    idx = np.array([0, 0, 1, 1])
+    a, _ = ca.compute_gdpo_outcome_advantage(r, m, idx)
+    g, _ = ca.compute_grpo_outcome_advantage(r, m, idx)
+    want = VF.masked_whiten(g, m) * m
+    assert torch.allclose(a, want, atol=1e-6)
+    # two weighted components from the non-tensor batch
+    nt = {"fmt": np.array([1.0, 0.0, 1.0, 0.0], dtype=np.float32), "acc": np.array([0.0, 1.0, 1.0, 3.0], dtype=np.float32)}
+    a2, _ = ca.compute_gdpo_outcome_advantage(r, m, idx, config={"gdpo_reward_keys": ["fmt", "acc"], "gdpo_reward_weights": [0.5, 2.0]},
+                                              non_tensor_batch=nt, batch={})
+    comb = torch.zeros(4, 4)
+    for w, k in ((0.5, "fmt"), (2.0, "acc")):
+        rk = torch.zeros(4, 4)
+        rk[:, 0] = torch.from_numpy(nt[k])
+        comb = comb + w * ca.compute_grpo_outcome_advantage(rk, m, idx)[0]
+    assert torch.allclose(a2, VF.masked_whiten(comb, m) * m, atol=1e-6)
 
 
 @pytest.mark.parametrize("mode", ["token-mean", "token-sum", "seq-mean-token-sum", "seq-mean-token-mean", "seq-mean-token-sum-norm"])

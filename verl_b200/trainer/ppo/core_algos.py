@@ -221,9 +221,8 @@ def compute_gdpo_outcome_advantage(token_level_rewards, response_mask, index, ep
         for w, c in zip(weights, comps):
             mean, std, _ = _group_mean_std(c, gid, ng)
             total = total + w * ((c - mean) / (std + epsilon) if norm_adv_by_std_in_grpo else (c - mean))
-        if total.numel() > 1:
-            total = (total - total.mean()) / (total.std() + epsilon)
-        a = total.unsqueeze(-1) * response_mask
+        # whitened over tokens, so longer responses weigh more in the batch statistics (as the reference does)
+        a = VF.masked_whiten(total.unsqueeze(-1) * response_mask, response_mask) * response_mask
     return a, a
 
 
@@ -353,37 +352,59 @@ def compute_gpg_outcome_advantage(token_level_rewards, response_mask, index, eps
     return a, a
 
 
-def _otb_core(token_level_rewards, response_mask, index, old_log_probs, sum_pi_squared, epsilon, handle_zero_tail,
-              rollout_is_weights=None):
-    """Variance-optimal per-timestep baseline B_t = sum_i G_i W_i(t) / sum_i W_i(t) within each group, where
-    W_i(t) is the cumulative path-variance proxy sum_{s<=t} (1 - 2 pi_s + sum pi^2_s) of sample i."""
-    with torch.no_grad():
-        returns = (token_level_rewards * response_mask).sum(-1, keepdim=True).expand_as(response_mask)
-        pi_t = torch.exp(old_log_probs)
-        w_step = (1.0 - 2.0 * pi_t + sum_pi_squared) * response_mask
-        if rollout_is_weights is not None:
-            w_step = w_step * rollout_is_weights.pow(2)
-        W = torch.cumsum(w_step, dim=-1)
-        if handle_zero_tail:
-            # past the end of a sequence keep its final cumulative weight so it still votes in the baseline
-            last = W.gather(-1, (response_mask.sum(-1, keepdim=True).long() - 1).clamp(min=0))
-            W = torch.where(response_mask > 0, W, last.expand_as(W))
-        gid, ng = _group_ids(index)
-        gid = gid.to(returns.device)
-        L = returns.shape[1]
-        num = torch.zeros(ng, L, dtype=returns.dtype, device=returns.device).index_add_(0, gid, returns * W)
-        den = torch.zeros(ng, L, dtype=returns.dtype, device=returns.device).index_add_(0, gid, W)
-        base = num / (den + epsilon)
-        a = (returns - base[gid]) * response_mask
-    return a, returns * response_mask
+def _otb_baselines(returns, W, valid, gid, ng, lengths, epsilon, handle_zero_tail):
+    """Per-timestep baseline of every sample's group on an aligned [bs, L] frame.
+
+    ``valid`` marks the positions that vote: B_g(t) = sum_{i in g} G_i(t) W_i(t) valid_i(t) / (sum W_i(t) valid_i(t) + eps).
+    Groups of one sample get baseline zero (the advantage is the return). With ``handle_zero_tail`` the unique
+    longest sample of a group gets baseline zero beyond the length of the second longest: only it votes there."""
+    bs, L = returns.shape
+    dev = returns.device
+    gid = gid.to(dev)
+    Wv = W * valid
+    num = torch.zeros(ng, L, dtype=returns.dtype, device=dev).index_add_(0, gid, returns * Wv)
+    den = torch.zeros(ng, L, dtype=returns.dtype, device=dev).index_add_(0, gid, Wv)
+    base = (num / (den + epsilon))[gid]
+    count = torch.zeros(ng, dtype=torch.long, device=dev).index_add_(0, gid, torch.ones(bs, dtype=torch.long, device=dev))
+    base = base * (count[gid] > 1).unsqueeze(-1)
+    if handle_zero_tail and bs > 0:
+        lengths = lengths.to(dev).long()
+        # longest and second-longest length per group (counting multiplicity), without a Python loop over groups
+        top = torch.zeros(ng, dtype=torch.long, device=dev).scatter_reduce_(0, gid, lengths, reduce="amax", include_self=True)
+        n_top = torch.zeros(ng, dtype=torch.long, device=dev).index_add_(0, gid, (lengths == top[gid]).long())
+        rest = torch.where(lengths == top[gid], torch.zeros_like(lengths), lengths)
+        second = torch.zeros(ng, dtype=torch.long, device=dev).scatter_reduce_(0, gid, rest, reduce="amax", include_self=True)
+        lone = (lengths == top[gid]) & (n_top[gid] == 1) & (count[gid] > 1) & (top[gid] > second[gid])
+        pos = torch.arange(L, device=dev).unsqueeze(0)
+        base = torch.where(lone.unsqueeze(-1) & (pos >= second[gid].unsqueeze(-1)), torch.zeros_like(base), base)
+    return base
+
+
+def _otb_inputs(token_level_rewards, response_mask, old_log_probs, sum_pi_squared, rollout_is_weights):
+    """Reward-to-go returns and the cumulative path-variance proxy W_t = sum_{s<=t} (1 - 2 pi_s + sum pi_s^2) over
+    generated tokens (times the squared truncated importance weight when rollout correction is on)."""
+    returns = (token_level_rewards * response_mask).flip(-1).cumsum(-1).flip(-1)
+    w_step = 1.0 - 2.0 * torch.exp(old_log_probs) + sum_pi_squared
+    if rollout_is_weights is not None:
+        w_step = w_step * rollout_is_weights.pow(2)
+    return returns, torch.cumsum(w_step * response_mask, dim=-1)
 
 
 @register_adv_est(AdvantageEstimator.OPTIMAL_TOKEN_BASELINE)
 def compute_optimal_token_baseline_advantage(token_level_rewards, response_mask, index, old_log_probs,
                                              sum_pi_squared, rollout_is_weights=None, handle_zero_tail: bool = True,
                                              epsilon: float = 1e-8, config=None, **kwargs):
-    return _otb_core(token_level_rewards, response_mask, index, old_log_probs, sum_pi_squared, epsilon,
-                     handle_zero_tail, rollout_is_weights)
+    """Variance-optimal per-timestep baseline within each prompt group; returns (advantages, reward-to-go).
+
+    Parity target: ``verl/trainer/ppo/core_algos.py:871-985``: finished samples leave both sums, a single-sample group
+    keeps its return as the advantage, the tail rule uses the longest against the second-longest response."""
+    with torch.no_grad():
+        returns, W = _otb_inputs(token_level_rewards, response_mask, old_log_probs, sum_pi_squared, rollout_is_weights)
+        gid, ng = _group_ids(index)
+        base = _otb_baselines(returns, W, response_mask.to(returns.dtype), gid, ng, response_mask.sum(-1), epsilon,
+                              handle_zero_tail)
+        adv = (returns - base) * response_mask
+    return adv, returns
 
 
 @register_adv_est(AdvantageEstimator.TIR_OPTIMAL_TOKEN_BASELINE)
@@ -391,10 +412,31 @@ def compute_multi_turn_optimal_token_baseline_advantage(token_level_rewards, res
                                                         sum_pi_squared, rollout_is_weights=None,
                                                         handle_zero_tail: bool = True, epsilon: float = 1e-8,
                                                         config=None, **kwargs):
-    """Multi-turn variant: tool/observation tokens (mask 0 inside the trajectory) neither accumulate variance
-    nor receive an advantage; the baseline is indexed by the count of generated tokens so far."""
-    return _otb_core(token_level_rewards, response_mask, index, old_log_probs, sum_pi_squared, epsilon,
-                     handle_zero_tail, rollout_is_weights)
+    """Multi-turn variant: tool / observation tokens (mask 0 inside the trajectory) neither accumulate variance nor
+    receive an advantage, and the baseline is indexed by the number of generated tokens so far: the generated tokens
+    of every sample are compacted to the left before the group statistics and scattered back afterwards. Samples
+    without a generated token belong to no group. Parity target: ``verl/trainer/ppo/core_algos.py:988-1121``."""
+    with torch.no_grad():
+        returns, W = _otb_inputs(token_level_rewards, response_mask, old_log_probs, sum_pi_squared, rollout_is_weights)
+        bs, L = returns.shape
+        m = response_mask > 0
+        lengths = m.sum(-1)
+        # stable left-compaction: generated tokens first, in order
+        order = torch.argsort((~m).to(torch.int8), dim=-1, stable=True)
+        filled = (torch.arange(L, device=returns.device).unsqueeze(0) < lengths.unsqueeze(-1)).to(returns.dtype)
+        c_ret = torch.gather(returns, 1, order) * filled
+        c_W = torch.gather(W, 1, order) * filled
+        keep = lengths > 0
+        adv_c = torch.zeros_like(c_ret)
+        if bool(keep.any()):
+            idx_np = np.asarray(index, dtype=object)[keep.cpu().numpy()]
+            gid, ng = _group_ids(idx_np)
+            # every compacted position below the length votes; the frame is zero beyond it, as in the reference
+            ones = torch.ones_like(c_ret[keep])
+            base = _otb_baselines(c_ret[keep], c_W[keep], ones, gid, ng, lengths[keep], epsilon, handle_zero_tail)
+            adv_c[keep] = c_ret[keep] - base
+        adv = torch.zeros_like(returns).scatter_(1, order, adv_c * filled) * response_mask
+    return adv, returns
 
 
 # ----------------------------------------------------------------------------------------------- rewards / agg
