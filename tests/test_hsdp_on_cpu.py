@@ -82,3 +82,36 @@ def test_hybrid_sharding_matches_unsharded(fsdp_size, tmp_path):
         assert ((got - ref.params.flat.float()).abs() > 3e-4).float().mean() < 1e-3
         assert res[r]["reload_equal"]
         assert res[r]["files"] == [f"model_world_size_{fsdp_size}_rank_{i}.pt" for i in range(fsdp_size)]
+    if fsdp_size == 2:
+        # a checkpoint written by two shards loads into one: every range is rebuilt from the files that overlap it
+        one = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=11, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
+        one.initialize()
+        one.load_checkpoint(str(tmp_path))
+        n = one.params.numel
+        assert torch.equal(one.params.flat.float()[:n], torch.from_numpy(res[0]["flat"])[:n])
+        assert one.opt_step_count == 1 and float(one.exp_avg.abs().sum()) > 0
+        assert abs(float(one.exp_avg.double().pow(2).sum()) - float(ref.exp_avg.double().pow(2).sum())) < 1e-4 * float(ref.exp_avg.double().pow(2).sum()) + 1e-12
+        # a shard file that is gone is an error, not a silent fresh start
+        os.remove(os.path.join(str(tmp_path), "optim_world_size_2_rank_1.pt"))
+        with pytest.raises(FileNotFoundError, match="world size 2"):
+            one.load_checkpoint(str(tmp_path))
+
+
+def test_checkpoint_load_refuses_missing_files_and_rotates(tmp_path):
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    from verl_b200.models import get_preset
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+
+    eng = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2))
+    eng.initialize()
+    with pytest.raises(FileNotFoundError):
+        eng.load_checkpoint(str(tmp_path / "nowhere"))
+    dirs = [str(tmp_path / f"global_step_{i}" / "actor") for i in range(3)]
+    for d in dirs:
+        eng.save_checkpoint(d, max_ckpt_to_keep=2)
+    assert not os.path.isdir(dirs[0]) and os.path.isdir(dirs[1]) and os.path.isdir(dirs[2])
+    os.remove(os.path.join(dirs[2], "model_world_size_1_rank_0.pt"))
+    with pytest.raises(FileNotFoundError, match="model_world_size_1_rank_0"):
+        eng.load_checkpoint(dirs[2])
+    eng.load_checkpoint(dirs[1])

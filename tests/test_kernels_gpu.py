@@ -348,9 +348,44 @@ def test_activation_offload_gives_identical_gradients(ops):
     assert torch.equal(grads[0], grads[1])
 
 
-def test_bounded_wait_reports_status_instead_of_hanging(ops):
-    """The status word is readable and clear after the tests above (no kernel wait ran out)."""
-    assert int(ops.gemm_status()) == 0
+def test_bounded_wait_runs_out_reports_status_and_gates_the_update(ops):
+    """A barrier on a flag that nobody sets gives up after its limit: the status word says so, the device stays usable,
+    and the poisoned norm accumulator makes the fused AdamW kernel skip (state untouched, old weights republished)."""
+    import time
+
+    assert int(ops.gemm_status()) == 0 and int(ops.comm_status()) == 0
+    pads = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(2)]  # this GPU plays rank 0 of 2; "rank 1" never arrives
+    ptrs = torch.tensor([p.data_ptr() for p in pads], dtype=torch.int64)
+    ctrl = torch.zeros(4, device=DEV)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ops.peer_barrier(ptrs, 0, 1, 0.2, ctrl[:1])
+    torch.cuda.synchronize()
+    assert 0.15 < time.time() - t0 < 5.0
+    assert int(pads[0][0]) == 1 and int(pads[1][0]) == 1 and int(pads[0][1]) == 0  # own arrival was published to both pads
+    assert torch.isinf(ctrl[0])
+    assert int(ops.comm_status()) == 4 and int(ops.comm_status()) == 0  # reported once, then cleared
+    # the step that follows: the sum of squares stays non-finite, the clip kernel raises the skip flag, AdamW leaves state alone
+    n = 4096
+    g = torch.randn(n, device=DEV)
+    ops.sumsq_(g, ctrl)
+    ops.clip_coef_(ctrl, 1.0)
+    assert float(ctrl[2]) == 1.0
+    master = torch.randn(n, device=DEV)
+    m, v = torch.rand(n, device=DEV), torch.rand(n, device=DEV)
+    m0, v0, master0 = m.clone(), v.clone(), master.clone()
+    work = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+    ops.adamw_allgather_(master, g, m, v, torch.tensor([work.data_ptr()], dtype=torch.int64), 0, 0, 0, ctrl, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(master, master0) and torch.equal(m, m0) and torch.equal(v, v0)
+    assert torch.equal(work, master0.bfloat16())
+    # a barrier whose peers have all arrived returns at once and poisons nothing
+    pads[0][1] = 2
+    ctrl.zero_()
+    ops.peer_barrier(ptrs, 0, 2, 0.2, ctrl[:1])
+    torch.cuda.synchronize()
+    assert float(ctrl[0]) == 0.0 and int(ops.comm_status()) == 0
+    assert float(torch.ones(8, device=DEV).sum()) == 8.0
 
 
 def test_rollout_engine_cuda_graph_matches_eager(ops):

@@ -427,9 +427,14 @@ inline const unsigned long long* uptr(const Tensor& t) {
   return reinterpret_cast<const unsigned long long*>(t.data_ptr());
 }
 
-void peer_barrier(const Tensor& pad_ptrs, int64_t rank, int64_t epoch, double limit_s) {
+void peer_barrier(const Tensor& pad_ptrs, int64_t rank, int64_t epoch, double limit_s, const c10::optional<Tensor>& poison) {
   count(1);
-  CHECK_RC(vb_peer_barrier(uptr(pad_ptrs), (int)rank, (int)pad_ptrs.numel(), (unsigned int)epoch, limit_s, cur_stream()),
+  float* pz = nullptr;
+  if (poison.has_value()) {
+    TORCH_CHECK(poison->is_cuda() && poison->scalar_type() == at::kFloat && poison->numel() >= 1, "poison: fp32 CUDA tensor");
+    pz = poison->data_ptr<float>();
+  }
+  CHECK_RC(vb_peer_barrier(uptr(pad_ptrs), (int)rank, (int)pad_ptrs.numel(), (unsigned int)epoch, limit_s, pz, cur_stream()),
            "vb_peer_barrier");
 }
 

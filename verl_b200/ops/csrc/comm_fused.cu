@@ -40,8 +40,12 @@ __device__ int g_comm_status[4];
 
 // Each rank owns a pad of uint32 slots. Rank r writes `epoch` into slot [r] of every peer's pad, then waits until
 // all W slots of its own pad hold a value >= epoch. Epochs only grow, so pads never need clearing.
+// When the wait runs out the kernel records ST_TIMEOUT_PEER in the status word and, if `poison` is given, stores
+// +inf there: a caller that points it at the squared-gradient-norm accumulator makes the step that follows see a
+// non-finite norm on every rank (after the norm is summed over ranks) and skip its update on the device, before any
+// host has read the status.
 __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int W, uint32_t epoch, unsigned long long limit_ns,
-                                    int* status) {
+                                    int* status, float* poison) {
   const int t = threadIdx.x;
   if (t < W) {
     __threadfence_system();
@@ -52,6 +56,7 @@ __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int W, uint32_t epo
     while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
       if ((++spins & 0xff) == 0 && gtimer() - t0 > limit_ns) {
         atomicExch(status, 4);  // ST_TIMEOUT_PEER
+        if (poison != nullptr) *poison = __int_as_float(0x7f800000);
         break;
       }
     }
@@ -219,10 +224,10 @@ using namespace vb;
 extern "C" {
 
 int vb_peer_barrier(const unsigned long long* pad_ptrs, int rank, int W, unsigned int epoch, double limit_s,
-                    cudaStream_t s) {
+                    float* poison_on_timeout, cudaStream_t s) {
   if (W > MAX_PEERS) return -1;
   peer_barrier_kernel<<<1, 32, 0, s>>>(make_peers(pad_ptrs, W), rank, W, epoch,
-                                       static_cast<unsigned long long>(limit_s * 1e9), comm_status_ptr());
+                                       static_cast<unsigned long long>(limit_s * 1e9), comm_status_ptr(), poison_on_timeout);
   return static_cast<int>(cudaGetLastError());
 }
 

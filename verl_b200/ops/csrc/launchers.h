@@ -77,7 +77,8 @@ int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, const void*
                        cudaStream_t stream);
 int vb_pd_status();
 // comm_fused.cu
-int vb_peer_barrier(const unsigned long long* pad_ptrs, int rank, int W, unsigned int epoch, double limit_s, cudaStream_t s);
+int vb_peer_barrier(const unsigned long long* pad_ptrs, int rank, int W, unsigned int epoch, double limit_s,
+                    float* poison_on_timeout, cudaStream_t s);
 int vb_rs_sumsq(const unsigned long long* grad_ptrs, unsigned long long mc_ptr, float* out, long long lo, long long n, int W,
                 int rank, float scale, float* ctrl, cudaStream_t s);
 int vb_adamw_allgather(float* master, const float* grad, float* m, float* v, const unsigned long long* param_ptrs,

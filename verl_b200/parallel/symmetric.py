@@ -66,11 +66,12 @@ class PeerBarrier:
         self.epoch = 0
         dist.barrier(group)  # pads are zero everywhere before the first device-side epoch is written
 
-    def __call__(self, limit_s: float = 20.0) -> None:
+    def __call__(self, limit_s: float = 20.0, poison: Optional[torch.Tensor] = None) -> None:
+        """``poison``: an fp32 device scalar that receives +inf if the wait runs out (see ``peer_barrier_kernel``)."""
         from ..ops import native
 
         self.epoch += 1
-        native.ops().peer_barrier(self.buf.ptrs, self.rank, self.epoch, float(limit_s))
+        native.ops().peer_barrier(self.buf.ptrs, self.rank, self.epoch, float(limit_s), poison)
 
 
 class FusedRowParallelLinear:

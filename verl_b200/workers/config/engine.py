@@ -67,6 +67,9 @@ class FSDPEngineConfig(EngineConfig):
     enable_gradient_checkpointing: bool = True
     enable_activation_offload: bool = False
     fused_comm: bool = True  # peer-memory fused reduce-scatter + AdamW + all-gather when symmetric memory is available
+    # limit of the device-side barriers around the fused optimizer step: ranks do not talk during gradient accumulation, so
+    # it has to cover the skew a whole mini-batch can build up; when it runs out the step is skipped on every rank
+    peer_barrier_timeout_s: float = 120.0
     strategy: str = "fsdp"
 
     def __post_init__(self):

@@ -206,6 +206,7 @@ class NativeEngine(BaseEngine):
         ec = self.engine_config
         seed = int(getattr(ec, "seed", 42))
         self.fused_comm = False
+        self.peer_barrier_timeout_s = float(getattr(ec, "peer_barrier_timeout_s", 120.0) or 120.0)
         self._sym_params = self._sym_grads = self._peer_barrier = None
         if self._shared_params is not None:
             self.params = self._shared_params
@@ -690,6 +691,8 @@ class NativeEngine(BaseEngine):
         if self.qat.enable:
             self._apply_qat()  # fresh bf16 casts of the master weights -> their NVFP4 values
         norm = float(norm)
+        if not math.isfinite(norm):
+            self.opt_step_count -= 1  # a skipped step does not advance the bias correction
         if self.lazy_grad:
             self.tparams.detach_main_grad()
             self.grad_shard = None
@@ -755,9 +758,12 @@ class NativeEngine(BaseEngine):
         ops = native.ops()
         use_mc = os.environ.get("VERL_B200_MULTIMEM", "0") == "1"
         lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
-        self.opt_step_count += 1
-        self._peer_barrier()
+        # The barrier's wait is bounded. If it runs out on this rank (a straggler further behind than the limit), the
+        # kernel poisons the squared-norm accumulator with +inf; the sum over ranks below spreads that to every rank,
+        # the straggler included once it arrives, so the AdamW kernel takes its non-finite branch everywhere: optimizer
+        # state stays untouched and the old weights are republished. Only then does the host read the status and raise.
         self.ctrl.zero_()
+        self._peer_barrier(limit_s=self.peer_barrier_timeout_s, poison=self.ctrl[:1])
         ops.rs_sumsq_(self._sym_grads.ptrs, self._sym_grads.multicast_ptr if use_mc else 0, self.grad_shard, self.shard_lo,
                       self.rank, 1.0 / self.world, self.ctrl)
         dist.all_reduce(self.ctrl[:1], group=self.group)
@@ -765,13 +771,17 @@ class NativeEngine(BaseEngine):
         ops.adamw_allgather_(self.master, self.grad_shard, self.exp_avg, self.exp_avg_sq, self._sym_params.ptrs,
                              self._sym_params.multicast_ptr if use_mc else 0, self.shard_lo, self.rank, self.ctrl, lr,
                              float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay), self.opt_step_count)
-        self._peer_barrier()
-        if self.qat.enable:
-            self._apply_qat()
+        self._peer_barrier(limit_s=self.peer_barrier_timeout_s)
         norm = float(self.ctrl[3])
         code = int(ops.comm_status())
         if code != 0:
-            raise RuntimeError(f"peer barrier timed out (status {code}): a rank did not reach the optimizer step")
+            self.opt_step_count -= 1
+            raise RuntimeError(f"peer barrier timed out after {self.peer_barrier_timeout_s:.0f} s (status {code}): a rank did not "
+                               f"reach the optimizer step; the update was skipped on every rank, optimizer state is unchanged")
+        if not math.isfinite(norm):
+            self.opt_step_count -= 1  # skipped step (non-finite gradient here, or a barrier that ran out on a peer)
+        if self.qat.enable:
+            self._apply_qat()
         return norm
 
     def _qat_scale_group(self):
@@ -832,6 +842,7 @@ class NativeEngine(BaseEngine):
         if "model" in contents:
             src = self.master if not self.forward_only else self._owned(self.tparams.flat).float()
             torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.tparams.numel,
+                        "shard_numel": self.shard_numel, "dense_numel": self.dense_numel, "local_numel": self.local_numel,
                         "offsets": self.tparams.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
         if "optimizer" in contents and not self.forward_only:
             torch.save({"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "step": self.opt_step_count},
@@ -853,6 +864,55 @@ class NativeEngine(BaseEngine):
                 save_hf_weights(self.params, hf_dir)
         if self.world > 1:
             dist.barrier(group=self.group)
+        self._rotate_checkpoints(local_path, max_ckpt_to_keep)
+
+    def _rotate_checkpoints(self, local_path: str, max_ckpt_to_keep: Optional[int]) -> None:
+        """Keep at most ``max_ckpt_to_keep`` of the directories this engine has written (oldest removed first, by rank 0,
+        after every rank has finished writing the new one). Parity target: ``verl/utils/checkpoint/checkpoint_manager.py``
+        (``remove_previous_save_local_path``)."""
+        saved = self.__dict__.setdefault("_saved_ckpt_paths", [])
+        path = os.path.abspath(local_path)
+        if path in saved:
+            saved.remove(path)
+        saved.append(path)
+        if not max_ckpt_to_keep or int(max_ckpt_to_keep) <= 0:
+            return
+        while len(saved) > int(max_ckpt_to_keep):
+            old = saved.pop(0)
+            if self.rank == 0 and os.path.isdir(old):
+                import shutil
+
+                shutil.rmtree(old, ignore_errors=True)
+
+    def _saved_world_size(self, local_path: str) -> Optional[int]:
+        cfg_path = os.path.join(local_path, "fsdp_config.json")
+        if os.path.exists(cfg_path):
+            with open(cfg_path) as f:
+                return int(json.load(f).get("world_size", 0)) or None
+        return None
+
+    def _read_owned_range(self, local_path: str, prefix: str, keys: tuple, saved_world: int) -> dict:
+        """Rebuild this rank's slice [shard_lo, shard_lo + shard_numel) of the replicated region from the shard files of a
+        checkpoint written with another shard world size. Elements beyond the saved region are alignment padding (zero)."""
+        lo, n = self.shard_lo, self.shard_numel
+        out = {k: torch.zeros(n, dtype=torch.float32) for k in keys}
+        meta = {}
+        for r0 in range(saved_world):
+            path = os.path.join(local_path, f"{prefix}_world_size_{saved_world}_rank_{r0}.pt")
+            if not os.path.exists(path):
+                raise FileNotFoundError(f"checkpoint shard {path} is missing (the checkpoint records shard world size {saved_world})")
+            st = torch.load(path, map_location="cpu", weights_only=False)
+            n0 = int(st[keys[0]].numel())
+            lo0 = int(st["shard_lo"]) if "shard_lo" in st else r0 * n0
+            if int(st.get("local_numel", 0) or 0) != 0:
+                raise RuntimeError("a checkpoint with rank-local (expert-parallel) parameters can only be loaded with the shard "
+                                   f"world size it was written with ({saved_world})")
+            a, b = max(lo, lo0), min(lo + n, lo0 + n0)
+            if a < b:
+                for k in keys:
+                    out[k][a - lo : b - lo].copy_(st[k][a - lo0 : b - lo0])
+            meta = {k: v for k, v in st.items() if k not in keys}
+        return {**meta, **out}
 
     def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, del_local_after_load: bool = False,
                         **kwargs) -> None:
@@ -860,30 +920,61 @@ class NativeEngine(BaseEngine):
             return
         W, r = self.sh_world, self.sh_rank
         contents = list(getattr(self.checkpoint_config, "load_contents", ["model", "optimizer", "extra"]) or [])
-        sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-        mp = os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt")
-        if "model" in contents and os.path.exists(mp):
-            st = torch.load(mp, map_location="cpu", weights_only=False)
-            assert st["numel"] == self.tparams.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
+        if not os.path.isdir(local_path):
+            raise FileNotFoundError(f"checkpoint directory {local_path} does not exist")
+        saved_W = self._saved_world_size(local_path)
+
+        def shard_file(prefix: str) -> Optional[str]:
+            """This rank's file of the current layout, or None when the checkpoint was sharded differently."""
+            path = os.path.join(local_path, f"{prefix}_world_size_{W}_rank_{r}.pt")
+            if os.path.exists(path):
+                return path
+            if saved_W is None or saved_W == W:
+                raise FileNotFoundError(
+                    f"{path} is missing: load_contents asks for it and the checkpoint "
+                    + (f"records shard world size {saved_W}" if saved_W else "has no fsdp_config.json naming its shard world size")
+                    + f" (this engine shards over {W})")
+            return None
+
+        if "model" in contents:
+            mp = shard_file("model")
+            if mp is not None:
+                st = torch.load(mp, map_location="cpu", weights_only=False)
+                assert st["numel"] == self.tparams.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
+                owned = st["flat_shard"]
+            else:
+                if self.local_numel:
+                    raise RuntimeError(f"rank-local parameters: the checkpoint (shard world size {saved_W}) must be loaded with {saved_W} shards")
+                owned = self._read_owned_range(local_path, "model", ("flat_shard",), saved_W)["flat_shard"]
             if not self.forward_only:
-                self.master.copy_(st["flat_shard"])
-            self._scatter_owned(st["flat_shard"].to(self.device), self.tparams.flat)
+                self.master.copy_(owned)
+            self._scatter_owned(owned.to(self.device), self.tparams.flat)
             self._publish_shard()
             if self.lora is not None:
                 self.lora.merge()
-        op = os.path.join(local_path, f"optim_world_size_{W}_rank_{r}.pt")
-        if "optimizer" in contents and not self.forward_only and os.path.exists(op):
-            st = torch.load(op, map_location="cpu", weights_only=False)
+        if "optimizer" in contents and not self.forward_only:
+            op = shard_file("optim")
+            st = torch.load(op, map_location="cpu", weights_only=False) if op is not None else \
+                self._read_owned_range(local_path, "optim", ("exp_avg", "exp_avg_sq"), saved_W)
             self.exp_avg.copy_(st["exp_avg"])
             self.exp_avg_sq.copy_(st["exp_avg_sq"])
             self.opt_step_count = int(st["step"])
-        ep = os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt")
-        if "extra" in contents and os.path.exists(ep):
-            st = torch.load(ep, map_location="cpu", weights_only=False)
-            self.sched_step = int(st["sched_step"])
-            torch.set_rng_state(st["rng"])
-            if st.get("cuda_rng") is not None and self.device.type == "cuda":
-                torch.cuda.set_rng_state(st["cuda_rng"])
+        if "extra" in contents:
+            ep = os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt")
+            if not os.path.exists(ep):
+                if saved_W is None or saved_W == W:
+                    raise FileNotFoundError(f"{ep} is missing although load_contents asks for the extra state")
+                # another shard world size: the schedule position is shared by all ranks, random streams start afresh
+                ep = os.path.join(local_path, f"extra_state_world_size_{saved_W}_rank_0.pt")
+                if not os.path.exists(ep):
+                    raise FileNotFoundError(f"{ep} is missing (the checkpoint records shard world size {saved_W})")
+                self.sched_step = int(torch.load(ep, map_location="cpu", weights_only=False)["sched_step"])
+            else:
+                st = torch.load(ep, map_location="cpu", weights_only=False)
+                self.sched_step = int(st["sched_step"])
+                torch.set_rng_state(st["rng"])
+                if st.get("cuda_rng") is not None and self.device.type == "cuda":
+                    torch.cuda.set_rng_state(st["cuda_rng"])
 
 
 @EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "fsdp_turbo", "native", "veomni", "torchtitan", "automodel"],
