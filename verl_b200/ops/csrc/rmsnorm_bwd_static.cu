@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <cstdint>
 #include <mutex>
 
 namespace {
@@ -154,10 +155,21 @@ extern "C" int vb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
   if (T < 0) return -3;
   if (H <= 0 || (H % 8) != 0) return -1;
   if (H > kMaxH) return -2;
+  // every row is read and written in 16-byte packets: a null or unaligned pointer would fault on the device, so it is
+  // turned away here, before anything is launched
+  if (dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr || dw == nullptr) return -5;
+  const auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (misaligned(dy, 16) || misaligned(x, 16) || misaligned(w, 16) || misaligned(dx, 16) ||
+      (dres_in != nullptr && misaligned(dres_in, 16)) || misaligned(rstd, 4) || misaligned(dw, 4))
+    return -6;
   float* partial = nullptr;
   const int rc = buffer_for_current_device(&partial);
   if (rc != 0) return rc;
-  if (T == 0) return 0;
+  if (T == 0) {
+    // no rows: the weight gradient of this call is zero; "overwritten" still has to hold
+    if (!accumulate_dw) return static_cast<int>(cudaMemsetAsync(dw, 0, static_cast<size_t>(H) * sizeof(float), stream));
+    return 0;
+  }
   const int blocks = T < kMaxBlocks ? T : kMaxBlocks;
   const int vpt = (H / 8 + kThreads - 1) / kThreads;
   const auto* dy_ = static_cast<const __nv_bfloat16*>(dy);
@@ -181,6 +193,8 @@ extern "C" const char* vb_rmsnorm_bwd_static_strerror(int code) {
     case -2: return "vb_rmsnorm_bwd_static: row length H exceeds the built-in buffer (max 8192); use vb_rmsnorm_bwd with your own scratch";
     case -3: return "vb_rmsnorm_bwd_static: negative row count";
     case -4: return "vb_rmsnorm_bwd_static: device ordinal beyond the per-device table (64)";
+    case -5: return "vb_rmsnorm_bwd_static: dy, x, w, rstd, dx and dw must not be null";
+    case -6: return "vb_rmsnorm_bwd_static: dy, x, w, dx and dres_in must be 16-byte aligned (rstd and dw 4-byte aligned)";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "vb_rmsnorm_bwd_static: unknown code";
   }
 }

@@ -15,11 +15,16 @@ extern "C" {
 #define VB_RMSNORM_BWD_STATIC_MAX_BLOCKS 148 // partial rows kept (one per SM)
 
 // dx[T,H] (bf16) and dw[H] (fp32; overwritten, or added to when accumulate_dw != 0) from dy, x, w (bf16),
-// rstd[T] (fp32) and an optional incoming residual gradient dres_in (bf16, may be null).
+// rstd[T] (fp32) and an optional incoming residual gradient dres_in (bf16, may be null).  Rows are contiguous
+// (row stride H).  dy, x, w, dx and dres_in are read and written 16 bytes at a time and must be 16-byte
+// aligned; rstd and dw need the natural 4-byte alignment.  With T == 0 there is nothing to sum: dw is set to
+// zero (left as it is when accumulate_dw != 0) and dx is not touched.
 //
 // Returns 0, a positive cudaError_t, or a negative code that vb_rmsnorm_bwd_static_strerror() explains:
 //   -1  H is not a multiple of 8            -2  H exceeds VB_RMSNORM_BWD_STATIC_MAX_H
 //   -3  T is negative                       -4  more devices than the per-device table holds
+//   -5  a required pointer is null          -6  a pointer is not aligned as stated above
+// The argument checks (-1 .. -6) run on the host before anything is launched.
 //
 // * No cudaMalloc / cudaFree / allocating library call is made, on the first call or later.
 // * The first call on each device looks up the address of the built-in buffer (cudaGetSymbolAddress) and

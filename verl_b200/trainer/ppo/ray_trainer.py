@@ -59,17 +59,77 @@ class ResourcePoolManager:
         return sum(n for procs in self.resource_pool_spec.values() for n in procs)
 
 
-def apply_kl_penalty(data: DataProto, kl_ctrl, kl_penalty: str = "kl"):
-    """token_level_rewards = token_level_scores - beta * KL(old || ref); updates the adaptive controller."""
+class DataParallelView:
+    """What a rank of a controller-replicated (SPMD) run needs to compute statistics over the *global* batch: gathers of
+    per-sample tensors / arrays over the distinct data-parallel replicas, and the position of the local samples in the
+    gathered batch. ``stride`` ranks in a row hold the same data (a model-parallel block); one of them is counted."""
+
+    def __init__(self, group, stride: int = 1):
+        self.group, self.stride = group, max(1, int(stride))
+        self.rank = dist.get_rank(group) // self.stride
+        self.world = dist.get_world_size(group) // self.stride
+        self._sizes = None
+
+    def _pick(self, parts: list) -> list:
+        return parts[:: self.stride]
+
+    def sizes(self, n: int) -> list[int]:
+        if self._sizes is None:
+            got = [None] * dist.get_world_size(self.group)
+            dist.all_gather_object(got, int(n), group=self.group)
+            self._sizes = self._pick(got)
+        return self._sizes
+
+    def tensor(self, t: torch.Tensor) -> torch.Tensor:
+        sizes = self.sizes(t.shape[0])
+        if len(set(sizes)) == 1:
+            parts = [torch.empty_like(t) for _ in range(dist.get_world_size(self.group))]
+            dist.all_gather(parts, t.contiguous(), group=self.group)
+            return torch.cat(self._pick(parts), dim=0)
+        got = [None] * dist.get_world_size(self.group)
+        dist.all_gather_object(got, t.cpu(), group=self.group)
+        return torch.cat([x.to(t.device) for x in self._pick(got)], dim=0)
+
+    def array(self, a: np.ndarray) -> np.ndarray:
+        got = [None] * dist.get_world_size(self.group)
+        dist.all_gather_object(got, a, group=self.group)
+        return np.concatenate(self._pick(got), axis=0)
+
+    def local(self, t, n: int):
+        lo = sum(self.sizes(n)[: self.rank])
+        return t[lo : lo + n]
+
+    def sum(self, *vals: float) -> list[float]:
+        """Sums over the distinct replicas of a few host scalars."""
+        t = torch.tensor([float(v) for v in vals], dtype=torch.float64)
+        got = [None] * dist.get_world_size(self.group)
+        dist.all_gather_object(got, t, group=self.group)
+        return torch.stack(self._pick(got)).sum(0).tolist()
+
+
+def apply_kl_penalty(data: DataProto, kl_ctrl, kl_penalty: str = "kl", dp: Optional[DataParallelView] = None):
+    """token_level_rewards = token_level_scores - beta * KL(old || ref); updates the adaptive controller with the mean
+    KL and the size of the *global* batch (``dp``: the other data-parallel ranks hold the rest of it)."""
     mask = data.batch["response_mask"]
     scores = data.batch["token_level_scores"]
     bsz = data.batch.batch_size[0]
     kld = core_algos.kl_penalty(data.batch["old_log_probs"], data.batch["ref_log_prob"], kl_penalty=kl_penalty) * mask
     beta = kl_ctrl.value
     data.batch["token_level_rewards"] = scores - beta * kld
-    current = torch.mean(VF.masked_mean(kld, mask=mask, axis=-1), dim=0).item()
+    per_seq = VF.masked_mean(kld, mask=mask, axis=-1)
+    if dp is not None and dp.world > 1:
+        total, count = dp.sum(per_seq.sum().item(), bsz)
+        current, bsz = total / max(count, 1.0), int(count)
+    else:
+        current = torch.mean(per_seq, dim=0).item()
     kl_ctrl.update(current_kl=current, n_steps=bsz)
     return data, {"actor/reward_kl_penalty": current, "actor/reward_kl_penalty_coeff": beta}
+
+
+# estimators whose result depends on statistics of the whole batch (whitening, batch-size scaling): in a run where every
+# rank holds a slice of the batch they are evaluated on the gathered batch, so the result does not depend on the
+# data-parallel size
+BATCH_WIDE_ESTIMATORS = ("gae", "reinforce_plus_plus", "reinforce_plus_plus_baseline", "gpg", "gdpo")
 
 
 def compute_response_mask(data: DataProto) -> torch.Tensor:
@@ -78,14 +138,26 @@ def compute_response_mask(data: DataProto) -> torch.Tensor:
 
 
 def compute_advantage(data: DataProto, adv_estimator, gamma: float = 1.0, lam: float = 1.0, num_repeat: int = 1,
-                      norm_adv_by_std_in_grpo: bool = True, config=None) -> DataProto:
+                      norm_adv_by_std_in_grpo: bool = True, config=None, dp: Optional[DataParallelView] = None) -> DataProto:
     """Fill ``advantages`` / ``returns`` with the configured estimator (device kernels for GAE and GRPO when the
-    batch lives on a GPU)."""
+    batch lives on a GPU). With ``dp`` (this rank holds a slice of the batch) the estimators of
+    ``BATCH_WIDE_ESTIMATORS`` run on the gathered batch and the local rows are kept."""
     if "response_mask" not in data.batch.keys():
         data.batch["response_mask"] = compute_response_mask(data)
+    name = adv_estimator.value if isinstance(adv_estimator, AdvantageEstimator) else str(adv_estimator)
+    if dp is not None and dp.world > 1 and name in BATCH_WIDE_ESTIMATORS and not (config is not None and config.get("use_pf_ppo", False)):
+        n = data.batch.batch_size[0]
+        keys = [k for k in ("token_level_rewards", "response_mask", "values", "reward_baselines", "old_log_probs", "sum_pi_squared",
+                            "rollout_is_weights", "prompts", "attention_mask") if k in data.batch.keys()]
+        full = DataProto.from_dict(tensors={k: dp.tensor(data.batch[k]) for k in keys},
+                                   non_tensors={k: dp.array(np.asarray(v)) for k, v in data.non_tensor_batch.items()
+                                                if k == "uid" or (name == "gdpo" and np.asarray(v).dtype != object)})
+        full = compute_advantage(full, adv_estimator, gamma, lam, num_repeat, norm_adv_by_std_in_grpo, config, dp=None)
+        data.batch["advantages"] = dp.local(full.batch["advantages"], n).contiguous()
+        data.batch["returns"] = dp.local(full.batch["returns"], n).contiguous()
+        return data
     mask = data.batch["response_mask"]
     rewards = data.batch["token_level_rewards"]
-    name = adv_estimator.value if isinstance(adv_estimator, AdvantageEstimator) else str(adv_estimator)
     if name == "gae":
         if rewards.is_cuda:
             from ...ops import functional as OF
@@ -172,6 +244,18 @@ class RayPPOTrainer:
                 return dist.get_rank(g) // mp, dist.get_world_size(g) // mp
             return dist.get_rank(g), dist.get_world_size(g)
         return 0, 1
+
+    def _dp_view(self) -> Optional[DataParallelView]:
+        """Access to the rest of the global batch when every rank drives its own slice (SPMD), else None."""
+        if not (self.spmd and dist.is_initialized()):
+            return None
+        from ...utils.distributed import get_data_parallel_group
+
+        g = get_data_parallel_group()
+        mp = self._model_parallel_size()
+        stride = mp if mp > 1 and (g is None or str(self.config.actor_rollout_ref.actor.get("strategy", "fsdp")) != "megatron") else 1
+        view = DataParallelView(g, stride)
+        return view if view.world > 1 else None
 
     def _model_parallel_size(self) -> int:
         a = self.config.actor_rollout_ref.actor
@@ -532,7 +616,8 @@ class RayPPOTrainer:
                     batch = batch.union(self.critic_wg.compute_values(batch))
             with marked_timer("adv", timing_raw, color="brown"):
                 if algo.get("use_kl_in_reward", False):
-                    batch, kl_m = apply_kl_penalty(batch, kl_ctrl=self.kl_ctrl_in_reward, kl_penalty=algo.get("kl_penalty", "kl"))
+                    batch, kl_m = apply_kl_penalty(batch, kl_ctrl=self.kl_ctrl_in_reward, kl_penalty=algo.get("kl_penalty", "kl"),
+                                                   dp=self._dp_view())
                     metrics.update(kl_m)
                 else:
                     batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
@@ -544,7 +629,8 @@ class RayPPOTrainer:
                     metrics.update(rc_m)
                 batch = compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
                                           lam=algo.get("lam", 1.0), num_repeat=rollout_cfg.n,
-                                          norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo)
+                                          norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo,
+                                          dp=self._dp_view())
             if self.use_critic:
                 with marked_timer("update_critic", timing_raw, color="pink"):
                     cout = self.critic_wg.update_critic(batch)
