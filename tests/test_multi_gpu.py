@@ -1,6 +1,8 @@
-"""Two-rank GPU tests (NCCL + peer memory): fused reduce-scatter/AdamW/all-gather vs the NCCL path, one-shot peer
-all-reduce, and a peer barrier whose wait runs out and reports a status instead of hanging.
-Skipped when fewer than two GPUs are visible."""
+"""Two-rank GPU tests (NCCL + peer memory), one test per protocol on a shared pair of worker processes: one-shot peer
+all-reduce, GEMM with the all-reduce in its epilogue, a weight read in place from its owner, expert-parallel dispatch /
+combine, the fused reduce-scatter / AdamW / all-gather optimizer step against the NCCL path, the same kernels through the
+NVSwitch multicast mapping, expert-parallel training, and a peer barrier whose wait runs out and reports a status instead
+of hanging. Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 
@@ -16,33 +18,17 @@ def _port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, queue):
-    try:
-        _worker_body(rank, world, port, queue)
-    except Exception:  # report instead of leaving the parent waiting
-        import traceback
-
-        queue.put((rank, {"error": traceback.format_exc()}))
-
-
-def _worker_body(rank, world, port, queue):
-    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _sec_allreduce(rank, world, dev, ops, res):
     import torch.distributed as dist
+    from functools import partial
 
     from verl_b200.models.config import ModelConfig
     from verl_b200.ops import native
     from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
-    from verl_b200.utils.distributed import initialize_global_process_group
     from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
     from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
     from verl_b200.workers.utils.losses import sft_loss
-    from functools import partial
 
-    initialize_global_process_group()
-    dev = torch.device("cuda", rank)
-    ops = native.ops()
-    res = {}
     # ---- one-shot peer all-reduce
     buf = SymmetricBuffer.allocate(4096, torch.bfloat16, dev)
     bar = PeerBarrier(dev)
@@ -53,6 +39,19 @@ def _worker_body(rank, world, port, queue):
     bar()
     expect = sum((torch.arange(4096, device=dev) % 7 + r).float() for r in range(world))
     res["allreduce_err"] = (outt.float() - expect).abs().max().item()
+
+
+def _sec_gemm_allreduce(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- row-parallel GEMM with the all-reduce inside the epilogue: three calls in a row (epochs, buffer halves)
     from verl_b200.parallel.symmetric import FusedRowParallelLinear
 
@@ -94,6 +93,19 @@ def _worker_body(rank, world, port, queue):
     res["gemm_ar_err"] = max(errs)
     res["gemm_ar_identical"] = all(same)
     res["gemm_status"] = int(ops.gemm_status())
+
+
+def _sec_peer_sharded_weight(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- weight stored in row blocks on the ranks, read in place by the GEMM (no gather)
     from verl_b200.parallel.symmetric import PeerShardedLinear
 
@@ -108,6 +120,19 @@ def _worker_body(rank, world, port, queue):
     refp = xs.float().cpu() @ w_full.float().t() + bias_p.float()
     res["peer_b_err"] = ((yp.float().cpu() - refp).norm() / refp.norm()).item()
     psl.barrier()
+
+
+def _sec_expert_parallel_layer(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- expert-parallel MoE layer (dispatch / combine over peer memory) against the single-GPU layer
     from verl_b200.models import DecoderModel, FlatParams
     from verl_b200.parallel.expert_parallel import ExpertParallelMoE
@@ -130,6 +155,19 @@ def _worker_body(rank, world, port, queue):
     res["ep_repeat_equal"] = bool(torch.equal(ep_out, ep_out2))
     res["ep_dropped"] = int(ep.dropped)
     res["ep_status"] = int(ops.comm_status())
+
+
+def _sec_fused_optimizer(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- engines: fused peer-memory optimizer vs NCCL
     arch = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, eos_token_id=2, pad_token_id=0)
@@ -158,6 +196,19 @@ def _worker_body(rank, world, port, queue):
     res["param_diff"] = (finals[True][0] - finals[False][0]).abs().max().item()
     res["norm_diff"] = max(abs(a - b) for a, b in zip(finals[True][1], finals[False][1]))
     res["norm"] = finals[True][1]
+
+
+def _sec_expert_parallel_training(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- expert-parallel training engine (experts split over the two ranks, NCCL token exchange) vs replicated experts
     from verl_b200.workers.config import McoreEngineConfig
     from verl_b200.workers.engine.base import EngineRegistry
@@ -181,6 +232,19 @@ def _worker_body(rank, world, port, queue):
     res["ep_train_norms"] = (ep_res["rep"][0], ep_res["ep"][0])
     res["ep_train_param_diff"] = (ep_res["rep"][1] - ep_res["ep"][1]).abs().max().item()
     os.environ["VERL_B200_FUSED_COMM"] = "1"
+
+
+def _sec_barrier_timeout(rank, world, dev, ops, res):
+    import torch.distributed as dist
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.ops import native
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
     # ---- a barrier that nobody else joins runs out after its limit and reports through the status word
     lonely = PeerBarrier(dev)
     torch.cuda.synchronize()
@@ -191,35 +255,187 @@ def _worker_body(rank, world, port, queue):
         res["timeout_status"] = int(ops.comm_status())
         res["alive_after_timeout"] = float(torch.ones(4, device=dev).sum())
     dist.barrier()
-    queue.put((rank, res))
-    dist.destroy_process_group()
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_rank_fused_optimizer_and_peer_collectives():
-    import torch.multiprocessing as mp
 
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    results = dict(q.get(timeout=240) for _ in range(2))
-    for p in procs:
-        p.join(timeout=60)
-    for r in (0, 1):
-        assert "error" not in results[r], results[r]["error"]
-    for r in (0, 1):
-        res = results[r]
+def _sec_multimem(rank, world, dev, ops, res):
+    """The reduce-scatter and AdamW + all-gather kernels through the NVSwitch multicast mapping (``multimem.ld_reduce`` /
+    ``multimem.st``) against the same kernels on plain peer loads / stores."""
+    from verl_b200.parallel.symmetric import PeerBarrier, SymmetricBuffer
+
+    n = 1 << 16
+    grads = SymmetricBuffer.allocate(n, torch.float32, dev)
+    params = SymmetricBuffer.allocate(n, torch.bfloat16, dev)
+    params_mc = SymmetricBuffer.allocate(n, torch.bfloat16, dev)
+    bar = PeerBarrier(dev)
+    res["multicast_available"] = bool(grads.multicast_ptr and params_mc.multicast_ptr)
+    if not res["multicast_available"]:
+        return
+    g = torch.Generator(device="cpu").manual_seed(11 + rank)
+    grads.tensor.copy_(torch.randn(n, generator=g).to(dev))
+    sh = n // world
+    lo = rank * sh
+    outs, ctrls = [], []
+    bar()
+    for mc in (0, grads.multicast_ptr):
+        o, c = torch.empty(sh, device=dev), torch.zeros(4, device=dev)
+        ops.rs_sumsq_(grads.ptrs, mc, o, lo, rank, 1.0 / world, c)
+        outs.append(o)
+        ctrls.append(c)
+    torch.cuda.synchronize()
+    res["rs_diff"] = (outs[0] - outs[1]).abs().max().item()
+    res["rs_scale"] = outs[0].abs().max().item()
+    res["sumsq_rel"] = abs(float(ctrls[0][0]) - float(ctrls[1][0])) / max(float(ctrls[0][0]), 1e-12)
+    bar()
+    states = []
+    for mc, buf in ((0, params), (params_mc.multicast_ptr, params_mc)):
+        gm = torch.Generator(device="cpu").manual_seed(40 + rank)
+        master = torch.randn(sh, generator=gm).to(dev)
+        m, v = torch.zeros(sh, device=dev), torch.zeros(sh, device=dev)
+        c = torch.tensor([0.0, 1.0, 0.0, 0.0], device=dev)
+        ops.adamw_allgather_(master, outs[0], m, v, buf.ptrs, mc, lo, rank, c, 1e-2, 0.9, 0.999, 1e-8, 0.01, 1)
+        torch.cuda.synchronize()
+        bar()
+        states.append((master.clone(), buf.tensor.clone()))
+    torch.cuda.synchronize()
+    res["adamw_master_equal"] = bool(torch.equal(states[0][0], states[1][0]))
+    res["adamw_published_equal"] = bool(torch.equal(states[0][1], states[1][1]))  # every rank's slice arrived, both ways
+    res["own_slice_ok"] = bool(torch.equal(states[1][1][lo:lo + sh], states[1][0].bfloat16()))
+    res["status"] = int(ops.comm_status())
+    bar()
+
+
+SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
+
+
+def _worker(rank, world, port, cmd_q, res_q):
+    """One rank of the shared pair: initialise once, then run the sections the parent asks for."""
+    try:
+        os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                          MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+
+        from verl_b200.ops import native
+        from verl_b200.utils.distributed import initialize_global_process_group
+
+        initialize_global_process_group()
+        dev = torch.device("cuda", rank)
+        ops = native.ops()
+        res_q.put((rank, "ready", {}))
+    except Exception:
+        import traceback
+
+        res_q.put((rank, "ready", {"error": traceback.format_exc()}))
+        return
+    while True:
+        name = cmd_q.get()
+        if name is None:
+            break
+        res = {}
+        try:
+            SECTIONS[name](rank, world, dev, ops, res)
+            torch.cuda.synchronize()
+        except Exception:
+            import traceback
+
+            res["error"] = traceback.format_exc()
+        res_q.put((rank, name, res))
+    try:
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+class _Pair:
+    def __init__(self):
+        import torch.multiprocessing as mp
+
+        ctx = mp.get_context("spawn")
+        self.res_q = ctx.Queue()
+        self.cmd_qs = [ctx.Queue() for _ in range(2)]
+        port = _port()
+        self.procs = [ctx.Process(target=_worker, args=(r, 2, port, self.cmd_qs[r], self.res_q)) for r in range(2)]
+        for p in self.procs:
+            p.start()
+        self._collect("ready", 300)
+
+    def _collect(self, name, timeout):
+        got = {}
+        for _ in range(2):
+            rank, what, res = self.res_q.get(timeout=timeout)
+            assert what == name, (what, name)
+            got[rank] = res
+        for r in (0, 1):
+            assert "error" not in got[r], got[r]["error"]
+        return got
+
+    def run(self, name, timeout=300):
+        for q in self.cmd_qs:
+            q.put(name)
+        return self._collect(name, timeout)
+
+    def close(self):
+        for q in self.cmd_qs:
+            q.put(None)
+        for p in self.procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()  # this exact child, after it had its chance to leave between steps
+
+
+@pytest.fixture(scope="module")
+def pair():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    p = _Pair()
+    yield p
+    p.close()
+
+
+def test_one_shot_peer_allreduce(pair):
+    for res in pair.run("allreduce").values():
         assert res["allreduce_err"] == 0.0
-        assert res["ep_err"] < 2e-2 and res["ep_repeat_equal"] and res["ep_dropped"] == 0 and res["ep_status"] == 0, res
+
+
+def test_gemm_with_allreduce_epilogue(pair):
+    for res in pair.run("gemm_allreduce").values():
         assert res["gemm_ar_err"] < 1e-2 and res["gemm_ar_identical"] and res["gemm_status"] == 0, res
         assert res["gemm_ar_splitk_used"] > 1, res   # the decode-sized case went through the K-split path
+
+
+def test_weight_read_in_place_from_its_owner(pair):
+    for res in pair.run("peer_sharded_weight").values():
         assert res["peer_b_err"] < 1e-2, res
+
+
+def test_expert_parallel_layer_over_peer_memory(pair):
+    for res in pair.run("expert_parallel_layer").values():
+        assert res["ep_err"] < 2e-2 and res["ep_repeat_equal"] and res["ep_dropped"] == 0 and res["ep_status"] == 0, res
+
+
+def test_fused_optimizer_step_matches_nccl_path(pair):
+    for res in pair.run("fused_optimizer").values():
         assert res["replica_diff_True"] == 0.0 and res["replica_diff_False"] == 0.0
         assert res["param_diff"] < 2e-2, res      # bf16 weights after two identical-math updates
         assert res["norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res
+
+
+def test_multimem_kernels_match_peer_loads(pair):
+    got = pair.run("multimem")
+    if not got[0]["multicast_available"]:
+        pytest.skip("no NVSwitch multicast mapping for symmetric buffers on this machine")
+    for res in got.values():
+        assert res["rs_diff"] <= 1e-6 * max(1.0, res["rs_scale"]) and res["sumsq_rel"] < 1e-5, res
+        assert res["adamw_master_equal"] and res["adamw_published_equal"] and res["own_slice_ok"] and res["status"] == 0, res
+
+
+def test_expert_parallel_training_matches_replicated_experts(pair):
+    for res in pair.run("expert_parallel_training").values():
         n_rep, n_ep = res["ep_train_norms"]
         assert abs(n_rep - n_ep) < 1e-2 * max(1.0, n_rep) and res["ep_train_param_diff"] < 5e-3, res  # one AdamW step of lr 1e-3
-    assert results[0]["timeout_status"] == 4 and results[0]["alive_after_timeout"] == 4.0
+
+
+def test_peer_barrier_that_nobody_joins_reports_status(pair):
+    got = pair.run("barrier_timeout")
+    assert got[0]["timeout_status"] == 4 and got[0]["alive_after_timeout"] == 4.0
