@@ -25,10 +25,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
-import subprocess
 import sys
-import threading
 import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
@@ -113,56 +110,6 @@ class _HostEvent:
         return (other.t - self.t) * 1e3
 
 
-class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
-
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "500",
-                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except Exception:
-            self.proc = None
-
-    def _read(self):
-        for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        return self.snapshot()
-
-    def snapshot(self) -> dict:
-        """Summary of the samples so far (the sampler keeps running)."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in list(self.lines):
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        busy = [c for c in sm if c > 0]
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
-
-
 def build_config(args, world: int):
     if args.no_prefix_sharing:
         os.environ["VERL_B200_SHARE_PREFIX"] = "0"
@@ -224,6 +171,7 @@ def main():
     from verl_b200.trainer.ppo.reward import load_reward_manager
     from verl_b200.single_controller.local import SPMDWorkerGroup
     from verl_b200.utils.distributed import initialize_global_process_group
+    from verl_b200.utils.profiler.clocks import ClockSampler
 
     on_gpu = args.device == "cuda"
     if not on_gpu:
@@ -304,7 +252,7 @@ def main():
     # step runs through the trainer's public ``train_step``, the per-sample scores and the metric scalars are read
     # back (D2H inside the end-to-end region).  ``value`` sums per-step CUDA-event spans that start after the H2D copy
     # and end before the read-back; ``e2e`` is the span of the whole loop.
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and on_gpu else None
+    sampler = ClockSampler(torch.cuda.current_device(), period_s=0.5) if rank == 0 and on_gpu else None
     if sampler:
         sampler.start()
     gbs = args.prompts_per_gpu * world

@@ -226,3 +226,41 @@ def test_precision_debugger_writes_per_layer_statistics(tmp_path):
     assert [r["name"] for r in rows] == [f"layers.{i}.{k}" for i in range(L) for k in ("attn_out", "mlp_out")]
     assert all(r["nan"] == 0 and r["norm"] > 0 and r["shape"] == [24, eng.arch.hidden_size] for r in rows)
     assert eng.model.stats_hook is None
+
+
+def test_clock_sampler_reads_a_fake_nvml():
+    import time
+
+    from verl_b200.utils.profiler.clocks import ClockSampler
+
+    class FakeNvml:
+        NVML_CLOCK_SM = 1
+
+        def __init__(self):
+            self.calls = 0
+
+        def nvmlInit(self):
+            pass
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetMaxClockInfo(self, h, kind):
+            return 1965
+
+        def nvmlDeviceGetClockInfo(self, h, kind):
+            self.calls += 1
+            return 210 if self.calls <= 2 else 1500  # idle before the load arrives
+
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 950_000
+
+        def nvmlDeviceGetCurrentClocksEventReasons(self, h):
+            return 0x4 | 0x1  # power cap + idle bit (the latter is not a throttle reason)
+
+    s = ClockSampler(0, period_s=0.002, nvml=FakeNvml()).start()
+    time.sleep(0.05)
+    mid = s.snapshot()
+    rec = s.stop()
+    assert rec["sm_mhz"] == 1500.0 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == ["sw_power_cap"]
+    assert rec["power_w_max"] == 950.0 and rec["samples"] >= mid["samples"] > 2

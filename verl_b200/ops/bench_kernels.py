@@ -17,6 +17,7 @@ import os
 
 import torch
 
+from ..utils.profiler.clocks import ClockSampler
 from . import native
 
 
@@ -40,9 +41,17 @@ class Timer:
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def __call__(self, fn) -> float:
+        """Mean milliseconds per call; ``self.clocks`` holds the SM clock record of this timed region."""
         for _ in range(self.warmup):
             fn()
         torch.cuda.synchronize()
+        sampler = ClockSampler(self.dev.index or 0, period_s=0.01).start()
+        try:
+            return self._timed(fn)
+        finally:
+            self.clocks = sampler.stop()
+
+    def _timed(self, fn) -> float:
         total = 0.0
         for _ in range(self.iters):
             self.flush.zero_()
@@ -81,6 +90,7 @@ def main(argv=None):
         if bytes_ is not None:
             gbs = bytes_ / ms / 1e6
             rec.update(gbs=round(gbs, 1), frac_hbm=round(gbs / pk["hbm_gbs"], 3), hbm_peak=f"{pk['hbm_gbs']} GB/s {tag}")
+        rec["clocks"] = getattr(T, "clocks", None)
         print(json.dumps(rec), flush=True)
 
     tok = 4096 if a.small else 16384

@@ -44,6 +44,7 @@ def main(argv=None):
     from ..ops import native
     from ..ops import functional as F
     from ..utils.distributed import initialize_global_process_group
+    from ..utils.profiler.clocks import ClockSampler
     from .symmetric import FusedRowParallelLinear, PeerBarrier, SymmetricBuffer
 
     initialize_global_process_group()
@@ -55,12 +56,15 @@ def main(argv=None):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     bar = PeerBarrier(dev)
 
+    clock_log: list = []  # rank 0's SM clock record of every timed region since the last report
+
     def timed(fn) -> float:
         """Mean over iterations of the max over ranks of the device time of ``fn`` (ms)."""
         for _ in range(a.warmup):
             fn()
         torch.cuda.synchronize()
         per_iter = []
+        sampler = ClockSampler(dev.index or 0, period_s=0.01).start() if rank == 0 else None
         for _ in range(a.iters):
             flush.zero_()
             dist.barrier()
@@ -71,6 +75,8 @@ def main(argv=None):
             e1.record()
             torch.cuda.synchronize()
             per_iter.append(e0.elapsed_time(e1))
+        if sampler is not None:
+            clock_log.append(sampler.stop())
         t = torch.tensor(per_iter, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.mean())
@@ -83,8 +89,10 @@ def main(argv=None):
                               "speedup": None if ms_nccl is None else round(ms_nccl / ms_fused, 3),
                               "roofline_ms": round(floor_ms, 4), "frac_of_roofline": round(floor_ms / ms_fused, 3),
                               "link_gbs": round(link_bytes / ms_fused / 1e6, 1),
+                              "clocks": list(clock_log),
                               "denominators": f"{pk['bf16_tflops']} TFLOP/s, {pk['hbm_gbs']} GB/s {tag}; NVLink {NVLINK_GBS} GB/s per direction"}),
                   flush=True)
+        clock_log.clear()
 
     n = (a.numel // (world * 1024)) * world * 1024
     shard = n // world

@@ -56,11 +56,15 @@ def main(argv=None):
     eng.temperature = 1.0
     eng._decode_steps(a.warmup)
     torch.cuda.synchronize()
+    from ....utils.profiler.clocks import ClockSampler
+
+    sampler = ClockSampler(dev.index or 0, period_s=0.02).start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     eng._decode_steps(a.steps)
     e1.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / a.steps
     weight_bytes = (P.numel - (0 if cfg.tie_word_embeddings else cfg.vocab_size * cfg.hidden_size)) * 2
     kv_bytes = S * (a.ctx + a.steps // 2) * cfg.num_hidden_layers * 2 * cfg.kv_size * 2
@@ -68,7 +72,7 @@ def main(argv=None):
     print(json.dumps({"model": a.model, "seqs": S, "ctx": a.ctx, "graph": not a.eager, "ms_per_step": round(ms, 3),
                       "tokens_per_s": round(S / ms * 1e3, 1), "hbm_floor_ms": round(floor_ms, 3),
                       "fraction_of_hbm_roofline": round(floor_ms / ms, 3),
-                      "group": a.group, "shared_ctx": a.shared_ctx if a.group > 1 else 0}))
+                      "group": a.group, "shared_ctx": a.shared_ctx if a.group > 1 else 0, "clocks": clocks}))
 
 
 if __name__ == "__main__":
