@@ -261,7 +261,7 @@ def main():
     pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
     host_scores = pin(torch.empty(args.prompts_per_gpu * args.n, dtype=torch.float32))
     tokens = h2d = d2h = 0
-    reshard_s, phase_sum = 0.0, {}
+    reshard_s, phase_sum, grad_norms = 0.0, {}, []
 
     def report(k: int, partial: bool) -> None:
         """Collective over ranks; rank 0 prints one JSON line for the first ``k`` timed steps."""
@@ -301,6 +301,7 @@ def main():
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "api": "RayPPOTrainer.train_step on prompts staged from pinned host memory; scores and metrics read back"},
             "reshard_ms_per_step": 1e3 * reshard_s / k,
+            "grad_norm_per_step": [round(g, 4) for g in grad_norms[:k]],  # finite: the optimizer really stepped
             "gpu_launches": int(launch_count() - n0),
             "clocks": (sampler.stop() if not partial else sampler.snapshot()) if sampler else None,
             "phases_s": {name: round(v / k, 3) for name, v in phase_sum.items()},
@@ -327,6 +328,7 @@ def main():
         d2h = scores.numel() * 4 + 8 * len([v for v in last_metrics.values() if isinstance(v, (int, float))])
         tokens += int(sum(trainer.last_batch.meta_info["global_token_num"]))
         reshard_s += float(last_metrics.get("timing_s/update_weights", 0.0))
+        grad_norms.append(float(last_metrics.get("actor/grad_norm", float("nan"))))
         for k, v in last_metrics.items():
             if k.startswith("timing_s/") and isinstance(v, (int, float)):
                 phase_sum[k.split("/", 1)[1]] = phase_sum.get(k.split("/", 1)[1], 0.0) + float(v)

@@ -106,20 +106,54 @@ def _sec_peer_sharded_weight(rank, world, dev, ops, res):
     from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
     from verl_b200.workers.utils.losses import sft_loss
 
-    # ---- weight stored in row blocks on the ranks, read in place by the GEMM (no gather)
-    from verl_b200.parallel.symmetric import PeerShardedLinear
+    # ---- weight stored in slices on the ranks, gathered by the GEMM that consumes it (fetch warps, panel flags)
+    from verl_b200.parallel.symmetric import PeerShardedLinear, ShardedRange
 
-    g = torch.Generator(device="cpu").manual_seed(90)
-    w_full = (torch.randn(1024, 512, generator=g) * 0.05).bfloat16()
-    bias_p = torch.randn(1024, generator=g).bfloat16()
-    psl = PeerShardedLinear(1024, 512, dev)
-    psl.load_shard(w_full[rank * 512:(rank + 1) * 512].to(dev))
-    psl.barrier()
-    xs = torch.randn(300 + 17 * rank, 512, generator=g).bfloat16().to(dev)   # every rank has its own tokens
-    yp = psl(xs, bias_p.to(dev))
-    refp = xs.float().cpu() @ w_full.float().t() + bias_p.float()
-    res["peer_b_err"] = ((yp.float().cpu() - refp).norm() / refp.norm()).item()
-    psl.barrier()
+    errs, gathered_ok = [], []
+    # (N, K, rows): a weight of exactly 2 x 32 chunks; one whose slices are padded and whose last panel is ragged; a
+    # narrow one (128-wide tiles) with fewer tiles than SMs
+    for case, (N, K, rows) in enumerate([(1024, 512, 300), (1160, 1032, 1500), (128, 256, 40)]):
+        g = torch.Generator(device="cpu").manual_seed(90 + case)
+        w_full = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+        bias_p = torch.randn(N, generator=g).bfloat16()
+        psl = PeerShardedLinear(N, K, dev)
+        psl.load_full(w_full.to(dev))
+        psl.barrier()
+        for rep in range(2):  # second call: panel counters are cleared by the launcher, the arena is overwritten
+            xs = torch.randn(rows + 17 * rank, K, generator=g).bfloat16().to(dev)   # every rank has its own tokens
+            yp = psl(xs, bias_p.to(dev))
+            refp = xs.float().cpu() @ w_full.float().t() + bias_p.float()
+            errs.append(((yp.float().cpu() - refp).norm() / refp.norm()).item())
+            gathered_ok.append(bool(torch.equal(psl.gathered.cpu(), w_full)))
+        psl.barrier()
+    res["peer_b_err"] = max(errs)
+    res["peer_b_gathered"] = all(gathered_ok)
+    # ---- a GEMM on local operands that carries an unrelated gather (prefetch of what a later kernel needs), in two halves
+    total = 3 * 16384 * world + 4096
+    rng = ShardedRange(total, dev)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    full = torch.randint(0, 255, (total,), generator=g, dtype=torch.uint8)
+    rng.store_from_full(full.to(dev))
+    rng.barrier()
+    arena = torch.zeros(total, dtype=torch.uint8, device=dev)
+    a_l = torch.randn(200, 256, generator=g).bfloat16().to(dev)
+    b_l = torch.randn(384, 256, generator=g).bfloat16().to(dev)
+    half = rng.num_chunks // 2
+    y1 = ops.gemm_fetch(a_l, b_l, None, None, False, False, False, False, rng.buf.ptrs, arena, total, rng.slice_bytes, 0, half, -1, None, 2.0)
+    torch.cuda.synchronize()
+    res["piggyback_first_half"] = bool(torch.equal(arena[: half * 16384].cpu(), full[: half * 16384])) and int(arena[half * 16384:].sum()) == 0
+    # second half rides on a weight-gradient shaped GEMM (both operands MN-major, fp32 accumulate)
+    acc = torch.ones(256, 384, device=dev)
+    gy = torch.randn(200, 256, generator=g).bfloat16().to(dev)
+    gx = torch.randn(200, 384, generator=g).bfloat16().to(dev)
+    ops.gemm_fetch(gy, gx, None, acc, True, True, True, True, rng.buf.ptrs, arena, total, rng.slice_bytes, half, rng.num_chunks, -1, None, 2.0)
+    torch.cuda.synchronize()
+    res["piggyback_all"] = bool(torch.equal(arena.cpu(), full))
+    ref1 = a_l.float() @ b_l.float().t()
+    res["piggyback_gemm_err"] = max(((y1.float() - ref1).norm() / ref1.norm()).item(),
+                                    ((acc - (1.0 + gy.float().t() @ gx.float())).norm() / (gy.float().t() @ gx.float()).norm()).item())
+    res["fetch_status"] = int(ops.gemm_status())
+    rng.barrier()
 
 
 def _sec_expert_parallel_layer(rank, world, dev, ops, res):
@@ -404,9 +438,10 @@ def test_gemm_with_allreduce_epilogue(pair):
         assert res["gemm_ar_splitk_used"] > 1, res   # the decode-sized case went through the K-split path
 
 
-def test_weight_read_in_place_from_its_owner(pair):
+def test_gemm_that_gathers_its_sharded_weight(pair):
     for res in pair.run("peer_sharded_weight").values():
-        assert res["peer_b_err"] < 1e-2, res
+        assert res["peer_b_err"] < 1e-2 and res["peer_b_gathered"], res
+        assert res["piggyback_first_half"] and res["piggyback_all"] and res["piggyback_gemm_err"] < 1e-2 and res["fetch_status"] == 0, res
 
 
 def test_expert_parallel_layer_over_peer_memory(pair):

@@ -45,8 +45,18 @@ class CheckpointEngineRegistry:
 
         return deco
 
+    # transports of the reference whose libraries are absent here: they run the relay ring over torch.distributed p2p
+    ALIASES = {"nixl": "ring", "mooncake": "ring", "kimi": "ring", "hccl": "ring"}
+    _warned: set = set()
+
     @classmethod
     def get(cls, backend: str) -> type["CheckpointEngine"]:
+        if backend in cls.ALIASES and backend not in cls._warned:
+            import warnings
+
+            cls._warned.add(backend)
+            warnings.warn(f"checkpoint engine '{backend}' is served by the '{cls.ALIASES[backend]}' relay chain over torch.distributed "
+                          f"point-to-point messages (the {backend} transport library is not part of this framework)", stacklevel=2)
         if backend not in cls._registry:
             from . import delta_checkpoint_engine, nccl_checkpoint_engine, ring_checkpoint_engine  # noqa: F401  (self-registering)
         if backend not in cls._registry:

@@ -1198,6 +1198,8 @@ class DecoderModel:
     @torch.no_grad()
     def _backward(self, state: dict, grads) -> None:
         hN = state["hN"]
+        if self.pre_layer_hook is not None:  # the head's unit is the first one the backward pass touches
+            self.pre_layer_hook(self.cfg.num_hidden_layers, "backward")
         if state["kind"] == "lm":
             g_lp, g_ent = grads
             if g_lp is None:

@@ -512,25 +512,49 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   return d;
 }
 
-// D = a @ B^T (+ bias) where B's row blocks [rows_per_rank, K] (K-major, contiguous) live on the ranks of a group and are read
-// in place over NVLink; b_ptrs: int64 CPU tensor with every rank's block address (peer-mapped on this device).
-Tensor gemm_peer_b(const Tensor& a, const Tensor& b_ptrs, int64_t rows_per_rank, const OptTensor& bias, const OptTensor& out) {
+// GEMM (same operand conventions as `gemm`) that also runs a staged all-gather: chunks [chunk_begin, chunk_end) of 16 KB of a
+// byte range kept in equal slices on the ranks of a group (src_ptrs: int64 CPU tensor, peer-mapped slice addresses) are copied
+// into `dst` (a local uint8 / bf16 buffer) by an extra warp of every CTA. b_off_bytes >= 0: `b` is the view of `dst` at that byte
+// offset and is gathered by this launch itself; tiles wait for their rows (`panels`: int32 scratch, one word per column tile).
+Tensor gemm_fetch(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTensor& out, bool a_mn, bool b_mn, bool out_f32,
+                  bool accumulate, const Tensor& src_ptrs, Tensor dst, int64_t total_bytes, int64_t slice_bytes, int64_t chunk_begin,
+                  int64_t chunk_end, int64_t b_off_bytes, const OptTensor& panels, double limit_s) {
   CHECK_BF16(a);
-  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1, "gemm_peer_b: K-major 2-D activation");
+  CHECK_BF16(b);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_fetch: 2-D row-major operands");
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && (int64_t)dst.nbytes() >= total_bytes, "gemm_fetch: dst too small");
   const c10::cuda::CUDAGuard guard(a.device());
-  const int64_t M = a.size(0), K = a.size(1), world = b_ptrs.numel(), N = world * rows_per_rank;
-  Tensor d = out.has_value() ? *out : at::empty({M, N}, a.options());
-  TORCH_CHECK(d.scalar_type() == at::kBFloat16 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_peer_b: bad out");
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK(K == (b_mn ? b.size(0) : b.size(1)), "gemm_fetch: contraction mismatch");
+  Tensor d;
+  if (out.has_value()) {
+    d = *out;
+    TORCH_CHECK(d.dim() == 2 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_fetch: bad out shape");
+    TORCH_CHECK(d.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "gemm_fetch: bad out dtype");
+  } else {
+    TORCH_CHECK(!accumulate, "gemm_fetch: accumulate needs out");
+    d = at::empty({M, N}, a.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  }
   const void* bias_ptr = nullptr;
   if (bias.has_value()) {
-    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm_peer_b: bad bias");
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm_fetch: bad bias");
     bias_ptr = bias->data_ptr();
   }
-  if (M == 0) return d;
+  unsigned int* pc = nullptr;
+  if (b_off_bytes >= 0) {
+    TORCH_CHECK(panels.has_value() && panels->is_cuda() && panels->scalar_type() == at::kInt && panels->numel() >= (N + 127) / 128,
+                "gemm_fetch: panels: int32 CUDA tensor with one word per 128 output columns");
+    pc = reinterpret_cast<unsigned int*>(panels->data_ptr<int>());
+  }
+  if (M == 0 || N == 0) return d;
   count(1);
-  const int rc = vb_gemm_bf16_peer_b(a.data_ptr(), uptr(b_ptrs), d.data_ptr(), bias_ptr, (int)M, (int)K, a.stride(0), K, d.stride(0),
-                                     (int)world, (int)rows_per_rank, cur_stream());
-  TORCH_CHECK(rc == 0, "vb_gemm_bf16_peer_b failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+  const int rc = vb_gemm_bf16_fetch(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                                    d.stride(0), a_mn, b_mn, out_f32, accumulate, uptr(src_ptrs), (int)src_ptrs.numel(),
+                                    reinterpret_cast<unsigned long long>(dst.data_ptr()), total_bytes, slice_bytes, (int)chunk_begin,
+                                    (int)chunk_end, b_off_bytes, pc, limit_s, cur_stream());
+  TORCH_CHECK(rc == 0, "vb_gemm_bf16_fetch failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
   return d;
 }
 
@@ -772,7 +796,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("adamw_allgather_", &adamw_allgather_);
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
-  m.def("gemm_peer_b", &gemm_peer_b);
+  m.def("gemm_fetch", &gemm_fetch);
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);

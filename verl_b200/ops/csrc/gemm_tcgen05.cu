@@ -76,10 +76,23 @@ struct GemmParams {
   const int* grp_seg_start;  // [E + 1]
   int grp_b_rows;            // rows one expert occupies in the stacked 2-D view of B
   int grp_E;
-  // peer-sharded B (weights split by rows over the ranks of a group, read in place over NVLink): rank r owns rows
-  // [r * peer_rows, (r + 1) * peer_rows) of B and has its own tensor map
-  int peer_rows, peer_world;
+  // staged all-gather (FETCH variants). A byte range of `fetch_total` bytes is stored in equal slices of `fetch_slice`
+  // bytes on the ranks of a group (rank r holds bytes [r * slice, (r + 1) * slice) at fetch_src[r], peer-mapped). The
+  // extra warp of every CTA copies 16 KB chunks [fetch_c0, fetch_c1) of it into local memory at fetch_dst while the
+  // tensor pipe works. When B itself lies inside that range (at byte offset fetch_b_off, N * K * 2 bytes, rows
+  // contiguous), fetch_panel counts the chunks that have landed per BN-row panel of B and the TMA producer holds a
+  // tile back until its panel is complete; tiles then sweep all rows of the output per panel, so panels are needed
+  // at an even rate over the whole GEMM.
+  unsigned long long fetch_src[AR_MAX_RANKS];
+  unsigned long long fetch_dst;
+  long long fetch_total, fetch_slice, fetch_b_off;
+  int fetch_c0, fetch_c1;
+  unsigned int* fetch_panel;   // [ceil(N / BN)] zero at launch; null: B is local already, nothing waits
+  unsigned long long fetch_limit_ns;
 };
+
+constexpr int FETCH_CHUNK = 16384;  // bytes per copy job of the fetch warp
+constexpr int ST_TIMEOUT_FETCH = 14;
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -87,6 +100,11 @@ __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int
 __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ unsigned long long ar_now_ns() {
@@ -105,11 +123,9 @@ struct GemmSmem {
   static constexpr int TOTAL = RING + 256 + 1024;  // barriers + alignment slack
 };
 
-// Kernel body. ``tma_bs`` holds one tensor map of B (PEERS == 1) or one per rank of a group whose members each store a
-// row block of B (PEERS > 1): the producer then fetches every B tile from the memory of the rank that owns it.
-template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI, int PEERS>
-__device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap* tma_bs, const GemmParams& p) {
-  const CUtensorMap& tma_b = tma_bs[0];
+// Kernel body. FETCH adds a seventh warp that stages peer memory into local memory (see GemmParams::fetch_*).
+template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI, bool FETCH>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmParams& p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int A_BYTES = GemmSmem<BN, STAGES>::A_BYTES;
@@ -133,14 +149,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
   const int num_tiles = (p.grp_mode == 2) ? num_mn * p.grp_E : num_mn * splits;
   const int num_kb_total = (p.K + BK - 1) / BK;
   const int kb_per = (num_kb_total + splits - 1) / splits;
-  constexpr int GROUP_M = 8;
+  // rasterisation: groups of GROUP_M row tiles share their B panels through L2; a launch that waits for B panels to
+  // arrive sweeps every row tile of a panel before it moves to the next panel
+  const int GROUP_M = (FETCH && p.fetch_panel != nullptr) ? num_m : 8;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
-    if constexpr (PEERS > 1) {
-      for (int r = 1; r < p.peer_world; ++r) tma_prefetch_desc(&tma_bs[r]);
-    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -206,10 +221,35 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int panel_ready = -1;  // FETCH: last panel of B known to be complete in local memory
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m0, n0, kb0, kb1, b_off;
         long long d_off;
         if (!decode_tile(t, m0, n0, kb0, kb1, b_off, d_off)) continue;
+        if constexpr (FETCH) {
+          const int panel = n0 / BN;
+          if (p.fetch_panel != nullptr && panel != panel_ready) {
+            // chunks of this launch that intersect the panel's bytes
+            const long long lo = p.fetch_b_off + static_cast<long long>(n0) * p.K * 2;
+            const long long hi = p.fetch_b_off + static_cast<long long>(min(n0 + BN, p.N)) * p.K * 2;
+            const long long e_lo = max(lo / FETCH_CHUNK, static_cast<long long>(p.fetch_c0));
+            const long long e_hi = min((hi - 1) / FETCH_CHUNK, static_cast<long long>(p.fetch_c1) - 1);
+            const unsigned int expect = e_hi >= e_lo ? static_cast<unsigned int>(e_hi - e_lo + 1) : 0u;
+            const unsigned long long t0 = ar_now_ns();
+            unsigned int spins = 0;
+            while (ld_acquire_gpu_u32(p.fetch_panel + panel) < expect) {
+              if ((++spins & 0x3f) == 0 && ar_now_ns() - t0 > p.fetch_limit_ns) {
+                atomicExch(p.status, ST_TIMEOUT_FETCH);
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            // the chunks were written with ordinary stores; the tile loads below read them through the async proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            panel_ready = panel;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, ST_TIMEOUT_PRODUCER);
@@ -226,10 +266,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tma_a, &full_bar[stage], m0 + 64 * j, k0);
           }
-          if constexpr (PEERS > 1) {
-            const int owner = n0 / p.peer_rows;  // a tile never straddles two owners: peer_rows % BN == 0
-            tma_load_2d(sb, &tma_bs[owner], &full_bar[stage], k0, n0 - owner * p.peer_rows);
-          } else if constexpr (!B_MN) {
+          if constexpr (!B_MN) {
             tma_load_2d(sb, &tma_b, &full_bar[stage], k0, b_off + n0);
           } else {
 #pragma unroll
@@ -291,6 +328,45 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (FETCH && warp == 6) {
+    // ------------------------------------------------------------------ fetch warp: peer memory -> local memory
+    // Chunks are dealt round-robin over the CTAs in address order, so every CTA works on the panels that are needed
+    // first. 16 independent 16-byte loads per lane are in flight before the first store (8 KB per warp).
+    if constexpr (FETCH) {
+      const long long panel_bytes = static_cast<long long>(BN) * p.K * 2;
+      const long long b_end = p.fetch_b_off + static_cast<long long>(p.N) * p.K * 2;
+      for (int c = p.fetch_c0 + static_cast<int>(blockIdx.x); c < p.fetch_c1; c += static_cast<int>(gridDim.x)) {
+        const long long off = static_cast<long long>(c) * FETCH_CHUNK;
+        const long long len = min(static_cast<long long>(FETCH_CHUNK), p.fetch_total - off);
+        const int owner = static_cast<int>(off / p.fetch_slice);
+        const uint4* src = reinterpret_cast<const uint4*>(p.fetch_src[owner] + (off - owner * p.fetch_slice));
+        uint4* dst = reinterpret_cast<uint4*>(p.fetch_dst + off);
+        const int n16 = static_cast<int>(len >> 4);
+        for (int base = 0; base < n16; base += 32 * 16) {
+          uint4 v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = base + j * 32 + lane;
+            if (i < n16) v[j] = src[i];
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = base + j * 32 + lane;
+            if (i < n16) dst[i] = v[j];
+          }
+        }
+        if (p.fetch_panel != nullptr && off < b_end && off + len > p.fetch_b_off) {
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) {
+            const long long lo = max(off, p.fetch_b_off) - p.fetch_b_off;
+            const long long hi = min(off + len, b_end) - p.fetch_b_off;
+            for (long long pp = lo / panel_bytes; pp <= (hi - 1) / panel_bytes; ++pp) atomicAdd(p.fetch_panel + pp, 1u);
+          }
         }
       }
     }
@@ -573,18 +649,18 @@ template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmParams p) {
-  gemm_body<BN, A_MN, B_MN, STAGES, EPI, 1>(tma_a, &tma_b, p);
+  gemm_body<BN, A_MN, B_MN, STAGES, EPI, false>(tma_a, tma_b, p);
 }
 
-struct PeerMaps {
-  CUtensorMap m[AR_MAX_RANKS];
-};
+constexpr int GEMM_FETCH_THREADS = GEMM_THREADS + 32;
 
-// D = A * B^T with B's row blocks living on the ranks of a group (sharded weights, no gather): K-major operands.
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_peer_b_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ PeerMaps maps, const GemmParams p) {
-  gemm_body<BN, false, false, STAGES, EPI_STORE, AR_MAX_RANKS>(tma_a, maps.m, p);
+// The same GEMM with a fetch warp: the all-gather of a sharded byte range (the GEMM's own B operand, or whatever a later
+// kernel needs) runs inside the GEMM, over peer loads, behind the tensor pipe.
+template <int BN, bool A_MN, bool B_MN, int STAGES>
+__global__ void __launch_bounds__(GEMM_FETCH_THREADS, 1)
+gemm_bf16_fetch_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                       const GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, STAGES, EPI_STORE, true>(tma_a, tma_b, p);
 }
 
 // Device address of the status word, resolved once (outside any stream capture).
@@ -874,61 +950,93 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
   return static_cast<int>(e);
 }
 
-// D[M, N] = A[M, K] * B^T (+ bias) where B [N, K] is stored in row blocks of ``rows_per_rank`` on the ranks of a group and
-// read in place from their memory (TMA loads over NVLink, no all-gather): b_ptrs[r] = rank r's block (peer-mapped).
-// rows_per_rank must be a multiple of the tile width (256, or 128 when N <= 128 * world); N = world * rows_per_rank.
-extern "C" int vb_gemm_bf16_peer_b(const void* A, const unsigned long long* b_ptrs, void* D, const void* bias, int M, int K,
-                                   long long lda, long long ldb, long long ldd, int world, int rows_per_rank,
-                                   cudaStream_t stream) {
-  const int N = world * rows_per_rank;
+// GEMM with a staged all-gather running inside it (see GemmParams::fetch_*): D = op(A) * op(B) as vb_gemm_bf16, while
+// the extra warp of every CTA copies chunks [chunk_begin, chunk_end) (16 KB each) of a byte range that is stored in
+// equal slices on the ranks of a group (src_ptrs[r]: rank r's slice, peer-mapped; slice_bytes a multiple of 16 KB) to
+// local memory at dst. With b_off_bytes >= 0 the B operand is the K-major matrix at dst + b_off_bytes (rows contiguous,
+// ldb == K) and is being gathered by this very launch: `panel_counters` (ceil(N / tile width) words, cleared here) then
+// hold every tile back until the rows it reads have landed. With b_off_bytes < 0 the copy is unrelated to this GEMM's
+// operands (it prefetches what a later kernel needs) and nothing waits for it inside the kernel. Peers' slices must not
+// change while the kernel runs. A wait that runs out after limit_s reports code 14 through vb_gemm_status().
+extern "C" int vb_gemm_bf16_fetch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                  long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int out_f32,
+                                  int accumulate, const unsigned long long* src_ptrs, int world, unsigned long long dst,
+                                  long long total_bytes, long long slice_bytes, int chunk_begin, int chunk_end,
+                                  long long b_off_bytes, unsigned int* panel_counters, double limit_s,
+                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -1;
+  if ((lda % 8) || (ldb % 8) || (ldd % (out_f32 ? 4 : 8))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
   if (world < 1 || world > AR_MAX_RANKS) return -4;
-  const bool wide = rows_per_rank % 256 == 0;
+  if (total_bytes < 0 || (total_bytes & 15) || (dst & 15) || slice_bytes <= 0 || total_bytes > slice_bytes * world) return -7;
+  if (world > 1 && (slice_bytes % FETCH_CHUNK)) return -7;
+  const long long num_chunks = (total_bytes + FETCH_CHUNK - 1) / FETCH_CHUNK;
+  if (chunk_begin < 0 || chunk_end < chunk_begin || chunk_end > num_chunks) return -8;
+  const bool panel_mode = b_off_bytes >= 0;
+  const bool wide = N > 128;
   const int BN = wide ? 256 : 128;
-  if (rows_per_rank % BN) return -6;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
-  CUtensorMap ta;
-  PeerMaps maps{};
-  if (!make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
-  for (int r = 0; r < world; ++r) {
-    if (b_ptrs[r] & 15) return -2;
-    if (!make_tmap_2d(&maps.m[r], reinterpret_cast<const void*>(b_ptrs[r]), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, ldb,
-                      BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
-      return -3;
+  if (panel_mode) {
+    if (a_mn || b_mn || ldb != K || panel_counters == nullptr) return -9;
+    if (reinterpret_cast<unsigned long long>(B) != dst + static_cast<unsigned long long>(b_off_bytes)) return -9;
+    if (b_off_bytes + static_cast<long long>(N) * K * 2 > total_bytes) return -9;
+    // every chunk of B must be copied by this launch, or its panel would never complete
+    if (chunk_begin > b_off_bytes / FETCH_CHUNK || chunk_end <= (b_off_bytes + static_cast<long long>(N) * K * 2 - 1) / FETCH_CHUNK)
+      return -9;
+    cudaError_t em = cudaMemsetAsync(panel_counters, 0, sizeof(unsigned int) * ((N + BN - 1) / BN), stream);
+    if (em != cudaSuccess) return static_cast<int>(em);
   }
-  for (int r = world; r < AR_MAX_RANKS; ++r) maps.m[r] = maps.m[0];
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!a_mn) ok = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       ok = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return -3;
+  if (!b_mn) ok = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       ok = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return -3;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_f32 = out_f32; p.accumulate = accumulate;
   p.status = status_ptr();
   p.k_splits = 1;
-  p.peer_rows = rows_per_rank; p.peer_world = world;
-  const int sms = num_sms();
-  const int tiles = ((M + BM - 1) / BM) * (N / BN);
-  const int grid = tiles < sms ? tiles : sms;
-  cudaError_t e;
-  if (wide) {
-    auto kern = gemm_bf16_peer_b_kernel<256, 4>;
-    constexpr int smem = GemmSmem<256, 4>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
-      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured = true;
-    }
-    kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, maps, p);
-  } else {
-    auto kern = gemm_bf16_peer_b_kernel<128, 6>;
-    constexpr int smem = GemmSmem<128, 6>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
-      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured = true;
-    }
-    kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, maps, p);
+  for (int r = 0; r < world; ++r) {
+    if (src_ptrs[r] & 15) return -2;
+    p.fetch_src[r] = src_ptrs[r];
   }
+  p.fetch_dst = dst; p.fetch_total = total_bytes; p.fetch_slice = slice_bytes;
+  p.fetch_b_off = panel_mode ? b_off_bytes : 0;
+  p.fetch_c0 = chunk_begin; p.fetch_c1 = chunk_end;
+  p.fetch_panel = panel_mode ? panel_counters : nullptr;
+  p.fetch_limit_ns = static_cast<unsigned long long>((limit_s > 0.0 ? limit_s : 2.0) * 1e9);
+  const int sms = num_sms();
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  // the copy needs its warps even when the GEMM has few tiles: one CTA per SM, idle tensor pipes cost nothing
+  const int grid = (chunk_end > chunk_begin) ? sms : (tiles < sms ? tiles : sms);
+  cudaError_t e = cudaSuccess;
+#define VB_FETCH(BN_, AM, BMJ, ST)                                                                              \
+  do {                                                                                                          \
+    auto kern = gemm_bf16_fetch_kernel<BN_, AM, BMJ, ST>;                                                       \
+    constexpr int smem = GemmSmem<BN_, ST>::TOTAL;                                                              \
+    static bool configured = false;                                                                             \
+    if (!configured) {                                                                                          \
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                        \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                         \
+      configured = true;                                                                                        \
+    }                                                                                                           \
+    kern<<<grid, GEMM_FETCH_THREADS, smem, stream>>>(ta, tb, p);                                                \
+  } while (0)
+  if (wide) {
+    if (!a_mn && !b_mn) VB_FETCH(256, false, false, 4);
+    else if (!a_mn && b_mn) VB_FETCH(256, false, true, 4);
+    else if (a_mn && b_mn) VB_FETCH(256, true, true, 4);
+    else VB_FETCH(256, true, false, 4);
+  } else {
+    if (!a_mn && !b_mn) VB_FETCH(128, false, false, 6);
+    else if (!a_mn && b_mn) VB_FETCH(128, false, true, 6);
+    else if (a_mn && b_mn) VB_FETCH(128, true, true, 6);
+    else VB_FETCH(128, true, false, 6);
+  }
+#undef VB_FETCH
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -11,8 +11,11 @@ int vb_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M,
 int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                     long long ldb, long long ldd, int a_mn, int b_mn, int out_f32, int accumulate, int max_ctas, int k_splits,
                     float* splitk_ws, cudaStream_t stream);
-int vb_gemm_bf16_peer_b(const void* A, const unsigned long long* b_ptrs, void* D, const void* bias, int M, int K, long long lda,
-                        long long ldb, long long ldd, int world, int rows_per_rank, cudaStream_t stream);
+int vb_gemm_bf16_fetch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
+                       long long ldb, long long ldd, int a_mn, int b_mn, int out_f32, int accumulate,
+                       const unsigned long long* src_ptrs, int world, unsigned long long dst, long long total_bytes,
+                       long long slice_bytes, int chunk_begin, int chunk_end, long long b_off_bytes,
+                       unsigned int* panel_counters, double limit_s, cudaStream_t stream);
 int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                                   long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                   const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,

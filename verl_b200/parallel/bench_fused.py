@@ -159,27 +159,27 @@ def main(argv=None):
                    hbm_bytes=2.0 * (M * Kl + N * Kl + 2 * M * N), link_bytes=2.0 * M * N * (world - 1))
             del fl
     if want("ag_gemm"):
-        # fully sharded weight (row blocks on the ranks) consumed in place by the GEMM, against all-gather + GEMM
+        # fully sharded weight (equal slices on the ranks) gathered by the GEMM that consumes it, against all-gather + GEMM
         from .symmetric import PeerShardedLinear
 
         N, K, M = 37888, 3584, 8192   # gate_up projection of Qwen2.5-7B, 8192 tokens per rank
-        N = N // (world * 256) * (world * 256)
         lin = PeerShardedLinear(N, K, dev)
-        lin.shard.normal_(0, 0.05)
+        lin.range.slice.view(torch.bfloat16).normal_(0, 0.05)
         lin.barrier()
         x = (torch.randn(M, K, device=dev) * 0.05).bfloat16()
         y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-        w_full = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
+        per = lin.range.slice_bytes // 2
+        w_pad = torch.empty(world * per, device=dev, dtype=torch.bfloat16)
 
         def fused():
             lin(x, None, out=y)
 
         def nccl():
-            dist.all_gather_into_tensor(w_full, lin.shard)
-            F.gemm(x, w_full, out=y)
+            dist.all_gather_into_tensor(w_pad, lin.range.slice.view(torch.bfloat16))
+            F.gemm(x, w_pad[: N * K].view(N, K), out=y)
 
-        report("sharded_weight_gemm_no_gather", [M, N, K], timed(fused), timed(nccl), flops=2.0 * M * N * K,
-               hbm_bytes=2.0 * (M * K + N * K / world + M * N), link_bytes=2.0 * N * K * (world - 1) / world)
+        report("sharded_weight_gemm_fused_gather", [M, N, K], timed(fused), timed(nccl), flops=2.0 * M * N * K,
+               hbm_bytes=2.0 * (M * K + N * K + M * N), link_bytes=2.0 * N * K * (world - 1) / world)
     if want("moe_ep"):
         # expert-parallel MoE layer of Qwen3-30B-A3B: router + dispatch + grouped GEMMs + combine
         from .expert_parallel import ExpertParallelMoE

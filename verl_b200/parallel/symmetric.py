@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available"]
+__all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available", "ShardedRange", "PeerShardedLinear", "FusedRowParallelLinear"]
 
 
 def symmetric_available() -> bool:
@@ -107,32 +107,75 @@ class FusedRowParallelLinear:
                                            self.splitk_ws)
 
 
-class PeerShardedLinear:
-    """Linear layer whose weight [N, K] is stored in equal row blocks on the ranks of a group (1 / world of the bytes per
-    GPU) and never gathered: the GEMM kernel fetches every weight tile by TMA from the memory of the rank that owns it,
-    over NVLink, while the tensor cores work on the previous tile. Every rank computes the full ``x @ W^T`` for its own
-    tokens. This is the parameter all-gather of a fully sharded layout folded into the consuming GEMM.
+FETCH_CHUNK = 16384  # bytes per copy job of a GEMM's fetch warp (``FETCH_CHUNK`` in gemm_tcgen05.cu)
 
-    ``load_shard`` stores this rank's rows; call ``barrier()`` (or any collective) after a weight update so that no
-    rank reads rows that a peer is still writing."""
 
-    def __init__(self, n: int, k: int, device, group=None, dtype=torch.bfloat16):
+class ShardedRange:
+    """A run of bytes kept in equal slices on the ranks of a group (1 / world of it per GPU, in peer-mapped memory) that
+    GEMM kernels gather into a local arena while they compute (``ops.gemm_fetch``): the parameter all-gather of a fully
+    sharded layout, carried by the fetch warps of the kernels that run anyway.
+
+    ``slice_bytes`` is rounded up to whole 16 KB chunks so that a chunk never straddles two owners; rank r holds bytes
+    [r * slice_bytes, (r + 1) * slice_bytes) of the range (the tail of the last slice is padding)."""
+
+    def __init__(self, total_bytes: int, device, group=None):
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        assert n % self.world == 0 and (n // self.world) % 128 == 0 and k % 8 == 0, "row blocks must be multiples of 128 rows"
-        self.n, self.k, self.rows = int(n), int(k), int(n) // self.world
-        self.buf = SymmetricBuffer.allocate(self.rows * self.k, dtype, device, group, zero=True)
-        self.shard = self.buf.tensor.view(self.rows, self.k)
+        assert total_bytes % 16 == 0, "ranges are copied 16 bytes at a time"
+        self.total_bytes = int(total_bytes)
+        per = -(-self.total_bytes // self.world)
+        self.slice_bytes = -(-per // FETCH_CHUNK) * FETCH_CHUNK
+        self.num_chunks = -(-self.total_bytes // FETCH_CHUNK)
+        self.buf = SymmetricBuffer.allocate(self.slice_bytes, torch.uint8, device, group, zero=True)
+        self.slice = self.buf.tensor                      # this rank's bytes of the range
         self._barrier = PeerBarrier(device, group)
 
-    def load_shard(self, rows: torch.Tensor) -> None:
-        self.shard.copy_(rows)
+    @property
+    def owned(self) -> tuple[int, int]:
+        """[lo, hi) byte range of the whole that this rank stores."""
+        lo = min(self.rank * self.slice_bytes, self.total_bytes)
+        return lo, min(lo + self.slice_bytes, self.total_bytes)
+
+    def store_from_full(self, full_bytes: torch.Tensor) -> None:
+        """Keep this rank's slice of a full copy (uint8 view of ``total_bytes`` bytes)."""
+        lo, hi = self.owned
+        self.slice[: hi - lo].copy_(full_bytes[lo:hi])
 
     def barrier(self) -> None:
+        """After an update of the slices: nobody gathers bytes that their owner is still writing."""
         self._barrier()
+
+
+class PeerShardedLinear:
+    """Linear layer whose weight [N, K] is stored in equal slices on the ranks of a group (1 / world of the bytes per GPU)
+    and gathered by the very GEMM that consumes it: an extra warp in every CTA copies the weight, 16 KB at a time and in
+    the order the tiles need it, from its owners' memory over NVLink into a local arena; a tile starts as soon as the
+    rows it reads have landed, and every remote byte crosses the link once. Every rank computes the full ``x @ W^T``
+    for its own tokens. This is the parameter all-gather of a fully sharded layout fused into the consuming GEMM.
+
+    Call ``barrier()`` (or any collective) after a weight update so that no rank reads bytes that a peer is still
+    writing. The arena holds the gathered weight until the next call; ``gathered`` exposes it (valid after a call)."""
+
+    def __init__(self, n: int, k: int, device, group=None, dtype=torch.bfloat16, limit_s: float = 5.0):
+        assert dtype == torch.bfloat16 and k % 8 == 0
+        self.n, self.k, self.limit_s = int(n), int(k), float(limit_s)
+        self.range = ShardedRange(self.n * self.k * 2, device, group)
+        self.rank, self.world = self.range.rank, self.range.world
+        self.arena = torch.empty(self.range.total_bytes, dtype=torch.uint8, device=device)
+        self.gathered = self.arena.view(torch.bfloat16).view(self.n, self.k)
+        self.panels = torch.zeros((self.n + 127) // 128, dtype=torch.int32, device=device)
+
+    def load_full(self, weight: torch.Tensor) -> None:
+        """Shard a full [N, K] weight (every rank passes the same values; each keeps its slice)."""
+        self.range.store_from_full(weight.contiguous().view(-1).view(torch.uint8))
+
+    def barrier(self) -> None:
+        self.range.barrier()
 
     def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         from ..ops import native
 
         assert x.shape[-1] == self.k
-        return native.ops().gemm_peer_b(x, self.buf.ptrs, self.rows, bias, out)
+        r = self.range
+        return native.ops().gemm_fetch(x, self.gathered, bias, out, False, False, False, False, r.buf.ptrs, self.arena,
+                                       r.total_bytes, r.slice_bytes, 0, r.num_chunks, 0, self.panels, self.limit_s)

@@ -130,11 +130,22 @@ class EngineRegistry:
 
         return deco
 
+    # backend names of the reference that have no engine of their own here: what they are served by, said once per name
+    ALIASES = {"veomni": "native", "torchtitan": "native", "automodel": "native", "fsdp_turbo": "native", "mindspeed": "mp"}
+    _warned: set = set()
+
     @classmethod
     def get_engine_cls(cls, model_type: str, backend: str, device: Optional[str] = None):
         from ...utils.device import get_device_name
 
         device = device or get_device_name()
+        if backend in cls.ALIASES and backend not in cls._warned:
+            import warnings
+
+            cls._warned.add(backend)
+            warnings.warn(f"engine backend '{backend}' has no implementation of its own in this framework: it runs on the "
+                          f"'{cls.ALIASES[backend]}' engine ({'sharded data-parallel' if cls.ALIASES[backend] == 'native' else 'tensor x pipeline x expert parallel'}); "
+                          f"options specific to {backend} are ignored", stacklevel=2)
         if backend in ("megatron", "mp", "mindspeed") and backend not in cls._engines.get(model_type, {}):
             from . import mp  # noqa: F401  (registers the tensor x pipeline parallel engines)
         try:

@@ -758,6 +758,7 @@ class NativeEngine(BaseEngine):
         ops = native.ops()
         use_mc = os.environ.get("VERL_B200_MULTIMEM", "0") == "1"
         lr = self.lr_override if getattr(self, "lr_override", None) is not None else lr_at_step(oc, self.sched_step)
+        self.opt_step_count += 1
         # The barrier's wait is bounded. If it runs out on this rank (a straggler further behind than the limit), the
         # kernel poisons the squared-norm accumulator with +inf; the sum over ranks below spreads that to every rank,
         # the straggler included once it arrives, so the AdamW kernel takes its non-finite branch everywhere: optimizer
