@@ -62,6 +62,10 @@ class FSDPModelMerger(BaseModelMerger):
         numel = int(shards[0]["numel"])
         flat = torch.zeros(numel, dtype=torch.float32)
         for s in shards:
+            if s.get("layout") == "unit_sharded":  # zero_stage=3: a slice of every unit; (flat_lo, flat_hi, offset in the shard)
+                for a, b, so in s["ranges"]:
+                    flat[a:b] = s["flat_shard"][so : so + (b - a)].float()
+                continue
             lo = int(s["shard_lo"])
             n = min(s["flat_shard"].numel(), numel - lo)
             flat[lo : lo + n] = s["flat_shard"][:n].float()

@@ -94,7 +94,15 @@ class TaskRunner:
             initialize_global_process_group()
         trainer_cls, v1, extra = RayPPOTrainer, False, {}
         in_process = wg_cls.__name__ in ("InProcessWorkerGroup", "SPMDWorkerGroup")
-        if config.trainer.get("use_v1", False) and in_process:
+        use_v1 = bool(config.trainer.get("use_v1", True)) and in_process
+        if use_v1:
+            why = _v1_unsupported_reason(config)
+            if why:
+                import warnings
+
+                warnings.warn(f"trainer.use_v1=true, but {why}: running the synchronous v0 trainer instead", stacklevel=2)
+                use_v1 = False
+        if use_v1:
             from .ppo.v1.trainer_base import get_trainer_cls
 
             v1cfg = config.trainer.get("v1") or {}
@@ -115,6 +123,22 @@ class TaskRunner:
             trainer.init_workers()
         trainer.fit()
         return trainer
+
+
+def _v1_unsupported_reason(config) -> Optional[str]:
+    """The v1 (replay-buffer) trainers drive the native continuous-batching rollout engine step by step; a model family that
+    samples through the library module's own cache has no such engine. Returns why v1 cannot run, or None."""
+    try:
+        from ..utils.config import omega_conf_to_dataclass
+        from ..workers.config import HFModelConfig
+
+        m = config.actor_rollout_ref.model
+        mc = m if isinstance(m, HFModelConfig) else omega_conf_to_dataclass(m, HFModelConfig)
+        if getattr(mc.arch, "is_generic", False):
+            return f"model family '{mc.arch.model_type}' samples through the library module (no step-wise rollout engine)"
+    except Exception:
+        return None
+    return None
 
 
 def _split_job_impl(config, rollout_ranks: int, tokenizer):

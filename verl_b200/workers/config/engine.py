@@ -43,12 +43,14 @@ class EngineConfig(BaseConfig):
 
 @dataclass
 class FSDPEngineConfig(EngineConfig):
-    """Sharded data-parallel engine (``zero_stage=2``): gradients and optimizer state are sharded over the data-parallel
-    group while every GPU keeps a full bf16 working copy of the weights, which removes all parameter gathers from the
-    forward / backward path and lets the colocated rollout engine read the weights in place. That fits 180 GB for dense
-    models up to roughly 20 B parameters (2 bytes of weights + 4 bytes of transient fp32 gradients per parameter); larger
-    models shard the weights themselves with the tensor x pipeline x expert parallel engine (``strategy=megatron``).
-    ``zero_stage=3`` (working weights sharded too, gathered per layer) is not implemented and is rejected."""
+    """Sharded data-parallel engine. ``zero_stage=2`` (default): gradients and optimizer state are sharded over the
+    data-parallel group while every GPU keeps a full bf16 working copy of the weights, which removes all parameter gathers
+    from the forward / backward path and lets the colocated rollout engine read the weights in place. That fits 180 GB for
+    dense models up to roughly 20 B parameters (2 bytes of weights + 4 bytes of transient fp32 gradients per parameter).
+    ``zero_stage=3`` (the reference's FULL_SHARD): the working weights are sharded as well, per unit (embedding, each layer,
+    head); a unit is gathered into one of two arenas while the previous unit computes, its gradients are reduce-scattered as
+    the backward pass leaves it, and the rollout engine gets a gathered replica at every weight hand-over. Larger models can
+    also shard with the tensor x pipeline x expert parallel engine (``strategy=megatron``)."""
 
     wrap_policy: dict = field(default_factory=dict)
     offload_policy: bool = False
@@ -74,10 +76,9 @@ class FSDPEngineConfig(EngineConfig):
 
     def __post_init__(self):
         assert self.strategy in ("fsdp", "fsdp2", "fsdp_turbo"), f"strategy {self.strategy} not supported"
-        if int(self.zero_stage) != 2:
+        if int(self.zero_stage) not in (2, 3):
             raise NotImplementedError("zero_stage must be 2 (replicated bf16 working weights, sharded gradients and optimizer "
-                                      "state); shard the weights of larger models with strategy=megatron (tensor / pipeline / "
-                                      "expert parallelism)")
+                                      "state) or 3 (working weights sharded per layer as well)")
 
 
 @dataclass

@@ -309,12 +309,20 @@ class NativeEngine(BaseEngine):
             from ....utils.activation_offload import ActivationOffloader
 
             self.model.offloader = ActivationOffloader(self.device)
+        # zero_stage=3: the bf16 working weights are sharded too (per unit: embedding, each layer, head) and gathered unit by
+        # unit around their use; gradients are reduce-scattered per unit as the backward pass leaves it
+        self.zero3 = int(getattr(ec, "zero_stage", 2) or 2) == 3 and self._shared_params is None
+        if self.zero3:
+            self._shard_working_weights()
         # The replicated region [0, dense_numel) is optimised in equal shards over the data-parallel group; a rank-local tail
         # region (the experts of an expert-parallel shard) is optimised whole by its owner.
         self.dense_numel = int(getattr(self.tparams, "dense_numel", self.tparams.numel))
         self.local_numel = self.tparams.numel - self.dense_numel
         self.shard_numel = self.dense_numel // self.sh_world
         self.shard_lo = self.sh_rank * self.shard_numel
+        if self.zero3:  # this rank's slices of every unit, contiguous in its own store
+            self.dense_numel = self.shard_numel = self.tparams.owned_numel
+            self.local_numel = self.shard_lo = 0
         assert self.local_numel == 0 or (self.world > 1 and not self.fused_comm and self.lora is None and self.rep_world == 1)
         # The fp32 gradient buffer only lives from optimizer_zero_grad() to the end of optimizer_step(), so its
         # memory (4 bytes/param) is available to the rollout KV cache in between.
@@ -349,6 +357,37 @@ class NativeEngine(BaseEngine):
             assert self.lora is None, "QAT and LoRA are exclusive"
             self._apply_qat()
         self._initialized = True
+
+    def _shard_working_weights(self) -> None:
+        """Replace the full working buffer by this rank's slices (``UnitShardedParams``) and hook the decoder's unit
+        boundaries to its prefetch / gradient-reduction logic. The full buffer exists once, during initialisation."""
+        from ....models.sharded_weights import UnitShardedParams
+
+        assert not self.arch.is_generic and self.lora is None and self.rep_world == 1 and not self.fused_comm, \
+            "zero_stage=3 supports the hand-scheduled model families without LoRA, hybrid sharding or the peer-memory optimizer"
+        assert self.sp_size == 1 and not getattr(self.arch, "num_local_experts", 0), \
+            "zero_stage=3 does not combine with sequence / context / expert parallelism"
+        assert str(getattr(self.optimizer_config, "optimizer", "AdamW") or "AdamW").lower() != "muon", "zero_stage=3 runs AdamW"
+        full = self.params
+        sharded = UnitShardedParams(full, group=self.sh_group, device=self.device, dtype=self.dtype)
+        sharded.load_from_full(full.flat)
+        self.params = self.tparams = sharded
+        self.model.params = sharded
+        self.model.pre_layer_hook = sharded.pre_layer_hook
+        self.model.post_layer_backward_hook = sharded.post_layer_backward_hook
+        del full
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def gather_full_params(self, out: Optional[FlatParams] = None, dtype=None) -> FlatParams:
+        """The whole model in the full flat layout on this rank (collective when the weights are sharded): what the
+        colocated rollout engine, the reference policy's initial copy and merged exports read."""
+        if self.zero3:
+            return self.params.materialize_full(out)
+        if out is not None:
+            out.flat.copy_(self.params.flat)
+            return out
+        return self.params
 
     def _load_or_init(self, seed: int) -> None:
         mc = self.model_config
@@ -599,6 +638,10 @@ class NativeEngine(BaseEngine):
             flat[self.dense_numel :].copy_(owned[self.shard_numel :].to(flat.dtype))
 
     def _alloc_grads(self) -> None:
+        if self.zero3:
+            self.tparams.attach_main_grad()
+            self.grad_shard = self.tparams.grad_shard
+            return
         self.tparams.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
         self.grad_shard = self.tparams.main_grad[sl] if self.sh_world == 1 else torch.zeros_like(self.master)
@@ -616,6 +659,12 @@ class NativeEngine(BaseEngine):
     def optimizer_zero_grad(self) -> None:
         if self.forward_only:
             return
+        if self.zero3:
+            if self.tparams.grad_shard is None:
+                self._alloc_grads()
+            else:
+                self.tparams.zero_grad()
+            return
         if self.tparams.main_grad is None:
             self._alloc_grads()
         else:
@@ -632,7 +681,11 @@ class NativeEngine(BaseEngine):
         if self.fused_comm:
             return self._fused_optimizer_step()
         D, n_sh = self.dense_numel, self.shard_numel
-        if W > 1:
+        if self.zero3:
+            # every unit's gradient was reduce-scattered (sum) when the backward pass left it; the mean is one scale away
+            if W > 1:
+                self.grad_shard.mul_(1.0 / W)
+        elif W > 1:
             if self.device.type == "cuda":
                 if self.sh_world > 1:
                     dist.reduce_scatter_tensor(self.grad_shard[:n_sh], mg[:D], op=dist.ReduceOp.AVG, group=self.sh_group)
@@ -798,6 +851,9 @@ class NativeEngine(BaseEngine):
 
     def _publish_shard(self) -> None:
         """All-gather this rank's updated slice of the working weights into every replica."""
+        if self.zero3:
+            self.tparams.invalidate()  # gathered copies of the old weights are stale; the store itself was updated in place
+            return
         if self.sh_world == 1:
             return
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
@@ -840,10 +896,14 @@ class NativeEngine(BaseEngine):
             return
         contents = list(getattr(self.checkpoint_config, "save_contents", ["model", "optimizer", "extra"]) or [])
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
+        # an HF export needs the whole model: gathering it is a collective, so every rank takes part before rank 0 writes
+        self._full_for_export = self.gather_full_params() if "hf_model" in contents else None
         if "model" in contents:
             src = self.master if not self.forward_only else self._owned(self.tparams.flat).float()
             torch.save({"flat_shard": src.cpu(), "shard_lo": self.shard_lo, "numel": self.tparams.numel,
                         "shard_numel": self.shard_numel, "dense_numel": self.dense_numel, "local_numel": self.local_numel,
+                        **({"layout": "unit_sharded", "ranges": self.tparams.owned_index_ranges(), "numel": self.tparams.numel}
+                           if self.zero3 else {}),
                         "offsets": self.tparams.offsets}, os.path.join(local_path, f"model_world_size_{W}_rank_{r}.pt"))
         if "optimizer" in contents and not self.forward_only:
             torch.save({"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "step": self.opt_step_count},
@@ -854,7 +914,8 @@ class NativeEngine(BaseEngine):
                        os.path.join(local_path, f"extra_state_world_size_{W}_rank_{r}.pt"))
         if self.rank == 0:
             with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
-                json.dump({"FSDP_version": 2, "world_size": W, "layout": "verl_b200.flat", "value_head": self.value_head}, f)
+                json.dump({"FSDP_version": 2, "world_size": W, "layout": "verl_b200.flat", "value_head": self.value_head,
+                           "zero_stage": 3 if self.zero3 else 2}, f)
             hf_dir = os.path.join(local_path, "huggingface")
             self.arch.save_pretrained(hf_dir)
             if self.lora is not None:
@@ -862,7 +923,8 @@ class NativeEngine(BaseEngine):
             if "hf_model" in contents:
                 from ....utils.model import save_hf_weights
 
-                save_hf_weights(self.params, hf_dir)
+                save_hf_weights(self._full_for_export, hf_dir)
+        self._full_for_export = None
         if self.world > 1:
             dist.barrier(group=self.group)
         self._rotate_checkpoints(local_path, max_ckpt_to_keep)
@@ -941,11 +1003,15 @@ class NativeEngine(BaseEngine):
             mp = shard_file("model")
             if mp is not None:
                 st = torch.load(mp, map_location="cpu", weights_only=False)
+                if (st.get("layout") == "unit_sharded") != self.zero3:
+                    raise RuntimeError(f"checkpoint was written with zero_stage={3 if st.get('layout') == 'unit_sharded' else 2}, this engine "
+                                       f"runs zero_stage={3 if self.zero3 else 2}: merge it to HF weights (model_merger) and load those")
                 assert st["numel"] == self.tparams.numel and st["shard_lo"] == self.shard_lo, "checkpoint/model layout mismatch"
                 owned = st["flat_shard"]
             else:
-                if self.local_numel:
-                    raise RuntimeError(f"rank-local parameters: the checkpoint (shard world size {saved_W}) must be loaded with {saved_W} shards")
+                if self.local_numel or self.zero3:
+                    raise RuntimeError(f"rank-local or unit-sharded parameters: the checkpoint (shard world size {saved_W}) must be loaded "
+                                       f"with {saved_W} shards")
                 owned = self._read_owned_range(local_path, "model", ("flat_shard",), saved_W)["flat_shard"]
             if not self.forward_only:
                 self.master.copy_(owned)

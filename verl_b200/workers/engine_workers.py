@@ -285,7 +285,10 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 self.ref = EngineRegistry.new("language_model", "fsdp", model_config=mc, engine_config=rec, optimizer_config=None)
             self.ref.initialize()
             if self.actor is not None:  # the reference policy starts as an exact copy of the actor
-                self.ref.params.flat.copy_(self.actor.params.flat)
+                if getattr(self.actor, "zero3", False):
+                    self.actor.gather_full_params(out=self.ref.params)
+                else:
+                    self.ref.params.flat.copy_(self.actor.params.flat)
         if self._is_rollout:
             from .rollout.native.engine import RolloutEngine
 
@@ -294,7 +297,7 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
             src = self.actor if self.actor is not None else self.ref
             topo = getattr(src, "topo", None) if src is not None else None
             self._mp_actor = topo is not None and topo.tp * topo.pp > 1
-            self._regather = topo is not None and (self._mp_actor or topo.ep > 1)
+            self._regather = (topo is not None and (self._mp_actor or topo.ep > 1)) or bool(getattr(src, "zero3", False))
             if self._regather:
                 # the trainer holds a shard of the model (1/(tp*pp) of it, or 1/ep of the experts): the rollout engine gets a
                 # full replica that update_weights() re-assembles from the shards after every optimizer step; with tensor /
@@ -537,9 +540,12 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         buffer in place, so this only invalidates cached KV; returns the device time spent."""
         t0 = time.time()
         if getattr(self, "_regather", False) and self.rollout is not None:
-            fresh = self._mp_engine.gather_full_params()
-            self.rollout_params.flat.copy_(fresh.flat)
-            del fresh
+            if getattr(self._mp_engine, "zero3", False):
+                self._mp_engine.gather_full_params(out=self.rollout_params)  # unit by unit, straight into the replica
+            else:
+                fresh = self._mp_engine.gather_full_params()
+                self.rollout_params.flat.copy_(fresh.flat)
+                del fresh
         if self.rollout is not None:
             self.rollout.clear_kv_cache()
         if get_device_name() == "cuda":
