@@ -339,6 +339,49 @@ def _sec_multimem(rank, world, dev, ops, res):
     bar()
 
 
+def _sec_zero3_engine(rank, world, dev, ops, res):
+    """zero_stage=3 on GPUs: units gathered by the GEMM kernels' fetch warps, and by a collective on a side stream,
+    against zero_stage=2 (NCCL optimizer path) on the same data."""
+    from functools import partial
+
+    import torch.distributed as dist
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
+    # wide enough that the projections qualify as carriers of the gather (>= 128 output tiles of 128 x 256)
+    arch = ModelConfig(model_type="qwen2", vocab_size=4096, hidden_size=1024, intermediate_size=4096, num_hidden_layers=3,
+                       num_attention_heads=8, num_key_value_heads=2, head_dim=128, eos_token_id=2, pad_token_id=0)
+    g = torch.Generator().manual_seed(200 + rank)
+    ids = torch.randint(3, 4096, (8, 1024), generator=g)
+    am = torch.ones_like(ids)
+    data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 256:].to(dev), "response_mask": am[:, 256:].to(dev)}
+    finals = {}
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    for name, stage, fused in (("z2", 2, "1"), ("z3_fused", 3, "1"), ("z3_nccl", 3, "0")):
+        os.environ["VERL_B200_ZERO3_FUSED"] = fused
+        eng = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=4, zero_stage=stage),
+                                     OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        norms = [float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"]) for _ in range(2)]
+        torch.cuda.synchronize()
+        finals[name] = (eng.gather_full_params().flat.float().clone(), norms)
+        if stage == 3:
+            res[f"{name}_fused"] = bool(eng.zero3_fused_gather)
+            res[f"{name}_counts"] = (eng.params.gather_count, eng.params.reduce_count, eng.params.flush_count)
+        del eng
+        torch.cuda.empty_cache()
+    os.environ["VERL_B200_FUSED_COMM"] = "1"
+    os.environ["VERL_B200_ZERO3_FUSED"] = "1"
+    for name in ("z3_fused", "z3_nccl"):
+        res[f"{name}_param_diff"] = (finals[name][0] - finals["z2"][0]).abs().max().item()
+        res[f"{name}_norm_diff"] = max(abs(a - b) for a, b in zip(finals[name][1], finals["z2"][1]))
+    res["norm"] = finals["z2"][1]
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
 SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
 
 
@@ -474,3 +517,12 @@ def test_expert_parallel_training_matches_replicated_experts(pair):
 def test_peer_barrier_that_nobody_joins_reports_status(pair):
     got = pair.run("barrier_timeout")
     assert got[0]["timeout_status"] == 4 and got[0]["alive_after_timeout"] == 4.0
+
+
+def test_zero3_engine_matches_zero2_on_gpus(pair):
+    for res in pair.run("zero3_engine", timeout=600).values():
+        assert res["z3_fused_fused"] and not res["z3_nccl_fused"], res
+        for name in ("z3_fused", "z3_nccl"):
+            assert res[f"{name}_param_diff"] < 2e-2 and res[f"{name}_norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res
+            assert res[f"{name}_counts"][0] > 0 and res[f"{name}_counts"][1] > 0, res
+        assert res["status"] == (0, 0), res

@@ -54,12 +54,18 @@ class UnitShardedParams:
             self.store_off[u] = off
             off += self.slice_elems[u]
         self.owned_numel = off
-        self.sym = None
+        self.sym = self._peer_barrier = None
+        self._fetch: Optional[dict] = None          # a gather in progress on the fetch warps of the running GEMMs
+        self._flops_seen = 0.0                      # GEMM work since the current unit was entered
+        self._flops_last = 0.0                      # ... of the unit before it (the budget of the next gather)
         if symmetric:
-            from ..parallel.symmetric import SymmetricBuffer
+            # peer-mapped store: units are gathered by the GEMM kernels themselves (``ops.gemm_fetch``), no collective
+            from ..parallel.symmetric import PeerBarrier, SymmetricBuffer
 
             self.sym = SymmetricBuffer.allocate(off, self.dtype, self.device, group)
             self.store = self.sym.tensor
+            self._peer_barrier = PeerBarrier(self.device, group)
+            self._esz = esz
         else:
             self.store = torch.zeros(off, dtype=self.dtype, device=self.device)
         self.flat = self.store                                                  # what this rank holds (dtype / size queries)
@@ -75,7 +81,7 @@ class UnitShardedParams:
         self.grad_shard: Optional[torch.Tensor] = None                          # fp32 [owned_numel]: sum over ranks, this rank's slices
         self._grads_on = False
         self._names_of = {u: [s for s in self.specs if s.layer == u] for u in self.units}
-        self.gather_count = self.reduce_count = 0
+        self.gather_count = self.reduce_count = self.flush_count = 0
         self._phase = "forward"
         self._touched = [False, False]
 
@@ -123,10 +129,63 @@ class UnitShardedParams:
         return dst
 
     def invalidate(self) -> None:
-        """After the store changed (optimizer step, checkpoint load): gathered copies are stale."""
+        """After the store changed (optimizer step, checkpoint load): gathered copies are stale. With a peer-mapped store
+        this is also the point where every rank waits for the others' stores to be final before anyone reads them."""
         self._wait_all()
+        self._fetch = None
         self.resident = [None, None]
         self._views = [{}, {}]
+        if self._peer_barrier is not None:
+            self._peer_barrier()
+
+    # ------------------------------------------------------------------ gathers carried by the GEMM kernels
+    def _start_fetch(self, u: int, slot: int) -> None:
+        se = self.slice_elems[u]
+        slice_bytes = se * self._esz
+        cps = slice_bytes // CHUNK_BYTES                 # chunks per slice
+        # this rank's own slice is one device-to-device copy away; the fetch warps bring the other ranks' slices
+        self.arenas[slot][self.rank * se : (self.rank + 1) * se].copy_(self.store[self.store_off[u] : self.store_off[u] + se])
+        todo = [iv for iv in ((0, self.rank * cps), ((self.rank + 1) * cps, self.world * cps)) if iv[1] > iv[0]]
+        self._fetch = dict(unit=u, slot=slot, todo=todo, chunks=(self.world - 1) * cps, slice_bytes=slice_bytes,
+                           total=self.world * slice_bytes, src=self.sym.ptrs + self.store_off[u] * self._esz,
+                           budget=0.8 * max(self._flops_last, 1.0))
+        from ..ops import functional as F
+
+        F.set_fetch_rider(self)
+
+    def take(self, flops: float):
+        """Asked by every large GEMM (``ops.functional.gemm``): the share of the pending gather that this GEMM carries,
+        in proportion to its work against the work of the previous unit, so the gather ends before the unit does."""
+        self._flops_seen += flops
+        f = self._fetch
+        if f is None or not f["todo"]:
+            return None
+        n = max(1, int(f["chunks"] * flops / f["budget"]) + 1)
+        c0, hi = f["todo"][0]
+        c1 = min(hi, c0 + n)
+        if c1 >= hi:
+            f["todo"].pop(0)
+        else:
+            f["todo"][0] = (c1, hi)
+        return f["src"], self.arenas[f["slot"]], f["total"], f["slice_bytes"], c0, c1
+
+    def _finish_fetch(self) -> None:
+        """The unit is needed now: whatever the GEMMs so far did not carry rides on small GEMMs of its own."""
+        f = self._fetch
+        if f is not None and f["todo"]:
+            from ..ops import native
+
+            if not hasattr(self, "_dummy"):
+                self._dummy = (torch.zeros(128, 64, dtype=torch.bfloat16, device=self.device),
+                               torch.zeros(128, 64, dtype=torch.bfloat16, device=self.device),
+                               torch.zeros(128, 128, dtype=torch.bfloat16, device=self.device))
+            a, b, d = self._dummy
+            for c0, c1 in f["todo"]:
+                native.ops().gemm_fetch(a, b, None, d, False, False, False, False, f["src"], self.arenas[f["slot"]], f["total"],
+                                        f["slice_bytes"], c0, c1, -1, None, 2.0)
+                self.flush_count += 1
+            f["todo"] = []
+        self._fetch = None
 
     def _wait_all(self) -> None:
         for slot, ev in list(self._pending.items()):
@@ -163,14 +222,23 @@ class UnitShardedParams:
     def acquire(self, u: int) -> int:
         """Make unit ``u`` resident (gathering it now unless a prefetch already did) and return its arena slot."""
         slot = self._slot_of(u)
+        if self._fetch is not None and (slot is None or self._fetch["unit"] == u):
+            self._finish_fetch()  # the arena it fills is about to be used, or to be given to another unit
         if slot is None:
             slot = 1 - self._last_slot
             self._retarget(slot)
-            self._gather_into(u, self.arenas[slot])
+            if self.sym is not None:
+                self._start_fetch(u, slot)
+                self._finish_fetch()
+                self.gather_count += 1
+            else:
+                self._gather_into(u, self.arenas[slot])
             self.resident[slot] = u
             self._build_views(slot, u)
         elif slot in self._pending:
             torch.cuda.current_stream(self.device).wait_event(self._pending.pop(slot))
+        if slot != self._last_slot:
+            self._flops_last, self._flops_seen = self._flops_seen, 0.0
         self._last_slot = slot
         if self._grads_on and self._phase == "backward":
             self._touched[slot] = True  # views with gradient targets are about to be handed out
@@ -184,7 +252,12 @@ class UnitShardedParams:
         slot = 1 - self._last_slot
         if slot in self._pending or (self._grads_on and self._touched[slot]):
             return  # busy, or its gradients still wait for their reduction: the gather happens at acquire time
-        if self._side is None:
+        if self.sym is not None:
+            if self._fetch is not None:
+                return
+            self._start_fetch(u, slot)      # same stream as the GEMMs that carry it: no events needed
+            self.gather_count += 1
+        elif self._side is None:
             self._gather_into(u, self.arenas[slot])
         else:
             # kernels already queued on the compute stream may still read the arena that is about to be overwritten

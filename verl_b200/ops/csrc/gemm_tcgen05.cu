@@ -78,7 +78,7 @@ struct GemmParams {
   int grp_E;
   // staged all-gather (FETCH variants). A byte range of `fetch_total` bytes is stored in equal slices of `fetch_slice`
   // bytes on the ranks of a group (rank r holds bytes [r * slice, (r + 1) * slice) at fetch_src[r], peer-mapped). The
-  // extra warp of every CTA copies 16 KB chunks [fetch_c0, fetch_c1) of it into local memory at fetch_dst while the
+  // copy warps of every CTA move 16 KB chunks [fetch_c0, fetch_c1) of it into local memory at fetch_dst while the
   // tensor pipe works. When B itself lies inside that range (at byte offset fetch_b_off, N * K * 2 bytes, rows
   // contiguous), fetch_panel counts the chunks that have landed per BN-row panel of B and the TMA producer holds a
   // tile back until its panel is complete; tiles then sweep all rows of the output per panel, so panels are needed
@@ -91,7 +91,8 @@ struct GemmParams {
   unsigned long long fetch_limit_ns;
 };
 
-constexpr int FETCH_CHUNK = 16384;  // bytes per copy job of the fetch warp
+constexpr int FETCH_CHUNK = 16384;  // bytes per copy job of a fetch warp
+constexpr int FETCH_WARPS = 4;      // copy warps per CTA (warps 6..9): peer loads are latency-bound, bytes in flight = rate
 constexpr int ST_TIMEOUT_FETCH = 14;
 
 __device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
@@ -123,7 +124,7 @@ struct GemmSmem {
   static constexpr int TOTAL = RING + 256 + 1024;  // barriers + alignment slack
 };
 
-// Kernel body. FETCH adds a seventh warp that stages peer memory into local memory (see GemmParams::fetch_*).
+// Kernel body. FETCH adds copy warps that stage peer memory into local memory (see GemmParams::fetch_*).
 template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI, bool FETCH>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmParams& p) {
   extern __shared__ uint8_t smem_raw[];
@@ -331,14 +332,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         }
       }
     }
-  } else if (FETCH && warp == 6) {
-    // ------------------------------------------------------------------ fetch warp: peer memory -> local memory
-    // Chunks are dealt round-robin over the CTAs in address order, so every CTA works on the panels that are needed
-    // first. 16 independent 16-byte loads per lane are in flight before the first store (8 KB per warp).
+  } else if (FETCH && warp >= 6) {
+    // ------------------------------------------------------------------ fetch warps: peer memory -> local memory
+    // Chunks are dealt round-robin over all fetch warps of the grid in address order, so every CTA works on the panels
+    // that are needed first. 16 independent 16-byte loads per lane are in flight before the first store (8 KB per warp).
     if constexpr (FETCH) {
       const long long panel_bytes = static_cast<long long>(BN) * p.K * 2;
       const long long b_end = p.fetch_b_off + static_cast<long long>(p.N) * p.K * 2;
-      for (int c = p.fetch_c0 + static_cast<int>(blockIdx.x); c < p.fetch_c1; c += static_cast<int>(gridDim.x)) {
+      const int fw = static_cast<int>(blockIdx.x) * FETCH_WARPS + (warp - 6);
+      const int fw_stride = static_cast<int>(gridDim.x) * FETCH_WARPS;
+      for (int c = p.fetch_c0 + fw; c < p.fetch_c1; c += fw_stride) {
         const long long off = static_cast<long long>(c) * FETCH_CHUNK;
         const long long len = min(static_cast<long long>(FETCH_CHUNK), p.fetch_total - off);
         const int owner = static_cast<int>(off / p.fetch_slice);
@@ -652,9 +655,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   gemm_body<BN, A_MN, B_MN, STAGES, EPI, false>(tma_a, tma_b, p);
 }
 
-constexpr int GEMM_FETCH_THREADS = GEMM_THREADS + 32;
+constexpr int GEMM_FETCH_THREADS = GEMM_THREADS + 32 * FETCH_WARPS;
 
-// The same GEMM with a fetch warp: the all-gather of a sharded byte range (the GEMM's own B operand, or whatever a later
+// The same GEMM with fetch warps: the all-gather of a sharded byte range (the GEMM's own B operand, or whatever a later
 // kernel needs) runs inside the GEMM, over peer loads, behind the tensor pipe.
 template <int BN, bool A_MN, bool B_MN, int STAGES>
 __global__ void __launch_bounds__(GEMM_FETCH_THREADS, 1)
@@ -951,7 +954,7 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
 }
 
 // GEMM with a staged all-gather running inside it (see GemmParams::fetch_*): D = op(A) * op(B) as vb_gemm_bf16, while
-// the extra warp of every CTA copies chunks [chunk_begin, chunk_end) (16 KB each) of a byte range that is stored in
+// the copy warps of every CTA move chunks [chunk_begin, chunk_end) (16 KB each) of a byte range that is stored in
 // equal slices on the ranks of a group (src_ptrs[r]: rank r's slice, peer-mapped; slice_bytes a multiple of 16 KB) to
 // local memory at dst. With b_off_bytes >= 0 the B operand is the K-major matrix at dst + b_off_bytes (rows contiguous,
 // ldb == K) and is being gathered by this very launch: `panel_counters` (ceil(N / tile width) words, cleared here) then

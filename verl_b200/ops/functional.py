@@ -47,11 +47,30 @@ def _ops():
 
 
 # ----------------------------------------------------------------------------------------------- GEMM
+_FETCH_RIDER = None
+
+
+def set_fetch_rider(rider) -> None:
+    """``rider.take(flops)`` is asked by every large GEMM whether it should carry a piece of a pending gather of sharded
+    bytes (``ops.gemm_fetch``: an extra warp per CTA copies them from their owners' memory while the tensor pipe works);
+    it answers ``(src_ptrs, dst, total_bytes, slice_bytes, chunk_begin, chunk_end)`` or None. ``None`` removes the rider."""
+    global _FETCH_RIDER
+    _FETCH_RIDER = rider
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
          a_mn: bool = False, b_mn: bool = False, out_f32: bool = False, accumulate: bool = False,
          max_ctas: int = 0) -> torch.Tensor:
     """``D = A @ B^T (+bias)``; ``a_mn``/``b_mn`` mean the operand is stored transposed ([K, M] / [K, N])."""
     if a.is_cuda:
+        if _FETCH_RIDER is not None and max_ctas == 0:
+            M = a.shape[1] if a_mn else a.shape[0]
+            K = a.shape[0] if a_mn else a.shape[1]
+            N = b.shape[1] if b_mn else b.shape[0]
+            if (M // 128) * (N // 256) >= 128:  # fills the machine without a K split: its CTAs can carry copy work
+                job = _FETCH_RIDER.take(2.0 * M * N * K)
+                if job is not None:
+                    return _ops().gemm_fetch(a, b, bias, out, a_mn, b_mn, out_f32, accumulate, *job, -1, None, 2.0)
         return _ops().gemm(a, b, bias, out, a_mn, b_mn, out_f32, accumulate, max_ctas)
     A = a.t() if a_mn else a
     Bt = b if b_mn else b.t()

@@ -180,6 +180,37 @@ def main(argv=None):
 
         report("sharded_weight_gemm_fused_gather", [M, N, K], timed(fused), timed(nccl), flops=2.0 * M * N * K,
                hbm_bytes=2.0 * (M * K + N * K + M * N), link_bytes=2.0 * N * K * (world - 1) / world)
+    if want("zero3_step"):
+        # one optimizer round (2 micro-batches of 16k tokens, forward + backward + update) of a 6-layer slice of Qwen2.5-7B:
+        # replicated working weights against weights sharded per unit, gathered by the GEMM kernels or by NCCL on a side stream
+        from functools import partial
+
+        from ..models.config import ModelConfig
+        from ..workers.config import FSDPEngineConfig, OptimizerConfig
+        from ..workers.engine.native.engine import NativeEngineWithLMHead
+        from ..workers.utils.losses import sft_loss
+
+        arch = ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=6,
+                           num_attention_heads=28, num_key_value_heads=4, head_dim=128, eos_token_id=2, pad_token_id=0,
+                           tie_word_embeddings=False, attention_bias=True)
+        ids = torch.randint(3, 152064, (16, 2048), device=dev)
+        am = torch.ones_like(ids)
+        data = {"input_ids": ids, "attention_mask": am, "responses": ids[:, 512:], "response_mask": am[:, 512:]}
+        rows = {}
+        for name, stage, fz, fc in (("zero2_nccl_optimizer", 2, "1", "0"), ("zero3_gather_in_gemm", 3, "1", "0"), ("zero3_gather_nccl", 3, "0", "0")):
+            os.environ["VERL_B200_ZERO3_FUSED"], os.environ["VERL_B200_FUSED_COMM"] = fz, fc
+            eng = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=8, zero_stage=stage,
+                                                                enable_gradient_checkpointing=False),
+                                         OptimizerConfig(lr=1e-6, clip_grad=1.0))
+            eng.initialize()
+            rows[name] = timed(lambda: eng.train_batch(dict(data), partial(sft_loss, None)))
+            del eng
+            torch.cuda.empty_cache()
+        os.environ["VERL_B200_ZERO3_FUSED"] = os.environ["VERL_B200_FUSED_COMM"] = "1"
+        if rank == 0:
+            print(json.dumps({"case": "zero3_optimizer_round", "world": world, "tokens_per_rank": 2 * 16384, "layers": 6,
+                              "ms": {k: round(v, 2) for k, v in rows.items()}, "clocks": list(clock_log)}), flush=True)
+        clock_log.clear()
     if want("moe_ep"):
         # expert-parallel MoE layer of Qwen3-30B-A3B: router + dispatch + grouped GEMMs + combine
         from .expert_parallel import ExpertParallelMoE

@@ -138,6 +138,17 @@ def _v1_unsupported_reason(config) -> Optional[str]:
             return f"model family '{mc.arch.model_type}' samples through the library module (no step-wise rollout engine)"
     except Exception:
         return None
+    # a training replica that spans several ranks (sequence / context / tensor / pipeline parallel) shares one set of prompts
+    # and exchanges the generated rows inside the replica; that exchange lives in the synchronous generate_sequences path
+    a = config.actor_rollout_ref.actor
+    fc = a.get("fsdp_config") or {}
+    m = a.get("megatron") or {}
+    span = max(int(a.get("ulysses_sequence_parallel_size", 1) or 1), int((fc.get("context_parallel_size", 1) if hasattr(fc, "get") else 1) or 1))
+    if str(a.get("strategy", "fsdp")) == "megatron":
+        span = max(span, int(m.get("tensor_model_parallel_size", 1) or 1) * int(m.get("pipeline_model_parallel_size", 1) or 1)
+                   * int(m.get("context_parallel_size", 1) or 1))
+    if span > 1:
+        return f"the training replica spans {span} ranks (sequence / context / tensor / pipeline parallelism)"
     return None
 
 

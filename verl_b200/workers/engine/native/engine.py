@@ -217,6 +217,7 @@ class NativeEngine(BaseEngine):
                           and not int(getattr(self.model_config, "lora_rank", 0) or 0)
                           and self.world > 1 and self.group is None  # symmetric buffers are bound to the world group
                           and self.rep_world == 1
+                          and int(getattr(ec, "zero_stage", 2) or 2) != 3  # sharded working weights have their own peer-memory path
                           and os.environ.get("VERL_B200_FUSED_COMM", "1") != "0")
             buf = None
             if want_fused:
@@ -369,7 +370,15 @@ class NativeEngine(BaseEngine):
             "zero_stage=3 does not combine with sequence / context / expert parallelism"
         assert str(getattr(self.optimizer_config, "optimizer", "AdamW") or "AdamW").lower() != "muon", "zero_stage=3 runs AdamW"
         full = self.params
-        sharded = UnitShardedParams(full, group=self.sh_group, device=self.device, dtype=self.dtype)
+        # on GPUs with peer-mapped memory the units are gathered by the GEMM kernels themselves (fetch warps), else by a
+        # collective on a side stream
+        fused = False
+        if self.device.type == "cuda" and self.world > 1 and self.group is None and os.environ.get("VERL_B200_ZERO3_FUSED", "1") != "0":
+            from ....parallel.symmetric import symmetric_available
+
+            fused = symmetric_available() and bool(getattr(self.engine_config, "fused_comm", True))
+        self.zero3_fused_gather = fused
+        sharded = UnitShardedParams(full, group=self.sh_group, device=self.device, dtype=self.dtype, symmetric=fused)
         sharded.load_from_full(full.flat)
         self.params = self.tparams = sharded
         self.model.params = sharded
