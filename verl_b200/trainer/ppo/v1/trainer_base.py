@@ -198,7 +198,9 @@ class PPOTrainer(RayPPOTrainer):
         return self._to_device(batch)
 
     def _step_once(self, metrics: dict, timing_raw: dict) -> Optional[DataProto]:
-        bs = int(self.config.data.train_batch_size)
+        # train_batch_size counts prompts of the whole job; a controller-replicated rank trains on its share
+        _, dp_world = self._dp_rank_world()
+        bs = max(1, int(self.config.data.train_batch_size) // max(1, dp_world))
         self.on_sample_begin()
         with marked_timer("gen", timing_raw, color="red"):
             meta = self.replay_buffer.sample(bs, current_version=self.param_version, pump=self._pump)
