@@ -114,8 +114,19 @@ def main(argv=None):
             dist.reduce_scatter_tensor(out, grads.tensor, op=dist.ReduceOp.AVG)
             ops.sumsq_(out, ctrl)
 
-        report("grad_reduce_scatter_sumsq", [n], timed(fused), timed(nccl), hbm_bytes=4.0 * shard * (world + 1),
+        t_nccl = timed(nccl)
+        report("grad_reduce_scatter_sumsq", [n], timed(fused), t_nccl, hbm_bytes=4.0 * shard * (world + 1),
                link_bytes=4.0 * shard * (world - 1))
+        if grads.multicast_ptr:
+            # the same kernel through the NVSwitch multicast mapping: one multimem.ld_reduce returns the sum over the ranks,
+            # so only the reduced shard crosses this GPU's link
+            def fused_mc():
+                bar()
+                ops.rs_sumsq_(grads.ptrs, grads.multicast_ptr, out, lo, rank, 1.0 / world, ctrl)
+                bar()
+
+            report("grad_reduce_scatter_sumsq_multimem", [n], timed(fused_mc), t_nccl, hbm_bytes=4.0 * shard * 2,
+                   link_bytes=4.0 * shard)
         del grads
     if want("ag"):
         # AdamW on the shard + publication of the new bf16 weights into every replica
@@ -135,8 +146,17 @@ def main(argv=None):
             ops.adamw_(master, g, m, v, flat[lo : lo + shard], ctrl, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, False)
             dist.all_gather_into_tensor(flat, flat[lo : lo + shard].clone())
 
-        report("adamw_allgather_bf16", [n], timed(fused), timed(nccl), hbm_bytes=shard * (4.0 * 7 + 2.0 * world),
+        t_nccl = timed(nccl)
+        report("adamw_allgather_bf16", [n], timed(fused), t_nccl, hbm_bytes=shard * (4.0 * 7 + 2.0 * world),
                link_bytes=2.0 * shard * (world - 1))
+        if params.multicast_ptr:
+            def fused_mc():  # one multimem.st per 16 bytes reaches every replica: the shard leaves this GPU once
+                bar()
+                ops.adamw_allgather_(master, g, m, v, params.ptrs, params.multicast_ptr, lo, rank, ctrl, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1)
+                bar()
+
+            report("adamw_allgather_bf16_multimem", [n], timed(fused_mc), t_nccl, hbm_bytes=shard * (4.0 * 7 + 2.0),
+                   link_bytes=2.0 * shard)
         del params
     if want("gemm_ar"):
         # row-parallel linear (down projection of Qwen2.5-7B): partial GEMM + all-reduce
