@@ -264,3 +264,45 @@ def test_clock_sampler_reads_a_fake_nvml():
     rec = s.stop()
     assert rec["sm_mhz"] == 1500.0 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == ["sw_power_cap"]
     assert rec["power_w_max"] == 950.0 and rec["samples"] >= mid["samples"] > 2
+
+
+def test_platform_registry_and_out_of_tree_platform(monkeypatch):
+    from contextlib import contextmanager
+
+    from verl_b200.plugin.platform import PlatformBase, PlatformRegistry, get_platform, set_platform
+    from verl_b200.plugin.platform.platform_cpu import PlatformCPU
+    from verl_b200.utils import device as D
+
+    set_platform(None)
+    p = get_platform()
+    assert p.device_name == "cpu" and p.communication_backend_name() == "gloo" and not p.is_ipc_supported()
+    assert {"b200", "cuda", "cpu"} <= set(PlatformRegistry.registered_names())
+    assert D.get_nccl_backend() == "gloo" and D.get_device_id() == 0 and D.get_device_capability() == (None, None)
+    b200 = PlatformRegistry.get("b200")()
+    assert b200.ray_resource_options(1) == {"num_gpus": 1} and b200.visible_devices_envvar() == "CUDA_VISIBLE_DEVICES"
+    assert b200.communication_backend_name() == "nccl" and b200.ray_noset_envvars()
+
+    @PlatformRegistry.register("toy")
+    class Toy(PlatformCPU):
+        vendor_name = "toy"
+
+        def communication_backend_name(self):
+            return "toyccl"
+
+        def ray_resource_name(self):
+            return "TOY"
+
+        ray_resource_options = PlatformBase.ray_resource_options
+
+    monkeypatch.setenv("VERL_PLATFORM", "toy")
+    set_platform(None)
+    try:
+        assert get_platform().vendor_name == "toy" and D.get_nccl_backend() == "toyccl"
+        assert get_platform().ray_resource_options(2) == {"resources": {"TOY": 2}}
+        with pytest.raises(AssertionError):
+            PlatformRegistry.register("bad")(object)
+    finally:
+        monkeypatch.delenv("VERL_PLATFORM")
+        set_platform(None)
+    with pytest.raises(TypeError):
+        PlatformBase()  # abstract

@@ -23,30 +23,42 @@ def get_device_name() -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"
 
 
+def _platform():
+    """The active device platform (``verl_b200.plugin.platform``); the helpers below are its short forms."""
+    from ..plugin.platform import get_platform
+
+    p = get_platform()
+    if p.device_name != get_device_name() and not os.getenv("VERL_PLATFORM"):
+        # the device was forced after the platform was first detected (tests switch to the CPU oracle): detect again
+        from ..plugin.platform import set_platform
+
+        set_platform(None)
+        p = get_platform()
+    return p
+
+
 def get_torch_device():
-    return torch.cuda if get_device_name() == "cuda" else torch.cpu
+    return _platform().device_module
 
 
 def get_device_id() -> int:
-    return torch.cuda.current_device() if get_device_name() == "cuda" else 0
+    return _platform().current_device()
 
 
 def get_nccl_backend() -> str:
-    return "nccl" if get_device_name() == "cuda" else "gloo"
+    return _platform().communication_backend_name()
 
 
 def get_visible_devices_keyword() -> str:
-    return "CUDA_VISIBLE_DEVICES"
+    return _platform().visible_devices_envvar()
 
 
 def is_support_ipc() -> bool:
-    return get_device_name() == "cuda"
+    return _platform().is_ipc_supported()
 
 
 def get_device_capability(device_id: int = 0):
-    if get_device_name() != "cuda":
-        return (None, None)
-    return torch.cuda.get_device_capability(device_id)
+    return _platform().get_device_capability(device_id)
 
 
 def set_expandable_segments(enable: bool) -> None:
