@@ -86,7 +86,10 @@ class BaseCheckpointManager:
 
     def _flags(self, which: str) -> list:
         d = self.checkpoint_config
-        v = (d.get(which) if d is not None else None) or ["model", "optimizer", "extra"]
+        v = None
+        if d is not None:  # a mapping (config tree) or an object with attributes (dataclass)
+            v = d.get(which) if hasattr(d, "get") else getattr(d, which, None)
+        v = v or ["model", "optimizer", "extra"]
         return list(v)
 
     @property

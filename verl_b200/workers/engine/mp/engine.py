@@ -381,10 +381,60 @@ class ModelParallelEngine(NativeEngine):
             return []
         return self._delta_exporter.export(update_snapshot)
 
+    # ------------------------------------------------------------------------------------ checkpoint (layout schema v2)
+    @property
+    def global_rank(self) -> int:
+        return dist.get_rank() if dist.is_initialized() else 0
+
+    def _ckpt_manager(self):
+        if getattr(self, "_ckpt_mgr", None) is None:
+            from ....utils.checkpoint.megatron_checkpoint_manager import MegatronCheckpointManager
+
+            self._ckpt_mgr = MegatronCheckpointManager(self, checkpoint_config=self.checkpoint_config,
+                                                       role="critic" if self.value_head else "actor")
+        return self._ckpt_mgr
+
+    def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
+                        max_ckpt_to_keep: Optional[int] = None, **kwargs) -> None:
+        """One directory per model-parallel rank under ``model|optimizer|extra/dist_ckpt`` plus a manifest
+        (``utils/checkpoint/megatron_checkpoint_manager.py``); old checkpoints rotate as in the data-parallel engine."""
+        self._ckpt_manager().save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+        self._rotate_checkpoints(local_path, max_ckpt_to_keep)
+
+    def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, del_local_after_load: bool = False, **kwargs) -> None:
+        if local_path is None:
+            return
+        self._ckpt_manager().load_checkpoint(local_path, hdfs_path, del_local_after_load)
+        if self.qat.enable:
+            self._apply_qat()
+
+    def optimizer_state(self) -> dict:
+        """This rank's optimizer shard: fp32 masters, Adam moments, step counters."""
+        return {"master": self.master.cpu(), "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(),
+                "step": self.opt_step_count, "sched_step": self.sched_step, "shard_lo": self.shard_lo, "shard_numel": self.shard_numel}
+
+    def load_optimizer_state(self, st: dict) -> None:
+        assert st["shard_lo"] == self.shard_lo and st["master"].numel() == self.master.numel(), "optimizer shard layout mismatch"
+        self.master.copy_(st["master"])
+        self.exp_avg.copy_(st["exp_avg"])
+        self.exp_avg_sq.copy_(st["exp_avg_sq"])
+        self.opt_step_count, self.sched_step = int(st["step"]), int(st["sched_step"])
+        # the working weights follow the masters (identical to what was saved, up to the bf16 cast)
+        self._scatter_owned(self.master.to(self.device), self.tparams.flat)
+        self._publish_shard()
+
+    def reset_master_from_params(self) -> None:
+        """Model weights were loaded without optimizer state: the fp32 masters restart from them."""
+        self.master.copy_(self._owned(self.tparams.flat).float())
+
     def local_named_tensors(self):
         """(full-model name of the shard, local tensor) pairs: what the model-parallel checkpoint layout stores."""
         for m in self.maps:
             yield m.full_name, self.params.views[m.local_name]
+
+    def shard_meta(self) -> dict:
+        """full-model name -> (kind, blocks) of every local tensor: how the merger places a shard in the whole tensor."""
+        return {m.full_name: (m.kind, tuple(m.blocks)) for m in self.maps}
 
     def load_local_named_tensors(self, tensors: dict) -> None:
         for m in self.maps:
