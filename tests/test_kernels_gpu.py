@@ -272,6 +272,60 @@ def test_sampler_distribution_and_logprob(ops):
     assert int(tok.max()) < 100
 
 
+def _kept_set(x: torch.Tensor, temperature: float, top_k: int, top_p: float) -> torch.Tensor:
+    """Reference of the filtered sampler's kept set for one row (fp64): the k largest values and whatever ties with the
+    k-th, then the smallest set of largest values whose mass reaches top_p of that, ties with the boundary value kept."""
+    x = x.double() / temperature
+    keep = torch.ones_like(x, dtype=torch.bool)
+    if 0 < top_k < x.numel():
+        keep &= x >= torch.topk(x, top_k).values[-1]
+    if top_p < 1.0:
+        e = torch.where(keep, torch.exp(x - x.max()), torch.zeros_like(x))
+        vals, inv = torch.unique(x, return_inverse=True)           # ascending
+        group = torch.zeros_like(vals).index_add_(0, inv, e)
+        cum_from_top = torch.flip(torch.cumsum(torch.flip(group, [0]), 0), [0])
+        # the boundary group is the highest-valued group (scanning down) at which the cumulative mass reaches the target
+        reached = cum_from_top >= top_p * e.sum()
+        boundary = vals[reached.nonzero().max()]
+        keep &= x >= boundary
+    return keep
+
+
+def test_filtered_sampler_top_k_top_p(ops):
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(1)
+    # (a) full vocabulary, ties everywhere (bf16 logits): token inside the kept set, log-prob of the renormalised distribution
+    V, B = 152064, 6
+    lg = (torch.randn(B, V) * 2.5).bfloat16()
+    for temperature, top_k, top_p in ((1.0, 50, 1.0), (0.7, -1, 0.9), (1.3, 200, 0.5), (1.0, 1, 1.0), (1.0, -1, 0.01)):
+        tok, lp = F.sample_tokens(lg.to(DEV), temperature, torch.arange(B).to(DEV) + 7, 11, valid_vocab=V, top_k=top_k, top_p=top_p)
+        tok, lp = tok.cpu(), lp.cpu()
+        for r in range(B):
+            keep = _kept_set(lg[r].float(), temperature, top_k, top_p)
+            assert bool(keep[tok[r]]), (temperature, top_k, top_p, r)
+            xs = lg[r].double() / temperature
+            ref = xs[tok[r]] - torch.logsumexp(xs[keep], 0)
+            assert abs(float(lp[r]) - float(ref)) < 2e-3, (temperature, top_k, top_p, r, float(lp[r]), float(ref))
+        if top_k == 1:
+            assert torch.equal(tok, lg.float().argmax(-1))
+    # (b) empirical distribution on a small row of distinct values: top-k = 3 keeps {3, 2, 1}, top-p = 0.6 keeps {3} u {2}
+    row = torch.tensor([[0.0, 1.0, 2.0, 3.0] + [-30.0] * 60]).bfloat16().repeat(6000, 1).to(DEV)
+    tok, _ = F.sample_tokens(row, 1.0, torch.arange(6000).to(DEV), 0, top_k=3)
+    hist = torch.bincount(tok.cpu(), minlength=4)[:4].float() / 6000
+    want = torch.softmax(torch.tensor([1.0, 2.0, 3.0]), 0)
+    assert hist[0] == 0 and (hist[1:] - want).abs().max() < 0.03
+    tok, _ = F.sample_tokens(row, 1.0, torch.arange(6000).to(DEV), 0, top_p=0.7)   # p(3) = 0.64 < 0.7 <= p(3) + p(2)
+    hist = torch.bincount(tok.cpu(), minlength=4)[:4].float() / 6000
+    assert hist[0] == 0 and hist[1] == 0 and (hist[2:] - torch.softmax(torch.tensor([2.0, 3.0]), 0)).abs().max() < 0.03
+    # (c) vocabulary mask and negative logits only
+    neg = (-torch.rand(3, 5000) * 20 - 1).bfloat16()
+    tok, lp = F.sample_tokens(neg.to(DEV), 1.0, torch.arange(3).to(DEV), 2, valid_vocab=1000, top_k=5, top_p=0.95)
+    for r in range(3):
+        keep = _kept_set(neg[r, :1000].float(), 1.0, 5, 0.95)
+        assert int(tok[r]) < 1000 and bool(keep[int(tok[r])])
+
+
 def test_advantage_kernels(ops):
     import numpy as np
 

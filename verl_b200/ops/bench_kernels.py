@@ -109,6 +109,25 @@ def main(argv=None):
             out = torch.empty(M, N, device=dev, dtype=torch.float32 if amn else torch.bfloat16)
             ms = T(lambda: ops.gemm(A, B, None, out, amn, bmn, amn, False, 0))
             report(name, [M, N, K], ms, flops=2.0 * M * N * K, bytes_=2.0 * (M * K + N * K) + out.element_size() * M * N)
+    if want("fp8"):
+        # block-scaled e4m3 (1x128) linear against the bf16 GEMM on the same shapes: decode-sized and prefill-sized rows of
+        # the Qwen2.5-7B projections. "fp8_total" includes the on-the-fly quantisation of the activation.
+        for name, (M, N, K) in {"qkv_decode": (320, 4608, H), "gate_up_decode": (320, 2 * I, H), "down_decode": (320, H, I),
+                                "gate_up_prefill": (tok, 2 * I if not a.small else 8192, H), "down_prefill": (tok, H, I if not a.small else 8192)}.items():
+            x, w = rnd(M, K), rnd(N, K)
+            wq, ws = F.fp8_quantize_1x128(w)
+            xq, xs = F.fp8_quantize_1x128(x)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            ms_bf16 = T(lambda: ops.gemm(x, w, None, out, False, False, False, False, 0))
+            c_bf16 = T.clocks
+            ms_gemm = T(lambda: ops.gemm_fp8_blockscale(xq, xs, wq, ws, None))
+            ms_total = T(lambda: F.linear_fp8(x, wq, ws))
+            rec = {"kernel": f"fp8_blockscale_{name}", "shape": [M, N, K], "ms_bf16": round(ms_bf16, 4), "ms_fp8_gemm": round(ms_gemm, 4),
+                   "ms_fp8_total": round(ms_total, 4), "speedup_gemm": round(ms_bf16 / ms_gemm, 3), "speedup_total": round(ms_bf16 / ms_total, 3),
+                   "tflops_fp8_gemm": round(2.0 * M * N * K / ms_gemm / 1e9, 1),
+                   "weight_gbs_fp8": round(N * K / ms_gemm / 1e6, 1), "weight_gbs_bf16": round(2.0 * N * K / ms_bf16 / 1e6, 1),
+                   "clocks": {"bf16": c_bf16, "fp8": T.clocks}}
+            print(json.dumps(rec), flush=True)
     if want("lmhead"):
         Vs = 32768 if a.small else V
         h, w = rnd(tok, H), rnd(Vs, H)

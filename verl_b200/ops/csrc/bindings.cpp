@@ -385,6 +385,24 @@ std::tuple<Tensor, Tensor> sample(const Tensor& logits, int64_t valid_vocab, dou
   return {tok, lp};
 }
 
+// Same with top-k (<= 0: off) and top-p (>= 1: off) filtering done inside the kernel (histogram selection, no sort).
+std::tuple<Tensor, Tensor> sample_topkp(const Tensor& logits, int64_t valid_vocab, double inv_temp, int64_t top_k, double top_p,
+                                        const Tensor& seeds, int64_t step) {
+  CHECK_BF16(logits);
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && seeds.scalar_type() == at::kLong);
+  TORCH_CHECK(inv_temp > 0.0 && top_p > 0.0, "sample_topkp: sampling only (greedy decoding uses sample)");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t B = logits.size(0);
+  Tensor tok = at::empty({B}, logits.options().dtype(at::kLong));
+  Tensor lp = at::empty({B}, logits.options().dtype(at::kFloat));
+  count(1);
+  CHECK_RC(vb_sample_topkp(logits.data_ptr(), logits.stride(0), (int)B, (int)logits.size(1), (int)valid_vocab, (float)inv_temp,
+                           (int)top_k, (float)top_p, reinterpret_cast<long long*>(seeds.data_ptr()), step,
+                           reinterpret_cast<long long*>(tok.data_ptr()), lp.data_ptr<float>(), cur_stream()),
+           "vb_sample_topkp");
+  return {tok, lp};
+}
+
 // rewards/mask fp32 [B, L]; group int32 [B] in [0, num_groups). Returns (advantages [B,L], scores [B]).
 std::tuple<Tensor, Tensor> grpo_advantage(const Tensor& rewards, const Tensor& mask, const Tensor& group,
                                           int64_t num_groups, double eps, bool norm_by_std) {
@@ -836,6 +854,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("kv_append_", &kv_append_);
   m.def("paged_decode", &paged_decode);
   m.def("sample", &sample);
+  m.def("sample_topkp", &sample_topkp);
   m.def("grpo_advantage", &grpo_advantage);
   m.def("gae", &gae);
 }

@@ -62,6 +62,8 @@ int vb_paged_decode(const void* q, long long ldq, const void* kc, const void* vc
                     int block_size, float scale, cudaStream_t s);
 int vb_sample(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, const long long* seeds,
               long long step, long long* tokens, float* logprobs, cudaStream_t s);
+int vb_sample_topkp(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, int top_k, float top_p,
+                    const long long* seeds, long long step, long long* tokens, float* logprobs, cudaStream_t s);
 // attention_fwd_tcgen05.cu
 int vb_attn_fwd(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                 const int* cu_seqlens, int num_seqs, int total_tokens, int nh, int nkv, int hd, float scale, void* out,

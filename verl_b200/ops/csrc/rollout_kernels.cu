@@ -263,6 +263,197 @@ __global__ void sample_kernel(const __nv_bfloat16* __restrict__ logits, long lon
   }
 }
 
+// ---- top-k / top-p (nucleus) sampling without a sort.
+// bf16 logits have at most 65536 distinct values, so the k-th largest value and the nucleus boundary are found exactly by
+// two rounds of 256-bin histograms over an order-preserving 16-bit key (high byte, then low byte inside the boundary
+// bin): counts for top-k, probability mass for top-p (evaluated on the distribution that top-k left, as the reference
+// samplers do). Every element whose key is >= the boundary key is kept: elements that tie with the boundary value stay
+// in. The token is then drawn by Gumbel-max among the kept ones and its log-prob is that of the renormalised
+// distribution. One block per row; the row (V * 2 bytes) is re-read from L2 by each pass.
+__device__ __forceinline__ unsigned int bf16_key(__nv_bfloat16 v) {
+  const unsigned int u = __bfloat16_as_ushort(v);
+  return (u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u);
+}
+
+__global__ void sample_topkp_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int valid_vocab, float inv_temp,
+                                    int top_k, float top_p, const long long* __restrict__ seeds, long long step,
+                                    long long* __restrict__ tokens, float* __restrict__ logprobs) {
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  __shared__ int cnt[256];
+  __shared__ float mass[256];
+  __shared__ float red[32];
+  __shared__ int sh_i[4];
+  __shared__ float sh_f[4];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  auto block_max = [&](float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = red[0];
+      for (int k = 1; k < nw; ++k) t = fmaxf(t, red[k]);
+      sh_f[0] = t;
+    }
+    __syncthreads();
+    const float r = sh_f[0];
+    __syncthreads();
+    return r;
+  };
+  auto block_sum = [&](float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int k = 0; k < nw; ++k) t += red[k];   // fixed order
+      sh_f[0] = t;
+    }
+    __syncthreads();
+    const float r = sh_f[0];
+    __syncthreads();
+    return r;
+  };
+  // pass A: row maximum (of the temperature-scaled logits)
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) m = fmaxf(m, __bfloat162float(lr[i]) * inv_temp);
+  m = block_max(m);
+  unsigned int thr = 0;  // keep key >= thr
+  if (top_k > 0 && top_k < valid_vocab) {
+    // passes B, C: the key of the k-th largest element
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) cnt[b] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) atomicAdd(&cnt[bf16_key(lr[i]) >> 8], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int c = 0, b = 255;
+      for (; b > 0; --b) {
+        if (c + cnt[b] >= top_k) break;
+        c += cnt[b];
+      }
+      sh_i[0] = b;
+      sh_i[1] = c;  // elements strictly above bin b
+    }
+    __syncthreads();
+    const int hb = sh_i[0], above = sh_i[1];
+    __syncthreads();
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) cnt[b] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) {
+      const unsigned int k = bf16_key(lr[i]);
+      if (static_cast<int>(k >> 8) == hb) atomicAdd(&cnt[k & 255u], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int c = above, b = 255;
+      for (; b > 0; --b) {
+        if (c + cnt[b] >= top_k) break;
+        c += cnt[b];
+      }
+      sh_i[2] = (hb << 8) | b;
+    }
+    __syncthreads();
+    thr = static_cast<unsigned int>(sh_i[2]);
+    __syncthreads();
+  }
+  if (top_p < 1.f) {
+    // passes D, E: the smallest set of the largest elements whose mass reaches top_p of what top-k kept
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) mass[b] = 0.f;
+    __syncthreads();
+    float z = 0.f;
+    for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) {
+      const unsigned int k = bf16_key(lr[i]);
+      if (k >= thr) {
+        const float e = __expf(__bfloat162float(lr[i]) * inv_temp - m);
+        z += e;
+        atomicAdd(&mass[k >> 8], e);
+      }
+    }
+    z = block_sum(z);
+    if (threadIdx.x == 0) {
+      float c = 0.f;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (c + mass[b] >= top_p * z) break;
+        c += mass[b];
+      }
+      sh_i[0] = b;
+      sh_f[1] = c;
+    }
+    __syncthreads();
+    const int hb = sh_i[0];
+    const float above = sh_f[1];
+    __syncthreads();
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) mass[b] = 0.f;
+    __syncthreads();
+    for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) {
+      const unsigned int k = bf16_key(lr[i]);
+      if (k >= thr && static_cast<int>(k >> 8) == hb) atomicAdd(&mass[k & 255u], __expf(__bfloat162float(lr[i]) * inv_temp - m));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float c = above;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (c + mass[b] >= top_p * z) break;
+        c += mass[b];
+      }
+      const unsigned int tp = (static_cast<unsigned int>(hb) << 8) | static_cast<unsigned int>(b);
+      sh_i[2] = static_cast<int>(tp > thr ? tp : thr);
+    }
+    __syncthreads();
+    thr = static_cast<unsigned int>(sh_i[2]);
+    __syncthreads();
+  }
+  // pass F: Gumbel-max among the kept elements, normaliser of the kept set
+  const uint64_t key = mix64(static_cast<uint64_t>(seeds[row]) ^ (static_cast<uint64_t>(step) * 0xD1342543DE82EF95ull));
+  float l = 0.f, best = -INFINITY, best_x = 0.f;
+  int best_i = 0;
+  for (int i = threadIdx.x; i < valid_vocab; i += blockDim.x) {
+    if (bf16_key(lr[i]) < thr) continue;
+    const float x = __bfloat162float(lr[i]) * inv_temp;
+    l += __expf(x - m);
+    const uint64_t h = mix64(key + static_cast<uint64_t>(i));
+    const float u = (static_cast<float>(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float score = x - __logf(-__logf(u));
+    if (score > best) {
+      best = score;
+      best_i = i;
+      best_x = x;
+    }
+  }
+  l = block_sum(l);
+  __shared__ float sb[32], sx[32];
+  __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float b2 = __shfl_xor_sync(0xffffffffu, best, o), x2 = __shfl_xor_sync(0xffffffffu, best_x, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (b2 > best || (b2 == best && i2 < best_i)) {
+      best = b2;
+      best_i = i2;
+      best_x = x2;
+    }
+  }
+  if (lane == 0) {
+    sb[w] = best; sx[w] = best_x; si[w] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < nw; ++k) {
+      if (sb[k] > best || (sb[k] == best && si[k] < best_i)) {
+        best = sb[k];
+        best_i = si[k];
+        best_x = sx[k];
+      }
+    }
+    tokens[row] = best_i;
+    if (logprobs) logprobs[row] = best_x - (m + __logf(l));
+  }
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -298,6 +489,16 @@ int vb_paged_decode(const void* q, long long ldq, const void* kc, const void* vc
         reinterpret_cast<__nv_bfloat16*>(out), ldo, nh, nkv, block_size, sl2);
   else
     return -2;
+  return static_cast<int>(cudaGetLastError());
+}
+
+int vb_sample_topkp(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, int top_k, float top_p,
+                    const long long* seeds, long long step, long long* tokens, float* logprobs, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (valid_vocab <= 0 || valid_vocab > V) valid_vocab = V;
+  if (inv_temp <= 0.f || top_p <= 0.f) return -1;  // greedy decoding goes through vb_sample
+  sample_topkp_kernel<<<B, 1024, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, valid_vocab, inv_temp, top_k, top_p,
+                                         seeds, step, tokens, logprobs);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -530,9 +530,12 @@ def sample_tokens(logits: torch.Tensor, temperature: float, seeds: torch.Tensor,
     """Returns (tokens int64 [B], logprobs fp32 [B]) — the log-prob is of the processed distribution."""
     B, V = logits.shape
     vv = valid_vocab if 0 < valid_vocab <= V else V
-    if logits.is_cuda and top_k <= 0 and top_p >= 1.0 and logits.dtype == torch.bfloat16:
+    if logits.is_cuda and logits.dtype == torch.bfloat16:
         inv_temp = 0.0 if temperature <= 0 else 1.0 / temperature
-        return _ops().sample(logits, vv, inv_temp, seeds, step)
+        if (top_k <= 0 and top_p >= 1.0) or temperature <= 0:
+            return _ops().sample(logits, vv, inv_temp, seeds, step)
+        # filtered sampling stays on the device (and inside a captured decode graph): histogram selection, no sort
+        return _ops().sample_topkp(logits, vv, inv_temp, int(top_k), float(top_p), seeds, step)
     x = logits[:, :vv].float()
     if temperature <= 0:
         tok = x.argmax(-1)
