@@ -46,3 +46,126 @@ def test_fully_async_trains_and_respects_staleness_budget(monkeypatch):
     assert r.max_samples_per_version() == 12  # 4 samples x 2 updates x (1 + 0.5)
     assert r.produced >= 16 and r.stats["pauses"] >= 1
     assert r.produced <= 16 + r.max_samples_per_version()  # never ran ahead by more than one budget
+
+
+class _StepServer:
+    """A rollout server stand-in: emits one token per tick; the token is 1000 * weight_version + position, so a sequence
+    shows which weights produced each of its tokens. ``abort_all_requests`` ends every running call with what it has."""
+
+    def __init__(self, name):
+        self.name, self.version, self.running, self.calls, self.paused = name, 0, {}, 0, False
+        self._abort = 0
+
+    async def generate(self, prompt_ids, sampling_params, request_id, **kw):
+        import asyncio
+
+        from verl_b200.workers.rollout.replica import TokenOutput
+
+        self.calls += 1
+        self.running[request_id] = True
+        epoch = self._abort
+        out = []
+        try:
+            while len(out) < sampling_params["max_tokens"]:
+                await asyncio.sleep(0.001)
+                if self._abort != epoch:
+                    return TokenOutput(out, [0.0] * len(out), None, "aborted")
+                while self.paused:
+                    await asyncio.sleep(0.001)
+                out.append(1000 * self.version + len(prompt_ids) + len(out))
+            return TokenOutput(out, [0.0] * len(out), None, "length")
+        finally:
+            self.running.pop(request_id, None)
+
+    async def abort_all_requests(self):
+        self._abort += 1
+        self.paused = True
+
+    async def resume_generation(self):
+        self.paused = False
+
+
+class _Replica:
+    def __init__(self, name):
+        self.server_address, self.server_handle = name, _StepServer(name)
+
+    async def abort_all_requests(self):
+        await self.server_handle.abort_all_requests()
+
+
+def _manager(replicas, response_length=40):
+    from verl_b200.workers.rollout.llm_server import LLMServerManager
+
+    return LLMServerManager({"prompt_length": 8, "response_length": response_length}, replicas, fully_async=True)
+
+
+def test_partial_rollout_resumes_under_new_weights():
+    """A weight update aborts what runs; the client keeps the tokens made so far and the same request continues with the
+    new weights for the rest of its budget: no token is generated twice and none is lost."""
+    import asyncio
+
+    async def go():
+        rep = _Replica("r0")
+        sm = _manager([rep])
+        client = sm.client()
+        task = asyncio.ensure_future(client.generate("req", prompt_ids=[1, 2, 3], sampling_params={"max_tokens": 30}))
+        await asyncio.sleep(0.015)
+        # parameter sync: abort, install version 1, resume
+        await rep.server_handle.abort_all_requests()
+        rep.server_handle.version = 1
+        await rep.server_handle.resume_generation()
+        out = await task
+        return out, rep.server_handle.calls
+
+    out, calls = asyncio.run(go())
+    assert len(out.token_ids) == 30 and out.stop_reason == "length" and calls == 2
+    versions = [t // 1000 for t in out.token_ids]
+    cut = versions.index(1)
+    assert 0 < cut < 30 and versions == [0] * cut + [1] * (30 - cut)          # old-weight prefix, new-weight rest
+    assert [t % 1000 for t in out.token_ids] == list(range(3, 33))             # contiguous positions: nothing redone or dropped
+    assert out.num_preempted == 1
+
+
+def test_rebalance_moves_inflight_requests_to_added_replicas():
+    import asyncio
+
+    from verl_b200.experimental.fully_async_policy.fully_async_rollouter import FullyAsyncRollouter
+    from verl_b200.experimental.fully_async_policy.message_queue import MessageQueue
+
+    async def go():
+        r0 = _Replica("r0")
+        sm = _manager([r0], response_length=400)
+        client = sm.client()
+        roll = FullyAsyncRollouter(agent_worker=None, server_manager=sm, message_queue=MessageQueue(8, 1), prompt_source=lambda k: [],
+                                   n=1, sampling_params={}, required_samples=4, max_queue_size=2)
+        tasks = [asyncio.ensure_future(client.generate(f"q{i}", prompt_ids=[1], sampling_params={"max_tokens": 300})) for i in range(8)]
+        await asyncio.sleep(0.01)
+        assert sm.lb.snapshot() == {"r0": 8}
+        r1, r2, r3 = _Replica("r1"), _Replica("r2"), _Replica("r3")
+        await roll.add_replicas([r1, r2, r3])
+        assert sm.lb.snapshot() == {"r0": 8, "r1": 0, "r2": 0, "r3": 0}      # sticky: nothing moves by itself
+        diag = await roll.rebalance_requests()
+        await asyncio.sleep(0.08)                                                # retries land (client retry interval 0.05 s)
+        loads = sm.lb.snapshot()
+        outs = await asyncio.gather(*tasks)
+        return diag, loads, outs, roll
+
+    diag, loads, outs, roll = asyncio.run(go())
+    assert diag["cleared_entries"] == 8 and diag["inflight_after_wait"] == 0 and roll.stats["rebalances"] == 1
+    assert sorted(loads.values()) == [2, 2, 2, 2], loads
+    assert all(len(o.token_ids) == 300 and [t % 1000 for t in o.token_ids] == list(range(1, 301)) for o in outs)
+
+
+def test_rollouter_pauses_on_a_full_queue():
+    from verl_b200.experimental.fully_async_policy.fully_async_rollouter import FullyAsyncRollouter
+    from verl_b200.experimental.fully_async_policy.message_queue import MessageQueue
+
+    q = MessageQueue(8, 1)
+    roll = FullyAsyncRollouter(agent_worker=None, server_manager=None, message_queue=q, prompt_source=lambda k: [{"x": 1}], n=1,
+                               sampling_params={}, required_samples=100, max_queue_size=2)
+    assert not roll._should_pause_generation()
+    q.put_sample("a", 0)
+    q.put_sample("b", 0)
+    assert roll._should_pause_generation() and roll.stats["pause_reason"] == "queue_full"
+    q.get_sample(0)
+    assert not roll._should_pause_generation()

@@ -28,7 +28,8 @@ __all__ = ["FullyAsyncRollouter"]
 class FullyAsyncRollouter:
     def __init__(self, agent_worker, server_manager, message_queue: MessageQueue, prompt_source: Callable[[int], list[dict]],
                  n: int, sampling_params: dict, required_samples: int, trigger_parameter_sync_step: int = 1,
-                 staleness_threshold: float = 1.0, max_concurrent_samples: Optional[int] = None, total_samples: Optional[int] = None):
+                 staleness_threshold: float = 1.0, max_concurrent_samples: Optional[int] = None, total_samples: Optional[int] = None,
+                 max_queue_size: Optional[int] = None):
         self.w, self.sm, self.mq = agent_worker, server_manager, message_queue
         self.prompt_source, self.n, self.sp = prompt_source, int(n), dict(sampling_params)
         self.required_samples = int(required_samples)
@@ -36,6 +37,9 @@ class FullyAsyncRollouter:
         self.staleness_threshold = float(staleness_threshold)
         self.max_concurrent = int(max_concurrent_samples or 2 * required_samples)
         self.total_samples = total_samples
+        # finished samples waiting for the trainer: production also stops while the queue is full (nothing would be gained
+        # by producing samples that push older ones out)
+        self.max_queue_size = int(max_queue_size) if max_queue_size else None
         self.param_version = 0
         self.submitted = self.produced = self.produced_since_sync = 0
         self.paused = False
@@ -49,7 +53,13 @@ class FullyAsyncRollouter:
     def _should_pause_generation(self) -> bool:
         if self.total_samples is not None and self.submitted >= self.total_samples:
             return True
-        return self.produced_since_sync + len(self.running) >= self.max_samples_per_version()
+        if self.max_queue_size is not None and self.mq.get_queue_size() >= self.max_queue_size:
+            self.stats["pause_reason"] = "queue_full"
+            return True
+        if self.produced_since_sync + len(self.running) >= self.max_samples_per_version():
+            self.stats["pause_reason"] = "staleness"
+            return True
+        return False
 
     def update_param_version(self, version: int) -> None:
         """Called by the parameter synchroniser after a weight sync: the budget starts over."""
@@ -113,8 +123,25 @@ class FullyAsyncRollouter:
             if r in self.sm.replicas:
                 self.sm.replicas.remove(r)
 
-    def rebalance_requests(self) -> dict:
-        return self.sm.lb.snapshot()
+    async def rebalance_requests(self, wait_inflight_timeout_s: float = 30.0, wait_inflight_poll_interval_s: float = 0.01) -> dict:
+        """Spread the requests in flight evenly over the replicas that are active now (after replicas were added, the old
+        ones carry everything and the new ones nothing): (1) forget the sticky request -> server map, (2) abort what every
+        replica runs (the clients keep the partial outputs and re-issue the rest), (3) wait until the aborted calls have
+        released their servers, so that the counts the router sees are true, (4) let the replicas generate again: the
+        retries go to the least-loaded replicas. Returns the diagnostics of step 1 plus what was still in flight at the
+        end of step 3. Parity target: ``fully_async_rollouter.py:1211-1274``."""
+        result = self.sm.lb.clear_sticky_cache()
+        replicas = list(self.sm.replicas)
+        if replicas:
+            await asyncio.gather(*[r.server_handle.abort_all_requests() for r in replicas])
+        deadline = time.time() + wait_inflight_timeout_s
+        while self.sm.lb.get_total_inflight() > 0 and time.time() < deadline:
+            await asyncio.sleep(wait_inflight_poll_interval_s)
+        result["inflight_after_wait"] = self.sm.lb.get_total_inflight()
+        if replicas:
+            await asyncio.gather(*[r.server_handle.resume_generation() for r in replicas])
+        self.stats["rebalances"] = self.stats.get("rebalances", 0) + 1
+        return result
 
     def statistics(self) -> dict:
         return {"rollouter/submitted": self.submitted, "rollouter/produced": self.produced, "rollouter/running": len(self.running),

@@ -61,6 +61,16 @@ class GlobalRequestLoadBalancer:
     def snapshot(self) -> dict[str, int]:
         return dict(self._inflight)
 
+    def get_total_inflight(self) -> int:
+        return sum(self._inflight.values())
+
+    def clear_sticky_cache(self) -> dict:
+        """Forget which server each request was pinned to: the next ``acquire_server`` of every request (a retry after an
+        abort included) goes to the least-loaded server. Returns what was cleared and the loads at that moment."""
+        n = len(self._sticky)
+        self._sticky.clear()
+        return {"cleared_entries": n, "server_loads": dict(self._inflight)}
+
 
 class LLMServerClient:
     """``generate(request_id, prompt_ids, sampling_params) -> TokenOutput`` against the balanced replicas."""
