@@ -162,6 +162,55 @@ def test_paged_decode_attention_and_kv_append(ops):
     assert torch.equal(flat[900], k[1]) and torch.equal(flat[0], k[6]) and flat[1].abs().sum() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64)])
+def test_grouped_prefix_paged_decode_matches_reference(ops, nh, nkv, hd):
+    """Sequences that share their leading pages in groups: the group kernel + per-sequence kernel + merge give the fp32
+    reference; members of different sizes, a sequence in no group, an inactive member, an empty group row, and a group
+    whose shared pages do not divide evenly over the prefix splits."""
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(3)
+    B, bs, nb, maxb = 12, 64, 96, 10
+    kc, vc = torch.randn(nb, bs, nkv, hd).bfloat16(), torch.randn(nb, bs, nkv, hd).bfloat16()
+    perm = torch.randperm(nb).tolist()
+    bt = torch.zeros(B, maxb, dtype=torch.int32)
+    take = lambda n: [perm.pop() for _ in range(n)]
+    groups = {0: ([0, 1, 2, 3, 4], 3), 1: ([5, 6], 5), 3: ([7, 8, 9], 1)}     # gid -> (member sequences, shared pages); gid 2 stays empty
+    cl = torch.zeros(B, dtype=torch.int32)
+    skip = torch.zeros(B, dtype=torch.int32)
+    for gid, (members, pages) in groups.items():
+        shared = take(pages)
+        for j, b in enumerate(members):
+            own = take(3)
+            bt[b, :pages] = torch.tensor(shared, dtype=torch.int32)
+            bt[b, pages:pages + 3] = torch.tensor(own, dtype=torch.int32)
+            cl[b] = pages * bs + 1 + 37 * j + (bs if j == 1 else 0)              # ragged tails, some reaching a second own page
+            skip[b] = pages
+    for b in (10, 11):                                                           # in no group
+        bt[b, :4] = torch.tensor(take(4), dtype=torch.int32)
+        cl[b] = 70 + 100 * (b - 10)
+    cl[8] = 0                                                                    # an inactive member of group 3
+    members = torch.full((4, 8), -1, dtype=torch.int32)
+    grp_pages = torch.zeros(4, dtype=torch.int32)
+    for gid, (m, pages) in groups.items():
+        members[gid, : len(m)] = torch.tensor(m, dtype=torch.int32)
+        grp_pages[gid] = pages
+    q = torch.randn(B, nh, hd).bfloat16()
+    ref = F.paged_decode_attention(q.float(), kc.float(), vc.float(), bt, cl)
+    for psplit, nsplit in ((2, 1), (1, 2), (3, 3)):
+        ws = torch.empty(B * nh * (psplit + nsplit) * (hd + 2), device=DEV)
+        ws.fill_(float("nan"))                                                   # stale scratch must not leak into the result
+        o = F.paged_decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV),
+                                     groups=(members.to(DEV), grp_pages.to(DEV), skip.to(DEV), ws, psplit, nsplit))
+        torch.cuda.synchronize()
+        live = cl > 0
+        assert torch.isfinite(o[live.to(DEV)]).all()
+        assert rel(o[live.to(DEV)], ref[live]) < 1e-2, (psplit, nsplit, rel(o[live.to(DEV)], ref[live]))
+        plain = F.paged_decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cl.to(DEV))
+        assert rel(o[live.to(DEV)], plain[live.to(DEV)]) < 5e-3
+    assert int(ops.gemm_status()) == 0
+
+
 def _attn_reference(q, k, v, lens, scale):
     """fp32 causal GQA attention per sequence with autograd."""
     outs, off = [], 0

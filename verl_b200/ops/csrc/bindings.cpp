@@ -329,6 +329,34 @@ void kv_append_(const Tensor& k, const Tensor& v, const Tensor& slot, Tensor kc,
            "vb_kv_append");
 }
 
+// Decode attention with grouped shared prefixes (see vb_paged_decode_grouped). members int32 [NG, 8], grp_pages int32 [NG],
+// skip int32 [B]; workspace: fp32 tensor of at least B * nh * (psplit + nsplit) * (hd + 2) elements (kept by the caller so that a
+// captured decode step allocates nothing).
+Tensor paged_decode_grouped(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_table, const Tensor& ctx_len,
+                            const Tensor& members, const Tensor& grp_pages, const Tensor& skip, double scale, int64_t psplit,
+                            int64_t nsplit, Tensor workspace) {
+  CHECK_BF16(q);
+  CHECK_BF16(kc);
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2) && kc.dim() == 4 && kc.size(1) == 64);
+  for (const Tensor* t : {&block_table, &ctx_len, &members, &grp_pages, &skip})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_contiguous() && t->is_cuda(), "paged_decode_grouped: int32 contiguous CUDA index tensors");
+  TORCH_CHECK(members.dim() == 2 && members.size(1) == 8 && grp_pages.numel() == members.size(0) && skip.numel() == q.size(0));
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), nh = q.size(1), hd = q.size(2), nkv = kc.size(2), slots = psplit + nsplit;
+  TORCH_CHECK(workspace.scalar_type() == at::kFloat && workspace.is_contiguous() && workspace.numel() >= B * nh * slots * (hd + 2),
+              "paged_decode_grouped: workspace too small");
+  Tensor out = at::empty({B, nh, hd}, q.options());
+  float* po = workspace.data_ptr<float>();
+  float* pml = po + B * nh * slots * hd;
+  count(3);
+  CHECK_RC(vb_paged_decode_grouped(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), kc.size(0) * 64, block_table.data_ptr<int>(),
+                                   (int)block_table.size(1), ctx_len.data_ptr<int>(), members.data_ptr<int>(), grp_pages.data_ptr<int>(),
+                                   skip.data_ptr<int>(), (int)members.size(0), out.data_ptr(), out.stride(0), (int)B, (int)nh, (int)nkv,
+                                   (int)hd, 64, (float)scale, (int)psplit, (int)nsplit, po, pml, cur_stream()),
+           "vb_paged_decode_grouped");
+  return out;
+}
+
 // q: [B, nh, hd] view; caches [num_blocks, block_size, nkv, hd]; block_table int32 [B, max_blocks]; ctx_len int32 [B]
 Tensor paged_decode(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& block_table,
                     const Tensor& ctx_len, double scale) {
@@ -853,6 +881,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("accum_bf16_f32_", &accum_bf16_f32_);
   m.def("kv_append_", &kv_append_);
   m.def("paged_decode", &paged_decode);
+  m.def("paged_decode_grouped", &paged_decode_grouped);
   m.def("sample", &sample);
   m.def("sample_topkp", &sample_topkp);
   m.def("grpo_advantage", &grpo_advantage);

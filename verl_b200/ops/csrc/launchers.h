@@ -60,6 +60,10 @@ int vb_kv_append(const void* k, const void* v, long long ldk, long long ldv, con
 int vb_paged_decode(const void* q, long long ldq, const void* kc, const void* vc, const int* block_table,
                     int max_blocks, const int* ctx_len, void* out, long long ldo, int B, int nh, int nkv, int hd,
                     int block_size, float scale, cudaStream_t s);
+int vb_paged_decode_grouped(const void* q, long long ldq, const void* kc, const void* vc, long long num_slots, const int* block_table,
+                            int max_blocks, const int* ctx_len, const int* members, const int* grp_pages, const int* skip, int NG,
+                            void* out, long long ldo, int B, int nh, int nkv, int hd, int block_size, float scale, int psplit,
+                            int nsplit, float* part_o, float* part_ml, cudaStream_t stream);
 int vb_sample(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, const long long* seeds,
               long long step, long long* tokens, float* logprobs, cudaStream_t s);
 int vb_sample_topkp(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, int top_k, float top_p,

@@ -33,6 +33,10 @@ struct PagedDecodeParams {
   int nh, nkv, nsplit;
   float scale_log2;
   int* status;
+  // grouped-prefix mode: the leading skip[b] pages of sequence b are covered by the group kernel below; this kernel then
+  // starts behind them and writes its partial results into slots [slot0, slot0 + nsplit) of nslots per (sequence, head)
+  const int* skip;  // [B] or null
+  int slot0, nslots;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -78,8 +82,9 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   const int G = p.nh / p.nkv;
   const int len = p.ctx_len[b];
   const int npages = (len + PD_PAGE - 1) / PD_PAGE;
-  const int per = (npages + p.nsplit - 1) / p.nsplit;
-  const int pg0 = split * per, pg1 = min(npages, pg0 + per);
+  const int first = p.skip != nullptr ? min(p.skip[b], npages) : 0;
+  const int per = (npages - first + p.nsplit - 1) / p.nsplit;
+  const int pg0 = first + split * per, pg1 = min(npages, pg0 + per);
   const int n = max(0, pg1 - pg0);
   const int* bt = p.block_table + static_cast<long long>(b) * p.max_blocks;
 
@@ -242,15 +247,210 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       acc += sM[(w * 16 + g) * (HD + 2) + d] * f;
     }
     const int head = kvh * G + g;
-    if (p.nsplit == 1) {
+    if (p.nslots <= 1) {
       p.out[b * p.ldo + static_cast<long long>(head) * HD + d] = __float2bfloat16(Lsum > 0.f ? acc / Lsum : 0.f);
     } else {
-      const long long base = (static_cast<long long>(b) * p.nh + head) * p.nsplit + split;
+      const long long base = (static_cast<long long>(b) * p.nh + head) * p.nslots + p.slot0 + split;
       p.part_o[base * HD + d] = acc;
       if (d == 0) {
         p.part_ml[base * 2] = M;
         p.part_ml[base * 2 + 1] = Lsum;
+        if (p.skip != nullptr && split == 0 && first == 0) {
+          // a sequence outside every group: its prefix slots hold the neutral element of the merge
+          for (int sl = 0; sl < p.slot0; ++sl) {
+            p.part_ml[(base - p.slot0 - split + sl) * 2] = -INFINITY;
+            p.part_ml[(base - p.slot0 - split + sl) * 2 + 1] = 0.f;
+          }
+        }
       }
+    }
+  }
+}
+
+// ---- grouped prefix: the sequences of a group (the samples of one prompt) share their leading pages. One CTA per
+// (group, KV head, split of the shared pages) streams those pages ONCE; warp w holds the query heads of member w and
+// runs all 64 tokens of every page against them (four 16-token sub-blocks, one online softmax per member). The result
+// of each member goes to partial slot `split` of that sequence; the per-sequence kernel above covers the pages behind
+// the shared ones and paged_decode_merge_kernel joins the slots by their log-sum-exp.
+constexpr int PG_MEMBERS = 8;
+
+struct PagedDecodeGroupParams {
+  const __nv_bfloat16* q;
+  long long ldq;
+  const int* block_table;
+  int max_blocks;
+  const int* members;    // [NG, PG_MEMBERS] sequence index or -1; member 0 of a live group is valid
+  const int* grp_pages;  // [NG] shared pages (0: empty group)
+  float* part_o;
+  float* part_ml;
+  int nh, nkv, psplit, nslots;
+  float scale_log2;
+  int* status;
+};
+
+template <int HD>
+struct PGSmem {
+  static constexpr int TILE = PD_PAGE * HD * 2;
+  static constexpr int STAGE = 2 * TILE;
+  static constexpr int OFF_Q = PD_STAGES * STAGE;            // PG_MEMBERS x 16 x HD bf16
+  static constexpr int OFF_BAR = OFF_Q + PG_MEMBERS * 16 * HD * 2;
+  static constexpr int TOTAL = OFF_BAR + 64 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PG_MEMBERS * 32, 1)
+paged_decode_group_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                          const PagedDecodeGroupParams p) {
+  using L = PGSmem<HD>;
+  constexpr int PANELS = HD / 64;
+  const int g = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int npages = p.grp_pages[g];
+  if (npages <= 0) return;  // uniform over the CTA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_Q);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* empty = full + PD_STAGES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.nh / p.nkv;
+  const int b = p.members[g * PG_MEMBERS + warp];
+  const int per = (npages + p.psplit - 1) / p.psplit;
+  const int pg0 = split * per, pg1 = min(npages, pg0 + per);
+  const int n = max(0, pg1 - pg0);
+  const int* bt = p.block_table + static_cast<long long>(p.members[g * PG_MEMBERS]) * p.max_blocks;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    for (int s = 0; s < PD_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], PG_MEMBERS);
+    }
+    mbar_fence_init();
+  }
+  // this warp's member: query heads of the KV head, zero padded to 16 rows
+  for (int i = lane; i < 16 * HD / 8; i += 32) {
+    const int gh = i / (HD / 8), c = i % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (b >= 0 && gh < G) v = *reinterpret_cast<const uint4*>(p.q + b * p.ldq + static_cast<long long>(kvh * G + gh) * HD + c * 8);
+    *reinterpret_cast<uint4*>(sQ + (warp * 16 + gh) * HD + c * 8) = v;
+  }
+  __syncthreads();
+
+  auto issue = [&](int i) {
+    const int s = i % PD_STAGES;
+    const int row = bt[pg0 + i] * PD_PAGE;
+    uint8_t* dst = smem + s * L::STAGE;
+    mbar_expect_tx(&full[s], L::STAGE);
+#pragma unroll
+    for (int c = 0; c < PANELS; ++c) {
+      tma_load_2d(dst + c * (PD_PAGE * 128), &tm_k, &full[s], kvh * HD + 64 * c, row);
+      tma_load_2d(dst + L::TILE + c * (PD_PAGE * 128), &tm_v, &full[s], kvh * HD + 64 * c, row);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < min(n, PD_STAGES); ++i) issue(i);
+  }
+  uint32_t qa[HD / 16][4];
+  {
+    const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+      const int row = (mi & 1) * 8 + r, col = k * 16 + (mi >> 1) * 8;
+      ldsm_x4(qa[k], smem_u32(sQ + (warp * 16 + row) * HD + col));
+    }
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  bool ok = true;
+  for (int i = 0; i < n; ++i) {
+    const int s = i % PD_STAGES;
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (i / PD_STAGES) & 1))) { ok = false; break; }
+    const uint32_t kbase = smem_u32(smem + s * L::STAGE), vbase = kbase + L::TILE;
+    if (b >= 0) {
+#pragma unroll 1
+      for (int tb = 0; tb < PD_PAGE / 16; ++tb) {
+        const int t0w = tb * 16;
+        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+          const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb) {
+            const int tok = t0w + nb * 8 + r;
+#pragma unroll
+            for (int k2 = 0; k2 < HD / 32; ++k2) {
+              const int dc = k2 * 4 + mi;
+              uint32_t kb[4];
+              ldsm_x4(kb, kbase + (dc >> 3) * (PD_PAGE * 128) + tok * 128 + (((dc & 7) ^ (tok & 7)) << 4));
+              mma_bf16_16816(sacc[nb], qa[2 * k2], kb[0], kb[1]);
+              mma_bf16_16816(sacc[nb], qa[2 * k2 + 1], kb[2], kb[3]);
+            }
+          }
+        }
+        float alpha[2];
+        uint32_t pa[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // every token of a shared page lies inside every member's context
+          const float v0 = sacc[0][h * 2] * p.scale_log2, v1 = sacc[0][h * 2 + 1] * p.scale_log2;
+          const float v2 = sacc[1][h * 2] * p.scale_log2, v3 = sacc[1][h * 2 + 1] * p.scale_log2;
+          float mx = fmaxf(fmaxf(v0, v1), fmaxf(v2, v3));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float mn = fmaxf(m_run[h], mx);
+          alpha[h] = exp2f(m_run[h] - mn);
+          const float e0 = exp2f(v0 - mn), e1 = exp2f(v1 - mn), e2 = exp2f(v2 - mn), e3 = exp2f(v3 - mn);
+          float sum = (e0 + e1) + (e2 + e3);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          l_run[h] = l_run[h] * alpha[h] + sum;
+          m_run[h] = mn;
+          pa[h] = pack_bf16x2(e0, e1);
+          pa[2 + h] = pack_bf16x2(e2, e3);
+        }
+        {
+          const int mi = lane >> 3, r = lane & 7;
+          const int tok = t0w + (mi & 1) * 8 + r;
+#pragma unroll
+          for (int j2 = 0; j2 < HD / 16; ++j2) {
+            const int dc = j2 * 2 + (mi >> 1);
+            uint32_t vb[4];
+            ldsm_x4_t(vb, vbase + (dc >> 3) * (PD_PAGE * 128) + tok * 128 + (((dc & 7) ^ (tok & 7)) << 4));
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+              float* oo = o[2 * j2 + q2];
+              oo[0] *= alpha[0]; oo[1] *= alpha[0]; oo[2] *= alpha[1]; oo[3] *= alpha[1];
+              mma_bf16_16816(o[2 * j2 + q2], pa, vb[2 * q2], vb[2 * q2 + 1]);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+    if (threadIdx.x == 0 && i + PD_STAGES < n) {
+      if (mbar_wait(&empty[s], (i / PD_STAGES) & 1)) issue(i + PD_STAGES);
+      else atomicExch(p.status, ST_TIMEOUT_PRODUCER);
+    }
+    __syncwarp();
+  }
+  if (!ok && lane == 0) atomicExch(p.status, ST_TIMEOUT_EPILOGUE);
+  if (b < 0) return;
+  // this member's partial result for slot `split` (a split without pages writes the neutral element)
+  const int h0 = lane >> 2, cpair = (lane & 3) * 2;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int gh = h0 + hh * 8;
+    if (gh >= G) continue;
+    const long long base = (static_cast<long long>(b) * p.nh + kvh * G + gh) * p.nslots + split;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+      *reinterpret_cast<float2*>(p.part_o + base * HD + j * 8 + cpair) = make_float2(o[j][hh * 2], o[j][hh * 2 + 1]);
+    if ((lane & 3) == 0) {
+      p.part_ml[base * 2] = m_run[hh];
+      p.part_ml[base * 2 + 1] = l_run[hh];
     }
   }
 }
@@ -268,7 +468,8 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, cons
   float L = 0.f, acc = 0.f;
   for (int s = 0; s < nsplit; ++s) {
     const float ms = part_ml[(bh * nsplit + s) * 2];
-    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+    if (ms == -INFINITY) continue;  // an empty slot: its values were never written
+    const float f = exp2f(ms - M);
     L += part_ml[(bh * nsplit + s) * 2 + 1] * f;
     acc += part_o[(bh * nsplit + s) * hd + d] * f;
   }
@@ -317,6 +518,7 @@ extern "C" int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, 
   p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.ldq = ldq; p.block_table = block_table; p.max_blocks = max_blocks;
   p.ctx_len = ctx_len; p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.part_o = part_o; p.part_ml = part_ml;
   p.nh = nh; p.nkv = nkv; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.skip = nullptr; p.slot0 = 0; p.nslots = nsplit;
   cudaError_t e = (hd == 128) ? launch_pd<128>(tk, tv, p, B, stream) : launch_pd<64>(tk, tv, p, B, stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (nsplit > 1) {
@@ -326,6 +528,64 @@ extern "C" int vb_paged_decode_v2(const void* q, long long ldq, const void* kc, 
     e = cudaGetLastError();
   }
   return static_cast<int>(e);
+}
+
+template <int HD>
+static cudaError_t launch_pg(const CUtensorMap& tk, const CUtensorMap& tv, const PagedDecodeGroupParams& p, int NG,
+                             cudaStream_t stream) {
+  auto kern = paged_decode_group_kernel<HD>;
+  constexpr int smem = PGSmem<HD>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid(NG, p.nkv, p.psplit);
+  kern<<<grid, PG_MEMBERS * 32, smem, stream>>>(tk, tv, p);
+  return cudaGetLastError();
+}
+
+// Decode attention for sequences that share their leading pages in groups (the samples of one prompt).
+//  members [NG, 8]   sequence index of every member of a group (-1: none; entry 0 valid when grp_pages > 0)
+//  grp_pages [NG]    pages shared by the members of the group (0: no such group)
+//  skip [B]          for every sequence the number of leading pages its group covers (0: in no group)
+// The group kernel reads the shared pages once per group into `psplit` partial slots, the per-sequence kernel covers the
+// rest of every context in `nsplit` slots, and the merge kernel joins the psplit + nsplit slots.
+// Scratch: part_o of B*nh*(psplit+nsplit)*hd floats, part_ml of B*nh*(psplit+nsplit)*2 floats.
+extern "C" int vb_paged_decode_grouped(const void* q, long long ldq, const void* kc, const void* vc, long long num_slots,
+                                       const int* block_table, int max_blocks, const int* ctx_len, const int* members,
+                                       const int* grp_pages, const int* skip, int NG, void* out, long long ldo, int B, int nh,
+                                       int nkv, int hd, int block_size, float scale, int psplit, int nsplit, float* part_o,
+                                       float* part_ml, cudaStream_t stream) {
+  if (B == 0) return 0;
+  if (block_size != PD_PAGE || (hd != 64 && hd != 128) || nh % nkv || nh / nkv > 16) return -2;
+  if (psplit < 1 || nsplit < 1 || NG < 1 || part_o == nullptr || part_ml == nullptr) return -4;
+  CUtensorMap tk, tv;
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint64_t cols = static_cast<uint64_t>(nkv) * hd;
+  if (!make_tmap_2d(&tk, kc, bf, 2, num_slots, cols, cols, 64, PD_PAGE, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!make_tmap_2d(&tv, vc, bf, 2, num_slots, cols, cols, 64, PD_PAGE, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  static int* status = nullptr;
+  if (status == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_pd_status);
+  const int nslots = psplit + nsplit;
+  PagedDecodeGroupParams g{};
+  g.q = reinterpret_cast<const __nv_bfloat16*>(q); g.ldq = ldq; g.block_table = block_table; g.max_blocks = max_blocks;
+  g.members = members; g.grp_pages = grp_pages; g.part_o = part_o; g.part_ml = part_ml; g.nh = nh; g.nkv = nkv;
+  g.psplit = psplit; g.nslots = nslots; g.scale_log2 = scale * 1.4426950408889634f; g.status = status;
+  cudaError_t e = (hd == 128) ? launch_pg<128>(tk, tv, g, NG, stream) : launch_pg<64>(tk, tv, g, NG, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  PagedDecodeParams p{};
+  p.q = g.q; p.ldq = ldq; p.block_table = block_table; p.max_blocks = max_blocks; p.ctx_len = ctx_len;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.part_o = part_o; p.part_ml = part_ml;
+  p.nh = nh; p.nkv = nkv; p.nsplit = nsplit; p.scale_log2 = g.scale_log2; p.status = status;
+  p.skip = skip; p.slot0 = psplit; p.nslots = nslots;
+  e = (hd == 128) ? launch_pd<128>(tk, tv, p, B, stream) : launch_pd<64>(tk, tv, p, B, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const long long total = static_cast<long long>(B) * nh * hd;
+  paged_decode_merge_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, stream>>>(
+      part_o, part_ml, reinterpret_cast<__nv_bfloat16*>(out), ldo, B, nh, hd, nslots);
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int vb_pd_status() {

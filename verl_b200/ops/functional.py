@@ -501,10 +501,18 @@ def kv_append_(k, v, slots, k_cache, v_cache) -> None:
     vc[slots[ok]] = v[ok]
 
 
-def paged_decode_attention(q, k_cache, v_cache, block_table, ctx_len, scale: Optional[float] = None):
-    """One query token per sequence against a paged cache [num_blocks, block_size, nkv, hd]."""
+def paged_decode_attention(q, k_cache, v_cache, block_table, ctx_len, scale: Optional[float] = None, groups=None):
+    """One query token per sequence against a paged cache [num_blocks, block_size, nkv, hd].
+
+    ``groups`` = (members int32 [NG, 8], grp_pages int32 [NG], skip int32 [B], workspace fp32, psplit, nsplit): sequences
+    that share their leading pages (the samples of one prompt) have those pages read once per group by a kernel that
+    holds every member's query heads, and only the rest of each context per sequence; same result as without."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if q.is_cuda:
+        if groups is not None:
+            members, grp_pages, skip, ws, psplit, nsplit = groups
+            return _ops().paged_decode_grouped(q, k_cache, v_cache, block_table, ctx_len, members, grp_pages, skip, scale,
+                                               int(psplit), int(nsplit), ws)
         return _ops().paged_decode(q, k_cache, v_cache, block_table, ctx_len, scale)
     B, nh, hd = q.shape
     bs, nkv = k_cache.shape[1], k_cache.shape[2]

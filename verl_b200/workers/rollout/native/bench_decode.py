@@ -29,6 +29,8 @@ def main(argv=None):
     ap.add_argument("--hbm-gbs", type=float, default=6545.6)
     ap.add_argument("--group", type=int, default=1, help="consecutive sequences that share the pages of their first --shared-ctx tokens")
     ap.add_argument("--shared-ctx", type=int, default=1024)
+    ap.add_argument("--no-grouped-kernel", action="store_true",
+                    help="with --group: keep the shared pages in the block tables but read them per sequence (plain decode kernel)")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     cfg = get_preset(a.model)
@@ -45,6 +47,12 @@ def main(argv=None):
         shared_pages = min(a.shared_ctx, a.ctx) // bs
         lead = (torch.arange(S, device=dev) // a.group) * a.group
         eng.block_table[:, :shared_pages] = eng.block_table[lead, :shared_pages]
+        if eng.grouped_decode and not a.no_grouped_kernel and a.group <= 8:
+            # what the engine's admission does for the samples of a prompt: one decode group per prompt
+            ng = S // a.group
+            eng.grp_members[:ng, : a.group] = torch.arange(ng * a.group, dtype=torch.int32, device=dev).view(ng, a.group)
+            eng.grp_pages[:ng] = shared_pages
+            eng.seq_skip[: ng * a.group] = shared_pages
     eng.tok.fill_(5)
     eng.pos.fill_(a.ctx)
     eng.ctx.fill_(a.ctx + 1)
@@ -72,7 +80,8 @@ def main(argv=None):
     print(json.dumps({"model": a.model, "seqs": S, "ctx": a.ctx, "graph": not a.eager, "ms_per_step": round(ms, 3),
                       "tokens_per_s": round(S / ms * 1e3, 1), "hbm_floor_ms": round(floor_ms, 3),
                       "fraction_of_hbm_roofline": round(floor_ms / ms, 3),
-                      "group": a.group, "shared_ctx": a.shared_ctx if a.group > 1 else 0, "clocks": clocks}))
+                      "group": a.group, "shared_ctx": a.shared_ctx if a.group > 1 else 0,
+                      "grouped_kernel": bool(a.group > 1 and eng.grouped_decode and not a.no_grouped_kernel), "clocks": clocks}))
 
 
 if __name__ == "__main__":

@@ -27,6 +27,7 @@ max_num_seqs / max_num_batched_tokens, dummy-weight start, KV release/resume, ab
 from __future__ import annotations
 
 import math
+import os
 import time
 import zlib
 from collections import OrderedDict, deque
@@ -281,6 +282,72 @@ class RolloutEngine:
         self.temperature = 1.0
         self.top_k, self.top_p = -1, 1.0
         self.free_slots = list(range(S - 1, -1, -1))
+        # grouped decode attention: the samples of a prompt share its full pages; a group kernel reads them once per group
+        # (``ops.paged_decode_grouped``). Host mirror: group id -> member slots, slot -> group id.
+        nh_l = self.cfg.num_attention_heads // self.tp_size
+        nkv_l = self.cfg.num_key_value_heads // self.tp_size
+        self.grouped_decode = (self.is_cuda and self.share_prefill and self.bs == 64 and self.cfg.head_dim in (64, 128)
+                               and nh_l // max(1, nkv_l) <= 16 and os.environ.get("VERL_B200_GROUPED_DECODE", "1") != "0")
+        self._groups: dict[int, list[int]] = {}
+        self._slot_group: dict[int, int] = {}
+        self._free_gids = list(range(S - 1, -1, -1))
+        if self.grouped_decode:
+            self.grp_members = torch.full((S, 8), -1, dtype=torch.int32, device=dev)
+            self.grp_pages = torch.zeros(S, dtype=torch.int32, device=dev)
+            self.seq_skip = torch.zeros(S, dtype=torch.int32, device=dev)
+            self.pd_splits = (2, 1 if S * nkv_l >= 296 else min(8, -(-296 // (S * nkv_l))))
+            self.pd_ws = torch.empty(S * nh_l * sum(self.pd_splits) * (self.cfg.head_dim + 2), dtype=torch.float32, device=dev)
+
+    # ------------------------------------------------------------------------------------ decode groups
+    def _form_groups(self, reqs: list, leaders: list[int], lead_idx: list[int], lens: list[int]) -> None:
+        """After a prefill wave: the requests that share a leader's prompt pages become decode groups of up to 8 members."""
+        if not self.grouped_decode:
+            return
+        by_leader: dict[int, list[int]] = {}
+        for i, r in enumerate(reqs):
+            by_leader.setdefault(lead_idx[i], []).append(i)
+        for j, idxs in by_leader.items():
+            nfull = lens[leaders[j]] // self.bs
+            if len(idxs) < 2 or nfull == 0:
+                continue
+            for c0 in range(0, len(idxs), 8):
+                part = idxs[c0 : c0 + 8]
+                if len(part) < 2 or not self._free_gids:
+                    continue
+                gid = self._free_gids.pop()
+                slots = [reqs[i].slot for i in part]
+                self._groups[gid] = slots
+                for sl in slots:
+                    self._slot_group[sl] = gid
+                self._write_group(gid, nfull)
+
+    def _write_group(self, gid: int, pages: Optional[int] = None) -> None:
+        slots = self._groups.get(gid, [])
+        row = torch.full((8,), -1, dtype=torch.int32)
+        row[: len(slots)] = torch.tensor(slots, dtype=torch.int32)
+        self.grp_members[gid] = row.to(self.device)
+        if pages is not None:
+            self.grp_pages[gid] = pages
+            self.seq_skip[torch.tensor(slots, dtype=torch.int64, device=self.device)] = pages
+
+    def _leave_group(self, slot: int) -> None:
+        """A sequence's slot is released: it leaves its group; a group of one is dissolved (nothing left to share)."""
+        gid = self._slot_group.pop(slot, None)
+        if gid is None:
+            return
+        self.seq_skip[slot] = 0
+        members = self._groups[gid]
+        members.remove(slot)
+        if len(members) < 2:
+            for sl in members:
+                self._slot_group.pop(sl, None)
+                self.seq_skip[sl] = 0
+            self._groups.pop(gid)
+            self.grp_pages[gid] = 0
+            self.grp_members[gid] = -1
+            self._free_gids.append(gid)
+        else:
+            self._write_group(gid)
 
     def _ensure_out(self, cap: int) -> None:
         if cap > self.out_cap:
@@ -392,6 +459,7 @@ class RolloutEngine:
             idx = torch.tensor([r.slot for r in reqs], dtype=torch.int64, device=self.device)
             for r in reqs:
                 self.running.pop(r.slot)
+                self._leave_group(r.slot)
                 self._release_blocks(r.blocks)
                 self.free_slots.append(r.slot)
             self.active[idx] = False
@@ -572,6 +640,8 @@ class RolloutEngine:
             self.seen[slots, tok] = True
         n = torch.tensor(lens, dtype=torch.int32, device=dev)
         self.block_table[slots] = bt_rows.to(dev)
+        if len(leaders) < len(reqs):
+            self._form_groups(reqs, leaders, lead_idx, lens)
         self.tok[slots] = tok
         self.pos[slots] = n
         self.ctx[slots] = n + 1
@@ -618,6 +688,7 @@ class RolloutEngine:
         a = F.embedding(self.tok, P["embed_tokens.weight"])
         r = None
         cos, sin = self.model._cos, self.model._sin
+        pd_groups = (self.grp_members, self.grp_pages, self.seq_skip, self.pd_ws, *self.pd_splits) if self.grouped_decode else None
         if self.record_routing:
             from ....models.decoder import RouterReplay
 
@@ -641,7 +712,7 @@ class RolloutEngine:
             F.apply_rope_(q, self.pos, cos, sin)
             F.apply_rope_(k, self.pos, cos, sin)
             F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
-            attn = F.paged_decode_attention(q, self.kv[i, 0], self.kv[i, 1], self.block_table, ctx_eff)
+            attn = F.paged_decode_attention(q, self.kv[i, 0], self.kv[i, 1], self.block_table, ctx_eff, groups=pd_groups)
             if tp is not None:
                 o = tp.row_linear(attn.reshape(S, Q), W["self_attn.o_proj.weight"][:, tp.rows(cfg.q_size)], None)
             else:
@@ -751,6 +822,7 @@ class RolloutEngine:
                 # the next turn of a conversation starts with this prompt + response: every generated token but the last
                 # has gone through the model, its keys / values are in the pages
                 self._index_pages(r.prompt + t[:-1], r.blocks, len(r.prompt) + n - 1)
+            self._leave_group(s)
             self._release_blocks(r.blocks)
             self.free_slots.append(s)
         self.active[idx] = False
