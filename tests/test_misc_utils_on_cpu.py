@@ -306,3 +306,49 @@ def test_platform_registry_and_out_of_tree_platform(monkeypatch):
         set_platform(None)
     with pytest.raises(TypeError):
         PlatformBase()  # abstract
+
+
+def test_tqbridge_swaps_handles_for_batches_and_writes_results_back():
+    import asyncio
+
+    from verl_b200.utils.tensordict_lite import TensorDict
+    from verl_b200.utils.transfer_queue import KVBatchMeta, TransferQueue, tqbridge
+
+    q = TransferQueue()
+    for i in range(4):
+        q.put(f"k{i}", {"x": torch.full((3,), float(i)), "name": f"row{i}"}, tags={"v": 0})
+
+    class Worker:
+        collects = True
+
+        def query_collect_info(self, mesh):
+            return self.collects
+
+        @tqbridge(queue=q)
+        def double(self, batch):
+            assert batch.batch_size[0] == 4 and list(batch["name"]) == ["row0", "row1", "row2", "row3"]
+            return TensorDict({"y": batch["x"] * 2}, batch_size=(4,))
+
+        @tqbridge(dispatch_mode={"mesh_name": "actor"}, queue=q)
+        def triple(self, batch):
+            return TensorDict({"z": batch["x"] * 3}, batch_size=(len(batch["x"]),))
+
+        @tqbridge(queue=q)
+        async def norm(self, batch, scale=1.0):
+            return float(batch["x"].sum()) * scale
+
+    w = Worker()
+    meta = q.get_meta(["k0", "k1", "k2", "k3"], fields=["x", "name"])
+    out = w.double(meta)
+    assert isinstance(out, KVBatchMeta) and out.keys == meta.keys and out.fields == ["name", "x", "y"]
+    assert torch.equal(q.get(["k2"])[0]["y"], torch.full((3,), 4.0))
+    # plain batches pass through untouched
+    plain = w.double.__wrapped__(w, TensorDict({"x": torch.ones(4, 3), "name": ["row0", "row1", "row2", "row3"]}, batch_size=(4,)))
+    assert torch.equal(plain["y"], torch.full((4, 3), 2.0))
+    # only the collecting worker of a replica writes back
+    w.collects = False
+    assert len(w.triple(meta)) == 0 and "z" not in q.get(["k0"])[0]
+    w.collects = True
+    assert len(w.triple(meta)) == 4 and torch.equal(q.get(["k3"])[0]["z"], torch.full((3,), 9.0))
+    # coroutine functions, and outputs that are not row batches are returned as they are
+    assert asyncio.run(w.norm(meta, scale=2.0)) == pytest.approx(2.0 * 3 * (0 + 1 + 2 + 3))

@@ -15,7 +15,7 @@ import threading
 from dataclasses import dataclass, field
 from typing import Any, Callable, Iterable, Optional
 
-__all__ = ["KVBatchMeta", "TransferQueue", "get_default_queue"]
+__all__ = ["KVBatchMeta", "TransferQueue", "get_default_queue", "tqbridge"]
 
 
 @dataclass
@@ -119,3 +119,99 @@ def get_default_queue() -> TransferQueue:
     if _default is None:
         _default = TransferQueue()
     return _default
+
+
+# ----------------------------------------------------------------------------------------------- tqbridge
+def _is_collecting_worker(dispatch_mode, args) -> bool:
+    """Whether the worker that runs the decorated method is the one whose output is kept: with an nd-mesh dispatch only the
+    collecting rank of each data-parallel group writes back, so the rows of a replica are not stored several times."""
+    if dispatch_mode is None or not args:
+        return True
+    worker = args[0]
+    mesh = dispatch_mode.get("mesh_name") if isinstance(dispatch_mode, dict) else None
+    query = getattr(worker, "query_collect_info", None)
+    if mesh is None or query is None:
+        return True
+    try:
+        return bool(query(mesh))
+    except Exception:
+        return True
+
+
+def _rows_to_batch(rows: list[dict], meta: "KVBatchMeta"):
+    """Per-key field dictionaries -> one batch-first tensor dictionary (tensors stacked, the rest as object arrays)."""
+    import numpy as np
+    import torch
+
+    from .tensordict_lite import TensorDict
+
+    if not rows:
+        return TensorDict({}, batch_size=(0,))
+    out = {}
+    for f in rows[0]:
+        vals = [r[f] for r in rows]
+        if all(isinstance(v, torch.Tensor) for v in vals) and len({tuple(v.shape) for v in vals}) == 1:
+            out[f] = torch.stack(vals)
+        else:
+            out[f] = np.array(vals, dtype=object)
+    return TensorDict(out, batch_size=(len(rows),))
+
+
+def tqbridge(dispatch_mode=None, queue: Optional["TransferQueue"] = None, put_data: bool = True):
+    """Decorator that lets a method written for real batches be called with a :class:`KVBatchMeta` handle instead.
+
+    Every ``KVBatchMeta`` among the arguments is replaced by the batch it names (a batch-first tensor dictionary fetched
+    from the queue); the method runs; if it returns a tensor dictionary with one row per key, its fields are written back
+    under the same keys and the *handle* is returned (with the new field names added), so the data never travels through
+    the controller. Calls without a handle go straight through. Coroutine functions are supported. With ``dispatch_mode``
+    only the collecting worker of a data-parallel group writes back (the others return an empty handle).
+
+    Parity target: ``verl/utils/transferqueue_utils.py:347-470``."""
+    import asyncio
+    import functools
+
+    def find(args, kwargs):
+        for v in list(args) + list(kwargs.values()):
+            if isinstance(v, KVBatchMeta):
+                return v
+        return None
+
+    def decorator(func):
+        def before(args, kwargs):
+            q = queue or get_default_queue()
+            meta = find(args, kwargs)
+            conv = lambda v: _rows_to_batch(q.get_data(v), v) if isinstance(v, KVBatchMeta) else v
+            return q, meta, [conv(a) for a in args], {k: conv(v) for k, v in kwargs.items()}
+
+        def after(q, meta, args, output):
+            from .tensordict_lite import TensorDict
+
+            rows = isinstance(output, TensorDict) and len(output.batch_size) > 0 and output.batch_size[0] == len(meta)
+            if not (put_data and rows):
+                return output
+            if not _is_collecting_worker(dispatch_mode, args):
+                return KVBatchMeta([], meta.partition_id, meta.fields, [])
+            names = list(output.keys())
+            for i, key in enumerate(meta.keys):
+                q.put(key, {f: output[f][i] for f in names}, partition_id=meta.partition_id)
+            fields = None if meta.fields is None else sorted(set(meta.fields) | set(names))
+            return KVBatchMeta(list(meta.keys), meta.partition_id, fields, list(meta.tags))
+
+        if asyncio.iscoroutinefunction(func):
+            @functools.wraps(func)
+            async def inner(*args, **kwargs):
+                if find(args, kwargs) is None:
+                    return await func(*args, **kwargs)
+                q, meta, a2, k2 = before(args, kwargs)
+                return after(q, meta, a2, await func(*a2, **k2))
+        else:
+            @functools.wraps(func)
+            def inner(*args, **kwargs):
+                if find(args, kwargs) is None:
+                    return func(*args, **kwargs)
+                q, meta, a2, k2 = before(args, kwargs)
+                return after(q, meta, a2, func(*a2, **k2))
+
+        return inner
+
+    return decorator
