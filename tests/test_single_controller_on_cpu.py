@@ -96,3 +96,48 @@ def test_multiprocess_group_gloo_and_failure_detection():
     finally:
         wg.shutdown()
     assert not any(p.is_alive() for p in wg._procs)
+
+
+class _Adder(Worker):
+    def __init__(self, bias):
+        super().__init__()
+        self.bias = bias
+        self._register_dispatch_collect_info("adder", dp_rank=self.rank, is_collect=True)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def add(self, x):
+        return x + self.bias + 100 * self.rank
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn(mesh_name="adder"))
+    def add_rows(self, data):
+        return DataProto.from_dict(tensors={"y": data.batch["x"] + self.bias})
+
+
+class _Scaler(Worker):
+    def __init__(self, factor):
+        super().__init__()
+        self.factor = factor
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def scale(self, x):
+        # the roles of a fused worker see each other
+        return x * self.factor + self.fused_worker_dict["adder"].bias
+
+
+@pytest.mark.parametrize("backend", ["inprocess", "multiprocess"])
+def test_fused_worker_roles_share_processes(backend):
+    from verl_b200.single_controller.base.fused import create_colocated_worker_cls_fused
+    from verl_b200.single_controller.local import InProcessWorkerGroup, MultiprocessWorkerGroup
+
+    cia = create_colocated_worker_cls_fused({"adder": ClassWithInitArgs(_Adder, bias=7), "scaler": ClassWithInitArgs(_Scaler, factor=3)})
+    assert cia.cls.__name__ == "FusedWorker_adder_scaler" and cia.cls.is_fused_worker
+    wg = (InProcessWorkerGroup if backend == "inprocess" else MultiprocessWorkerGroup)(2, cia)
+    views = wg.spawn_fused({"adder", "scaler"})
+    assert views["adder"].add(1) == [8, 108] and views["scaler"].scale(2) == [13, 13]
+    assert not hasattr(views["adder"], "scale") and views["adder"].world_size == 2
+    out = views["adder"].add_rows(DataProto.from_dict(tensors={"x": torch.arange(4.0)}))   # nd-mesh dispatch through the view
+    assert torch.equal(out.batch["y"], torch.arange(4.0) + 7)
+    wg.fuse({"adder", "scaler"})
+    assert wg.adder.add(0) == [7, 107] and wg.scaler.scale(1) == [10, 10]
+    if hasattr(wg, "shutdown"):
+        wg.shutdown()

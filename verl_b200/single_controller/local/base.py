@@ -71,6 +71,17 @@ class _LocalGroupBase(WorkerGroup):
     def execute_rank_zero_sync(self, method_name: str, *args, **kwargs):
         return _resolve(self.execute_rank_zero_async(method_name, *args, **kwargs))
 
+    # -- several roles in one process (``base/fused.py``)
+    def spawn_fused(self, prefix_set) -> dict:
+        from ..base.fused import spawn_fused
+
+        return spawn_fused(self, prefix_set, func_generator)
+
+    def fuse(self, prefix_set):
+        from ..base.fused import fuse
+
+        return fuse(self, prefix_set, func_generator)
+
     @staticmethod
     def _slice_args(i: int, n: int, args, kwargs):
         """Per-worker arguments: lists of length n are split, everything else is broadcast."""

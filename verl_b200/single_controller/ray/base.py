@@ -18,7 +18,7 @@ from typing import Any, Optional
 from ..base.decorator import MAGIC_ATTR, Execute, get_predefined_dispatch_fn, get_predefined_execute_fn
 from ..base.worker_group import ClassWithInitArgs, ResourcePool, WorkerGroup
 
-__all__ = ["RayResourcePool", "RayClassWithInitArgs", "RayWorkerGroup", "create_colocated_worker_cls"]
+__all__ = ["RayResourcePool", "RayClassWithInitArgs", "RayWorkerGroup", "create_colocated_worker_cls", "create_colocated_worker_cls_fused"]
 
 
 def _ray():
@@ -191,6 +191,19 @@ class RayWorkerGroup(WorkerGroup):
     @property
     def worker_names(self) -> list[str]:
         return self._worker_names
+
+
+def create_colocated_worker_cls_fused(class_dict: dict[str, RayClassWithInitArgs]):
+    """Fused form of ``create_colocated_worker_cls``: the roles keep their own method names and are addressed through
+    per-role views (``RayWorkerGroup.spawn_fused`` / ``fuse``); the generated worker class comes from ``base/fused.py``."""
+    from ..base.fused import _build_fused_cls
+
+    import ray
+
+    cia = RayClassWithInitArgs(cls=ray.remote(_build_fused_cls(class_dict)))
+    cia.fused_worker_used = True
+    cia.raw_cls_dict = {name: c.cls for name, c in class_dict.items()}
+    return cia
 
 
 def create_colocated_worker_cls(class_dict: dict[str, RayClassWithInitArgs]):
