@@ -283,11 +283,14 @@ class RolloutEngine:
         self.top_k, self.top_p = -1, 1.0
         self.free_slots = list(range(S - 1, -1, -1))
         # grouped decode attention: the samples of a prompt share its full pages; a group kernel reads them once per group
-        # (``ops.paged_decode_grouped``). Host mirror: group id -> member slots, slot -> group id.
+        # (``ops.paged_decode_grouped``). Host mirror: group id -> member slots, slot -> group id. Off by default: measured at
+        # 320 sequences x 2048 tokens of context in groups of 5, the per-sequence kernel already finds the shared pages in L2
+        # (12.5 ms per decode step) and the group kernel, whose warps walk a page's 64 tokens one after the other, does not
+        # beat that (12.9 ms); VERL_B200_GROUPED_DECODE=1 turns it on.
         nh_l = self.cfg.num_attention_heads // self.tp_size
         nkv_l = self.cfg.num_key_value_heads // self.tp_size
         self.grouped_decode = (self.is_cuda and self.share_prefill and self.bs == 64 and self.cfg.head_dim in (64, 128)
-                               and nh_l // max(1, nkv_l) <= 16 and os.environ.get("VERL_B200_GROUPED_DECODE", "1") != "0")
+                               and nh_l // max(1, nkv_l) <= 16 and os.environ.get("VERL_B200_GROUPED_DECODE", "0") == "1")
         self._groups: dict[int, list[int]] = {}
         self._slot_group: dict[int, int] = {}
         self._free_gids = list(range(S - 1, -1, -1))
