@@ -508,6 +508,50 @@ def test_rollout_engine_cuda_graph_matches_eager(ops):
     assert outs[True] == outs[False] and all(len(t) == 9 for t in outs[True])
 
 
+def test_rollout_engine_grouped_decode_follows_its_groups(ops, monkeypatch):
+    """The samples of a prompt decode as a group (shared prompt pages read once by the group kernel); groups shrink and
+    dissolve as members finish at different lengths. Same log-probs as the per-sequence kernel, and the token sequences
+    agree except where bf16 attention outputs tip a near-tie."""
+    from verl_b200.models import FlatParams, ModelConfig
+    from verl_b200.workers.rollout.native.engine import RolloutEngine, SamplingParams
+
+    cfg = ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, eos_token_id=-1, pad_token_id=0)
+    P = FlatParams(cfg, dtype=torch.bfloat16, device=DEV)
+    P.init_weights(seed=0, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    base = [torch.randint(3, 2048, (n,), generator=g).tolist() for n in (150, 70, 200)]   # 2, 1 and 3 full pages of 64
+    prompts, params = [], []
+    for i, p in enumerate(base):
+        for j in range(4):                                                               # 4 samples per prompt, unequal lengths
+            prompts.append(p)
+            params.append(SamplingParams(temperature=1.0, max_tokens=6 + 5 * j + i, seed=100 * i + j, logprobs=True))
+    prompts.append([9, 8, 7])                                                            # a request of its own
+    params.append(SamplingParams(temperature=1.0, max_tokens=12, seed=999, logprobs=True))
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("VERL_B200_GROUPED_DECODE", flag)
+        eng = RolloutEngine(cfg, P, max_num_seqs=16, max_model_len=320, block_size=64, num_blocks=80, sync_interval=4, eos_token_id=-1)
+        assert eng.grouped_decode == (flag == "1")
+        for p, sp in zip(prompts, params):
+            eng.add_request(p, sp)
+        res = []
+        while len(res) < len(prompts):
+            res += eng.step()
+        outs[flag] = {o.request_id: o for o in res}
+        if flag == "1":
+            assert not eng._groups and not eng._slot_group and int(eng.grp_pages.sum()) == 0 and int(eng.seq_skip.sum()) == 0
+    same = 0
+    for rid, a in outs["1"].items():
+        b = outs["0"][rid]
+        assert len(a.token_ids) == len(b.token_ids)
+        n = next((i for i, (x, y) in enumerate(zip(a.token_ids, b.token_ids)) if x != y), len(a.token_ids))
+        same += n == len(a.token_ids)
+        assert max(abs(x - y) for x, y in zip(a.log_probs[: max(n, 1)], b.log_probs[: max(n, 1)])) < 5e-2
+    assert same >= len(prompts) - 2
+    assert int(ops.gemm_status()) == 0
+
+
 def test_nvfp4_fake_quant_matches_reference():
     """NVFP4 fake-quantisation kernel against the plain PyTorch formulation of the same op (fp32 math)."""
     from verl_b200.utils.qat import nvfp4_fake_quantize, nvfp4_global_scale
