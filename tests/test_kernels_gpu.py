@@ -211,6 +211,40 @@ def test_grouped_prefix_paged_decode_matches_reference(ops, nh, nkv, hd):
     assert int(ops.gemm_status()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64)])
+def test_fused_rope_kv_append_matches_the_separate_ops(ops, nh, nkv, hd):
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(5)
+    T, nb, bs = 37, 8, 64
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd).bfloat16().to(DEV)
+    pos = torch.randint(0, 500, (T,), dtype=torch.int32, device=DEV)
+    inv = 1.0 / (1e4 ** (torch.arange(0, hd, 2).float() / hd))
+    ang = torch.arange(512).float()[:, None] * inv[None]
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    slots = torch.randperm(nb * bs)[:T].to(DEV)
+    slots[3] = -1                                                     # an inactive sequence: q is rotated, nothing is appended
+    kc, vc = (torch.zeros(nb, bs, nkv, hd, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    fused = qkv.clone()
+    F.rope_kv_append_(fused, pos, cos, sin, slots, kc, vc, nh, nkv, hd)
+    ref = qkv.clone()
+    q = ref[:, : nh * hd].view(T, nh, hd)
+    k = ref[:, nh * hd : (nh + nkv) * hd].view(T, nkv, hd)
+    v = ref[:, (nh + nkv) * hd :].view(T, nkv, hd)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    F.apply_rope_(q, pos, cos, sin)
+    F.apply_rope_(k, pos, cos, sin)
+    F.kv_append_(k, v, slots, kc2, vc2)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, ref) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    # and against fp32 math on the host
+    half = hd // 2
+    x = qkv.float().cpu()[:, : nh * hd].view(T, nh, hd)
+    c, s_ = cos.cpu()[pos.cpu().long()][:, None], sin.cpu()[pos.cpu().long()][:, None]
+    want = torch.cat([x[..., :half] * c - x[..., half:] * s_, x[..., half:] * c + x[..., :half] * s_], -1)
+    assert rel(fused[:, : nh * hd].view(T, nh, hd), want) < 1e-2
+
+
 def _attn_reference(q, k, v, lens, scale):
     """fp32 causal GQA attention per sequence with autograd."""
     outs, off = [], 0

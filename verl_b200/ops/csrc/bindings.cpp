@@ -228,6 +228,22 @@ void rope_(Tensor x, const Tensor& pos, const Tensor& cos_t, const Tensor& sin_t
   CHECK_RC(rc, "vb_rope");
 }
 
+// qkv bf16 [T, (nh + 2 nkv) * hd] (projection output, row-contiguous); caches [num_blocks, block_size, nkv, hd]; slot int64 [T]
+void rope_kv_append_(Tensor qkv, const Tensor& pos, const Tensor& cos_t, const Tensor& sin_t, const Tensor& slot, Tensor kc, Tensor vc,
+                     int64_t nh, int64_t nkv, int64_t hd) {
+  CHECK_BF16(qkv);
+  CHECK_F32(cos_t);
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (nh + 2 * nkv) * hd, "rope_kv_append: qkv [T, (nh + 2 nkv) * hd]");
+  TORCH_CHECK(pos.scalar_type() == at::kInt && pos.is_contiguous() && slot.scalar_type() == at::kLong && slot.is_contiguous());
+  TORCH_CHECK(kc.is_contiguous() && vc.is_contiguous() && kc.dim() == 4 && kc.size(2) == nkv && kc.size(3) == hd);
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  count(1);
+  CHECK_RC(vb_rope_kv_append(qkv.data_ptr(), qkv.stride(0), pos.data_ptr<int>(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                             reinterpret_cast<long long*>(slot.data_ptr()), kc.data_ptr(), vc.data_ptr(), (int)qkv.size(0), (int)nh,
+                             (int)nkv, (int)hd, cur_stream()),
+           "vb_rope_kv_append");
+}
+
 Tensor swiglu_fwd(const Tensor& gu) {
   CHECK_BF16(gu);
   TORCH_CHECK(gu.is_contiguous() && gu.dim() == 2);
@@ -882,6 +898,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("kv_append_", &kv_append_);
   m.def("paged_decode", &paged_decode);
   m.def("paged_decode_grouped", &paged_decode_grouped);
+  m.def("rope_kv_append_", &rope_kv_append_);
   m.def("sample", &sample);
   m.def("sample_topkp", &sample_topkp);
   m.def("grpo_advantage", &grpo_advantage);

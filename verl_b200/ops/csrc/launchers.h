@@ -64,6 +64,8 @@ int vb_paged_decode_grouped(const void* q, long long ldq, const void* kc, const 
                             int max_blocks, const int* ctx_len, const int* members, const int* grp_pages, const int* skip, int NG,
                             void* out, long long ldo, int B, int nh, int nkv, int hd, int block_size, float scale, int psplit,
                             int nsplit, float* part_o, float* part_ml, cudaStream_t stream);
+int vb_rope_kv_append(void* qkv, long long ld, const int* pos, const float* cos_t, const float* sin_t, const long long* slot,
+                      void* kc, void* vc, int T, int nh, int nkv, int hd, cudaStream_t s);
 int vb_sample(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, const long long* seeds,
               long long step, long long* tokens, float* logprobs, cudaStream_t s);
 int vb_sample_topkp(const void* logits, long long ld, int B, int V, int valid_vocab, float inv_temp, int top_k, float top_p,

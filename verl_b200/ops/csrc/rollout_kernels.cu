@@ -38,6 +38,44 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
   }
 }
 
+// Decode step, one launch per layer instead of three: rotary embedding of q (in place), rotary embedding of k, and the
+// append of the rotated k and of v to the paged cache. qkv is the projection output [T, (nh + 2 nkv) * hd] (row stride ld):
+// q heads first, then k heads, then v heads. One block per token; threads cover the rotary pairs of all q and k heads and
+// the 16-byte pieces of v. A token whose slot is negative (an inactive sequence) only gets its q rotated.
+__global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, const int* __restrict__ pos,
+                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                      const long long* __restrict__ slot, __nv_bfloat16* __restrict__ kc,
+                                      __nv_bfloat16* __restrict__ vc, int nh, int nkv, int hd) {
+  const long long t = blockIdx.x;
+  const int half = hd >> 1, pairs = half >> 1;  // two rotary pairs per thread
+  const int p = pos[t];
+  const long long s = slot[t];
+  __nv_bfloat16* row = qkv + t * ld;
+  const int rot_heads = nh + nkv;
+  for (int idx = threadIdx.x; idx < rot_heads * pairs; idx += blockDim.x) {
+    const int h = idx / pairs, i = (idx - h * pairs) * 2;
+    __nv_bfloat16* base = row + static_cast<long long>(h) * hd;
+    const float2 c = *reinterpret_cast<const float2*>(cos_t + static_cast<long long>(p) * half + i);
+    const float2 sn = *reinterpret_cast<const float2*>(sin_t + static_cast<long long>(p) * half + i);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + i));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + half + i));
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+    *reinterpret_cast<__nv_bfloat162*>(base + i) = lo;
+    *reinterpret_cast<__nv_bfloat162*>(base + half + i) = hi;
+    if (h >= nh && s >= 0) {  // a key head: the rotated values also go to the cache
+      __nv_bfloat16* kd = kc + s * static_cast<long long>(nkv) * hd + static_cast<long long>(h - nh) * hd;
+      *reinterpret_cast<__nv_bfloat162*>(kd + i) = lo;
+      *reinterpret_cast<__nv_bfloat162*>(kd + half + i) = hi;
+    }
+  }
+  if (s >= 0) {
+    const uint4* vs = reinterpret_cast<const uint4*>(row + static_cast<long long>(nh + nkv) * hd);
+    uint4* vd = reinterpret_cast<uint4*>(vc + s * static_cast<long long>(nkv) * hd);
+    for (int i = threadIdx.x; i < (nkv * hd) >> 3; i += blockDim.x) vd[i] = vs[i];
+  }
+}
+
 // ------------------------------------------------------------------------------------------ decode attention
 // q: [B, nh, hd] (row stride ldq); cache: [num_slots, nkv, hd]; block_table: [B, max_blocks]; ctx_len: [B].
 // grid = (B, nkv); 4 warps; each warp walks 32-token tiles: the score phase is lane-per-token (no shuffles
@@ -467,6 +505,16 @@ int vb_kv_append(const void* k, const void* v, long long ldk, long long ldv, con
   kv_append_kernel<<<T, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(k), reinterpret_cast<const __nv_bfloat16*>(v),
                                      ldk, ldv, slot, reinterpret_cast<__nv_bfloat16*>(kc),
                                      reinterpret_cast<__nv_bfloat16*>(vc), nkv * hd);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int vb_rope_kv_append(void* qkv, long long ld, const int* pos, const float* cos_t, const float* sin_t, const long long* slot,
+                      void* kc, void* vc, int T, int nh, int nkv, int hd, cudaStream_t s) {
+  if (T == 0) return 0;
+  if ((hd % 8) || (ld % 8) || ((nkv * hd) % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(vc)) & 15) return -2;
+  rope_kv_append_kernel<<<T, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(qkv), ld, pos, cos_t, sin_t, slot,
+                                          reinterpret_cast<__nv_bfloat16*>(kc), reinterpret_cast<__nv_bfloat16*>(vc), nh, nkv, hd);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -501,6 +501,23 @@ def kv_append_(k, v, slots, k_cache, v_cache) -> None:
     vc[slots[ok]] = v[ok]
 
 
+def rope_kv_append_(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, slots: torch.Tensor,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, nh: int, nkv: int, hd: int) -> None:
+    """Decode-step fusion: rotate the q and k heads of ``qkv`` [T, (nh + 2 nkv) * hd] in place and append the rotated k
+    and v rows to the paged caches at ``slots`` (negative: skip the append). One kernel on a GPU; the same three steps
+    through the separate ops elsewhere."""
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16:
+        _ops().rope_kv_append_(qkv, pos, cos, sin, slots, k_cache, v_cache, int(nh), int(nkv), int(hd))
+        return
+    T = qkv.shape[0]
+    q = qkv[:, : nh * hd].view(T, nh, hd)
+    k = qkv[:, nh * hd : (nh + nkv) * hd].view(T, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd :].view(T, nkv, hd)
+    apply_rope_(q, pos, cos, sin)
+    apply_rope_(k, pos, cos, sin)
+    kv_append_(k, v, slots, k_cache, v_cache)
+
+
 def paged_decode_attention(q, k_cache, v_cache, block_table, ctx_len, scale: Optional[float] = None, groups=None):
     """One query token per sequence against a paged cache [num_blocks, block_size, nkv, hd].
 

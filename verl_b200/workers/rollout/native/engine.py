@@ -712,9 +712,12 @@ class RolloutEngine:
                 kn = F.rms_norm(k.reshape(S * nkv, hd).contiguous(), W["self_attn.k_norm.weight"], cfg.rms_norm_eps)[0]
                 q.copy_(qn.view(S, nh, hd))
                 k.copy_(kn.view(S, nkv, hd))
-            F.apply_rope_(q, self.pos, cos, sin)
-            F.apply_rope_(k, self.pos, cos, sin)
-            F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
+            if cfg.qk_norm or not qkv.is_contiguous():
+                F.apply_rope_(q, self.pos, cos, sin)
+                F.apply_rope_(k, self.pos, cos, sin)
+                F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
+            else:  # one launch: rotate q and k in the projection output, append k and v to the cache
+                F.rope_kv_append_(qkv, self.pos, cos, sin, slot_map, self.kv[i, 0], self.kv[i, 1], nh, nkv, hd)
             attn = F.paged_decode_attention(q, self.kv[i, 0], self.kv[i, 1], self.block_table, ctx_eff, groups=pd_groups)
             if tp is not None:
                 o = tp.row_linear(attn.reshape(S, Q), W["self_attn.o_proj.weight"][:, tp.rows(cfg.q_size)], None)
