@@ -53,6 +53,31 @@ def test_gemm_bias_fp32_accumulate(ops):
     assert rel(out, ref) < 1e-5
 
 
+@pytest.mark.parametrize("shape", [(320, 3584, 18944), (320, 4608, 3584), (77, 264, 4096), (130, 1024, 8192)])
+def test_gemm_k_split_folds_inside_the_kernel(ops, shape):
+    """Skinny GEMMs run K-split; the split that finishes a slab last folds the partial sums, adds the bias and writes the
+    output in the same kernel. Several launches in a row: the slab counters return to zero by themselves."""
+    M, N, K = shape
+    assert int(ops.gemm_suggest_splits(M, N, K)) > 1
+    torch.manual_seed(2)
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    ref = A.float() @ B.float().t()
+    n0 = int(ops.launch_count())
+    for _ in range(3):
+        d = ops.gemm(A, B, bias, None, False, False, False, False, 0)
+        assert rel(d, ref + bias.float()) < 1e-2
+    assert int(ops.launch_count()) - n0 == 3                     # one launch per GEMM: no separate reduce kernel
+    out = torch.randn(M, N, device=DEV)
+    want = out + ref
+    ops.gemm(A, B, None, out, False, False, True, True, 0)        # fp32 output, accumulate
+    assert rel(out, want) < 1e-4
+    d2 = ops.gemm(A, B.t().contiguous(), None, None, False, True, False, False, 0)   # B stored [K, N]
+    assert rel(d2, ref) < 1e-2
+    assert int(ops.gemm_status()) == 0
+
+
 def test_rmsnorm_fwd_bwd(ops):
     from verl_b200.ops import functional as F
 

@@ -89,7 +89,18 @@ struct GemmParams {
   int fetch_c0, fetch_c1;
   unsigned int* fetch_panel;   // [ceil(N / BN)] zero at launch; null: B is local already, nothing waits
   unsigned long long fetch_limit_ns;
+  // K-split with the fold inside the kernel: every split writes its fp32 partial slab to the workspace (D above) and
+  // counts itself on the slab's counter; the split that arrives last sums all partials of the slab, adds the bias and
+  // writes the real output. Counters return to zero, so they never need clearing between launches.
+  unsigned int* fix_counter;   // [num output tiles * 4] or null (partials stay in the workspace for a later kernel)
+  void* fix_out;
+  long long fix_ldd;
+  const __nv_bfloat16* fix_bias;
+  int fix_out_f32, fix_accumulate;
 };
+
+constexpr int FIX_COUNTERS = 16384;
+__device__ unsigned int g_fix_counters[FIX_COUNTERS];
 
 constexpr int FETCH_CHUNK = 16384;  // bytes per copy job of a fetch warp
 constexpr int FETCH_WARPS = 4;      // copy warps per CTA (warps 6..9): peer loads are latency-bound, bytes in flight = rate
@@ -541,6 +552,57 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         acc = 0;
         acc_phase ^= 1;
       }
+      if constexpr (EPI == EPI_STORE) {
+        if (p.fix_counter != nullptr && splits > 1) {
+          __threadfence();  // this warp's slab of its split is in the workspace before it counts itself
+          __syncwarp();
+          const int slab = (t % num_mn) * 4 + q;
+          unsigned int before = 0;
+          if (lane == 0) before = atomicAdd(p.fix_counter + slab, 1u);
+          before = __shfl_sync(0xffffffffu, before, 0);
+          if (before == static_cast<unsigned int>(splits - 1)) {
+            if (lane == 0) p.fix_counter[slab] = 0;
+            __threadfence();
+            // rows one after the other, lanes across the columns: coalesced reads of every split's row
+            const int colw = n0 + lane * 8;
+            if (lane * 8 < BN && colw < p.N) {
+              float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (p.fix_bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) b8[j] = __bfloat162float(p.fix_bias[colw + j]);
+              }
+              for (int rr = 0; rr < 32; ++rr) {
+                const int rw = m0 + q * 32 + rr;
+                if (rw >= p.M) break;
+                float a8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a8[j] = b8[j];
+                const float* ws = reinterpret_cast<const float*>(p.D) + static_cast<long long>(rw) * p.ldd + colw;
+                for (int sp = 0; sp < splits; ++sp) {
+                  const float4 v0 = *reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * p.M * p.ldd);
+                  const float4 v1 = *reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * p.M * p.ldd + 4);
+                  a8[0] += v0.x; a8[1] += v0.y; a8[2] += v0.z; a8[3] += v0.w;
+                  a8[4] += v1.x; a8[5] += v1.y; a8[6] += v1.z; a8[7] += v1.w;
+                }
+                if (p.fix_out_f32) {
+                  float* o = reinterpret_cast<float*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw;
+                  if (p.fix_accumulate) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a8[j] += o[j];
+                  }
+                  *reinterpret_cast<float4*>(o) = make_float4(a8[0], a8[1], a8[2], a8[3]);
+                  *reinterpret_cast<float4*>(o + 4) = make_float4(a8[4], a8[5], a8[6], a8[7]);
+                } else {
+                  uint4 v;
+                  v.x = pack_bf16x2(a8[0], a8[1]); v.y = pack_bf16x2(a8[2], a8[3]);
+                  v.z = pack_bf16x2(a8[4], a8[5]); v.w = pack_bf16x2(a8[6], a8[7]);
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw) = v;
+                }
+              }
+            }
+          }
+        }
+      }
       if constexpr (EPI == EPI_ALLREDUCE) {
         // publish: all 32 rows of this warp's slab are written -> raise flag (tile, q) with release semantics
         __threadfence_system();
@@ -886,8 +948,19 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_f32 = out_f32; p.accumulate = accumulate; p.status = status;
   p.k_splits = 1;
+  bool fold_in_kernel = false;
   if (splitk_ws != nullptr && k_splits > 1) {
-    // partial sums as fp32 [k_splits][M][N] in the workspace; vb_splitk_reduce folds them (+bias) into D
+    // partial sums as fp32 [k_splits][M][N] in the workspace; the split that finishes a slab last folds them (+bias)
+    // into D inside the GEMM kernel. (When the partials are wanted as they are, or the output has more slabs than the
+    // counter table, the separate reduce kernel below does it.)
+    const long long slabs = 4LL * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    fold_in_kernel = !g_partials_only && slabs <= FIX_COUNTERS;
+    if (fold_in_kernel) {
+      static unsigned int* counters = nullptr;
+      if (counters == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), g_fix_counters);
+      p.fix_counter = counters; p.fix_out = D; p.fix_ldd = ldd; p.fix_bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+      p.fix_out_f32 = out_f32; p.fix_accumulate = accumulate;
+    }
     p.k_splits = k_splits; p.D = splitk_ws; p.ldd = N; p.bias = nullptr; p.out_f32 = 1; p.accumulate = 0;
   }
   cudaError_t e;
@@ -904,7 +977,7 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
     else VB_LAUNCH(128, true, false, 6);
   }
 #undef VB_LAUNCH
-  if (e == cudaSuccess && p.k_splits > 1 && !g_partials_only) {
+  if (e == cudaSuccess && p.k_splits > 1 && !g_partials_only && !fold_in_kernel) {
     const long long total4 = static_cast<long long>(M) * N / 4;
     splitk_reduce_kernel<<<static_cast<int>((total4 + 255) / 256), 256, 0, stream>>>(
         splitk_ws, reinterpret_cast<const __nv_bfloat16*>(bias), D, ldd, M, N, p.k_splits, out_f32, accumulate);
