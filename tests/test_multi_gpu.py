@@ -382,6 +382,53 @@ def _sec_zero3_engine(rank, world, dev, ops, res):
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
+def _sec_peer_reshard(rank, world, dev, ops, res):
+    """Model-parallel shards pushed peer to peer into every rank's full-layout replica (``parallel/reshard.py``) against
+    the replica assembled with collectives: tensor-parallel (rows, columns, replicated, vocabulary-parallel head) and
+    expert-parallel (expert blocks, dense tensors from one writer) engines."""
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.parallel.reshard import PeerReshard
+    from verl_b200.workers.config import McoreEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.base import EngineRegistry
+    from verl_b200.workers.utils.losses import sft_loss
+
+    dense = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, eos_token_id=2, pad_token_id=0)
+    moe = ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,
+                      moe_intermediate_size=128, eos_token_id=2, pad_token_id=0, qk_norm=True)
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    for name, arch, ec in (("tp", dense, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)),
+                           ("ep", moe, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, expert_model_parallel_size=2))):
+        eng = EngineRegistry.new("language_model", "megatron", arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        plan = PeerReshard.try_create(eng)
+        res[f"{name}_created"] = plan is not None
+        if plan is None:
+            continue
+        plan.full.flat.fill_(7.0)                       # stale replica content must be overwritten everywhere
+        plan.run()
+        torch.cuda.synchronize()
+        want = eng.gather_full_params().flat.to(plan.full.flat.dtype)
+        res[f"{name}_equal_0"] = bool(torch.equal(plan.full.flat[: want.numel()], want))
+        g = torch.Generator().manual_seed(300 + (0 if name == "tp" else rank))
+        ids = torch.randint(3, 1024, (4, 40), generator=g)
+        am = torch.ones_like(ids)
+        data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 16:].to(dev), "response_mask": am[:, 16:].to(dev)}
+        eng.train_batch(dict(data), partial(sft_loss, None))
+        plan.run()
+        torch.cuda.synchronize()
+        want = eng.gather_full_params().flat.to(plan.full.flat.dtype)
+        res[f"{name}_equal_1"] = bool(torch.equal(plan.full.flat[: want.numel()], want))
+        res[f"{name}_jobs"] = (int(plan.jobs.shape[0]), int(plan.total_blocks), int(plan.bytes_per_run))
+        del eng, plan
+        torch.cuda.empty_cache()
+    os.environ["VERL_B200_FUSED_COMM"] = "1"
+    res["status"] = int(ops.comm_status())
+
+
 SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
 
 
@@ -526,3 +573,11 @@ def test_zero3_engine_matches_zero2_on_gpus(pair):
             assert res[f"{name}_param_diff"] < 2e-2 and res[f"{name}_norm_diff"] < 1e-2 * max(1.0, max(res["norm"])), res
             assert res[f"{name}_counts"][0] > 0 and res[f"{name}_counts"][1] > 0, res
         assert res["status"] == (0, 0), res
+
+
+def test_model_parallel_shards_pushed_into_every_replica(pair):
+    for res in pair.run("peer_reshard", timeout=600).values():
+        for name in ("tp", "ep"):
+            assert res[f"{name}_created"] and res[f"{name}_equal_0"] and res[f"{name}_equal_1"], res
+            assert res[f"{name}_jobs"][0] > 0
+        assert res["status"] == 0, res

@@ -620,6 +620,16 @@ Tensor gemm_fetch(const Tensor& a, const Tensor& b, const OptTensor& bias, const
   return d;
 }
 
+// jobs: int64 CUDA tensor [njobs, 6] = (dst address, src address, rows, row bytes, dst row stride, src row stride), all in bytes;
+// block_start: int32 CUDA tensor [njobs + 1] (16 KB blocks per job, prefix sums). Destinations may be peer-mapped memory.
+void scatter_copy_(const Tensor& jobs, const Tensor& block_start, int64_t total_blocks) {
+  TORCH_CHECK(jobs.is_cuda() && jobs.scalar_type() == at::kLong && jobs.dim() == 2 && jobs.size(1) == 6 && jobs.is_contiguous());
+  TORCH_CHECK(block_start.is_cuda() && block_start.scalar_type() == at::kInt && block_start.numel() == jobs.size(0) + 1);
+  const c10::cuda::CUDAGuard guard(jobs.device());
+  count(1);
+  CHECK_RC(vb_scatter_copy(jobs.data_ptr(), block_start.data_ptr<int>(), (int)jobs.size(0), (int)total_blocks, cur_stream()), "vb_scatter_copy");
+}
+
 int64_t comm_status() { return vb_comm_status(); }
 
 // ---- fp8 (e4m3) with 1x128 block scales
@@ -860,6 +870,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_fetch", &gemm_fetch);
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
+  m.def("scatter_copy_", &scatter_copy_);
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
   m.def("fp8_quant_128x128", &fp8_quant_128x128);

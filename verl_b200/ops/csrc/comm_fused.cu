@@ -206,6 +206,32 @@ __global__ void allreduce_peer_kernel(PeerPtrs bufs, __nv_bfloat16* __restrict__
   reinterpret_cast<uint4*>(out)[i8] = o;
 }
 
+// ---- train -> rollout reshard: a table of 2-D copy jobs, any of whose destinations may be peer memory.
+// Job j copies rows[j] rows of row_bytes[j] bytes (a multiple of 16) from src (row stride src_stride) to dst (row stride
+// dst_stride); addresses 16-byte aligned. Blocks [block_start[j], block_start[j + 1]) belong to job j, 16 KB each.
+struct CopyJob {
+  unsigned long long dst, src;
+  long long rows, row_bytes, dst_stride, src_stride;
+};
+
+__global__ void scatter_copy_kernel(const CopyJob* __restrict__ jobs, const int* __restrict__ block_start, int njobs) {
+  // the job of this block: last j with block_start[j] <= blockIdx.x
+  int lo = 0, hi = njobs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (block_start[mid] <= static_cast<int>(blockIdx.x)) lo = mid; else hi = mid - 1;
+  }
+  const CopyJob jb = jobs[lo];
+  const long long per_row = jb.row_bytes >> 4;                 // 16-byte units per row
+  const long long total = jb.rows * per_row;
+  const long long u0 = static_cast<long long>(blockIdx.x - block_start[lo]) * 1024;   // 1024 units = 16 KB per block
+  for (long long u = u0 + threadIdx.x; u < min(total, u0 + 1024); u += blockDim.x) {
+    const long long r = u / per_row, c = u - r * per_row;
+    const uint4 v = *reinterpret_cast<const uint4*>(jb.src + r * jb.src_stride + (c << 4));
+    *reinterpret_cast<uint4*>(jb.dst + r * jb.dst_stride + (c << 4)) = v;
+  }
+}
+
 static int* comm_status_ptr() {
   static int* p = nullptr;
   if (p == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_comm_status);
@@ -266,6 +292,12 @@ int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n
   if (n == 0) return 0;
   allreduce_peer_kernel<<<static_cast<int>((n / 8 + 255) / 256), 256, 0, s>>>(make_peers(buf_ptrs, W),
                                                                               reinterpret_cast<__nv_bfloat16*>(out), n, W, rank);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int vb_scatter_copy(const void* jobs, const int* block_start, int njobs, int total_blocks, cudaStream_t s) {
+  if (njobs <= 0 || total_blocks <= 0) return 0;
+  scatter_copy_kernel<<<total_blocks, 256, 0, s>>>(reinterpret_cast<const CopyJob*>(jobs), block_start, njobs);
   return static_cast<int>(cudaGetLastError());
 }
 

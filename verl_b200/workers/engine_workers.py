@@ -305,7 +305,18 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 from ..utils.distributed import set_data_parallel_group
 
                 self._mp_engine = src
-                self.rollout_params = src.gather_full_params()
+                # shards go peer to peer into every rank's replica when the job allows it (parallel/reshard.py), else the
+                # replica is assembled with collectives
+                self._reshard = None
+                if getattr(src, "topo", None) is not None and os.environ.get("VERL_B200_PEER_RESHARD", "1") != "0":
+                    from ..parallel.reshard import PeerReshard
+
+                    self._reshard = PeerReshard.try_create(src)
+                if self._reshard is not None:
+                    self.rollout_params = self._reshard.full
+                    self._reshard.run()
+                else:
+                    self.rollout_params = src.gather_full_params()
                 if self._mp_actor:
                     set_data_parallel_group(topo.dp_group)
 
@@ -540,7 +551,9 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
         buffer in place, so this only invalidates cached KV; returns the device time spent."""
         t0 = time.time()
         if getattr(self, "_regather", False) and self.rollout is not None:
-            if getattr(self._mp_engine, "zero3", False):
+            if getattr(self, "_reshard", None) is not None:
+                self._reshard.run()                                          # peer stores straight into every replica
+            elif getattr(self._mp_engine, "zero3", False):
                 self._mp_engine.gather_full_params(out=self.rollout_params)  # unit by unit, straight into the replica
             else:
                 fresh = self._mp_engine.gather_full_params()
