@@ -429,6 +429,43 @@ def _sec_peer_reshard(rank, world, dev, ops, res):
     res["status"] = int(ops.comm_status())
 
 
+def _sec_fused_tp_training(rank, world, dev, ops, res):
+    """Tensor-parallel training with the all-reduce inside the GEMM epilogue (row-parallel forwards, column-parallel input
+    gradients) against the same engine on GEMM + NCCL all-reduce."""
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.workers.config import McoreEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.base import EngineRegistry
+    from verl_b200.workers.utils.losses import sft_loss
+
+    arch = ModelConfig(model_type="llama", vocab_size=2048, hidden_size=1024, intermediate_size=2048, num_hidden_layers=2,
+                       num_attention_heads=8, num_key_value_heads=4, head_dim=128, eos_token_id=2, pad_token_id=0)
+    g = torch.Generator().manual_seed(77)
+    ids = torch.randint(3, 2048, (4, 300), generator=g)
+    am = torch.ones_like(ids)
+    data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 100:].to(dev), "response_mask": am[:, 100:].to(dev)}
+    out = {}
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    for flag in ("1", "0"):
+        os.environ["VERL_B200_FUSED_TP"] = flag
+        ec = McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)
+        object.__setattr__(ec, "sequence_parallel", False)
+        eng = EngineRegistry.new("language_model", "megatron", arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        res[f"fused_{flag}"] = bool(getattr(eng, "fused_tp_collectives", False))
+        norms = [float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"]) for _ in range(2)]
+        lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float()
+        out[flag] = (norms, lp.clone(), eng.gather_full_params().flat.float().clone())
+        del eng
+        torch.cuda.empty_cache()
+    os.environ["VERL_B200_FUSED_TP"] = os.environ["VERL_B200_FUSED_COMM"] = "1"
+    res["norms"] = (out["1"][0], out["0"][0])
+    res["lp_diff"] = (out["1"][1] - out["0"][1]).abs().max().item()
+    res["param_diff"] = (out["1"][2] - out["0"][2]).abs().max().item()
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
 SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
 
 
@@ -581,3 +618,11 @@ def test_model_parallel_shards_pushed_into_every_replica(pair):
             assert res[f"{name}_created"] and res[f"{name}_equal_0"] and res[f"{name}_equal_1"], res
             assert res[f"{name}_jobs"][0] > 0
         assert res["status"] == 0, res
+
+
+def test_tensor_parallel_training_with_fused_collectives(pair):
+    for res in pair.run("fused_tp_training", timeout=600).values():
+        assert res["fused_1"] and not res["fused_0"], res
+        for a, b in zip(*res["norms"]):
+            assert abs(a - b) < 2e-2 * max(1.0, b), res
+        assert res["lp_diff"] < 5e-2 and res["param_diff"] < 2e-2 and res["status"] == (0, 0), res

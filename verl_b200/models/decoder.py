@@ -366,6 +366,10 @@ class DecoderModel:
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
         self.tp_reduce: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
+        # tensor-parallel training on GPUs: ``tp_linear_sum(x, w, b_mn)`` = (x @ w^T, or x @ w with b_mn) summed over the
+        # tensor-parallel group by ONE kernel (GEMM with the all-reduce in its epilogue over peer memory); replaces the
+        # GEMM + collective pairs behind the row-parallel projections and in the input gradients of the column-parallel ones
+        self.tp_linear_sum: Optional[Callable[..., torch.Tensor]] = None
         self.stats_hook: Optional[Callable[[str, torch.Tensor], None]] = None  # called with (name, tensor) per layer output
         self.vocab_parallel = None                          # (group, first vocabulary row) of a vocabulary-parallel LM head
         self.mlp_tile_tokens = 0                            # > 0: sequence-tiled dense MLP (tokens per tile)
@@ -484,6 +488,8 @@ class DecoderModel:
                 S.update(qkv=qkv, attn=attn2, lse=lse)
         if self.tp is not None:
             return self.tp.row_linear(attn2, W["self_attn.o_proj.weight"][:, self.tp.rows(cfg.q_size)], None)
+        if self.tp_linear_sum is not None and W.get("self_attn.o_proj.bias") is None:
+            return self.tp_linear_sum(attn2, W["self_attn.o_proj.weight"], False)
         o = self._lin(W, "self_attn.o_proj.weight", attn2, S)
         return self.tp_reduce(o) if self.tp_reduce is not None else o
 
@@ -571,9 +577,12 @@ class DecoderModel:
                                  self._grad_of(wk), True)
             gq.copy_(dqp.view(T, nh, hd))
             gk.copy_(dkp.view(T, nkv, hd))
-        g_h1 = F.gemm(g_qkv, W["self_attn.qkv_proj.weight"], b_mn=True)
-        if self.tp_reduce is not None:
-            g_h1 = self.tp_reduce(g_h1)
+        if self.tp_linear_sum is not None:
+            g_h1 = self.tp_linear_sum(g_qkv, W["self_attn.qkv_proj.weight"], True)
+        else:
+            g_h1 = F.gemm(g_qkv, W["self_attn.qkv_proj.weight"], b_mn=True)
+            if self.tp_reduce is not None:
+                g_h1 = self.tp_reduce(g_h1)
         self._wgrad(W["self_attn.qkv_proj.weight"], g_qkv, h1)
         b = W.get("self_attn.qkv_proj.bias")
         if b is not None and getattr(b, "main_grad", None) is not None:
@@ -635,6 +644,8 @@ class DecoderModel:
         gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
         if S is not None:
             S["gu"] = gu
+        if self.tp_linear_sum is not None and W.get("mlp.down_proj.bias") is None:
+            return self.tp_linear_sum(F.swiglu(gu), W["mlp.down_proj.weight"], False)
         d = self._lin(W, "mlp.down_proj.weight", F.swiglu(gu), S)
         return self.tp_reduce(d) if self.tp_reduce is not None else d
 
@@ -658,9 +669,12 @@ class DecoderModel:
         g_act = F.gemm(g_d, W["mlp.down_proj.weight"], b_mn=True)
         self._wgrad(W["mlp.down_proj.weight"], g_d, act)
         g_gu = F.swiglu_bwd(g_act, gu)
-        g_h2 = F.gemm(g_gu, W["mlp.gate_up_proj.weight"], b_mn=True)
-        if self.tp_reduce is not None:
-            g_h2 = self.tp_reduce(g_h2)
+        if self.tp_linear_sum is not None:
+            g_h2 = self.tp_linear_sum(g_gu, W["mlp.gate_up_proj.weight"], True)
+        else:
+            g_h2 = F.gemm(g_gu, W["mlp.gate_up_proj.weight"], b_mn=True)
+            if self.tp_reduce is not None:
+                g_h2 = self.tp_reduce(g_h2)
         self._wgrad(W["mlp.gate_up_proj.weight"], g_gu, h2)
         return g_h2
 

@@ -993,10 +993,26 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
 //  epoch         this rank's two-word call counter (zero before the first call); all ranks must issue the same
 //                sequence of calls on these buffers. Waits on peers give up after limit_s seconds and report through
 //                vb_gemm_status() (code 13); the output is then undefined but the kernel returns.
+extern "C" int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                         long long lda, long long ldb, long long ldd, int b_mn,
+                                         const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
+                                         unsigned int* epoch, long long buf_elems, int world, int rank, double limit_s,
+                                         cudaStream_t stream);
+
 extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                                       long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                       const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
                                       int world, int rank, double limit_s, cudaStream_t stream) {
+  return vb_gemm_bf16_allreduce_ex(A, B, D, bias, M, N, K, lda, ldb, ldd, 0, part_ptrs, flag_ptrs, epoch, buf_elems, world,
+                                   rank, limit_s, stream);
+}
+
+// b_mn != 0: B is stored [K, N] (the input gradient of a column-parallel layer: D = dY_r W_r summed over the ranks).
+extern "C" int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
+                                         long long lda, long long ldb, long long ldd, int b_mn,
+                                         const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
+                                         unsigned int* epoch, long long buf_elems, int world, int rank, double limit_s,
+                                         cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % 8)) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return -2;
@@ -1008,7 +1024,11 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
   const int BN = wide ? 256 : 128;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
-  if (!make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  if (!b_mn) {
+    if (!make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  } else {
+    if (!make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  }
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
@@ -1021,8 +1041,10 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
     p.ar_flag[r] = flag_ptrs[r];
   }
   cudaError_t e;
-  if (wide) e = launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
-  else e = launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
+  if (wide) e = b_mn ? launch_variant<256, false, true, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream)
+                     : launch_variant<256, false, false, 4, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
+  else e = b_mn ? launch_variant<128, false, true, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream)
+                : launch_variant<128, false, false, 6, EPI_ALLREDUCE>(ta, tb, p, sms, stream);
   return static_cast<int>(e);
 }
 

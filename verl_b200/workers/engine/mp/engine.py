@@ -23,6 +23,8 @@ from typing import Callable, Generator, Optional
 import torch
 import torch.distributed as dist
 
+from ....ops import functional as F
+
 from ....models.weights import FlatParams
 from ....parallel.model_parallel import ModelParallelTopology, build_shard_map, copy_full_to_local, copy_local_to_full
 from ....utils.distributed import get_data_parallel_group, set_data_parallel_group
@@ -93,6 +95,26 @@ class ModelParallelEngine(NativeEngine):
                 return x
 
             self.model.tp_reduce = reduce
+            self.fused_tp_collectives = False
+            if (self.device.type == "cuda" and dist.get_world_size() == self.topo.tp and os.environ.get("VERL_B200_FUSED_TP", "1") != "0"
+                    and not (bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1)):
+                # one kernel per row-parallel projection / column-parallel input gradient: GEMM with the all-reduce in its
+                # epilogue over peer memory (peer-mapped buffers are bound to the default group: the tensor-parallel group has
+                # to be the whole job; other layouts keep GEMM + NCCL)
+                from ....parallel.symmetric import FusedRowParallelLinear, symmetric_available
+
+                if symmetric_available():
+                    rows = int(getattr(self.engine_config, "max_token_len_per_gpu", 0) or 0) or 16384
+                    rows = max(rows, int(getattr(self.engine_config, "infer_max_token_len_per_gpu", 0) or 0))
+                    fused = FusedRowParallelLinear(rows, self.full_arch.hidden_size, self.device, None)
+
+                    def linear_sum(x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+                        if x.shape[0] > fused.max_rows:  # a micro-batch beyond the planned size: GEMM + collective
+                            return reduce(F.gemm(x, w, b_mn=b_mn))
+                        return fused(x.contiguous(), w, None, None, b_mn)
+
+                    self.model.tp_linear_sum = linear_sum
+                    self.fused_tp_collectives = True
             if bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1:
                 # (with context parallelism the stream is already token-sliced over the context-parallel block, and the
                 # tensor-parallel group keeps the plain all-reduce form)
