@@ -444,25 +444,27 @@ def _sec_fused_tp_training(rank, world, dev, ops, res):
     g = torch.Generator().manual_seed(77)
     ids = torch.randint(3, 2048, (4, 300), generator=g)
     am = torch.ones_like(ids)
+    am[0, :1] = 0                                      # 599 tokens in the first micro-batch: ragged token slices
     data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 100:].to(dev), "response_mask": am[:, 100:].to(dev)}
-    out = {}
     os.environ["VERL_B200_FUSED_COMM"] = "0"
-    for flag in ("1", "0"):
-        os.environ["VERL_B200_FUSED_TP"] = flag
-        ec = McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)
-        object.__setattr__(ec, "sequence_parallel", False)
-        eng = EngineRegistry.new("language_model", "megatron", arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
-        eng.initialize()
-        res[f"fused_{flag}"] = bool(getattr(eng, "fused_tp_collectives", False))
-        norms = [float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"]) for _ in range(2)]
-        lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float()
-        out[flag] = (norms, lp.clone(), eng.gather_full_params().flat.float().clone())
-        del eng
-        torch.cuda.empty_cache()
+    for sp in (False, True):
+        out = {}
+        for flag in ("1", "0"):
+            os.environ["VERL_B200_FUSED_TP"] = flag
+            ec = McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)
+            object.__setattr__(ec, "sequence_parallel", sp)
+            eng = EngineRegistry.new("language_model", "megatron", arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
+            eng.initialize()
+            res[f"fused_{flag}_sp{int(sp)}"] = bool(getattr(eng, "fused_tp_collectives", False)) and eng.model.tp_linear_sum is not None
+            norms = [float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"]) for _ in range(2)]
+            lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float()
+            out[flag] = (norms, lp.clone(), eng.gather_full_params().flat.float().clone())
+            del eng
+            torch.cuda.empty_cache()
+        res[f"norms_sp{int(sp)}"] = (out["1"][0], out["0"][0])
+        res[f"lp_diff_sp{int(sp)}"] = (out["1"][1] - out["0"][1]).abs().max().item()
+        res[f"param_diff_sp{int(sp)}"] = (out["1"][2] - out["0"][2]).abs().max().item()
     os.environ["VERL_B200_FUSED_TP"] = os.environ["VERL_B200_FUSED_COMM"] = "1"
-    res["norms"] = (out["1"][0], out["0"][0])
-    res["lp_diff"] = (out["1"][1] - out["0"][1]).abs().max().item()
-    res["param_diff"] = (out["1"][2] - out["0"][2]).abs().max().item()
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
@@ -621,8 +623,12 @@ def test_model_parallel_shards_pushed_into_every_replica(pair):
 
 
 def test_tensor_parallel_training_with_fused_collectives(pair):
-    for res in pair.run("fused_tp_training", timeout=600).values():
-        assert res["fused_1"] and not res["fused_0"], res
-        for a, b in zip(*res["norms"]):
-            assert abs(a - b) < 2e-2 * max(1.0, b), res
-        assert res["lp_diff"] < 5e-2 and res["param_diff"] < 2e-2 and res["status"] == (0, 0), res
+    """All-reduce form (plain tensor parallelism) and reduce-scatter form (sequence parallelism; 599 token rows per
+    micro-batch, so the two ranks' slices are ragged) of the GEMM epilogue against GEMM + NCCL."""
+    for res in pair.run("fused_tp_training", timeout=900).values():
+        for sp in (0, 1):
+            assert res[f"fused_1_sp{sp}"] and not res[f"fused_0_sp{sp}"], res
+            for a, b in zip(*res[f"norms_sp{sp}"]):
+                assert abs(a - b) < 2e-2 * max(1.0, b), res
+            assert res[f"lp_diff_sp{sp}"] < 5e-2 and res[f"param_diff_sp{sp}"] < 2e-2, res
+        assert res["status"] == (0, 0), res

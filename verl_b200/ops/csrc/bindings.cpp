@@ -536,7 +536,7 @@ void allreduce_peer_(const Tensor& buf_ptrs, Tensor out, int64_t rank) {
 // part_ptrs / flag_ptrs: CPU int64 tensors [world] with every rank's partial buffer and flag array addresses.
 Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, const Tensor& part_ptrs, const Tensor& flag_ptrs,
                       Tensor epoch, int64_t buf_elems, int64_t rank, double limit_s, const OptTensor& out,
-                      const OptTensor& splitk_ws, bool b_mn) {
+                      const OptTensor& splitk_ws, bool b_mn, int64_t rs_rows) {
   CHECK_BF16(a);
   CHECK_BF16(b);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == (b_mn ? b.size(0) : b.size(1)),
@@ -544,8 +544,10 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   TORCH_CHECK(epoch.scalar_type() == at::kInt && epoch.numel() >= 2 && epoch.is_cuda(), "gemm_allreduce: int32 cuda epoch[2]");
   const c10::cuda::CUDAGuard guard(a.device());
   const int64_t M = a.size(0), K = a.size(1), N = b_mn ? b.size(1) : b.size(0);
-  Tensor d = out.has_value() ? *out : at::empty({M, N}, a.options());
-  TORCH_CHECK(d.scalar_type() == at::kBFloat16 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "gemm_allreduce: bad out");
+  // rs_rows > 0: reduce-scatter over rows; the result is this rank's [rs_rows, N] slice (zero where the slice runs past M)
+  const int64_t out_rows = rs_rows > 0 ? rs_rows : M;
+  Tensor d = out.has_value() ? *out : (rs_rows > 0 ? at::zeros({out_rows, N}, a.options()) : at::empty({M, N}, a.options()));
+  TORCH_CHECK(d.scalar_type() == at::kBFloat16 && d.size(0) == out_rows && d.size(1) == N && d.stride(1) == 1, "gemm_allreduce: bad out");
   const void* bias_ptr = nullptr;
   if (bias.has_value()) {
     TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm_allreduce: bad bias");
@@ -553,7 +555,7 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   }
   if (M == 0) return d;
   // decode-sized calls (few output tiles, deep K): K-split GEMM over all SMs + one fused reduce / all-reduce kernel
-  const int splits = (splitk_ws.has_value() && !b_mn) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
+  const int splits = (splitk_ws.has_value() && !b_mn && rs_rows <= 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
   if (splits > 1 && splitk_ws->numel() >= splits * M * N) {
     CHECK_F32((*splitk_ws));
     count(2);
@@ -567,7 +569,7 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   }
   count(1);
   const int rc = vb_gemm_bf16_allreduce_ex(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
-                                           b.stride(0), d.stride(0), b_mn ? 1 : 0, uptr(part_ptrs), uptr(flag_ptrs),
+                                           b.stride(0), d.stride(0), b_mn ? 1 : 0, (int)rs_rows, uptr(part_ptrs), uptr(flag_ptrs),
                                            reinterpret_cast<unsigned int*>(epoch.data_ptr<int>()), buf_elems, (int)part_ptrs.numel(),
                                            (int)rank, limit_s, cur_stream());
   TORCH_CHECK(rc == 0, "vb_gemm_bf16_allreduce failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");

@@ -67,6 +67,8 @@ struct GemmParams {
   long long ar_buf_elems;
   unsigned int* ar_epoch;   // this rank's [2]: {calls completed, CTAs finished in the running call}
   unsigned long long ar_limit_ns;  // how long a slab waits for its peers before giving up
+  int ar_rs_rows;  // > 0: reduce-scatter over rows: this rank sums (and stores, at row - rank * ar_rs_rows) only rows
+                   // [rank * ar_rs_rows, (rank + 1) * ar_rs_rows); the other slabs are published and left to their owners
   // grouped (mixture-of-experts) modes; all row segments are padded to multiples of 128 rows
   //  1: rows grouped by expert  D[rows, N] = A[rows, K] * B_e^T, expert of each 128-row tile from grp_tile_expert
   //  2: contraction grouped     D_e[M, N] (+)= A[seg_e, M]^T * B[seg_e, N] for every expert e (weight gradients)
@@ -610,9 +612,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         const int slot = (t % num_mn) * 4 + q;
         if (lane == 0) st_release_sys_u32(reinterpret_cast<unsigned int*>(p.ar_flag[p.ar_rank]) + slot, ar_epoch_now);
         // pass B: wait (bounded) for the same slab of every peer, then sum all partials in rank order
+        int rs_lo = 0, rs_hi = 0x7fffffff;
+        bool mine = true;
+        if (p.ar_rs_rows > 0) {
+          rs_lo = p.ar_rank * p.ar_rs_rows;
+          rs_hi = rs_lo + p.ar_rs_rows;
+          const int s0 = m0 + q * 32;
+          mine = s0 < rs_hi && s0 + 32 > rs_lo;  // uniform over the warp
+        }
         bool peers_ok = true;
         const unsigned long long t_start = ar_now_ns();
-        for (int r = 0; r < p.ar_world; ++r) {
+        for (int r = 0; mine && r < p.ar_world; ++r) {
           if (r == p.ar_rank) continue;
           const unsigned int* f = reinterpret_cast<const unsigned int*>(p.ar_flag[r]) + slot;
           while (static_cast<int>(ld_acquire_sys_u32(f) - ar_epoch_now) < 0) {
@@ -627,7 +637,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         peers_ok = __all_sync(0xffffffffu, peers_ok);
         if (!peers_ok) {
           if (lane == 0) atomicExch(p.status, ST_TIMEOUT_EPILOGUE + 10);
-        } else {
+        } else if (mine) {
           // lanes sweep the columns of one (BN = 256) or two (BN = 128) rows at a time: 16-byte pieces of a row are
           // contiguous across lanes, so every peer read is a full 512-byte (256-byte) burst over NVLink
           constexpr int LPR = BN / 8;   // lanes per row
@@ -646,7 +656,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
               const int orow = m0 + q * 32 + rr + u * RPI + lane / LPR;
-              ok[u] = col_ok && orow < p.M;
+              ok[u] = col_ok && orow < p.M && orow >= rs_lo && orow < rs_hi;
               off[u] = half + static_cast<long long>(orow) * p.N + col;
 #pragma unroll
               for (int j = 0; j < 8; ++j) acc8[u][j] = 0.f;
@@ -681,7 +691,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
               o.y = pack_bf16x2(acc8[u][2] + bias8[2], acc8[u][3] + bias8[3]);
               o.z = pack_bf16x2(acc8[u][4] + bias8[4], acc8[u][5] + bias8[5]);
               o.w = pack_bf16x2(acc8[u][6] + bias8[6], acc8[u][7] + bias8[7]);
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow) * p.ldd + col) = o;
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow - rs_lo) * p.ldd + col) = o;
             }
           }
         }
@@ -994,7 +1004,7 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
 //                sequence of calls on these buffers. Waits on peers give up after limit_s seconds and report through
 //                vb_gemm_status() (code 13); the output is then undefined but the kernel returns.
 extern "C" int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
-                                         long long lda, long long ldb, long long ldd, int b_mn,
+                                         long long lda, long long ldb, long long ldd, int b_mn, int rs_rows,
                                          const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
                                          unsigned int* epoch, long long buf_elems, int world, int rank, double limit_s,
                                          cudaStream_t stream);
@@ -1003,13 +1013,16 @@ extern "C" int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, con
                                       long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                       const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
                                       int world, int rank, double limit_s, cudaStream_t stream) {
-  return vb_gemm_bf16_allreduce_ex(A, B, D, bias, M, N, K, lda, ldb, ldd, 0, part_ptrs, flag_ptrs, epoch, buf_elems, world,
-                                   rank, limit_s, stream);
+  return vb_gemm_bf16_allreduce_ex(A, B, D, bias, M, N, K, lda, ldb, ldd, 0, 0, part_ptrs, flag_ptrs, epoch, buf_elems,
+                                   world, rank, limit_s, stream);
 }
 
 // b_mn != 0: B is stored [K, N] (the input gradient of a column-parallel layer: D = dY_r W_r summed over the ranks).
+// rs_rows > 0: reduce-scatter over rows instead of all-reduce: D is this rank's [rs_rows, N] slice (rows
+// [rank * rs_rows, (rank + 1) * rs_rows) of the sum; rows at or beyond M are not written). Every rank must own at least one
+// row below M (the wait on its own slabs is what keeps a rank from running two calls ahead of a peer).
 extern "C" int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
-                                         long long lda, long long ldb, long long ldd, int b_mn,
+                                         long long lda, long long ldb, long long ldd, int b_mn, int rs_rows,
                                          const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
                                          unsigned int* epoch, long long buf_elems, int world, int rank, double limit_s,
                                          cudaStream_t stream) {
@@ -1036,6 +1049,8 @@ extern "C" int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, 
   p.k_splits = 1;
   p.ar_world = world; p.ar_rank = rank; p.ar_buf_elems = buf_elems; p.ar_epoch = epoch;
   p.ar_limit_ns = static_cast<unsigned long long>((limit_s > 0.0 ? limit_s : 2.0) * 1e9);
+  if (rs_rows > 0 && static_cast<long long>(rs_rows) * (world - 1) >= M) return -6;  // a rank without rows
+  p.ar_rs_rows = rs_rows > 0 ? rs_rows : 0;
   for (int r = 0; r < world; ++r) {
     p.ar_part[r] = part_ptrs[r];
     p.ar_flag[r] = flag_ptrs[r];

@@ -21,7 +21,7 @@ int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const v
                                   const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
                                   double limit_s, int k_splits, float* splitk_ws, cudaStream_t stream);
 int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
-                             long long ldb, long long ldd, int b_mn, const unsigned long long* part_ptrs,
+                             long long ldb, long long ldd, int b_mn, int rs_rows, const unsigned long long* part_ptrs,
                              const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
                              double limit_s, cudaStream_t stream);
 int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,

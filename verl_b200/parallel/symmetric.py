@@ -100,13 +100,15 @@ class FusedRowParallelLinear:
         dist.barrier(group)  # flags are zero everywhere before anyone publishes epoch 1
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 b_mn: bool = False):
-        """``b_mn``: ``b`` is stored [K, N] (the input gradient of a column-parallel layer: ``dY_r @ W_r`` summed over ranks)."""
+                 b_mn: bool = False, scatter_rows: int = 0):
+        """``b_mn``: ``b`` is stored [K, N] (the input gradient of a column-parallel layer: ``dY_r @ W_r`` summed over ranks).
+        ``scatter_rows`` > 0: reduce-scatter instead of all-reduce: returns this rank's ``[scatter_rows, N]`` slice of the
+        sum (rows ``rank * scatter_rows ...``; zero where the slice runs past the input's rows); every rank must own a row."""
         from ..ops import native
 
         assert a.shape[0] <= self.max_rows and (b.shape[1] if b_mn else b.shape[0]) == self.n
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
-                                           self.splitk_ws, bool(b_mn))
+                                           self.splitk_ws, bool(b_mn), int(scatter_rows))
 
 
 FETCH_CHUNK = 16384  # bytes per copy job of a GEMM's fetch warp (``FETCH_CHUNK`` in gemm_tcgen05.cu)

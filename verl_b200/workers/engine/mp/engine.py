@@ -96,25 +96,27 @@ class ModelParallelEngine(NativeEngine):
 
             self.model.tp_reduce = reduce
             self.fused_tp_collectives = False
-            if (self.device.type == "cuda" and dist.get_world_size() == self.topo.tp and os.environ.get("VERL_B200_FUSED_TP", "1") != "0"
-                    and not (bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1)):
-                # one kernel per row-parallel projection / column-parallel input gradient: GEMM with the all-reduce in its
-                # epilogue over peer memory (peer-mapped buffers are bound to the default group: the tensor-parallel group has
-                # to be the whole job; other layouts keep GEMM + NCCL)
+            use_sp = bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1
+            fused = None
+            if self.device.type == "cuda" and dist.get_world_size() == self.topo.tp and os.environ.get("VERL_B200_FUSED_TP", "1") != "0":
+                # one kernel per row-parallel projection / column-parallel input gradient: GEMM with the all-reduce (or, with
+                # sequence parallelism, the reduce-scatter over token rows) in its epilogue over peer memory. Peer-mapped
+                # buffers are bound to the default group: the tensor-parallel group has to be the whole job; other layouts
+                # keep GEMM + NCCL.
                 from ....parallel.symmetric import FusedRowParallelLinear, symmetric_available
 
                 if symmetric_available():
                     rows = int(getattr(self.engine_config, "max_token_len_per_gpu", 0) or 0) or 16384
                     rows = max(rows, int(getattr(self.engine_config, "infer_max_token_len_per_gpu", 0) or 0))
                     fused = FusedRowParallelLinear(rows, self.full_arch.hidden_size, self.device, None)
-
-                    def linear_sum(x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
-                        if x.shape[0] > fused.max_rows:  # a micro-batch beyond the planned size: GEMM + collective
-                            return reduce(F.gemm(x, w, b_mn=b_mn))
-                        return fused(x.contiguous(), w, None, None, b_mn)
-
-                    self.model.tp_linear_sum = linear_sum
                     self.fused_tp_collectives = True
+            if fused is not None and not use_sp:
+                def linear_sum(x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+                    if x.shape[0] > fused.max_rows:  # a micro-batch beyond the planned size: GEMM + collective
+                        return reduce(F.gemm(x, w, b_mn=b_mn))
+                    return fused(x.contiguous(), w, None, None, b_mn)
+
+                self.model.tp_linear_sum = linear_sum
             if bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1:
                 # (with context parallelism the stream is already token-sliced over the context-parallel block, and the
                 # tensor-parallel group keeps the plain all-reduce form)
@@ -125,6 +127,17 @@ class ModelParallelEngine(NativeEngine):
                 assert not self.full_arch.is_moe, "sequence parallelism covers dense blocks"
                 self.model.tsp = TensorSequenceParallel(grp, self.topo.tp_rank, self.topo.tp)
                 self.model.tp_reduce = self.model.tsp.scatter_sum
+                if fused is not None:
+                    tsp, W = self.model.tsp, self.topo.tp
+
+                    def linear_scatter(x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+                        T = x.shape[0]
+                        n = tsp.local_rows(T)
+                        if T > fused.max_rows or n * (W - 1) >= T:  # too large for the buffers, or a rank without rows
+                            return tsp.scatter_sum(F.gemm(x, w, b_mn=b_mn))
+                        return fused(x.contiguous(), w, None, None, b_mn, scatter_rows=n)
+
+                    self.model.tp_linear_sum = linear_scatter
         # replicated-parameter mask for the gradient norm (embedding, norms, head, biases of row-parallel layers)
         self._rep_ranges = [(self.params.offsets[m.local_name], self.params.views[m.local_name].numel())
                             for m in self.maps if m.kind == "rep"]
