@@ -468,6 +468,42 @@ def _sec_fused_tp_training(rank, world, dev, ops, res):
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
+def _sec_sequence_and_context_parallel(rank, world, dev, ops, res):
+    """Ulysses sequence parallelism (head exchange) and context parallelism (key / value gather, zigzag token split) on
+    GPUs: both ranks work on the same micro-batches; log-probs and the gradient norm equal the plain engine's."""
+    from functools import partial
+
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
+    arch = ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, eos_token_id=2, pad_token_id=0)
+    g = torch.Generator().manual_seed(5)                      # the same rows on both ranks
+    ids = torch.randint(3, 2048, (4, 200), generator=g)
+    am = torch.ones_like(ids)
+    am[2, :7] = 0
+    data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 60:].to(dev), "response_mask": am[:, 60:].to(dev)}
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    out = {}
+    for name, kw in (("plain", {}), ("ulysses", {"ulysses_sequence_parallel_size": 2}), ("context", {"context_parallel_size": 2})):
+        eng = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2, **kw), OptimizerConfig(lr=1e-3, clip_grad=1.0))
+        eng.initialize()
+        lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float().clone()
+        norm = float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"])
+        out[name] = (lp, norm, eng.params.flat.float().clone())
+        del eng
+        torch.cuda.empty_cache()
+    os.environ["VERL_B200_FUSED_COMM"] = "1"
+    m = data["response_mask"].bool()
+    for name in ("ulysses", "context"):
+        res[f"{name}_lp_diff"] = (out[name][0][m] - out["plain"][0][m]).abs().max().item()
+        res[f"{name}_norms"] = (out[name][1], out["plain"][1])
+        res[f"{name}_param_diff"] = (out[name][2] - out["plain"][2]).abs().max().item()
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
 SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
 
 
@@ -631,4 +667,12 @@ def test_tensor_parallel_training_with_fused_collectives(pair):
             for a, b in zip(*res[f"norms_sp{sp}"]):
                 assert abs(a - b) < 2e-2 * max(1.0, b), res
             assert res[f"lp_diff_sp{sp}"] < 5e-2 and res[f"param_diff_sp{sp}"] < 2e-2, res
+        assert res["status"] == (0, 0), res
+
+
+def test_sequence_and_context_parallel_on_gpus(pair):
+    for res in pair.run("sequence_and_context_parallel", timeout=600).values():
+        for name in ("ulysses", "context"):
+            a, b = res[f"{name}_norms"]
+            assert res[f"{name}_lp_diff"] < 5e-2 and abs(a - b) < 2e-2 * max(1.0, b) and res[f"{name}_param_diff"] < 2e-2, res
         assert res["status"] == (0, 0), res
