@@ -64,6 +64,10 @@ def parse_args():
     p.add_argument("--no-prefix-sharing", action="store_true",
                    help="pack every sample's prompt separately in the log-prob / training passes and prefill it separately "
                         "(default: the n samples of a prompt share its tokens; results are identical)")
+    p.add_argument("--offload", default="auto", choices=["auto", "on", "off"],
+                   help="Adam moments and the reference policy's weights in pinned host memory (optimizer_offload / ref param_offload), "
+                        "which leaves the GPU's memory to activations instead of recomputation; auto = on one GPU, where the whole "
+                        "unsharded optimizer state would sit on it")
     p.add_argument("--critic", action="store_true", help="PPO with a critic of the same architecture and GAE instead of GRPO")
     return p.parse_args()
 
@@ -135,6 +139,8 @@ def build_config(args, world: int):
         "trainer.resume_mode=disable", "trainer.save_freq=-1", "trainer.test_freq=-1", "trainer.logger=[]",
         "trainer.worker_group=spmd", f"trainer.device={args.device}",
     ]
+    if args.offload == "on" or (args.offload == "auto" and world == 1 and args.train_tp * args.train_pp * args.train_ep == 1):
+        ov += ["actor_rollout_ref.actor.fsdp_config.optimizer_offload=true", "actor_rollout_ref.ref.fsdp_config.param_offload=true"]
     if args.layers > 0:
         ov += [f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}"]
     mp = args.train_tp * args.train_pp
@@ -294,6 +300,8 @@ def main():
                        "algorithm": "ppo+critic+gae" if args.critic else "grpo",
                        **({"reduced_model_layers": args.layers} if args.layers > 0 else {}),
                        "shared_prompt_packing": not args.no_prefix_sharing,
+                       "host_offload": "adam moments + reference weights" if getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "_offloaded_states", ()) else "none",
+                       "kept_activation_layers": getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "last_kept_layers", None),
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
                        "time_budget_s": args.time_budget_s,
                        "mean_response_len": last_metrics.get("response_length/mean")},
@@ -306,6 +314,13 @@ def main():
             "clocks": (sampler.stop() if not partial else sampler.snapshot()) if sampler else None,
             "phases_s": {name: round(v / k, 3) for name, v in phase_sum.items()},
         }
+        eng = getattr(trainer.actor_rollout_wg.worker, "rollout", None)
+        st = getattr(eng, "stats", None)
+        if isinstance(st, dict) and st.get("decode_steps"):
+            # rank 0's rollout engine, cumulative since construction (warm-up steps included): where ``gen`` goes
+            out["rollout_stats"] = {"decode_steps": int(st["decode_steps"]), "decode_gpu_ms_per_step": round(1e3 * st.get("decode_gpu_s", 0.0) / st["decode_steps"], 3),
+                                    "prefill_tokens": int(st.get("prefill_tokens", 0)), "prefill_host_s": round(st.get("prefill_s", 0.0), 2),
+                                    "kv_blocks": int(getattr(eng, "num_blocks", 0) or 0)}
         if partial:
             out["partial"] = True
         print(json.dumps(out), flush=True)

@@ -54,27 +54,60 @@ def test_gemm_bias_fp32_accumulate(ops):
 
 
 @pytest.mark.parametrize("shape", [(320, 3584, 18944), (320, 4608, 3584), (77, 264, 4096), (130, 1024, 8192)])
-def test_gemm_k_split_folds_inside_the_kernel(ops, shape):
-    """Skinny GEMMs run K-split; the split that finishes a slab last folds the partial sums, adds the bias and writes the
-    output in the same kernel. Several launches in a row: the slab counters return to zero by themselves."""
+def test_gemm_k_split(ops, shape):
+    """GEMMs with few output tiles and a deep K run K-split in the general kernel (the layouts the transposed kernel for
+    few tokens does not serve: fp32 accumulation into the output, B stored [K, N]); partial sums are folded by the reduce
+    launch or, with VERL_B200_SPLITK_FOLD=1, by the split that finishes a slab last. Several launches in a row: the slab
+    counters return to zero by themselves."""
     M, N, K = shape
     assert int(ops.gemm_suggest_splits(M, N, K)) > 1
     torch.manual_seed(2)
     A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
     B = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
-    bias = torch.randn(N, device=DEV).bfloat16()
     ref = A.float() @ B.float().t()
+    Bt = B.t().contiguous()
     n0 = int(ops.launch_count())
     for _ in range(3):
-        d = ops.gemm(A, B, bias, None, False, False, False, False, 0)
-        assert rel(d, ref + bias.float()) < 1e-2
-    assert int(ops.launch_count()) - n0 == 3                     # one launch per GEMM: no separate reduce kernel
+        d2 = ops.gemm(A, Bt, None, None, False, True, False, False, 0)   # B stored [K, N]
+        assert rel(d2, ref) < 1e-2
+    assert int(ops.launch_count()) - n0 == (3 if int(ops.gemm_fold_in_kernel()) else 6)
     out = torch.randn(M, N, device=DEV)
     want = out + ref
     ops.gemm(A, B, None, out, False, False, True, True, 0)        # fp32 output, accumulate
     assert rel(out, want) < 1e-4
-    d2 = ops.gemm(A, B.t().contiguous(), None, None, False, True, False, False, 0)   # B stored [K, N]
-    assert rel(d2, ref) < 1e-2
+    assert int(ops.gemm_status()) == 0
+
+
+@pytest.mark.parametrize("shape", [(320, 4608, 3584), (320, 3584, 18944), (320, 37888, 3584), (1, 256, 64), (5, 264, 72), (16, 128, 4096),
+                                   (77, 152, 200), (130, 1024, 8192), (256, 3584, 3584), (257, 520, 1024), (512, 4608, 3584),
+                                   (320, 2304, 3584), (64, 151936, 896)])
+def test_gemm_few_tokens_transposed_kernel(ops, shape):
+    """Up to 512 tokens: the kernel that puts 128 weight rows on the tensor core's M axis and all tokens on its N axis, K
+    split over CTAs whose partial sums every split folds for its own share of the rows inside the same launch. Against
+    the fp32 product, with bias, row-strided input and output, several launches in a row (the counters of a tile return
+    to zero), and bit-equal across launches."""
+    M, N, K = shape
+    s = int(ops.gemm_skinny_splits(M, N, K))
+    assert s >= 1
+    torch.manual_seed(3)
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    ref = A.float() @ B.float().t() + bias.float()
+    n0 = int(ops.launch_count())
+    outs = [ops.gemm(A, B, bias, None, False, False, False, False, 0) for _ in range(3)]
+    assert int(ops.launch_count()) - n0 == 3
+    torch.cuda.synchronize()
+    assert int(ops.gemm_status()) == 0
+    assert rel(outs[0], ref) < 1e-2
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    # a view into a wider buffer as input (row stride > K) and as output (row stride > N)
+    wide = torch.zeros(M, K + 64, device=DEV, dtype=torch.bfloat16)
+    wide[:, 8 : 8 + K] = A
+    big = torch.full((M, N + 24), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(wide[:, 8 : 8 + K], B, None, big[:, 8 : 8 + N], False, False, False, False, 0)
+    assert rel(big[:, 8 : 8 + N], ref - bias.float()) < 1e-2
+    assert bool((big[:, :8] == 7).all()) and bool((big[:, 8 + N :] == 7).all())
     assert int(ops.gemm_status()) == 0
 
 

@@ -134,3 +134,49 @@ def test_library_module_family_on_gpu():
     assert (lp[m] - ref[m]).abs().max() < 1e-1
     losses = [float(eng.train_batch(dict(data), partial(sft_loss, None))["loss"]) for _ in range(4)]
     assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_host_offload_on_gpu():
+    """Adam moments streamed through the GPU from pinned host memory (several chunks, two staging buffers, three streams)
+    give the weights of the engine that keeps them resident; a forward-only engine with ``param_offload`` frees its weights
+    outside ``eval_mode()`` and computes the same log-probs after they come back."""
+    from verl_b200.models import ModelConfig
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
+    arch = ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, eos_token_id=2, pad_token_id=0)
+
+    def make(**kw):
+        e = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=3, **kw),
+                                   OptimizerConfig(lr=1e-3, clip_grad=1.0, weight_decay=0.1) if not kw.get("forward_only") else None)
+        e.initialize()
+        return e
+
+    plain, off = make(), make(optimizer_offload=True, param_offload=True)
+    if not off._offloaded_states:
+        pytest.skip("not enough free host memory to page-lock the optimizer state")
+    assert off.exp_avg.device.type == "cpu" and off.exp_avg.is_pinned() and off.master.device.type == "cpu"
+    off.offload_chunk_elems = -(-off.master.numel() // 5) // 8 * 8
+    for _ in range(3):
+        a = plain.train_batch(dict(_data()), partial(sft_loss, None))
+        b = off.train_batch(dict(_data()), partial(sft_loss, None))
+        assert abs(float(a["loss"]) - float(b["loss"])) < 1e-6
+    off._offload_sync()
+    assert torch.equal(plain.params.flat, off.params.flat)
+    assert torch.equal(plain.exp_avg_sq.cpu(), off.exp_avg_sq) and torch.equal(plain.master.cpu(), off.master)
+
+    ref = make(forward_only=True, param_offload=True)
+    if ref._param_host is None:
+        pytest.skip("not enough free host memory to page-lock the weights")
+    ref.params.flat.copy_(plain.params.flat)
+    data = _data()
+    with ref.eval_mode():
+        lp0 = ref.infer_batch(dict(data))["model_output"]["log_probs"].clone()
+    assert ref.params.flat.untyped_storage().size() == 0
+    before = torch.cuda.memory_allocated()
+    with ref.eval_mode():
+        assert torch.cuda.memory_allocated() > before
+        lp1 = ref.infer_batch(dict(data))["model_output"]["log_probs"].clone()
+    assert torch.equal(lp0, lp1) and ref.params.flat.untyped_storage().size() == 0

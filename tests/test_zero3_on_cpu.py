@@ -112,3 +112,42 @@ def test_zero3_matches_zero2(preset, tmp_path):
     assert exported, "hf_model export missing"
     for k, v in exported.items():
         assert torch.allclose(merged[k].float(), v.float(), atol=1e-2), k
+
+
+def test_optimizer_offload_matches_resident_state(tmp_path):
+    """``optimizer_offload``: the chunk walk over host-resident Adam moments (three chunks here) gives the weights of the
+    engine that keeps its state in place, and a checkpoint written from the offloaded state loads into a plain engine."""
+    import torch
+    from functools import partial
+
+    from verl_b200.models import ModelConfig
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
+    arch = ModelConfig(model_type="qwen2", vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=8, eos_token_id=2, pad_token_id=0)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(3, 128, (4, 12), generator=g)
+    data = {"input_ids": ids, "attention_mask": torch.ones_like(ids), "responses": ids[:, -6:], "response_mask": torch.ones(4, 6, dtype=torch.long)}
+
+    def make(offload, params=False):
+        e = NativeEngineWithLMHead(arch, FSDPEngineConfig(seed=3, micro_batch_size_per_gpu=2, optimizer_offload=offload, param_offload=params),
+                                   OptimizerConfig(lr=1e-2, clip_grad=1.0, weight_decay=0.1))
+        e.initialize()
+        return e
+
+    plain, off, off_all = make(False), make(True), make(True, True)
+    assert off._offloaded_states == ("exp_avg", "exp_avg_sq") and off_all._offloaded_states == ("exp_avg", "exp_avg_sq", "master")
+    for e in (off, off_all):
+        e.offload_chunk_elems = -(-e.master.numel() // 3)
+    for _ in range(3):
+        outs = [e.train_batch(dict(data), partial(sft_loss, None)) for e in (plain, off, off_all)]
+        assert abs(float(outs[0]["loss"]) - float(outs[1]["loss"])) < 1e-6 and abs(float(outs[0]["loss"]) - float(outs[2]["loss"])) < 1e-6
+    for e in (off, off_all):
+        assert torch.allclose(plain.params.flat, e.params.flat, atol=1e-7)
+        assert torch.allclose(plain.exp_avg_sq, e.exp_avg_sq, atol=1e-10) and torch.allclose(plain.master, e.master, atol=1e-7)
+    off.save_checkpoint(str(tmp_path / "c"))
+    fresh = make(False)
+    fresh.load_checkpoint(str(tmp_path / "c"))
+    assert torch.equal(fresh.exp_avg, off.exp_avg) and torch.equal(fresh.master, off.master) and fresh.opt_step_count == 3

@@ -109,6 +109,20 @@ def main(argv=None):
             out = torch.empty(M, N, device=dev, dtype=torch.float32 if amn else torch.bfloat16)
             ms = T(lambda: ops.gemm(A, B, None, out, amn, bmn, amn, False, 0))
             report(name, [M, N, K], ms, flops=2.0 * M * N * K, bytes_=2.0 * (M * K + N * K) + out.element_size() * M * N)
+    if want("gemm_decode_set"):
+        # every GEMM of a decode step at 320 tokens (Qwen2.5-7B projections and LM head), with the library GEMM beside it
+        for name, (M, N, K) in {"qkv": (320, 4608, H), "o": (320, H, H), "gate_up": (320, 2 * I, H), "down": (320, H, I),
+                                "lm_head": (320, V, H), "qkv_64tok": (64, 4608, H), "down_tp2": (320, H, I // 2)}.items():
+            A, B = rnd(M, K), rnd(N, K)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            ms = T(lambda: ops.gemm(A, B, None, out, False, False, False, False, 0))
+            ck = T.clocks
+            ms_lib = T(lambda: torch.matmul(A, B.t(), out=out))
+            rec = {"kernel": f"gemm_decode_{name}", "shape": [M, N, K], "ms": round(ms, 4), "ms_library": round(ms_lib, 4),
+                   "ratio_to_library": round(ms_lib / ms, 3), "weight_gbs": round(2.0 * N * K / ms / 1e6, 1),
+                   "frac_hbm": round(2.0 * N * K / ms / 1e6 / pk["hbm_gbs"], 3), "splits": int(ops.gemm_skinny_splits(M, N, K)),
+                   "clocks": {"ours": ck, "library": T.clocks}}
+            print(json.dumps(rec), flush=True)
     if want("fp8"):
         # block-scaled e4m3 (1x128) linear against the bf16 GEMM on the same shapes: decode-sized and prefill-sized rows of
         # the Qwen2.5-7B projections. "fp8_total" includes the on-the-fly quantisation of the activation.

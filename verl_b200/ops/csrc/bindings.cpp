@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 
 namespace {
 
@@ -27,6 +28,12 @@ inline const float* fptr(const OptTensor& t) { return t.has_value() ? t->data_pt
 #define CHECK_BF16(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kBFloat16, #x " must be a CUDA bf16 tensor")
 #define CHECK_F32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kFloat, #x " must be a CUDA fp32 tensor")
 #define CHECK_RC(rc, what) TORCH_CHECK((rc) == 0, what " failed with code ", (rc))
+
+// VERL_B200_SKINNY_GEMM=0 routes GEMMs with few tokens through the general kernel (read once per process).
+static bool skinny_enabled() {
+  static const bool on = [] { const char* v = getenv("VERL_B200_SKINNY_GEMM"); return v == nullptr || v[0] != '0'; }();
+  return on;
+}
 
 // D = A * B^T (+bias).  a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn); rows may be strided.
 Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTensor& out, bool a_mn, bool b_mn,
@@ -55,11 +62,26 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
     bias_ptr = bias->data_ptr();
   }
   if (M == 0 || N == 0) return d;
+  if (skinny_enabled() && M <= 512 && !a_mn && !b_mn && !out_f32 && !accumulate && max_ctas == 0 && N % 8 == 0 && K % 8 == 0 &&
+      a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && d.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(d.data_ptr()) % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0) {
+    // few tokens: the transposed kernel (128 weight rows x all tokens per CTA, K split with the fold inside the launch)
+    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
+    if (s >= 1) {
+      Tensor ws;
+      if (s > 1) ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
+      count(1);
+      const int rc = vb_gemm_skinny(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
+                                    b.stride(0), d.stride(0), s, s > 1 ? ws.data_ptr<float>() : nullptr, 0, cur_stream());
+      TORCH_CHECK(rc == 0, "vb_gemm_skinny failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+      return d;
+    }
+  }
   // skinny GEMMs (decode: few output tiles, deep K) are split along K so that every SM streams weights
   const int splits = (max_ctas == 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
   Tensor ws;
   if (splits > 1) ws = at::empty({splits, M, N}, a.options().dtype(at::kFloat));
-  count(1);  // a K-split GEMM folds its partial sums inside the same kernel
+  count((splits > 1 && !vb_gemm_fold_in_kernel()) ? 2 : 1);  // GEMM (+ the reduce launch of a K-split one)
   const int rc = vb_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
                                  b.stride(0), d.stride(0), a_mn, b_mn, out_f32, accumulate, (int)max_ctas, splits,
                                  splits > 1 ? ws.data_ptr<float>() : nullptr, cur_stream());
@@ -68,7 +90,8 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
 }
 
 int64_t gemm_status() {
-  const int a = vb_gemm_status();
+  int a = vb_gemm_status();
+  if (a == 0) a = vb_gemm_skinny_status();
   int b = vb_attn_status();
   if (b == 0) b = vb_attn_bwd_status();
   if (b == 0) b = vb_fp8_status();
@@ -555,7 +578,16 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   }
   if (M == 0) return d;
   // decode-sized calls (few output tiles, deep K): K-split GEMM over all SMs + one fused reduce / all-reduce kernel
-  const int splits = (splitk_ws.has_value() && !b_mn && rs_rows <= 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
+  int splits = (splitk_ws.has_value() && !b_mn && rs_rows <= 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
+  int skinny = 0;
+  if (splitk_ws.has_value() && !b_mn && rs_rows <= 0 && skinny_enabled() && M <= 512 && K % 8 == 0 && a.stride(0) % 8 == 0 &&
+      b.stride(0) % 8 == 0) {
+    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
+    if (s > 1) {
+      splits = s;
+      skinny = 1;
+    }
+  }
   if (splits > 1 && splitk_ws->numel() >= splits * M * N) {
     CHECK_F32((*splitk_ws));
     count(2);
@@ -563,7 +595,7 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
                                                   b.stride(0), d.stride(0), uptr(part_ptrs), uptr(flag_ptrs),
                                                   reinterpret_cast<unsigned int*>(epoch.data_ptr<int>()), buf_elems,
                                                   (int)part_ptrs.numel(), (int)rank, limit_s, splits, splitk_ws->data_ptr<float>(),
-                                                  cur_stream());
+                                                  skinny, cur_stream());
     TORCH_CHECK(rc2 == 0, "vb_gemm_bf16_splitk_allreduce failed with code ", rc2, " (M=", M, " N=", N, " K=", K, ")");
     return d;
   }
@@ -871,6 +903,8 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_fetch", &gemm_fetch);
+  m.def("gemm_skinny_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)(skinny_enabled() ? vb_gemm_skinny_splits((int)M, (int)N, (int)K) : 0); });
+  m.def("gemm_fold_in_kernel", []() { return (int64_t)vb_gemm_fold_in_kernel(); });
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("scatter_copy_", &scatter_copy_);
   m.def("comm_status", &comm_status);

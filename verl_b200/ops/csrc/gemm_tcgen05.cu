@@ -20,6 +20,7 @@
 
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace vb {
 
@@ -565,7 +566,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           if (before == static_cast<unsigned int>(splits - 1)) {
             if (lane == 0) p.fix_counter[slab] = 0;
             __threadfence();
-            // rows one after the other, lanes across the columns: coalesced reads of every split's row
+            // lanes across the columns (coalesced 1 KB row reads), eight rows per round: the sixteen loads of a split are
+            // all issued before the first is consumed (one warp folds a slab alone, so its latency is on the critical
+            // path of the launch)
             const int colw = n0 + lane * 8;
             if (lane * 8 < BN && colw < p.N) {
               float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -573,32 +576,51 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 #pragma unroll
                 for (int j = 0; j < 8; ++j) b8[j] = __bfloat162float(p.fix_bias[colw + j]);
               }
-              for (int rr = 0; rr < 32; ++rr) {
-                const int rw = m0 + q * 32 + rr;
-                if (rw >= p.M) break;
-                float a8[8];
+              const float* __restrict__ wsb = reinterpret_cast<const float*>(p.D) + colw;
+              const long long split_stride = static_cast<long long>(p.M) * p.ldd;
+              constexpr int RB = 8;
+#pragma unroll 1
+              for (int rr = 0; rr < 32; rr += RB) {
+                const int rbase = m0 + q * 32 + rr;
+                if (rbase >= p.M) break;
+                float a8[RB][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a8[j] = b8[j];
-                const float* ws = reinterpret_cast<const float*>(p.D) + static_cast<long long>(rw) * p.ldd + colw;
+                for (int u = 0; u < RB; ++u)
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) a8[u][j] = b8[j];
                 for (int sp = 0; sp < splits; ++sp) {
-                  const float4 v0 = *reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * p.M * p.ldd);
-                  const float4 v1 = *reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * p.M * p.ldd + 4);
-                  a8[0] += v0.x; a8[1] += v0.y; a8[2] += v0.z; a8[3] += v0.w;
-                  a8[4] += v1.x; a8[5] += v1.y; a8[6] += v1.z; a8[7] += v1.w;
-                }
-                if (p.fix_out_f32) {
-                  float* o = reinterpret_cast<float*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw;
-                  if (p.fix_accumulate) {
+                  float4 v[RB][2];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) a8[j] += o[j];
+                  for (int u = 0; u < RB; ++u) {
+                    const int rw = min(rbase + u, p.M - 1);  // rows past the end re-read the last row; they are not stored
+                    const float* src = wsb + sp * split_stride + static_cast<long long>(rw) * p.ldd;
+                    v[u][0] = __ldcg(reinterpret_cast<const float4*>(src));
+                    v[u][1] = __ldcg(reinterpret_cast<const float4*>(src + 4));
                   }
-                  *reinterpret_cast<float4*>(o) = make_float4(a8[0], a8[1], a8[2], a8[3]);
-                  *reinterpret_cast<float4*>(o + 4) = make_float4(a8[4], a8[5], a8[6], a8[7]);
-                } else {
-                  uint4 v;
-                  v.x = pack_bf16x2(a8[0], a8[1]); v.y = pack_bf16x2(a8[2], a8[3]);
-                  v.z = pack_bf16x2(a8[4], a8[5]); v.w = pack_bf16x2(a8[6], a8[7]);
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw) = v;
+#pragma unroll
+                  for (int u = 0; u < RB; ++u) {
+                    a8[u][0] += v[u][0].x; a8[u][1] += v[u][0].y; a8[u][2] += v[u][0].z; a8[u][3] += v[u][0].w;
+                    a8[u][4] += v[u][1].x; a8[u][5] += v[u][1].y; a8[u][6] += v[u][1].z; a8[u][7] += v[u][1].w;
+                  }
+                }
+#pragma unroll
+                for (int u = 0; u < RB; ++u) {
+                  const int rw = rbase + u;
+                  if (rw >= p.M) break;
+                  if (p.fix_out_f32) {
+                    float* o = reinterpret_cast<float*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw;
+                    if (p.fix_accumulate) {
+#pragma unroll
+                      for (int j = 0; j < 8; ++j) a8[u][j] += o[j];
+                    }
+                    *reinterpret_cast<float4*>(o) = make_float4(a8[u][0], a8[u][1], a8[u][2], a8[u][3]);
+                    *reinterpret_cast<float4*>(o + 4) = make_float4(a8[u][4], a8[u][5], a8[u][6], a8[u][7]);
+                  } else {
+                    uint4 v4;
+                    v4.x = pack_bf16x2(a8[u][0], a8[u][1]); v4.y = pack_bf16x2(a8[u][2], a8[u][3]);
+                    v4.z = pack_bf16x2(a8[u][4], a8[u][5]); v4.w = pack_bf16x2(a8[u][6], a8[u][7]);
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.fix_out) + static_cast<long long>(rw) * p.fix_ldd + colw) = v4;
+                  }
                 }
               }
             }
@@ -930,6 +952,14 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* D, const void* b
                          stream);
 }
 
+// VERL_B200_SPLITK_FOLD=1 folds the partial sums of a K-split GEMM inside the GEMM kernel instead of a second launch
+// (read once per process). Off by default: inside the decode graph the fold by the last-arriving warp measured 0.3 ms
+// per step slower than the reduce kernel, which spreads the same reads over every SM.
+extern "C" int vb_gemm_fold_in_kernel() {
+  static const bool on = [] { const char* v = getenv("VERL_B200_SPLITK_FOLD"); return v != nullptr && v[0] == '1'; }();
+  return on ? 1 : 0;
+}
+
 // k_splits > 1 needs splitk_ws of k_splits * M * N floats.
 static bool g_partials_only = false;  // set by the all-reduce launcher: leave the K-split partial sums in the workspace
 
@@ -964,7 +994,7 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
     // into D inside the GEMM kernel. (When the partials are wanted as they are, or the output has more slabs than the
     // counter table, the separate reduce kernel below does it.)
     const long long slabs = 4LL * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    fold_in_kernel = !g_partials_only && slabs <= FIX_COUNTERS;
+    fold_in_kernel = vb_gemm_fold_in_kernel() && !g_partials_only && slabs <= FIX_COUNTERS;
     if (fold_in_kernel) {
       static unsigned int* counters = nullptr;
       if (counters == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), g_fix_counters);
@@ -1156,18 +1186,25 @@ extern "C" int vb_gemm_bf16_fetch(const void* A, const void* B, void* D, const v
 // Decode-sized variant of the row-parallel linear: the GEMM runs K-split over all SMs into ``splitk_ws``
 // (k_splits * M * N floats), then one kernel folds the splits and performs the all-reduce over peer memory.
 // flag_ptrs need ceil(M * N / 2048) entries; part_ptrs / epoch / limit_s as for vb_gemm_bf16_allreduce.
+extern "C" int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K, long long ldx,
+                              long long ldw, long long ldd, int splits, float* ws, int partials_only, cudaStream_t stream);
 extern "C" int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                                              long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                              const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
                                              int world, int rank, double limit_s, int k_splits, float* splitk_ws,
-                                             cudaStream_t stream) {
+                                             int skinny, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N % 8) || (ldd % 8) || k_splits < 2 || splitk_ws == nullptr) return -1;
   if (world < 1 || world > AR_MAX_RANKS || rank < 0 || rank >= world) return -4;
   if (static_cast<long long>(M) * N > buf_elems) return -5;
-  g_partials_only = true;
-  const int rc = vb_gemm_bf16_ex(A, B, splitk_ws, nullptr, M, N, K, lda, ldb, N, 0, 0, 1, 0, 0, k_splits, splitk_ws, stream);
-  g_partials_only = false;
+  int rc;
+  if (skinny) {  // the transposed kernel for few tokens: k_splits comes from vb_gemm_skinny_splits
+    rc = vb_gemm_skinny(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, k_splits, splitk_ws, 1, stream);
+  } else {
+    g_partials_only = true;
+    rc = vb_gemm_bf16_ex(A, B, splitk_ws, nullptr, M, N, K, lda, ldb, N, 0, 0, 1, 0, 0, k_splits, splitk_ws, stream);
+    g_partials_only = false;
+  }
   if (rc != 0) return rc;
   SplitKAllReduceParams p{};
   p.ws = splitk_ws; p.splits = k_splits; p.total = static_cast<long long>(M) * N; p.N = N;

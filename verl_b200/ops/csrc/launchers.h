@@ -19,7 +19,11 @@ int vb_gemm_bf16_fetch(const void* A, const void* B, void* D, const void* bias, 
 int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                                   long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                   const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
-                                  double limit_s, int k_splits, float* splitk_ws, cudaStream_t stream);
+                                  double limit_s, int k_splits, float* splitk_ws, int skinny, cudaStream_t stream);
+int vb_gemm_skinny_splits(int M, int N, int K);
+int vb_gemm_skinny_status();
+int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K, long long ldx, long long ldw,
+                   long long ldd, int splits, float* ws, int partials_only, cudaStream_t stream);
 int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                              long long ldb, long long ldd, int b_mn, int rs_rows, const unsigned long long* part_ptrs,
                              const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
@@ -32,6 +36,7 @@ int vb_gemm_grouped(int mode, const void* A, const void* B, void* D, int rows_ca
                     long long ldd, int b_mn, int accumulate, int E, const int* tile_expert, const int* num_mtiles,
                     const int* seg_start, cudaStream_t stream);
 int vb_gemm_suggest_splits(int M, int N, int K);
+int vb_gemm_fold_in_kernel();
 int vb_gemm_status();
 int vb_lmhead_num_tiles(int V);
 int vb_lmhead_fwd(const void* hidden, const void* weight, const long long* labels, float inv_temp, float* partial,

@@ -24,6 +24,7 @@ Parity target: ``verl/workers/engine/fsdp/transformer_impl.py`` (``FSDPEngine`` 
 from __future__ import annotations
 
 import json
+import logging
 import math
 import os
 from typing import Any, Callable, Generator, Optional
@@ -39,6 +40,28 @@ from ....ops import native
 from ....utils.device import get_device_name
 from ...config.optimizer import lr_at_step
 from ..base import BaseEngine, EngineRegistry
+
+logger = logging.getLogger(__name__)
+
+
+def _host_has_room(nbytes: int) -> bool:
+    """Whether ``nbytes`` of page-locked host memory can be taken with a wide margin (twice the size plus 16 GB must be
+    available, within the container's memory limit when there is one)."""
+    try:
+        import psutil
+
+        avail = psutil.virtual_memory().available
+        for path in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+            try:
+                raw = open(path).read().strip()
+                if raw.isdigit():
+                    used_path = path.replace("memory.max", "memory.current").replace("limit_in_bytes", "usage_in_bytes")
+                    avail = min(avail, int(raw) - int(open(used_path).read().strip()))
+            except OSError:
+                pass
+        return avail > 2 * nbytes + (16 << 30)
+    except Exception:
+        return False
 
 __all__ = ["NativeEngine", "NativeEngineWithLMHead", "NativeEngineWithValueHead", "pack_padded_batch",
            "collate_multi_modal_inputs"]
@@ -345,6 +368,7 @@ class NativeEngine(BaseEngine):
             self.master = self._owned(self.tparams.flat).float()
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
+            self._setup_optimizer_offload()
             self.grad_shard = None
             self.ctrl = torch.zeros(4, dtype=torch.float32, device=self.device)
             if not self.lazy_grad:
@@ -357,6 +381,7 @@ class NativeEngine(BaseEngine):
         if self.qat.enable and self._shared_params is None:
             assert self.lora is None, "QAT and LoRA are exclusive"
             self._apply_qat()
+        self._setup_param_offload()
         self._initialized = True
 
     def _shard_working_weights(self) -> None:
@@ -430,6 +455,149 @@ class NativeEngine(BaseEngine):
             keep = int(t.item())
         self.last_kept_layers = keep
         return keep
+
+
+    # ------------------------------------------------------------------------------------ host offload
+    _offloaded_states: tuple = ()  # names of the optimizer tensors that live in host memory
+
+    def _setup_optimizer_offload(self) -> None:
+        """``optimizer_offload``: the Adam moments live in pinned host memory and pass through the GPU in chunks during
+        the optimizer step (copy in, fused AdamW, copy out on three streams, so both directions of the host link and the
+        update kernel overlap). ``param_offload`` of a trainable engine adds the fp32 master weights. The memory goes to
+        activations: with the moments of a 7B model on the host a single GPU keeps every layer's activations instead of
+        recomputing most layers. Parity target: ``verl/utils/fsdp_utils.py`` (``offload_fsdp_optimizer`` /
+        ``load_fsdp_optimizer``: whole-state copies before and after the step)."""
+        ec = self.engine_config
+        self._offloaded_states: tuple = ()
+        self._stage: dict = {}
+        if not bool(getattr(ec, "optimizer_offload", False)):
+            return
+        if self.muon is not None or self.fused_comm or self.zero3 or self.lora is not None or self.local_numel:
+            logger.warning("optimizer_offload is implemented for the plain sharded AdamW path; keeping the optimizer state on the device")
+            return
+        names = ["exp_avg", "exp_avg_sq"]
+        qat = getattr(ec, "qat", None) or {}
+        if bool(getattr(ec, "param_offload", False)) and not bool(qat.get("enable", False) if hasattr(qat, "get") else getattr(qat, "enable", False)):
+            names.append("master")
+        cuda = self.device.type == "cuda"
+        if cuda and not _host_has_room(sum(getattr(self, nm).numel() * 4 for nm in names)):
+            logger.warning("optimizer_offload: not enough free host memory for the optimizer state; keeping it on the device")
+            return
+        host = {}
+        try:
+            for nm in names:
+                t = getattr(self, nm)
+                host[nm] = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=cuda)
+                host[nm].copy_(t)
+        except RuntimeError as e:  # page-locking that much memory was refused
+            logger.warning("optimizer_offload: %s; keeping the optimizer state on the device", e)
+            return
+        for nm in names:
+            setattr(self, nm, host[nm])
+        del t, host
+        self._offloaded_states = tuple(names)
+        self.offload_chunk_elems = int(os.environ.get("VERL_B200_OFFLOAD_CHUNK", 32 << 20))
+        if cuda:
+            torch.cuda.empty_cache()
+            self._offload_streams = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
+            c = min(self.offload_chunk_elems, max(1, self.master.numel()))
+            self._stage = {nm: [torch.empty(c, dtype=torch.float32, device=self.device) for _ in range(2)] for nm in names}
+
+    def _offload_sync(self) -> None:
+        """Host copies of the offloaded state are complete (before anything on the host reads them)."""
+        if self._offloaded_states and self.device.type == "cuda":
+            self._offload_streams[1].synchronize()
+
+    def _streamed_adamw(self, own: slice, dst: Optional[slice], lr: float, coef: Optional[float] = None) -> None:
+        """AdamW over the owned range ``own`` with part of the state on the host: chunk by chunk, two staging buffers per
+        offloaded tensor. ``dst``: where the bf16 working weights of the range go (device path; the kernel writes them)."""
+        oc = self.optimizer_config
+        b1, b2 = float(oc.betas[0]), float(oc.betas[1])
+        names, C = self._offloaded_states, self.offload_chunk_elems
+        cuda = self.device.type == "cuda"
+        if cuda:
+            ops = native.ops()
+            cur = torch.cuda.current_stream(self.device)
+            s_in, s_out = self._offload_streams
+            s_in.wait_stream(s_out)  # the previous step's copies to the host are complete before its staging buffers are reused
+            s_in.wait_stream(cur)
+            out_done: list = [None, None]
+        for ci, lo in enumerate(range(own.start, own.stop, C)):
+            hi = min(lo + C, own.stop)
+            k, b = hi - lo, ci % 2
+            part = {nm: getattr(self, nm)[lo:hi] for nm in ("master", "exp_avg", "exp_avg_sq")}
+            if not cuda:
+                g = self.grad_shard[lo:hi] * coef
+                part["exp_avg"].mul_(b1).add_(g, alpha=1 - b1)
+                part["exp_avg_sq"].mul_(b2).addcmul_(g, g, value=1 - b2)
+                bc1, bc2 = 1 - b1 ** self.opt_step_count, 1 - b2 ** self.opt_step_count
+                part["master"].mul_(1 - lr * oc.weight_decay)
+                part["master"].addcdiv_(part["exp_avg"], (part["exp_avg_sq"].sqrt() / math.sqrt(bc2)).add_(oc.eps), value=-lr / bc1)
+                continue
+            with torch.cuda.stream(s_in):
+                if out_done[b] is not None:
+                    s_in.wait_event(out_done[b])
+                for nm in names:
+                    self._stage[nm][b][:k].copy_(part[nm], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            dev = {nm: (self._stage[nm][b][:k] if nm in names else part[nm]) for nm in part}
+            d0 = dst.start + (lo - own.start)
+            ops.adamw_(dev["master"], self.grad_shard[lo:hi], dev["exp_avg"], dev["exp_avg_sq"], self.tparams.flat[d0 : d0 + k],
+                       self.ctrl, lr, b1, b2, float(oc.eps), float(oc.weight_decay), self.opt_step_count, 1.0, False)
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for nm in names:
+                    part[nm].copy_(self._stage[nm][b][:k], non_blocking=True)
+                out_done[b] = torch.cuda.Event()
+                out_done[b].record(s_out)
+
+    def _setup_param_offload(self) -> None:
+        """``param_offload`` of a forward-only engine (the reference policy): the working weights wait in pinned host memory
+        and occupy the device only inside ``eval_mode()``. The parameter views stay valid: the buffer's storage is emptied
+        and refilled in place. Parity target: ``verl/utils/fsdp_utils.py`` (``offload_fsdp_model_to_cpu`` /
+        ``load_fsdp_model_to_gpu``)."""
+        self._param_host = None
+        if not (self.forward_only and bool(getattr(self.engine_config, "param_offload", False)) and self.device.type == "cuda"):
+            return
+        if self._shared_params is not None or self.arch.is_generic:
+            return  # weights that another engine owns stay where their owner keeps them
+        if not _host_has_room(self.params.flat.numel() * self.params.flat.element_size()):
+            logger.warning("param_offload: not enough free host memory for the weights; keeping them on the device")
+            return
+        try:
+            self._param_host = torch.empty(self.params.flat.shape, dtype=self.params.flat.dtype, device="cpu", pin_memory=True)
+        except RuntimeError as e:
+            logger.warning("param_offload: %s; keeping the weights on the device", e)
+            self._param_host = None
+            return
+        self._param_resident = True
+        self._param_dirty = True  # the device copy holds values the host copy has not seen
+
+    def _enter_mode(self, mode: str, **kwargs) -> None:
+        if getattr(self, "_param_host", None) is not None and not self._param_resident:
+            flat = self.params.flat
+            flat.untyped_storage().resize_(self._param_host.numel() * self._param_host.element_size())
+            flat.copy_(self._param_host, non_blocking=True)
+            self._param_resident = True
+
+    def _exit_mode(self, mode: str, **kwargs) -> None:
+        if getattr(self, "_param_host", None) is not None and self._param_resident:
+            if self._param_dirty:
+                self._param_host.copy_(self.params.flat)
+                self._param_dirty = False
+            torch.cuda.current_stream(self.device).synchronize()
+            self.params.flat.untyped_storage().resize_(0)
+            self._param_resident = False
+
+    def mark_params_changed(self) -> None:
+        """The device weights were overwritten from outside (a checkpoint, a weight hand-over): the host copy is stale."""
+        if getattr(self, "_param_host", None) is not None:
+            assert self._param_resident, "write the weights inside eval_mode(): they are on the host now"
+            self._param_dirty = True
 
     # ------------------------------------------------------------------------------------ topology
     def get_data_parallel_size(self) -> int:
@@ -653,7 +821,8 @@ class NativeEngine(BaseEngine):
             return
         self.tparams.attach_main_grad(self._sym_grads.tensor if self.fused_comm else None)
         sl = slice(self.shard_lo, self.shard_lo + self.shard_numel)
-        self.grad_shard = self.tparams.main_grad[sl] if self.sh_world == 1 else torch.zeros_like(self.master)
+        self.grad_shard = self.tparams.main_grad[sl] if self.sh_world == 1 else \
+            torch.zeros(self.master.numel(), dtype=torch.float32, device=self.device)
 
     def _complete_partial_grads(self) -> None:
         """Hook for model-parallel engines: gradients of replicated parameters that every rank of a model-parallel group
@@ -722,7 +891,9 @@ class NativeEngine(BaseEngine):
             self._global_sumsq_correction()
             ops.clip_coef_(self.ctrl, float(oc.clip_grad))
             for own, dst in ((slice(0, n_sh), sl), (slice(n_sh, n_sh + self.local_numel), slice(D, D + self.local_numel))):
-                if own.stop > own.start:
+                if own.stop > own.start and self._offloaded_states:
+                    self._streamed_adamw(own, dst, lr)
+                elif own.stop > own.start:
                     ops.adamw_(self.master[own], self.grad_shard[own], self.exp_avg[own], self.exp_avg_sq[own], self.tparams.flat[dst],
                                self.ctrl, lr, float(oc.betas[0]), float(oc.betas[1]), float(oc.eps), float(oc.weight_decay),
                                self.opt_step_count, 1.0, False)
@@ -737,6 +908,11 @@ class NativeEngine(BaseEngine):
             norm = ss.sqrt().float()
             if torch.isfinite(norm):
                 coef = min(1.0, float(oc.clip_grad) / (float(norm) + 1e-6)) if oc.clip_grad and oc.clip_grad > 0 else 1.0
+                if self._offloaded_states:  # the chunk walk of the offloaded optimizer, with host arithmetic
+                    self._streamed_adamw(slice(0, self.master.numel()), None, lr, coef=coef)
+                    self._scatter_owned(self.master, self.tparams.flat)
+                    coef = None
+            if torch.isfinite(norm) and coef is not None:
                 g = self.grad_shard * coef
                 b1, b2 = oc.betas
                 self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
@@ -889,6 +1065,8 @@ class NativeEngine(BaseEngine):
         tgt = torch.device(device) if device != "cuda" else self.device
         if optimizer:
             for name in ("master", "exp_avg", "exp_avg_sq"):
+                if name in self._offloaded_states:  # lives on the host for good (optimizer_offload)
+                    continue
                 t = getattr(self, name)
                 if t.device != tgt:
                     setattr(self, name, t.to(tgt, non_blocking=True))
@@ -898,6 +1076,8 @@ class NativeEngine(BaseEngine):
     def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
                         max_ckpt_to_keep: Optional[int] = None, **kwargs) -> None:
         os.makedirs(local_path, exist_ok=True)
+        if not self.forward_only:
+            self._offload_sync()
         W, r = self.sh_world, self.sh_rank  # replicas of a block hold identical shards: block 0 writes, everyone reads
         if self.rep_rank != 0:
             if self.world > 1:
@@ -990,6 +1170,10 @@ class NativeEngine(BaseEngine):
                         **kwargs) -> None:
         if local_path is None:
             return
+        if getattr(self, "_param_host", None) is not None:  # weights offloaded to the host: make them resident, the load overwrites them
+            self._enter_mode("eval")
+            self._param_dirty = True
+        self._offload_sync()
         W, r = self.sh_world, self.sh_rank
         contents = list(getattr(self.checkpoint_config, "load_contents", ["model", "optimizer", "extra"]) or [])
         if not os.path.isdir(local_path):

@@ -273,6 +273,9 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                 object.__setattr__(rec, "use_dynamic_bsz", bool(rcfg.get("log_prob_use_dynamic_bsz", False)))
                 if rcfg.get("log_prob_max_token_len_per_gpu"):
                     object.__setattr__(rec, "infer_max_token_len_per_gpu", rcfg.get("log_prob_max_token_len_per_gpu"))
+                rfc = rcfg.get("fsdp_config")
+                if rfc is not None and bool(rfc.get("param_offload", False) if hasattr(rfc, "get") else getattr(rfc, "param_offload", False)):
+                    object.__setattr__(rec, "param_offload", True)
             if self.actor is not None and getattr(self.actor, "topo", None) is not None:  # same model-parallel layout as the actor
                 from .config import McoreEngineConfig
 

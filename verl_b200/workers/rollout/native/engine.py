@@ -142,6 +142,7 @@ class RolloutEngine:
         self.running: dict[int, _Request] = {}
         self.finished: list[RequestOutput] = []
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
+        self._decode_events: list = []
         self._alloc_state()
         self.resume_kv_cache()
         if self.quantization == "fp8":
@@ -289,6 +290,8 @@ class RolloutEngine:
         # beat that (12.9 ms); VERL_B200_GROUPED_DECODE=1 turns it on.
         nh_l = self.cfg.num_attention_heads // self.tp_size
         nkv_l = self.cfg.num_key_value_heads // self.tp_size
+        # VERL_B200_FUSED_ROPE_APPEND=0: rotate q, rotate k and append to the cache as three launches instead of one
+        self.fused_rope_append = os.environ.get("VERL_B200_FUSED_ROPE_APPEND", "1") != "0"
         self.grouped_decode = (self.is_cuda and self.share_prefill and self.bs == 64 and self.cfg.head_dim in (64, 128)
                                and nh_l // max(1, nkv_l) <= 16 and os.environ.get("VERL_B200_GROUPED_DECODE", "0") == "1")
         self._groups: dict[int, list[int]] = {}
@@ -712,7 +715,7 @@ class RolloutEngine:
                 kn = F.rms_norm(k.reshape(S * nkv, hd).contiguous(), W["self_attn.k_norm.weight"], cfg.rms_norm_eps)[0]
                 q.copy_(qn.view(S, nh, hd))
                 k.copy_(kn.view(S, nkv, hd))
-            if cfg.qk_norm or not qkv.is_contiguous():
+            if cfg.qk_norm or not qkv.is_contiguous() or not self.fused_rope_append:
                 F.apply_rope_(q, self.pos, cos, sin)
                 F.apply_rope_(k, self.pos, cos, sin)
                 F.kv_append_(k, v, slot_map, self.kv[i, 0], self.kv[i, 1])
@@ -758,6 +761,10 @@ class RolloutEngine:
     @torch.no_grad()
     def _decode_steps(self, n: int) -> None:
         t0 = time.time()
+        ev = None
+        if self.is_cuda:  # device time of the decode steps, read at the next host synchronisation (``_sync_retire``)
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         if not self.use_graph or self.cfg.is_moe:
             for _ in range(n):
                 self._decode_body()
@@ -788,6 +795,9 @@ class RolloutEngine:
             from ....ops import native
 
             native.add_launches(self._graph_kernels * n)
+        if ev is not None:
+            ev[1].record()
+            self._decode_events.append(ev)
         self.stats["decode_steps"] += n
         self.stats["decode_s"] += time.time() - t0
 
@@ -797,6 +807,10 @@ class RolloutEngine:
             return
         active = self.active.cpu()
         gen = self.gen.cpu()
+        if self._decode_events:
+            self._decode_events[-1][1].synchronize()
+            self.stats["decode_gpu_s"] = self.stats.get("decode_gpu_s", 0.0) + sum(a.elapsed_time(b) for a, b in self._decode_events) * 1e-3
+            self._decode_events.clear()
         done_slots = [s for s, r in self.running.items()
                       if (not bool(active[s])) or (abort and (force_rids is None or r.rid in force_rids))]
         if not done_slots:
