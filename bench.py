@@ -65,9 +65,8 @@ def parse_args():
                    help="pack every sample's prompt separately in the log-prob / training passes and prefill it separately "
                         "(default: the n samples of a prompt share its tokens; results are identical)")
     p.add_argument("--offload", default="auto", choices=["auto", "on", "off"],
-                   help="Adam moments and the reference policy's weights in pinned host memory (optimizer_offload / ref param_offload), "
-                        "which leaves the GPU's memory to activations instead of recomputation; auto = on one GPU, where the whole "
-                        "unsharded optimizer state would sit on it")
+                   help="second Adam moment in pinned host memory (optimizer_offload), which leaves the GPU's memory to activations "
+                        "instead of recomputation; auto = on one GPU, where the whole unsharded optimizer state would sit on it")
     p.add_argument("--critic", action="store_true", help="PPO with a critic of the same architecture and GAE instead of GRPO")
     return p.parse_args()
 
@@ -140,7 +139,9 @@ def build_config(args, world: int):
         "trainer.worker_group=spmd", f"trainer.device={args.device}",
     ]
     if args.offload == "on" or (args.offload == "auto" and world == 1 and args.train_tp * args.train_pp * args.train_ep == 1):
-        ov += ["actor_rollout_ref.actor.fsdp_config.optimizer_offload=true", "actor_rollout_ref.ref.fsdp_config.param_offload=true"]
+        # the second Adam moment alone (4 bytes per parameter) makes room for every layer's activations of a 7B model
+        ov += ["actor_rollout_ref.actor.fsdp_config.optimizer_offload=true",
+               "actor_rollout_ref.actor.fsdp_config.optimizer_offload_states=exp_avg_sq"]
     if args.layers > 0:
         ov += [f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}"]
     mp = args.train_tp * args.train_pp
@@ -300,7 +301,7 @@ def main():
                        "algorithm": "ppo+critic+gae" if args.critic else "grpo",
                        **({"reduced_model_layers": args.layers} if args.layers > 0 else {}),
                        "shared_prompt_packing": not args.no_prefix_sharing,
-                       "host_offload": "adam moments + reference weights" if getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "_offloaded_states", ()) else "none",
+                       "host_offload": ",".join(getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "_offloaded_states", ())) or "none",
                        "kept_activation_layers": getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "last_kept_layers", None),
                        "l2": "inputs_larger_than_L2 (15 GB of weights stream through every pass)",
                        "time_budget_s": args.time_budget_s,
@@ -314,6 +315,9 @@ def main():
             "clocks": (sampler.stop() if not partial else sampler.snapshot()) if sampler else None,
             "phases_s": {name: round(v / k, 3) for name, v in phase_sum.items()},
         }
+        opt_s = getattr(getattr(trainer.actor_rollout_wg.worker, "actor", None), "last_optimizer_step_s", None)
+        if opt_s is not None:
+            out["optimizer_step_s"] = round(float(opt_s), 3)  # the last step's, inside update_actor
         eng = getattr(trainer.actor_rollout_wg.worker, "rollout", None)
         st = getattr(eng, "stats", None)
         if isinstance(st, dict) and st.get("decode_steps"):

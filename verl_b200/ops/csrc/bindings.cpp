@@ -35,6 +35,12 @@ static bool skinny_enabled() {
   return on;
 }
 
+// Rows per launch of the transposed kernel: at most 512, equal blocks (a multiple of 16 rows) for more.
+static int skinny_rows(int64_t M) {
+  const int64_t blocks = (M + 511) / 512;
+  return (int)(((M + blocks - 1) / blocks + 15) / 16 * 16);
+}
+
 // D = A * B^T (+bias).  a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn); rows may be strided.
 Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTensor& out, bool a_mn, bool b_mn,
             bool out_f32, bool accumulate, int64_t max_ctas) {
@@ -62,18 +68,25 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
     bias_ptr = bias->data_ptr();
   }
   if (M == 0 || N == 0) return d;
-  if (skinny_enabled() && M <= 512 && !a_mn && !b_mn && !out_f32 && !accumulate && max_ctas == 0 && N % 8 == 0 && K % 8 == 0 &&
+  if (skinny_enabled() && M <= 1024 && !a_mn && !b_mn && !out_f32 && !accumulate && max_ctas == 0 && N % 8 == 0 && K % 8 == 0 &&
       a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && d.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(d.data_ptr()) % 8 == 0 &&
       reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0) {
-    // few tokens: the transposed kernel (128 weight rows x all tokens per CTA, K split with the fold inside the launch)
-    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
+    // few tokens: the transposed kernel (128 weight rows x all tokens per CTA, K split with the fold inside the launch);
+    // more than 512 tokens go in equal row blocks, one launch each (the weights of the later blocks come from L2)
+    const int rb = skinny_rows(M);
+    const int s = vb_gemm_skinny_splits(rb, (int)N, (int)K);
     if (s >= 1) {
       Tensor ws;
       if (s > 1) ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
-      count(1);
-      const int rc = vb_gemm_skinny(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0),
-                                    b.stride(0), d.stride(0), s, s > 1 ? ws.data_ptr<float>() : nullptr, 0, cur_stream());
-      TORCH_CHECK(rc == 0, "vb_gemm_skinny failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+      const auto* ap = reinterpret_cast<const at::BFloat16*>(a.data_ptr());
+      auto* dp = reinterpret_cast<at::BFloat16*>(d.data_ptr());
+      for (int64_t r0 = 0; r0 < M; r0 += rb) {
+        const int rows = (int)std::min<int64_t>(rb, M - r0);
+        count(1);
+        const int rc = vb_gemm_skinny(ap + r0 * a.stride(0), b.data_ptr(), dp + r0 * d.stride(0), bias_ptr, rows, (int)N, (int)K, a.stride(0),
+                                      b.stride(0), d.stride(0), s, s > 1 ? ws.data_ptr<float>() + r0 * N : nullptr, (int)M, 0, cur_stream());
+        TORCH_CHECK(rc == 0, "vb_gemm_skinny failed with code ", rc, " (M=", rows, " of ", M, " N=", N, " K=", K, ")");
+      }
       return d;
     }
   }
@@ -580,12 +593,13 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   // decode-sized calls (few output tiles, deep K): K-split GEMM over all SMs + one fused reduce / all-reduce kernel
   int splits = (splitk_ws.has_value() && !b_mn && rs_rows <= 0) ? vb_gemm_suggest_splits((int)M, (int)N, (int)K) : 1;
   int skinny = 0;
-  if (splitk_ws.has_value() && !b_mn && rs_rows <= 0 && skinny_enabled() && M <= 512 && K % 8 == 0 && a.stride(0) % 8 == 0 &&
-      b.stride(0) % 8 == 0) {
-    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
+  if (splitk_ws.has_value() && !b_mn && rs_rows <= 0 && skinny_enabled() && M <= 1024 && K % 8 == 0 && a.stride(0) % 8 == 0 &&
+      b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0) {
+    const int rb = skinny_rows(M);
+    const int s = vb_gemm_skinny_splits(rb, (int)N, (int)K);
     if (s > 1) {
       splits = s;
-      skinny = 1;
+      skinny = rb;  // rows per launch of the transposed kernel
     }
   }
   if (splits > 1 && splitk_ws->numel() >= splits * M * N) {
@@ -903,7 +917,9 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("allreduce_peer_", &allreduce_peer_);
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_fetch", &gemm_fetch);
-  m.def("gemm_skinny_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)(skinny_enabled() ? vb_gemm_skinny_splits((int)M, (int)N, (int)K) : 0); });
+  m.def("gemm_skinny_splits", [](int64_t M, int64_t N, int64_t K) {
+    return (int64_t)((skinny_enabled() && M <= 1024) ? vb_gemm_skinny_splits(skinny_rows(M), (int)N, (int)K) : 0);
+  });
   m.def("gemm_fold_in_kernel", []() { return (int64_t)vb_gemm_fold_in_kernel(); });
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("scatter_copy_", &scatter_copy_);

@@ -44,6 +44,7 @@ struct SkinnyParams {
   long long ldd;
   const __nv_bfloat16* bias;
   float* ws;
+  long long ws_split_stride;  // floats between the partial sums of consecutive splits
   unsigned int* arrive;  // per weight tile: split CTAs that have written their partial sums
   unsigned int* done;    // per weight tile: split CTAs that have finished folding
   int* status;
@@ -198,7 +199,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       acc_phase ^= 1;
       const bool direct = p.splits == 1;
       const float bv = (direct && p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.f;
-      float* wsp = p.ws + (static_cast<long long>(sp) * p.M) * p.N + n;
+      float* wsp = p.ws + static_cast<long long>(sp) * p.ws_split_stride + n;
       __nv_bfloat16* dp = p.D + n;
 #pragma unroll 1
       for (int c = 0; c < chunks; ++c) {
@@ -253,7 +254,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             b4.z = __bfloat162float(p.bias[col + 2]); b4.w = __bfloat162float(p.bias[col + 3]);
           }
           const float* __restrict__ src = p.ws + col;
-          const long long split_stride = static_cast<long long>(p.M) * p.N;
+          const long long split_stride = p.ws_split_stride;
           constexpr int RB = 4;  // rows in flight per thread
 #pragma unroll 1
           for (int m = r0 + (et >> 5); m < r1; m += 4 * RB) {
@@ -364,10 +365,12 @@ extern "C" int vb_gemm_skinny_status() {
 // D[M, N] (bf16, row stride ldd) = X[M, K] W[N, K]^T (+bias). splits: the value vb_gemm_skinny_splits returned (or a
 // forced count together with partials_only); ws: fp32 workspace of splits * M * N floats when splits > 1.
 // partials_only != 0: leave the partial sums in ws as [splits][M][N] and do not touch D (bias is ignored).
+// ws_rows: rows between consecutive splits in ws (0 = M); a caller that covers more than 512 tokens with several
+// launches passes the total row count and offsets X, D and ws by the rows of each launch.
 // Returns 0 on success, a negative code for arguments the kernel does not serve, a positive cudaError_t otherwise.
 extern "C" int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K,
-                              long long ldx, long long ldw, long long ldd, int splits, float* ws, int partials_only,
-                              cudaStream_t stream) {
+                              long long ldx, long long ldw, long long ldd, int splits, float* ws, int ws_rows,
+                              int partials_only, cudaStream_t stream) {
   SkinnyParams p{};
   if (!sk_plan(M, N, K, splits, p)) return -1;
   if (splits > 0 && p.splits != splits) return -4;  // the caller sized ws for another split count
@@ -393,6 +396,7 @@ extern "C" int vb_gemm_skinny(const void* X, const void* W, void* D, const void*
   p.ldd = ldd;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.ws = ws;
+  p.ws_split_stride = static_cast<long long>(ws_rows > 0 ? ws_rows : M) * N;
   // launches in flight at the same time (several streams) must not share counters
   static unsigned int launch_seq = 0;
   const unsigned int slot = (launch_seq++ % (SK_COUNTERS / SK_SLOT)) * SK_SLOT;

@@ -1187,7 +1187,8 @@ extern "C" int vb_gemm_bf16_fetch(const void* A, const void* B, void* D, const v
 // (k_splits * M * N floats), then one kernel folds the splits and performs the all-reduce over peer memory.
 // flag_ptrs need ceil(M * N / 2048) entries; part_ptrs / epoch / limit_s as for vb_gemm_bf16_allreduce.
 extern "C" int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K, long long ldx,
-                              long long ldw, long long ldd, int splits, float* ws, int partials_only, cudaStream_t stream);
+                              long long ldw, long long ldd, int splits, float* ws, int ws_rows, int partials_only,
+                              cudaStream_t stream);
 extern "C" int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const void* bias, int M, int N, int K,
                                              long long lda, long long ldb, long long ldd, const unsigned long long* part_ptrs,
                                              const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems,
@@ -1198,8 +1199,14 @@ extern "C" int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void*
   if (world < 1 || world > AR_MAX_RANKS || rank < 0 || rank >= world) return -4;
   if (static_cast<long long>(M) * N > buf_elems) return -5;
   int rc;
-  if (skinny) {  // the transposed kernel for few tokens: k_splits comes from vb_gemm_skinny_splits
-    rc = vb_gemm_skinny(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, k_splits, splitk_ws, 1, stream);
+  if (skinny > 0) {
+    // the transposed kernel for few tokens, `skinny` rows per launch: k_splits comes from vb_gemm_skinny_splits(skinny, N, K)
+    rc = 0;
+    for (int r0 = 0; r0 < M && rc == 0; r0 += skinny) {
+      const int rows = M - r0 < skinny ? M - r0 : skinny;
+      rc = vb_gemm_skinny(reinterpret_cast<const __nv_bfloat16*>(A) + static_cast<long long>(r0) * lda, B, nullptr, nullptr, rows, N, K,
+                          lda, ldb, N, k_splits, splitk_ws + static_cast<long long>(r0) * N, M, 1, stream);
+    }
   } else {
     g_partials_only = true;
     rc = vb_gemm_bf16_ex(A, B, splitk_ws, nullptr, M, N, K, lda, ldb, N, 0, 0, 1, 0, 0, k_splits, splitk_ws, stream);

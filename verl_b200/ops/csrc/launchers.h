@@ -23,7 +23,7 @@ int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const v
 int vb_gemm_skinny_splits(int M, int N, int K);
 int vb_gemm_skinny_status();
 int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K, long long ldx, long long ldw,
-                   long long ldd, int splits, float* ws, int partials_only, cudaStream_t stream);
+                   long long ldd, int splits, float* ws, int ws_rows, int partials_only, cudaStream_t stream);
 int vb_gemm_bf16_allreduce_ex(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
                              long long ldb, long long ldd, int b_mn, int rs_rows, const unsigned long long* part_ptrs,
                              const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,

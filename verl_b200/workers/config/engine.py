@@ -22,6 +22,10 @@ class EngineConfig(BaseConfig):
     strategy: str = "fsdp"
     param_offload: bool = False
     optimizer_offload: bool = False
+    # which Adam state optimizer_offload keeps in pinned host memory: "moments" (exp_avg and exp_avg_sq) or one of the two
+    # by name; every offloaded tensor crosses the host link twice per optimizer step, so offload no more than the
+    # activations need
+    optimizer_offload_states: str = "moments"
     grad_offload: bool = False
     forward_only: bool = False
     dtype: str = "bfloat16"

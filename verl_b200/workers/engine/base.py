@@ -49,7 +49,15 @@ class BaseEngine(ABC):
         """zero-grad -> forward/backward over micro-batches -> optimizer step -> scheduler step."""
         self.optimizer_zero_grad()
         out = self.forward_backward_batch(data, loss_function, forward_only=False)
+        ev = None
+        if torch.cuda.is_available() and getattr(getattr(self, "device", None), "type", "cpu") == "cuda":
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         grad_norm = self.optimizer_step()
+        if ev is not None:  # device time of the optimizer step (gradient reduction, clip, update, weight publication)
+            ev[1].record()
+            ev[1].synchronize()
+            self.last_optimizer_step_s = ev[0].elapsed_time(ev[1]) * 1e-3
         lr = self.lr_scheduler_step()
         out.setdefault("metrics", {})
         out["metrics"]["grad_norm"] = grad_norm

@@ -475,7 +475,9 @@ class NativeEngine(BaseEngine):
         if self.muon is not None or self.fused_comm or self.zero3 or self.lora is not None or self.local_numel:
             logger.warning("optimizer_offload is implemented for the plain sharded AdamW path; keeping the optimizer state on the device")
             return
-        names = ["exp_avg", "exp_avg_sq"]
+        which = str(getattr(ec, "optimizer_offload_states", "moments") or "moments")
+        assert which in ("moments", "exp_avg", "exp_avg_sq"), f"optimizer_offload_states={which!r}"
+        names = ["exp_avg", "exp_avg_sq"] if which == "moments" else [which]
         qat = getattr(ec, "qat", None) or {}
         if bool(getattr(ec, "param_offload", False)) and not bool(qat.get("enable", False) if hasattr(qat, "get") else getattr(qat, "enable", False)):
             names.append("master")
