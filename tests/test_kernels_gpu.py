@@ -82,7 +82,7 @@ def test_gemm_k_split(ops, shape):
                                    (77, 152, 200), (130, 1024, 8192), (256, 3584, 3584), (257, 520, 1024), (512, 4608, 3584),
                                    (320, 2304, 3584), (64, 151936, 896), (640, 4608, 3584), (640, 3584, 1792), (1000, 264, 512)])
 def test_gemm_few_tokens_transposed_kernel(ops, shape):
-    """Up to 512 tokens per launch (up to 1024 as two row blocks): the kernel that puts 128 weight rows on the tensor core's M axis and all tokens on its N axis, K
+    """Up to 512 tokens per CTA (up to 1024 as two token blocks of the same launch): the kernel that puts 128 weight rows on the tensor core's M axis and all tokens on its N axis, K
     split over CTAs whose partial sums every split folds for its own share of the rows inside the same launch. Against
     the fp32 product, with bias, row-strided input and output, several launches in a row (the counters of a tile return
     to zero), and bit-equal across launches."""
@@ -96,7 +96,7 @@ def test_gemm_few_tokens_transposed_kernel(ops, shape):
     ref = A.float() @ B.float().t() + bias.float()
     n0 = int(ops.launch_count())
     outs = [ops.gemm(A, B, bias, None, False, False, False, False, 0) for _ in range(3)]
-    assert int(ops.launch_count()) - n0 == 3 * -(-M // 512)
+    assert int(ops.launch_count()) - n0 == 3
     torch.cuda.synchronize()
     assert int(ops.gemm_status()) == 0
     assert rel(outs[0], ref) < 1e-2
@@ -109,6 +109,53 @@ def test_gemm_few_tokens_transposed_kernel(ops, shape):
     assert rel(big[:, 8 : 8 + N], ref - bias.float()) < 1e-2
     assert bool((big[:, :8] == 7).all()) and bool((big[:, 8 + N :] == 7).all())
     assert int(ops.gemm_status()) == 0
+
+
+@pytest.mark.parametrize("M", [320, 640, 37, 1000])
+def test_gemm_row_ranges_of_a_fused_weight(ops, M):
+    """The q | k | v rows of one tensor-parallel rank inside the replicated fused projection weight (and gate | up; ranges
+    that are no multiple of 128 rows) as one launch: outputs side by side, bias taken by weight row."""
+    from verl_b200.ops import functional as F
+
+    torch.manual_seed(5)
+    K = 3584
+    for total, ranges in ((4608, [(1792, 1792), (3584 + 256, 256), (4096 + 256, 256)]), (2 * 1184, [(0, 592), (1184, 592)]),
+                          (1024, [(8, 200), (512, 72), (600, 128), (900, 24)])):
+        A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+        Wt = (torch.randn(total, K, device=DEV) * 0.5).bfloat16()
+        bias = torch.randn(total, device=DEV).bfloat16()
+        n0 = int(ops.launch_count())
+        out = F.gemm_row_ranges(A, Wt, bias, ranges)
+        assert int(ops.launch_count()) - n0 == 1
+        ref = torch.cat([A.float() @ Wt[w0 : w0 + r].float().t() + bias[w0 : w0 + r].float() for w0, r in ranges], dim=1)
+        assert out.shape == ref.shape and rel(out, ref) < 1e-2
+        out2 = F.gemm_row_ranges(A, Wt, None, ranges)
+        assert rel(out2, ref - torch.cat([bias[w0 : w0 + r].float() for w0, r in ranges]).unsqueeze(0)) < 1e-2
+    torch.cuda.synchronize()
+    assert int(ops.gemm_status()) == 0
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 200), (2048, 1184, 512), (1500, 4736, 3584), (128, 64, 64)])
+def test_gemm_with_swiglu_epilogue(ops, shape):
+    """Up-projection of a gated MLP with the activation in the GEMM epilogue: the stacked [gate; up] weight is read through
+    a 3-D tensor map that interleaves the halves row by row, so that a thread holds both members of every pair. Against
+    the fp32 product; the pre-activation output has the stacked layout of the separate GEMM."""
+    M, I, K = shape
+    torch.manual_seed(4)
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    Wt = (torch.randn(2 * I, K, device=DEV) * 0.1).bfloat16()
+    gu_ref = A.float() @ Wt.float().t()
+    act_ref = torch.nn.functional.silu(gu_ref[:, :I]) * gu_ref[:, I:]
+    act, gu = ops.gemm_swiglu(A, Wt, True)
+    torch.cuda.synchronize()
+    assert int(ops.gemm_status()) == 0
+    assert act.shape == (M, I) and gu.shape == (M, 2 * I)
+    assert rel(gu, gu_ref) < 1e-2 and rel(act, act_ref) < 1e-2
+    act2, none = ops.gemm_swiglu(A, Wt, False)
+    assert none.numel() == 0 and torch.equal(act, act2)
+    # the separate kernels on the same inputs agree up to the bf16 rounding of the pre-activation
+    sep = ops.swiglu_fwd(ops.gemm(A, Wt, None, None, False, False, False, False, 0))
+    assert rel(act, sep) < 2e-2
 
 
 def test_rmsnorm_fwd_bwd(ops):

@@ -408,11 +408,18 @@ def _sec_peer_reshard(rank, world, dev, ops, res):
         res[f"{name}_created"] = plan is not None
         if plan is None:
             continue
+        def differing(plan, eng):
+            """Names of the tensors whose replica differs from the collective gather (alignment gaps between tensors belong
+            to nobody and are not compared)."""
+            want = eng.gather_full_params()
+            return [n for n, v in plan.full.views.items() if not torch.equal(v, want.views[n].to(v.dtype))]
+
         plan.full.flat.fill_(7.0)                       # stale replica content must be overwritten everywhere
         plan.run()
         torch.cuda.synchronize()
-        want = eng.gather_full_params().flat.to(plan.full.flat.dtype)
-        res[f"{name}_equal_0"] = bool(torch.equal(plan.full.flat[: want.numel()], want))
+        bad = differing(plan, eng)
+        res[f"{name}_equal_0"] = not bad
+        res[f"{name}_bad_0"] = bad[:4]
         g = torch.Generator().manual_seed(300 + (0 if name == "tp" else rank))
         ids = torch.randint(3, 1024, (4, 40), generator=g)
         am = torch.ones_like(ids)
@@ -420,8 +427,9 @@ def _sec_peer_reshard(rank, world, dev, ops, res):
         eng.train_batch(dict(data), partial(sft_loss, None))
         plan.run()
         torch.cuda.synchronize()
-        want = eng.gather_full_params().flat.to(plan.full.flat.dtype)
-        res[f"{name}_equal_1"] = bool(torch.equal(plan.full.flat[: want.numel()], want))
+        bad = differing(plan, eng)
+        res[f"{name}_equal_1"] = not bad
+        res[f"{name}_bad_1"] = bad[:4]
         res[f"{name}_jobs"] = (int(plan.jobs.shape[0]), int(plan.total_blocks), int(plan.bytes_per_run))
         del eng, plan
         torch.cuda.empty_cache()
@@ -493,6 +501,8 @@ def _sec_sequence_and_context_parallel(rank, world, dev, ops, res):
         lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float().clone()
         norm = float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"])
         out[name] = (lp, norm, eng.params.flat.float().clone())
+        if name == "ulysses":
+            res["ulysses_over_peer_memory"] = bool(getattr(eng.model.sp, "_peer", None))
         del eng
         torch.cuda.empty_cache()
     os.environ["VERL_B200_FUSED_COMM"] = "1"
@@ -501,6 +511,31 @@ def _sec_sequence_and_context_parallel(rank, world, dev, ops, res):
         res[f"{name}_lp_diff"] = (out[name][0][m] - out["plain"][0][m]).abs().max().item()
         res[f"{name}_norms"] = (out[name][1], out["plain"][1])
         res[f"{name}_param_diff"] = (out[name][2] - out["plain"][2]).abs().max().item()
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
+def _sec_peer_all_to_all(rank, world, dev, ops, res):
+    """The Ulysses head <-> sequence exchange as one peer-store kernel between two barriers, against the collective
+    all-to-all: bit-equal, from a strided source (the query slice of a fused projection), several sizes in a row (the
+    buffer grows), and back."""
+    import torch.distributed as dist
+
+    from verl_b200.models.decoder import UlyssesSequenceParallel
+    from verl_b200.parallel.symmetric import PeerAllToAll
+
+    a2a = PeerAllToAll(dev)
+    ref = UlyssesSequenceParallel(dist.group.WORLD, rank, world)
+    ref._peer = False                                         # the collective formulation
+    ok = True
+    for i, (tl, h, d) in enumerate([(37, 4, 128), (300, 8, 64), (1024, 28, 128), (5, 2, 64)]):
+        g = torch.Generator().manual_seed(100 * i + rank)
+        wide = torch.randn(tl, h * d + 256, generator=g).to(dev).bfloat16()
+        x = wide[:, : h * d].view(tl, h, d)                   # row stride wider than the rows
+        y = a2a.seq_to_heads(x)
+        ok &= torch.equal(y, ref.seq_to_heads(x))
+        ok &= torch.equal(a2a.heads_to_seq(y), x)
+        ok &= torch.equal(ref.heads_to_seq(y), x)
+    res["equal"] = bool(ok)
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
@@ -670,8 +705,14 @@ def test_tensor_parallel_training_with_fused_collectives(pair):
         assert res["status"] == (0, 0), res
 
 
+def test_ulysses_exchange_over_peer_memory(pair):
+    for res in pair.run("peer_all_to_all").values():
+        assert res["equal"] and res["status"] == (0, 0), res
+
+
 def test_sequence_and_context_parallel_on_gpus(pair):
     for res in pair.run("sequence_and_context_parallel", timeout=600).values():
+        assert res["ulysses_over_peer_memory"], res
         for name in ("ulysses", "context"):
             a, b = res[f"{name}_norms"]
             assert res[f"{name}_lp_diff"] < 5e-2 and abs(a - b) < 2e-2 * max(1.0, b) and res[f"{name}_param_diff"] < 2e-2, res

@@ -109,6 +109,24 @@ class UlyssesSequenceParallel:
 
     def __init__(self, group, rank: int, size: int):
         self.group, self.rank, self.size = group, int(rank), int(size)
+        self._peer = None  # PeerAllToAll, created at the first exchange on GPUs with peer-mapped memory
+
+    def _peer_exchange(self, x: torch.Tensor):
+        """The peer-memory exchange for this group, or None (CPU, one rank, no peer-mapped memory, VERL_B200_PEER_ULYSSES=0):
+        the collective formulation is used then. Every rank of the group takes the same branch."""
+        if self._peer is None:
+            import os
+
+            self._peer = False
+            if x.is_cuda and self.size > 1 and os.environ.get("VERL_B200_PEER_ULYSSES", "1") != "0":
+                from ..parallel.symmetric import PeerAllToAll, symmetric_available
+
+                if symmetric_available():
+                    try:
+                        self._peer = PeerAllToAll(x.device, self.group)
+                    except Exception:  # no peer mapping for this group: stay on the collective
+                        self._peer = False
+        return self._peer or None
 
     def local_slice(self, total: int) -> slice:
         assert total % self.size == 0, "the packed stream must be padded to a multiple of the sequence-parallel size"
@@ -135,6 +153,10 @@ class UlyssesSequenceParallel:
 
         tl, h, d = x.shape
         hs = h // self.size
+        peer = self._peer_exchange(x)
+        if peer is not None and x.stride(2) == 1 and x.stride(1) == d and (hs * d * x.element_size()) % 16 == 0 and \
+                (x.stride(0) * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0:
+            return peer.seq_to_heads(x)
         send = x.view(tl, self.size, hs, d).permute(1, 0, 2, 3).contiguous()  # [size, tl, hs, d]: block j goes to rank j
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=self.group)                  # block i came from rank i: its tokens, my heads
@@ -146,6 +168,9 @@ class UlyssesSequenceParallel:
 
         t, hs, d = x.shape
         tl = t // self.size
+        peer = self._peer_exchange(x)
+        if peer is not None and x.is_contiguous() and (hs * d * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0:
+            return peer.heads_to_seq(x)
         send = x.view(self.size, tl, hs, d).contiguous()                      # block j: rank j's tokens, my heads
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=self.group)                  # block i: my tokens, rank i's heads
@@ -499,22 +524,14 @@ class DecoderModel:
         Q, KV = cfg.q_size, cfg.kv_size
         Ql, KVl = Q // tp.size, KV // tp.size
         w, b = W["self_attn.qkv_proj.weight"], W.get("self_attn.qkv_proj.bias")
-        out = torch.empty(h1.shape[0], Ql + 2 * KVl, dtype=h1.dtype, device=h1.device)
-        col = 0
-        for base, width in ((0, Ql), (Q, KVl), (Q + KV, KVl)):
-            rows = slice(base + tp.rank * width, base + (tp.rank + 1) * width)
-            F.gemm(h1, w[rows], b[rows] if b is not None else None, out=out[:, col : col + width])
-            col += width
-        return out
+        return F.gemm_row_ranges(h1, w, b, [(tp.rank * Ql, Ql), (Q + tp.rank * KVl, KVl), (Q + KV + tp.rank * KVl, KVl)])
 
     def mlp_tp(self, W, h2: torch.Tensor) -> torch.Tensor:
         cfg, tp = self.cfg, self.tp
         I = cfg.intermediate_size
         Il = I // tp.size
         w = W["mlp.gate_up_proj.weight"]
-        gu = torch.empty(h2.shape[0], 2 * Il, dtype=h2.dtype, device=h2.device)
-        F.gemm(h2, w[tp.rank * Il : (tp.rank + 1) * Il], out=gu[:, :Il])
-        F.gemm(h2, w[I + tp.rank * Il : I + (tp.rank + 1) * Il], out=gu[:, Il:])
+        gu = F.gemm_row_ranges(h2, w, W.get("mlp.gate_up_proj.bias"), [(tp.rank * Il, Il), (I + tp.rank * Il, Il)])
         return tp.row_linear(F.swiglu(gu), W["mlp.down_proj.weight"][:, tp.rows(I)], None)
 
     def _attn_bwd(self, W, g_o, h1, batch: PackedBatch, S: dict):
@@ -641,12 +658,17 @@ class DecoderModel:
             if S is not None:
                 S["gu"] = None
             return self.tp_reduce(d) if self.tp_reduce is not None else d
-        gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
+        if W.get("mlp.gate_up_proj.bias") is None and (S is not None or self.fp8_weights is None):
+            # the activation runs in the epilogue of the up-projection; a kept layer also gets the pre-activation
+            act, gu = F.gemm_swiglu(h2, W["mlp.gate_up_proj.weight"], want_gate_up=S is not None)
+        else:
+            gu = self._lin(W, "mlp.gate_up_proj.weight", h2, S)
+            act = F.swiglu(gu)
         if S is not None:
             S["gu"] = gu
         if self.tp_linear_sum is not None and W.get("mlp.down_proj.bias") is None:
-            return self.tp_linear_sum(F.swiglu(gu), W["mlp.down_proj.weight"], False)
-        d = self._lin(W, "mlp.down_proj.weight", F.swiglu(gu), S)
+            return self.tp_linear_sum(act, W["mlp.down_proj.weight"], False)
+        d = self._lin(W, "mlp.down_proj.weight", act, S)
         return self.tp_reduce(d) if self.tp_reduce is not None else d
 
     def _mlp_bwd(self, W, g_d, h2, S: dict):

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
+#include <vector>
 
 namespace {
 
@@ -35,10 +36,43 @@ static bool skinny_enabled() {
   return on;
 }
 
-// Rows per launch of the transposed kernel: at most 512, equal blocks (a multiple of 16 rows) for more.
-static int skinny_rows(int64_t M) {
-  const int64_t blocks = (M + 511) / 512;
-  return (int)(((M + blocks - 1) / blocks + 15) / 16 * 16);
+// Row ranges of one weight matrix against few tokens in one launch: out[:, c_s : c_s + rows_s] = a @ w[w0_s : w0_s + rows_s]^T
+// (+ bias[w0_s : ...]) with the ranges' outputs side by side. ranges: flat list (w0, rows, w0, rows, ...), at most four ranges,
+// rows multiples of 8. Returns false (and does nothing) when the shape is not served: the caller then runs one GEMM per range.
+bool gemm_row_ranges_(const Tensor& a, const Tensor& w, const OptTensor& bias, std::vector<int64_t> ranges, Tensor out) {
+  if (!skinny_enabled() || !a.is_cuda() || a.scalar_type() != at::kBFloat16 || w.scalar_type() != at::kBFloat16) return false;
+  const int64_t M = a.size(0), K = a.size(1);
+  const int nseg = (int)(ranges.size() / 2);
+  if (a.dim() != 2 || w.dim() != 2 || w.size(1) != K || a.stride(1) != 1 || w.stride(1) != 1 || M < 1 || M > 1024 || nseg < 1 || nseg > 4 ||
+      K % 8 || a.stride(0) % 8 || w.stride(0) % 8 || out.stride(0) % 4 || out.stride(1) != 1 || out.scalar_type() != at::kBFloat16 ||
+      reinterpret_cast<uintptr_t>(out.data_ptr()) % 8 || reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 ||
+      reinterpret_cast<uintptr_t>(w.data_ptr()) % 16)
+    return false;
+  int w0[4], rows[4];
+  int64_t N = 0;
+  for (int s = 0; s < nseg; ++s) {
+    w0[s] = (int)ranges[2 * s];
+    rows[s] = (int)ranges[2 * s + 1];
+    if (rows[s] <= 0 || rows[s] % 8 || w0[s] < 0 || w0[s] + rows[s] > w.size(0)) return false;
+    N += rows[s];
+  }
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N, "gemm_row_ranges_: out must be [M, sum of the ranges' rows]");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == w.size(0) && bias->is_contiguous(), "gemm_row_ranges_: bias per row of w");
+    bias_ptr = bias->data_ptr();
+  }
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int s = vb_gemm_skinny_seg_splits((int)M, (int)K, nseg, w0, rows);
+  if (s < 1) return false;
+  Tensor ws;
+  if (s > 1) ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
+  count(1);
+  const int rc = vb_gemm_skinny_seg(a.data_ptr(), w.data_ptr(), out.data_ptr(), bias_ptr, (int)M, (int)K, (int)w.size(0), a.stride(0),
+                                    w.stride(0), out.stride(0), nseg, w0, rows, s, s > 1 ? ws.data_ptr<float>() : nullptr, (int)M, 0,
+                                    cur_stream());
+  TORCH_CHECK(rc == 0, "vb_gemm_skinny_seg failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+  return true;
 }
 
 // D = A * B^T (+bias).  a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn); rows may be strided.
@@ -71,22 +105,15 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
   if (skinny_enabled() && M <= 1024 && !a_mn && !b_mn && !out_f32 && !accumulate && max_ctas == 0 && N % 8 == 0 && K % 8 == 0 &&
       a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && d.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(d.data_ptr()) % 8 == 0 &&
       reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0) {
-    // few tokens: the transposed kernel (128 weight rows x all tokens per CTA, K split with the fold inside the launch);
-    // more than 512 tokens go in equal row blocks, one launch each (the weights of the later blocks come from L2)
-    const int rb = skinny_rows(M);
-    const int s = vb_gemm_skinny_splits(rb, (int)N, (int)K);
+    // few tokens: the transposed kernel (128 weight rows x up to 512 tokens per CTA, K split with the fold inside the launch)
+    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
     if (s >= 1) {
       Tensor ws;
       if (s > 1) ws = at::empty({s, M, N}, a.options().dtype(at::kFloat));
-      const auto* ap = reinterpret_cast<const at::BFloat16*>(a.data_ptr());
-      auto* dp = reinterpret_cast<at::BFloat16*>(d.data_ptr());
-      for (int64_t r0 = 0; r0 < M; r0 += rb) {
-        const int rows = (int)std::min<int64_t>(rb, M - r0);
-        count(1);
-        const int rc = vb_gemm_skinny(ap + r0 * a.stride(0), b.data_ptr(), dp + r0 * d.stride(0), bias_ptr, rows, (int)N, (int)K, a.stride(0),
-                                      b.stride(0), d.stride(0), s, s > 1 ? ws.data_ptr<float>() + r0 * N : nullptr, (int)M, 0, cur_stream());
-        TORCH_CHECK(rc == 0, "vb_gemm_skinny failed with code ", rc, " (M=", rows, " of ", M, " N=", N, " K=", K, ")");
-      }
+      count(1);
+      const int rc = vb_gemm_skinny(a.data_ptr(), b.data_ptr(), d.data_ptr(), bias_ptr, (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                                    d.stride(0), s, s > 1 ? ws.data_ptr<float>() : nullptr, (int)M, 0, cur_stream());
+      TORCH_CHECK(rc == 0, "vb_gemm_skinny failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
       return d;
     }
   }
@@ -100,6 +127,25 @@ Tensor gemm(const Tensor& a, const Tensor& b, const OptTensor& bias, const OptTe
                                  splits > 1 ? ws.data_ptr<float>() : nullptr, cur_stream());
   TORCH_CHECK(rc == 0, "vb_gemm_bf16 failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
   return d;
+}
+
+// act = silu(a W_gate^T) * (a W_up^T) for the stacked weight w = [W_gate; W_up] ([2I, K]); with want_gu the pre-activation
+// [M, 2I] is returned as well (else an empty tensor).
+std::tuple<Tensor, Tensor> gemm_swiglu(const Tensor& a, const Tensor& w, bool want_gu) {
+  CHECK_BF16(a);
+  CHECK_BF16(w);
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.stride(1) == 1 && w.stride(1) == 1 && a.size(1) == w.size(1) && w.size(0) % 2 == 0,
+              "gemm_swiglu: a [M, K], w [2I, K]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), K = a.size(1), I = w.size(0) / 2;
+  Tensor act = at::empty({M, I}, a.options());
+  Tensor gu = want_gu ? at::empty({M, 2 * I}, a.options()) : at::empty({0}, a.options());
+  if (M == 0) return {act, gu};
+  count(1);
+  const int rc = vb_gemm_bf16_swiglu(a.data_ptr(), w.data_ptr(), act.data_ptr(), want_gu ? gu.data_ptr() : nullptr, (int)M, (int)I, (int)K,
+                                     a.stride(0), w.stride(0), act.stride(0), 2 * I, cur_stream());
+  TORCH_CHECK(rc == 0, "vb_gemm_bf16_swiglu failed with code ", rc, " (M=", M, " I=", I, " K=", K, ")");
+  return {act, gu};
 }
 
 int64_t gemm_status() {
@@ -595,11 +641,10 @@ Tensor gemm_allreduce(const Tensor& a, const Tensor& b, const OptTensor& bias, c
   int skinny = 0;
   if (splitk_ws.has_value() && !b_mn && rs_rows <= 0 && skinny_enabled() && M <= 1024 && K % 8 == 0 && a.stride(0) % 8 == 0 &&
       b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0) {
-    const int rb = skinny_rows(M);
-    const int s = vb_gemm_skinny_splits(rb, (int)N, (int)K);
+    const int s = vb_gemm_skinny_splits((int)M, (int)N, (int)K);
     if (s > 1) {
       splits = s;
-      skinny = rb;  // rows per launch of the transposed kernel
+      skinny = 1;
     }
   }
   if (splits > 1 && splitk_ws->numel() >= splits * M * N) {
@@ -918,7 +963,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_fetch", &gemm_fetch);
   m.def("gemm_skinny_splits", [](int64_t M, int64_t N, int64_t K) {
-    return (int64_t)((skinny_enabled() && M <= 1024) ? vb_gemm_skinny_splits(skinny_rows(M), (int)N, (int)K) : 0);
+    return (int64_t)((skinny_enabled() && M <= 1024) ? vb_gemm_skinny_splits((int)M, (int)N, (int)K) : 0);
   });
   m.def("gemm_fold_in_kernel", []() { return (int64_t)vb_gemm_fold_in_kernel(); });
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
@@ -940,6 +985,8 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_grouped_wgrad_", &gemm_grouped_wgrad_);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
+  m.def("gemm_swiglu", &gemm_swiglu);
+  m.def("gemm_row_ranges_", &gemm_row_ranges_);
   m.def("launch_count", &launch_count);
   m.def("add_launches", &add_launches);
   m.def("attn_fwd", &attn_fwd);

@@ -38,7 +38,11 @@ constexpr int GEMM_THREADS = 192;
 //  EPI_ALLREDUCE  row-parallel (K-sharded) linear of a tensor-parallel group: every rank computes a partial tile,
 //               publishes it as bf16 in its own peer-visible buffer, raises a per-(tile, warp) flag, then sums
 //               the partials of all ranks in rank order (bitwise identical on every rank) and stores D.
-enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2, EPI_ALLREDUCE = 3 };
+//  EPI_SWIGLU   gated MLP up-projection: B is the stacked [gate; up] weight [2I, K], loaded through a 3-D tensor map that
+//               interleaves the two halves row by row (accumulator column 2j = gate_j, 2j+1 = up_j), so that a thread
+//               holds both members of a pair: D[M, I] = silu(gate) * up as bf16; optionally the pre-activation is
+//               also written in the stacked layout ([M, 2I], what the backward pass of a kept layer reads).
+enum { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2, EPI_ALLREDUCE = 3, EPI_SWIGLU = 4 };
 
 constexpr int AR_MAX_RANKS = 8;
 
@@ -100,6 +104,9 @@ struct GemmParams {
   long long fix_ldd;
   const __nv_bfloat16* fix_bias;
   int fix_out_f32, fix_accumulate;
+  // EPI_SWIGLU: N counts accumulator columns (2 * I); D is the activation [M, I]
+  __nv_bfloat16* gu_out;  // pre-activation [M, 2I] (gate columns first), or null
+  long long gu_ld;
 };
 
 constexpr int FIX_COUNTERS = 16384;
@@ -281,7 +288,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tma_a, &full_bar[stage], m0 + 64 * j, k0);
           }
-          if constexpr (!B_MN) {
+          if constexpr (EPI == EPI_SWIGLU) {
+            // (k, half, row) box of 64 x 2 x BN/2: shared-memory row 2j holds gate row n0/2 + j, row 2j + 1 its up row
+            tma_load_3d(sb, &tma_b, &full_bar[stage], k0, 0, n0 >> 1);
+          } else if constexpr (!B_MN) {
             tma_load_2d(sb, &tma_b, &full_bar[stage], k0, b_off + n0);
           } else {
 #pragma unroll
@@ -481,6 +491,43 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
                 v.z = pack_bf16x2(d[j + 4], d[j + 5]);
                 v.w = pack_bf16x2(d[j + 6], d[j + 7]);
                 *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            }
+          }
+        } else if constexpr (EPI == EPI_SWIGLU) {
+          if (row_ok) {
+            const int ac0 = col0 >> 1;        // first activation column of this chunk
+            const int npairs = ncols >> 1;    // multiple of 4
+            const int inter = p.N >> 1;
+            float act[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+              act[j] = g / (1.f + __expf(-g)) * u;
+            }
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + ac0;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              if (j < npairs) {
+                uint2 v;
+                v.x = pack_bf16x2(act[j], act[j + 1]);
+                v.y = pack_bf16x2(act[j + 2], act[j + 3]);
+                *reinterpret_cast<uint2*>(out + j) = v;
+              }
+            }
+            if (p.gu_out != nullptr) {
+              __nv_bfloat16* go = p.gu_out + static_cast<long long>(row) * p.gu_ld + ac0;
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                if (j < npairs) {
+                  uint2 g4, u4;
+                  g4.x = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 2]));
+                  g4.y = pack_bf16x2(__uint_as_float(r[2 * j + 4]), __uint_as_float(r[2 * j + 6]));
+                  u4.x = pack_bf16x2(__uint_as_float(r[2 * j + 1]), __uint_as_float(r[2 * j + 3]));
+                  u4.y = pack_bf16x2(__uint_as_float(r[2 * j + 5]), __uint_as_float(r[2 * j + 7]));
+                  *reinterpret_cast<uint2*>(go + j) = g4;
+                  *reinterpret_cast<uint2*>(go + inter + j) = u4;
+                }
               }
             }
           }
@@ -1026,6 +1073,27 @@ extern "C" int vb_gemm_bf16_ex(const void* A, const void* B, void* D, const void
   return static_cast<int>(e);
 }
 
+// Gated MLP up-projection with the activation in the epilogue: act[M, I] = silu(A W_gate^T) * (A W_up^T) for the stacked
+// weight W = [W_gate; W_up] ([2I, K], K-major, row stride ldw). gu_out (or null): the pre-activation [M, 2I] in the
+// stacked layout, row stride gu_ld, for a backward pass that keeps it. I must be a multiple of 4.
+extern "C" int vb_gemm_bf16_swiglu(const void* A, const void* W, void* act, void* gu_out, int M, int I, int K,
+                                   long long lda, long long ldw, long long ldd, long long gu_ld, cudaStream_t stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if ((I % 4) || (lda % 8) || (ldw % 8) || (ldd % 4) || (gu_out != nullptr && (gu_ld % 4))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -2;
+  if ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gu_out)) & 7) return -2;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  // (k, half, row): half 0 = gate rows [0, I), half 1 = up rows [I, 2I)
+  if (!make_tmap_3d(&tb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, 2, I, static_cast<uint64_t>(I) * ldw, ldw, BK, 2, 128,
+                    CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  GemmParams p{};
+  p.M = M; p.N = 2 * I; p.K = K; p.D = act; p.ldd = ldd; p.status = status_ptr(); p.k_splits = 1;
+  p.gu_out = reinterpret_cast<__nv_bfloat16*>(gu_out); p.gu_ld = gu_ld;
+  return static_cast<int>(launch_variant<256, false, false, 4, EPI_SWIGLU>(ta, tb, p, num_sms(), stream));
+}
+
 // Row-parallel linear of a tensor-parallel group with the all-reduce done inside the GEMM epilogue over peer memory:
 // D[M,N] = sum_r A_r[M,K_r] B_r[N,K_r]^T (+bias), identical bits on every rank. A and B are K-major.
 //  part_ptrs[r]  rank r's partial buffer (bf16, 2 * buf_elems elements, peer-mapped); buf_elems >= M*N
@@ -1200,13 +1268,8 @@ extern "C" int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void*
   if (static_cast<long long>(M) * N > buf_elems) return -5;
   int rc;
   if (skinny > 0) {
-    // the transposed kernel for few tokens, `skinny` rows per launch: k_splits comes from vb_gemm_skinny_splits(skinny, N, K)
-    rc = 0;
-    for (int r0 = 0; r0 < M && rc == 0; r0 += skinny) {
-      const int rows = M - r0 < skinny ? M - r0 : skinny;
-      rc = vb_gemm_skinny(reinterpret_cast<const __nv_bfloat16*>(A) + static_cast<long long>(r0) * lda, B, nullptr, nullptr, rows, N, K,
-                          lda, ldb, N, k_splits, splitk_ws + static_cast<long long>(r0) * N, M, 1, stream);
-    }
+    // the transposed kernel for few tokens: k_splits comes from vb_gemm_skinny_splits
+    rc = vb_gemm_skinny(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, k_splits, splitk_ws, M, 1, stream);
   } else {
     g_partials_only = true;
     rc = vb_gemm_bf16_ex(A, B, splitk_ws, nullptr, M, N, K, lda, ldb, N, 0, 0, 1, 0, 0, k_splits, splitk_ws, stream);

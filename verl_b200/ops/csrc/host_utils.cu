@@ -32,6 +32,19 @@ bool make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, in
   return r == CUDA_SUCCESS;
 }
 
+bool make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d0, uint64_t d1,
+                  uint64_t d2, uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1, uint32_t box2,
+                  CUtensorMapSwizzle sw) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) return false;
+  cuuint64_t gdim[3] = {d0, d1, d2};
+  cuuint64_t gstride[2] = {stride1_elems * static_cast<uint64_t>(elem_bytes), stride2_elems * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
 
 int num_sms() {
   static int sms = 0;

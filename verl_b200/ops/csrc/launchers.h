@@ -21,6 +21,10 @@ int vb_gemm_bf16_splitk_allreduce(const void* A, const void* B, void* D, const v
                                   const unsigned long long* flag_ptrs, unsigned int* epoch, long long buf_elems, int world, int rank,
                                   double limit_s, int k_splits, float* splitk_ws, int skinny, cudaStream_t stream);
 int vb_gemm_skinny_splits(int M, int N, int K);
+int vb_gemm_skinny_seg_splits(int M, int K, int nseg, const int* seg_w0, const int* seg_rows);
+int vb_gemm_skinny_seg(const void* X, const void* W, void* D, const void* bias, int M, int K, int w_rows, long long ldx, long long ldw,
+                       long long ldd, int nseg, const int* seg_w0, const int* seg_rows, int splits, float* ws, int ws_rows,
+                       int partials_only, cudaStream_t stream);
 int vb_gemm_skinny_status();
 int vb_gemm_skinny(const void* X, const void* W, void* D, const void* bias, int M, int N, int K, long long ldx, long long ldw,
                    long long ldd, int splits, float* ws, int ws_rows, int partials_only, cudaStream_t stream);
@@ -35,6 +39,8 @@ int vb_gemm_bf16_allreduce(const void* A, const void* B, void* D, const void* bi
 int vb_gemm_grouped(int mode, const void* A, const void* B, void* D, int rows_cap, int M, int N, int K, long long lda, long long ldb,
                     long long ldd, int b_mn, int accumulate, int E, const int* tile_expert, const int* num_mtiles,
                     const int* seg_start, cudaStream_t stream);
+int vb_gemm_bf16_swiglu(const void* A, const void* W, void* act, void* gu_out, int M, int I, int K, long long lda, long long ldw,
+                        long long ldd, long long gu_ld, cudaStream_t stream);
 int vb_gemm_suggest_splits(int M, int N, int K);
 int vb_gemm_fold_in_kernel();
 int vb_gemm_status();

@@ -267,6 +267,11 @@ PFN_encodeTiled get_encode_tiled();
 // Returns false on failure.
 bool make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
                   uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw);
+// 3-D tensor [d2, d1, d0] (d0 contiguous; strides of d1 and d2 in elements, multiples of 16 bytes); box = {box0, box1, box2}
+// lands in shared memory with d0 innermost, then d1, then d2.
+bool make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d0, uint64_t d1,
+                  uint64_t d2, uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1, uint32_t box2,
+                  CUtensorMapSwizzle sw);
 int num_sms();
 
 }  // namespace vb

@@ -14,6 +14,8 @@ from __future__ import annotations
 import math
 from typing import Optional
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -84,6 +86,23 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, 
             out.copy_(d.to(out.dtype))
         return out
     return d if out_f32 else d.to(a.dtype)
+
+
+def gemm_row_ranges(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ranges, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a @ w[w0 : w0 + rows]^T (+ bias[w0 : w0 + rows])`` for every ``(w0, rows)`` of ``ranges``, results side by side: the
+    q | k | v (or gate | up) rows of one tensor-parallel rank inside the replicated fused weight. Up to 1024 tokens on the
+    GPU run as one launch of the kernel for few tokens; otherwise one GEMM per range."""
+    n = sum(int(r) for _, r in ranges)
+    if out is None:
+        out = torch.empty(a.shape[0], n, dtype=a.dtype, device=a.device)
+    if a.is_cuda and a.shape[0] <= 1024 and len(ranges) <= 4:
+        if _ops().gemm_row_ranges_(a, w, bias, [int(v) for pr in ranges for v in pr], out):
+            return out
+    col = 0
+    for w0, rows in ranges:
+        gemm(a, w[w0 : w0 + rows], bias[w0 : w0 + rows] if bias is not None else None, out=out[:, col : col + rows])
+        col += rows
+    return out
 
 
 def _accumulate_wgrad(param: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor) -> Optional[torch.Tensor]:
@@ -238,6 +257,22 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
         return _ops().swiglu_fwd(gate_up)
     g, u = gate_up.chunk(2, dim=-1)
     return F.silu(g) * u
+
+
+FUSED_SWIGLU = os.environ.get("VERL_B200_FUSED_SWIGLU", "1") != "0"
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, want_gate_up: bool = False):
+    """``silu(x W_gate^T) * (x W_up^T)`` for the stacked weight ``[W_gate; W_up]``; returns ``(act, gate_up or None)``.
+    Training-sized inputs on the GPU run the GEMM whose epilogue applies the activation (the [tokens, 2I] pre-activation
+    is only written when ``want_gate_up``, for a backward pass that keeps it); decode-sized ones keep the kernel for few
+    tokens plus the activation kernel."""
+    if (x.is_cuda and FUSED_SWIGLU and x.dim() == 2 and x.shape[0] > 1024 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w_gate_up.is_contiguous() and w_gate_up.shape[0] % 8 == 0 and w_gate_up.shape[1] % 8 == 0):
+        act, gu = _ops().gemm_swiglu(x, w_gate_up, bool(want_gate_up))
+        return act, (gu if want_gate_up else None)
+    gu = gemm(x, w_gate_up)
+    return swiglu(gu), (gu if want_gate_up else None)
 
 
 def swiglu_bwd(dout: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:

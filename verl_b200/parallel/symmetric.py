@@ -15,7 +15,8 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-__all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available", "ShardedRange", "PeerShardedLinear", "FusedRowParallelLinear"]
+__all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available", "ShardedRange", "PeerShardedLinear", "FusedRowParallelLinear",
+           "PeerAllToAll"]
 
 
 def symmetric_available() -> bool:
@@ -109,6 +110,70 @@ class FusedRowParallelLinear:
         assert a.shape[0] <= self.max_rows and (b.shape[1] if b_mn else b.shape[0]) == self.n
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
                                            self.splitk_ws, bool(b_mn), int(scatter_rows))
+
+
+class PeerAllToAll:
+    """The head <-> sequence exchange of Ulysses sequence parallelism over peer memory. One copy kernel stores every block
+    straight from the (strided) source into its place in the destination rank's peer-mapped buffer, 16 KB per thread
+    block, so the pack pass in front of a collective all-to-all disappears and the bytes cross NVLink once; two
+    device-side barriers bracket the stores (nobody overwrites a buffer its owner still reads; nobody reads before every
+    block has landed). The result is copied out of the buffer, which the next exchange reuses.
+
+    Parity target: ``verl/utils/ulysses.py:137-195`` (``all_to_all_tensor`` behind ``gather_seq_scatter_heads`` /
+    ``gather_heads_scatter_seq``)."""
+
+    BLOCK = 16384
+
+    def __init__(self, device, group=None, limit_s: float = 30.0):
+        self.device, self.group, self.limit_s = device, group, float(limit_s)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.buf: Optional[SymmetricBuffer] = None
+        self.cap_bytes = 0
+        self.barrier = PeerBarrier(device, group)
+
+    def _ensure(self, nbytes: int) -> None:
+        if nbytes > self.cap_bytes:  # every rank of the group sees the same sizes, so they re-allocate together
+            self.cap_bytes = max(2 * self.cap_bytes, -(-nbytes // (1 << 20)) * (1 << 20))
+            self.buf = SymmetricBuffer.allocate(self.cap_bytes, torch.uint8, self.device, self.group, zero=False)
+
+    def _run(self, jobs: list, out_bytes: int) -> torch.Tensor:
+        from ..ops import native
+
+        starts, n = [0], 0
+        for _, _, rows, rb, _, _ in jobs:
+            n += -(-(rows * rb) // self.BLOCK)
+            starts.append(n)
+        for dst, src, rows, rb, ds, ss in jobs:
+            assert dst % 16 == 0 and src % 16 == 0 and rb % 16 == 0 and ds % 16 == 0 and ss % 16 == 0, "16-byte units"
+        j = torch.tensor(jobs, dtype=torch.int64).view(-1, 6).to(self.device)
+        b = torch.tensor(starts, dtype=torch.int32).to(self.device)
+        self.barrier(limit_s=self.limit_s)
+        if n:
+            native.ops().scatter_copy_(j, b, n)
+        self.barrier(limit_s=self.limit_s)
+        return self.buf.tensor[:out_bytes]
+
+    def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
+        """[T/size, heads, hd] (my tokens, all heads) -> [T, heads/size, hd] (all tokens, my heads)."""
+        tl, h, d = x.shape
+        W, esz = self.world, x.element_size()
+        hs = h // W
+        assert x.stride(2) == 1 and x.stride(1) == d
+        row, blk = hs * d * esz, tl * hs * d * esz
+        self._ensure(W * blk)
+        jobs = [(int(self.buf.ptrs[j]) + self.rank * blk, x.data_ptr() + j * row, tl, row, row, x.stride(0) * esz) for j in range(W)]
+        return self._run(jobs, W * blk).view(x.dtype).view(W * tl, hs, d).clone()
+
+    def heads_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, heads/size, hd] -> [T/size, heads, hd]: every block lands in its final place (column block of the row)."""
+        t, hs, d = x.shape
+        W, esz = self.world, x.element_size()
+        tl = t // W
+        assert x.is_contiguous()
+        row = hs * d * esz
+        self._ensure(tl * W * row)
+        jobs = [(int(self.buf.ptrs[j]) + self.rank * row, x.data_ptr() + j * tl * row, tl, row, W * row, row) for j in range(W)]
+        return self._run(jobs, tl * W * row).view(x.dtype).view(tl, W * hs, d).clone()
 
 
 FETCH_CHUNK = 16384  # bytes per copy job of a GEMM's fetch warp (``FETCH_CHUNK`` in gemm_tcgen05.cu)
