@@ -539,6 +539,73 @@ def _sec_peer_all_to_all(rank, world, dev, ops, res):
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
+def _sec_peer_share(rank, world, dev, ops, res):
+    """Small all-gather with a device-side call counter: eager calls, then the same kernel captured in a CUDA graph and
+    replayed (each replay is a new call: nothing in the graph depends on a host-side counter)."""
+    from verl_b200.parallel.symmetric import PeerShare
+
+    share = PeerShare(64, dev)
+    ok = True
+    for i in range(5):
+        src = (torch.arange(40, device=dev, dtype=torch.int32) + 1000 * rank + 7 * i)
+        out = share(src)
+        want = torch.stack([torch.arange(40, device=dev, dtype=torch.int32) + 1000 * r + 7 * i for r in range(world)])
+        ok &= torch.equal(out, want)
+    src = torch.zeros(64, device=dev, dtype=torch.int32)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        warm = share(src)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = share(src)
+        out2 = share(out[(rank + 1) % world].contiguous())   # what the neighbour sent goes round again
+    for i in range(6):
+        src.fill_(100 * i + rank)
+        g.replay()
+        torch.cuda.synchronize()
+        ok &= bool((out == torch.tensor([[100 * i + r] for r in range(world)], device=dev, dtype=torch.int32)).all())
+        ok &= bool((out2[rank] == 100 * i + (rank + 1) % world).all())
+    res["equal"] = bool(ok)
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
+def _sec_rollout_tensor_parallel(rank, world, dev, ops, res):
+    """The rollout engine over the two GPUs as one tensor-parallel group (row ranges of the fused weights in one launch,
+    GEMM + all-reduce kernels, every rank sampling its half of the batch inside the captured decode graph) against the
+    single-GPU engine on the same weights: same lengths, log-probs equal up to the first bf16 near-tie."""
+    import torch.distributed as dist
+
+    from verl_b200.models import FlatParams, ModelConfig
+    from verl_b200.workers.rollout.native.engine import RolloutEngine, SamplingParams
+
+    cfg = ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, eos_token_id=-1, pad_token_id=0)
+    P = FlatParams(cfg, dtype=torch.bfloat16, device=dev)
+    P.init_weights(seed=0, std=0.05)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(3, 2048, (n,), generator=g).tolist() for n in (40, 3, 22, 40, 17, 9)]
+    sp = SamplingParams(temperature=1.0, max_tokens=24, logprobs=True, seed=5)
+    tp = RolloutEngine(cfg, P, max_num_seqs=8, max_model_len=128, block_size=16, num_blocks=64, eos_token_id=-1, seed=0, tp_group=dist.group.WORLD)
+    outs = tp.generate(prompts, sp)
+    res["split_sampling"] = tp._tp_share is not None
+    res["graph"] = tp._graph is not None
+    full = RolloutEngine(cfg, P, max_num_seqs=8, max_model_len=128, block_size=16, num_blocks=64, eos_token_id=-1, seed=0)
+    ref = full.generate(prompts, sp)
+    same, worst = 0, 0.0
+    for a, b in zip(outs, ref):
+        n = next((i for i, (x, y) in enumerate(zip(a.token_ids, b.token_ids)) if x != y), len(a.token_ids))
+        same += n == len(a.token_ids)
+        worst = max(worst, max(abs(x - y) for x, y in zip(a.log_probs[: max(n, 1)], b.log_probs[: max(n, 1)])))
+    res["same"], res["lp_diff"], res["lens"] = same, worst, [len(o.token_ids) for o in outs]
+    toks = torch.tensor([o.token_ids for o in outs], device=dev)
+    other = [torch.empty_like(toks) for _ in range(world)]
+    dist.all_gather(other, toks)
+    res["ranks_agree"] = all(bool(torch.equal(o, toks)) for o in other)
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
 SECTIONS = {name[len("_sec_"):]: fn for name, fn in list(globals().items()) if name.startswith("_sec_")}
 
 
@@ -707,6 +774,17 @@ def test_tensor_parallel_training_with_fused_collectives(pair):
 
 def test_ulysses_exchange_over_peer_memory(pair):
     for res in pair.run("peer_all_to_all").values():
+        assert res["equal"] and res["status"] == (0, 0), res
+
+
+def test_rollout_engine_tensor_parallel_on_gpus(pair):
+    for res in pair.run("rollout_tensor_parallel", timeout=600).values():
+        assert res["split_sampling"] and res["ranks_agree"] and res["lens"] == [24] * 6, res
+        assert res["same"] >= 4 and res["lp_diff"] < 6e-2 and res["status"] == (0, 0), res
+
+
+def test_small_all_gather_inside_a_cuda_graph(pair):
+    for res in pair.run("peer_share").values():
         assert res["equal"] and res["status"] == (0, 0), res
 
 

@@ -723,6 +723,18 @@ void scatter_copy_(const Tensor& jobs, const Tensor& block_start, int64_t total_
   CHECK_RC(vb_scatter_copy(jobs.data_ptr(), block_start.data_ptr<int>(), (int)jobs.size(0), (int)total_blocks, cur_stream()), "vb_scatter_copy");
 }
 
+// Graph-safe all-gather of a few words per rank over peer memory: out[r, :n] = rank r's src. buf_ptrs / flag_ptrs: CPU int64 [world].
+void peer_share_(const Tensor& buf_ptrs, const Tensor& flag_ptrs, Tensor epoch, const Tensor& src, Tensor out, int64_t cap, int64_t rank,
+                 double limit_s) {
+  TORCH_CHECK(src.is_cuda() && out.is_cuda() && src.scalar_type() == at::kInt && out.scalar_type() == at::kInt && src.is_contiguous() &&
+              out.is_contiguous() && out.numel() == src.numel() * buf_ptrs.numel(), "peer_share_: int32 src [n], out [world, n]");
+  TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == at::kInt && epoch.numel() >= 1, "peer_share_: int32 cuda epoch");
+  const c10::cuda::CUDAGuard guard(src.device());
+  count(1);
+  CHECK_RC(vb_peer_share(uptr(buf_ptrs), uptr(flag_ptrs), reinterpret_cast<unsigned int*>(epoch.data_ptr<int>()), src.data_ptr(), out.data_ptr(),
+                         (int)src.numel(), (int)cap, (int)rank, (int)buf_ptrs.numel(), limit_s, cur_stream()), "vb_peer_share");
+}
+
 int64_t comm_status() { return vb_comm_status(); }
 
 // ---- fp8 (e4m3) with 1x128 block scales
@@ -968,6 +980,7 @@ TORCH_LIBRARY(verl_b200, m) {
   m.def("gemm_fold_in_kernel", []() { return (int64_t)vb_gemm_fold_in_kernel(); });
   m.def("gemm_suggest_splits", [](int64_t M, int64_t N, int64_t K) { return (int64_t)vb_gemm_suggest_splits((int)M, (int)N, (int)K); });
   m.def("scatter_copy_", &scatter_copy_);
+  m.def("peer_share_", &peer_share_);
   m.def("comm_status", &comm_status);
   m.def("fp8_quant_1x128", &fp8_quant_1x128);
   m.def("fp8_quant_128x128", &fp8_quant_128x128);

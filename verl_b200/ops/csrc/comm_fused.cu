@@ -232,6 +232,45 @@ __global__ void scatter_copy_kernel(const CopyJob* __restrict__ jobs, const int*
   }
 }
 
+// Small all-gather over peer memory whose call counter lives on the device, so that it can sit inside a captured graph:
+// every rank stores its n words into slot [parity of the call][its rank] of every rank's buffer, raises its flag on every
+// rank to the call number, waits (bounded) until all flags of its own pad have reached it and copies the W slots out.
+// Two halves alternate by call parity: a rank can be at most one call ahead of a peer (its next call waits for that
+// peer's flag), so a slot is never overwritten while its owner still reads it.
+//  bufs.p[r]: 2 * W * cap words; flags.p[r]: W words, zero before the first call; epoch: this rank's call counter.
+__global__ void peer_share_kernel(PeerPtrs bufs, PeerPtrs flags, uint32_t* epoch, const uint32_t* __restrict__ src,
+                                  uint32_t* __restrict__ out, int n, int cap, int rank, int W, unsigned long long limit_ns,
+                                  int* status) {
+  __shared__ uint32_t s_e;
+  if (threadIdx.x == 0) s_e = *epoch + 1u;
+  __syncthreads();
+  const uint32_t e = s_e;
+  const long long slot = (static_cast<long long>(e & 1u) * W + rank) * cap;
+  for (int r = 0; r < W; ++r) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(bufs.p[(rank + r) % W]) + slot;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W) {
+    st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + rank, e);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + threadIdx.x;
+    const uint64_t t0 = gtimer();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - e) < 0) {
+      if ((++spins & 0xff) == 0 && gtimer() - t0 > limit_ns) {
+        atomicExch(status, 4);  // ST_TIMEOUT_PEER
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const volatile uint32_t* mybuf = reinterpret_cast<const volatile uint32_t*>(bufs.p[rank]) + static_cast<long long>(e & 1u) * W * cap;
+  for (int r = 0; r < W; ++r)
+    for (int i = threadIdx.x; i < n; i += blockDim.x) out[static_cast<long long>(r) * n + i] = mybuf[static_cast<long long>(r) * cap + i];
+  if (threadIdx.x == 0) *epoch = e;
+}
+
 static int* comm_status_ptr() {
   static int* p = nullptr;
   if (p == nullptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_comm_status);
@@ -298,6 +337,15 @@ int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n
 int vb_scatter_copy(const void* jobs, const int* block_start, int njobs, int total_blocks, cudaStream_t s) {
   if (njobs <= 0 || total_blocks <= 0) return 0;
   scatter_copy_kernel<<<total_blocks, 256, 0, s>>>(reinterpret_cast<const CopyJob*>(jobs), block_start, njobs);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int vb_peer_share(const unsigned long long* buf_ptrs, const unsigned long long* flag_ptrs, unsigned int* epoch, const void* src,
+                  void* out, int n, int cap, int rank, int W, double limit_s, cudaStream_t s) {
+  if (W > MAX_PEERS || n < 0 || n > cap) return -1;
+  peer_share_kernel<<<1, 256, 0, s>>>(make_peers(buf_ptrs, W), make_peers(flag_ptrs, W), epoch, reinterpret_cast<const uint32_t*>(src),
+                                      reinterpret_cast<uint32_t*>(out), n, cap, rank, W,
+                                      static_cast<unsigned long long>((limit_s > 0 ? limit_s : 2.0) * 1e9), comm_status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 

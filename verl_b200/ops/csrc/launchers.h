@@ -110,6 +110,8 @@ int vb_rs_sumsq(const unsigned long long* grad_ptrs, unsigned long long mc_ptr, 
 int vb_adamw_allgather(float* master, const float* grad, float* m, float* v, const unsigned long long* param_ptrs,
                        unsigned long long mc_ptr, long long lo, long long n, int W, int rank, const float* ctrl, float lr,
                        float beta1, float beta2, float eps, float wd, int step, cudaStream_t s);
+int vb_peer_share(const unsigned long long* buf_ptrs, const unsigned long long* flag_ptrs, unsigned int* epoch, const void* src,
+                  void* out, int n, int cap, int rank, int W, double limit_s, cudaStream_t s);
 int vb_scatter_copy(const void* jobs, const int* block_start, int njobs, int total_blocks, cudaStream_t s);
 int vb_allreduce_peer(const unsigned long long* buf_ptrs, void* out, long long n, int W, int rank, cudaStream_t s);
 int vb_comm_status();

@@ -16,7 +16,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["SymmetricBuffer", "PeerBarrier", "symmetric_available", "ShardedRange", "PeerShardedLinear", "FusedRowParallelLinear",
-           "PeerAllToAll"]
+           "PeerAllToAll", "PeerShare"]
 
 
 def symmetric_available() -> bool:
@@ -110,6 +110,29 @@ class FusedRowParallelLinear:
         assert a.shape[0] <= self.max_rows and (b.shape[1] if b_mn else b.shape[0]) == self.n
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
                                            self.splitk_ws, bool(b_mn), int(scatter_rows))
+
+
+class PeerShare:
+    """All-gather of a few 32-bit words per rank over peer memory in one kernel whose call counter lives on the device, so it
+    can sit inside a captured CUDA graph (the tensor-parallel rollout ranks each sample half of the batch and share the
+    tokens and log-probs). ``cap``: words one rank may contribute per call."""
+
+    def __init__(self, cap: int, device, group=None, limit_s: float = 20.0):
+        self.cap, self.limit_s = int(cap), float(limit_s)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.buf = SymmetricBuffer.allocate(2 * self.world * self.cap, torch.int32, device, group, zero=True)
+        self.flags = SymmetricBuffer.allocate(max(self.world, 16), torch.int32, device, group, zero=True)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # flags are zero everywhere before anyone publishes call 1
+
+    def __call__(self, src: torch.Tensor) -> torch.Tensor:
+        """``src`` int32 [n] (n <= cap, the same n on every rank) -> int32 [world, n]."""
+        from ..ops import native
+
+        out = torch.empty(self.world, src.numel(), dtype=torch.int32, device=src.device)
+        native.ops().peer_share_(self.buf.ptrs, self.flags.ptrs, self.epoch, src, out, self.cap, self.rank, self.limit_s)
+        return out
 
 
 class PeerAllToAll:

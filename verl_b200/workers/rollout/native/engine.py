@@ -128,6 +128,7 @@ class RolloutEngine:
         self._num_blocks_req = num_blocks
         self.model = DecoderModel(cfg, params, max_positions=self.max_model_len + 1)
         self.model.kv_hook = self._prefill_kv_hook
+        self._tp_share = None
         if self.tp_size > 1:
             assert not cfg.is_moe, "tensor-parallel rollout of MoE models is not implemented (use expert parallelism)"
             self.model.tp = TensorParallelShard(self.tp_rank, self.tp_size, self._make_row_linear())
@@ -156,6 +157,12 @@ class RolloutEngine:
 
             fused = FusedRowParallelLinear(max(self.max_batched, self.S), self.cfg.hidden_size, self.device, self.tp_group)
             self._fused_row = fused
+            # decode: every rank of the group computes the logits of, and samples, its own share of the sequences; the
+            # tokens and log-probs are shared over peer memory (VERL_B200_TP_SPLIT_SAMPLING=0: every rank samples all)
+            if self.S % self.tp_size == 0 and os.environ.get("VERL_B200_TP_SPLIT_SAMPLING", "1") != "0":
+                from ....parallel.symmetric import PeerShare
+
+                self._tp_share = PeerShare(2 * (self.S // self.tp_size), self.device, self.tp_group)
             return lambda a, w, bias: fused(a, w, bias)
 
         def row_linear(a, w, bias):
@@ -730,10 +737,19 @@ class RolloutEngine:
             a = self.model._mlp_fwd(W, h2, None)
             r = x2
         hN = F.rms_norm(a, P["norm.weight"], cfg.rms_norm_eps, residual=r)[0]
-        logits = F.gemm(hN, P.lm_head_weight)
-        if self._use_penalty:
-            logits = self._penalise(logits)
-        tok, lp = F.sample_tokens(logits, self.temperature, self.seeds, 0, self.valid_vocab, self.top_k, self.top_p)
+        if tp is not None and self._tp_share is not None and not self._use_penalty:
+            sh = S // tp.size
+            mine = slice(tp.rank * sh, (tp.rank + 1) * sh)
+            logits = F.gemm(hN[mine], P.lm_head_weight)
+            tok_h, lp_h = F.sample_tokens(logits, self.temperature, self.seeds[mine].contiguous(), 0, self.valid_vocab, self.top_k, self.top_p)
+            both = self._tp_share(torch.cat([tok_h.to(torch.int32), lp_h.float().view(torch.int32)]))   # [tp, 2 * sh]
+            tok = both[:, :sh].reshape(S).long()
+            lp = both[:, sh:].reshape(S).view(torch.float32)
+        else:
+            logits = F.gemm(hN, P.lm_head_weight)
+            if self._use_penalty:
+                logits = self._penalise(logits)
+            tok, lp = F.sample_tokens(logits, self.temperature, self.seeds, 0, self.valid_vocab, self.top_k, self.top_p)
         # ---- state update (all on device)
         rows = torch.arange(S, device=self.device)
         if self.record_routing:
