@@ -12,32 +12,66 @@ from verl_b200.protocol import DataProto
 
 # --------------------------------------------------------------------------------------------- rollout correction
 def test_rollout_rejection_mask_and_importance_weights():
-    from verl_b200.trainer.ppo.rollout_corr_helper import (compute_offpolicy_metrics, compute_rollout_correction_and_add_to_batch,
-                                                           compute_rollout_correction_weights, compute_rollout_rejection_mask)
+    import math
 
-    lr = torch.log(torch.tensor([[1.0, 3.0, 0.4], [1.1, 0.9, 1.0]]))      # pi_train / pi_rollout per token
+    from verl_b200.trainer.ppo.rollout_corr_helper import (compute_offpolicy_metrics, compute_rollout_corr_metrics_from_logprobs,
+                                                           compute_rollout_correction_and_add_to_batch, compute_rollout_correction_weights,
+                                                           compute_rollout_rejection_mask)
+
+    ratio = [[1.0, 3.0, 0.4], [1.1, 0.9, 1.0]]                             # pi_train / pi_rollout per token
+    lr = torch.log(torch.tensor(ratio))
     mask = torch.tensor([[1, 1, 1], [1, 1, 0]])
     keep, m = compute_rollout_rejection_mask(lr, mask, "token_k1", "0.5_2.0")
-    assert keep.tolist() == [[1, 0, 0], [1, 1, 0]] and abs(m["rollout_corr/rollout_rs_masked_fraction"] - 0.4) < 1e-6
+    assert keep.tolist() == [[1, 0, 0], [1, 1, 0]] and abs(m["rollout_rs_masked_fraction"] - 0.4) < 1e-6
+    assert abs(m["rollout_rs_token_k1_masked_fraction"] - 0.4) < 1e-6 and m["rollout_rs_seq_masked_fraction"] == 0.5
+    # k1 = -log(ratio): the band is on pi_rollout / pi_train, so an asymmetric band keeps the ratio 3 (k1 = log 1/3) here
+    keep, _ = compute_rollout_rejection_mask(lr, mask, "token_k1", "0.3_2.0")
+    assert keep.tolist() == [[1, 1, 0], [1, 1, 0]]
     keep, m = compute_rollout_rejection_mask(lr, mask, "seq_mean_k1", "0.9_1.1")
-    # geometric means: (1*3*0.4)^(1/3) = 1.063 (kept), sqrt(1.1*0.9) = 0.995 (kept)
-    assert keep.tolist() == [[1, 1, 1], [1, 1, 0]] and m["rollout_corr/rollout_rs_seq_masked_fraction"] == 0.0
+    # geometric means of the ratios: (1*3*0.4)^(1/3) = 1.063, sqrt(1.1*0.9) = 0.995: both inside the band
+    assert keep.tolist() == [[1, 1, 1], [1, 1, 0]] and m["rollout_rs_seq_masked_fraction"] == 0.0
+    assert abs(m["rollout_rs_seq_mean_k1_seq_max"] - (-math.log(0.99) / 2)) < 1e-5
     keep, _ = compute_rollout_rejection_mask(lr, mask, "token_k2", 0.05)   # 0.5 * log-ratio^2 <= 0.05
     assert keep.tolist() == [[1, 0, 0], [1, 1, 0]]
+    # k3 = r - 1 - log r per token; several options at once: every one must pass
+    k3 = [[r - 1 - math.log(r) for r in row] for row in ratio]
+    keep, m = compute_rollout_rejection_mask(lr, mask, "seq_max_k3,token_k1", "0.5,0.5_2.5")
+    assert keep.tolist() == [[0, 0, 0], [1, 1, 0]]                         # row 0: max k3 = 3 - 1 - log 3 = 0.90 > 0.5
+    assert abs(m["rollout_rs_seq_max_k3_seq_max"] - max(k3[0])) < 1e-5 and abs(m["rollout_rs_seq_max_k3_seq_min"] - max(k3[1][:2])) < 1e-6
+    for bad in (("seq_max_k1", "0.5_2"), ("token_k9", 1.0), ("token_k2", "0.1_0.2"), ("token_k1,token_k2", "1,2,3")):
+        with pytest.raises(ValueError):
+            compute_rollout_rejection_mask(lr, mask, *bad)
+
     w, m = compute_rollout_correction_weights(lr, mask, "token", 2.0)
     assert torch.allclose(w, torch.tensor([[1.0, 2.0, 0.4], [1.1, 0.9, 0.0]]), atol=1e-6)
-    assert abs(m["rollout_corr/rollout_is_truncated_fraction"] - 0.2) < 1e-6 and abs(m["rollout_corr/rollout_is_max"] - 3.0) < 1e-5
-    w, _ = compute_rollout_correction_weights(lr, mask, "sequence", 10.0)
+    assert abs(m["rollout_is_ratio_fraction_high"] - 0.2) < 1e-6 and abs(m["rollout_is_max"] - 2.0) < 1e-5
+    vals = [1.0, 2.0, 0.4, 1.1, 0.9]
+    mean = sum(vals) / 5
+    assert abs(m["rollout_is_mean"] - mean) < 1e-6
+    assert abs(m["rollout_is_eff_sample_size"] - 1.0 / (sum((v / mean) ** 2 for v in vals) / 5)) < 1e-5
+    w, m = compute_rollout_correction_weights(lr, mask, "token", "0.5_2.0")   # band: weights outside it are zeroed
+    assert torch.allclose(w, torch.tensor([[1.0, 0.0, 0.0], [1.1, 0.9, 0.0]]), atol=1e-6) and abs(m["rollout_is_oob_ratio"] - 0.4) < 1e-6
+    w, m = compute_rollout_correction_weights(lr, mask, "sequence", 10.0)
     assert torch.allclose(w[0], torch.full((3,), 1.2), atol=1e-5) and torch.allclose(w[1, :2], torch.full((2,), 0.99), atol=1e-5)
+    assert abs(m["rollout_is_max"] - 1.2) < 1e-5 and w[1, 2] == 0
+    w, m = compute_rollout_correction_weights(lr, mask, "token", 2.0, rollout_is_batch_normalize=True)
+    assert abs(m["rollout_is_batch_norm_factor"] - mean) < 1e-6 and abs(float((w * mask).sum()) / 5 - 1.0) < 1e-6
+
     old = torch.log(torch.tensor([[0.5, 0.6, 0.2], [0.55, 0.45, 0.5]]))
     roll = old - lr
     om = compute_offpolicy_metrics(old, roll, mask)
-    assert abs(om["rollout_corr/kl"] - float(-(lr * mask).sum() / 5)) < 1e-6 and om["rollout_corr/chi2_token"] > 0
+    assert abs(om["kl"] - float(-(lr * mask).sum() / 5)) < 1e-6 and om["chi2_token"] > 0
+    assert abs(om["chi2_seq"] - ((1.2 ** 2 + 0.99 ** 2) / 2 - 1)) < 1e-5
+    assert abs(om["k3_kl"] - (sum(k3[0]) + sum(k3[1][:2])) / 5) < 1e-6
+    assert set(compute_rollout_corr_metrics_from_logprobs(old, roll, mask)) == {f"rollout_corr/{k}" for k in om}
     batch = DataProto.from_dict(tensors={"old_log_probs": old, "rollout_log_probs": roll, "response_mask": mask})
     out, metrics = compute_rollout_correction_and_add_to_batch(batch, {"rollout_is": "token", "rollout_is_threshold": 2.0,
                                                                         "rollout_rs": "token_k1", "rollout_rs_threshold": "0.5_2.0"})
     assert out.batch["response_mask"].tolist() == [[1, 0, 0], [1, 1, 0]] and "rollout_is_weights" in out.batch.keys()
-    assert "rollout_corr/kl" in metrics and "rollout_corr/rollout_is_mean" in metrics
+    assert "rollout_corr/kl" in metrics and "rollout_corr/rollout_is_mean" in metrics and "rollout_corr/rollout_rs_token_k1_mean" in metrics
+    batch = DataProto.from_dict(tensors={"old_log_probs": old, "rollout_log_probs": roll, "response_mask": mask})
+    out, metrics = compute_rollout_correction_and_add_to_batch(batch, {})      # diagnostics only
+    assert "rollout_is_weights" not in out.batch.keys() and out.batch["response_mask"].tolist() == mask.tolist()
 
 
 # --------------------------------------------------------------------------------------------- metrics
