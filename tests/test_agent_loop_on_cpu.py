@@ -139,3 +139,50 @@ def test_fully_async_client_resumes_after_abort():
     cl = FullyAsyncLLMServerClient(cfg, {"s": Flaky()}, GlobalRequestLoadBalancer(["s"]), retry_interval=0.0)
     out = asyncio.run(cl.generate("req", prompt_ids=[9, 9], sampling_params={"max_tokens": 6}))
     assert out.token_ids == [1, 2, 3, 4, 5, 6] and len(out.log_probs) == 6 and out.stop_reason == "length"
+
+
+def test_trajectory_info_greedy_rows_traces_and_performance_metrics():
+    """Rows of one dataset index get consecutive repeat numbers; a row marked ``__do_sample__ = False`` is decoded greedily
+    while its neighbours sample; traced spans carry the trajectory of the task that recorded them (the trajectories run
+    concurrently); the manager reports min / max / mean of every timer and the slowest trajectory."""
+    from verl_b200.experimental.agent_loop.agent_loop import get_trajectory_info
+    from verl_b200.utils.rollout_trace import TRACE_RING, RolloutTraceConfig
+
+    info = get_trajectory_info(7, [4, 4, 4, 9, 9, 2], False)
+    assert [t["rollout_n"] for t in info] == [0, 1, 2, 0, 1, 0] and info[3] == {"step": 7, "sample_index": 9, "rollout_n": 0, "validate": False}
+
+    config = _cfg()
+    rc = config.actor_rollout_ref.rollout
+    RolloutTraceConfig.init("p", "e", "memory", max_samples_per_step_per_worker=1)
+    TRACE_RING.clear()
+
+    class Scorer:
+        async def compute_score_for(self, out, kwargs):
+            await asyncio.sleep(0.01)
+            return float(len(out.response_ids))
+
+    async def go(greedy_rows):
+        mgr = await LLMServerManager.create(rc, engines=_engines(1), model_config=None)
+        alm = AgentLoopManager(config, mgr, num_workers=1, reward_loop_worker=Scorer())
+        g = torch.Generator().manual_seed(0)
+        row = torch.randint(3, 500, (1, 8), generator=g)
+        ids = row.repeat(4, 1)                                      # four repeats of two dataset rows
+        batch = DataProto.from_dict(tensors={"input_ids": ids, "attention_mask": torch.ones(4, 8, dtype=torch.int64)},
+                                    non_tensors={"index": np.array([11, 11, 12, 12]),
+                                                 "__do_sample__": np.array([i not in greedy_rows for i in range(4)])},
+                                    meta_info={"temperature": 1.0, "global_steps": 3})
+        return await alm.generate_sequences_async(batch)
+
+    out = asyncio.run(go({1, 3}))
+    resp = out.batch["responses"]
+    assert torch.equal(resp[1], resp[3])                             # same prompt, both greedy
+    assert not torch.equal(resp[0], resp[1]) or not torch.equal(resp[2], resp[3])   # the sampled rows differ from the greedy ones
+    assert out.batch["rm_scores"].sum(-1).tolist() == [12.0] * 4
+    t = out.meta_info["timing"]
+    for k in ("generate_sequences", "tool_calls", "compute_score", "num_preempted"):
+        assert t[f"agent_loop/{k}/min"] <= t[f"agent_loop/{k}/mean"] <= t[f"agent_loop/{k}/max"]
+    assert t["agent_loop/compute_score/min"] >= 0.01 and t["agent_loop/slowest/prompt_length"] == 8 and t["agent_loop/slowest/response_length"] == 12
+    spans = [s for s in TRACE_RING if s["op"].endswith("_run_traced")]
+    assert len(spans) == 2 and len({s["sample_index"] for s in spans}) == 1      # one dataset row traced: both of its repeats
+    assert sorted(s["rollout_n"] for s in spans) == [0, 1] and all(s["step"] == 3 for s in spans)
+    RolloutTraceConfig.reset()

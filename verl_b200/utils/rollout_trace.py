@@ -4,6 +4,7 @@ ring that tests and debuggers can read). Parity target: ``verl/utils/rollout_tra
 from __future__ import annotations
 
 import contextlib
+import contextvars
 import functools
 import inspect
 import time
@@ -55,17 +56,20 @@ class RolloutTraceConfig:
         cls._instance = None
 
 
+# Attributes of the trajectory that the current task works on. A context variable, not a global stack: the trajectories
+# of a batch run as concurrent asyncio tasks, each of which sees only the attributes it set itself.
+_trace_attrs: contextvars.ContextVar = contextvars.ContextVar("rollout_trace_attrs", default=None)
+
+
 @contextlib.contextmanager
 def rollout_trace_attr(sample_index=None, step=None, rollout_n=None, name="rollout_trace", validate=False, trace: bool = True):
-    attrs = dict(sample_index=sample_index, step=step, rollout_n=rollout_n, validate=validate)
-    _attr_stack.append(attrs)
+    """Spans recorded inside carry these attributes; ``trace=False`` records none (a sampled-out trajectory)."""
+    token = _trace_attrs.set({"sample_index": sample_index, "step": step, "rollout_n": rollout_n, "validate": validate,
+                              "_trace": bool(trace)})
     try:
         yield
     finally:
-        _attr_stack.pop()
-
-
-_attr_stack: list = []
+        _trace_attrs.reset(token)
 
 
 def rollout_trace_op(fn):
@@ -73,7 +77,9 @@ def rollout_trace_op(fn):
 
     def record(name, t0, ok):
         if RolloutTraceConfig.get_backend() is not None:
-            TRACE_RING.append({"op": name, "seconds": time.time() - t0, "ok": ok, **(_attr_stack[-1] if _attr_stack else {})})
+            attrs = dict(_trace_attrs.get() or {})
+            if attrs.pop("_trace", True):
+                TRACE_RING.append({"op": name, "seconds": time.time() - t0, "ok": ok, **attrs})
 
     if inspect.iscoroutinefunction(fn):
         @functools.wraps(fn)
