@@ -93,3 +93,32 @@ def test_one_step_off_single_pool(monkeypatch):
     assert type(t).__name__ == "OneStepOffRayTrainer" and t.param_version == 3
     ages = t.last_batch  # batches after the first were generated one version earlier
     assert ages is not None
+
+
+def test_async_trainer_checkpoints_its_buffer_and_reissues_inflight_prompts(monkeypatch, tmp_path):
+    """The asynchronous trainers keep the replay buffer in the checkpoint; after a resume the groups that were still being
+    generated start again from their stored prompts (partial trajectories dropped), finished groups are trained on as
+    they are, and training goes on."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.trainer.main_ppo import main
+
+    base = [a for a in ARGS if not a.startswith(("trainer.resume_mode", "trainer.total_training_steps"))] + [
+        "trainer.v1.trainer_mode=colocate_async", f"trainer.default_local_dir={tmp_path}", "trainer.save_freq=2"]
+    t = main(base + ["trainer.resume_mode=disable", "trainer.total_training_steps=2"])
+    state = tmp_path / "global_step_2" / "transfer_queue" / "state.pt"
+    assert state.exists()
+    import torch
+
+    saved = torch.load(state, weights_only=False)
+    tags = saved["tags"]["train"]
+    live = [k for k, v in tags.items() if v.get("kind") == "prompt" and v.get("status") in ("pending", "running")]
+    done = [k for k, v in tags.items() if v.get("kind") == "prompt" and v.get("status") == "finished"]
+    assert saved["metadata"] == {"global_steps": 2, "param_version": 2} and (live or done)
+
+    t2 = main(base + ["trainer.resume_mode=auto", "trainer.total_training_steps=3"])
+    assert t2.global_steps == 4 and t2.param_version == 3            # resumed at step 2, trained step 3
+    q = t2.replay_buffer.q
+    for uid in live:                                                 # re-issued groups: consumed, or complete again, never half
+        if uid in q.list_keys("train"):
+            tg = q.get_tags(uid, "train")
+            assert tg["done"] <= tg["n"] and tg["start_version"] >= 2

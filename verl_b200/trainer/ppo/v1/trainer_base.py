@@ -17,6 +17,7 @@ Parity target: ``verl/trainer/ppo/v1/trainer_base.py`` (class :118, ``_build_rep
 from __future__ import annotations
 
 import asyncio
+import os
 import time
 import uuid
 from typing import Any, Optional
@@ -252,6 +253,53 @@ class PPOTrainer(RayPPOTrainer):
             logger.log(data=metrics, step=self.global_steps)
             self.global_steps += 1
         self.shutdown()
+
+    # ------------------------------------------------------------------ checkpoint of the buffer
+    def _save_checkpoint(self) -> None:
+        """Actor / critic / dataloader as in the synchronous trainer; the asynchronous modes also keep the replay buffer:
+        groups that are finished but not yet trained on, and the prompts whose trajectories are still being generated.
+        Parity target: ``verl/trainer/ppo/v1/trainer_base.py:887-960``."""
+        super()._save_checkpoint()
+        if self.replay_buffer.is_async:
+            rank, _ = self._dp_rank_world()
+            root = os.path.join(self.config.trainer.default_local_dir, f"global_step_{self.global_steps}")
+            self.replay_buffer.q.save_checkpoint(os.path.join(root, "transfer_queue" if rank == 0 else f"transfer_queue_rank{rank}"),
+                                                 metadata={"global_steps": self.global_steps, "param_version": self.param_version})
+
+    def _load_checkpoint(self) -> int:
+        step = super()._load_checkpoint()
+        if step and self.replay_buffer.is_async:
+            rank, _ = self._dp_rank_world()
+            folder = os.path.join(self.config.trainer.default_local_dir, f"global_step_{step}") \
+                if self.config.trainer.get("resume_mode", "auto") != "resume_path" else str(self.config.trainer.get("resume_from_path"))
+            path = os.path.join(folder, "transfer_queue" if rank == 0 else f"transfer_queue_rank{rank}")
+            if os.path.exists(os.path.join(path, "state.pt")):
+                meta = self.replay_buffer.q.load_checkpoint(path)
+                self.param_version = int(meta.get("param_version", self.param_version))
+                self._reissue_inflight_prompts()
+        return step
+
+    def _reissue_inflight_prompts(self, partition_id: str = "train") -> int:
+        """Prompt groups that were pending or running when the checkpoint was written start again from their stored prompt:
+        the partial trajectories they had produced are dropped, their counters reset, their sessions re-submitted under the
+        current parameter version. Parity target: ``verl/trainer/ppo/v1/trainer_base.py:849-885``."""
+        from .replay_buffer import PENDING, RUNNING
+
+        q = self.replay_buffer.q
+        live = q.list_keys(partition_id, lambda k, t: t.get("kind") == "prompt" and t.get("status") in (PENDING, RUNNING))
+        if not live:
+            return 0
+        old = q.list_keys(partition_id, lambda k, t: t.get("kind") == "traj" and t.get("uid") in set(live))
+        q.delete(old, partition_id)
+        prompts = []
+        for uid in live:
+            payload = dict(q.get([uid], None, partition_id)[0].get("prompt", {}))
+            payload["uid"] = uid
+            prompts.append(payload)
+            q.delete([uid], partition_id)   # _submit_prompts stores it again with fresh counters
+        self._submit_prompts(prompts, partition_id)
+        print(f"Re-issued {len(live)} in-flight prompts for step {self.global_steps}; cleared {len(old)} partial trajectories")
+        return len(live)
 
     def shutdown(self) -> None:
         for t in list(self._tasks):

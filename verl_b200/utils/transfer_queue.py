@@ -110,6 +110,37 @@ class TransferQueue:
         with self._cond:
             return self._cond.wait_for(predicate, timeout)
 
+    # ---- persistence (the asynchronous trainers checkpoint what is finished but not yet trained on, and the prompts in flight)
+    def save_checkpoint(self, path: str, metadata: Optional[dict] = None) -> None:
+        """Every partition's fields and tags into ``path/state.pt`` (written to a temporary name first, so a crash in the
+        middle of a save leaves the previous file). Parity target: ``transfer_queue.save_checkpoint`` as used by
+        ``verl/trainer/ppo/v1/trainer_base.py:887-960``."""
+        import os
+
+        import torch
+
+        os.makedirs(path, exist_ok=True)
+        with self._lock:
+            state = {"values": {p: {k: dict(v) for k, v in part.items()} for p, part in self._values.items()},
+                     "tags": {p: {k: dict(t) for k, t in part.items()} for p, part in self._tags.items()},
+                     "metadata": dict(metadata or {})}
+        tmp = os.path.join(path, "state.pt.tmp")
+        torch.save(state, tmp)
+        os.replace(tmp, os.path.join(path, "state.pt"))
+
+    def load_checkpoint(self, path: str) -> dict:
+        """Replace the queue's content by a saved state; returns the metadata stored with it."""
+        import os
+
+        import torch
+
+        state = torch.load(os.path.join(path, "state.pt"), weights_only=False)
+        with self._cond:
+            self._values = {p: dict(part) for p, part in state["values"].items()}
+            self._tags = {p: dict(part) for p, part in state["tags"].items()}
+            self._cond.notify_all()
+        return dict(state.get("metadata", {}))
+
 
 _default: Optional[TransferQueue] = None
 
