@@ -169,3 +169,42 @@ def test_rollouter_pauses_on_a_full_queue():
     assert roll._should_pause_generation() and roll.stats["pause_reason"] == "queue_full"
     q.get_sample(0)
     assert not roll._should_pause_generation()
+
+
+def test_rollouter_step_accounting_and_capacity_utilisation():
+    """The producer's step record after a weight sync: utilisation is the time-weighted share of the capacity in use, with
+    the capacity that held during each interval (replicas come and go inside a step); idle time starts when production
+    ran dry; the concurrency limit follows the number of replicas."""
+    import time
+
+    from verl_b200.experimental.fully_async_policy.fully_async_rollouter import FullyAsyncRollouter
+    from verl_b200.experimental.fully_async_policy.message_queue import MessageQueue
+
+    class SM:
+        replicas = [object(), object()]
+
+    r = FullyAsyncRollouter(agent_worker=None, server_manager=SM(), message_queue=MessageQueue(64), prompt_source=lambda k: [],
+                            n=1, sampling_params={}, required_samples=4, max_concurrent_samples=8)
+    t0 = 1000.0
+    # 2 s with 4 of 8 busy, 1 s with 8 of 16 after two replicas joined, 1 s with 20 of 16 (clamped), 1 s without capacity
+    r._active_history = [(t0, 4, 8), (t0 + 2, 8, 16), (t0 + 3, 20, 16), (t0 + 4, 3, 0), (t0 + 5, 0, 8)]
+    real_time = time.time
+    try:
+        time.time = lambda: t0 + 5
+        u = r._compute_rollout_resource_utilization()
+    finally:
+        time.time = real_time
+    assert abs(u - (2 * 4 + 1 * 8 + 1 * 16) / (2 * 8 + 1 * 16 + 1 * 16)) < 1e-9
+    assert len(r._active_history) == 1
+
+    assert r._per_replica == 4.0
+    SM.replicas = [object()] * 3
+    r._update_max_concurrent_samples()
+    assert r.max_concurrent == 12
+    r._step_generated, r._step_start = 5, real_time() - 2.0
+    r._idle_start = r._step_start + 0.5                        # production ran dry half a second into the step
+    rec = r.reset_staleness()
+    assert rec["fully_async/rollouter/step_generated_samples"] == 5 and r.completed_steps == 1 and r._step_generated == 0
+    assert abs(rec["fully_async/rollouter/active_time"] - 0.5) < 1e-6 and 0.7 < rec["fully_async/rollouter/idle_ratio"] < 0.8
+    assert 0.0 <= rec["dynamic_resource/rollout_resource_utilization"] <= 1.0 and r.step_samples_history == [(1, 5)]
+    assert r.statistics()["rollouter/max_concurrent_samples"] == 12

@@ -7,9 +7,14 @@ samples that would be stale when consumed reaches the budget
 (finished-but-unconsumed + in flight), and resumes after the next sync. Replicas can be added, removed and
 rebalanced while requests are running.
 
-Parity target: ``verl/experimental/fully_async_policy/fully_async_rollouter.py`` (``_feed_samples`` :859,
-``_processor_worker`` :902, ``_streaming_generation_main`` :1017, ``_should_pause_generation`` :1142,
-``add_replicas/remove_replicas/rebalance_requests`` :144-264, :1199-1274).
+After every weight sync ``reset_staleness`` closes the producer's "step": it reports how long the replicas were busy and
+idle since the previous sync, how many groups were produced, and the time-weighted utilisation of the rollout capacity
+(which changes when replicas come and go).
+
+Parity target: ``verl/experimental/fully_async_policy/fully_async_rollouter.py`` (``_compute_rollout_resource_utilization``
+:536, ``reset_staleness`` :594, ``_feed_samples`` :859, ``_record_active_count`` :892, ``_processor_worker`` :902,
+``_streaming_generation_main`` :1017, ``_should_pause_generation`` :1142, ``add_replicas/remove_replicas/rebalance_requests``
+:144-264, :1199-1274, ``_update_max_concurrent_samples`` :1274).
 """
 
 from __future__ import annotations
@@ -45,6 +50,14 @@ class FullyAsyncRollouter:
         self.paused = False
         self.running: dict[str, asyncio.Task] = {}
         self.stats = {"pauses": 0, "failed": 0}
+        # bookkeeping of the producer's step (the span between two weight syncs)
+        self._per_replica = self.max_concurrent / max(1, self._num_replicas())  # concurrency one replica is worth
+        self._active_history: list[tuple[float, int, int]] = [(time.time(), 0, self.max_concurrent)]
+        self._step_start = time.time()
+        self._idle_start = 0.0          # when production last ran dry (paused with nothing in flight)
+        self._step_generated = 0
+        self.completed_steps = 0
+        self.step_samples_history: list[tuple[int, int]] = []
 
     # ---- staleness control
     def max_samples_per_version(self) -> int:
@@ -61,11 +74,58 @@ class FullyAsyncRollouter:
             return True
         return False
 
-    def update_param_version(self, version: int) -> None:
-        """Called by the parameter synchroniser after a weight sync: the budget starts over."""
+    def update_param_version(self, version: int) -> dict:
+        """Called by the parameter synchroniser after a weight sync: the budget starts over. Returns the timing record of
+        the step that ended (``reset_staleness``)."""
         self.param_version = int(version)
-        self.produced_since_sync = self.mq.get_queue_size()  # what is still queued was made under older weights
+        return self.reset_staleness()
+
+    # ---- utilisation of the rollout capacity
+    def _num_replicas(self) -> int:
+        return len(getattr(self.sm, "replicas", None) or []) or 1
+
+    def _record_active_count(self) -> None:
+        """Event-driven history (time, trajectories groups in flight, capacity): one entry whenever either number changes."""
+        self._active_history.append((time.time(), len(self.running), self.max_concurrent))
+
+    def _update_max_concurrent_samples(self) -> None:
+        """The concurrency limit follows the number of active replicas (each replica is worth what it was worth at start)."""
+        self.max_concurrent = max(1, int(round(self._per_replica * self._num_replicas())))
+        self._record_active_count()
+
+    def _compute_rollout_resource_utilization(self) -> float:
+        """Share of the rollout capacity that was in use since the previous call: with the history entries (t_k, A_k, S_k),
+        sum_k (t_{k+1} - t_k) * min(A_k, S_k) / sum_k (t_{k+1} - t_k) * S_k. Every interval uses the capacity that held
+        during it (replicas can come and go inside a step); intervals without capacity carry no weight."""
+        self._record_active_count()
+        num = den = 0.0
+        for (t0, active, cap), (t1, _, _) in zip(self._active_history, self._active_history[1:]):
+            dt = t1 - t0
+            if dt <= 0 or cap <= 0:
+                continue
+            num += dt * min(active, cap)
+            den += dt * cap
+        self._active_history = [self._active_history[-1]]
+        return num / den if den > 0 else 0.0
+
+    def reset_staleness(self) -> dict:
+        """After a weight sync: what is still queued or in flight was started under older weights and counts against the
+        new budget; production resumes. Returns the producer-side timing of the step that ended."""
         self.paused = False
+        self.produced_since_sync = self.mq.get_queue_size()
+        now = time.time()
+        span = max(now - self._step_start, 1e-6)
+        active = self._idle_start - self._step_start if self._idle_start > self._step_start else span
+        timing = {"fully_async/rollouter/active_time": active, "fully_async/rollouter/version_time": span,
+                  "fully_async/rollouter/idle_ratio": 1.0 - active / span,
+                  "fully_async/rollouter/step_generated_samples": self._step_generated,
+                  "dynamic_resource/rollout_resource_utilization": self._compute_rollout_resource_utilization()}
+        if self._step_generated > 0:
+            self.completed_steps += 1
+            self.step_samples_history = (self.step_samples_history + [(self.completed_steps, self._step_generated)])[-16:]
+        self._step_generated = 0
+        self._step_start = now
+        return timing
 
     # ---- production
     async def _one_sample(self, prompt: dict) -> None:
@@ -79,10 +139,12 @@ class FullyAsyncRollouter:
         sample = RolloutSample(sample_id=f"{uid}@{v0}", uid=uid, trajectories=good, prompt=prompt, param_version_start=v0,
                                param_version_end=self.param_version, processing_time=time.time() - t0, failed=bool(bad))
         self.running.pop(uid, None)
+        self._record_active_count()
         if good:
             self.mq.put_sample(sample, self.param_version)
             self.produced += 1
             self.produced_since_sync += 1
+            self._step_generated += 1
 
     def feed(self) -> int:
         """Admit prompts up to the concurrency and staleness limits; returns how many were started."""
@@ -92,6 +154,8 @@ class FullyAsyncRollouter:
                 if not self.paused:
                     self.paused = True
                     self.stats["pauses"] += 1
+                if not self.running and self._idle_start <= self._step_start:
+                    self._idle_start = time.time()   # nothing in flight and nothing may start: the replicas idle from here
                 break
             got = self.prompt_source(1)
             if not got:
@@ -101,6 +165,8 @@ class FullyAsyncRollouter:
             self.running[p["uid"]] = asyncio.ensure_future(self._one_sample(p))
             self.submitted += 1
             started += 1
+        if started:
+            self._record_active_count()
         return started
 
     async def run(self, stop: Callable[[], bool], idle_sleep: float = 0.0) -> None:
@@ -112,6 +178,7 @@ class FullyAsyncRollouter:
     # ---- elastic replicas
     async def add_replicas(self, replicas: list) -> None:
         await self.sm.add_replicas(replicas)
+        self._update_max_concurrent_samples()
 
     async def remove_replicas(self, replicas: list) -> None:
         """Stop routing to the replicas, abort what they run (clients re-issue elsewhere with the partial output)."""
@@ -122,6 +189,7 @@ class FullyAsyncRollouter:
             self.sm.servers.pop(r.server_address, None)
             if r in self.sm.replicas:
                 self.sm.replicas.remove(r)
+        self._update_max_concurrent_samples()
 
     async def rebalance_requests(self, wait_inflight_timeout_s: float = 30.0, wait_inflight_poll_interval_s: float = 0.01) -> dict:
         """Spread the requests in flight evenly over the replicas that are active now (after replicas were added, the old
@@ -146,4 +214,6 @@ class FullyAsyncRollouter:
     def statistics(self) -> dict:
         return {"rollouter/submitted": self.submitted, "rollouter/produced": self.produced, "rollouter/running": len(self.running),
                 "rollouter/pauses": self.stats["pauses"], "rollouter/failed_sessions": self.stats["failed"],
-                "rollouter/param_version": self.param_version, "rollouter/queue_size": self.mq.get_queue_size()}
+                "rollouter/param_version": self.param_version, "rollouter/queue_size": self.mq.get_queue_size(),
+                "rollouter/max_concurrent_samples": self.max_concurrent, "rollouter/completed_steps": self.completed_steps,
+                "rollouter/paused": int(self.paused)}

@@ -94,7 +94,9 @@ class FullyAsyncTrainer(PPOTrainer):
             resume_fn=lambda: self._each_server("resume_generation"),
             transfer_fn=lambda v: self.actor_rollout_wg.update_weights(v),
             message_queue=self.mq,
-            set_version_fn=lambda v: (self.rollouter.update_param_version(v), self._each_server("set_global_steps", v)))
+            set_version_fn=lambda v: (setattr(self, "_rollouter_step_timing", self.rollouter.update_param_version(v)),
+                                      self._each_server("set_global_steps", v)))
+        self._rollouter_step_timing: dict = {}
         self.aggregator = MetricsAggregator()
         self.local_updates = 0
 
@@ -154,6 +156,7 @@ class FullyAsyncTrainer(PPOTrainer):
         res = res if isinstance(res, dict) else {}
         metrics["timing_s/param_sync"] = float(res.get("timing_s/param_sync", 0.0))
         metrics["fully_async/param_version"] = self.param_version
+        metrics.update(self._rollouter_step_timing or {})   # the producer's record of the step that this sync closed
 
     def step(self):
         return self.fit_step()

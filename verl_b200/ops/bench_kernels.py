@@ -205,6 +205,18 @@ def main(argv=None):
         gu = rnd(tok, 2 * Is)
         ms = T(lambda: F.swiglu(gu))
         report("swiglu_fwd", [tok, Is], ms, bytes_=2.0 * tok * Is * 3)
+    if want("gemm_swiglu"):
+        # up-projection of the gated MLP: GEMM with the activation in its epilogue against GEMM + activation kernel
+        Is = 4096 if a.small else I
+        x, w = rnd(tok, H), rnd(2 * Is, H)
+        ms_f = T(lambda: ops.gemm_swiglu(x, w, False))
+        ck = T.clocks
+        ms_fk = T(lambda: ops.gemm_swiglu(x, w, True))
+        ms_s = T(lambda: F.swiglu(ops.gemm(x, w, None, None, False, False, False, False, 0)))
+        print(json.dumps({"kernel": "gemm_swiglu_fused", "shape": [tok, 2 * Is, H], "ms_fused": round(ms_f, 4),
+                          "ms_fused_keep_preactivation": round(ms_fk, 4), "ms_gemm_plus_activation": round(ms_s, 4),
+                          "tflops_fused": round(2.0 * tok * 2 * Is * H / ms_f / 1e9, 1), "speedup": round(ms_s / ms_f, 3),
+                          "clocks": {"fused": ck, "separate": T.clocks}}), flush=True)
     if want("adamw"):
         n = (64 << 20) if a.small else (512 << 20)
         master, g = torch.randn(n, device=dev), torch.randn(n, device=dev)
