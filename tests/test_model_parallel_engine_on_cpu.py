@@ -139,6 +139,23 @@ def test_tensor_parallel_with_per_head_norms_matches_unsharded():
         assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
 
 
+@pytest.mark.parametrize("world,tp,pp,preset", [(2, 2, 1, "tiny-moe"), (2, 2, 1, "tiny-qwen2-moe"), (4, 2, 2, "tiny-moe")])
+def test_expert_tensor_parallel_matches_unsharded(world, tp, pp, preset):
+    """Mixture-of-experts layers under tensor parallelism: every expert's (and the shared expert's) intermediate width is
+    cut over the two ranks, the router stays whole. Same gradient norm, same updated full model (experts, router, shared
+    expert gate re-assembled from the shards) and the same log-probs as one process."""
+    ref_norm, ref_lp, ref_flat = _reference(preset)
+    res = _run(world, tp, pp, preset=preset)
+    dp = res[0]["dp"]
+    rows = ref_lp.chunk(dp)
+    for r in range(world):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert got.shape == ref_flat.shape
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r // (tp * pp)], atol=1e-4), r
+
+
 def test_expert_parallel_engine_matches_unsharded():
     """Two ranks, each with half of the experts and half of the batch: same gradient norm, same updated full model and the
     same log-probs as one process that holds every expert and sees the whole batch."""

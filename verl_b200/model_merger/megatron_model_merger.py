@@ -79,7 +79,7 @@ class MegatronModelMerger(BaseModelMerger):
 
         from ..models import make_flat_params
         from ..models.config import ModelConfig
-        from ..parallel.model_parallel import ShardMap, _slices
+        from ..parallel.model_parallel import ShardMap, _slices, cat_dim
 
         arch = ModelConfig.from_pretrained(self.config.hf_model_config_path)
         value_head = self.config.is_value_model
@@ -97,10 +97,10 @@ class MegatronModelMerger(BaseModelMerger):
                     continue
                 kind, blocks = meta[name]
                 parts = _slices(ShardMap(name, name, kind, tuple(blocks)), full.views[name], tp, t, ep, e)
-                off = 0
+                off, dim = 0, cat_dim(kind)
                 for part in parts:
-                    n = part.shape[0] if len(parts) > 1 else local.shape[0]
-                    part.copy_((local[off : off + n] if len(parts) > 1 else local).float())
+                    n = part.shape[dim] if len(parts) > 1 else local.shape[dim] if local.dim() > dim else 0
+                    part.copy_((local.narrow(dim, off, n) if len(parts) > 1 else local).float())
                     off += n
                 seen.add(name)
         missing = [n for n in full.views if n not in seen]

@@ -72,9 +72,16 @@ class ModelConfig:
 
         assert self.num_attention_heads % tp == 0 and self.num_key_value_heads % tp == 0, "tp must divide the head counts"
         assert self.is_moe or self.intermediate_size % tp == 0
+        # mixture-of-experts layers under tensor parallelism: every expert's (and the shared expert's) intermediate width is
+        # cut over the tensor-parallel ranks (expert tensor parallelism = tp), the router stays replicated
+        etp = tp if self.is_moe else 1
+        assert not self.is_moe or (self.moe_intermediate_size % etp == 0 and self.shared_expert_intermediate_size % etp == 0), \
+            "tp must divide the experts' intermediate sizes"
         c = dataclasses.replace(self, num_attention_heads=self.num_attention_heads // tp,
                                 num_key_value_heads=self.num_key_value_heads // tp,
                                 intermediate_size=self.intermediate_size // tp if not self.is_moe else self.intermediate_size,
+                                moe_intermediate_size=self.moe_intermediate_size // etp,
+                                shared_expert_intermediate_size=self.shared_expert_intermediate_size // etp,
                                 num_hidden_layers=self.num_hidden_layers if num_layers is None else num_layers,
                                 head_dim=self.head_dim, has_embedding=has_embedding, has_head=has_head,
                                 num_local_experts=(self.num_experts // ep if self.is_moe and ep > 1 else 0),

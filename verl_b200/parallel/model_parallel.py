@@ -30,7 +30,7 @@ import torch.distributed as dist
 from ..models.config import ModelConfig
 from ..models.weights import FlatParams
 
-__all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to_local", "copy_local_to_full"]
+__all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to_local", "copy_local_to_full", "cat_dim"]
 
 
 class ModelParallelTopology:
@@ -105,8 +105,10 @@ class ModelParallelTopology:
 class ShardMap:
     local_name: str
     full_name: str
-    kind: str              # rep | rows | cols | experts (dim 0 cut over the expert-parallel group)
-    blocks: tuple = ()     # rows: sizes of the stacked blocks of the FULL tensor, each block is cut into tp slices
+    # rep | rows | cols | experts (dim 0 cut over the expert-parallel group) | expert_rows / expert_cols (stacked expert
+    # matrices [E, rows, cols] under tensor parallelism: dim 1 cut block-wise like ``rows``, dim 2 cut like ``cols``)
+    kind: str
+    blocks: tuple = ()     # rows / expert_rows: sizes of the stacked blocks of the FULL tensor, each block is cut into tp slices
 
 
 def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_head: bool = False,
@@ -129,6 +131,14 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
             out.append(ShardMap(name, full_name, "rows", (full_cfg.vocab_size,)))
         elif rest.startswith("mlp.experts.") and topo.ep > 1:
             out.append(ShardMap(name, full_name, "experts"))
+        elif rest == "mlp.experts.gate_up_proj" and topo.tp > 1:
+            out.append(ShardMap(name, full_name, "expert_rows", (full_cfg.moe_intermediate_size, full_cfg.moe_intermediate_size)))
+        elif rest == "mlp.experts.down_proj" and topo.tp > 1:
+            out.append(ShardMap(name, full_name, "expert_cols"))
+        elif rest == "mlp.shared_expert.gate_up_proj.weight":
+            out.append(ShardMap(name, full_name, "rows", (full_cfg.shared_expert_intermediate_size,) * 2))
+        elif rest == "mlp.shared_expert.down_proj.weight":
+            out.append(ShardMap(name, full_name, "cols"))
         elif rest.startswith("self_attn.qkv_proj"):
             out.append(ShardMap(name, full_name, "rows", (full_cfg.q_size, full_cfg.kv_size, full_cfg.kv_size)))
         elif rest.startswith("mlp.gate_up_proj"):
@@ -150,12 +160,21 @@ def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int, ep: int = 1,
     if m.kind == "cols":
         w = full.shape[1] // tp
         return [full[:, tp_rank * w : (tp_rank + 1) * w]]
+    if m.kind == "expert_cols":
+        w = full.shape[2] // tp
+        return [full[:, :, tp_rank * w : (tp_rank + 1) * w]]
     parts, off = [], 0
     for b in m.blocks:
         w = b // tp
-        parts.append(full[off + tp_rank * w : off + (tp_rank + 1) * w])
+        lo = off + tp_rank * w
+        parts.append(full[:, lo : lo + w] if m.kind == "expert_rows" else full[lo : lo + w])
         off += b
     return parts
+
+
+def cat_dim(kind: str) -> int:
+    """Dimension along which the views of ``_slices`` line up in the local tensor."""
+    return {"cols": 1, "expert_rows": 1, "expert_cols": 2}.get(kind, 0)
 
 
 @torch.no_grad()
@@ -165,8 +184,7 @@ def copy_full_to_local(full: FlatParams, local: FlatParams, maps: list[ShardMap]
         if m.full_name not in full.views:
             continue  # e.g. lm_head of a tied model
         parts = _slices(m, full.views[m.full_name], tp, tp_rank, ep, ep_rank)
-        dim = 1 if m.kind == "cols" else 0
-        src = parts[0] if len(parts) == 1 else torch.cat(parts, dim)
+        src = parts[0] if len(parts) == 1 else torch.cat(parts, cat_dim(m.kind))
         local.views[m.local_name].copy_(src.to(local.views[m.local_name].dtype))
 
 
@@ -182,8 +200,8 @@ def copy_local_to_full(local: FlatParams, full: FlatParams, maps: list[ShardMap]
         if len(parts) == 1:
             parts[0].copy_(src.to(parts[0].dtype))
             continue
-        off = 0
+        off, dim = 0, cat_dim(m.kind)
         for p in parts:
-            n = p.shape[0]
-            p.copy_(src[off : off + n].to(p.dtype))
+            n = p.shape[dim]
+            p.copy_(src.narrow(dim, off, n).to(p.dtype))
             off += n

@@ -41,6 +41,22 @@ def full_positions(m: ShardMap, idx: torch.Tensor, local_shape: tuple, full_shap
     if m.kind == "cols":
         lc, fc = local_shape[1], full_shape[1]
         return (idx // lc) * fc + idx % lc + tp_rank * lc
+    if m.kind == "expert_cols":              # [E, rows, cols / tp]: the last dimension is cut
+        lc, fc = local_shape[2], full_shape[2]
+        return (idx // lc) * fc + idx % lc + tp_rank * lc
+    if m.kind == "expert_rows":              # [E, rows / tp (block-wise), cols]: per expert like ``rows``
+        cols = local_shape[2]
+        e, rem = idx // (local_shape[1] * cols), idx % (local_shape[1] * cols)
+        row, c = rem // cols, rem % cols
+        full_row = torch.empty_like(row)
+        l0 = f0 = 0
+        for b in m.blocks:
+            w = b // tp
+            sel = (row >= l0) & (row < l0 + w)
+            full_row[sel] = row[sel] - l0 + f0 + tp_rank * w
+            l0 += w
+            f0 += b
+        return (e * full_shape[1] + full_row) * cols + c
     inner = 1
     for d in local_shape[1:]:
         inner *= d

@@ -66,7 +66,15 @@ class ModelParallelEngine(NativeEngine):
             return
         self.topo = get_topology(self.tp_size, self.pp_size, self.ep_size)
         if self.full_arch.is_moe and self.tp_size > 1:
-            raise NotImplementedError("mixture-of-experts layers are not tensor-parallel; use expert_model_parallel_size")
+            # experts under tensor parallelism: every expert's intermediate width is cut over the tensor-parallel ranks
+            # (expert tensor parallelism, the reference's default ``expert_tensor_parallel_size = tensor_model_parallel_size``)
+            etp = getattr(self.engine_config, "expert_tensor_parallel_size", None)
+            if etp is not None and int(etp) != self.tp_size:
+                raise NotImplementedError(f"expert_tensor_parallel_size={etp}: experts are cut over the whole tensor-parallel group "
+                                          f"({self.tp_size}); leave it unset or set it to the tensor-parallel size")
+            if self.ep_size > 1:
+                raise NotImplementedError("expert parallelism shards whole experts over the data-parallel ranks and needs tp = 1; "
+                                          "with tp > 1 the experts are tensor-parallel instead")
         if self.full_arch.tie_word_embeddings and self.pp_size > 1:
             raise NotImplementedError("pipeline parallelism with tied input/output embeddings needs the embedding shared between "
                                       "the first and the last stage; use pipeline_model_parallel_size=1 for this model")
@@ -95,6 +103,8 @@ class ModelParallelEngine(NativeEngine):
                 return x
 
             self.model.tp_reduce = reduce
+            if self.full_arch.is_moe:
+                self.model.etp_sum = reduce
             self.fused_tp_collectives = False
             use_sp = bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1
             fused = None
