@@ -68,7 +68,7 @@ __all__ = ["NativeEngine", "NativeEngineWithLMHead", "NativeEngineWithValueHead"
 
 
 def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: Optional[torch.Tensor],
-                      response_length: int):
+                      response_length: int, lens_list: Optional[list] = None):
     """Remove padding from a [b, P+R] batch (left-padded prompt, right-padded response).
 
     Returns ``(packed_batch, labels, resp_index, resp_valid)`` where ``labels[t]`` is the next token of packed
@@ -77,8 +77,9 @@ def pack_padded_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, pos
     """
     b, L = input_ids.shape
     mask = attention_mask.bool()
-    lens = mask.sum(-1)
-    lens_list = lens.tolist()  # one host sync per micro-batch
+    if lens_list is None:  # (callers that know the row lengths on the host pass them: no device synchronisation here)
+        lens_list = mask.sum(-1).tolist()
+    lens_list = [int(x) for x in lens_list]
     ids = input_ids[mask]
     labels = torch.roll(input_ids, shifts=-1, dims=1)[mask]
     if position_ids is None:
@@ -122,18 +123,37 @@ def prompt_group_ids(input_ids: torch.Tensor, attention_mask: torch.Tensor, resp
     return gid.tolist()
 
 
+def _ranges(segments: list) -> "np.ndarray":
+    """Concatenation of ``arange(start, start + n)`` over ``(start, n)`` pairs, built with two array operations."""
+    import numpy as np
+
+    if not segments:
+        return np.zeros(0, dtype=np.int64)
+    seg = np.asarray(segments, dtype=np.int64).reshape(-1, 2)
+    starts, lens = seg[:, 0], seg[:, 1]
+    total = int(lens.sum())
+    if total == 0:
+        return np.zeros(0, dtype=np.int64)
+    first = np.concatenate([[0], np.cumsum(lens)[:-1]])
+    return np.repeat(starts - first, lens) + np.arange(total, dtype=np.int64)
+
+
 def pack_shared_prefix_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: Optional[torch.Tensor],
-                             response_length: int, gids: list[int]):
+                             response_length: int, gids: list[int], plen: Optional[list] = None, rlen: Optional[list] = None):
     """Packing with the prompt of every group stored once (see ``PackedBatch.expand_index``).
 
     Returns ``(packed_batch, positions_sel, labels_sel, resp_valid)``: ``positions_sel[n]`` is the stream position whose
-    output predicts the n-th valid response token (row-major over ``resp_valid``) and ``labels_sel[n]`` that token."""
+    output predicts the n-th valid response token (row-major over ``resp_valid``) and ``labels_sel[n]`` that token.
+    ``plen`` / ``rlen``: valid prompt / response tokens per row when the caller already has them on the host (saves the
+    device synchronisation that reading them from the mask costs). The index arrays are built on the host from a handful
+    of (start, length) segments per row and copied over once each."""
     b, L = input_ids.shape
     P = L - response_length
     dev = input_ids.device
     mask = attention_mask.bool()
-    plen = mask[:, :P].sum(-1).tolist()
-    rlen = mask[:, P:].sum(-1).tolist()
+    if plen is None or rlen is None:
+        plen = mask[:, :P].sum(-1).tolist()
+        rlen = mask[:, P:].sum(-1).tolist()
     src, expand, collapse, pos_sel, lab_src, lens_e = [], [], [], [], [], []
     t_d = t_e = 0
     i = 0
@@ -141,27 +161,27 @@ def pack_shared_prefix_batch(input_ids: torch.Tensor, attention_mask: torch.Tens
         j = i
         while j + 1 < b and gids[j + 1] == gids[i]:
             j += 1
-        p = plen[i]
+        p = int(plen[i])
         prompt_lo = t_d
-        src.append(torch.arange(i * L + P - p, i * L + P))              # the leader's prompt tokens
-        collapse.append(torch.arange(t_e, t_e + p))                      # represented by the leader's copy
+        src.append((i * L + P - p, p))                 # the leader's prompt tokens
+        collapse.append((t_e, p))                      # represented by the leader's copy
         t_d += p
         for m in range(i, j + 1):
-            r = rlen[m]
-            src.append(torch.arange(m * L + P, m * L + P + r))
-            expand.append(torch.arange(prompt_lo, prompt_lo + p))
-            expand.append(torch.arange(t_d, t_d + r))
-            collapse.append(torch.arange(t_e + p, t_e + p + r))
+            r = int(rlen[m])
+            src.append((m * L + P, r))
+            expand.append((prompt_lo, p))
+            expand.append((t_d, r))
+            collapse.append((t_e + p, r))
             if r > 0:
-                pos_sel.append(torch.tensor([prompt_lo + p - 1], dtype=torch.int64))
-                pos_sel.append(torch.arange(t_d, t_d + r - 1))
-                lab_src.append(torch.arange(m * L + P, m * L + P + r))
+                pos_sel.append((prompt_lo + p - 1, 1))
+                pos_sel.append((t_d, r - 1))
+                lab_src.append((m * L + P, r))
             lens_e.append(p + r)
             t_d += r
             t_e += p + r
         i = j + 1
-    cat = lambda xs: (torch.cat(xs) if xs else torch.zeros(0, dtype=torch.int64)).to(dev)
-    src_t, lab_t = cat(src), cat(lab_src)
+    to_dev = lambda segs: torch.from_numpy(_ranges(segs)).to(dev, non_blocking=True)
+    src_t, lab_t = to_dev(src), to_dev(lab_src)
     flat_ids = input_ids.reshape(-1)
     ids_d = flat_ids[src_t]
     if position_ids is None:
@@ -171,8 +191,8 @@ def pack_shared_prefix_batch(input_ids: torch.Tensor, attention_mask: torch.Tens
     cu = torch.zeros(len(lens_e) + 1, dtype=torch.int32)
     cu[1:] = torch.cumsum(torch.tensor(lens_e, dtype=torch.int32), 0)
     batch = PackedBatch(input_ids=ids_d.contiguous(), positions=pos_full[src_t].to(torch.int32).contiguous(), cu_seqlens=cu.to(dev),
-                        max_seqlen=max(lens_e) if lens_e else 0, cu_seqlens_cpu=cu, expand_index=cat(expand), collapse_index=cat(collapse))
-    return batch, cat(pos_sel), flat_ids[lab_t].contiguous(), mask[:, P:]
+                        max_seqlen=max(lens_e) if lens_e else 0, cu_seqlens_cpu=cu, expand_index=to_dev(expand), collapse_index=to_dev(collapse))
+    return batch, to_dev(pos_sel), flat_ids[lab_t].contiguous(), mask[:, P:]
 
 
 class NativeEngine(BaseEngine):
@@ -674,6 +694,10 @@ class NativeEngine(BaseEngine):
             idx = torch.tensor(p, dtype=torch.int64, device=ids.device)
             mb = {k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v)
                   for k, v in data.items()} | {"_rows": p} | ({"_gids": [gids_all[r] for r in p]} if share else {})
+            if share:      # lengths already read for the split: the packing of each micro-batch reuses them
+                mb["_plen"], mb["_rlen"] = [pl[r] for r in p], [rl[r] for r in p]
+            elif dyn:
+                mb["_lens"] = [lens[r] for r in p]
             if mb.get("multi_modal_inputs") is not None:   # per-row processor outputs (vision-language models)
                 mb["multi_modal_inputs"] = [data["multi_modal_inputs"][r] for r in p]
             out.append(mb)
@@ -730,15 +754,27 @@ class NativeEngine(BaseEngine):
         return outs, rows, losses, metrics
 
     def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
-        batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
-                                                                  mb.get("position_ids"), R)
-        # the LM head (a third of a 7B forward's head+tail work at vocabulary 152k) runs only where a response token is
-        # predicted: prompt positions never enter a loss or a returned log-prob
-        if self.sp_size > 1:
-            return self._forward_micro_sp(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad)
-        positions = resp_index[resp_valid]
-        position_labels = None
         gids = mb.get("_gids")
+        replay_or_record = self.arch.is_moe and (mb.get("routed_experts") is not None or (bool(mb.get("record_routing", False)) and not need_grad))
+        shared = (gids is not None and len(set(gids)) < len(gids) and self.model.tp is None and self.sp_size == 1
+                  and not replay_or_record)
+        if shared:
+            # members of a group share their prompt: it is embedded, projected and fed through the MLPs once
+            batch, positions, position_labels, resp_valid = pack_shared_prefix_batch(
+                mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R, gids, mb.get("_plen"), mb.get("_rlen"))
+            labels = None
+        else:
+            lens = mb.get("_lens")
+            if lens is None and mb.get("_plen") is not None:
+                lens = [a + b for a, b in zip(mb["_plen"], mb["_rlen"])]
+            batch, labels, resp_index, resp_valid = pack_padded_batch(mb["input_ids"], mb["attention_mask"],
+                                                                      mb.get("position_ids"), R, lens)
+            # the LM head (a third of a 7B forward's head+tail work at vocabulary 152k) runs only where a response token is
+            # predicted: prompt positions never enter a loss or a returned log-prob
+            if self.sp_size > 1:
+                return self._forward_micro_sp(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad)
+            positions = resp_index[resp_valid]
+            position_labels = None
         # router replay (mixture-of-experts): take every router's expert choice from the batch, or record it for the batch
         replay = mb.get("routed_experts") if self.arch.is_moe else None
         record = bool(mb.get("record_routing", False)) and self.arch.is_moe and not need_grad
@@ -751,10 +787,6 @@ class NativeEngine(BaseEngine):
             mask = mb["attention_mask"].bool()
             self.model.router_replay = (RouterReplay.from_tokens(replay[mask], moe_layers) if replay is not None
                                         else RouterReplay("record"))
-        if gids is not None and len(set(gids)) < len(gids) and self.model.tp is None:
-            # members of a group share their prompt: it is embedded, projected and fed through the MLPs once
-            batch, positions, position_labels, resp_valid = pack_shared_prefix_batch(mb["input_ids"], mb["attention_mask"],
-                                                                                     mb.get("position_ids"), R, gids)
         extra = {}
         if mb.get("multi_modal_inputs") is not None:
             assert self.arch.is_multimodal, "multi_modal_inputs need a vision-language architecture"
