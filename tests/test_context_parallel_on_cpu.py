@@ -206,3 +206,119 @@ def test_zigzag_layout_bookkeeping():
     assert torch.equal(gathered[order], torch.arange(total))
     flat = ContextParallel(None, 1, size, zigzag=False)
     assert flat.pad_multiple() == 3 and flat.chunks(total) == [(8, 16)] and flat._stream_order(total, "cpu") is None
+
+
+def test_dynamic_cp_scheduler_packs_rows_into_aligned_groups():
+    from verl_b200.utils.dynamic_cp_scheduler import DynamicCPScheduler, required_group_size
+
+    assert [required_group_size(n, 100, 8) for n in (1, 100, 101, 200, 201, 799)] == [1, 1, 2, 2, 4, 8]
+    with pytest.raises(ValueError):
+        required_group_size(801, 100, 8)
+    with pytest.raises(ValueError):
+        DynamicCPScheduler(100, 6)
+    lens = [790, 30, 410, 95, 180, 60, 20, 399, 100, 5, 150, 77]
+    sch = DynamicCPScheduler(100, 8)
+    plan = sch.schedule(lens)
+    seen = []
+    for mb in plan:
+        assert len(mb) == 8
+        for r, a in enumerate(mb):
+            if not a.rows:
+                continue
+            assert a.start % a.size == 0 and a.start <= r < a.start + a.size           # aligned window that contains the rank
+            assert all(mb[q].rows == a.rows and mb[q].size == a.size for q in range(a.start, a.start + a.size))
+            assert all(-(-lens[i] // a.size) <= 100 for i in a.rows)
+            if r == a.start:
+                seen += a.rows
+    assert sorted(seen) == list(range(len(lens)))                                       # every row exactly once
+    loads = sch.loads(lens, plan)
+    assert all(x <= 100 + 1e-9 for mb in loads for x in mb)
+    assert len(plan) <= 4                                                               # 2516 tokens, 800 per micro-batch at best
+    # one long row: the whole block; only short rows: single ranks, spread over the block
+    assert [a.size for a in DynamicCPScheduler(100, 4).schedule([400])[0]] == [4] * 4
+    p = DynamicCPScheduler(100, 4).schedule([50, 50, 50, 50])
+    assert len(p) == 1 and sorted(a.rows[0] for a in p[0]) == [0, 1, 2, 3] and all(a.size == 1 for a in p[0])
+
+
+def _ragged_data():
+    """Rows of 24, 17, 12 and 24 valid tokens (right-padded responses), so that the rows need different group sizes."""
+    data = _data()
+    am = data["attention_mask"].clone()
+    am[1, 20:] = 0
+    am[2, 12:] = 0
+    data["attention_mask"] = am
+    data["response_mask"] = am[:, -data["responses"].shape[1]:].clone()
+    return data
+
+
+def _dyn_proc(rank, world, port, cp, q):
+    try:
+        os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                          VERL_ENGINE_DEVICE="cpu")
+        from functools import partial
+
+        from verl_b200.models import get_preset
+        from verl_b200.utils.distributed import initialize_global_process_group
+        from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+        from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+        from verl_b200.workers.utils.losses import sft_loss
+
+        initialize_global_process_group()
+        ec = FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2, context_parallel_size=cp, dynamic_context_parallel=True,
+                              max_seqlen_per_dp_cp_rank=12)
+        eng = NativeEngineWithLMHead(get_preset("tiny-llama"), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05))
+        eng.initialize()
+        dp = world // cp
+        data = _ragged_data()
+        shard = {k: v.chunk(dp)[rank // cp] for k, v in data.items()}
+        out = eng.train_batch(dict(shard), partial(sft_loss, None))
+        sizes = sorted({a.size for mb in eng.last_dcp_plan for a in mb if a.rows})
+        lp = eng.infer_batch(dict(shard))["model_output"]["log_probs"]
+        q.put((rank, {"grad_norm": float(out["metrics"]["grad_norm"]), "flat": eng.params.flat.float().numpy(), "lp": lp.float().numpy(),
+                      "sizes": sizes, "restored": eng.sp_size == cp}))
+    except Exception:
+        import traceback
+
+        q.put((rank, {"error": traceback.format_exc()}))
+
+
+@pytest.mark.parametrize("world,cp", [(4, 4), (2, 2)])
+def test_dynamic_context_parallel_matches_single_rank(world, cp):
+    """A group size per row (rows of 24, 17, 12 and 24 tokens with 12 tokens per rank: groups of 2, 2, 1 and 2 ranks) gives
+    the update and the log-probs of one rank that holds everything."""
+    import torch.multiprocessing as mp
+
+    os.environ["VERL_ENGINE_DEVICE"] = "cpu"
+    from functools import partial
+
+    from verl_b200.models import get_preset
+    from verl_b200.workers.config import FSDPEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
+    from verl_b200.workers.utils.losses import sft_loss
+
+    data = _ragged_data()
+    ref = NativeEngineWithLMHead(get_preset("tiny-llama"), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
+    ref.initialize()
+    ref_norm = float(ref.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"])
+    ref_lp = ref.infer_batch(dict(data))["model_output"]["log_probs"]
+    ref_flat = ref.params.flat.clone()
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_dyn_proc, args=(r, world, port, cp, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in range(world))
+    for p in ps:
+        p.join(timeout=30)
+    m = data["attention_mask"][:, -ref_lp.shape[1]:].bool()
+    for r in range(world):
+        assert "error" not in res[r], res[r]["error"]
+        assert res[r]["restored"] and len(res[r]["sizes"]) >= 2, res[r]["sizes"]           # more than one group size was in use
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        n = min(ref_flat.numel(), res[r]["flat"].size)     # the flat buffer is padded to a multiple of the world size
+        assert torch.allclose(torch.from_numpy(res[r]["flat"])[:n], ref_flat.float()[:n], atol=3e-4), r
+        assert torch.allclose(torch.from_numpy(res[r]["lp"])[m], ref_lp[m], atol=1e-4), r

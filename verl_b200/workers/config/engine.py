@@ -69,6 +69,10 @@ class FSDPEngineConfig(EngineConfig):
     # keys / values around attention (no constraint on the number of KV heads; exclusive with Ulysses)
     context_parallel_size: int = 1
     context_parallel_mode: str = "zigzag"   # zigzag (rank i holds chunks i and 2 cp - 1 - i of the stream: balanced causal work) | contiguous
+    # a group size per row instead of one for the run: every row is cut over the smallest power-of-two group of the block's
+    # ranks that keeps its share under max_seqlen_per_dp_cp_rank tokens (context_parallel_size = the block, a power of two)
+    dynamic_context_parallel: bool = False
+    max_seqlen_per_dp_cp_rank: int = 4096
     zero_stage: int = 2
     enable_gradient_checkpointing: bool = True
     enable_activation_offload: bool = False

@@ -323,6 +323,7 @@ class NativeEngine(BaseEngine):
             assert not self.arch.is_generic, "context parallelism needs one of the natively supported model families"
             self.sp_size = self.cp_size
         self.sp_group, self.sp_rank = None, 0
+        self._dcp_scheduler, self._dcp = None, {}
         if self.sp_size > 1:
             assert self.world % self.sp_size == 0 and not self.value_head, "sequence parallel size must divide the data-parallel world"
             assert self.cp_size > 1 or self.arch.num_key_value_heads % self.sp_size == 0, "sequence parallel size must divide the KV heads"
@@ -344,8 +345,31 @@ class NativeEngine(BaseEngine):
                 mode = str(getattr(ec, "context_parallel_mode", "zigzag") or "zigzag")
                 assert mode in ("zigzag", "contiguous"), f"context_parallel_mode {mode!r}"
                 self.model.sp = ContextParallel(self.sp_group, self.sp_rank, self.sp_size, zigzag=(mode == "zigzag"))
+                if bool(getattr(ec, "dynamic_context_parallel", False)):
+                    # a group size per row: one ContextParallel object (and process group) per power-of-two size and aligned
+                    # window of the block; the scheduler says which one a micro-batch uses on this rank
+                    from ....utils.dynamic_cp_scheduler import DynamicCPScheduler
+
+                    C = self.sp_size
+                    self._dcp_scheduler = DynamicCPScheduler(int(getattr(ec, "max_seqlen_per_dp_cp_rank", 4096)), C)
+                    self._dcp = {C: (self.model.sp, self.sp_group, self.sp_rank), 1: (None, None, 0)}
+                    size = C // 2
+                    while size >= 2:
+                        if self.group is None:   # collective creation: every rank walks every block and window
+                            for g0 in range(0, self.world, size):
+                                grp = dist.new_group(pool[g0 : g0 + size])
+                                if g0 <= self.rank < g0 + size:
+                                    self._dcp[size] = (ContextParallel(grp, self.rank - g0, size, zigzag=(mode == "zigzag")), grp, self.rank - g0)
+                        else:
+                            g0 = self.rank // size * size
+                            grp = dist.new_group(pool[g0 : g0 + size], use_local_synchronization=True)
+                            self._dcp[size] = (ContextParallel(grp, self.rank - g0, size, zigzag=(mode == "zigzag")), grp, self.rank - g0)
+                        size //= 2
             else:
                 self.model.sp = UlyssesSequenceParallel(self.sp_group, self.sp_rank, self.sp_size)
+        # the block of ranks that holds the same rows (with dynamic context parallelism ``sp_size`` / ``sp_group`` / ``sp_rank``
+        # follow the group of the micro-batch at hand; the block itself does not change)
+        self._blk_size, self._blk_rank = self.sp_size, self.sp_rank
         # shared-prompt packing of GRPO groups (same results, fewer tokens through every projection and MLP)
         self._share_prefix = (bool(getattr(ec, "use_prefix_grouper", True)) and os.environ.get("VERL_B200_SHARE_PREFIX", "1") != "0"
                               and self.sp_size == 1 and not self.arch.is_generic)
@@ -637,6 +661,8 @@ class NativeEngine(BaseEngine):
         ids = data["input_ids"]
         n = ids.shape[0]
         dyn = bool(data.get("use_dynamic_bsz", getattr(ec, "use_dynamic_bsz", False)))
+        if self._dcp_scheduler is not None:
+            return self._dynamic_cp_micro_batches(data)
         share = self._share_prefix and "responses" in data and not self.value_head
         gids_all = prompt_group_ids(ids, data["attention_mask"], data["responses"].shape[1]) if share else None
         if share and len(set(gids_all)) == len(gids_all):
@@ -703,6 +729,26 @@ class NativeEngine(BaseEngine):
             out.append(mb)
         return out
 
+    def _dynamic_cp_micro_batches(self, data: dict) -> list[dict]:
+        """Micro-batches of dynamic context parallelism: the scheduler packs the block's rows (every rank of the block holds
+        all of them) into micro-batches of per-row groups; this rank keeps the ones it takes part in. ``_dcp`` = size of the
+        group that works on the micro-batch, ``_dcp_leader`` = this rank reports the group's outputs to the block."""
+        ids = data["input_ids"]
+        n = ids.shape[0]
+        lens = [int(x) for x in data["attention_mask"].sum(-1).tolist()]
+        plan = self._dcp_scheduler.schedule(lens)
+        self.last_dcp_plan = plan
+        out = []
+        for ranks in plan:
+            a = ranks[self._blk_rank]
+            if not a.rows:
+                continue
+            idx = torch.tensor(a.rows, dtype=torch.int64, device=ids.device)
+            mb = {k: (v[idx] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == n else v) for k, v in data.items()}
+            mb.update(_rows=list(a.rows), _dcp=a.size, _dcp_leader=self._blk_rank == a.start, _lens=[lens[r] for r in a.rows])
+            out.append(mb)
+        return out
+
     def forward_backward_batch(self, data, loss_function: Optional[Callable] = None, forward_only: bool = False) -> dict:
         """``data``: dict-like with padded ``input_ids``/``attention_mask``/``position_ids`` [b, P+R], ``responses``
         [b, R] and whatever the loss function needs.  Returns ``{"model_output": {...}, "loss": ..., "metrics": ...}``
@@ -721,18 +767,38 @@ class NativeEngine(BaseEngine):
             if self.world > 1:
                 pack = torch.stack([tok, seqs])
                 dist.all_reduce(pack, group=self.group)
-                tok, seqs = pack[0] / self.sp_size, pack[1] / self.sp_size  # the ranks of a sequence-parallel block hold the same rows
+                tok, seqs = pack[0] / self._blk_size, pack[1] / self._blk_size  # the ranks of a sequence-parallel block hold the same rows
             data["global_batch_info"] = dict(dp_size=self.world, batch_num_tokens=tok, global_batch_size=seqs,
                                              loss_scale_factor=data.get("loss_scale_factor"))
         mbs = self._micro_batches(data, forward_only)
         outs, rows, losses, metrics = self._run_micro_batches(mbs, R, temperature, calc_entropy, loss_function, forward_only)
-        inv = torch.empty(n, dtype=torch.int64, device=self.device)
-        inv[torch.tensor(rows, dtype=torch.int64, device=self.device)] = torch.arange(n, device=self.device)
-        model_output = {k: torch.cat(v, 0)[inv] for k, v in outs.items()}
+        if self._dcp_scheduler is not None:
+            self.sp_size = self._blk_size      # back to the block: what other code sees between passes
+            self.model.sp, self.sp_group, self.sp_rank = self._dcp[self._blk_size]
+            model_output = self._dynamic_cp_collect(mbs, outs, n, R, calc_entropy or not forward_only)
+        else:
+            inv = torch.empty(n, dtype=torch.int64, device=self.device)
+            inv[torch.tensor(rows, dtype=torch.int64, device=self.device)] = torch.arange(n, device=self.device)
+            model_output = {k: torch.cat(v, 0)[inv] for k, v in outs.items()}
         result = {"model_output": model_output, "metrics": metrics}
         if losses:
             result["loss"] = torch.stack(losses).sum()
         return result
+
+    def _dynamic_cp_collect(self, mbs: list[dict], outs: dict, n: int, R: int, with_entropy: bool) -> dict:
+        """Per-row outputs of the whole block on every rank of it: each group's first rank writes the rows its group worked
+        on into a zeroed [n, R] tensor, the block sums them (every row was computed by exactly one group)."""
+        keys = ["log_probs"] + (["entropy"] if with_entropy else [])
+        full = {k: torch.zeros(n, R, dtype=torch.float32, device=self.device) for k in keys}
+        for i, mb in enumerate(mbs):
+            if not mb["_dcp_leader"]:
+                continue
+            idx = torch.tensor(mb["_rows"], dtype=torch.int64, device=self.device)
+            for k in keys:
+                full[k][idx] = outs[k][i].float()
+        stacked = torch.stack([full[k] for k in keys])
+        dist.all_reduce(stacked, group=self._dcp[self._dcp_scheduler.cp_size][1])
+        return {k: stacked[j] for j, k in enumerate(keys)}
 
     def _run_micro_batches(self, mbs: list[dict], R: int, temperature: float, calc_entropy: bool, loss_function, forward_only: bool):
         """Forward (+ loss + backward) of every micro-batch; model-parallel engines override this with their schedule."""
@@ -754,6 +820,11 @@ class NativeEngine(BaseEngine):
         return outs, rows, losses, metrics
 
     def _forward_micro(self, mb: dict, R: int, temperature: float, calc_entropy: bool, need_grad: bool) -> dict:
+        if "_dcp" in mb:
+            # dynamic context parallelism: this micro-batch runs in the group the scheduler chose for its rows (the decoder
+            # reads ``model.sp`` in the forward pass and in the backward pass that follows before the next micro-batch)
+            self.model.sp, self.sp_group, self.sp_rank = self._dcp[mb["_dcp"]]
+            self.sp_size = mb["_dcp"]
         gids = mb.get("_gids")
         replay_or_record = self.arch.is_moe and (mb.get("routed_experts") is not None or (bool(mb.get("record_routing", False)) and not need_grad))
         shared = (gids is not None and len(set(gids)) < len(gids) and self.model.tp is None and self.sp_size == 1
