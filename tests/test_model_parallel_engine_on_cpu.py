@@ -14,7 +14,18 @@ def _data(seed=0, b=4, L=24, R=16, V=500):
     return {"input_ids": ids, "attention_mask": am, "responses": ids[:, -R:], "response_mask": am[:, -R:]}
 
 
-def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False):
+def _arch(preset: str):
+    """``name`` or ``name:L`` (the preset with L layers)."""
+    import dataclasses
+
+    from verl_b200.models import get_preset
+
+    name, _, layers = preset.partition(":")
+    cfg = get_preset(name)
+    return dataclasses.replace(cfg, num_hidden_layers=int(layers)) if layers else cfg
+
+
+def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False, vpp=1):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                           VERL_ENGINE_DEVICE="cpu")
@@ -31,7 +42,9 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedu
                                micro_batch_size_per_gpu=mbs if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
         object.__setattr__(ec, "pipeline_schedule", schedule)
         object.__setattr__(ec, "sequence_parallel", sp)
-        eng = EngineRegistry.new("language_model", "megatron", get_preset(preset), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
+        if vpp > 1:
+            object.__setattr__(ec, "virtual_pipeline_model_parallel_size", vpp)
+        eng = EngineRegistry.new("language_model", "megatron", _arch(preset), ec, OptimizerConfig(lr=1e-2, clip_grad=0.05), device="cpu")
         eng.initialize()
         dp = eng.topo.dp
         data = _data()
@@ -51,7 +64,7 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedu
         q.put((rank, {"error": traceback.format_exc()}))
 
 
-def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False):
+def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=False, vpp=1):
     import torch.multiprocessing as mp
 
     with socket.socket() as s:
@@ -59,7 +72,7 @@ def _run(world, tp, pp, ep=1, preset="tiny-llama", mbs=2, schedule="1f1b", sp=Fa
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset, mbs, schedule, sp)) for r in range(world)]
+    ps = [ctx.Process(target=_proc, args=(r, world, port, tp, pp, q, ep, preset, mbs, schedule, sp, vpp)) for r in range(world)]
     for p in ps:
         p.start()
     res = dict(q.get(timeout=300) for _ in range(world))
@@ -79,7 +92,7 @@ def _reference(preset="tiny-llama"):
     from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
     from verl_b200.workers.utils.losses import sft_loss
 
-    eng = NativeEngineWithLMHead(get_preset(preset), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
+    eng = NativeEngineWithLMHead(_arch(preset), FSDPEngineConfig(seed=7, micro_batch_size_per_gpu=2), OptimizerConfig(lr=1e-2, clip_grad=0.05))
     eng.initialize()
     out = eng.train_batch(dict(_data()), partial(sft_loss, None))
     lp = eng.infer_batch(dict(_data()))["model_output"]["log_probs"]
@@ -99,6 +112,22 @@ def test_model_parallel_engine_matches_unsharded(world, tp, pp):
     for r in range(world):
         d = r // (tp * pp)
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[d], atol=1e-4), r
+
+
+@pytest.mark.parametrize("world,tp,pp,vpp,layers,mbs", [(2, 1, 2, 2, 4, 1), (2, 1, 2, 3, 6, 2), (3, 1, 3, 2, 6, 1), (4, 2, 2, 2, 4, 1)])
+def test_interleaved_pipeline_stages_match_unsharded(world, tp, pp, vpp, layers, mbs):
+    """Virtual pipeline stages: every rank holds ``vpp`` chunks of the layer stack (chunk v of stage s = block v * pp + s)
+    and a micro-batch goes ``vpp`` times round the ring; fewer (4 rows in 2) and more (4 rows in 4) micro-batches than
+    stages; with tensor parallelism. Same update, log-probs and re-assembled full model as one process."""
+    ref_norm, ref_lp, ref_flat = _reference(f"tiny-llama:{layers}")
+    res = _run(world, tp, pp, preset=f"tiny-llama:{layers}", mbs=mbs, vpp=vpp)
+    dp = res[0]["dp"]
+    rows = ref_lp.chunk(dp)
+    for r in range(world):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r // (tp * pp)], atol=1e-4), r
 
 
 @pytest.mark.parametrize("world,pp,mbs,schedule", [(2, 2, 1, "1f1b"), (3, 3, 1, "1f1b"), (2, 2, 1, "gpipe")])

@@ -388,6 +388,7 @@ class DecoderModel:
         self.fp8_weights: Optional[dict] = None         # data_ptr of a bf16 weight -> (e4m3 copy, block scales)
         self.offloader = None                           # ActivationOffloader: inputs of recomputed layers live on the host
         self.etp_sum = None                             # all-reduce over the tensor-parallel group (experts cut over it)
+        self.chunk = None                               # (lo, hi, first, last): the model chunk the next pass runs (virtual stages)
         # tensor-parallel training (this model is one shard: 1/tp of heads and MLP width): ``reduce(x)`` must sum x over the
         # tensor-parallel group in place. Forward: after the row-parallel o_proj / down_proj. Backward: on the input
         # gradients of the column-parallel qkv_proj / gate_up_proj.
@@ -1103,7 +1104,11 @@ class DecoderModel:
         self._ensure_rope(batch.max_seqlen + 1)
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(-1, "forward")
-        if cfg.has_embedding:
+        # model chunk (interleaved pipeline stages): layers [lo, hi) of this model; the embedding belongs to the first chunk
+        # and the final norm + head to the last one
+        lo, hi, c_first, c_last = self.chunk if self.chunk is not None else (0, cfg.num_hidden_layers, True, True)
+        use_embed = cfg.has_embedding and c_first
+        if use_embed:
             ids = batch.input_ids if self.sp is None else batch.input_ids[self.sp.local_rows(batch.num_tokens, batch.input_ids.device)]
             a = F.embedding(ids, self.params["embed_tokens.weight"])
             if self.tsp is not None:
@@ -1114,7 +1119,7 @@ class DecoderModel:
         r = None
         saved: list[Any] = []
         keep_from = self._first_kept_layer(batch.num_tokens) if save else 0
-        for i in range(cfg.num_hidden_layers):
+        for i in range(lo, hi):
             if save and i < keep_from:  # only the layer input is kept; the layer runs again in the backward pass
                 saved.append(self.offloader.offload(i, (a, r)) if self.offloader is not None else (a, r))
                 a, r = self._layer_fwd(i, a, r, batch, None)
@@ -1125,14 +1130,15 @@ class DecoderModel:
                     saved.append(S)
         if self.pre_layer_hook is not None:
             self.pre_layer_hook(cfg.num_hidden_layers, "forward")
-        if not cfg.has_head:
+        span = (lo, hi, use_embed)
+        if not (cfg.has_head and c_last):
             # stage boundary: the next stage continues from the summed stream (its first norm sees residual None)
             out = a if r is None else a + r
-            return out, (dict(batch=batch, layers=saved, boundary=True) if save else None)
+            return out, (dict(batch=batch, layers=saved, boundary=True, span=span) if save else None)
         hN, xN, rstdN = F.rms_norm(a, self.params["norm.weight"], cfg.rms_norm_eps, residual=r)
         if self.tsp is not None:
             hN = self.tsp.gather(hN, batch.num_tokens)  # the heads see every token
-        state = dict(batch=batch, layers=saved, xN=xN, rstdN=rstdN, hN=hN) if save else None
+        state = dict(batch=batch, layers=saved, xN=xN, rstdN=rstdN, hN=hN, span=span) if save else None
         return hN, state
 
     def _trunk_bwd(self, state: dict, g_hN: torch.Tensor) -> Optional[torch.Tensor]:
@@ -1150,10 +1156,11 @@ class DecoderModel:
         if self.post_layer_backward_hook is not None:
             self.post_layer_backward_hook(cfg.num_hidden_layers)
         g_d = g_x2 = g
-        for i in reversed(range(cfg.num_hidden_layers)):
-            S = state["layers"][i]
+        lo, hi, use_embed = state.get("span") or (0, cfg.num_hidden_layers, cfg.has_embedding)
+        for i in reversed(range(lo, hi)):
+            S = state["layers"][i - lo]
             if self.offloader is not None and not isinstance(S, (tuple, dict)):
-                nxt = state["layers"][i - 1] if i > 0 else None
+                nxt = state["layers"][i - lo - 1] if i > lo else None
                 if nxt is not None and not isinstance(nxt, (tuple, dict)):
                     self.offloader.prefetch(nxt)  # the previous layer's input travels back while this layer computes
                 S = self.offloader.wait(S)
@@ -1162,9 +1169,9 @@ class DecoderModel:
                 S = {}
                 self._layer_fwd(i, a, r, batch, S)
             g = self._layer_bwd(i, g_d, g_x2, batch, S)
-            state["layers"][i] = None
+            state["layers"][i - lo] = None
             g_d = g_x2 = g
-        if not cfg.has_embedding:
+        if not use_embed:
             if self.post_layer_backward_hook is not None:
                 self.post_layer_backward_hook(-1)
             return g
@@ -1231,8 +1238,8 @@ class DecoderModel:
     # ------------------------------------------------------------------------------------ pipeline stages
     @torch.no_grad()
     def forward_stage(self, batch: PackedBatch, stage_input: Optional[torch.Tensor] = None, save: bool = True):
-        """A stage without head: returns (boundary stream [T, H], state for ``backward_stage``)."""
-        assert not self.cfg.has_head
+        """A stage (or model chunk) without head: returns (boundary stream [T, H], state for ``backward_stage``)."""
+        assert not self.cfg.has_head or (self.chunk is not None and not self.chunk[3])
         return self._trunk_fwd(batch, save=save, stage_input=stage_input)
 
     @torch.no_grad()

@@ -36,7 +36,7 @@ __all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to
 class ModelParallelTopology:
     """Process groups of a TP x PP x DP job. Every rank of the job must construct it (group creation is collective)."""
 
-    def __init__(self, tp: int = 1, pp: int = 1, ranks: Optional[list[int]] = None, ep: int = 1):
+    def __init__(self, tp: int = 1, pp: int = 1, ranks: Optional[list[int]] = None, ep: int = 1, vpp: int = 1):
         self.world_ranks = list(ranks) if ranks is not None else list(range(dist.get_world_size() if dist.is_initialized() else 1))
         n = len(self.world_ranks)
         assert n % (tp * pp) == 0, f"world size {n} is not a multiple of tp*pp = {tp * pp}"
@@ -44,6 +44,10 @@ class ModelParallelTopology:
         # expert parallelism borrows the data-parallel dimension: the ranks of a data-parallel group split the experts
         assert ep == 1 or (ep == self.dp and tp == 1), "expert parallelism: ep must equal the data-parallel size, with tp = 1"
         self.ep = ep
+        # interleaved (virtual) pipeline stages: every rank holds ``vpp`` model chunks; chunk v of stage s is block
+        # v * pp + s of the layer stack, so a micro-batch visits the ranks of the pipeline group vpp times round
+        assert vpp >= 1 and (vpp == 1 or pp > 1), "virtual pipeline stages need pipeline_model_parallel_size > 1"
+        self.vpp = int(vpp)
         me = dist.get_rank() if dist.is_initialized() else 0
         self.index = self.world_ranks.index(me)
         self.tp_rank = self.index % tp
@@ -78,6 +82,8 @@ class ModelParallelTopology:
         self.prev_rank = g(self.dp_rank, self.pp_rank - 1, self.tp_rank) if self.pp_rank > 0 else None
         self.next_rank = g(self.dp_rank, self.pp_rank + 1, self.tp_rank) if self.pp_rank < pp - 1 else None
         self.last_stage_rank = g(self.dp_rank, pp - 1, self.tp_rank)
+        self.ring_prev = g(self.dp_rank, (self.pp_rank - 1) % pp, self.tp_rank)   # neighbours on the ring the chunks travel
+        self.ring_next = g(self.dp_rank, (self.pp_rank + 1) % pp, self.tp_rank)
         self.ep_rank = self.dp_rank if ep > 1 else 0
         self.ep_group = self.dp_group if ep > 1 else None
 
@@ -95,8 +101,18 @@ class ModelParallelTopology:
         lo = self.pp_rank * base + min(self.pp_rank, rem)
         return lo, lo + base + (1 if self.pp_rank < rem else 0)
 
+    def local_layers(self, num_layers: int) -> list[int]:
+        """Index in the full model of every local layer, in local order (chunk by chunk with virtual stages)."""
+        if self.vpp == 1:
+            lo, hi = self.layer_range(num_layers)
+            return list(range(lo, hi))
+        assert num_layers % (self.pp * self.vpp) == 0, \
+            f"{num_layers} layers do not split into {self.pp} x {self.vpp} equal blocks (pipeline x virtual stages)"
+        blk = num_layers // (self.pp * self.vpp)
+        return [(v * self.pp + self.pp_rank) * blk + j for v in range(self.vpp) for j in range(blk)]
+
     def local_config(self, cfg: ModelConfig, vocab_parallel: bool = True) -> ModelConfig:
-        lo, hi = self.layer_range(cfg.num_hidden_layers)
+        lo, hi = 0, len(self.local_layers(cfg.num_hidden_layers))
         return cfg.local_shard(tp=self.tp, num_layers=hi - lo, has_embedding=self.is_first_stage, has_head=self.is_last_stage,
                                ep=self.ep, vocab_parallel=vocab_parallel)
 
@@ -116,7 +132,7 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
     """One entry per tensor of the local shard model, in the local parameter order."""
     from ..models.weights import build_param_specs
 
-    lo, _ = topo.layer_range(full_cfg.num_hidden_layers)
+    layer_of = topo.local_layers(full_cfg.num_hidden_layers)
     local_cfg = topo.local_config(full_cfg, vocab_parallel and not value_head)
     out = []
     for spec in build_param_specs(local_cfg, value_head and topo.is_last_stage):
@@ -124,7 +140,7 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
         full_name = name
         if name.startswith("layers."):
             i, rest = name.split(".", 2)[1:]
-            full_name = f"layers.{int(i) + lo}.{rest}"
+            full_name = f"layers.{layer_of[int(i)]}.{rest}"
         else:
             rest = name
         if name == "lm_head.weight" and local_cfg.head_vocab_size:

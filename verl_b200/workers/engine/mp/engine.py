@@ -36,11 +36,11 @@ __all__ = ["ModelParallelEngine", "ModelParallelEngineWithLMHead", "ModelParalle
 _TOPOLOGIES: dict = {}
 
 
-def get_topology(tp: int, pp: int, ep: int = 1) -> ModelParallelTopology:
+def get_topology(tp: int, pp: int, ep: int = 1, vpp: int = 1) -> ModelParallelTopology:
     """One topology (set of process groups) per (tp, pp, ep) and process: actor, critic and reference engines share it."""
-    key = (tp, pp, ep)
+    key = (tp, pp, ep, vpp)
     if key not in _TOPOLOGIES:
-        _TOPOLOGIES[key] = ModelParallelTopology(tp, pp, ep=ep)
+        _TOPOLOGIES[key] = ModelParallelTopology(tp, pp, ep=ep, vpp=vpp)
     return _TOPOLOGIES[key]
 
 
@@ -51,6 +51,7 @@ class ModelParallelEngine(NativeEngine):
         self.tp_size = g("tensor_model_parallel_size", 1)
         self.pp_size = g("pipeline_model_parallel_size", 1)
         self.ep_size = g("expert_model_parallel_size", 1) if self.arch.is_moe else 1
+        self.vpp_size = g("virtual_pipeline_model_parallel_size", 1)
         self.full_arch = self.arch
         if g("context_parallel_size", 1) > 1 and self.pp_size > 1:
             raise NotImplementedError("context parallelism is combined with tensor and data parallelism; pipeline stages "
@@ -64,7 +65,7 @@ class ModelParallelEngine(NativeEngine):
     def initialize(self) -> None:
         if self._initialized:
             return
-        self.topo = get_topology(self.tp_size, self.pp_size, self.ep_size)
+        self.topo = get_topology(self.tp_size, self.pp_size, self.ep_size, self.vpp_size)
         if self.full_arch.is_moe and self.tp_size > 1:
             # experts under tensor parallelism: every expert's intermediate width is cut over the tensor-parallel ranks
             # (expert tensor parallelism, the reference's default ``expert_tensor_parallel_size = tensor_model_parallel_size``)
@@ -218,6 +219,8 @@ class ModelParallelEngine(NativeEngine):
         topo = self.topo
         if topo.pp == 1:
             return super()._run_micro_batches(mbs, R, temperature, calc_entropy, loss_function, forward_only)
+        if topo.vpp > 1:
+            return self._run_interleaved(mbs, R, temperature, calc_entropy, loss_function, forward_only)
         need_grad = not forward_only and loss_function is not None
         first, last = topo.is_first_stage, topo.is_last_stage
         packed = [pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R) for mb in mbs]
@@ -305,6 +308,110 @@ class ModelParallelEngine(NativeEngine):
             for k, v in out.items():
                 outs.setdefault(k, []).append(v.detach())
         # the loss and its metrics live on the last stage: share them inside the pipeline group
+        losses, metrics = self._broadcast_loss(losses, metrics, M, loss_function is not None)
+        return outs, rows, losses, metrics
+
+    def _run_interleaved(self, mbs: list[dict], R: int, temperature: float, calc_entropy: bool, loss_function, forward_only: bool):
+        """Interleaved (virtual) pipeline stages: every rank holds V model chunks and a micro-batch travels V times round
+        the ring of P ranks. The schedule is breadth-first and in lockstep: with W = max(M, P), rank s runs chunk v of
+        micro-batch i at step v * W + i + s (the backward pass mirrors it), so the start-up bubble is P - 1 steps of a
+        1 / V model chunk instead of a whole stage. After every step a rank sends what it produced to the next rank of
+        the ring and receives what the previous rank produced, both in ONE batched point-to-point call whose partner calls
+        are the neighbours' calls of the same step: no rank ever waits on a call of another step, whatever M, P and V are.
+        A value that arrives before its consumer's step waits in a buffer. All chunk states are kept until their backward."""
+        topo = self.topo
+        P, V, s_rank, M = topo.pp, topo.vpp, topo.pp_rank, len(mbs)
+        need_grad = not forward_only and loss_function is not None
+        packed = [pack_padded_batch(mb["input_ids"], mb["attention_mask"], mb.get("position_ids"), R) for mb in mbs]
+        assert self.model.tsp is None, "virtual pipeline stages are not combined with sequence parallelism"
+        Ts = [p[0].num_tokens for p in packed]
+        rows: list[int] = [r for mb in mbs for r in mb["_rows"]]
+        blk = self.arch.num_hidden_layers // V
+        W = max(M, P)
+        losses, metrics = [], {}
+        head_out: list = [None] * M
+        states: dict = {}
+
+        def item_at(rank: int, t: int, backward: bool):
+            """(v, i) that ``rank`` works on at step ``t``, or None."""
+            k = t - (P - 1 - rank if backward else rank)
+            if k < 0:
+                return None
+            v, i = divmod(k, W)
+            if v >= V or i >= M:
+                return None
+            return (V - 1 - v if backward else v), i
+
+        def is_entry(rank, v):
+            return rank == 0 and v == 0
+
+        def is_exit(rank, v):
+            return rank == P - 1 and v == V - 1
+
+        steps = (V - 1) * W + M + P - 1
+        inbox: dict = {}
+        prev_r, next_r = (s_rank - 1) % P, (s_rank + 1) % P
+        # ---- forward
+        for t in range(steps):
+            mine = item_at(s_rank, t, False)
+            send = None
+            if mine is not None:
+                v, i = mine
+                self.model.chunk = (v * blk, (v + 1) * blk, v == 0, v == V - 1)
+                batch, labels, resp_index, resp_valid = packed[i]
+                x_in = None if is_entry(s_rank, v) else inbox.pop((v, i))
+                if is_exit(s_rank, v):
+                    out = self._head_outputs(batch, labels, resp_index, resp_valid, temperature, calc_entropy, need_grad, x_in)
+                    st = getattr(self.model, "last_state", None) if need_grad else None
+                    loss = None
+                    if loss_function is not None:
+                        loss, m = loss_function(model_output=out, data=mbs[i], dp_group=None)
+                        losses.append(loss.detach())
+                        for k_, v_ in m.items():
+                            metrics.setdefault(k_, []).append(v_)
+                    states[(v, i)] = (st, loss)
+                    head_out[i] = {k_: v_.detach() for k_, v_ in out.items()}
+                else:
+                    send, st = self.model.forward_stage(batch, x_in, save=need_grad)
+                    states[(v, i)] = (st, None)
+            # what the previous rank of the ring produced in this step is the input of one of my later items
+            theirs = item_at(prev_r, t, False)
+            recv_key = None
+            if theirs is not None and not is_exit(prev_r, theirs[0]):
+                recv_key = (theirs[0] + 1, theirs[1]) if prev_r == P - 1 else theirs
+            got = self._exchange(send, topo.ring_next if send is not None else None,
+                                 Ts[recv_key[1]] if recv_key is not None else None, topo.ring_prev if recv_key is not None else None)
+            if recv_key is not None:
+                inbox[recv_key] = got
+        # ---- backward
+        if need_grad:
+            for t in range(steps):
+                mine = item_at(s_rank, t, True)
+                send = None
+                if mine is not None:
+                    v, i = mine
+                    st, loss = states.pop((v, i))
+                    if is_exit(s_rank, v):
+                        loss.backward()
+                        g_in = st.get("g_input")
+                    else:
+                        g_in = self.model.backward_stage(st, inbox.pop(("g", v, i)))
+                    send = None if is_entry(s_rank, v) else g_in
+                theirs = item_at(next_r, t, True)
+                recv_key = None
+                if theirs is not None and not is_entry(next_r, theirs[0]):
+                    recv_key = ("g", theirs[0] - 1, theirs[1]) if next_r == 0 else ("g", theirs[0], theirs[1])
+                got = self._exchange(send, topo.ring_prev if send is not None else None,
+                                     Ts[recv_key[2]] if recv_key is not None else None, topo.ring_next if recv_key is not None else None)
+                if recv_key is not None:
+                    inbox[recv_key] = got
+        states.clear()
+        self.model.chunk = None
+        outs: dict[str, list] = {}
+        for i in range(M):
+            out = self._broadcast_outputs(head_out[i], packed[i][3].shape, calc_entropy or need_grad)
+            for k_, v_ in out.items():
+                outs.setdefault(k_, []).append(v_.detach())
         losses, metrics = self._broadcast_loss(losses, metrics, M, loss_function is not None)
         return outs, rows, losses, metrics
 
