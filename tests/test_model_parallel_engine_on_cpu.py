@@ -39,7 +39,7 @@ def _proc(rank, world, port, tp, pp, q, ep=1, preset="tiny-llama", mbs=2, schedu
 
         initialize_global_process_group()
         ec = McoreEngineConfig(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp, expert_model_parallel_size=ep, seed=7,
-                               micro_batch_size_per_gpu=mbs if ep == 1 else (1 + rank))  # ep: unequal micro-batch counts get evened out
+                               micro_batch_size_per_gpu=mbs if ep == 1 else (1 + rank // (tp * pp)))  # ep: unequal micro-batch counts get evened out
         object.__setattr__(ec, "pipeline_schedule", schedule)
         object.__setattr__(ec, "sequence_parallel", sp)
         if vpp > 1:
@@ -183,6 +183,22 @@ def test_expert_tensor_parallel_matches_unsharded(world, tp, pp, preset):
         assert got.shape == ref_flat.shape
         assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
         assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r // (tp * pp)], atol=1e-4), r
+
+
+def test_expert_parallel_with_expert_tensor_parallel_matches_unsharded():
+    """Four ranks: two data-parallel replicas that split the experts between them, each replica two tensor-parallel ranks
+    that split every expert's width (and the attention heads). Tokens travel to the owner of their expert inside each
+    tensor-parallel rank's own expert-parallel group; the re-assembled full model, the gradient norm and the log-probs
+    equal one process."""
+    ref_norm, ref_lp, ref_flat = _reference("tiny-moe")
+    res = _run(4, 2, 1, ep=2, preset="tiny-moe")
+    rows = ref_lp.chunk(2)
+    for r in range(4):
+        assert abs(res[r]["grad_norm"] - ref_norm) < 2e-4 * max(1.0, ref_norm), (r, res[r]["grad_norm"], ref_norm)
+        got = torch.from_numpy(res[r]["full"])
+        assert got.shape == ref_flat.shape
+        assert torch.allclose(got, ref_flat.float(), atol=3e-4), (r, (got - ref_flat.float()).abs().max())
+        assert torch.allclose(torch.from_numpy(res[r]["log_probs"]), rows[r // 2], atol=1e-4), r
 
 
 def test_expert_parallel_engine_matches_unsharded():

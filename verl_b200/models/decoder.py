@@ -898,7 +898,7 @@ class DecoderModel:
         k = cfg.num_experts_per_tok
         T, H = h2.shape
         g_dp = g_d[tok]
-        g_wp = (g_dp.float() * M["y"].float()).sum(-1)
+        g_wp = self._etp_sum((g_dp.float() * M["y"].float()).sum(-1))
         g_y_recv = ep.exchange_rows((g_dp * wp.unsqueeze(-1)).contiguous(), M["in_splits"], M["out_splits"])
         g_x_sorted = self._experts_apply_bwd(W, g_y_recv[perm].contiguous(), M["x"], M["gu"], M["counts"])
         g_x_recv = torch.empty_like(g_x_sorted)
@@ -906,6 +906,7 @@ class DecoderModel:
         g_x_send = ep.exchange_rows(g_x_recv, M["out_splits"], M["in_splits"])
         g_h2 = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
         g_h2.index_add_(0, tok, g_x_send.float())
+        g_h2 = self._etp_sum(g_h2)  # the experts' part is a partial sum when their width is cut over the tensor-parallel group
         g_w = torch.empty(T * k, dtype=torch.float32, device=h2.device)
         g_w[order] = g_wp
         with torch.enable_grad():

@@ -30,7 +30,7 @@ import torch.distributed as dist
 from ..models.config import ModelConfig
 from ..models.weights import FlatParams
 
-__all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to_local", "copy_local_to_full", "cat_dim"]
+__all__ = ["ModelParallelTopology", "ShardMap", "build_shard_map", "copy_full_to_local", "copy_local_to_full", "cat_dim", "EXPERT_KINDS"]
 
 
 class ModelParallelTopology:
@@ -42,7 +42,8 @@ class ModelParallelTopology:
         assert n % (tp * pp) == 0, f"world size {n} is not a multiple of tp*pp = {tp * pp}"
         self.tp, self.pp, self.dp = tp, pp, n // (tp * pp)
         # expert parallelism borrows the data-parallel dimension: the ranks of a data-parallel group split the experts
-        assert ep == 1 or (ep == self.dp and tp == 1), "expert parallelism: ep must equal the data-parallel size, with tp = 1"
+        # (with tp > 1 as well, every expert's width is additionally cut over the tensor-parallel group)
+        assert ep == 1 or ep == self.dp, "expert parallelism: ep must equal the data-parallel size"
         self.ep = ep
         # interleaved (virtual) pipeline stages: every rank holds ``vpp`` model chunks; chunk v of stage s is block
         # v * pp + s of the layer stack, so a micro-batch visits the ranks of the pipeline group vpp times round
@@ -145,7 +146,7 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
             rest = name
         if name == "lm_head.weight" and local_cfg.head_vocab_size:
             out.append(ShardMap(name, full_name, "rows", (full_cfg.vocab_size,)))
-        elif rest.startswith("mlp.experts.") and topo.ep > 1:
+        elif rest.startswith("mlp.experts.") and topo.ep > 1 and topo.tp == 1:
             out.append(ShardMap(name, full_name, "experts"))
         elif rest == "mlp.experts.gate_up_proj" and topo.tp > 1:
             out.append(ShardMap(name, full_name, "expert_rows", (full_cfg.moe_intermediate_size, full_cfg.moe_intermediate_size)))
@@ -168,9 +169,11 @@ def build_shard_map(full_cfg: ModelConfig, topo: ModelParallelTopology, value_he
 
 def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int, ep: int = 1, ep_rank: int = 0) -> list[torch.Tensor]:
     """Views of the full tensor that, concatenated along the sharded dimension, form the local tensor."""
-    if m.kind == "experts":
+    if m.kind in EXPERT_KINDS and ep > 1:     # dim 0 (experts) is cut over the expert-parallel group first
         n = full.shape[0] // ep
-        return [full[ep_rank * n : (ep_rank + 1) * n]]
+        full = full[ep_rank * n : (ep_rank + 1) * n]
+    if m.kind == "experts":
+        return [full]
     if m.kind == "rep" or tp == 1:
         return [full]
     if m.kind == "cols":
@@ -186,6 +189,9 @@ def _slices(m: ShardMap, full: torch.Tensor, tp: int, tp_rank: int, ep: int = 1,
         parts.append(full[:, lo : lo + w] if m.kind == "expert_rows" else full[lo : lo + w])
         off += b
     return parts
+
+
+EXPERT_KINDS = ("experts", "expert_rows", "expert_cols")
 
 
 def cat_dim(kind: str) -> int:

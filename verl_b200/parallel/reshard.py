@@ -20,7 +20,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.weights import FlatParams
-from .model_parallel import _slices
+from .model_parallel import EXPERT_KINDS, _slices
 from .symmetric import PeerBarrier, SymmetricBuffer, symmetric_available
 
 __all__ = ["PeerReshard"]
@@ -68,7 +68,7 @@ class PeerReshard:
             # one writer per tensor that several ranks hold identically
             if m.kind == "rep" and topo.tp > 1 and topo.tp_rank != 0:
                 continue
-            if m.kind != "experts" and topo.ep > 1 and topo.ep_rank != 0:
+            if m.kind not in EXPERT_KINDS and topo.ep > 1 and topo.ep_rank != 0:
                 continue
             src = eng.params.views[m.local_name]
             assert src.is_contiguous()

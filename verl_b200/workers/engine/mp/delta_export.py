@@ -41,9 +41,10 @@ def full_positions(m: ShardMap, idx: torch.Tensor, local_shape: tuple, full_shap
     if m.kind == "cols":
         lc, fc = local_shape[1], full_shape[1]
         return (idx // lc) * fc + idx % lc + tp_rank * lc
+    e_off = ep_rank * local_shape[0] if (ep > 1 and m.kind in ("expert_rows", "expert_cols")) else 0   # first expert held here
     if m.kind == "expert_cols":              # [E, rows, cols / tp]: the last dimension is cut
         lc, fc = local_shape[2], full_shape[2]
-        return (idx // lc) * fc + idx % lc + tp_rank * lc
+        return (idx // lc) * fc + idx % lc + tp_rank * lc + e_off * full_shape[1] * fc
     if m.kind == "expert_rows":              # [E, rows / tp (block-wise), cols]: per expert like ``rows``
         cols = local_shape[2]
         e, rem = idx // (local_shape[1] * cols), idx % (local_shape[1] * cols)
@@ -56,7 +57,7 @@ def full_positions(m: ShardMap, idx: torch.Tensor, local_shape: tuple, full_shap
             full_row[sel] = row[sel] - l0 + f0 + tp_rank * w
             l0 += w
             f0 += b
-        return (e * full_shape[1] + full_row) * cols + c
+        return ((e + e_off) * full_shape[1] + full_row) * cols + c
     inner = 1
     for d in local_shape[1:]:
         inner *= d
@@ -106,7 +107,7 @@ class ShardDeltaExporter:
                 continue
             if m.kind == "rep" and self.tp > 1 and self.tp_rank != 0:
                 continue                      # every tensor-parallel rank holds the same values: one exporter is enough
-            if m.kind != "experts" and self.ep > 1 and self.ep_rank != 0:
+            if m.kind not in ("experts", "expert_rows", "expert_cols") and self.ep > 1 and self.ep_rank != 0:
                 continue                      # everything but the experts is replicated over the expert-parallel group
             lo = P.offsets[m.local_name]
             view = P.views[m.local_name]

@@ -73,9 +73,7 @@ class ModelParallelEngine(NativeEngine):
             if etp is not None and int(etp) != self.tp_size:
                 raise NotImplementedError(f"expert_tensor_parallel_size={etp}: experts are cut over the whole tensor-parallel group "
                                           f"({self.tp_size}); leave it unset or set it to the tensor-parallel size")
-            if self.ep_size > 1:
-                raise NotImplementedError("expert parallelism shards whole experts over the data-parallel ranks and needs tp = 1; "
-                                          "with tp > 1 the experts are tensor-parallel instead")
+            # (with expert_model_parallel_size > 1 as well: whole experts over the data-parallel ranks, their width over tp)
         if self.full_arch.tie_word_embeddings and self.pp_size > 1:
             raise NotImplementedError("pipeline parallelism with tied input/output embeddings needs the embedding shared between "
                                       "the first and the last stage; use pipeline_model_parallel_size=1 for this model")
@@ -504,10 +502,13 @@ class ModelParallelEngine(NativeEngine):
                         full.views[m.full_name].zero_()
             dist.all_reduce(full.flat, group=topo.mp_group)
         if topo.ep > 1:
+            from ....parallel.model_parallel import EXPERT_KINDS
+
             for m in self.maps:
-                if m.kind == "experts":
+                if m.kind in EXPERT_KINDS:
                     dst = full.views[m.full_name]
-                    src = self.params.views[m.local_name].to(work).contiguous()
+                    n = dst.shape[0] // topo.ep     # this replica's experts, already whole (summed over its tensor-parallel ranks)
+                    src = dst[topo.ep_rank * n : (topo.ep_rank + 1) * n].clone()
                     if self.device.type == "cuda":
                         dist.all_gather_into_tensor(dst, src, group=topo.ep_group)
                     else:

@@ -38,7 +38,7 @@ _ROLLOUT_REGISTRY: dict[tuple[str, str], str] = {
     ("native", "async"): "verl_b200.workers.rollout.native.adapter.NativeRollout",
     ("native", "sync"): "verl_b200.workers.rollout.native.adapter.NativeRollout",
     ("hf", "sync"): "verl_b200.workers.rollout.hf_rollout.HFRollout",
-    ("naive", "sync"): "verl_b200.workers.rollout.naive_rollout.NaiveRollout",
+    ("naive", "sync"): "verl_b200.workers.rollout.naive.naive_rollout.NaiveRollout",
     # optional library back-end (import-gated); the native engine is the default and the measured path
     ("vllm", "async"): "verl_b200.workers.rollout.vllm_rollout.vllm_rollout.VLLMRollout",
     ("vllm", "sync"): "verl_b200.workers.rollout.vllm_rollout.vllm_rollout.VLLMRollout",
