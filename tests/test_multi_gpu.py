@@ -243,7 +243,8 @@ def _sec_expert_parallel_training(rank, world, dev, ops, res):
     from verl_b200.workers.engine.native.engine import NativeEngineWithLMHead
     from verl_b200.workers.utils.losses import sft_loss
 
-    # ---- expert-parallel training engine (experts split over the two ranks, NCCL token exchange) vs replicated experts
+    # ---- expert-parallel training engine (experts split over the two ranks, token copies stored into the owner's buffer by
+    # one peer-memory copy kernel per exchange) vs replicated experts
     from verl_b200.workers.config import McoreEngineConfig
     from verl_b200.workers.engine.base import EngineRegistry
 
@@ -263,6 +264,8 @@ def _sec_expert_parallel_training(rank, world, dev, ops, res):
         out = eng.train_batch(dict(data), partial(sft_loss, None))
         full = eng.gather_full_params().flat.float() if name == "ep" else eng.params.flat.float().clone()
         ep_res[name] = (float(out["metrics"]["grad_norm"]), full)
+        if name == "ep":
+            res["ep_over_peer_memory"] = bool(getattr(eng.model.ep, "_peer", None))
     res["ep_train_norms"] = (ep_res["rep"][0], ep_res["ep"][0])
     res["ep_train_param_diff"] = (ep_res["rep"][1] - ep_res["ep"][1]).abs().max().item()
     os.environ["VERL_B200_FUSED_COMM"] = "1"
@@ -736,6 +739,7 @@ def test_expert_parallel_training_matches_replicated_experts(pair):
     for res in pair.run("expert_parallel_training").values():
         n_rep, n_ep = res["ep_train_norms"]
         assert abs(n_rep - n_ep) < 1e-2 * max(1.0, n_rep) and res["ep_train_param_diff"] < 5e-3, res  # one AdamW step of lr 1e-3
+        assert res["ep_over_peer_memory"], res
 
 
 def test_peer_barrier_that_nobody_joins_reports_status(pair):

@@ -335,6 +335,37 @@ class ExpertParallelGroup:
 
     def __init__(self, group, rank: int, size: int):
         self.group, self.rank, self.size = group, int(rank), int(size)
+        self._peer = None  # PeerAllToAll, created at the first exchange on GPUs with peer-mapped memory
+
+    def _peer_exchange(self, x: torch.Tensor):
+        """The peer-memory row exchange for this group, or None (CPU, no peer-mapped memory, VERL_B200_PEER_EP=0): the
+        collective formulation is used then. Every rank of the group takes the same branch."""
+        if self._peer is None:
+            import os
+
+            self._peer = False
+            if x.is_cuda and self.size > 1 and os.environ.get("VERL_B200_PEER_EP", "1") != "0":
+                from ..parallel.symmetric import PeerAllToAll, symmetric_available
+
+                if symmetric_available():
+                    try:
+                        self._peer = PeerAllToAll(x.device, self.group)
+                    except Exception:
+                        self._peer = False
+        return self._peer or None
+
+    def gather_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """``counts`` [size, E_local] (copies this rank sends to each (owner, local expert)) of every rank:
+        [source rank, owner, E_local], the same tensor on all ranks."""
+        import torch.distributed as dist
+
+        send = counts.contiguous()
+        out = torch.empty(self.size, *send.shape, dtype=send.dtype, device=send.device)
+        if send.is_cuda:
+            dist.all_gather_into_tensor(out, send, group=self.group)
+        else:
+            dist.all_gather(list(out.unbind(0)), send, group=self.group)
+        return out
 
     def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
         """``counts`` [size, E_local]: copies this rank sends to each (owner, local expert). Returns the same matrix seen
@@ -346,10 +377,16 @@ class ExpertParallelGroup:
         dist.all_to_all_single(recv, send, group=self.group)
         return recv
 
-    def exchange_rows(self, x: torch.Tensor, in_splits: list, out_splits: list) -> torch.Tensor:
-        """Rows of ``x`` go to the ranks in blocks of ``in_splits``; returns the ``sum(out_splits)`` rows received."""
+    def exchange_rows(self, x: torch.Tensor, in_splits: list, out_splits: list, rows: Optional[list] = None) -> torch.Tensor:
+        """Rows of ``x`` go to the ranks in blocks of ``in_splits``; returns the ``sum(out_splits)`` rows received.
+        ``rows[s][d]`` (rows rank s sends to rank d in THIS exchange, known to all ranks) enables the peer-memory path: one
+        copy kernel stores every block into its place of the receiver's buffer, no collective."""
         import torch.distributed as dist
 
+        if rows is not None and x.dim() == 2 and (x.shape[1] * x.element_size()) % 16 == 0:
+            peer = self._peer_exchange(x)
+            if peer is not None:
+                return peer.exchange_rows(x.contiguous(), rows)
         out = torch.empty(sum(out_splits), *x.shape[1:], dtype=x.dtype, device=x.device)
         dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=self.group)
         return out
@@ -869,10 +906,14 @@ class DecoderModel:
         order = torch.argsort(flat_e, stable=True)          # copies sorted by global expert = by (owner, local expert)
         tok = torch.div(order, k, rounding_mode="floor")
         send_counts = counts.long().view(ep.size, El)
-        recv_counts = ep.exchange_counts(send_counts)       # [source rank, local expert]
-        both = torch.stack([send_counts, recv_counts]).cpu()  # the one host read of the layer: split sizes of the exchange
+        all_counts = ep.gather_counts(send_counts)          # [source rank, owner, local expert], the same on every rank
+        recv_counts = all_counts[:, ep.rank]                 # [source rank, local expert]
+        host = all_counts.cpu()                              # the one host read of the layer: every split size of the exchange
+        both = torch.stack([host[ep.rank], host[:, ep.rank]])
         in_splits, out_splits = both[0].sum(1).tolist(), both[1].sum(1).tolist()
-        x_recv = ep.exchange_rows(h2[tok], in_splits, out_splits)
+        rows_fwd = host.sum(-1).tolist()                     # rows_fwd[s][d]: token copies rank s sends to rank d
+        rows_back = [list(r) for r in zip(*rows_fwd)]        # the way back: what d received from s returns to s
+        x_recv = ep.exchange_rows(h2[tok], in_splits, out_splits, rows_fwd)
         # received rows are grouped by source rank, then local expert: regroup by local expert
         eid = torch.repeat_interleave(torch.arange(El, device=h2.device).repeat(ep.size), recv_counts.reshape(-1).to(h2.device))
         perm = torch.argsort(eid, stable=True)
@@ -882,13 +923,14 @@ class DecoderModel:
         y_sorted = self._experts_apply(W, x_sorted, local_counts, St)
         y_recv = torch.empty_like(y_sorted)
         y_recv[perm] = y_sorted
-        y_send = ep.exchange_rows(y_recv, out_splits, in_splits)  # back to the ranks of the tokens, in `order`
+        y_send = ep.exchange_rows(y_recv, out_splits, in_splits, rows_back)  # back to the ranks of the tokens, in `order`
         wp = w.reshape(-1)[order].to(h2.dtype)
         out = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
         out.index_add_(0, tok, (y_send * wp.unsqueeze(-1)).float())
         if S is not None:
             S.update(moe=dict(ep=True, logits=logits, idx=idx, order=order, tok=tok, wp=wp, y=y_send, perm=perm, x=x_sorted,
-                              gu=St["gu"], counts=local_counts, in_splits=in_splits, out_splits=out_splits))
+                              gu=St["gu"], counts=local_counts, in_splits=in_splits, out_splits=out_splits, rows_fwd=rows_fwd,
+                              rows_back=rows_back))
         return out.to(h2.dtype)
 
     def _moe_bwd_ep(self, W, g_d, h2, S: dict):
@@ -899,11 +941,11 @@ class DecoderModel:
         T, H = h2.shape
         g_dp = g_d[tok]
         g_wp = self._etp_sum((g_dp.float() * M["y"].float()).sum(-1))
-        g_y_recv = ep.exchange_rows((g_dp * wp.unsqueeze(-1)).contiguous(), M["in_splits"], M["out_splits"])
+        g_y_recv = ep.exchange_rows((g_dp * wp.unsqueeze(-1)).contiguous(), M["in_splits"], M["out_splits"], M.get("rows_fwd"))
         g_x_sorted = self._experts_apply_bwd(W, g_y_recv[perm].contiguous(), M["x"], M["gu"], M["counts"])
         g_x_recv = torch.empty_like(g_x_sorted)
         g_x_recv[perm] = g_x_sorted
-        g_x_send = ep.exchange_rows(g_x_recv, M["out_splits"], M["in_splits"])
+        g_x_send = ep.exchange_rows(g_x_recv, M["out_splits"], M["in_splits"], M.get("rows_back"))
         g_h2 = torch.zeros(T, H, dtype=torch.float32, device=h2.device)
         g_h2.index_add_(0, tok, g_x_send.float())
         g_h2 = self._etp_sum(g_h2)  # the experts' part is a partial sum when their width is cut over the tensor-parallel group

@@ -168,13 +168,34 @@ class PeerAllToAll:
             starts.append(n)
         for dst, src, rows, rb, ds, ss in jobs:
             assert dst % 16 == 0 and src % 16 == 0 and rb % 16 == 0 and ds % 16 == 0 and ss % 16 == 0, "16-byte units"
-        j = torch.tensor(jobs, dtype=torch.int64).view(-1, 6).to(self.device)
-        b = torch.tensor(starts, dtype=torch.int32).to(self.device)
         self.barrier(limit_s=self.limit_s)
         if n:
+            j = torch.tensor(jobs, dtype=torch.int64).view(-1, 6).to(self.device)
+            b = torch.tensor(starts, dtype=torch.int32).to(self.device)
             native.ops().scatter_copy_(j, b, n)
         self.barrier(limit_s=self.limit_s)
         return self.buf.tensor[:out_bytes]
+
+    def exchange_rows(self, x: torch.Tensor, rows: list) -> torch.Tensor:
+        """Variable-size row exchange (token dispatch of expert parallelism): ``rows[s][d]`` = rows that rank s sends to
+        rank d, known to every rank. ``x`` holds this rank's rows for rank 0, then for rank 1, ...; returns the rows this
+        rank receives, ordered by source rank. Every block is stored straight into its final place of the receiver's
+        buffer (offset = the rows that lower-ranked sources send to the same receiver)."""
+        W, me = self.world, self.rank
+        assert x.dim() == 2 and x.is_contiguous()
+        row_bytes = x.shape[1] * x.element_size()
+        total_in = sum(rows[s][me] for s in range(W))
+        most = max(sum(rows[s][d] for s in range(W)) for d in range(W))   # the same on every rank: they re-allocate together
+        self._ensure(max(1, most) * row_bytes)
+        jobs, src_row = [], 0
+        for d in range(W):
+            n = rows[me][d]
+            if n:
+                dst_row = sum(rows[s][d] for s in range(me))
+                jobs.append((int(self.buf.ptrs[d]) + dst_row * row_bytes, x.data_ptr() + src_row * row_bytes, 1, n * row_bytes,
+                             n * row_bytes, n * row_bytes))
+            src_row += n
+        return self._run(jobs, total_in * row_bytes).view(x.dtype).view(total_in, x.shape[1]).clone()
 
     def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
         """[T/size, heads, hd] (my tokens, all heads) -> [T, heads/size, hd] (all tokens, my heads)."""
