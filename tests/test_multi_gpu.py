@@ -574,6 +574,66 @@ def _sec_peer_share(rank, world, dev, ops, res):
     res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
 
 
+def _sec_model_parallel_variants(rank, world, dev, ops, res):
+    """Engine layouts that were checked on gloo, on GPUs with bf16 weights and the native kernels: experts cut over the
+    tensor-parallel group, interleaved pipeline stages, and a context-parallel group size per row. Each against the plain
+    engine on the same rows: gradient norm, log-probs and the re-assembled weights after one step."""
+    import dataclasses
+    from functools import partial
+
+    from verl_b200.models import get_preset
+    from verl_b200.models.config import ModelConfig
+    from verl_b200.workers.config import FSDPEngineConfig, McoreEngineConfig, OptimizerConfig
+    from verl_b200.workers.engine.base import EngineRegistry
+    from verl_b200.workers.utils.losses import sft_loss
+
+    dense = ModelConfig(model_type="qwen2", vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=128, eos_token_id=2, pad_token_id=0)
+    moe = ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,
+                      moe_intermediate_size=128, eos_token_id=2, pad_token_id=0, qk_norm=True)
+    g = torch.Generator().manual_seed(11)                     # the same rows on both ranks
+    ids = torch.randint(3, 1000, (4, 160), generator=g)
+    am = torch.ones_like(ids)
+    am[1, 120:] = 0
+    am[2, 70:] = 0
+    data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 40:].to(dev), "response_mask": am[:, 40:].to(dev)}
+    os.environ["VERL_B200_FUSED_COMM"] = "0"
+    opt = lambda: OptimizerConfig(lr=1e-3, clip_grad=1.0)
+    cases = (("etp", moe, "megatron", McoreEngineConfig(seed=3, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)),
+             ("vpp", dense, "megatron", McoreEngineConfig(seed=3, micro_batch_size_per_gpu=2, pipeline_model_parallel_size=2,
+                                                            virtual_pipeline_model_parallel_size=2)),
+             ("dcp", dense, "fsdp", FSDPEngineConfig(seed=3, micro_batch_size_per_gpu=2, context_parallel_size=2,
+                                                      dynamic_context_parallel=True, max_seqlen_per_dp_cp_rank=96)))
+    plain = {}
+    for name, arch, backend, ec in cases:
+        if id(arch) not in plain:
+            ref = EngineRegistry.new("language_model", "fsdp", arch, FSDPEngineConfig(seed=3, micro_batch_size_per_gpu=2), opt())
+            ref.initialize()
+            lp = ref.infer_batch(dict(data))["model_output"]["log_probs"].float().clone()
+            norm = float(ref.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"])
+            plain[id(arch)] = (lp, norm, ref.params.flat.float().clone())
+            del ref
+            torch.cuda.empty_cache()
+        eng = EngineRegistry.new("language_model", backend, arch, ec, opt())
+        eng.initialize()
+        lp = eng.infer_batch(dict(data))["model_output"]["log_probs"].float().clone()
+        norm = float(eng.train_batch(dict(data), partial(sft_loss, None))["metrics"]["grad_norm"])
+        full = eng.gather_full_params().flat.float() if backend == "megatron" else eng.params.flat.float()
+        ref_lp, ref_norm, ref_flat = plain[id(arch)]
+        m = data["response_mask"].bool()
+        n = min(full.numel(), ref_flat.numel())
+        res[f"{name}_lp_diff"] = (lp[m] - ref_lp[m]).abs().max().item()
+        res[f"{name}_norms"] = (norm, ref_norm)
+        res[f"{name}_param_diff"] = (full[:n] - ref_flat[:n]).abs().max().item()
+        if name == "dcp":
+            res["dcp_sizes"] = sorted({a.size for mb in eng.last_dcp_plan for a in mb if a.rows})
+        del eng
+        torch.cuda.empty_cache()
+    os.environ["VERL_B200_FUSED_COMM"] = "1"
+    res["status"] = (int(ops.gemm_status()), int(ops.comm_status()))
+
+
 def _sec_rollout_tensor_parallel(rank, world, dev, ops, res):
     """The rollout engine over the two GPUs as one tensor-parallel group (row ranges of the fused weights in one launch,
     GEMM + all-reduce kernels, every rank sampling its half of the batch inside the captured decode graph) against the
@@ -779,6 +839,14 @@ def test_tensor_parallel_training_with_fused_collectives(pair):
 def test_ulysses_exchange_over_peer_memory(pair):
     for res in pair.run("peer_all_to_all").values():
         assert res["equal"] and res["status"] == (0, 0), res
+
+
+def test_expert_tensor_parallel_virtual_stages_and_dynamic_context_parallel_on_gpus(pair):
+    for res in pair.run("model_parallel_variants", timeout=900).values():
+        for name in ("etp", "vpp", "dcp"):
+            a, b = res[f"{name}_norms"]
+            assert res[f"{name}_lp_diff"] < 5e-2 and abs(a - b) < 2e-2 * max(1.0, b) and res[f"{name}_param_diff"] < 2e-2, (name, res)
+        assert res["dcp_sizes"] == [1, 2] and res["status"] == (0, 0), res
 
 
 def test_rollout_engine_tensor_parallel_on_gpus(pair):
