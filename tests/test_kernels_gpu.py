@@ -364,7 +364,8 @@ def _attn_reference(q, k, v, lens, scale):
     return torch.cat(outs, 0)
 
 
-@pytest.mark.parametrize("lens,nh,nkv", [([300, 129, 64, 1], 4, 2), ([1000], 7, 1), ([130, 257], 2, 2)])
+@pytest.mark.parametrize("lens,nh,nkv", [([300, 129, 64, 1], 4, 2), ([1000], 7, 1), ([130, 257], 2, 2),
+                                         ([3072, 2900], 28, 4)])   # the last: the benchmark's shape class (long rows, 28 / 4 heads)
 def test_attention_forward_and_backward_tcgen05(ops, lens, nh, nkv):
     torch.manual_seed(0)
     T, hd = sum(lens), 128

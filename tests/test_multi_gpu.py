@@ -404,7 +404,8 @@ def _sec_peer_reshard(rank, world, dev, ops, res):
                       moe_intermediate_size=128, eos_token_id=2, pad_token_id=0, qk_norm=True)
     os.environ["VERL_B200_FUSED_COMM"] = "0"
     for name, arch, ec in (("tp", dense, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2)),
-                           ("ep", moe, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, expert_model_parallel_size=2))):
+                           ("ep", moe, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, expert_model_parallel_size=2)),
+                           ("etp", moe, McoreEngineConfig(seed=9, micro_batch_size_per_gpu=2, tensor_model_parallel_size=2))):
         eng = EngineRegistry.new("language_model", "megatron", arch, ec, OptimizerConfig(lr=1e-3, clip_grad=1.0))
         eng.initialize()
         plan = PeerReshard.try_create(eng)
@@ -423,7 +424,7 @@ def _sec_peer_reshard(rank, world, dev, ops, res):
         bad = differing(plan, eng)
         res[f"{name}_equal_0"] = not bad
         res[f"{name}_bad_0"] = bad[:4]
-        g = torch.Generator().manual_seed(300 + (0 if name == "tp" else rank))
+        g = torch.Generator().manual_seed(300 + (rank if name == "ep" else 0))   # tensor-parallel ranks see the same rows
         ids = torch.randint(3, 1024, (4, 40), generator=g)
         am = torch.ones_like(ids)
         data = {"input_ids": ids.to(dev), "attention_mask": am.to(dev), "responses": ids[:, 16:].to(dev), "response_mask": am[:, 16:].to(dev)}

@@ -73,6 +73,21 @@ class PeerReshard:
             src = eng.params.views[m.local_name]
             assert src.is_contiguous()
             parts = _slices(m, self.full.views[m.full_name], topo.tp, topo.tp_rank, topo.ep, topo.ep_rank)
+            if m.kind in ("expert_rows", "expert_cols") and topo.tp > 1:
+                # stacked expert matrices [E, rows, cols] cut inside every expert: one job per expert and part
+                E_l, rows_l, cols_l = src.shape
+                r0 = 0
+                for part in parts:
+                    pr, pc = part.shape[1], part.shape[2]
+                    for e in range(E_l):
+                        off = part[e].data_ptr() - base
+                        s_addr = src.data_ptr() + ((e * rows_l + r0) * cols_l) * esz
+                        if m.kind == "expert_rows":   # pr whole rows of the expert: one contiguous run
+                            local.append((off, s_addr, 1, pr * pc * esz, pr * pc * esz, pr * pc * esz))
+                        else:                          # a column block of the expert's matrix
+                            local.append((off, s_addr, pr, pc * esz, part.stride(1) * esz, cols_l * esz))
+                    r0 += pr if m.kind == "expert_rows" else 0
+                continue
             row0 = 0
             for part in parts:
                 off = part.data_ptr() - base
