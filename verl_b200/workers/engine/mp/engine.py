@@ -105,7 +105,10 @@ class ModelParallelEngine(NativeEngine):
             if self.full_arch.is_moe:
                 self.model.etp_sum = reduce
             self.fused_tp_collectives = False
-            use_sp = bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1
+            # (mixture-of-experts blocks keep the whole token stream on every tensor-parallel rank: their routed tokens are
+            # not a token slice; sequence parallelism is therefore a dense-model option and is left off for them)
+            want_sp = bool(getattr(self.engine_config, "sequence_parallel", False)) and not self.full_arch.is_moe
+            use_sp = want_sp and self.cp_size == 1
             fused = None
             if self.device.type == "cuda" and dist.get_world_size() == self.topo.tp and os.environ.get("VERL_B200_FUSED_TP", "1") != "0":
                 # one kernel per row-parallel projection / column-parallel input gradient: GEMM with the all-reduce (or, with
@@ -126,14 +129,13 @@ class ModelParallelEngine(NativeEngine):
                     return fused(x.contiguous(), w, None, None, b_mn)
 
                 self.model.tp_linear_sum = linear_sum
-            if bool(getattr(self.engine_config, "sequence_parallel", False)) and self.cp_size == 1:
+            if use_sp:
                 # (with context parallelism the stream is already token-sliced over the context-parallel block, and the
                 # tensor-parallel group keeps the plain all-reduce form)
                 # token-sliced residual stream: reduce-scatter behind the row-parallel projections, all-gather in front of
                 # the column-parallel ones
                 from ....models.decoder import TensorSequenceParallel
 
-                assert not self.full_arch.is_moe, "sequence parallelism covers dense blocks"
                 self.model.tsp = TensorSequenceParallel(grp, self.topo.tp_rank, self.topo.tp)
                 self.model.tp_reduce = self.model.tsp.scatter_sum
                 if fused is not None:
