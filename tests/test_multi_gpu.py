@@ -678,6 +678,7 @@ def _worker(rank, world, port, cmd_q, res_q):
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                           MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        os.environ.pop("VERL_ENGINE_DEVICE", None)  # CPU test modules imported by the parent at collection pin it to "cpu"
         import torch.distributed as dist
 
         from verl_b200.ops import native
