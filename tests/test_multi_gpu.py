@@ -625,6 +625,7 @@ def _sec_model_parallel_variants(rank, world, dev, ops, res):
         m = data["response_mask"].bool()
         n = min(full.numel(), ref_flat.numel())
         res[f"{name}_lp_diff"] = (lp[m] - ref_lp[m]).abs().max().item()
+        res[f"{name}_lp_mean_diff"] = (lp[m] - ref_lp[m]).abs().mean().item()
         res[f"{name}_norms"] = (norm, ref_norm)
         res[f"{name}_param_diff"] = (full[:n] - ref_flat[:n]).abs().max().item()
         if name == "dcp":
@@ -847,7 +848,11 @@ def test_expert_tensor_parallel_virtual_stages_and_dynamic_context_parallel_on_g
     for res in pair.run("model_parallel_variants", timeout=900).values():
         for name in ("etp", "vpp", "dcp"):
             a, b = res[f"{name}_norms"]
-            assert res[f"{name}_lp_diff"] < 5e-2 and abs(a - b) < 2e-2 * max(1.0, b) and res[f"{name}_param_diff"] < 2e-2, (name, res)
+            # experts cut over two ranks add their halves in bf16 in another order than one rank does: the worst single
+            # log-probability may move by a bf16 step of the logits (2^-4 at |logit| >= 8), the mean stays far below it
+            worst = 1e-1 if name == "etp" else 5e-2
+            assert res[f"{name}_lp_diff"] < worst and res[f"{name}_lp_mean_diff"] < 1e-2, (name, res)
+            assert abs(a - b) < 2e-2 * max(1.0, b) and res[f"{name}_param_diff"] < 2e-2, (name, res)
         assert res["dcp_sizes"] == [1, 2] and res["status"] == (0, 0), res
 
 
