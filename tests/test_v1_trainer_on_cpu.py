@@ -122,3 +122,41 @@ def test_async_trainer_checkpoints_its_buffer_and_reissues_inflight_prompts(monk
         if uid in q.list_keys("train"):
             tg = q.get_tags(uid, "train")
             assert tg["done"] <= tg["n"] and tg["start_version"] >= 2
+
+
+def test_fit_step_runs_the_overridable_phases_in_order(monkeypatch):
+    """``fit_step`` is a template over ``_fit_*`` phases (the names of ``verl/experimental/separation/ray_trainer.py``):
+    wrapping each phase records the order, and overriding one changes only that part of the step."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.trainer.main_ppo import main
+
+    args = [a for a in ARGS if not a.startswith(("trainer.use_v1", "trainer.total_training_steps"))]
+    t = main(args + ["trainer.use_v1=false", "trainer.total_training_steps=1"])
+    assert t.global_steps == 2
+    order = []
+    names = ["_fit_prepare_step", "_fit_start_profile", "_fit_get_batch", "_fit_generate", "_fit_balance", "_fit_compute_reward",
+             "_fit_compute_log_prob", "_fit_compute_ref_log_prob", "_fit_compute_critic", "_fit_compute_advantage",
+             "_fit_update_critic", "_fit_update_actor", "_fit_update_weights", "_fit_dump_data", "_fit_validate",
+             "_fit_save_checkpoint", "_fit_stop_profile", "_fit_collect_metrics", "_fit_experimental", "_fit_postprocess_step"]
+    for n in names:
+        def wrap(*a, _n=n, _f=getattr(t, n), **k):
+            order.append(_n)
+            return _f(*a, **k)
+        monkeypatch.setattr(t, n, wrap)
+
+    def doubled_reward(batch, _f=t._fit_compute_reward):
+        batch = _f(batch)
+        batch.batch["token_level_scores"] = batch.batch["token_level_scores"] * 2
+        return batch
+
+    monkeypatch.setattr(t, "_fit_compute_reward", doubled_reward)
+    t.total_training_steps = 5
+    metrics, timing = t.fit_step(next(iter(t.train_dataloader)))
+    assert order == names and t.global_steps == 3 and metrics["training/global_step"] == 2
+    assert {"gen", "old_log_prob", "ref", "adv", "update_actor", "update_weights", "step"} <= set(timing)
+    scores = t.last_batch.batch["token_level_scores"].sum(-1)
+    assert abs(metrics["critic/score/mean"] - scores.mean().item()) < 1e-5 and "actor/entropy" in metrics
+    # the coarse phases used by the benchmark and the asynchronous trainers are the same methods, grouped
+    order.clear()
+    t.train_step(next(iter(t.train_dataloader)))
+    assert order == names[2:14] + ["_fit_collect_metrics"]

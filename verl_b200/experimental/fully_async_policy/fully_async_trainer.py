@@ -127,6 +127,7 @@ class FullyAsyncTrainer(PPOTrainer):
     def fit_step(self) -> Optional[tuple[dict, dict]]:
         metrics: dict[str, Any] = {}
         timing_raw: dict[str, float] = {}
+        self._bind_step(metrics, timing_raw)
         with marked_timer("step", timing_raw):
             self._each_server("resume_generation")
             with marked_timer("gen", timing_raw, color="red"):
@@ -145,11 +146,14 @@ class FullyAsyncTrainer(PPOTrainer):
             batch = self.learn_phase(batch, metrics, timing_raw)
             self.local_updates += 1
             if self.local_updates % self.trigger == 0:
-                self._fit_update_weights(metrics, timing_raw)
+                self._fit_update_weights()
         metrics.update(self.rollouter.statistics())
         return self.finish_step(batch, metrics, timing_raw)
 
-    def _fit_update_weights(self, metrics: dict, timing_raw: dict) -> None:
+    def _fit_update_weights(self) -> None:
+        """Push the weights to the rollouter through the parameter synchroniser and open a new parameter version (the
+        base class's in-place hand-over is what ``fit`` uses once, before the first step)."""
+        metrics, timing_raw = self.metrics, self.timing_raw
         with marked_timer("update_weights", timing_raw, color="red"):
             self.param_version += 1
             res = self.synchronizer.sync_weights(self.param_version)
@@ -169,7 +173,8 @@ class FullyAsyncTrainer(PPOTrainer):
             self.init()
         self.global_steps = 0
         self._load_checkpoint()
-        self.sync_phase(None, {}, {})
+        self._bind_step({}, {})
+        super()._fit_update_weights()
         self._each_server("wake_up")
         self.global_steps = 1
         while self.global_steps <= self.total_training_steps:

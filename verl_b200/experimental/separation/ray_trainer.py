@@ -2,7 +2,10 @@
 
 The split-job machinery (rank layout, prompt/sample queues, flat-buffer weight broadcast, rollout-only service) is
 ``verl_b200.trainer.ppo.v1.trainer_separate_async``; this class fixes the policy knobs that "separation" means in the
-reference: no hybrid switching (pools never exchange GPUs) and weights pushed after every step.
+reference: no hybrid switching (pools never exchange GPUs) and weights pushed after every step. The step itself is the
+template of ``_fit_*`` phases inherited from ``RayPPOTrainer`` (``fit_step``: prepare, profile, get batch, generate, reward,
+log-probs, reference log-probs, values, advantage, critic update, actor update, weight hand-over, dump, validate, checkpoint,
+metrics): a subclass changes one phase by overriding one method, as with the reference's class of the same name.
 
 Parity target: ``verl/experimental/separation/{ray_trainer.py 763, engine_workers.py 169, utils.py 95}``.
 """

@@ -499,170 +499,283 @@ class RayPPOTrainer:
             if cfg.trainer.get("val_only", False):
                 return
         self.global_steps += 1
-        last_val = None
+        self.logger, self.last_val_metrics = logger, None
         for epoch in range(cfg.trainer.total_epochs):
             for batch_dict in self.train_dataloader:
+                self.epoch = epoch
+                self._bind_step({}, {})
+                self._fit_prepare_step()
                 metrics, timing_raw = self.train_step(batch_dict)
-                is_last = self.global_steps >= self.total_training_steps
-                tf = cfg.trainer.get("test_freq", -1)
-                if self.val_reward_fn is not None and tf and tf > 0 and (is_last or self.global_steps % tf == 0):
-                    with marked_timer("testing", timing_raw):
-                        last_val = self._validate()
-                    metrics.update(last_val)
-                sf = cfg.trainer.get("save_freq", -1)
-                esi = should_save_ckpt_esi(max_steps_duration=timing_raw.get("step", 0.0),
-                                           redundant_time=cfg.trainer.get("esi_redundant_time", 0))
-                if sf and sf > 0 and (is_last or self.global_steps % sf == 0 or esi):
-                    with marked_timer("save_checkpoint", timing_raw):
-                        self._save_checkpoint()
-                metrics["training/global_step"] = self.global_steps
-                metrics["training/epoch"] = epoch
-                logger.log(data=metrics, step=self.global_steps)
-                self.global_steps += 1
-                if is_last:
-                    if last_val:
-                        print(f"Final validation metrics: {last_val}")
+                self._bind_step(metrics, timing_raw)
+                self._fit_validate()
+                self._fit_save_checkpoint()
+                self._fit_postprocess_step()
+                if self.is_last_step:
+                    if self.last_val_metrics:
+                        print(f"Final validation metrics: {self.last_val_metrics}")
                     return
+
+    # ---------------------------------------------------------------- one step as a template of overridable phases
+    # ``fit_step`` / ``train_step`` run the ``_fit_*`` methods below in order; a subclass changes one phase by overriding
+    # one method (same names and ``batch -> batch`` shape as ``verl/experimental/separation/ray_trainer.py:341-760``).
+    # The phases write to ``self.metrics`` and ``self.timing_raw``, which ``_bind_step`` points at the caller's dicts.
+
+    def _bind_step(self, metrics: Optional[dict] = None, timing_raw: Optional[dict] = None) -> None:
+        if metrics is not None or not hasattr(self, "metrics"):
+            self.metrics = {} if metrics is None else metrics
+        if timing_raw is not None or not hasattr(self, "timing_raw"):
+            self.timing_raw = {} if timing_raw is None else timing_raw
 
     def train_step(self, batch_dict: dict) -> tuple[dict, dict]:
         """One PPO/GRPO step on one batch of prompts: rollout -> reward -> log-probs -> advantage -> updates."""
-        cfg = self.config
-        algo = cfg.algorithm
-        rank, world = self._dp_rank_world()
         metrics: dict[str, Any] = {}
         timing_raw: dict[str, float] = {}
-        n_gpus = self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager is not None else world
-        rollout_cfg = cfg.actor_rollout_ref.rollout
         with marked_timer("step", timing_raw):
             batch = self.rollout_phase(batch_dict, metrics, timing_raw)
             batch = self.learn_phase(batch, metrics, timing_raw)
             self.sync_phase(batch, metrics, timing_raw)
         return self.finish_step(batch, metrics, timing_raw)
 
+    def fit_step(self, batch_dict: Any = None) -> tuple[dict, dict]:
+        """``train_step`` plus what ``fit`` does around it (validation, checkpoint, logging, step counter), as one call."""
+        self._bind_step({}, {})
+        self._fit_prepare_step()
+        self._fit_start_profile()
+        with marked_timer("step", self.timing_raw):
+            batch = self._fit_get_batch(batch_dict)
+            batch = self._fit_generate(batch)
+            batch = self._fit_balance(batch)
+            batch = self._fit_compute_reward(batch)
+            batch = self._fit_compute_log_prob(batch)
+            batch = self._fit_compute_ref_log_prob(batch)
+            batch = self._fit_compute_critic(batch)
+            batch = self._fit_compute_advantage(batch)
+            batch = self._fit_update_critic(batch)
+            batch = self._fit_update_actor(batch)
+            self._fit_update_weights()
+            self._fit_dump_data(batch)
+        self._fit_validate()
+        self._fit_save_checkpoint()
+        self._fit_stop_profile()
+        self._fit_collect_metrics(batch)
+        self._fit_experimental(batch)
+        self._fit_postprocess_step()
+        return self.metrics, self.timing_raw
+
     def rollout_phase(self, batch_dict: dict, metrics: dict, timing_raw: dict) -> DataProto:
         """Prompts -> n sampled responses per prompt, merged with the prompt-side fields."""
-        cfg = self.config
-        algo = cfg.algorithm
-        rank, world = self._dp_rank_world()
-        rollout_cfg = cfg.actor_rollout_ref.rollout
-        if True:
-            batch = DataProto.from_single_dict(batch_dict)
-            batch.meta_info["temperature"] = rollout_cfg.temperature
-            if "uid" not in batch.non_tensor_batch:
-                batch.non_tensor_batch["uid"] = np.array([f"{rank}-{self.global_steps}-{i}" for i in range(len(batch))], dtype=object)
-            gen_batch = self._get_gen_batch(batch)
-            gen_batch.meta_info = {"global_steps": self.global_steps, "temperature": rollout_cfg.temperature}
-            gen_batch = gen_batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
-            gen_batch = self._to_device(gen_batch)
-            with marked_timer("gen", timing_raw, color="red"):
-                from ...utils.skip import SkipManager
-
-                if cfg.get("skip") and not SkipManager.skip_instances and SkipManager.config is None:
-                    SkipManager.init(cfg)
-                SkipManager.set_step(self.global_steps)
-                gen_out = SkipManager.annotate("rollout")(lambda prompts: self.actor_rollout_wg.generate_sequences(prompts))(gen_batch)
-                timing_raw.update({f"gen/{k}": v for k, v in gen_out.meta_info.pop("timing", {}).items()})
-                gen_out.meta_info.pop("rollout_stats", None)
-            if str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX"):
-                with marked_timer("gen_max", timing_raw, color="purple"):
-                    base = deepcopy(gen_batch)
-                    base.meta_info["do_sample"] = False
-                    base_out = self.actor_rollout_wg.generate_sequences(base)
-                    tmp = batch.repeat(rollout_cfg.n, interleave=True).union(base_out)
-                    rb, _ = self._compute_reward(tmp, self.reward_fn)
-                    batch.batch = None
-                    baseline = rb.sum(-1)
-            batch = batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
-            batch = batch.union(gen_out)
-            if str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX"):
-                batch.batch["reward_baselines"] = baseline
-            if "response_mask" not in batch.batch.keys():
-                batch.batch["response_mask"] = compute_response_mask(batch)
-        return batch
+        self._bind_step(metrics, timing_raw)
+        return self._fit_generate(self._fit_get_batch(batch_dict))
 
     def learn_phase(self, batch: DataProto, metrics: dict, timing_raw: dict) -> DataProto:
         """Reward -> old/ref log-probs (-> values) -> advantages -> critic/actor updates on a generated batch."""
-        cfg = self.config
-        algo = cfg.algorithm
-        rollout_cfg = cfg.actor_rollout_ref.rollout
-        if True:
-            if cfg.trainer.get("balance_batch", True) and not self.spmd:
-                self._balance_batch(batch, metrics)
-            batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
-            with marked_timer("reward", timing_raw, color="yellow"):
-                reward_tensor, reward_extra = self._compute_reward(batch, self.reward_fn)
-                batch.batch["token_level_scores"] = reward_tensor
-                for k, v in reward_extra.items():
-                    batch.non_tensor_batch[k] = np.asarray(v)
-            with marked_timer("old_log_prob", timing_raw, color="blue"):
-                old = self.actor_rollout_wg.compute_log_prob(batch)
-                ent = old.batch["entropys"]
-                metrics["actor/entropy"] = agg_loss(ent, batch.batch["response_mask"].to(ent.dtype),
-                                                    cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean")).item()
-                old.batch.pop("entropys")
-                batch = batch.union(old)
-                if "rollout_log_probs" in batch.batch.keys():
-                    m = batch.batch["response_mask"].bool()
-                    diff = (torch.exp(batch.batch["rollout_log_probs"]) - torch.exp(batch.batch["old_log_probs"])).abs()
-                    sel = diff[m]
-                    if sel.numel():
-                        metrics.update({"training/rollout_probs_diff_max": sel.max().item(),
-                                        "training/rollout_probs_diff_mean": sel.mean().item()})
-            if self.use_reference_policy:
-                with marked_timer("ref", timing_raw, color="olive"):
-                    batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
-            if self.use_critic:
-                with marked_timer("values", timing_raw, color="cyan"):
-                    batch = batch.union(self.critic_wg.compute_values(batch))
-            with marked_timer("adv", timing_raw, color="brown"):
-                if algo.get("use_kl_in_reward", False):
-                    batch, kl_m = apply_kl_penalty(batch, kl_ctrl=self.kl_ctrl_in_reward, kl_penalty=algo.get("kl_penalty", "kl"),
-                                                   dp=self._dp_view())
-                    metrics.update(kl_m)
-                else:
-                    batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
-                rc = algo.get("rollout_correction")
-                if rc is not None and "rollout_log_probs" in batch.batch.keys() and (rc.get("rollout_is") or rc.get("rollout_rs")):
-                    from .rollout_corr_helper import compute_rollout_correction_and_add_to_batch
-
-                    batch, rc_m = compute_rollout_correction_and_add_to_batch(batch, rc)
-                    metrics.update(rc_m)
-                batch = compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
-                                          lam=algo.get("lam", 1.0), num_repeat=rollout_cfg.n,
-                                          norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo,
-                                          dp=self._dp_view())
-            if self.use_critic:
-                with marked_timer("update_critic", timing_raw, color="pink"):
-                    cout = self.critic_wg.update_critic(batch)
-                metrics.update(reduce_metrics(cout.meta_info["metrics"]))
-            if cfg.trainer.get("critic_warmup", 0) <= self.global_steps:
-                with marked_timer("update_actor", timing_raw, color="red"):
-                    aout = self.actor_rollout_wg.update_actor(batch)
-                metrics.update(reduce_metrics(aout.meta_info["metrics"]))
+        self._bind_step(metrics, timing_raw)
+        for phase in (self._fit_balance, self._fit_compute_reward, self._fit_compute_log_prob, self._fit_compute_ref_log_prob,
+                      self._fit_compute_critic, self._fit_compute_advantage, self._fit_update_critic, self._fit_update_actor):
+            batch = phase(batch)
         return batch
 
     def sync_phase(self, batch: Optional[DataProto], metrics: dict, timing_raw: dict) -> None:
         """Make the rollout side see the freshly updated weights (in place when colocated)."""
-        cfg = self.config
-        if True:
-            with marked_timer("update_weights", timing_raw, color="red"):
-                res = self.actor_rollout_wg.update_weights(self.global_steps)
-                res = res[0] if isinstance(res, list) else res
-                metrics["timing_s/update_weights_worker"] = float((res or {}).get("timing_s/update_weights", 0.0))
-            if batch is not None and cfg.trainer.get("rollout_data_dir"):
-                self._dump_generations(batch, cfg.trainer.rollout_data_dir)
+        self._bind_step(metrics, timing_raw)
+        self._fit_update_weights()
+        self._fit_dump_data(batch)
 
     def finish_step(self, batch: DataProto, metrics: dict, timing_raw: dict) -> tuple[dict, dict]:
+        self._bind_step(metrics, timing_raw)
+        self._fit_collect_metrics(batch)
+        return self.metrics, timing_raw
+
+    def _fit_prepare_step(self) -> None:
+        self.is_last_step = self.global_steps >= self.total_training_steps
+
+    def _fit_start_profile(self, should_profiler: Optional[bool] = None) -> None:
+        steps = (self.config.get("global_profiler") or {}).get("steps") or []
+        self.curr_step_profile = bool(should_profiler) if should_profiler is not None else self.global_steps in steps
+        if self.curr_step_profile and hasattr(self.actor_rollout_wg, "start_profile"):
+            with marked_timer("start_profile", self.timing_raw):
+                self.actor_rollout_wg.start_profile(profile_step=self.global_steps)
+
+    def _fit_stop_profile(self, should_profiler: Optional[bool] = None) -> None:
+        on = getattr(self, "curr_step_profile", False) if should_profiler is None else should_profiler
+        if on and hasattr(self.actor_rollout_wg, "stop_profile"):
+            with marked_timer("stop_profile", self.timing_raw):
+                self.actor_rollout_wg.stop_profile()
+        self.curr_step_profile = False
+
+    def _fit_get_batch(self, batch_dict: dict) -> DataProto:
+        rank, _ = self._dp_rank_world()
+        batch = DataProto.from_single_dict(batch_dict)
+        batch.meta_info["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        if "uid" not in batch.non_tensor_batch:
+            batch.non_tensor_batch["uid"] = np.array([f"{rank}-{self.global_steps}-{i}" for i in range(len(batch))], dtype=object)
+        return batch
+
+    def _fit_generate(self, batch: DataProto) -> DataProto:
+        cfg, algo, timing_raw = self.config, self.config.algorithm, self.timing_raw
+        rollout_cfg = cfg.actor_rollout_ref.rollout
+        remax = str(algo.adv_estimator) in ("remax", "AdvantageEstimator.REMAX")
+        gen_batch = self._get_gen_batch(batch)
+        gen_batch.meta_info = {"global_steps": self.global_steps, "temperature": rollout_cfg.temperature}
+        gen_batch = gen_batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
+        gen_batch = self._to_device(gen_batch)
+        with marked_timer("gen", timing_raw, color="red"):
+            from ...utils.skip import SkipManager
+
+            if cfg.get("skip") and not SkipManager.skip_instances and SkipManager.config is None:
+                SkipManager.init(cfg)
+            SkipManager.set_step(self.global_steps)
+            gen_out = SkipManager.annotate("rollout")(lambda prompts: self.actor_rollout_wg.generate_sequences(prompts))(gen_batch)
+            timing_raw.update({f"gen/{k}": v for k, v in gen_out.meta_info.pop("timing", {}).items()})
+            gen_out.meta_info.pop("rollout_stats", None)
+        if remax:
+            with marked_timer("gen_max", timing_raw, color="purple"):
+                base = deepcopy(gen_batch)
+                base.meta_info["do_sample"] = False
+                base_out = self.actor_rollout_wg.generate_sequences(base)
+                tmp = batch.repeat(rollout_cfg.n, interleave=True).union(base_out)
+                rb, _ = self._compute_reward(tmp, self.reward_fn)
+                batch.batch = None
+                baseline = rb.sum(-1)
+        batch = batch.repeat(repeat_times=rollout_cfg.n, interleave=True)
+        batch = batch.union(gen_out)
+        if remax:
+            batch.batch["reward_baselines"] = baseline
+        if "response_mask" not in batch.batch.keys():
+            batch.batch["response_mask"] = compute_response_mask(batch)
+        return batch
+
+    def _fit_balance(self, batch: DataProto) -> DataProto:
+        """Reorder the rows so every data-parallel rank gets about the same number of tokens; record the token counts."""
+        if self.config.trainer.get("balance_batch", True) and not self.spmd:
+            self._balance_batch(batch, self.metrics)
+        batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
+        return batch
+
+    def _fit_compute_reward(self, batch: DataProto) -> DataProto:
+        with marked_timer("reward", self.timing_raw, color="yellow"):
+            reward_tensor, reward_extra = self._compute_reward(batch, self.reward_fn)
+            batch.batch["token_level_scores"] = reward_tensor
+            for k, v in reward_extra.items():
+                batch.non_tensor_batch[k] = np.asarray(v)
+        return batch
+
+    def _fit_compute_log_prob(self, batch: DataProto) -> DataProto:
+        cfg, metrics = self.config, self.metrics
+        with marked_timer("old_log_prob", self.timing_raw, color="blue"):
+            old = self.actor_rollout_wg.compute_log_prob(batch)
+            ent = old.batch["entropys"]
+            metrics["actor/entropy"] = agg_loss(ent, batch.batch["response_mask"].to(ent.dtype),
+                                                cfg.actor_rollout_ref.actor.get("loss_agg_mode", "token-mean")).item()
+            old.batch.pop("entropys")
+            batch = batch.union(old)
+            if "rollout_log_probs" in batch.batch.keys():
+                m = batch.batch["response_mask"].bool()
+                diff = (torch.exp(batch.batch["rollout_log_probs"]) - torch.exp(batch.batch["old_log_probs"])).abs()
+                sel = diff[m]
+                if sel.numel():
+                    metrics.update({"training/rollout_probs_diff_max": sel.max().item(),
+                                    "training/rollout_probs_diff_mean": sel.mean().item()})
+        return batch
+
+    def _fit_compute_ref_log_prob(self, batch: DataProto) -> DataProto:
+        if self.use_reference_policy:
+            with marked_timer("ref", self.timing_raw, color="olive"):
+                batch = batch.union(self.ref_policy_wg.compute_ref_log_prob(batch))
+        return batch
+
+    def _fit_compute_critic(self, batch: DataProto) -> DataProto:
+        if self.use_critic:
+            with marked_timer("values", self.timing_raw, color="cyan"):
+                batch = batch.union(self.critic_wg.compute_values(batch))
+        return batch
+
+    def _fit_compute_advantage(self, batch: DataProto) -> DataProto:
+        algo, metrics = self.config.algorithm, self.metrics
+        with marked_timer("adv", self.timing_raw, color="brown"):
+            if algo.get("use_kl_in_reward", False):
+                batch, kl_m = apply_kl_penalty(batch, kl_ctrl=self.kl_ctrl_in_reward, kl_penalty=algo.get("kl_penalty", "kl"),
+                                               dp=self._dp_view())
+                metrics.update(kl_m)
+            else:
+                batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
+            rc = algo.get("rollout_correction")
+            if rc is not None and "rollout_log_probs" in batch.batch.keys() and (rc.get("rollout_is") or rc.get("rollout_rs")):
+                from .rollout_corr_helper import compute_rollout_correction_and_add_to_batch
+
+                batch, rc_m = compute_rollout_correction_and_add_to_batch(batch, rc)
+                metrics.update(rc_m)
+            batch = compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
+                                      lam=algo.get("lam", 1.0), num_repeat=self.config.actor_rollout_ref.rollout.n,
+                                      norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo,
+                                      dp=self._dp_view())
+        return batch
+
+    def _fit_update_critic(self, batch: DataProto) -> DataProto:
+        if self.use_critic:
+            with marked_timer("update_critic", self.timing_raw, color="pink"):
+                cout = self.critic_wg.update_critic(batch)
+            self.metrics.update(reduce_metrics(cout.meta_info["metrics"]))
+        return batch
+
+    def _fit_update_actor(self, batch: DataProto) -> DataProto:
+        if self.config.trainer.get("critic_warmup", 0) <= self.global_steps:
+            with marked_timer("update_actor", self.timing_raw, color="red"):
+                aout = self.actor_rollout_wg.update_actor(batch)
+            self.metrics.update(reduce_metrics(aout.meta_info["metrics"]))
+        return batch
+
+    def _fit_update_weights(self) -> None:
+        with marked_timer("update_weights", self.timing_raw, color="red"):
+            res = self.actor_rollout_wg.update_weights(self.global_steps)
+            res = res[0] if isinstance(res, list) else res
+            self.metrics["timing_s/update_weights_worker"] = float((res or {}).get("timing_s/update_weights", 0.0))
+
+    def _fit_dump_data(self, batch: Optional[DataProto]) -> None:
+        if batch is not None and self.config.trainer.get("rollout_data_dir"):
+            self._dump_generations(batch, self.config.trainer.rollout_data_dir)
+
+    def _fit_validate(self) -> None:
+        tf = self.config.trainer.get("test_freq", -1)
+        if self.val_reward_fn is not None and tf and tf > 0 and (self.is_last_step or self.global_steps % tf == 0):
+            with marked_timer("testing", self.timing_raw):
+                self.last_val_metrics = self._validate()
+            self.metrics.update(self.last_val_metrics)
+
+    def _fit_save_checkpoint(self) -> None:
+        cfg = self.config
+        sf = cfg.trainer.get("save_freq", -1)
+        esi = should_save_ckpt_esi(max_steps_duration=self.timing_raw.get("step", 0.0),
+                                   redundant_time=cfg.trainer.get("esi_redundant_time", 0))
+        if sf and sf > 0 and (self.is_last_step or self.global_steps % sf == 0 or esi):
+            with marked_timer("save_checkpoint", self.timing_raw):
+                self._save_checkpoint()
+
+    def _fit_collect_metrics(self, batch: DataProto) -> None:
+        metrics, timing_raw = self.metrics, self.timing_raw
         rank, world = self._dp_rank_world()
         n_gpus = self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager is not None else world
         metrics.update(compute_data_metrics(batch=batch, use_critic=self.use_critic))
         metrics.update(compute_timing_metrics(batch=batch, timing_raw=timing_raw))
         metrics.update(compute_throughout_metrics(batch=batch, timing_raw=timing_raw, n_gpus=max(1, n_gpus if not self.spmd else 1)))
-        metrics = self._allreduce_metrics(metrics)
+        reduced = self._allreduce_metrics(metrics)
+        if reduced is not metrics:
+            metrics.clear()
+            metrics.update(reduced)
         if self.spmd and world > 1:
             metrics["perf/throughput"] = metrics["perf/total_num_tokens"] / (metrics["perf/time_per_step"] * world)
         self.last_batch = batch
-        return metrics, timing_raw
+
+    def _fit_experimental(self, batch: DataProto) -> None:
+        """Hook for subclasses (curriculum samplers, extra dumps); nothing by default."""
+
+    def _fit_postprocess_step(self) -> None:
+        self.metrics["training/global_step"] = self.global_steps
+        self.metrics["training/epoch"] = getattr(self, "epoch", 0)
+        logger = getattr(self, "logger", None)
+        if logger is not None:
+            logger.log(data=self.metrics, step=self.global_steps)
+        self.global_steps += 1
 
     def _dump_generations(self, batch: DataProto, dump_path: str) -> None:
         os.makedirs(dump_path, exist_ok=True)
