@@ -89,6 +89,22 @@ def _sec_gemm_allreduce(rank, world, dev, ops, res):
         other = y.clone()
         dist.broadcast(other, src=0)
         same.append(bool(torch.equal(other, y)))
+    # the same sum as reduce-scatter in the epilogue + all-gather (what more than two ranks use for large calls): an odd
+    # number of rows (the last rank's share runs past the end), into a given output, then an even split written in place
+    for call, (M, give_out) in enumerate(((2999, False), (3000, True), (1501, True))):
+        g = torch.Generator(device="cpu").manual_seed(90 + call)
+        a_full = torch.randn(M, 1024, generator=g).bfloat16()
+        b_full = (torch.randn(1024, 1024, generator=g) * 0.05).bfloat16()
+        bias = torch.randn(1024, generator=g).bfloat16()
+        ks = slice(rank * 512, (rank + 1) * 512)
+        out = torch.full((M, 1024), 9.0, dtype=torch.bfloat16, device=dev) if give_out else None
+        y = fused(a_full[:, ks].contiguous().to(dev), b_full.to(dev)[:, ks], bias.to(dev), out=out, two_shot=True)
+        assert out is None or y is out
+        ref = a_full.float() @ b_full.float().t() + bias.float()
+        errs.append(((y.float().cpu() - ref).norm() / ref.norm()).item())
+        other = y.clone()
+        dist.broadcast(other, src=0)
+        same.append(bool(torch.equal(other, y)))
     res["gemm_ar_splitk_used"] = int(native.ops().gemm_suggest_splits(320, 1024, 4096)) if hasattr(native.ops(), "gemm_suggest_splits") else -1
     res["gemm_ar_err"] = max(errs)
     res["gemm_ar_identical"] = all(same)

@@ -101,15 +101,43 @@ class FusedRowParallelLinear:
         dist.barrier(group)  # flags are zero everywhere before anyone publishes epoch 1
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 b_mn: bool = False, scatter_rows: int = 0):
+                 b_mn: bool = False, scatter_rows: int = 0, two_shot: Optional[bool] = None):
         """``b_mn``: ``b`` is stored [K, N] (the input gradient of a column-parallel layer: ``dY_r @ W_r`` summed over ranks).
         ``scatter_rows`` > 0: reduce-scatter instead of all-reduce: returns this rank's ``[scatter_rows, N]`` slice of the
-        sum (rows ``rank * scatter_rows ...``; zero where the slice runs past the input's rows); every rank must own a row."""
+        sum (rows ``rank * scatter_rows ...``; zero where the slice runs past the input's rows); every rank must own a row.
+        ``two_shot``: reduce this rank's share of the rows in the epilogue, then all-gather the shares (see ``_two_shot``);
+        ``None`` picks it for large calls on more than two ranks."""
         from ..ops import native
 
         assert a.shape[0] <= self.max_rows and (b.shape[1] if b_mn else b.shape[0]) == self.n
+        M = a.shape[0]
+        if two_shot is None:
+            two_shot = self.world > 2 and M > 1024
+        if two_shot and scatter_rows == 0 and M >= self.world * self.world:
+            return self._two_shot(a, b, bias, out, b_mn)
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,
                                            self.splitk_ws, bool(b_mn), int(scatter_rows))
+
+    def _two_shot(self, a, b, bias, out, b_mn):
+        """All-reduce as reduce-scatter + all-gather. The one-kernel form has every rank pull the same tile from every peer:
+        (world - 1) x the output crosses each rank's link, which at 8 ranks costs more than the GEMM. Here a rank pulls and
+        sums only its ``1 / world`` of the rows inside the GEMM epilogue, and the bf16 shares are then exchanged by one
+        all-gather (in-switch multicast where the library uses it): 2 x (world - 1) / world of the output per link."""
+        from ..ops import native
+
+        M = a.shape[0]
+        rows = -(-M // self.world)
+        mine = native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank,
+                                           self.limit_s, None, None, bool(b_mn), rows)
+        direct = out is not None and rows * self.world == M and out.is_contiguous()
+        full = out if direct else torch.empty(rows * self.world, self.n, dtype=mine.dtype, device=mine.device)
+        dist.all_gather_into_tensor(full, mine, group=self.group)
+        if direct:
+            return out
+        if out is not None:
+            out.copy_(full[:M])
+            return out
+        return full[:M]
 
 
 class PeerShare:
