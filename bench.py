@@ -266,7 +266,10 @@ def main():
     ev = [(Event(), Event()) for _ in range(steps)]
     e_all0, e_all1 = Event(), Event()
     pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
-    host_scores = pin(torch.empty(args.prompts_per_gpu * args.n, dtype=torch.float32))
+    # a tensor x pipeline parallel replica feeds the same rows to all of its ranks: a rank then holds (and reads back) the
+    # replica's rows, and its tokens count once per replica
+    dup = max(1, args.train_tp * args.train_pp)
+    host_scores = pin(torch.empty(args.prompts_per_gpu * args.n * dup, dtype=torch.float32))
     tokens = h2d = d2h = 0
     reshard_s, phase_sum, grad_norms = 0.0, {}, []
 
@@ -275,7 +278,7 @@ def main():
         ms_dev = sum(ev[j][0].elapsed_time(ev[j][1]) for j in range(k))
         ms_all = e_all0.elapsed_time(e_all1)
         t = torch.tensor([ms_dev, ms_all], device=dev, dtype=torch.float64)
-        tok = torch.tensor([float(tokens)], device=dev, dtype=torch.float64)
+        tok = torch.tensor([float(tokens) / dup], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.all_reduce(tok)
