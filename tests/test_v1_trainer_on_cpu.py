@@ -160,3 +160,25 @@ def test_fit_step_runs_the_overridable_phases_in_order(monkeypatch):
     order.clear()
     t.train_step(next(iter(t.train_dataloader)))
     assert order == names[2:14] + ["_fit_collect_metrics"]
+
+
+def test_critic_token_budget_reaches_value_inference(monkeypatch):
+    """``critic.use_dynamic_bsz`` with ``forward_max_token_len_per_gpu`` splits ``compute_values`` into micro-batches under
+    the token budget (one micro-batch of the whole batch does not fit a GPU at the benchmark's size)."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from verl_b200.trainer.main_ppo import main
+
+    args = [a for a in ARGS if not a.startswith(("trainer.use_v1", "trainer.total_training_steps", "algorithm.adv_estimator",
+                                                  "actor_rollout_ref.actor.use_kl_loss"))]
+    t = main(args + ["trainer.use_v1=false", "trainer.total_training_steps=1", "algorithm.adv_estimator=gae",
+                     "actor_rollout_ref.actor.use_kl_loss=false", "critic.model.path=tiny-qwen2", "critic.ppo_mini_batch_size=4",
+                     "critic.use_dynamic_bsz=true", "critic.ppo_max_token_len_per_gpu=64", "critic.forward_max_token_len_per_gpu=56"])
+    eng = t.critic_wg._workers[0].engine
+    ec = eng.engine_config
+    assert ec.use_dynamic_bsz and ec.max_token_len_per_gpu == 64 and ec.infer_max_token_len_per_gpu == 56
+    data = {k: t.last_batch.batch[k] for k in ("input_ids", "attention_mask", "position_ids", "responses", "response_mask")}
+    parts = eng._micro_batches(dict(data), forward_only=True)
+    lens = [int(p["attention_mask"].sum()) for p in parts]
+    assert len(parts) >= 2 and sum(lens) == int(data["attention_mask"].sum()), lens
+    assert all(n <= 56 or p["input_ids"].shape[0] == 1 for n, p in zip(lens, parts)), lens
+    assert "critic/vf_loss" in t.metrics and t.last_batch.batch["values"].shape == (8, 12)

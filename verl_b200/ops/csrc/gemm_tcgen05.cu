@@ -145,6 +145,69 @@ struct GemmSmem {
   static constexpr int TOTAL = RING + 256 + 1024;  // barriers + alignment slack
 };
 
+// Pass B of the all-reduce epilogue for one warp's slab (32 rows x BN columns): sum the bf16 partials of all ranks in rank
+// order (+ bias) and store the rows that lie in [rs_lo, rs_hi). Lanes sweep the columns of one (BN = 256) or two
+// (BN = 128) rows at a time: the 16-byte pieces of a row are contiguous across lanes, so every peer read is a full 512-byte
+// (256-byte) burst over NVLink. A peer read costs microseconds of latency, so the loads of UNR row groups from ALL W ranks
+// are issued before the first is consumed: a slab costs 32 / (rows per group x UNR) dependent round trips, not that times
+// the number of ranks.
+template <int BN, int W, int UNR>
+__device__ __forceinline__ void ar_sum_slab(const GemmParams& p, long long half, int row0, int n0, int lane, int rs_lo, int rs_hi) {
+  static_assert(W <= AR_MAX_RANKS, "more ranks than pointer slots");
+  constexpr int LPR = BN / 8;    // lanes per row
+  constexpr int RPI = 32 / LPR;  // rows per row group
+  static_assert(32 % (RPI * UNR) == 0, "a slab is a whole number of batches");
+  const int col = n0 + (lane % LPR) * 8;
+  const bool col_ok = col < p.N;
+  float bias8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (p.bias != nullptr && col_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bias8[j] = __bfloat162float(p.bias[col + j]);
+  }
+#pragma unroll 1
+  for (int rr = 0; rr < 32; rr += RPI * UNR) {
+    uint4 v[W][UNR];
+#pragma unroll
+    for (int r = 0; r < W; ++r) {
+      if (r < p.ar_world) {
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.ar_part[r]);
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+          const int orow = row0 + rr + u * RPI + lane / LPR;
+          const bool ok = col_ok && orow < p.M && orow >= rs_lo && orow < rs_hi;
+          v[r][u] = ok ? __ldcg(reinterpret_cast<const uint4*>(src + half + static_cast<long long>(orow) * p.N + col))
+                       : make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int orow = row0 + rr + u * RPI + lane / LPR;
+      const bool ok = col_ok && orow < p.M && orow >= rs_lo && orow < rs_hi;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        if (r < p.ar_world) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[r][u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f2 = __bfloat1622float2(h[j]);
+            acc[2 * j] += f2.x;
+            acc[2 * j + 1] += f2.y;
+          }
+        }
+      }
+      if (!ok) continue;
+      uint4 o;
+      o.x = pack_bf16x2(acc[0] + bias8[0], acc[1] + bias8[1]);
+      o.y = pack_bf16x2(acc[2] + bias8[2], acc[3] + bias8[3]);
+      o.z = pack_bf16x2(acc[4] + bias8[4], acc[5] + bias8[5]);
+      o.w = pack_bf16x2(acc[6] + bias8[6], acc[7] + bias8[7]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow - rs_lo) * p.ldd + col) = o;
+    }
+  }
+}
+
 // Kernel body. FETCH adds copy warps that stage peer memory into local memory (see GemmParams::fetch_*).
 template <int BN, bool A_MN, bool B_MN, int STAGES, int EPI, bool FETCH>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmParams& p) {
@@ -707,62 +770,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         if (!peers_ok) {
           if (lane == 0) atomicExch(p.status, ST_TIMEOUT_EPILOGUE + 10);
         } else if (mine) {
-          // lanes sweep the columns of one (BN = 256) or two (BN = 128) rows at a time: 16-byte pieces of a row are
-          // contiguous across lanes, so every peer read is a full 512-byte (256-byte) burst over NVLink
-          constexpr int LPR = BN / 8;   // lanes per row
-          constexpr int RPI = 32 / LPR;  // rows per iteration
           const long long half = static_cast<long long>(ar_epoch_now & 1u) * p.ar_buf_elems;
-          const int col = n0 + (lane % LPR) * 8;
-          // eight row groups are fetched per round trip: a peer read costs microseconds of latency, so the loads of a
-          // rank are all issued before the first one is consumed
-          constexpr int UNR = 8;
-          const bool col_ok = col < p.N;
-#pragma unroll 1
-          for (int rr = 0; rr < 32; rr += RPI * UNR) {
-            long long off[UNR];
-            bool ok[UNR];
-            float acc8[UNR][8];
-#pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-              const int orow = m0 + q * 32 + rr + u * RPI + lane / LPR;
-              ok[u] = col_ok && orow < p.M && orow >= rs_lo && orow < rs_hi;
-              off[u] = half + static_cast<long long>(orow) * p.N + col;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc8[u][j] = 0.f;
-            }
-            for (int r = 0; r < p.ar_world; ++r) {
-              const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.ar_part[r]);
-              uint4 v[UNR];
-#pragma unroll
-              for (int u = 0; u < UNR; ++u) v[u] = ok[u] ? __ldcg(reinterpret_cast<const uint4*>(src + off[u])) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-              for (int u = 0; u < UNR; ++u) {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 f2 = __bfloat1622float2(h[j]);
-                  acc8[u][2 * j] += f2.x;
-                  acc8[u][2 * j + 1] += f2.y;
-                }
-              }
-            }
-            float bias8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (p.bias != nullptr && col_ok) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) bias8[j] = __bfloat162float(p.bias[col + j]);
-            }
-#pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-              if (!ok[u]) continue;
-              const int orow = m0 + q * 32 + rr + u * RPI + lane / LPR;
-              uint4 o;
-              o.x = pack_bf16x2(acc8[u][0] + bias8[0], acc8[u][1] + bias8[1]);
-              o.y = pack_bf16x2(acc8[u][2] + bias8[2], acc8[u][3] + bias8[3]);
-              o.z = pack_bf16x2(acc8[u][4] + bias8[4], acc8[u][5] + bias8[5]);
-              o.w = pack_bf16x2(acc8[u][6] + bias8[6], acc8[u][7] + bias8[7]);
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(orow - rs_lo) * p.ldd + col) = o;
-            }
-          }
+          // 16 sixteen-byte loads per lane are in flight per round trip whatever the group size (more would spill): more
+          // rows per round trip on few ranks, every rank's piece of fewer rows on many
+          if (p.ar_world <= 2) ar_sum_slab<BN, 2, 8>(p, half, m0 + q * 32, n0, lane, rs_lo, rs_hi);
+          else if (p.ar_world <= 4) ar_sum_slab<BN, 4, 4>(p, half, m0 + q * 32, n0, lane, rs_lo, rs_hi);
+          else ar_sum_slab<BN, AR_MAX_RANKS, 2>(p, half, m0 + q * 32, n0, lane, rs_lo, rs_hi);
         }
       }
     }

@@ -81,7 +81,7 @@ def main(argv=None):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.mean())
 
-    def report(name, shape, ms_fused, ms_nccl, flops=0.0, hbm_bytes=0.0, link_bytes=0.0):
+    def report(name, shape, ms_fused, ms_nccl, flops=0.0, hbm_bytes=0.0, link_bytes=0.0, **extra):
         floor_ms = max(flops / (pk["bf16_tflops"] * 1e9), hbm_bytes / (pk["hbm_gbs"] * 1e6), link_bytes / (NVLINK_GBS * 1e6))
         if rank == 0:
             print(json.dumps({"case": name, "world": world, "shape": shape, "ms_fused": round(ms_fused, 4),
@@ -89,7 +89,7 @@ def main(argv=None):
                               "speedup": None if ms_nccl is None else round(ms_nccl / ms_fused, 3),
                               "roofline_ms": round(floor_ms, 4), "frac_of_roofline": round(floor_ms / ms_fused, 3),
                               "link_gbs": round(link_bytes / ms_fused / 1e6, 1),
-                              "clocks": list(clock_log),
+                              "clocks": list(clock_log), **extra,
                               "denominators": f"{pk['bf16_tflops']} TFLOP/s, {pk['hbm_gbs']} GB/s {tag}; NVLink {NVLINK_GBS} GB/s per direction"}),
                   flush=True)
         clock_log.clear()
@@ -175,8 +175,25 @@ def main(argv=None):
                 F.gemm(x, w, out=y)
                 dist.all_reduce(y)
 
-            report("row_parallel_gemm_allreduce", [M, N, Kl], timed(fused), timed(nccl), flops=2.0 * M * N * Kl,
+            t_nccl = timed(nccl)
+            report("row_parallel_gemm_allreduce", [M, N, Kl], timed(fused), t_nccl, flops=2.0 * M * N * Kl,
                    hbm_bytes=2.0 * (M * Kl + N * Kl + 2 * M * N), link_bytes=2.0 * M * N * (world - 1))
+            if world > 2 and M > 1024:
+                # the two in-kernel forms on their own (the default above picks per call size and group size), each checked
+                # against the library formulation's result
+                nccl()
+                want_y = y.float().clone()
+                for name, flag, link in (("one_kernel", False, 2.0 * M * N * (world - 1)),
+                                         ("reduce_scatter_epilogue_then_allgather", True, 4.0 * M * N * (world - 1) / world)):
+                    def form(flag=flag):
+                        fl(x, w, None, out=y, two_shot=flag)
+
+                    y.zero_()
+                    form()
+                    err = ((y.float() - want_y).norm() / want_y.norm()).item()
+                    report(f"row_parallel_gemm_allreduce_{name}", [M, N, Kl], timed(form), t_nccl, flops=2.0 * M * N * Kl,
+                           hbm_bytes=2.0 * (M * Kl + N * Kl + 2 * M * N), link_bytes=link, rel_err_vs_library=round(err, 5),
+                           gemm_status=int(ops.gemm_status()))
             del fl
     if want("ag_gemm"):
         # fully sharded weight (equal slices on the ranks) gathered by the GEMM that consumes it, against all-gather + GEMM

@@ -9,6 +9,7 @@ carries the epoch flags of :func:`peer_barrier`.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -86,6 +87,8 @@ class FusedRowParallelLinear:
     def __init__(self, max_rows: int, n: int, device, group=None, limit_s: float = 20.0):
         self.limit_s = float(limit_s)
         self.group = group
+        # large calls on more than two ranks: GEMM + library all-reduce unless a form is asked for by name (``two_shot=``)
+        self.library_for_large = os.environ.get("VERL_B200_LARGE_ALLREDUCE", "library") == "library"
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.n, self.max_rows = int(n), int(max_rows)
@@ -111,8 +114,17 @@ class FusedRowParallelLinear:
 
         assert a.shape[0] <= self.max_rows and (b.shape[1] if b_mn else b.shape[0]) == self.n
         M = a.shape[0]
-        if two_shot is None:
-            two_shot = self.world > 2 and M > 1024
+        if two_shot is None and self.world > 2 and M > 1024 and scatter_rows == 0 and self.library_for_large:
+            # measured at 8 ranks (8192 x 3584 x 2368): GEMM + the library's in-switch all-reduce 0.37 - 0.42 ms, the
+            # reduce-scatter epilogue + all-gather 0.83 ms, the one-kernel form 1.02 ms: the in-kernel forms pull with plain
+            # peer loads and pay their latency per tile, the switch reduces in flight
+            from ..ops import functional as F
+
+            y = F.gemm(a, b, out=out, b_mn=bool(b_mn))
+            dist.all_reduce(y, group=self.group)
+            if bias is not None:
+                y.add_(bias)
+            return y
         if two_shot and scatter_rows == 0 and M >= self.world * self.world:
             return self._two_shot(a, b, bias, out, b_mn)
         return native.ops().gemm_allreduce(a, b, bias, self.part.ptrs, self.flags.ptrs, self.epoch, self.buf_elems, self.rank, self.limit_s, out,

@@ -178,6 +178,15 @@ class CriticWorker(TrainingWorker):
                 ec = omega_conf_to_dataclass(ec, FSDPEngineConfig)
             object.__setattr__(ec, "micro_batch_size_per_gpu", critic.get("ppo_micro_batch_size_per_gpu"))
             object.__setattr__(ec, "infer_micro_batch_size_per_gpu", critic.get("forward_micro_batch_size_per_gpu") or critic.get("ppo_micro_batch_size_per_gpu"))
+            # token-budgeted micro-batches for the update and for ``compute_values`` (``critic.use_dynamic_bsz``,
+            # ``ppo_max_token_len_per_gpu``, ``forward_max_token_len_per_gpu``: verl/workers/config/critic.py)
+            if critic.get("use_dynamic_bsz") is not None:
+                object.__setattr__(ec, "use_dynamic_bsz", bool(critic.get("use_dynamic_bsz")))
+            if critic.get("ppo_max_token_len_per_gpu"):
+                object.__setattr__(ec, "max_token_len_per_gpu", int(critic.get("ppo_max_token_len_per_gpu")))
+            fwd_budget = critic.get("forward_max_token_len_per_gpu") or critic.get("ppo_max_token_len_per_gpu")
+            if fwd_budget:
+                object.__setattr__(ec, "infer_max_token_len_per_gpu", int(fwd_budget))
             self.critic_config = critic
             config = TrainingWorkerConfig(model_type="value_model", model_config=mc, engine_config=ec,
                                           optimizer_config=omega_conf_to_dataclass(critic.get("optim"), OptimizerConfig),
