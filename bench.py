@@ -156,6 +156,8 @@ def build_config(args, world: int):
                "actor_rollout_ref.actor.clip_ratio=0.2", f"critic.model.path={args.model}", "critic.model.load_weights=false",
                f"critic.ppo_mini_batch_size={gbs}", "critic.use_dynamic_bsz=true", f"critic.ppo_max_token_len_per_gpu={args.max_token_len}",
                "critic.optim.lr=1e-5"]
+        if args.layers > 0:
+            ov += [f"+critic.model.override_config.num_hidden_layers={args.layers}"]
         if mp > 1:
             ov += ["critic@critic=megatron_critic", f"critic.megatron.tensor_model_parallel_size={args.train_tp}",
                    f"critic.megatron.pipeline_model_parallel_size={args.train_pp}"]
