@@ -80,6 +80,8 @@ class FSDPEngineConfig(EngineConfig):
     # limit of the device-side barriers around the fused optimizer step: ranks do not talk during gradient accumulation, so
     # it has to cover the skew a whole mini-batch can build up; when it runs out the step is skipped on every rank
     peer_barrier_timeout_s: float = 120.0
+    # option tree of the ``fsdp_turbo`` strategy (``workers/engine/native/turbo.py`` lists the keys that have an effect)
+    turbo_config: dict = field(default_factory=dict)
     strategy: str = "fsdp"
 
     def __post_init__(self):

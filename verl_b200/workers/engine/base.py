@@ -139,7 +139,7 @@ class EngineRegistry:
         return deco
 
     # backend names of the reference that have no engine of their own here: what they are served by, said once per name
-    ALIASES = {"veomni": "native", "torchtitan": "native", "automodel": "native", "fsdp_turbo": "native", "mindspeed": "mp"}
+    ALIASES = {"veomni": "native", "torchtitan": "native", "automodel": "native", "mindspeed": "mp"}
     _warned: set = set()
 
     @classmethod
@@ -154,6 +154,8 @@ class EngineRegistry:
             warnings.warn(f"engine backend '{backend}' has no implementation of its own in this framework: it runs on the "
                           f"'{cls.ALIASES[backend]}' engine ({'sharded data-parallel' if cls.ALIASES[backend] == 'native' else 'tensor x pipeline x expert parallel'}); "
                           f"options specific to {backend} are ignored", stacklevel=2)
+        if backend == "fsdp_turbo" and backend not in cls._engines.get(model_type, {}):
+            from .native import turbo  # noqa: F401  (registers the fully sharded, fused configuration of the native engine)
         if backend in ("megatron", "mp", "mindspeed") and backend not in cls._engines.get(model_type, {}):
             from . import mp  # noqa: F401  (registers the tensor x pipeline parallel engines)
         try:

@@ -1342,13 +1342,13 @@ class NativeEngine(BaseEngine):
                     torch.cuda.set_rng_state(st["cuda_rng"])
 
 
-@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "fsdp_turbo", "native", "veomni", "torchtitan", "automodel"],
+@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "native", "veomni", "torchtitan", "automodel"],
                          device=["cuda", "cpu"])
 class NativeEngineWithLMHead(NativeEngine):
     value_head = False
 
 
-@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "fsdp_turbo", "native", "veomni", "torchtitan", "automodel"],
+@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "native", "veomni", "torchtitan", "automodel"],
                          device=["cuda", "cpu"])
 class NativeEngineWithValueHead(NativeEngine):
     """Same trunk with a scalar head; ``model_output`` carries ``values`` [b, R] aligned with the responses."""

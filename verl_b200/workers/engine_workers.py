@@ -30,6 +30,7 @@ from .config import (ActorConfig, CheckpointConfig, FSDPActorConfig, FSDPEngineC
                      RolloutConfig, TrainingWorkerConfig)
 from .engine.base import EngineRegistry
 from .engine.native import engine as _native_engine  # noqa: F401  (registers the engines)
+from .engine.native import turbo as _turbo_engine  # noqa: F401  (registers the fsdp_turbo backend)
 from .utils.losses import ppo_loss, sft_loss, value_loss
 
 __all__ = ["TrainingWorker", "ActorRolloutRefWorker", "CriticWorker"]
