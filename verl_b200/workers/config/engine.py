@@ -120,7 +120,18 @@ class McoreEngineConfig(EngineConfig):
 
 @dataclass
 class VeOmniEngineConfig(FSDPEngineConfig):
+    """Option names of the reference's VeOmni backend (``verl/workers/config/engine.py:308-443``); translated onto the
+    engines of this framework by ``workers/engine/backends.py``."""
+
+    ulysses_parallel_size: int = 1
     expert_parallel_size: int = 1
+    enable_full_shard: bool = False
+    enable_fsdp_offload: bool = False
+    enable_reentrant: bool = False
+    init_device: str = "meta"
+    attn_implementation: str = "flash_attention_2"
+    moe_implementation: str = "fused"
+    activation_gpu_limit: float = 0.0
     strategy: str = "veomni"
 
     def __post_init__(self):
@@ -129,20 +140,45 @@ class VeOmniEngineConfig(FSDPEngineConfig):
 
 @dataclass
 class TorchtitanEngineConfig(EngineConfig):
+    """Option names of the reference's TorchTitan backend (``verl/workers/config/engine.py:461-523``)."""
+
+    wrap_policy: dict = field(default_factory=dict)
+    reshard_after_forward: str = "default"   # default | always | never
+    offload_policy: bool = False
+    data_parallel_size: int = 1
     data_parallel_shard_size: int = -1
     data_parallel_replicate_size: int = 1
     tensor_parallel_size: int = 1
     expert_parallel_size: int = 1
+    expert_tensor_parallel_size: int = 1
     pipeline_parallel_size: int = 1
     context_parallel_size: int = 1
+    attn_type: str = "flex"
+    activation_checkpoint: str = "selective"   # none | selective | full
+    max_seq_len: Optional[int] = None
     strategy: str = "torchtitan"
 
 
 @dataclass
 class AutomodelEngineConfig(EngineConfig):
+    """Option names of the reference's NeMo-Automodel backend (``verl/workers/config/engine.py:540-650``); the long names
+    are kept as synonyms of ``tp_size`` / ``cp_size`` / ``ep_size``."""
+
+    distributed_strategy: str = "fsdp2"
+    tp_size: int = 1
+    pp_size: int = 1
+    cp_size: int = 1
+    ep_size: int = 1
+    dp_replicate_size: int = 1
+    sequence_parallel: bool = False
+    activation_checkpointing: bool = False
     tensor_parallel_size: int = 1
     context_parallel_size: int = 1
     expert_parallel_size: int = 1
+    model_dtype: str = "fp32"
+    attn_implementation: str = "flash_attention_2"
+    backend_config: dict = field(default_factory=dict)
+    moe_config: dict = field(default_factory=dict)
     strategy: str = "automodel"
 
 

@@ -138,22 +138,17 @@ class EngineRegistry:
 
         return deco
 
-    # backend names of the reference that have no engine of their own here: what they are served by, said once per name
+    # backend names of the reference that have no runtime of their own here: ``new`` translates their option names onto
+    # one of the two engines (``backends.translate``); a bare class lookup gets the engine their default layout runs on
     ALIASES = {"veomni": "native", "torchtitan": "native", "automodel": "native", "mindspeed": "mp"}
-    _warned: set = set()
 
     @classmethod
     def get_engine_cls(cls, model_type: str, backend: str, device: Optional[str] = None):
         from ...utils.device import get_device_name
 
         device = device or get_device_name()
-        if backend in cls.ALIASES and backend not in cls._warned:
-            import warnings
-
-            cls._warned.add(backend)
-            warnings.warn(f"engine backend '{backend}' has no implementation of its own in this framework: it runs on the "
-                          f"'{cls.ALIASES[backend]}' engine ({'sharded data-parallel' if cls.ALIASES[backend] == 'native' else 'tensor x pipeline x expert parallel'}); "
-                          f"options specific to {backend} are ignored", stacklevel=2)
+        if backend not in cls._engines.get(model_type, {}) and backend not in ("megatron", "mp", "mindspeed"):
+            from .native import engine  # noqa: F401  (registers the sharded data-parallel engines)
         if backend == "fsdp_turbo" and backend not in cls._engines.get(model_type, {}):
             from .native import turbo  # noqa: F401  (registers the fully sharded, fused configuration of the native engine)
         if backend in ("megatron", "mp", "mindspeed") and backend not in cls._engines.get(model_type, {}):
@@ -167,4 +162,15 @@ class EngineRegistry:
     @classmethod
     def new(cls, model_type: str, backend: str, *args, **kwargs) -> BaseEngine:
         device = kwargs.pop("device", None)
+        from .backends import FOREIGN_BACKENDS, translate
+
+        if backend in FOREIGN_BACKENDS:
+            args = list(args)
+            ec = kwargs.get("engine_config", args[1] if len(args) > 1 else None)
+            if ec is not None:
+                backend, ec = translate(backend, ec)
+                if "engine_config" in kwargs or len(args) < 2:
+                    kwargs["engine_config"] = ec
+                else:
+                    args[1] = ec
         return cls.get_engine_cls(model_type, backend, device)(*args, **kwargs)
