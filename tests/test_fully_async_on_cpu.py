@@ -23,7 +23,7 @@ def test_metrics_aggregator_and_schedule_policies():
     agg.add_step_metrics({"a/mean": 1.0, "a/max": 1.0, "timing_s/gen": 2.0}, 1)
     agg.add_step_metrics({"a/mean": 4.0, "a/max": 3.0, "timing_s/gen": 1.0}, 3)
     m = agg.get_aggregated_metrics()
-    assert m == {"a/max": 3.0, "a/mean": 3.25, "timing_s/gen": 3.0}
+    assert m == {"a/max": 3.0, "a/mean": 2.5, "timing_s/gen": 3.0}  # plain mean over steps; weighting is opt-in by name
     log = []
     c = DynamicResourceController(DefaultDynamicSchedulePolicy(), elastic=2, add_fn=lambda k: log.append(+k), remove_fn=lambda k: log.append(-k))
     assert c.step(queue_size=0, required_samples=8, trainer_idle_s=5, trainer_step_s=5) == 1
@@ -46,6 +46,87 @@ def test_fully_async_trains_and_respects_staleness_budget(monkeypatch):
     assert r.max_samples_per_version() == 12  # 4 samples x 2 updates x (1 + 0.5)
     assert r.produced >= 16 and r.stats["pauses"] >= 1
     assert r.produced <= 16 + r.max_samples_per_version()  # never ran ahead by more than one budget
+    # the cycle's aggregated record: summed seconds, one utilisation ratio per side and the combined figure
+    agg = t.last_aggregated_metrics
+    assert 0.0 < agg["dynamic_resource/train_resource_utilization"] <= 1.0
+    assert 0.0 <= agg["dynamic_resource/rollout_resource_utilization"] <= 1.0
+    assert 0.0 <= agg["dynamic_resource/resource_utilization"] <= 1.0
+    assert abs(agg["fully_async/trainer/idle_ratio"] - agg["timing_s/gen"] / agg["timing_s/step"]) < 1e-9
+    assert agg["fully_async/param_version"] == 2 and agg["training/global_step"] == 4
+
+
+def test_metrics_aggregator_reduces_by_name_and_derives_cycle_figures():
+    from verl_b200.experimental.fully_async_policy.detach_utils import MetricsAggregator
+
+    a = MetricsAggregator(total_gpus=4, hybrid_gpus=2, standalone_gpus=2)
+    assert a.get_aggregated_metrics() == {}
+    rule = MetricsAggregator.rule
+    assert rule("timing_s/gen") == "sum" and rule("timing_s/agent_loop/tool_calls/max") == "max" and rule("perf/time_per_step") == "sum"
+    assert rule("critic/score/mean") == "mean" and rule("response_length/max") == "max" and rule("prompt_length/min") == "min"
+    assert rule("perf/total_num_tokens") == "sum" and rule("training/global_step") == "last" and rule("actor/pg_loss") == "mean"
+    assert rule("x/weighted_avg_thing") == "weighted"
+    steps = [
+        {"timing_s/step": 10.0, "timing_s/gen": 4.0, "timing_s/wait_for_enough_samples": 4.0, "perf/time_per_step": 10.0,
+         "perf/total_num_tokens": 4000, "perf/throughput": 1.0, "critic/score/mean": 0.2, "response_length/max": 50,
+         "global_seqlen/max": 900, "global_seqlen/min": 300, "global_seqlen/minmax_diff": 1, "training/global_step": 7,
+         "dynamic_resource/train_compute_time_s": 5.0, "dynamic_resource/train_allocated_time_s": 6.0, "x/weighted_avg_thing": 1.0,
+         "flag": True, "text": "ignored", "tensor": __import__("torch").tensor(2.0)},
+        {"timing_s/step": 30.0, "timing_s/gen": 6.0, "timing_s/wait_for_enough_samples": 6.0, "perf/time_per_step": 30.0,
+         "perf/total_num_tokens": 12000, "perf/throughput": 2.0, "critic/score/mean": 0.4, "response_length/max": 70,
+         "global_seqlen/max": 800, "global_seqlen/min": 200, "global_seqlen/minmax_diff": 1, "training/global_step": 8,
+         "dynamic_resource/train_compute_time_s": 13.0, "dynamic_resource/train_allocated_time_s": 24.0, "x/weighted_avg_thing": 4.0,
+         "tensor": __import__("torch").tensor(4.0)},
+    ]
+    a.add_step_metrics(steps[0], sample_count=1)
+    a.add_step_metrics(steps[1], sample_count=3)
+    assert a.get_current_stats()["step_count"] == 2 and a.get_current_stats()["total_samples"] == 4
+    out = a.get_aggregated_metrics(rollout_resource_utilization=0.5)
+    assert out["timing_s/step"] == 40.0 and out["critic/score/mean"] == pytest.approx(0.3) and out["response_length/max"] == 70
+    assert out["training/global_step"] == 8 and out["x/weighted_avg_thing"] == pytest.approx(3.25) and out["tensor"] == 3.0
+    assert "flag" not in out and "text" not in out
+    assert out["global_seqlen/minmax_diff"] == 900 - 200
+    assert out["perf/throughput"] == pytest.approx(16000 / (40.0 * 4))
+    assert out["fully_async/trainer/idle_ratio"] == pytest.approx(0.25)
+    u_train = 18.0 / 30.0
+    assert out["dynamic_resource/train_resource_utilization"] == pytest.approx(u_train)
+    x = 10.0 / 40.0
+    assert out["dynamic_resource/resource_utilization"] == pytest.approx(((1 - x) * 2 * u_train + (x * 2 + 2) * 0.5) / 4)
+    # without the rollouter's figure the combined one is not reported
+    assert "dynamic_resource/resource_utilization" not in a.get_aggregated_metrics()
+    a.reset()
+    assert a.step_count == 0 and a.get_aggregated_metrics() == {}
+
+
+def test_safe_create_task_keeps_and_reports_background_tasks(caplog):
+    import asyncio
+    import logging
+
+    from verl_b200.experimental.fully_async_policy.detach_utils import safe_create_task
+
+    async def ok():
+        return 1
+
+    async def boom():
+        raise RuntimeError("lost replica")
+
+    async def main():
+        held = set()
+        a = safe_create_task(ok(), "fine", held)
+        b = safe_create_task(boom(), "broken", held)
+        assert held == {a, b}
+        await asyncio.gather(a, b, return_exceptions=True)
+        await asyncio.sleep(0)
+        return held
+
+    with caplog.at_level(logging.ERROR):
+        loop = asyncio.new_event_loop()
+        try:
+            asyncio.set_event_loop(loop)
+            held = loop.run_until_complete(main())
+        finally:
+            asyncio.set_event_loop(None)
+            loop.close()
+    assert held == set() and any("broken" in r.getMessage() and "lost replica" in r.getMessage() for r in caplog.records)
 
 
 class _StepServer:

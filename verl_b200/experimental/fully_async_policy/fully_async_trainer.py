@@ -97,7 +97,9 @@ class FullyAsyncTrainer(PPOTrainer):
             set_version_fn=lambda v: (setattr(self, "_rollouter_step_timing", self.rollouter.update_param_version(v)),
                                       self._each_server("set_global_steps", v)))
         self._rollouter_step_timing: dict = {}
-        self.aggregator = MetricsAggregator()
+        # one pool: every GPU of the job switches between generation and training ("hybrid" in the utilisation formula)
+        n_gpus = int(self.config.trainer.get("n_gpus_per_node", 1) or 1) * int(self.config.trainer.get("nnodes", 1) or 1)
+        self.aggregator = MetricsAggregator(total_gpus=n_gpus, hybrid_gpus=n_gpus, standalone_gpus=0)
         self.local_updates = 0
 
     def _drive(self) -> None:
@@ -143,12 +145,26 @@ class FullyAsyncTrainer(PPOTrainer):
             metrics.update({"fully_async/staleness_span/mean": float(np.mean(spans)), "fully_async/staleness_span/max": float(np.max(spans)),
                             "fully_async/sample_age/mean": float(np.mean(age)), "fully_async/sample_age/max": float(np.max(age)),
                             "fully_async/queue_size": float(self.mq.get_queue_size())})
+            t_alloc = time.time()
             batch = self.learn_phase(batch, metrics, timing_raw)
             self.local_updates += 1
             if self.local_updates % self.trigger == 0:
                 self._fit_update_weights()
+            self._record_train_resource_utilization(time.time() - t_alloc)
+        # generation rests while this pool trains, so the time the trainer waited for samples IS the pool's generation turn
+        timing_raw["wait_for_enough_samples"] = timing_raw.get("gen", 0.0)
         metrics.update(self.rollouter.statistics())
         return self.finish_step(batch, metrics, timing_raw)
+
+    # phases of ``learn_phase`` that are training compute (the rest of a step's allocated time is hand-over and waiting)
+    _TRAIN_COMPUTE_TIMING_KEYS = ("reward", "old_log_prob", "ref", "values", "adv", "update_critic", "update_actor")
+
+    def _record_train_resource_utilization(self, allocated_time: float) -> None:
+        """Raw seconds, not a ratio: the aggregator sums both over the steps of a synchronisation cycle and divides once
+        (``dynamic_resource/train_resource_utilization``). Numerator: the training-compute phases; denominator: the wall
+        clock from the first of them to the end of the weight hand-over."""
+        self.metrics["dynamic_resource/train_compute_time_s"] = sum(self.timing_raw.get(k, 0.0) for k in self._TRAIN_COMPUTE_TIMING_KEYS)
+        self.metrics["dynamic_resource/train_allocated_time_s"] = float(allocated_time)
 
     def _fit_update_weights(self) -> None:
         """Push the weights to the rollouter through the parameter synchroniser and open a new parameter version (the
@@ -184,8 +200,10 @@ class FullyAsyncTrainer(PPOTrainer):
             metrics, _ = res
             self.aggregator.add_step_metrics(metrics, self.required_samples)
             if self.local_updates % self.trigger == 0:
-                agg = self.aggregator.get_aggregated_metrics()
+                agg = self.aggregator.get_aggregated_metrics(
+                    rollout_resource_utilization=(self._rollouter_step_timing or {}).get("dynamic_resource/rollout_resource_utilization"))
                 agg["training/global_step"] = self.global_steps
+                self.last_aggregated_metrics = agg
                 logger.log(data=agg, step=self.global_steps)
                 self.aggregator.reset()
             self.global_steps += 1
