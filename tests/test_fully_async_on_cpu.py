@@ -289,3 +289,59 @@ def test_rollouter_step_accounting_and_capacity_utilisation():
     assert abs(rec["fully_async/rollouter/active_time"] - 0.5) < 1e-6 and 0.7 < rec["fully_async/rollouter/idle_ratio"] < 0.8
     assert 0.0 <= rec["dynamic_resource/rollout_resource_utilization"] <= 1.0 and r.step_samples_history == [(1, 5)]
     assert r.statistics()["rollouter/max_concurrent_samples"] == 12
+
+
+def test_fully_async_checkpoint_keeps_queued_samples_and_inflight_prompts(monkeypatch, tmp_path):
+    """A run saves at the end of a synchronisation cycle; a second run resumes from it with the producer's counters, the
+    samples that were queued for the trainer and the prompts that were in flight (re-issued before any new prompt)."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    import os
+
+    import torch
+
+    from tests.test_v1_trainer_on_cpu import ARGS
+    from verl_b200.experimental.fully_async_policy.fully_async_main import main
+
+    base = [a for a in ARGS if not a.startswith(("trainer.resume_mode", "trainer.total_training_steps"))] + [
+        "+async_training.require_batches=1", "+async_training.trigger_parameter_sync_step=1", "+async_training.staleness_threshold=1.0",
+        f"trainer.default_local_dir={tmp_path}", "trainer.save_freq=2"]
+    base[-1] = "trainer.save_freq=1"
+    t1 = main(base + ["trainer.total_training_steps=1", "trainer.resume_mode=disable"])
+    folder = os.path.join(str(tmp_path), "global_step_1")
+    path = os.path.join(folder, "rollouter.pt")
+    sd = torch.load(path, weights_only=False)
+    own = torch.load(os.path.join(folder, "fully_async_trainer.pt"), weights_only=False)
+    assert own == {"local_updates": 1, "param_version": 1} and sd["param_version"] == 1
+    # the producer ran ahead of the trainer: eight groups were admitted, four were trained on, four wait in the queue
+    assert sd["produced"] == 8 and len(sd["queued"]) == 4 and sd["inflight_prompts"] == []
+    # make one of the queued groups an in-flight prompt instead, as if the checkpoint had caught it mid-generation
+    moved, _ = sd["queued"].pop()
+    sd["inflight_prompts"] = [dict(moved.prompt)]
+    sd["produced"] -= 1
+    torch.save(sd, path)
+    queued_ids = [s.sample_id for s, _ in sd["queued"]]
+    inflight_uids = [p["uid"] for p in sd["inflight_prompts"]]
+    assert len(queued_ids) == 3 and inflight_uids == [moved.uid]
+
+    # resume: look at the restored state before any training happens
+    from verl_b200.experimental.fully_async_policy import fully_async_trainer as fat
+
+    seen = {}
+    orig = fat.FullyAsyncTrainer._load_checkpoint
+
+    def spy(self):
+        step = orig(self)
+        seen.update(step=step, queued=[s.sample_id for s, _ in self.mq.snapshot()], replay=[p["uid"] for p in self.rollouter._replay],
+                    version=self.rollouter.param_version, local_updates=self.local_updates, produced=self.rollouter.produced,
+                    since_sync=self.rollouter.produced_since_sync)
+        return step
+
+    monkeypatch.setattr(fat.FullyAsyncTrainer, "_load_checkpoint", spy)
+    t2 = main(base + ["trainer.total_training_steps=2", "trainer.resume_mode=auto"])
+    assert seen["step"] == 1 and seen["queued"] == queued_ids and seen["replay"] == inflight_uids
+    assert seen["version"] == 1 and seen["local_updates"] == 1 and seen["produced"] == sd["produced"]
+    assert seen["since_sync"] == len(queued_ids)
+    assert t2.global_steps == 3 and t2.param_version == 2 and t2.local_updates == 2
+    # the fourth sample of the resumed step came from the re-issued prompt, admitted before any new one and not counted twice
+    assert not t2.rollouter._replay and t2.rollouter.produced == sd["produced"] + (t2.rollouter.submitted - sd["submitted"]) + 1
+    assert moved.uid in [u for u in t2.last_batch.non_tensor_batch["uid"]]

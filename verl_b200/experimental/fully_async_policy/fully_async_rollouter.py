@@ -49,6 +49,8 @@ class FullyAsyncRollouter:
         self.submitted = self.produced = self.produced_since_sync = 0
         self.paused = False
         self.running: dict[str, asyncio.Task] = {}
+        self._inflight_prompts: dict[str, dict] = {}   # what ``running`` was started from: a checkpoint re-issues these
+        self._replay: list[dict] = []                  # prompts restored from a checkpoint, served before new ones
         self.stats = {"pauses": 0, "failed": 0}
         # bookkeeping of the producer's step (the span between two weight syncs)
         self._per_replica = self.max_concurrent / max(1, self._num_replicas())  # concurrency one replica is worth
@@ -139,6 +141,7 @@ class FullyAsyncRollouter:
         sample = RolloutSample(sample_id=f"{uid}@{v0}", uid=uid, trajectories=good, prompt=prompt, param_version_start=v0,
                                param_version_end=self.param_version, processing_time=time.time() - t0, failed=bool(bad))
         self.running.pop(uid, None)
+        self._inflight_prompts.pop(uid, None)
         self._record_active_count()
         if good:
             self.mq.put_sample(sample, self.param_version)
@@ -157,17 +160,64 @@ class FullyAsyncRollouter:
                 if not self.running and self._idle_start <= self._step_start:
                     self._idle_start = time.time()   # nothing in flight and nothing may start: the replicas idle from here
                 break
-            got = self.prompt_source(1)
+            resumed = bool(self._replay)
+            got = [self._replay.pop(0)] if resumed else self.prompt_source(1)
             if not got:
                 break
             p = dict(got[0])
             p.setdefault("uid", uuid.uuid4().hex)
+            self._inflight_prompts[p["uid"]] = p
             self.running[p["uid"]] = asyncio.ensure_future(self._one_sample(p))
-            self.submitted += 1
+            self.submitted += 0 if resumed else 1   # a re-issued prompt was counted when it was first admitted
             started += 1
         if started:
             self._record_active_count()
         return started
+
+    # ---- checkpoint
+    def state_dict(self) -> dict:
+        """Everything a resumed run needs to lose no prompt: the counters, the finished samples still queued for the trainer
+        and the prompts whose trajectories were being generated (their partial output is not kept: they start again).
+        The reference saves the dataloader position only and loses both kinds
+        (``verl/experimental/fully_async_policy/fully_async_rollouter.py:655-670``)."""
+        return {"param_version": self.param_version, "submitted": self.submitted, "produced": self.produced,
+                "produced_since_sync": self.produced_since_sync, "completed_steps": self.completed_steps,
+                "stats": dict(self.stats), "step_samples_history": list(self.step_samples_history),
+                "inflight_prompts": [dict(p) for p in self._inflight_prompts.values()] + [dict(p) for p in self._replay],
+                "queued": self.mq.snapshot()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.param_version = int(sd.get("param_version", 0))
+        self.submitted, self.produced = int(sd.get("submitted", 0)), int(sd.get("produced", 0))
+        self.completed_steps = int(sd.get("completed_steps", 0))
+        self.stats.update(sd.get("stats", {}))
+        self.step_samples_history = [tuple(x) for x in sd.get("step_samples_history", [])]
+        self.mq.restore(sd.get("queued", []))
+        # queued samples were produced under older weights: they count against the staleness budget of the resumed version
+        self.produced_since_sync = self.mq.get_queue_size()
+        self._replay = [dict(p) for p in sd.get("inflight_prompts", [])]
+        self.paused = False
+
+    def save_checkpoint(self, folder: str) -> str:
+        import os
+
+        import torch
+
+        os.makedirs(folder, exist_ok=True)
+        path = os.path.join(folder, "rollouter.pt")
+        torch.save(self.state_dict(), path)
+        return path
+
+    def load_checkpoint(self, folder: str) -> bool:
+        import os
+
+        import torch
+
+        path = os.path.join(folder, "rollouter.pt")
+        if not os.path.exists(path):
+            return False
+        self.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
+        return True
 
     async def run(self, stop: Callable[[], bool], idle_sleep: float = 0.0) -> None:
         """Streaming main loop (for a dedicated event loop / thread)."""

@@ -13,6 +13,7 @@ Parity target: ``verl/experimental/fully_async_policy/fully_async_trainer.py`` (
 from __future__ import annotations
 
 import asyncio
+import os
 import time
 from typing import Any, Optional
 
@@ -181,6 +182,34 @@ class FullyAsyncTrainer(PPOTrainer):
     def step(self):
         return self.fit_step()
 
+    # ------------------------------------------------------------------ checkpoint
+    def _ckpt_folder(self, step: int) -> str:
+        t = self.config.trainer
+        if t.get("resume_mode", "auto") == "resume_path" and t.get("resume_from_path") and f"global_step_{step}" in str(t.get("resume_from_path")):
+            return str(t.get("resume_from_path"))
+        return os.path.join(str(t.default_local_dir), f"global_step_{step}")
+
+    def _save_checkpoint(self) -> None:
+        """Actor / dataloader as in the synchronous trainer, plus the producer's side: counters, samples still queued for the
+        trainer and the prompts that were in flight (``FullyAsyncRollouter.state_dict``)."""
+        super()._save_checkpoint()
+        self.rollouter.save_checkpoint(self._ckpt_folder(self.global_steps))
+        torch.save({"local_updates": self.local_updates, "param_version": self.param_version},
+                   os.path.join(self._ckpt_folder(self.global_steps), "fully_async_trainer.pt"))
+
+    def _load_checkpoint(self) -> int:
+        step = super()._load_checkpoint()
+        if step and hasattr(self, "rollouter"):
+            folder = self._ckpt_folder(step)
+            if self.rollouter.load_checkpoint(folder):
+                own = os.path.join(folder, "fully_async_trainer.pt")
+                if os.path.exists(own):
+                    st = torch.load(own, map_location="cpu", weights_only=False)
+                    self.local_updates, self.param_version = int(st["local_updates"]), int(st["param_version"])
+                self.rollouter.param_version = self.param_version
+                print(f"Resumed the rollouter: {self.mq.get_queue_size()} queued samples, {len(self.rollouter._replay)} prompts re-issued")
+        return step
+
     def fit(self) -> None:
         cfg = self.config
         logger = Tracking(project_name=cfg.trainer.get("project_name", "verl_b200"), experiment_name=cfg.trainer.get("experiment_name", "run"),
@@ -188,22 +217,25 @@ class FullyAsyncTrainer(PPOTrainer):
         if not hasattr(self, "replay_buffer"):
             self.init()
         self.global_steps = 0
-        self._load_checkpoint()
+        resumed = int(self._load_checkpoint() or 0)
         self._bind_step({}, {})
         super()._fit_update_weights()
         self._each_server("wake_up")
-        self.global_steps = 1
+        self.global_steps = resumed + 1
         while self.global_steps <= self.total_training_steps:
             res = self.fit_step()
             if res is None:
                 break
-            metrics, _ = res
+            metrics, timing_raw = res
             self.aggregator.add_step_metrics(metrics, self.required_samples)
             if self.local_updates % self.trigger == 0:
                 agg = self.aggregator.get_aggregated_metrics(
                     rollout_resource_utilization=(self._rollouter_step_timing or {}).get("dynamic_resource/rollout_resource_utilization"))
                 agg["training/global_step"] = self.global_steps
                 self.last_aggregated_metrics = agg
+                self.is_last_step = self.global_steps >= self.total_training_steps
+                self._bind_step(metrics, timing_raw)
+                self._fit_save_checkpoint()
                 logger.log(data=agg, step=self.global_steps)
                 self.aggregator.reset()
             self.global_steps += 1

@@ -74,6 +74,17 @@ class MessageQueue:
                     "dropped_samples": self.dropped_samples, "current_param_version": self.current_param_version,
                     "staleness_threshold": self.staleness_threshold, "max_queue_size": self.max_queue_size}
 
+    def snapshot(self) -> list:
+        """The queued ``(sample, parameter version)`` pairs, oldest first (for a checkpoint; the queue is left as it is)."""
+        with self._cond:
+            return list(self._q)
+
+    def restore(self, items: list) -> None:
+        """Put checkpointed pairs back in front of whatever is queued, oldest first."""
+        with self._cond:
+            self._q.extendleft(reversed([(s, int(v)) for s, v in items]))
+            self._cond.notify_all()
+
     def clear_queue(self) -> None:
         with self._cond:
             self._q.clear()
