@@ -221,6 +221,12 @@ class FullyAsyncTrainer(PPOTrainer):
         self._bind_step({}, {})
         super()._fit_update_weights()
         self._each_server("wake_up")
+        if self.val_reward_fn is not None and cfg.trainer.get("val_before_train", False):
+            val = self._validate()
+            if val:
+                logger.log(data=val, step=self.global_steps)
+            if cfg.trainer.get("val_only", False):
+                return
         self.global_steps = resumed + 1
         while self.global_steps <= self.total_training_steps:
             res = self.fit_step()
@@ -234,7 +240,8 @@ class FullyAsyncTrainer(PPOTrainer):
                 agg["training/global_step"] = self.global_steps
                 self.last_aggregated_metrics = agg
                 self.is_last_step = self.global_steps >= self.total_training_steps
-                self._bind_step(metrics, timing_raw)
+                self._bind_step(agg, timing_raw)
+                self._fit_validate()          # test_freq counts training steps; runs between two cycles, generation resting
                 self._fit_save_checkpoint()
                 logger.log(data=agg, step=self.global_steps)
                 self.aggregator.reset()
