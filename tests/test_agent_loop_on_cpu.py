@@ -186,3 +186,29 @@ def test_trajectory_info_greedy_rows_traces_and_performance_metrics():
     assert len(spans) == 2 and len({s["sample_index"] for s in spans}) == 1      # one dataset row traced: both of its repeats
     assert sorted(s["rollout_n"] for s in spans) == [0, 1] and all(s["step"] == 3 for s in spans)
     RolloutTraceConfig.reset()
+
+
+def test_expert_choices_of_the_rollout_land_on_the_padded_positions():
+    """Router replay from the rollout: per-trajectory records [tokens, layers, top-k] are placed on the padded
+    [prompt | response] positions; a trajectory without a record keeps zeros; a truncated prompt drops leading positions."""
+    from verl_b200.experimental.agent_loop.agent_loop import AgentLoopOutput, AgentLoopWorker
+
+    config = _cfg(P=4, R=3)
+    w = AgentLoopWorker(config, server_manager=None)
+
+    def rec(n_pos, base):
+        return (torch.arange(n_pos * 2 * 2).reshape(n_pos, 2, 2) + base).to(torch.int32)
+
+    outs = [AgentLoopOutput(prompt_ids=[5, 6], response_ids=[7, 8, 9], response_mask=[1, 1, 1], routed_experts=rec(4, 100)),
+            AgentLoopOutput(prompt_ids=[1, 2, 3, 4, 5, 6], response_ids=[7], response_mask=[1], routed_experts=rec(6, 200)),
+            AgentLoopOutput(prompt_ids=[5], response_ids=[7, 8], response_mask=[1, 1])]
+    out = w._postprocess(outs, DataProto(meta_info={"pad_token_id": 0}))
+    r = out.batch["routed_experts"]
+    assert r.shape == (3, 7, 2, 2) and r.dtype == torch.int32
+    # row 0: two prompt tokens sit at positions 2..3, responses from 4; four recorded positions (the last generated token never
+    # went through the rollout model)
+    assert torch.equal(r[0, 2:6], rec(4, 100)) and int(r[0, :2].abs().sum()) == 0 and int(r[0, 6].abs().sum()) == 0
+    # row 1: the prompt was cut to its last four tokens, so the first two recorded positions go with it
+    assert torch.equal(out.batch["prompts"][1], torch.tensor([3, 4, 5, 6])) and torch.equal(r[1, 0:4], rec(6, 200)[2:6])
+    assert int(r[2].abs().sum()) == 0
+    assert "routed_experts" not in w._postprocess(outs[2:], DataProto(meta_info={"pad_token_id": 0})).batch.keys()
