@@ -68,3 +68,50 @@ def test_teacher_servers_batch_requests_and_route_by_key():
     lg = models[0].forward_logits(PackedBatch.from_lengths(torch.tensor([5, 6, 7, 8, 9, 10, 11]), [7])).float()
     v, i = torch.topk(torch.log_softmax(lg, -1)[2:6], 4, -1)
     assert torch.equal(outs[0]["teacher_ids"][:4], i) and torch.allclose(outs[0]["teacher_logprobs"][:4], v, atol=1e-5)
+
+
+def test_agent_loop_attaches_teacher_records_to_sampled_trajectories_only():
+    """With a teacher manager the agent-loop worker asks the teacher picked by the sample's routing field for top-k
+    log-probs of every sampled trajectory and batches them as [b, R, k]; validation batches carry none."""
+    from verl_b200 import DataProto
+    from verl_b200.experimental.agent_loop import AgentLoopManager
+    from verl_b200.utils.config import DictConfig
+    from verl_b200.workers.rollout.llm_server import LLMServerManager
+    from verl_b200.workers.rollout.native.engine import RolloutEngine
+    import numpy as np
+
+    cfg = get_preset("tiny-qwen2")
+    teachers = {}
+    for name, seed in (("math", 1), ("code", 2)):
+        P = FlatParams(cfg, dtype=torch.float32)
+        P.init_weights(seed=seed, std=0.1)
+        teachers[name] = TeacherModelManager.from_models(name, [DecoderModel(cfg, P)], topk=4)
+    tm = AsyncTeacherLLMServerManager(MultiTeacherModelManager(teachers), response_length=6)
+    config = DictConfig({"distillation": {"enabled": True, "teacher_key": "domain"},
+                         "actor_rollout_ref": {"rollout": {"name": "native", "prompt_length": 8, "response_length": 6, "temperature": 1.0,
+                                                           "top_p": 1.0, "top_k": -1, "do_sample": True, "calculate_log_probs": True,
+                                                           "tensor_model_parallel_size": 1, "agent": {"num_workers": 1},
+                                                           "val_kwargs": {"temperature": 0.0, "do_sample": False}}}})
+    S = FlatParams(cfg, dtype=torch.float32)
+    S.init_weights(seed=3, std=0.1)
+    eng = RolloutEngine(cfg, S, max_num_seqs=4, max_model_len=64, block_size=8, sync_interval=2, eos_token_id=-1)
+
+    async def go(validate):
+        mgr = await LLMServerManager.create(config.actor_rollout_ref.rollout, engines=[eng], model_config=None)
+        alm = AgentLoopManager(config, mgr, teacher_server_manager=tm)
+        ids = torch.randint(3, 500, (4, 8))
+        batch = DataProto.from_dict(tensors={"input_ids": ids, "attention_mask": torch.ones(4, 8, dtype=torch.int64)},
+                                    non_tensors={"domain": np.array(["math", "code", "math", "other"], dtype=object)},
+                                    meta_info={"temperature": 1.0, "validate": validate})
+        return await alm.generate_sequences_async(batch)
+
+    out = asyncio.run(go(False))
+    ti, tl = out.batch["teacher_ids"], out.batch["teacher_logprobs"]
+    assert ti.shape == (4, 6, 4) and tl.shape == (4, 6, 4) and (tl <= 0).all()
+    assert "teacher_ids" not in out.non_tensor_batch
+    # row 1 was scored by the other teacher: re-scoring its tokens with each teacher tells which one answered
+    seq = out.batch["input_ids"][1].tolist()
+    for name, same in (("code", True), ("math", False)):
+        ref = asyncio.run(AsyncTeacherLLMServerManager(MultiTeacherModelManager(teachers), 6).compute_teacher_logprobs("x", seq[:8], seq[8:], name))
+        assert torch.allclose(ref["teacher_logprobs"], tl[1], atol=1e-5) == same
+    assert "teacher_ids" not in asyncio.run(go(True)).batch.keys()
