@@ -1,4 +1,5 @@
 """Distillation: forward-KL top-k loss against a dense reference, hidden-state path, teacher batching and routing."""
+import pytest
 import asyncio
 
 import torch
@@ -34,7 +35,7 @@ def test_hidden_path_and_scalar_loss_backward():
     assert torch.allclose(lq, ref, atol=1e-5)
     lp_t = torch.log_softmax(torch.randn(7, 4), -1)
     data = {"teacher_logprobs": lp_t.view(1, 7, 4), "teacher_ids": ids.view(1, 7, 4), "response_mask": torch.ones(1, 7)}
-    dc = DistillationConfig(enabled=True)
+    dc = DistillationConfig(enabled=True, distillation_loss=DistillationLossConfig(loss_mode="forward_kl_topk"))
     loss, m = distillation_loss({"loss_agg_mode": "token-mean"}, dc, {"topk_log_probs": lq.view(1, 7, 4)}, data)
     loss.backward()
     assert h.grad.abs().sum() > 0 and "distillation/loss_max" in m and "distillation/student_mass" in m
@@ -115,3 +116,26 @@ def test_agent_loop_attaches_teacher_records_to_sampled_trajectories_only():
         ref = asyncio.run(AsyncTeacherLLMServerManager(MultiTeacherModelManager(teachers), 6).compute_teacher_logprobs("x", seq[:8], seq[8:], name))
         assert torch.allclose(ref["teacher_logprobs"], tl[1], atol=1e-5) == same
     assert "teacher_ids" not in asyncio.run(go(True)).batch.keys()
+
+
+def test_on_policy_distillation_end_to_end_through_the_trainer(monkeypatch):
+    """``distillation.enabled`` builds the teacher, scores every trajectory with the sampled token's teacher log-prob and
+    trains the actor on task loss + k3 term; with ``use_task_rewards=false`` the distillation term alone drives the update."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    from tests.test_v1_trainer_on_cpu import ARGS
+    from verl_b200.trainer.main_ppo import main
+
+    args = [a for a in ARGS if not a.startswith(("trainer.use_v1", "trainer.total_training_steps"))] + [
+        "trainer.use_v1=false", "trainer.total_training_steps=1", "distillation.enabled=true",
+        "distillation.teacher_models.teacher_model.model_path=tiny-qwen2"]
+    t = main(args)
+    b = t.last_batch.batch
+    assert b["teacher_logprobs"].shape == (8, 12, 1) and b["teacher_ids"].shape == (8, 12, 1)
+    m = b["response_mask"].bool()
+    assert torch.equal(b["teacher_ids"][..., 0][m], b["responses"][m])          # the record is about the sampled tokens
+    assert (b["teacher_logprobs"][..., 0][m] < 0).all() and (b["teacher_logprobs"][..., 0][~m] == 0).all()
+    assert t.metrics["actor/distillation/loss"] > 0 and "actor/pg_loss" in t.metrics and "timing_s/teacher" in t.metrics
+    t2 = main(args + ["distillation.distillation_loss.use_task_rewards=false"])
+    assert t2.metrics["actor/distillation/loss"] > 0 and "actor/pg_loss" not in t2.metrics and t2.metrics["actor/grad_norm"] > 0
+    with pytest.raises(NotImplementedError, match="forward_kl_topk"):
+        main(args + ["distillation.distillation_loss.loss_mode=forward_kl_topk"])

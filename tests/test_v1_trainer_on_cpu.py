@@ -135,7 +135,8 @@ def test_fit_step_runs_the_overridable_phases_in_order(monkeypatch):
     assert t.global_steps == 2
     order = []
     names = ["_fit_prepare_step", "_fit_start_profile", "_fit_get_batch", "_fit_generate", "_fit_balance", "_fit_compute_reward",
-             "_fit_compute_log_prob", "_fit_compute_ref_log_prob", "_fit_compute_critic", "_fit_compute_advantage",
+             "_fit_compute_log_prob", "_fit_compute_ref_log_prob", "_fit_compute_critic", "_fit_compute_teacher_logprobs",
+             "_fit_compute_advantage",
              "_fit_update_critic", "_fit_update_actor", "_fit_update_weights", "_fit_dump_data", "_fit_validate",
              "_fit_save_checkpoint", "_fit_stop_profile", "_fit_collect_metrics", "_fit_experimental", "_fit_postprocess_step"]
     for n in names:
@@ -159,7 +160,7 @@ def test_fit_step_runs_the_overridable_phases_in_order(monkeypatch):
     # the coarse phases used by the benchmark and the asynchronous trainers are the same methods, grouped
     order.clear()
     t.train_step(next(iter(t.train_dataloader)))
-    assert order == names[2:14] + ["_fit_collect_metrics"]
+    assert order == names[2:15] + ["_fit_collect_metrics"]
 
 
 def test_critic_token_budget_reaches_value_inference(monkeypatch):

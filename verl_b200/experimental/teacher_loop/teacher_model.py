@@ -32,7 +32,8 @@ class TeacherServer:
         self.num_forwards = 0
 
     async def compute_topk_logprobs(self, token_ids: list[int], request_id: str = "") -> tuple[torch.Tensor, torch.Tensor]:
-        """(ids [len-1, k] int64, logprobs [len-1, k] fp32) on CPU: row ``t`` is the teacher's prediction of token ``t+1``."""
+        """(ids [len-1, k] int64, logprobs [len-1, k] fp32) on CPU: row ``t`` is the teacher's prediction of token ``t+1``
+        (its ``k`` most likely tokens; with ``topk=0`` one column: token ``t+1`` itself and its log-prob)."""
         fut = asyncio.get_running_loop().create_future()
         self._pending.append((list(token_ids), fut))
         if self._task is None:
@@ -69,11 +70,18 @@ class TeacherServer:
         hidden = self.model.forward_hidden(pb)
         W = self.model.params.lm_head_weight  # [V, H]
         ids_l, lps_l = [], []
+        # topk == 0: the log-prob of the token that actually follows (what the sampled-token KL estimators need); the last row
+        # of every sequence has no successor and is cut below, so the roll across sequence boundaries is harmless
+        nxt = torch.roll(flat, -1)
         for lo in range(0, hidden.size(0), self.chunk):
             h = hidden[lo : lo + self.chunk]
             logits = (h @ W.t()).float()
             lp = torch.log_softmax(logits, -1)
-            v, i = torch.topk(lp, min(self.topk, lp.size(-1)), dim=-1)
+            if self.topk <= 0:
+                i = nxt[lo : lo + self.chunk, None]
+                v = lp.gather(-1, i)
+            else:
+                v, i = torch.topk(lp, min(self.topk, lp.size(-1)), dim=-1)
             ids_l.append(i)
             lps_l.append(v)
         ids, lps = torch.cat(ids_l, 0).cpu(), torch.cat(lps_l, 0).cpu()

@@ -27,13 +27,15 @@ from ..ppo.core_algos import agg_loss, get_policy_loss_fn, kl_penalty
 
 __all__ = ["DistillationLossConfig", "DistillationConfig", "DistillationLossSettings", "register_distillation_loss",
            "get_distillation_loss_fn", "get_distillation_loss_settings", "is_distillation_enabled", "distillation_loss",
-           "compute_forward_kl_topk", "student_topk_log_probs", "kl_divergence"]
+           "compute_forward_kl_topk", "student_topk_log_probs", "kl_divergence", "distillation_ppo_loss"]
 
 
 @dataclass
 class DistillationLossConfig(BaseConfig):
-    loss_mode: str = "forward_kl_topk"
-    topk: int = 64
+    loss_mode: str = "k3"              # k1 | k2 | k3 | abs | mse | low_var_kl (sampled-token estimators) | forward_kl_topk
+    topk: int = 32
+    use_task_rewards: bool = True      # False: the task's policy-gradient loss is dropped, distillation alone trains the student
+    distillation_loss_coef: float = 1.0  # weight of the distillation term beside the task loss
     use_tail_term: bool = False        # add the KL term of the mass outside the top-k support
     log_prob_min_clamp: Optional[float] = -10.0
     loss_max_clamp: Optional[float] = 10.0
@@ -52,6 +54,10 @@ class DistillationConfig(BaseConfig):
     enabled: bool = False
     num_teachers: int = 1
     teacher_key: str = "data_source"   # non-tensor field that routes a sample to one of several teachers
+    # name -> {key: value of teacher_key served by this teacher (null = default), model_path, num_replicas}
+    teacher_models: dict = field(default_factory=dict)
+    n_gpus_per_node: int = 8
+    nnodes: int = 0                    # 0: the teachers share the trainer's GPUs
     distillation_loss: DistillationLossConfig = field(default_factory=DistillationLossConfig)
 
 
@@ -157,6 +163,32 @@ def _reverse_kl_estimator(config, distillation_config, model_output: dict, data:
     loss = kl_penalty(logp_s, logp_t, mode)
     m = data["response_mask"].bool()
     return loss, {"distillation/teacher_logprob": logp_t[m].mean().item()}
+
+
+def distillation_ppo_loss(config, distillation_config: DistillationConfig, model_output: dict, data: dict, dp_group=None):
+    """The actor's loss under on-policy distillation: task (PPO / GRPO) loss and distillation term combined.
+
+    * ``use_task_rewards`` and ``use_policy_gradient`` both off: only the distillation term (the policy loss is not even
+      computed);
+    * ``use_task_rewards`` off, ``use_policy_gradient`` on: the policy loss is computed for its metrics and dropped, the
+      distillation term (itself a policy-gradient loss with ``-distillation loss`` as advantage) has weight 1;
+    * ``use_task_rewards`` on: ``task loss + distillation_loss_coef * distillation term``.
+
+    Parity target: ``verl/trainer/distillation/losses.py:165-227``."""
+    from ...workers.utils.losses import ppo_loss
+
+    lc = distillation_config.distillation_loss
+    d_loss, d_metrics = distillation_loss(config, distillation_config, model_output, data)
+    if not lc.use_task_rewards and not lc.use_policy_gradient:
+        loss, metrics = 0.0, {}
+    else:
+        loss, metrics = ppo_loss(config, model_output, data, dp_group)
+        if not lc.use_task_rewards:
+            loss = 0.0
+    metrics = dict(metrics)
+    metrics.update(d_metrics)
+    coef = float(lc.distillation_loss_coef) if lc.use_task_rewards else 1.0
+    return loss + d_loss * coef, metrics
 
 
 def distillation_loss(config, distillation_config: DistillationConfig, model_output: dict, data: dict) -> tuple[torch.Tensor, dict[str, Any]]:

@@ -314,9 +314,13 @@ class RayPPOTrainer:
         actor_cls = self.role_worker_mapping.get(Role.ActorRollout) or self.role_worker_mapping.get(Role.ActorRolloutRef)
         if actor_cls is None:
             from ...workers.engine_workers import ActorRolloutRefWorker as actor_cls
-        self.actor_rollout_wg = self.ray_worker_group_cls(pool, ClassWithInitArgs(actor_cls, config=cfg.actor_rollout_ref, role=role),
+        from .utils import need_teacher_policy
+
+        extra = {"distillation_config": cfg.get("distillation")} if need_teacher_policy(cfg) else {}
+        self.actor_rollout_wg = self.ray_worker_group_cls(pool, ClassWithInitArgs(actor_cls, config=cfg.actor_rollout_ref, role=role, **extra),
                                                           **self.worker_group_kwargs)
         self.actor_rollout_wg.init_model()
+        self.teacher_server_manager = self._build_teachers() if need_teacher_policy(cfg) else None
         self.ref_policy_wg = self.actor_rollout_wg
         self.ref_in_actor = True
         self.critic_wg = None
@@ -329,6 +333,76 @@ class RayPPOTrainer:
             self.critic_wg = self.ray_worker_group_cls(cpool, ClassWithInitArgs(critic_cls, config=cfg.critic), **self.worker_group_kwargs)
             self.critic_wg.init_model()
         self.async_rollout_mode = False
+
+    def _build_teachers(self):
+        """Teacher models of on-policy distillation, colocated with the trainer: one frozen decoder per entry of
+        ``distillation.teacher_models`` (``model_path``: a checkpoint directory or a preset name; ``key``: the value of
+        ``distillation.teacher_key`` this teacher serves, the first entry is the default). They answer with the log-prob of
+        the sampled token (estimator losses) or their top-k (``forward_kl_topk``).
+        Parity target: ``verl/trainer/ppo/ray_trainer.py:925-940`` and ``verl/experimental/teacher_loop/teacher_model.py``."""
+        from ...experimental.teacher_loop import AsyncTeacherLLMServerManager, MultiTeacherModelManager, TeacherModelManager
+        from ...models import FlatParams
+        from ...models.config import ModelConfig, get_preset
+        from ...models.decoder import DecoderModel
+        from ...utils.device import get_device_name
+        from ..distillation.losses import get_distillation_loss_settings
+
+        dc = self.config.distillation
+        lc = dc.get("distillation_loss") or {}
+        topk = int(lc.get("topk", 32) or 32) if get_distillation_loss_settings(str(lc.get("loss_mode", "k3"))).use_topk else 0
+        dev = torch.device("cuda", torch.cuda.current_device()) if get_device_name() == "cuda" else torch.device("cpu")
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        managers = {}
+        for name, tc in (dc.get("teacher_models") or {}).items():
+            path = tc.get("model_path")
+            if not path:
+                continue
+            if os.path.isdir(str(path)):
+                from ...utils.model import load_hf_weights_into
+
+                arch = ModelConfig.from_pretrained(str(path))
+                params = FlatParams(arch, dtype=dtype, device=dev)
+                load_hf_weights_into(params, str(path))
+            else:
+                arch = get_preset(str(path))
+                params = FlatParams(arch, dtype=dtype, device=dev)
+                params.init_weights(seed=int(tc.get("seed", 1234)))
+            n = max(1, int(tc.get("num_replicas", 1) or 1))
+            managers[str(tc.get("key") or name)] = TeacherModelManager.from_models(str(tc.get("key") or name), [DecoderModel(arch, params)] * n, topk=topk)
+        if not managers:
+            raise ValueError("distillation.enabled needs at least one distillation.teacher_models.<name>.model_path")
+        rc = self.config.actor_rollout_ref.rollout
+        return AsyncTeacherLLMServerManager(MultiTeacherModelManager(managers), int(self.config.data.max_response_length),
+                                            int(getattr(self.tokenizer, "pad_token_id", 0) or 0))
+
+    def _fit_compute_teacher_logprobs(self, batch: DataProto) -> DataProto:
+        """On-policy distillation: the teachers' record for every trajectory of the batch, unless the rollout side attached it
+        already (the agent loop does, trajectory by trajectory)."""
+        if self.teacher_server_manager is None or "teacher_logprobs" in batch.batch.keys():
+            return batch
+        import asyncio
+
+        with marked_timer("teacher", self.timing_raw, color="purple"):
+            ids, am = batch.batch["input_ids"].cpu(), batch.batch["attention_mask"].cpu().bool()
+            P = ids.shape[1] - batch.batch["responses"].shape[1]
+            key = str(self.config.distillation.get("teacher_key", "data_source"))
+            routes = batch.non_tensor_batch.get(key)
+
+            async def go():
+                return await asyncio.gather(*[
+                    self.teacher_server_manager.compute_teacher_logprobs(
+                        f"t{self.global_steps}-{i}", ids[i, :P][am[i, :P]].tolist(), ids[i, P:][am[i, P:]].tolist(),
+                        routing_key=None if routes is None else routes[i]) for i in range(len(batch))])
+
+            loop = asyncio.new_event_loop()
+            try:
+                got = loop.run_until_complete(go())
+            finally:
+                loop.close()
+            dev = batch.batch["input_ids"].device
+            batch.batch["teacher_ids"] = torch.stack([g["teacher_ids"] for g in got]).to(dev)
+            batch.batch["teacher_logprobs"] = torch.stack([g["teacher_logprobs"] for g in got]).to(dev)
+        return batch
 
     # ------------------------------------------------------------------------------------ checkpoint
     def _save_checkpoint(self) -> None:
@@ -549,6 +623,7 @@ class RayPPOTrainer:
             batch = self._fit_compute_log_prob(batch)
             batch = self._fit_compute_ref_log_prob(batch)
             batch = self._fit_compute_critic(batch)
+            batch = self._fit_compute_teacher_logprobs(batch)
             batch = self._fit_compute_advantage(batch)
             batch = self._fit_update_critic(batch)
             batch = self._fit_update_actor(batch)
@@ -571,7 +646,8 @@ class RayPPOTrainer:
         """Reward -> old/ref log-probs (-> values) -> advantages -> critic/actor updates on a generated batch."""
         self._bind_step(metrics, timing_raw)
         for phase in (self._fit_balance, self._fit_compute_reward, self._fit_compute_log_prob, self._fit_compute_ref_log_prob,
-                      self._fit_compute_critic, self._fit_compute_advantage, self._fit_update_critic, self._fit_update_actor):
+                      self._fit_compute_critic, self._fit_compute_teacher_logprobs, self._fit_compute_advantage, self._fit_update_critic,
+                      self._fit_update_actor):
             batch = phase(batch)
         return batch
 

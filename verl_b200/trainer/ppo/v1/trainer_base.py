@@ -89,7 +89,8 @@ class PPOTrainer(RayPPOTrainer):
         self._setup_rollout()
         self.replay_buffer = self._build_replay_buffer()
         self.worker_tq = AgentLoopWorkerTQ(self.config, self.server_manager.client(), self.tokenizer, None,
-                                           replay_buffer=self.replay_buffer, version_fn=lambda: self.param_version)
+                                           replay_buffer=self.replay_buffer, version_fn=lambda: self.param_version,
+                                           teacher_server_manager=getattr(self, "teacher_server_manager", None))
         self.param_version = 0
         self._tasks: set = set()
         self._prompt_iter = None

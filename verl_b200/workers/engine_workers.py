@@ -218,11 +218,13 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
 
     ``role`` selects which parts exist: ``actor``, ``rollout``, ``ref``, ``actor_rollout``, ``actor_rollout_ref``."""
 
-    def __init__(self, config, role: str = "actor_rollout_ref", **kwargs):
+    def __init__(self, config, role: str = "actor_rollout_ref", distillation_config=None, **kwargs):
         Worker.__init__(self)
         DistProfilerExtension.__init__(self, None)
         self.config = config
         self.role = role
+        # on-policy distillation: the actor's loss becomes task loss + distillation term (verl/workers/engine_workers.py:462-467)
+        self.distillation_config = distillation_config
         self._is_actor = "actor" in role
         self._is_rollout = "rollout" in role
         self._is_ref = "ref" in role
@@ -272,6 +274,23 @@ class ActorRolloutRefWorker(Worker, DistProfilerExtension):
                                             optimizer_config=ac.optim, checkpoint_config=ac.checkpoint)
             self.actor.initialize()
             self.actor_loss = partial(ppo_loss, ac)
+            dc = self.distillation_config
+            if dc is not None and bool(dc.get("enabled", False) if hasattr(dc, "get") else getattr(dc, "enabled", False)):
+                from ..trainer.distillation.losses import (DistillationConfig, DistillationLossConfig, distillation_ppo_loss,
+                                                           get_distillation_loss_settings)
+
+                if not isinstance(dc, DistillationConfig):
+                    lc = dc.get("distillation_loss") or {}
+                    known = DistillationLossConfig.__dataclass_fields__
+                    dc = DistillationConfig(enabled=True, teacher_key=str(dc.get("teacher_key", "data_source")),
+                                            distillation_loss=DistillationLossConfig(**{k: v for k, v in dict(lc).items() if k in known}))
+                if get_distillation_loss_settings(dc.distillation_loss.loss_mode).use_topk:
+                    raise NotImplementedError(
+                        "distillation_loss.loss_mode=forward_kl_topk needs the student's log-probs on the teacher's top-k ids, "
+                        "which this engine's fused LM-head kernel does not return; use one of the sampled-token estimators "
+                        "(k1, k2, k3, abs, mse, low_var_kl)")
+                self.distillation_config = dc
+                self.actor_loss = partial(distillation_ppo_loss, ac, dc)
             # the ranks of a sequence-parallel block see the same prompts: they split the generation work among them
             self._sp_replica = getattr(self.actor, "sp_size", 1) > 1
         if self._is_ref:
