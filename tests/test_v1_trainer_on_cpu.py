@@ -183,3 +183,80 @@ def test_critic_token_budget_reaches_value_inference(monkeypatch):
     assert len(parts) >= 2 and sum(lens) == int(data["attention_mask"].sum()), lens
     assert all(n <= 56 or p["input_ids"].shape[0] == 1 for n, p in zip(lens, parts)), lens
     assert "critic/vf_loss" in t.metrics and t.last_batch.batch["values"].shape == (8, 12)
+
+
+def test_group_relative_advantage_over_sessions_with_several_rows():
+    """Only the final row of a session takes part in the group statistics; the other rows of the session get its value on
+    their own response tokens. Token-wise estimators see the batch unchanged."""
+    import numpy as np
+    import torch
+
+    from verl_b200 import DataProto
+    from verl_b200.trainer.ppo.v1.utils import (compute_advantage_for_multi_trajectories, has_multi_trajectory_sessions,
+                                                 split_trajectory_key)
+
+    assert split_trajectory_key("a_b_c_3_1") == ("a_b_c", "3", 1)
+    keys = ["p_0_0", "p_0_1", "p_1_0", "q_0_0", "q_1_0", "q_1_1"]
+    assert has_multi_trajectory_sessions(keys) and not has_multi_trajectory_sessions(["p_0_0", "p_1_0"])
+    R = 4
+    mask = torch.tensor([[1, 1, 0, 0], [1, 1, 1, 0], [1, 1, 1, 1], [0, 1, 1, 0], [1, 0, 0, 0], [1, 1, 0, 0]], dtype=torch.float32)
+    # outcome scores sit on the final rows: sessions p/0 -> 1.0, p/1 -> 0.0, q/0 -> 0.5, q/1 -> 2.5; the score on the
+    # non-final rows (p_0_0, q_1_0) must not matter
+    score = torch.zeros(6, R)
+    score[1, 2], score[2, 3], score[3, 2], score[5, 1] = 1.0, 0.0, 0.5, 2.5
+    score[0, 1], score[4, 0] = 9.0, -9.0
+    data = DataProto.from_dict(tensors={"token_level_rewards": score, "response_mask": mask, "responses": torch.zeros(6, R, dtype=torch.int64)},
+                               non_tensors={"uid": np.array(["p", "p", "p", "q", "q", "q"], dtype=object)})
+    out = compute_advantage_for_multi_trajectories(data, keys, "grpo", num_repeat=2, norm_adv_by_std_in_grpo=True)
+    adv = out.batch["advantages"]
+    # group p: scores (1, 0): mean 0.5, unbiased std 0.7071 -> +-0.7071; group q: (0.5, 2.5): mean 1.5, std 1.4142 -> -+0.7071
+    a = 0.5 / (0.5 ** 0.5 + 1e-6)
+    want = torch.tensor([a, a, -a, -a, a, a]).unsqueeze(-1) * mask
+    assert torch.allclose(adv, want, atol=1e-4), adv
+    assert torch.equal(out.batch["returns"], adv)
+    # a token-wise estimator is passed through
+    data2 = DataProto.from_dict(tensors={"token_level_rewards": score.clone(), "response_mask": mask, "values": torch.zeros(6, R),
+                                         "responses": torch.zeros(6, R, dtype=torch.int64)},
+                                non_tensors={"uid": np.array(["p", "p", "p", "q", "q", "q"], dtype=object)})
+    out2 = compute_advantage_for_multi_trajectories(data2, keys, "gae", gamma=1.0, lam=1.0)
+    assert out2.batch["advantages"].shape == (6, R) and float(out2.batch["advantages"][0].abs().sum()) > 0   # row 0's own reward counted
+
+
+def test_sessions_that_return_several_rows_train_through_the_replay_buffer(monkeypatch):
+    """An agent loop that cuts its session into two rows: both are stored (index 0 and 1), the group completes on the last
+    one, and the trainer's batch holds every row with its session's advantage."""
+    monkeypatch.setenv("VERL_ENGINE_DEVICE", "cpu")
+    import copy
+
+    from verl_b200.experimental.agent_loop import register
+    from verl_b200.experimental.agent_loop.single_turn_agent_loop import SingleTurnAgentLoop
+    from verl_b200.trainer.main_ppo import main
+
+    @register("two_piece_agent")
+    class TwoPieces(SingleTurnAgentLoop):
+        async def run(self, sampling_params, **kwargs):
+            whole = await super().run(sampling_params, **kwargs)
+            cut = max(1, len(whole.response_ids) // 2)
+            first = copy.copy(whole)
+            first.response_ids, first.response_mask = whole.response_ids[:cut], whole.response_mask[:cut]
+            first.response_logprobs = None if whole.response_logprobs is None else whole.response_logprobs[:cut]
+            first.reward_score = None
+            second = copy.copy(whole)
+            second.prompt_ids = whole.prompt_ids + whole.response_ids[:cut]
+            second.response_ids, second.response_mask = whole.response_ids[cut:], whole.response_mask[cut:]
+            second.response_logprobs = None if whole.response_logprobs is None else whole.response_logprobs[cut:]
+            return [first, second] if second.response_ids else [first]
+
+    t = main(ARGS + ["trainer.v1.trainer_mode=sync", "trainer.total_training_steps=1", "data.max_prompt_length=32",
+                     "+actor_rollout_ref.rollout.agent.default_agent_loop=two_piece_agent"])
+    b = t.last_batch
+    keys = b.non_tensor_batch["__traj_key__"].tolist()
+    assert len(keys) == 16 and sorted({k.rsplit("_", 1)[1] for k in keys}) == ["0", "1"]     # 4 prompts x 2 sessions x 2 rows
+    adv, m = b.batch["advantages"], b.batch["response_mask"].bool()
+    by_session = {}
+    for i, k in enumerate(keys):
+        v = adv[i][m[i]]
+        assert v.numel() > 0 and bool((v == v[0]).all())
+        by_session.setdefault(k.rsplit("_", 1)[0], []).append(float(v[0]))
+    assert all(len(v) == 2 and abs(v[0] - v[1]) < 1e-6 for v in by_session.values())          # both rows share the session's value
+    assert t.global_steps == 2 and "actor/pg_loss" in t.metrics

@@ -781,11 +781,15 @@ class RayPPOTrainer:
 
                 batch, rc_m = compute_rollout_correction_and_add_to_batch(batch, rc)
                 metrics.update(rc_m)
-            batch = compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
-                                      lam=algo.get("lam", 1.0), num_repeat=self.config.actor_rollout_ref.rollout.n,
-                                      norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo,
-                                      dp=self._dp_view())
+            batch = self._compute_advantage(batch, adv_estimator=algo.adv_estimator, gamma=algo.get("gamma", 1.0),
+                                            lam=algo.get("lam", 1.0), num_repeat=self.config.actor_rollout_ref.rollout.n,
+                                            norm_adv_by_std_in_grpo=algo.get("norm_adv_by_std_in_grpo", True), config=algo,
+                                            dp=self._dp_view())
         return batch
+
+    def _compute_advantage(self, batch: DataProto, **kw) -> DataProto:
+        """Estimator dispatch; the replay-buffer trainers override it for sessions that produced several rows."""
+        return compute_advantage(batch, **kw)
 
     def _fit_update_critic(self, batch: DataProto) -> DataProto:
         if self.use_critic:

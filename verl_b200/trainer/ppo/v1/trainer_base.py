@@ -67,11 +67,18 @@ class AgentLoopWorkerTQ(AgentLoopWorker):
     async def run_session(self, uid: str, session: int, agent_name: str, sampling_params: dict, kwargs: dict,
                           partition_id: str = "train") -> None:
         try:
-            out = await self._run_one(agent_name, sampling_params, kwargs)
-            fields = {"prompt_ids": out.prompt_ids, "response_ids": out.response_ids, "response_mask": out.response_mask,
-                      "response_logprobs": out.response_logprobs, "reward_score": out.reward_score, "num_turns": out.num_turns,
-                      "reward_extra_info": dict(out.extra_fields.get("reward_extra_info", {}) or {}), "output": out}
-            self.rb.add_trajectory(uid, session, 0, fields, self.version_fn(), failed=False, partition_id=partition_id)
+            got = await self._run_one(agent_name, sampling_params, kwargs)
+            # a session may hand back several training rows (index 0, 1, ...); the last one closes the session and carries
+            # its outcome; a session that returns nothing usable counts as failed
+            outs = [o for o in (got if isinstance(got, (list, tuple)) else [got]) if o is not None]
+            if not outs:
+                raise RuntimeError("the agent loop returned no trajectory")
+            for j, out in enumerate(outs):
+                fields = {"prompt_ids": out.prompt_ids, "response_ids": out.response_ids, "response_mask": out.response_mask,
+                          "response_logprobs": out.response_logprobs, "reward_score": out.reward_score, "num_turns": out.num_turns,
+                          "reward_extra_info": dict(out.extra_fields.get("reward_extra_info", {}) or {}), "output": out}
+                self.rb.add_trajectory(uid, session, j, fields, self.version_fn(), failed=False, last=j == len(outs) - 1,
+                                       partition_id=partition_id)
         except asyncio.CancelledError:
             raise
         except Exception as e:  # a failed session still completes its group
@@ -177,16 +184,18 @@ class PPOTrainer(RayPPOTrainer):
     # ------------------------------------------------------------------ consumer
     def _batch_from_meta(self, meta) -> DataProto:
         recs = self.replay_buffer.q.get_data(meta)
-        outs, uids = [], []
+        outs, uids, keys = [], [], []
         for key, r in zip(meta.keys, recs):
             if "output" in r:
                 outs.append(r["output"])
                 uids.append(key.rsplit("_", 2)[0])
+                keys.append(key)
         shell = DataProto.from_dict(tensors={"dummy": torch.zeros(len(outs), 1)}, meta_info={})
         batch = self.worker_tq._postprocess(outs, shell)
         batch.meta_info.pop("timing", None)
         batch.meta_info.pop("reward_extra_keys", None)
         batch.non_tensor_batch["uid"] = np.array(uids, dtype=object)
+        batch.non_tensor_batch["__traj_key__"] = np.array(keys, dtype=object)
         prompts = {u: self.replay_buffer.q.get([u], None, meta.partition_id)[0].get("prompt", {}) for u in set(uids)}
         for k in sorted({k for p in prompts.values() for k in p}):
             if k in batch.non_tensor_batch or k in ("uid",):
@@ -198,6 +207,15 @@ class PPOTrainer(RayPPOTrainer):
             batch.batch["response_mask"] = compute_response_mask(batch)
         batch.meta_info["temperature"] = self.config.actor_rollout_ref.rollout.temperature
         return self._to_device(batch)
+
+    def _compute_advantage(self, batch: DataProto, **kw) -> DataProto:
+        keys = batch.non_tensor_batch.get("__traj_key__")
+        if keys is not None:
+            from .utils import compute_advantage_for_multi_trajectories, has_multi_trajectory_sessions
+
+            if has_multi_trajectory_sessions(keys.tolist()):
+                return compute_advantage_for_multi_trajectories(batch, keys.tolist(), **kw)
+        return super()._compute_advantage(batch, **kw)
 
     def _step_once(self, metrics: dict, timing_raw: dict) -> Optional[DataProto]:
         # train_batch_size counts prompts of the whole job; a controller-replicated rank trains on its share
