@@ -97,6 +97,10 @@ class BaseModelMerger(ABC):
             self._test_state_dict(sd)
         elif self.config.operation == "merge":
             self.save_hf_model_and_tokenizer(sd)
+            if self.config.hf_model_config_path and os.path.isdir(self.config.hf_model_config_path):
+                from .output_validation import validate_hf_model_output
+
+                validate_hf_model_output(self.config.target_dir)   # a half-written output fails here, not at its first load
         else:
             raise ValueError(f"Unknown operation: {self.config.operation}")
 
