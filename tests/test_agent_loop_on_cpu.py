@@ -212,3 +212,50 @@ def test_expert_choices_of_the_rollout_land_on_the_padded_positions():
     assert torch.equal(out.batch["prompts"][1], torch.tensor([3, 4, 5, 6])) and torch.equal(r[1, 0:4], rec(6, 200)[2:6])
     assert int(r[2].abs().sum()) == 0
     assert "routed_experts" not in w._postprocess(outs[2:], DataProto(meta_info={"pad_token_id": 0})).batch.keys()
+
+
+from verl_b200.experimental.agent_loop.single_turn_agent_loop import SingleTurnAgentLoop  # noqa: E402
+
+
+class PrefixedLoop(SingleTurnAgentLoop):
+    """Declared through a configuration file below; defined at module level so the dotted path resolves."""
+
+    def __init__(self, *a, marker=None, **k):
+        super().__init__(*a, **k)
+        self.marker = marker
+
+    async def run(self, sampling_params, **kwargs):
+        out = await super().run(sampling_params, **kwargs)
+        out.extra_fields["marker"] = self.marker
+        return out
+
+
+def test_agent_loops_declared_in_a_configuration_file(tmp_path, monkeypatch):
+    from verl_b200.experimental.agent_loop import agent_loop as al
+    from verl_b200.experimental.agent_loop.utils import (build_gpt_oss_tool_response_text, load_agent_loop_configs,
+                                                         resolve_config_path)
+
+    (tmp_path / "loops.yaml").write_text("- name: prefixed\n  _target_: tests.test_agent_loop_on_cpu.PrefixedLoop\n  marker: 7\n")
+    monkeypatch.chdir(tmp_path)
+    assert resolve_config_path("loops.yaml") == str(tmp_path / "loops.yaml")
+    assert load_agent_loop_configs("loops.yaml")["prefixed"][1] == {"marker": 7}
+    import pytest
+
+    with pytest.raises(FileNotFoundError):
+        resolve_config_path("../outside.yaml")
+    config = _cfg()
+    config.actor_rollout_ref.rollout.agent["agent_loop_config_path"] = "loops.yaml"
+    config.actor_rollout_ref.rollout.agent["default_agent_loop"] = "prefixed"
+
+    async def go():
+        mgr = await LLMServerManager.create(config.actor_rollout_ref.rollout, engines=_engines(1), model_config=None)
+        alm = AgentLoopManager(config, mgr)
+        ids = torch.randint(3, 500, (2, 8))
+        return await alm.generate_sequences_async(DataProto.from_dict(tensors={"input_ids": ids, "attention_mask": torch.ones(2, 8, dtype=torch.int64)},
+                                                                      meta_info={"temperature": 1.0}))
+
+    out = asyncio.run(go())
+    assert out.non_tensor_batch["marker"].tolist() == [7, 7] and al._AGENT_LOOP_KWARGS["prefixed"] == {"marker": 7}
+    text = build_gpt_oss_tool_response_text([{"content": "4"}, {"content": "ok"}], ["add", "ping"])
+    assert text == ("<|start|>functions.add to=assistant<|channel|>commentary<|message|>4<|end|>"
+                    "<|start|>functions.ping to=assistant<|channel|>commentary<|message|>ok<|end|><|start|>assistant")
