@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Optional
 
-__all__ = ["RolloutMetricsExporter"]
+__all__ = ["RolloutMetricsExporter", "prometheus_scrape_config", "update_prometheus_config"]
 
 
 class RolloutMetricsExporter:
@@ -46,3 +46,52 @@ class RolloutMetricsExporter:
                 "kv_blocks_total": total, "kv_usage": (1.0 - free / total) if total else 0.0}
         for k, v in vals.items():
             self.gauges[k].labels(self.replica).set(v)
+
+
+def prometheus_scrape_config(server_addresses: list, scrape_interval: str = "10s") -> dict:
+    """The Prometheus configuration that scrapes the given ``host:port`` exporters as job ``rollout``."""
+    return {"global": {"scrape_interval": scrape_interval, "evaluation_interval": scrape_interval},
+            "scrape_configs": [{"job_name": "rollout", "static_configs": [{"targets": [str(a) for a in server_addresses]}]}]}
+
+
+def update_prometheus_config(config, server_addresses: list, rollout_name: Optional[str] = None, reload: bool = True,
+                             post=None) -> bool:
+    """Write the scrape configuration for the rollout exporters to ``config.file`` and ask a Prometheus server on this host
+    (``config.port``) to reload it. Returns whether the file was written; a failed reload (no server on this host) is not
+    an error, as on the nodes of a job that do not run Prometheus. ``post`` replaces the HTTP call in tests.
+
+    Parity target: ``verl/workers/rollout/utils.py:141-223`` (which also copies the file to every node through Ray; here
+    each host that calls this writes its own copy)."""
+    import logging
+    import os
+
+    import yaml
+
+    log = logging.getLogger(__name__)
+    get = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
+    if not server_addresses:
+        log.warning("No server addresses available to update Prometheus config")
+        return False
+    path = get("file")
+    if not path:
+        return False
+    try:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "w") as f:
+            yaml.dump(prometheus_scrape_config(server_addresses), f, default_flow_style=False, indent=2)
+        print(f"Updated Prometheus configuration at {path} with {len(server_addresses)} {(rollout_name or 'rollout').upper()} servers")
+    except OSError as e:
+        log.error("Failed to update Prometheus configuration: %s", e)
+        return False
+    if reload and get("port"):
+        url = f"http://127.0.0.1:{int(get('port'))}/-/reload"
+        try:
+            if post is not None:
+                post(url)
+            else:
+                import urllib.request
+
+                urllib.request.urlopen(urllib.request.Request(url, method="POST"), timeout=5).close()
+        except Exception:
+            pass  # no Prometheus server on this host
+    return True
