@@ -260,3 +260,29 @@ def test_sessions_that_return_several_rows_train_through_the_replay_buffer(monke
         by_session.setdefault(k.rsplit("_", 1)[0], []).append(float(v[0]))
     assert all(len(v) == 2 and abs(v[0] - v[1]) < 1e-6 for v in by_session.values())          # both rows share the session's value
     assert t.global_steps == 2 and "actor/pg_loss" in t.metrics
+
+
+def test_rounds_of_one_step_are_reduced_by_name():
+    import torch
+
+    from verl_b200.trainer.ppo.v1.utils import StepMetricsAggregator as A
+
+    assert A.rule("actor/lr") == "last" and A.rule("timing_s/gen") == "sum" and A.rule("timing_per_token_ms/adv") == "sum"
+    assert A.rule("training/off_policy/evicted_samples") == "sum" and A.rule("response_length/max") == "max"
+    assert A.rule("critic/score/mean") == "weighted" and A.rule("actor/pg_loss") == "weighted" and A.rule("training/global_step") == "last"
+    a = A()
+    assert a.get_aggregated_metrics() == {}
+    a.add_step_metrics({"actor/pg_loss": 1.0, "actor/lr": 1e-3, "timing_s/gen": 2.0, "response_length/max": 10, "response_length/min": 3,
+                        "global_seqlen/max": 90, "global_seqlen/min": 30, "global_seqlen/minmax_diff": 60,
+                        "training/off_policy/evicted_samples": 2, "training/off_policy/evicted_samples_staleness/mean": 3.0,
+                        "hist": {"0.0": 2, "1.0": 1}, "flag": True, "t": torch.tensor(4.0)}, sample_count=8)
+    a.add_step_metrics({"actor/pg_loss": 4.0, "actor/lr": 5e-4, "timing_s/gen": 3.0, "response_length/max": 7, "response_length/min": 1,
+                        "global_seqlen/max": 80, "global_seqlen/min": 20, "global_seqlen/minmax_diff": 60,
+                        "training/off_policy/evicted_samples": 6, "training/off_policy/evicted_samples_staleness/mean": 5.0,
+                        "hist": {"1.0": 4}, "t": torch.tensor(8.0)}, sample_count=24)
+    out = a.get_aggregated_metrics()
+    assert out["actor/pg_loss"] == pytest.approx((1.0 * 8 + 4.0 * 24) / 32) and out["actor/lr"] == 5e-4 and out["timing_s/gen"] == 5.0
+    assert out["response_length/max"] == 10 and out["response_length/min"] == 1 and out["global_seqlen/minmax_diff"] == 70
+    assert out["training/off_policy/evicted_samples"] == 8
+    assert out["training/off_policy/evicted_samples_staleness/mean"] == pytest.approx((3.0 * 2 + 5.0 * 6) / 8)   # weighted by evictions
+    assert out["hist"] == {"0.0": 2, "1.0": 5} and "flag" not in out and out["t"] == pytest.approx((4 * 8 + 8 * 24) / 32)

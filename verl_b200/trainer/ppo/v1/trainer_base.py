@@ -240,10 +240,23 @@ class PPOTrainer(RayPPOTrainer):
         batch = None
         with marked_timer("step", timing_raw):
             self.on_step_begin()
-            for _ in range(max(1, int(self._tc("parameter_sync_step", 1)))):
+            rounds = max(1, int(self._tc("parameter_sync_step", 1)))
+            if rounds == 1:
                 batch = self._step_once(metrics, timing_raw)
                 if batch is None:
                     return None
+            else:
+                # several optimizer rounds per weight hand-over: the step's record reduces the rounds' records by name
+                from .utils import StepMetricsAggregator
+
+                agg = StepMetricsAggregator()
+                for _ in range(rounds):
+                    m: dict[str, Any] = {}
+                    batch = self._step_once(m, timing_raw)
+                    if batch is None:
+                        return None
+                    agg.add_step_metrics(m, len(batch))
+                metrics.update(agg.get_aggregated_metrics())
             self.on_step_end(batch, metrics, timing_raw)
         return self.finish_step(batch, metrics, timing_raw)
 
