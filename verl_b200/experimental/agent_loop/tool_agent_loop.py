@@ -41,11 +41,13 @@ class ToolAgentLoop(AgentLoopBase):
         self.max_parallel_calls = int(mt.get("max_parallel_calls", 1))
         self.max_tool_response_length = int(mt.get("max_tool_response_length", 256))
         self.truncate_side = mt.get("tool_response_truncate_side", "middle")
-        path = mt.get("tool_config_path")
+        path, fn_path = mt.get("tool_config_path"), mt.get("function_tool_path")
         if tools is None:
-            if path not in self._tools_cache:
-                self._tools_cache[path] = {t.name: t for t in initialize_tools_from_config(path)}
-            self.tools = self._tools_cache[path]
+            if (path, fn_path) not in self._tools_cache:
+                from ...tools.registry import load_all_tools
+
+                self._tools_cache[(path, fn_path)] = {t.name: t for t in load_all_tools(path, fn_path)}
+            self.tools = self._tools_cache[(path, fn_path)]
         else:
             self.tools = {t.name: t for t in tools}
         self.tool_schemas = [t.tool_schema.model_dump(exclude_unset=True, exclude_none=True) for t in self.tools.values()]
