@@ -19,7 +19,7 @@ import os
 import torch
 import torch.nn.functional as F
 
-from . import native
+from . import audit, native
 
 __all__ = [
     "gemm",
@@ -237,6 +237,7 @@ def rope_table(max_pos: int, head_dim: int, theta: float, device, scaling: Optio
 def apply_rope_(x: torch.Tensor, positions: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
                 backward: bool = False) -> torch.Tensor:
     """In-place rotation of ``x`` [T, heads, hd] (a strided view is fine)."""
+    audit.check_index("apply_rope_", "positions", positions, cos_t.shape[0])
     if x.is_cuda:
         _ops().rope_(x, positions.to(torch.int32), cos_t, sin_t, backward)
         return x
@@ -286,6 +287,7 @@ def swiglu_bwd(dout: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------------------------- embedding
 def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    audit.check_index("embedding", "ids", ids, weight.shape[0])
     if weight.is_cuda:
         return _ops().embedding_fwd(ids.reshape(-1).contiguous(), weight)
     return F.embedding(ids.reshape(-1), weight)
@@ -295,6 +297,7 @@ DETERMINISTIC_ATTENTION = False  # set by enable_full_determinism(): order-stabl
 
 
 def embedding_bwd_(ids: torch.Tensor, dout: torch.Tensor, dweight: torch.Tensor) -> None:
+    audit.check_index("embedding_bwd_", "ids", ids, dweight.shape[0])
     if dout.is_cuda and DETERMINISTIC_ATTENTION:
         # deterministic mode: the kernel adds repeated token ids with atomics; the sorted accumulation is order-stable
         dweight.index_add_(0, ids.reshape(-1), dout.to(dweight.dtype))
@@ -321,6 +324,7 @@ def lmhead_logprob_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: t
                            temperature: float = 1.0):
     """(logprob, entropy, lse), each fp32 [T], of ``labels`` under ``softmax(hidden @ weight^T / T)``."""
     inv_temp = 1.0 / max(float(temperature), 1e-8)
+    audit.check_index("lmhead_logprob_entropy", "labels", labels, weight.shape[0])
     if hidden.is_cuda:
         return _ops().lmhead_fwd(hidden, weight, labels.contiguous(), inv_temp)
     return _torch_logprob_entropy(hidden, weight, labels, inv_temp)
@@ -525,6 +529,7 @@ def attention_with_prefix(q, k, v, k_prefix, v_prefix, cu_seqlens, prefix_lens, 
 
 
 def kv_append_(k, v, slots, k_cache, v_cache) -> None:
+    audit.check_index("kv_append_", "slots", slots, k_cache.numel() // (k_cache.shape[-2] * k_cache.shape[-1]), skip_negative=True)
     if k.is_cuda:
         _ops().kv_append_(k, v, slots, k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1]),
                           v_cache.view(-1, v_cache.shape[-2], v_cache.shape[-1]))
@@ -541,6 +546,10 @@ def rope_kv_append_(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin
     """Decode-step fusion: rotate the q and k heads of ``qkv`` [T, (nh + 2 nkv) * hd] in place and append the rotated k
     and v rows to the paged caches at ``slots`` (negative: skip the append). One kernel on a GPU; the same three steps
     through the separate ops elsewhere."""
+    if audit.enabled():
+        audit.check_index("rope_kv_append_", "pos", pos, cos.shape[0])
+        audit.check_index("rope_kv_append_", "slots", slots, k_cache.numel() // (nkv * hd), skip_negative=True)
+        audit.check_aligned("rope_kv_append_", "qkv", qkv)
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
         _ops().rope_kv_append_(qkv, pos, cos, sin, slots, k_cache, v_cache, int(nh), int(nkv), int(hd))
         return
@@ -560,6 +569,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, ctx_len, scale: Opt
     that share their leading pages (the samples of one prompt) have those pages read once per group by a kernel that
     holds every member's query heads, and only the rest of each context per sequence; same result as without."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    audit.check_paged_cache("paged_decode_attention", block_table, ctx_len, k_cache.shape[0], k_cache.shape[1])
     if q.is_cuda:
         if groups is not None:
             members, grp_pages, skip, ws, psplit, nsplit = groups
