@@ -45,9 +45,15 @@ def scope(on: bool = True):
         _ON = old
 
 
+def _capturing(t: torch.Tensor) -> bool:
+    """A check reads its verdict back to the host, which a stream that is being captured into a CUDA graph does not allow:
+    the operators of a captured decode step are audited in the eager warm-up steps that precede the capture, not inside it."""
+    return t.is_cuda and torch.cuda.is_current_stream_capturing()
+
+
 def check_index(op: str, name: str, t: Optional[torch.Tensor], hi: int, lo: int = 0, skip_negative: bool = False) -> None:
     """Every element of ``t`` lies in ``[lo, hi)``; with ``skip_negative`` negative values mean "no entry" and pass."""
-    if not _ON or t is None or t.numel() == 0:
+    if not _ON or t is None or t.numel() == 0 or _capturing(t):
         return
     if t.is_floating_point():
         raise AuditError(f"{op}: {name} must be an integer tensor, got {t.dtype}")
@@ -71,7 +77,7 @@ def check_aligned(op: str, name: str, t: Optional[torch.Tensor], nbytes: int = 1
 
 def check_paged_cache(op: str, block_table: torch.Tensor, ctx_len: torch.Tensor, num_blocks: int, block_size: int) -> None:
     """Block numbers that a sequence's context actually reaches are valid blocks, and the context fits its table row."""
-    if not _ON or block_table.numel() == 0:
+    if not _ON or block_table.numel() == 0 or _capturing(block_table):
         return
     max_ctx = block_table.shape[1] * block_size
     check_index(op, "ctx_len", ctx_len, max_ctx + 1)
