@@ -169,3 +169,21 @@ def test_linear_cross_entropy_autograd_matches_plain_torch():
     assert torch.allclose(m_lp, lp_r.mean(), atol=1e-5)
     lp2, ent2 = FusedLinearForPPO()(h.detach(), w.detach(), y, 0.7)
     assert torch.allclose(lp2, lp_r, atol=1e-5) and lp2.shape == (2, 5)
+
+
+def test_reward_config_dataclasses_check_the_manager_name():
+    import pytest
+
+    from verl_b200.workers.config.reward import RewardConfig, RewardManagerConfig, SandboxFusionConfig
+
+    c = RewardConfig()
+    assert c.reward_manager.name == "naive" and c.sandbox_fusion.max_concurrent == 64 and not c.reward_model.enable
+    assert RewardManagerConfig(name="dapo").name == "dapo" and RewardManagerConfig(name="rate_limited").source == "register"
+    with pytest.raises(ValueError, match="not registered"):
+        RewardManagerConfig(name="no_such_manager")
+    with pytest.raises(ValueError, match="module.path"):
+        RewardManagerConfig(source="importlib", name="Mine")
+    assert RewardManagerConfig(source="importlib", name="Mine", module={"path": "/x/y.py"}).module["path"] == "/x/y.py"
+    with pytest.raises(ValueError, match="unknown reward manager source"):
+        RewardManagerConfig(source="http")
+    assert SandboxFusionConfig(url="http://s").url == "http://s"

@@ -286,3 +286,41 @@ def test_rounds_of_one_step_are_reduced_by_name():
     assert out["training/off_policy/evicted_samples"] == 8
     assert out["training/off_policy/evicted_samples_staleness/mean"] == pytest.approx((3.0 * 2 + 5.0 * 6) / 8)   # weighted by evictions
     assert out["hist"] == {"0.0": 2, "1.0": 5} and "flag" not in out and out["t"] == pytest.approx((4 * 8 + 8 * 24) / 32)
+
+
+def test_adaptive_switch_threshold_and_benefit_rule():
+    from verl_b200.trainer.config.config import BaseModelConfig, HybridRolloutSwitchConfig, ModuleConfig, ProfileConfig
+    from verl_b200.trainer.ppo.v1.hybrid_switch import AdaptiveSwitchThreshold, SwitchCostWindow, switch_is_worth_it
+
+    with pytest.raises(ValueError):
+        HybridRolloutSwitchConfig(switch_threshold_ratio=0.0)
+    with pytest.raises(ValueError):
+        HybridRolloutSwitchConfig(switch_cost_window_size=0)
+    assert ProfileConfig().step_start == -1 and ModuleConfig().path is None and BaseModelConfig().lora == {}
+    cfg = HybridRolloutSwitchConfig(enable_switch=True, switch_threshold_ratio=0.4, switch_threshold_step_up=0.05,
+                                    switch_threshold_step_down=0.03, switch_threshold_release_steps=2)
+    t = AdaptiveSwitchThreshold(cfg, train_batch_size=64, parameter_sync_step=4)
+    assert t.threshold() == 26                       # round(0.4 * 64), above one mini-batch of 16
+    assert t.adapt(True) == pytest.approx(0.4)       # one idle step: not yet
+    assert t.adapt(True) == pytest.approx(0.45)      # two in a row: up
+    assert t.adapt(True) == pytest.approx(0.50) and t.threshold() == 32
+    assert t.adapt(False) == pytest.approx(0.50)     # one calm step resets the idle count, no move yet
+    assert t.adapt(True) == pytest.approx(0.50)      # ... and an idle step resets the calm count
+    assert t.adapt(False) == pytest.approx(0.50) and t.adapt(False) == pytest.approx(0.47)
+    for _ in range(40):
+        t.adapt(False)
+    assert t.ratio == pytest.approx(0.25) and t.threshold() == 16     # floor: one round's share of the batch
+    for _ in range(40):
+        t.adapt(True)
+    assert t.ratio == 1.0 and t.threshold() == 64
+    fixed = AdaptiveSwitchThreshold(HybridRolloutSwitchConfig(adaptive_switch_threshold=False), 64)
+    assert fixed.adapt(True) == fixed.adapt(True) == 0.4
+    w = SwitchCostWindow(size=2)
+    assert w.effective_cost() is None
+    for c in (4.0, 2.0, 1.0):
+        w.to_rollout.append(c)
+    w.to_trainer.append(3.0)
+    assert w.effective_cost() == pytest.approx(1.5 + 3.0)            # the window keeps the last two
+    assert not switch_is_worth_it(0, 1.0, 2.0, 1.0)
+    assert switch_is_worth_it(10, None, 2.0, 1.0) and switch_is_worth_it(10, 1.0, 2.0, None)
+    assert switch_is_worth_it(10, 1.0, 2.0, 4.9) and not switch_is_worth_it(10, 1.0, 2.0, 5.1)     # saves 10 * 1 * (1 - 1/2) = 5 s

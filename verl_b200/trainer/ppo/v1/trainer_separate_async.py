@@ -208,6 +208,18 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self.switch = SwitchController(enabled=bool(self._tc("hybrid_switch", True)) and self.topo.R > 0)
         self._runner: Optional[_GroupRunner] = None
         self._wait_started: Optional[float] = None
+        # how many prompt groups must be ready before lent GPUs go back to training (trainer.v1.hybrid_rollout.*); it adapts
+        # step by step to whether the trainer still had to wait, and is reported with the step's metrics
+        from ...config.config import HybridRolloutSwitchConfig
+        from .hybrid_switch import AdaptiveSwitchThreshold, SwitchCostWindow
+
+        hc = self._tc("hybrid_rollout", None) or {}
+        known = HybridRolloutSwitchConfig.__dataclass_fields__
+        self.hybrid_rollout_config = HybridRolloutSwitchConfig(**{k: v for k, v in dict(hc).items() if k in known})
+        self.switch_threshold = AdaptiveSwitchThreshold(self.hybrid_rollout_config, int(self.config.data.train_batch_size),
+                                                        int(self._tc("parameter_sync_step", 1) or 1))
+        self.switch_costs = SwitchCostWindow(self.hybrid_rollout_config.switch_cost_window_size)
+        self._last_wait_s = 0.0
 
     # ---- set-up
     def on_init_end(self) -> None:
@@ -282,6 +294,7 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self._each_server("resume_generation")
         self.mode = HybridEngineMode.ROLLOUT
         self._switch_t0 = t0
+        self.switch_costs.to_rollout.append(time.time() - t0)
 
     def switch_to_trainer(self) -> None:
         if self.mode is not HybridEngineMode.ROLLOUT:
@@ -292,6 +305,7 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self._each_server("sleep")
         self.mode = HybridEngineMode.TRAINER
         self.switch.record_switch_cost((time.time() - t0) + 0.0)
+        self.switch_costs.to_trainer.append(time.time() - t0)
 
     # ---- hooks
     def on_train_begin(self) -> None:
@@ -306,7 +320,8 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         self._top_up()
 
     def on_sample_end(self) -> None:
-        self.switch.record_wait(time.time() - (self._wait_started or time.time()))
+        self._last_wait_s = time.time() - (self._wait_started or time.time())
+        self.switch.record_wait(self._last_wait_s)
         self._wait_started = None
         if self.topo.R == 0:
             self._each_server("abort_all_requests")
@@ -326,6 +341,11 @@ class PPOTrainerSeparateAsync(PPOTrainer):
         metrics["hybrid/num_switches"] = self.switch.num_switches
         metrics["hybrid/avg_wait_s"] = self.switch.avg_wait_s
         metrics["hybrid/switch_cost_s"] = self.switch.switch_cost_s
+        had_idle = self._last_wait_s > float(getattr(self.replay_buffer, "poll_interval", 0.0) or 0.0) + 1e-3
+        metrics["separate_async/switch/threshold_ratio"] = self.switch_threshold.ratio
+        metrics["separate_async/switch/idle"] = float(had_idle)
+        self.switch_threshold.adapt(had_idle)
+        metrics["separate_async/switch/threshold"] = float(self.switch_threshold.threshold())
 
     def shutdown(self) -> None:
         if self.topo.R > 0:
