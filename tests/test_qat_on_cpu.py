@@ -57,3 +57,41 @@ def test_qat_engine_keeps_working_weights_quantised_and_masters_full_precision()
     o = eng.params.offsets[names[0]]
     m = eng.master[o : o + eng.params.views[names[0]].numel()]
     assert not torch.equal(m, eng.params.views[names[0]].reshape(-1).float())  # the master copy is not quantised
+
+
+def test_packed_nvfp4_export_round_trips_to_the_fake_quantised_weight():
+    import torch
+
+    from verl_b200.models import FlatParams, get_preset
+    from verl_b200.utils.qat.core import QATConfig, apply_qat_to_params, nvfp4_fake_quantize, qat_target_names
+    from verl_b200.utils.qat.exporter import QATWeightExporter, pack_nvfp4, unpack_nvfp4
+
+    torch.manual_seed(0)
+    w = torch.randn(8, 64) * 0.3
+    w[2, 16:32] = 0.0                                           # an all-zero block
+    w[5, 3] = -0.0
+    fq = nvfp4_fake_quantize(w)
+    packed, scale, gs = pack_nvfp4(w)
+    assert packed.dtype == torch.uint8 and packed.shape == (8, 32) and scale.dtype == torch.float8_e4m3fn and scale.shape == (8, 4)
+    assert torch.equal(unpack_nvfp4(packed, scale, gs, dtype=torch.float32), fq)        # same grid, same scales: bit for bit
+    p2, s2, g2 = pack_nvfp4(fq)                                                          # a weight already on the grid
+    assert torch.equal(unpack_nvfp4(p2, s2, g2, dtype=torch.float32), fq)
+    lo, hi = packed[0, 0] & 0xF, packed[0, 0] >> 4                                       # even column low nibble, odd column high
+    vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    sc = scale[0, 0].float() * gs[0]
+    for code, col in ((lo, 0), (hi, 1)):
+        v = vals[int(code) & 7] * (-1 if int(code) & 8 else 1) * sc
+        assert abs(float(v) - float(fq[0, col])) < 1e-7
+    # exporter over a model's parameters
+    cfg = QATConfig(enable=True)
+    params = FlatParams(get_preset("tiny-qwen2"), dtype=torch.float32)
+    params.init_weights(seed=1)
+    apply_qat_to_params(params, cfg)
+    targets = qat_target_names(params, cfg)
+    out = dict(QATWeightExporter(cfg).export(params))
+    assert targets and all(f"{n}_packed" in out and f"{n}_scale" in out and f"{n}_global_scale" in out and n not in out for n in targets)
+    assert any(k.endswith("norm.weight") for k in out) and "embed_tokens.weight" in out      # passed through
+    n = targets[0]
+    back = unpack_nvfp4(out[f"{n}_packed"], out[f"{n}_scale"], out[f"{n}_global_scale"], dtype=torch.float32)
+    assert torch.equal(back, params.views[n].view(-1, params.views[n].shape[-1]))
+    assert QATWeightExporter(cfg).quantization_config()["group_size"] == 16
